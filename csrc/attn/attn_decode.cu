@@ -1,0 +1,307 @@
+// K4: paged decode attention (one query token per sequence), split-KV, GQA-aware.
+//
+// One CTA handles (sequence, kv head, split).  All G = Hq/Hkv query heads that share the kv head
+// are processed together, so each K/V byte is fetched from HBM exactly once per step.  A group of
+// D/8 lanes owns one token: each lane loads one 16-byte chunk of the K row, partial dots are
+// reduced with xor-shuffles, and the same lanes own the matching 16-byte chunk of the output
+// accumulator for the P*V pass.  Four tokens per lane group are in flight per iteration and the
+// online-softmax rescale runs once per four tokens.  Partial (O, lse) of each split go to a
+// scratch buffer and a second kernel merges them.  Sliding window, ALiBi and "suffix only"
+// (kv_start, for cascade attention after a shared radix prefix) are predicates on the kv index.
+// Block-table entries are bounds-checked; a bad entry sets the error word and is masked.
+//
+// Replaces in the reference: the cached attention path of LlamaAttention::forward_with_cache
+// (crates/runtime/src/models_v2/llama.rs:1027-1156) where q_len == 1.
+#include "../common/ptx.cuh"
+#include "../include/unillm_b200.h"
+#include <math_constants.h>
+
+namespace ub {
+
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+
+template <int D, int G>
+__global__ void __launch_bounds__(128) attn_decode_kernel(const UbAttnArgs a, const int gchunks) {
+  constexpr int LPT = D / 8;        // lanes per token
+  constexpr int TPW = 32 / LPT;     // tokens per warp iteration
+  constexpr int UN = 4;             // tokens in flight per lane group
+  const int seq = blockIdx.x;
+  const int kvh = blockIdx.y / gchunks;
+  const int gc = blockIdx.y % gchunks;
+  const int split = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int grp = lane / LPT, chunk = lane % LPT;
+  const int Gtot = a.Hq / a.Hkv;
+  const int h0 = kvh * Gtot + gc * G;     // first query head of this CTA
+  const int gn = min(G, Gtot - gc * G);   // valid heads in this chunk
+
+  __shared__ float q_s[G][D];
+  __shared__ float red_o[4][G][D];
+  __shared__ float red_ml[4][G][2];
+
+  const int kv_len = a.seq_lens[seq];
+  const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(a.q) + (long long)seq * a.q_stride;
+  for (int i = threadIdx.x; i < G * D; i += 128) {
+    const int g = i / D, d = i % D;
+    q_s[g][d] = g < gn ? __bfloat162float(qp[(long long)(h0 + g) * D + d]) * a.scale * LOG2E : 0.f;
+  }
+  __syncthreads();
+
+  int lo = a.kv_start;
+  if (a.window > 0) lo = max(lo, kv_len - a.window);
+  lo = max(lo, 0);
+  const int span = max(kv_len - lo, 0);
+  int per = (span + a.splits - 1) / a.splits;
+  per = (per + a.block_size - 1) / a.block_size * a.block_size;
+  const int kv_lo = lo + split * per;
+  const int kv_hi = min(kv_len, kv_lo + per);
+
+  float m[G], l[G], acc[G][8];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -CUDART_INF_F; l[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
+  }
+  float slope[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+    slope[g] = (a.alibi_slopes != nullptr && g < gn) ? a.alibi_slopes[h0 + g] * LOG2E : 0.f;
+
+  const int* bt = a.block_tables + (long long)seq * a.max_blocks_per_seq;
+  const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(a.k_cache);
+  const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(a.v_cache);
+
+  for (int base = kv_lo + warp * (TPW * UN); base < kv_hi; base += 4 * TPW * UN) {
+    long long off[UN];
+    bool ok[UN];
+    uint4 kk[UN];
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int pos = base + u * TPW + grp;
+      ok[u] = pos < kv_hi;
+      off[u] = 0;
+      if (ok[u]) {
+        const int bi = pos / a.block_size;
+        int blk = bi < a.max_blocks_per_seq ? bt[bi] : -1;
+        if (blk < 0 || blk >= a.num_blocks) {
+          set_err(a.err, ERR_BOUNDS, seq);
+          ok[u] = false;
+        } else {
+          off[u] = (((long long)blk * a.Hkv + kvh) * a.block_size + (pos % a.block_size)) * D + chunk * 8;
+        }
+      }
+      kk[u] = ok[u] ? *reinterpret_cast<const uint4*>(kc + off[u]) : make_uint4(0, 0, 0, 0);
+    }
+    float s[UN][G];
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(&kk[u]);
+      float kf[8];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { kf[2 * e] = bf16_lo(w[e]); kf[2 * e + 1] = bf16_hi(w[e]); }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float d = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) d += q_s[g][chunk * 8 + e] * kf[e];
+        s[u][g] = d;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UN; ++u)
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int o = LPT / 2; o > 0; o >>= 1) s[u][g] += __shfl_xor_sync(0xffffffffu, s[u][g], o);
+        const int pos = base + u * TPW + grp;
+        s[u][g] = ok[u] ? s[u][g] + slope[g] * (float)(pos - (kv_len - 1)) : -CUDART_INF_F;
+      }
+    // V loads issued before the softmax math so they overlap it
+    uint4 vv[UN];
+#pragma unroll
+    for (int u = 0; u < UN; ++u)
+      vv[u] = ok[u] ? *reinterpret_cast<const uint4*>(vc + off[u]) : make_uint4(0, 0, 0, 0);
+    float p[UN][G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float mx = m[g];
+#pragma unroll
+      for (int u = 0; u < UN; ++u) mx = fmaxf(mx, s[u][g]);
+      const float alpha = (mx == -CUDART_INF_F) ? 1.f : exp2f(m[g] - mx);
+      float ps = 0.f;
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        p[u][g] = (s[u][g] == -CUDART_INF_F) ? 0.f : exp2f(s[u][g] - mx);
+        ps += p[u][g];
+      }
+      l[g] = l[g] * alpha + ps;
+      m[g] = mx;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[g][e] *= alpha;
+    }
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(&vv[u]);
+      float vf[8];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { vf[2 * e] = bf16_lo(w[e]); vf[2 * e + 1] = bf16_hi(w[e]); }
+#pragma unroll
+      for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[g][e] += p[u][g] * vf[e];
+    }
+  }
+
+  // merge the token groups inside the warp (lanes that own the same chunk)
+#pragma unroll
+  for (int o = LPT; o < 32; o <<= 1) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m[g], o);
+      const float l2 = __shfl_xor_sync(0xffffffffu, l[g], o);
+      const float mx = fmaxf(m[g], m2);
+      const float s1 = (m[g] == -CUDART_INF_F) ? 0.f : exp2f(m[g] - mx);
+      const float s2 = (m2 == -CUDART_INF_F) ? 0.f : exp2f(m2 - mx);
+      l[g] = l[g] * s1 + l2 * s2;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float a2 = __shfl_xor_sync(0xffffffffu, acc[g][e], o);
+        acc[g][e] = acc[g][e] * s1 + a2 * s2;
+      }
+      m[g] = mx;
+    }
+  }
+  if (grp == 0) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) red_o[warp][g][chunk * 8 + e] = acc[g][e];
+      if (chunk == 0) { red_ml[warp][g][0] = m[g]; red_ml[warp][g][1] = l[g]; }
+    }
+  }
+  __syncthreads();
+  // merge the 4 warps; thread i handles output elements i, i+128, ...
+  for (int i = threadIdx.x; i < gn * D; i += 128) {
+    const int g = i / D, d = i % D;
+    float mx = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mx = fmaxf(mx, red_ml[w][g][0]);
+    float lt = 0.f, o = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float sc = (red_ml[w][g][0] == -CUDART_INF_F) ? 0.f : exp2f(red_ml[w][g][0] - mx);
+      lt += red_ml[w][g][1] * sc;
+      o += red_o[w][g][d] * sc;
+    }
+    const float inv = lt > 0.f ? 1.f / lt : 0.f;
+    const float lse = lt > 0.f ? (mx + log2f(lt)) * LN2 : -CUDART_INF_F;
+    const int h = h0 + g;
+    if (a.splits == 1) {
+      reinterpret_cast<__nv_bfloat16*>(a.out)[(long long)seq * a.o_stride + (long long)h * D + d] =
+          __float2bfloat16(o * inv);
+      if (d == 0 && a.lse != nullptr) a.lse[(long long)seq * a.Hq + h] = lse;
+    } else {
+      float* sp = a.scratch + (((long long)seq * a.Hq + h) * a.splits + split) * (D + 2);
+      sp[d] = o * inv;
+      if (d == 0) sp[D] = lse;
+    }
+  }
+}
+
+// Merge the split partials: out = sum_i O_i * exp(lse_i - lse_max) / sum_i exp(lse_i - lse_max).
+__global__ void attn_split_merge_kernel(const float* scratch, __nv_bfloat16* out, float* lse_out, int Hq, int D,
+                                        int splits, long long o_stride) {
+  const int seq = blockIdx.x, h = blockIdx.y;
+  const float* sp = scratch + ((long long)seq * Hq + h) * splits * (D + 2);
+  float mx = -CUDART_INF_F;
+  for (int i = 0; i < splits; ++i) mx = fmaxf(mx, sp[i * (D + 2) + D]);
+  float den = 0.f;
+  for (int i = 0; i < splits; ++i) {
+    const float ls = sp[i * (D + 2) + D];
+    den += (ls == -CUDART_INF_F) ? 0.f : __expf(ls - mx);
+  }
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float o = 0.f;
+    for (int i = 0; i < splits; ++i) {
+      const float ls = sp[i * (D + 2) + D];
+      const float w = (ls == -CUDART_INF_F) ? 0.f : __expf(ls - mx);
+      o += sp[i * (D + 2) + d] * w;
+    }
+    out[(long long)seq * o_stride + (long long)h * D + d] = __float2bfloat16(den > 0.f ? o / den : 0.f);
+  }
+  if (threadIdx.x == 0 && lse_out != nullptr)
+    lse_out[(long long)seq * Hq + h] = den > 0.f ? mx + __logf(den) : -CUDART_INF_F;
+}
+
+// Merge two independently computed attention partials over disjoint key sets.
+__global__ void attn_merge2_kernel(const __nv_bfloat16* oa, const float* la, const __nv_bfloat16* ob, const float* lb,
+                                   __nv_bfloat16* out, float* lse_out, long long rows, int D) {
+  const long long r = blockIdx.x;
+  if (r >= rows) return;
+  const float a = la[r], b = lb[r];
+  const float mx = fmaxf(a, b);
+  const float wa = (a == -CUDART_INF_F) ? 0.f : __expf(a - mx);
+  const float wb = (b == -CUDART_INF_F) ? 0.f : __expf(b - mx);
+  const float den = wa + wb;
+  const float ia = den > 0.f ? wa / den : 0.f, ib = den > 0.f ? wb / den : 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const float v = __bfloat162float(oa[r * D + d]) * ia + __bfloat162float(ob[r * D + d]) * ib;
+    out[r * D + d] = __float2bfloat16(v);
+  }
+  if (threadIdx.x == 0 && lse_out != nullptr) lse_out[r] = den > 0.f ? mx + __logf(den) : -CUDART_INF_F;
+}
+
+template <int D>
+static int launch_decode(const UbAttnArgs& a, cudaStream_t st) {
+  const int Gtot = a.Hq / a.Hkv;
+  int G = 1;
+  while (G < Gtot && G < 8) G <<= 1;
+  if (D == 256 && G > 4) G = 4;
+  const int gchunks = (Gtot + G - 1) / G;
+  dim3 grid(a.num_seqs, a.Hkv * gchunks, a.splits);
+  switch (G) {
+    case 1: attn_decode_kernel<D, 1><<<grid, 128, 0, st>>>(a, gchunks); break;
+    case 2: attn_decode_kernel<D, 2><<<grid, 128, 0, st>>>(a, gchunks); break;
+    case 4: attn_decode_kernel<D, 4><<<grid, 128, 0, st>>>(a, gchunks); break;
+    default:
+      if constexpr (D <= 128) { attn_decode_kernel<D, 8><<<grid, 128, 0, st>>>(a, gchunks); }
+      break;
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return -(int)e;
+  if (a.splits > 1) {
+    dim3 g2(a.num_seqs, a.Hq);
+    attn_split_merge_kernel<<<g2, D <= 128 ? D : 128, 0, st>>>(a.scratch, reinterpret_cast<__nv_bfloat16*>(a.out),
+                                                               a.lse, a.Hq, D, a.splits, a.o_stride);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return -(int)e;
+  }
+  return 0;
+}
+
+}  // namespace ub
+
+extern "C" int ub_attn_decode(const UbAttnArgs* a, void* stream_v) {
+  using namespace ub;
+  if (a->num_seqs <= 0) return 0;
+  if (a->Hq % a->Hkv != 0 || a->splits < 1) return -2;
+  if (a->splits > 1 && a->scratch == nullptr) return -3;
+  cudaStream_t st = (cudaStream_t)stream_v;
+  switch (a->D) {
+    case 64: return launch_decode<64>(*a, st);
+    case 128: return launch_decode<128>(*a, st);
+    case 256: return launch_decode<256>(*a, st);
+    default: return -4;
+  }
+}
+
+extern "C" int ub_attn_merge(const void* o_a, const float* lse_a, const void* o_b, const float* lse_b, void* out,
+                             float* lse_out, long long rows, int D, void* stream_v) {
+  if (rows <= 0) return 0;
+  ub::attn_merge2_kernel<<<(unsigned)rows, D <= 128 ? D : 128, 0, (cudaStream_t)stream_v>>>(
+      (const __nv_bfloat16*)o_a, lse_a, (const __nv_bfloat16*)o_b, lse_b, (__nv_bfloat16*)out, lse_out, rows, D);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}

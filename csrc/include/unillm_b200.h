@@ -1,0 +1,247 @@
+/* C ABI of libunillm_b200_cuda.so: every entry point takes raw device pointers and a CUDA
+ * stream (as void*), launches asynchronously on that stream and returns 0 on success or a
+ * negative code.  No entry point allocates device memory unless its comment says so.
+ * The Python package binds these with ctypes (unillm_b200/ops/_native.py); the structs below
+ * are mirrored there field by field. */
+#ifndef UNILLM_B200_H_
+#define UNILLM_B200_H_
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define UB_MAX_RANKS 8
+#define UB_MAX_DEVICES 16
+
+enum UbAct {
+  UB_ACT_NONE = 0,
+  UB_ACT_SILU = 1,
+  UB_ACT_GELU = 2,
+  UB_ACT_GELU_TANH = 3,
+  UB_ACT_RELU = 4,
+  UB_ACT_RELU2 = 5,
+  UB_ACT_QUICK_GELU = 6,
+  UB_ACT_SIGMOID = 7,
+  UB_ACT_TANH = 8,
+  UB_ACT_SOFTPLUS = 9,
+  UB_ACT_EXP = 10,
+};
+
+/* ---------------- K1 / K2 / F1 / F3 : tcgen05 GEMM  out[M,N] = epi(x[M,K] @ w[N,K]^T) ---------------- */
+typedef struct UbGemmArgs {
+  const void* x;        /* bf16 [M, ldx]  */
+  const void* w;        /* bf16 [N or w_rows_total, ldw] */
+  void* out;            /* bf16 (or fp32 when out_f32) [M, ldo] */
+  const void* bias;     /* bf16 [N] or NULL */
+  const void* residual; /* bf16 [M, ldr] or NULL: added to the result */
+  int* err;             /* int[2] device error word or NULL */
+  int M, N, K;
+  long long ldx, ldw, ldo, ldr;
+  int act;              /* UbAct applied to the result (dual: to the gate half) */
+  int dual;             /* 1: out = act(x w_gate^T) * (x w_up^T); gate rows [0,N), up rows [up_row_off, +N) */
+  int up_row_off;
+  int w_rows_total;     /* dual: number of rows of w (e.g. 2*N) */
+  int out_f32;
+  float out_scale;      /* 0 or 1 = none */
+  int tile_tokens;      /* 0 = auto; else 16/32/64/128/256 */
+  /* F1: push rows to the rank that owns the token instead of writing `out`. */
+  int rs_world, rs_rank, rs_rows_per_rank;
+  void* rs_peer_out[UB_MAX_RANKS];
+  uint32_t* rs_peer_flag[UB_MAX_RANKS];
+  /* F3: wait for token rows gathered from other ranks. */
+  int ag_world, ag_rows_per_rank;
+  const uint32_t* ag_flags;
+  const uint32_t* ag_epoch;
+  uint32_t ag_signals_per_use;
+} UbGemmArgs;
+int ub_gemm_tn(const UbGemmArgs* args, void* stream);
+
+/* ---------------- K5 : normalisation ---------------- */
+typedef struct UbNormArgs {
+  const void* x;         /* bf16 [T, H] */
+  const void* residual;  /* bf16 [T, H] or NULL; when set h = x + residual is normalised */
+  const void* weight;    /* bf16 [H] or NULL */
+  const void* bias;      /* bf16 [H] or NULL (LayerNorm only) */
+  void* out;             /* bf16 [T, H] normalised */
+  void* residual_out;    /* bf16 [T, H] or NULL: receives h */
+  int* err;
+  int T, H;
+  float eps;
+  int kind;              /* 0 = RMSNorm, 1 = LayerNorm (mean-subtracting) */
+  int weight_offset_one; /* Gemma: scale by (1 + w) */
+  /* F1 consumer: sum `rs_world` partial slots [world][T][H] before the residual add (x is then the slot base). */
+  int rs_world;
+  const uint32_t* rs_flag;       /* local counter bumped by producers */
+  const uint32_t* epoch;         /* device word */
+  uint32_t rs_signals_per_use;
+  /* F3 producer: also push the normalised row into every peer's gather buffer at row (ag_rank*T + t). */
+  int ag_world, ag_rank;
+  void* ag_peer_out[UB_MAX_RANKS];
+  uint32_t* ag_peer_flag[UB_MAX_RANKS]; /* peer's counter for source `ag_rank` */
+} UbNormArgs;
+int ub_norm(const UbNormArgs* args, void* stream);
+
+/* ---------------- K6 : (q/k head RMSNorm) + RoPE + paged KV append ---------------- */
+typedef struct UbRopeArgs {
+  void* qkv;                 /* bf16 [T, (Hq + 2 Hkv) * D]; q and k are rotated in place */
+  const int* positions;      /* [T] */
+  const int* slot_mapping;   /* [T] flat slot = block * block_size + offset, or -1 to skip the append */
+  void* k_cache;             /* bf16 [num_blocks, Hkv, block_size, D] */
+  void* v_cache;
+  const void* q_norm_w;      /* bf16 [D] or NULL */
+  const void* k_norm_w;      /* bf16 [D] or NULL */
+  int* err;
+  int T, Hq, Hkv, D;
+  int rotary_dim;            /* <= D, even; 0 disables rotation */
+  int block_size;
+  long long num_slots;       /* num_blocks * block_size, for the bounds check */
+  float theta;
+  float pos_scale;           /* linear RoPE scaling: position * pos_scale (1 = none) */
+  float norm_eps;
+  int interleaved;           /* 0 = half-split pairs (i, i + rd/2); 1 = adjacent pairs (2i, 2i+1) */
+  /* Llama-3 style frequency scaling; factor <= 0 disables */
+  float l3_factor, l3_low_freq_factor, l3_high_freq_factor, l3_orig_ctx;
+} UbRopeArgs;
+int ub_rope_kv_append(const UbRopeArgs* args, void* stream);
+
+/* ---------------- K3 / K4 : paged attention ---------------- */
+typedef struct UbAttnArgs {
+  const void* q;             /* bf16 [T, Hq, D] with row stride q_stride elements */
+  const void* k_cache;       /* bf16 [num_blocks, Hkv, block_size, D] */
+  const void* v_cache;
+  void* out;                 /* bf16 [T, Hq, D] row stride o_stride */
+  float* lse;                /* fp32 [T, Hq] or NULL (natural-log sum-exp of scaled scores) */
+  const int* block_tables;   /* [num_seqs, max_blocks_per_seq] */
+  const int* seq_lens;       /* [num_seqs] kv length visible to the LAST query token of the sequence */
+  const int* q_start;        /* [num_seqs + 1] prefix sums of query tokens (prefill); NULL for decode (1 per seq) */
+  const float* alibi_slopes; /* [Hq] or NULL */
+  float* scratch;            /* decode split-KV partials: [num_seqs, Hq, splits, D + 2] fp32, or NULL when splits == 1 */
+  int* err;
+  int num_seqs, Hq, Hkv, D;
+  int block_size, max_blocks_per_seq, num_blocks;
+  long long q_stride, o_stride;
+  float scale;
+  int causal;                /* prefill: 1 = causal (query i sees kv <= kv_len - q_len + i), 0 = bidirectional */
+  int window;                /* > 0: sliding window (query sees at most `window` latest keys) */
+  int splits;                /* decode: number of KV splits per sequence */
+  int kv_start;              /* first kv position to attend (suffix attention after a shared prefix); 0 = all */
+  int total_q;               /* prefill: total query tokens */
+  int max_q_len;             /* prefill: max query tokens in one sequence (grid sizing) */
+} UbAttnArgs;
+int ub_attn_decode(const UbAttnArgs* args, void* stream);
+int ub_attn_prefill(const UbAttnArgs* args, void* stream);
+/* merge two partial attention results (o_a, lse_a) and (o_b, lse_b) -> out; rows = T*Hq, D columns */
+int ub_attn_merge(const void* o_a, const float* lse_a, const void* o_b, const float* lse_b, void* out, float* lse_out,
+                  long long rows, int D, void* stream);
+
+/* ---------------- K8 : sampling ---------------- */
+typedef struct UbSampleArgs {
+  const void* logits;        /* bf16 or fp32 [B, V] row stride ld */
+  long long ld;
+  int logits_f32;
+  int* out_ids;              /* [B] */
+  float* out_vals;           /* [B] or NULL: winning (max) logit, used for the vocab-parallel merge */
+  const float* temperature;  /* [B] or NULL (=> greedy) ; <= 0 means greedy for that row */
+  const float* top_p;        /* [B] or NULL */
+  const int* top_k;          /* [B] or NULL ; <= 0 means no limit (capped at 1024 internally when top_p < 1) */
+  const float* rep_penalty;  /* [B] or NULL */
+  const int* prev_ids;       /* [B, prev_ld] token history for the repetition penalty (-1 padded) or NULL */
+  int prev_ld;
+  unsigned long long seed;
+  unsigned long long step;   /* Philox offset; same (seed, step, row) gives the same draw on every rank */
+  int B, V;
+  int vocab_offset;          /* added to the returned ids (vocab-parallel shards) */
+  int* err;
+} UbSampleArgs;
+int ub_sample(const UbSampleArgs* args, void* stream);
+
+/* ---------------- K9 / K10 / misc element-wise ---------------- */
+int ub_embed_gather(const int* ids, const void* table, void* out, int T, int H, int V, float scale, int* err,
+                    void* stream);
+int ub_act_mul(const void* gate_up, void* out, long long T, int I, int act, void* stream); /* out = act(g)*u ; gate_up [T, 2I] */
+int ub_eltwise(const void* x, void* out, long long n, int act, float alpha, void* stream);  /* out = act(alpha * x) */
+int ub_add(const void* a, const void* b, void* out, long long n, float sa, float sb, void* stream);
+int ub_l2_normalize(const void* x, void* out, int T, int H, float eps, void* stream);
+
+/* ---------------- K7 / K13 : MoE ---------------- */
+typedef struct UbMoeRouteArgs {
+  const void* logits;       /* bf16 or fp32 [T, E] router logits */
+  int logits_f32;
+  int T, E, K;
+  int norm_topk;            /* 1: softmax over the K selected (Mixtral); 0: softmax over all E then pick (DeepSeek) */
+  int* topk_ids;            /* [T, K] */
+  float* topk_w;            /* [T, K] */
+  int* expert_counts;       /* [E]   (zeroed by the kernel) */
+  int* expert_offsets;      /* [E+1] exclusive prefix sums */
+  int* sorted_rows;         /* [T*K] source row (t*K + k) for each expert-sorted slot */
+  int* row_slot;            /* [T*K] inverse permutation */
+  int* err;
+} UbMoeRouteArgs;
+int ub_moe_route(const UbMoeRouteArgs* args, void* stream);
+int ub_moe_gather(const void* x, const int* sorted_rows, void* out, int rows, int K, int H, void* stream);
+int ub_moe_combine(const void* y, const int* row_slot, const float* topk_w, const void* residual, void* out, int T,
+                   int K, int H, void* stream);
+
+/* ---------------- K12 : GGUF-quantised weights ---------------- */
+int ub_dequant(const void* blocks, void* out_bf16, long long n_elems, int qtype, void* stream); /* qtype: 2=Q4_0 8=Q8_0 12=Q4_K 14=Q6_K */
+int ub_qgemv(const void* blocks, const void* x, void* out, int M, int N, int K, int qtype, void* stream); /* out[M,N] = x[M,K] @ deq(w[N,K])^T, M <= 8 */
+
+/* ---------------- K11 / K14-K17 : conv and scans ---------------- */
+int ub_causal_dwconv1d(const void* x, const void* w, const void* b, void* out, void* state, int B, int L, int C,
+                       int Kw, int act_silu, void* stream);
+int ub_selective_scan(const void* u, const void* delta, const void* A, const void* Bm, const void* Cm, const void* Dv,
+                      const void* z, void* out, float* state, int B, int L, int Dm, int Ns, int delta_softplus,
+                      void* stream);
+int ub_linear_recurrence(const void* a, const void* x, void* out, float* state, int B, int L, int C, void* stream);
+int ub_wkv4(const void* k, const void* v, const float* w, const float* u, void* out, float* state, int B, int L,
+            int C, void* stream);
+int ub_wkv6(const void* r, const void* k, const void* v, const void* w, const float* u, void* out, float* state,
+            int B, int L, int H, int Dh, void* stream);
+
+/* ---------------- comm helpers ---------------- */
+int ub_bump_epoch(uint32_t* epoch, void* stream);
+/* One-shot all-reduce for tiny messages: every rank pushes its vector into each peer's slot, then sums. */
+typedef struct UbAllReduceArgs {
+  const void* in;           /* bf16 [n] local */
+  void* out;                /* bf16 [n] */
+  void* peer_slots[UB_MAX_RANKS];     /* each: [world][n] bf16 on that peer */
+  uint32_t* peer_flags[UB_MAX_RANKS]; /* peer's counter */
+  const void* my_slots;     /* local [world][n] */
+  const uint32_t* my_flag;
+  const uint32_t* epoch;
+  int world, rank;
+  long long n;
+  int* err;
+} UbAllReduceArgs;
+int ub_allreduce_oneshot(const UbAllReduceArgs* args, void* stream);
+/* Wait until *flag (u32, wrap-safe) >= value; bounded (about 1 s), writes status 2 to err on timeout. */
+int ub_wait_flag(const uint32_t* flag, uint32_t value, int* err, void* stream);
+
+/* ---------------- device memory backend (kv/gpu_memory FFI surface) ---------------- */
+int ub_cuda_device_count(void);
+int ub_cuda_set_device(int dev);
+int ub_cuda_malloc_aligned(void** ptr, unsigned long long bytes, unsigned long long align);
+int ub_cuda_free(void* ptr);
+int ub_cuda_malloc_host(void** ptr, unsigned long long bytes);
+int ub_cuda_free_host(void* ptr);
+int ub_cuda_memcpy_h2d_async(void* dst, const void* src, unsigned long long bytes, void* stream);
+int ub_cuda_memcpy_d2h_async(void* dst, const void* src, unsigned long long bytes, void* stream);
+int ub_cuda_memcpy_d2d_async(void* dst, const void* src, unsigned long long bytes, void* stream);
+int ub_cuda_stream_create(void** stream);
+int ub_cuda_stream_destroy(void* stream);
+int ub_cuda_stream_synchronize(void* stream);
+int ub_cuda_device_synchronize(void);
+int ub_cuda_mem_info(unsigned long long* free_b, unsigned long long* total_b);
+typedef struct UbDeviceProps {
+  char name[128];
+  unsigned long long total_mem;
+  int sm_count, cc_major, cc_minor, max_smem_per_block, l2_bytes, clock_khz, mem_clock_khz, mem_bus_bits;
+} UbDeviceProps;
+int ub_cuda_device_props(int dev, UbDeviceProps* out);
+const char* ub_cuda_error_string(int code);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,251 @@
+// K5: RMSNorm / LayerNorm with fused residual add, plus the two collective roles it plays in the
+// tensor-parallel pipeline:
+//   * F1 consumer: the input may be `rs_world` partial slots pushed by the GEMM+reduce-scatter
+//     epilogues of all ranks; the kernel waits (bounded) on the local counter, sums the slots in
+//     fp32 in a fixed order (deterministic) and continues as usual.
+//   * F3 producer: the normalised row is also stored into every peer's all-gather buffer (plain
+//     16-byte peer stores over NVLink) and a per-source counter is bumped on each peer.
+// One CTA per token row; the row is staged in shared memory as fp32.
+//
+// Replaces in the reference: ops_fn::layer_norm / rms_norm / fused_residual_rms_norm
+// (crates/runtime/src/tensor_core.rs:973-1008, 1130-1143, 1398-1423) and the AVX2/NEON rms_norm
+// (crates/runtime/src/simd/arch/avx2.rs:155-201).
+#include "../common/ptx.cuh"
+#include "../include/unillm_b200.h"
+
+namespace ub {
+
+struct NormParams {
+  const __nv_bfloat16* x;
+  const __nv_bfloat16* residual;
+  const __nv_bfloat16* weight;
+  const __nv_bfloat16* bias;
+  __nv_bfloat16* out;
+  __nv_bfloat16* residual_out;
+  int* err;
+  int T, H;
+  float eps;
+  int kind, weight_offset_one;
+  int rs_world;
+  const uint32_t* rs_flag;
+  const uint32_t* epoch;
+  uint32_t rs_signals_per_use;
+  int ag_world, ag_rank;
+  __nv_bfloat16* ag_peer_out[UB_MAX_RANKS];
+  uint32_t* ag_peer_flag[UB_MAX_RANKS];
+};
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
+  if (warp == 0) {
+    t = warp_sum(t);
+    if (lane == 0) red[0] = t;
+  }
+  __syncthreads();
+  return red[0];
+}
+
+__global__ void __launch_bounds__(256) norm_kernel(const NormParams p) {
+  extern __shared__ float row[];  // [H]
+  __shared__ float red[32];
+  __shared__ int wait_failed;
+  const int t = blockIdx.x;
+  const int H = p.H;
+  const bool vec = (H % 8 == 0);
+
+  if (p.rs_world > 0) {
+    if (threadIdx.x == 0) {
+      wait_failed = 0;
+      const uint32_t want = (*p.epoch) * p.rs_signals_per_use;
+      const uint64_t t0 = globaltimer_ns();
+      uint32_t it = 0, v;
+      while (true) {
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.rs_flag) : "memory");
+        if (int32_t(v - want) >= 0) break;
+        if ((++it & 31u) == 0 && (globaltimer_ns() - t0 > UB_WAIT_NS)) {
+          set_err(p.err, ERR_FLAG_TIMEOUT, 1000 + t);
+          wait_failed = 1;
+          break;
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  const int nslots = p.rs_world > 0 ? p.rs_world : 1;
+  const long long slot_stride = (long long)p.T * H;
+  float ssum = 0.f, ssq = 0.f;
+  if (vec) {
+    for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
+      float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int s = 0; s < nslots; ++s) {
+        // L2-only load: with rs_world > 0 these rows were written by peers and L1 may hold a stale line
+        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(p.x + s * slot_stride + (long long)t * H + c * 8));
+        const uint32_t* a = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { f[2 * e] += bf16_lo(a[e]); f[2 * e + 1] += bf16_hi(a[e]); }
+      }
+      if (p.residual != nullptr) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p.residual + (long long)t * H + c * 8);
+        const uint32_t* a = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { f[2 * e] += bf16_lo(a[e]); f[2 * e + 1] += bf16_hi(a[e]); }
+      }
+      if (p.residual_out != nullptr) {
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          o[e] = pack_bf16x2(f[2 * e], f[2 * e + 1]);
+          // normalise the value that is actually stored so that later layers see a consistent residual
+          f[2 * e] = bf16_lo(o[e]); f[2 * e + 1] = bf16_hi(o[e]);
+        }
+        *reinterpret_cast<uint4*>(p.residual_out + (long long)t * H + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { row[c * 8 + e] = f[e]; ssum += f[e]; ssq += f[e] * f[e]; }
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float f = 0.f;
+      for (int s = 0; s < nslots; ++s) f += __bfloat162float(p.x[s * slot_stride + (long long)t * H + i]);
+      if (p.residual != nullptr) f += __bfloat162float(p.residual[(long long)t * H + i]);
+      if (p.residual_out != nullptr) {
+        __nv_bfloat16 b = __float2bfloat16(f);
+        p.residual_out[(long long)t * H + i] = b;
+        f = __bfloat162float(b);
+      }
+      row[i] = f; ssum += f; ssq += f * f;
+    }
+  }
+  float mean = 0.f, rstd;
+  if (p.kind == 1) {
+    mean = block_sum(ssum, red) / H;
+    // two-pass variance for accuracy
+    float sv = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) { float d = row[i] - mean; sv += d * d; }
+    rstd = rsqrtf(block_sum(sv, red) / H + p.eps);
+  } else {
+    rstd = rsqrtf(block_sum(ssq, red) / H + p.eps);
+  }
+
+  const float woff = p.weight_offset_one ? 1.f : 0.f;
+  if (vec) {
+    for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
+      float w[8], b[8];
+      if (p.weight != nullptr) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p.weight + c * 8);
+        const uint32_t* a = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { w[2 * e] = bf16_lo(a[e]) + woff; w[2 * e + 1] = bf16_hi(a[e]) + woff; }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) w[e] = 1.f;
+      }
+      if (p.bias != nullptr) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p.bias + c * 8);
+        const uint32_t* a = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { b[2 * e] = bf16_lo(a[e]); b[2 * e + 1] = bf16_hi(a[e]); }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) b[e] = 0.f;
+      }
+      uint32_t o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float y0 = (row[c * 8 + 2 * e] - mean) * rstd * w[2 * e] + b[2 * e];
+        const float y1 = (row[c * 8 + 2 * e + 1] - mean) * rstd * w[2 * e + 1] + b[2 * e + 1];
+        o[e] = pack_bf16x2(y0, y1);
+      }
+      const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
+      if (p.out != nullptr) *reinterpret_cast<uint4*>(p.out + (long long)t * H + c * 8) = ov;
+      if (p.ag_world > 0) {
+        const long long grow = (long long)p.ag_rank * p.T + t;
+        for (int r = 0; r < p.ag_world; ++r)
+          *reinterpret_cast<uint4*>(p.ag_peer_out[r] + grow * H + c * 8) = ov;
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      const float w = p.weight != nullptr ? __bfloat162float(p.weight[i]) + woff : 1.f;
+      const float b = p.bias != nullptr ? __bfloat162float(p.bias[i]) : 0.f;
+      const __nv_bfloat16 y = __float2bfloat16((row[i] - mean) * rstd * w + b);
+      if (p.out != nullptr) p.out[(long long)t * H + i] = y;
+      if (p.ag_world > 0) {
+        const long long grow = (long long)p.ag_rank * p.T + t;
+        for (int r = 0; r < p.ag_world; ++r) p.ag_peer_out[r][grow * H + i] = y;
+      }
+    }
+  }
+  if (p.ag_world > 0) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < p.ag_world) {
+      asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.ag_peer_flag[threadIdx.x]), "r"(1u) : "memory");
+    }
+  }
+}
+
+__global__ void bump_epoch_kernel(uint32_t* e) { *e = *e + 1; }
+
+__global__ void wait_flag_kernel(const uint32_t* flag, uint32_t value, int* err) {
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t it = 0, v;
+  while (true) {
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (int32_t(v - value) >= 0) return;
+    if ((++it & 31u) == 0 && (globaltimer_ns() - t0 > UB_WAIT_NS)) {
+      set_err(err, ERR_FLAG_TIMEOUT, 2000);
+      return;
+    }
+  }
+}
+
+}  // namespace ub
+
+extern "C" int ub_norm(const UbNormArgs* a, void* stream_v) {
+  using namespace ub;
+  if (a->T <= 0 || a->H <= 0) return 0;
+  if ((size_t)a->H * 4 > 160 * 1024) return -2;
+  NormParams p;
+  p.x = (const __nv_bfloat16*)a->x; p.residual = (const __nv_bfloat16*)a->residual;
+  p.weight = (const __nv_bfloat16*)a->weight; p.bias = (const __nv_bfloat16*)a->bias;
+  p.out = (__nv_bfloat16*)a->out; p.residual_out = (__nv_bfloat16*)a->residual_out;
+  p.err = a->err; p.T = a->T; p.H = a->H; p.eps = a->eps; p.kind = a->kind;
+  p.weight_offset_one = a->weight_offset_one;
+  p.rs_world = a->rs_world; p.rs_flag = a->rs_flag; p.epoch = a->epoch;
+  p.rs_signals_per_use = a->rs_signals_per_use;
+  p.ag_world = a->ag_world; p.ag_rank = a->ag_rank;
+  for (int i = 0; i < UB_MAX_RANKS; ++i) {
+    p.ag_peer_out[i] = (__nv_bfloat16*)a->ag_peer_out[i];
+    p.ag_peer_flag[i] = a->ag_peer_flag[i];
+  }
+  const size_t smem = (size_t)a->H * 4;
+  static bool attr_set[UB_MAX_DEVICES] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (smem > 48 * 1024 && dev < UB_MAX_DEVICES && !attr_set[dev]) {
+    cudaFuncSetAttribute(norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    attr_set[dev] = true;
+  }
+  norm_kernel<<<a->T, 256, smem, (cudaStream_t)stream_v>>>(p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+extern "C" int ub_bump_epoch(uint32_t* epoch, void* stream_v) {
+  ub::bump_epoch_kernel<<<1, 1, 0, (cudaStream_t)stream_v>>>(epoch);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+extern "C" int ub_wait_flag(const uint32_t* flag, uint32_t value, int* err, void* stream_v) {
+  ub::wait_flag_kernel<<<1, 1, 0, (cudaStream_t)stream_v>>>(flag, value, err);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}

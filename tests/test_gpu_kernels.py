@@ -1,0 +1,283 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+from tests.gpu_util import make_paged_cache, ref_attention
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _check_err_word():
+    yield
+    from unillm_b200.ops import cuda_ops
+
+    torch.cuda.synchronize()
+    cuda_ops.check_device_errors()
+
+
+def _rand(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16).cuda()
+
+
+def _close(got, ref, rtol=2e-2, atol=2e-2):
+    got, ref = got.float().cpu(), ref.float().cpu()
+    err = (got - ref).abs()
+    tol = atol + rtol * ref.abs()
+    bad = (err > tol).sum().item()
+    assert bad == 0, f"{bad}/{err.numel()} elements off; max err {err.max().item():.4g}, ref max {ref.abs().max().item():.4g}"
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (16, 256, 512), (7, 384, 4096), (33, 1024, 1024),
+                                   (100, 4096, 4096), (128, 6144, 4096), (256, 4096, 14336), (300, 520, 264),
+                                   (1024, 2048, 2048), (2000, 768, 3072)])
+def test_gemm_tn(M, N, K):
+    from unillm_b200.ops import cuda_ops
+
+    x, w = _rand(M, K, seed=1), _rand(N, K, scale=1 / math.sqrt(K), seed=2)
+    y = cuda_ops.gemm_tn(x, w)
+    ref = x.float() @ w.float().t()
+    _close(y, ref)
+
+
+@pytest.mark.parametrize("tile", [16, 32, 64, 128, 256])
+def test_gemm_tile_variants(tile):
+    from unillm_b200.ops import cuda_ops
+
+    M, N, K = 260, 640, 1088
+    x, w = _rand(M, K, seed=3), _rand(N, K, scale=1 / math.sqrt(K), seed=4)
+    y = cuda_ops.gemm_tn(x, w, tile_tokens=tile)
+    _close(y, x.float() @ w.float().t())
+
+
+def test_gemm_bias_residual_act_f32():
+    from unillm_b200.ops import cuda_ops
+
+    M, N, K = 77, 512, 768
+    x, w = _rand(M, K, seed=5), _rand(N, K, scale=1 / math.sqrt(K), seed=6)
+    b, r = _rand(N, seed=7), _rand(M, N, seed=8)
+    y = cuda_ops.gemm_tn(x, w, bias=b, residual=r, act="gelu")
+    ref = torch.nn.functional.gelu(x.float() @ w.float().t() + b.float()) + r.float()
+    _close(y, ref)
+    y32 = cuda_ops.gemm_tn(x, w, out_dtype=torch.float32)
+    assert y32.dtype == torch.float32
+    _close(y32, x.float() @ w.float().t(), rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("M", [5, 64, 130, 512])
+@pytest.mark.parametrize("act", ["silu", "gelu_tanh"])
+def test_gemm_dual_swiglu(M, act):
+    from unillm_b200.ops import cuda_ops
+
+    K, I = 1024, 1408
+    x, w = _rand(M, K, seed=9), _rand(2 * I, K, scale=1 / math.sqrt(K), seed=10)
+    y = cuda_ops.gemm_tn(x, w, dual_rows=I, act=act)
+    g = x.float() @ w[:I].float().t()
+    u = x.float() @ w[I:].float().t()
+    f = torch.nn.functional.silu if act == "silu" else (lambda t: torch.nn.functional.gelu(t, approximate="tanh"))
+    _close(y, f(g) * u)
+
+
+def test_gemm_deterministic():
+    from unillm_b200.ops import cuda_ops
+
+    x, w = _rand(200, 2048, seed=11), _rand(1536, 2048, scale=0.02, seed=12)
+    a = cuda_ops.gemm_tn(x, w)
+    b = cuda_ops.gemm_tn(x, w)
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("kind", ["rms", "layer"])
+@pytest.mark.parametrize("H", [64, 1000, 4096, 8192])
+def test_norm(kind, H):
+    from unillm_b200.ops import cuda_ops
+
+    T = 37
+    x, r, w, b = _rand(T, H, seed=1), _rand(T, H, seed=2), _rand(H, seed=3), _rand(H, seed=4)
+    y, h = cuda_ops.norm(x, w, bias=b if kind == "layer" else None, residual=r, eps=1e-5, kind=kind,
+                         want_residual_out=True)
+    hr = (x.float() + r.float()).to(torch.bfloat16).float()
+    if kind == "rms":
+        ref = hr * torch.rsqrt(hr.pow(2).mean(-1, keepdim=True) + 1e-5) * w.float()
+    else:
+        ref = torch.nn.functional.layer_norm(hr, (H,), w.float(), b.float(), 1e-5)
+    _close(h, hr, rtol=0, atol=0)
+    _close(y, ref)
+
+
+def _ref_rope(x, pos, theta, rd, interleaved=False):
+    # x [T, H, D] fp32
+    T, H, D = x.shape
+    half = rd // 2
+    inv = theta ** (-torch.arange(half).float() * 2 / rd)
+    ang = pos.float()[:, None] * inv[None]
+    c, s = ang.cos()[:, None], ang.sin()[:, None]
+    out = x.clone()
+    if interleaved:
+        x0, x1 = x[..., 0:rd:2], x[..., 1:rd:2]
+        out[..., 0:rd:2] = x0 * c - x1 * s
+        out[..., 1:rd:2] = x1 * c + x0 * s
+    else:
+        x0, x1 = x[..., :half], x[..., half:rd]
+        out[..., :half] = x0 * c - x1 * s
+        out[..., half:rd] = x1 * c + x0 * s
+    return out
+
+
+@pytest.mark.parametrize("D,rd,inter", [(128, 128, False), (64, 32, False), (128, 64, True)])
+def test_rope_kv_append(D, rd, inter):
+    from unillm_b200.ops import cuda_ops
+
+    T, Hq, Hkv, bs, nb = 21, 8, 2, 16, 9
+    qkv = _rand(T, (Hq + 2 * Hkv) * D, seed=1)
+    pos = torch.randint(0, 5000, (T,), dtype=torch.int32)
+    slots = torch.randperm(nb * bs)[:T].to(torch.int32)
+    kc = torch.zeros(nb, Hkv, bs, D, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    src = qkv.clone().float().cpu().view(T, Hq + 2 * Hkv, D)
+    cuda_ops.rope_kv_append(qkv, pos.cuda(), slots.cuda(), kc, vc, num_q_heads=Hq, num_kv_heads=Hkv, head_dim=D,
+                            rotary_dim=rd, theta=10000.0, interleaved=inter)
+    ref_qk = _ref_rope(src[:, :Hq + Hkv], pos, 10000.0, rd, inter)
+    got = qkv.float().cpu().view(T, Hq + 2 * Hkv, D)
+    _close(got[:, :Hq + Hkv], ref_qk, rtol=1e-2, atol=1e-2)
+    _close(got[:, Hq + Hkv:], src[:, Hq + Hkv:], rtol=0, atol=0)
+    for t in range(T):
+        blk, off = int(slots[t]) // bs, int(slots[t]) % bs
+        _close(kc[blk, :, off].cpu(), got[t, Hq:Hq + Hkv], rtol=0, atol=0)
+        _close(vc[blk, :, off].cpu(), src[t, Hq + Hkv:].to(torch.bfloat16), rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 128), (4, 4, 64), (16, 2, 128), (10, 1, 256)])
+@pytest.mark.parametrize("splits", [1, 4])
+def test_attn_decode(Hq, Hkv, D, splits):
+    from unillm_b200.ops import cuda_ops
+
+    lens = [1, 17, 300, 1000, 64]
+    kc, vc, bt, sl, dk, dv = make_paged_cache(len(lens), lens, Hkv, D)
+    q = _rand(len(lens), Hq, D, seed=5)
+    out, lse = cuda_ops.attn_decode(q, kc, vc, bt, sl, splits=splits, return_lse=True)
+    for i, l in enumerate(lens):
+        ro, rl = ref_attention(q[i:i + 1].cpu(), dk[i], dv[i], causal_offset=l - 1)
+        _close(out[i:i + 1], ro)
+        _close(lse[i:i + 1], rl, rtol=1e-2, atol=1e-2)
+
+
+def test_attn_decode_window_alibi_kvstart():
+    from unillm_b200.ops import cuda_ops
+
+    Hq, Hkv, D = 8, 2, 128
+    lens = [500, 77]
+    kc, vc, bt, sl, dk, dv = make_paged_cache(len(lens), lens, Hkv, D, seed=3)
+    q = _rand(len(lens), Hq, D, seed=6)
+    slopes = torch.tensor([2 ** (-(i + 1)) for i in range(Hq)], dtype=torch.float32)
+    out = cuda_ops.attn_decode(q, kc, vc, bt, sl, window=128, alibi_slopes=slopes.cuda(), splits=2)
+    for i, l in enumerate(lens):
+        ro, _ = ref_attention(q[i:i + 1].cpu(), dk[i], dv[i], causal_offset=l - 1, window=128, alibi=slopes)
+        _close(out[i:i + 1], ro)
+    out2 = cuda_ops.attn_decode(q, kc, vc, bt, sl, kv_start=64, splits=1)
+    for i, l in enumerate(lens):
+        ro, _ = ref_attention(q[i:i + 1].cpu(), dk[i], dv[i], causal_offset=l - 1, kv_start=64)
+        _close(out2[i:i + 1], ro)
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 128), (4, 4, 64), (6, 1, 128)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_attn_prefill(Hq, Hkv, D, causal):
+    from unillm_b200.ops import cuda_ops
+
+    kv_lens = [130, 64, 700, 33]
+    q_lens = [130, 10, 200, 33]     # full prefill, chunk with cached prefix, ...
+    kc, vc, bt, sl, dk, dv = make_paged_cache(len(kv_lens), kv_lens, Hkv, D, seed=4)
+    qs = [0]
+    for l in q_lens:
+        qs.append(qs[-1] + l)
+    q = _rand(qs[-1], Hq, D, seed=7)
+    q_start = torch.tensor(qs, dtype=torch.int32, device="cuda")
+    out, lse = cuda_ops.attn_prefill(q, kc, vc, bt, sl, q_start, max(q_lens), causal=causal, return_lse=True)
+    for i, (kl, ql) in enumerate(zip(kv_lens, q_lens)):
+        ro, rl = ref_attention(q[qs[i]:qs[i + 1]].cpu(), dk[i], dv[i], causal_offset=(kl - ql) if causal else None)
+        _close(out[qs[i]:qs[i + 1]], ro)
+        _close(lse[qs[i]:qs[i + 1]], rl, rtol=1e-2, atol=1e-2)
+
+
+def test_attn_prefill_window_and_cascade_merge():
+    from unillm_b200.ops import cuda_ops
+
+    Hq, Hkv, D = 8, 2, 128
+    kv_lens, q_lens = [400], [400]
+    kc, vc, bt, sl, dk, dv = make_paged_cache(1, kv_lens, Hkv, D, seed=5)
+    q = _rand(400, Hq, D, seed=8)
+    q_start = torch.tensor([0, 400], dtype=torch.int32, device="cuda")
+    out = cuda_ops.attn_prefill(q, kc, vc, bt, sl, q_start, 400, causal=True, window=100)
+    ro, _ = ref_attention(q.cpu(), dk[0], dv[0], causal_offset=0, window=100)
+    _close(out, ro)
+    # cascade: keys [0,256) as a bidirectional "shared prefix" pass + suffix pass, merged
+    pre_len = torch.tensor([256], dtype=torch.int32, device="cuda")
+    oa, la = cuda_ops.attn_prefill(q, kc, vc, bt, pre_len, q_start, 400, causal=False, return_lse=True)
+    # the suffix pass is causal over all 400 keys but only sees keys >= 256
+    ob, lb = cuda_ops.attn_prefill(q, kc, vc, bt, sl, q_start, 400, causal=True, kv_start=256, return_lse=True)
+    merged = cuda_ops.attn_merge(oa, la, ob, lb)
+    # reference: rows >= 256 see all keys <= their position; rows < 256 see the whole prefix + nothing else
+    ro_full, _ = ref_attention(q.cpu(), dk[0], dv[0], causal_offset=0)
+    _close(merged[256:], ro_full[256:])
+
+
+def test_sample_greedy_and_penalty():
+    from unillm_b200.ops import cuda_ops
+
+    B, V = 9, 32000
+    logits = _rand(B, V, seed=1)
+    ids, vals = cuda_ops.sample(logits, return_vals=True)
+    assert torch.equal(ids.cpu().long(), logits.float().argmax(-1).cpu())
+    _close(vals, logits.float().max(-1).values, rtol=0, atol=0)
+    prev = logits.float().argmax(-1).to(torch.int32)[:, None].contiguous()
+    pen = torch.full((B,), 100.0, device="cuda")
+    ids2 = cuda_ops.sample(logits, rep_penalty=pen, prev_ids=prev)
+    assert (ids2 != ids).all()
+
+
+def test_sample_topk_topp_distribution():
+    from unillm_b200.ops import cuda_ops
+
+    B, V = 512, 1000
+    base = torch.randn(V, generator=torch.Generator().manual_seed(3)) * 2
+    logits = base[None].repeat(B, 1).cuda()
+    temp = torch.full((B,), 0.8, device="cuda")
+    topk = torch.full((B,), 5, dtype=torch.int32, device="cuda")
+    ids = cuda_ops.sample(logits, temperature=temp, top_k=topk, seed=1234, step=7)
+    top5 = set(base.topk(5).indices.tolist())
+    assert set(ids.tolist()) <= top5
+    assert len(set(ids.tolist())) >= 3          # not degenerate
+    ids_again = cuda_ops.sample(logits, temperature=temp, top_k=topk, seed=1234, step=7)
+    assert torch.equal(ids, ids_again)          # same (seed, step, row) -> same draw
+    topp = torch.full((B,), 0.5, device="cuda")
+    ids_p = cuda_ops.sample(logits, temperature=temp, top_p=topp, seed=99, step=1)
+    probs = torch.softmax(base / 0.8, -1)
+    sp, si = probs.sort(descending=True)
+    cut = int((sp.cumsum(0) >= 0.5).nonzero()[0]) + 1
+    assert set(ids_p.tolist()) <= set(si[:cut].tolist())
+    # temperature only: empirical frequency of the mode is close to its probability
+    ids_t = cuda_ops.sample(logits, temperature=temp, seed=5, step=3)
+    mode = int(probs.argmax())
+    freq = (ids_t == mode).float().mean().item()
+    assert abs(freq - probs[mode].item()) < 0.08
+
+
+def test_eltwise_embed_actmul():
+    from unillm_b200.ops import cuda_ops
+
+    x = _rand(33, 1000, seed=1)
+    for act, f in [("gelu", torch.nn.functional.gelu), ("silu", torch.nn.functional.silu),
+                   ("relu2", lambda t: torch.relu(t) ** 2), ("sigmoid", torch.sigmoid), ("tanh", torch.tanh),
+                   ("quick_gelu", lambda t: t * torch.sigmoid(1.702 * t)), ("softplus", torch.nn.functional.softplus)]:
+        _close(cuda_ops.eltwise(x, act), f(x.float()))
+    _close(cuda_ops.add(x, x, 0.5, 2.0), 2.5 * x.float())
+    table = _rand(500, 256, seed=2)
+    ids = torch.randint(0, 500, (40,), dtype=torch.int32, device="cuda")
+    _close(cuda_ops.embed_gather(ids, table, scale=2.0), table[ids.long()].float() * 2.0)
+    gu = _rand(17, 2 * 384, seed=3)
+    _close(cuda_ops.act_mul(gu, "silu"), torch.nn.functional.silu(gu[:, :384].float()) * gu[:, 384:].float())
+    _close(cuda_ops.l2_normalize(x), torch.nn.functional.normalize(x.float(), dim=-1))

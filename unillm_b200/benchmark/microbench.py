@@ -1,0 +1,150 @@
+"""Device-timed micro-benchmarks of the hot kernels (CUDA events, warm-up, L2 flush between runs).
+
+``python -m unillm_b200.benchmark.microbench [gemm|attn|norm|all] [--json PATH]`` prints one line per
+case with the achieved TFLOP/s or GB/s and the fraction of the measured peak (MEASURED_PEAKS.json
+when present at the repository root).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+from pathlib import Path
+
+import torch
+
+from ..ops import cuda_ops
+
+
+def _peaks():
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+_flush = None
+
+
+def flush_l2():
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    _flush.zero_()
+
+
+def time_ms(fn, iters=10, warmup=3, flush=True):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush:
+            flush_l2()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    ts.sort()
+    return ts[len(ts) // 2], ts[0]
+
+
+def bench_gemm(results):
+    hbm, tf, how = _peaks()
+    shapes = [
+        # (M, N, K, dual) : Llama-3-8B decode / prefill shapes
+        (16, 6144, 4096, 0), (64, 6144, 4096, 0), (256, 6144, 4096, 0), (256, 4096, 4096, 0),
+        (256, 14336, 4096, 1), (256, 4096, 14336, 0), (256, 128256, 4096, 0),
+        (2048, 6144, 4096, 0), (2048, 14336, 4096, 1), (2048, 4096, 14336, 0), (8192, 8192, 8192, 0),
+    ]
+    for M, N, K, dual in shapes:
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(N * (2 if dual else 1), K, device="cuda", dtype=torch.bfloat16) * 0.02
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        fn = (lambda: cuda_ops.gemm_tn(x, w, dual_rows=N, act="silu", out=out)) if dual else (lambda: cuda_ops.gemm_tn(x, w, out=out))
+        med, best = time_ms(fn)
+        flops = 2.0 * M * N * K * (2 if dual else 1)
+        byts = 2.0 * (w.numel() + x.numel() + out.numel())
+        ref = (lambda: torch.nn.functional.silu(x @ w[:N].t()) * (x @ w[N:].t())) if dual else (lambda: x @ w.t())
+        rmed, _ = time_ms(ref)
+        r = dict(kind="gemm", M=M, N=N, K=K, dual=dual, ms=med, best_ms=best, tflops=flops / med / 1e9,
+                 gbs=byts / med / 1e6, frac_tflops=flops / med / 1e9 / tf, frac_hbm=byts / med / 1e6 / hbm,
+                 cublas_ms=rmed, peaks=how)
+        results.append(r)
+        print(json.dumps(r))
+
+
+def bench_attn(results):
+    hbm, tf, how = _peaks()
+    for B, ctx, Hq, Hkv, D in [(256, 1152, 32, 8, 128), (64, 4096, 32, 8, 128), (256, 1152, 4, 1, 128), (8, 4096, 8, 1, 128)]:
+        bs = 16
+        nblk = B * ((ctx + bs - 1) // bs)
+        kc = torch.randn(nblk, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
+        vc = torch.randn_like(kc)
+        bt = torch.randperm(nblk, device="cuda").to(torch.int32).view(B, -1)
+        sl = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+        q = torch.randn(B, Hq, D, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        scratch = torch.empty(B * Hq * 16 * (D + 2), dtype=torch.float32, device="cuda")
+        med, best = time_ms(lambda: cuda_ops.attn_decode(q, kc, vc, bt, sl, out=out, scratch=scratch, max_seq_len=ctx))
+        byts = 2.0 * 2 * B * ctx * Hkv * D
+        r = dict(kind="attn_decode", B=B, ctx=ctx, Hq=Hq, Hkv=Hkv, D=D, ms=med, best_ms=best, gbs=byts / med / 1e6,
+                 frac_hbm=byts / med / 1e6 / hbm, peaks=how)
+        results.append(r)
+        print(json.dumps(r))
+    for T, ctx, Hq, Hkv, D in [(2048, 2048, 32, 8, 128), (8192, 8192, 4, 1, 128)]:
+        bs = 16
+        nblk = (ctx + bs - 1) // bs
+        kc = torch.randn(nblk, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
+        vc = torch.randn_like(kc)
+        bt = torch.arange(nblk, device="cuda", dtype=torch.int32).view(1, -1)
+        sl = torch.tensor([ctx], dtype=torch.int32, device="cuda")
+        qs = torch.tensor([0, T], dtype=torch.int32, device="cuda")
+        q = torch.randn(T, Hq, D, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        med, best = time_ms(lambda: cuda_ops.attn_prefill(q, kc, vc, bt, sl, qs, T, out=out))
+        flops = 4.0 * T * ctx * Hq * D / 2
+        r = dict(kind="attn_prefill", T=T, ctx=ctx, Hq=Hq, Hkv=Hkv, D=D, ms=med, best_ms=best,
+                 tflops=flops / med / 1e9, frac_tflops=flops / med / 1e9 / tf, peaks=how)
+        results.append(r)
+        print(json.dumps(r))
+
+
+def bench_norm(results):
+    hbm, tf, how = _peaks()
+    for T, H in [(256, 4096), (8192, 4096), (8192, 8192)]:
+        x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+        r_ = torch.randn_like(x)
+        w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+        out, ro = torch.empty_like(x), torch.empty_like(x)
+        med, best = time_ms(lambda: cuda_ops.norm(x, w, residual=r_, out=out, residual_out=ro))
+        byts = 2.0 * 4 * T * H
+        r = dict(kind="rmsnorm_residual", T=T, H=H, ms=med, best_ms=best, gbs=byts / med / 1e6,
+                 frac_hbm=byts / med / 1e6 / hbm, peaks=how)
+        results.append(r)
+        print(json.dumps(r))
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", nargs="?", default="all", choices=["gemm", "attn", "norm", "all"])
+    ap.add_argument("--json", default=None)
+    a = ap.parse_args(argv)
+    results = []
+    if a.what in ("gemm", "all"):
+        bench_gemm(results)
+    if a.what in ("attn", "all"):
+        bench_attn(results)
+    if a.what in ("norm", "all"):
+        bench_norm(results)
+    if a.json:
+        os.makedirs(os.path.dirname(a.json) or ".", exist_ok=True)
+        Path(a.json).write_text(json.dumps(results, indent=1))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,406 @@
+"""Torch-tensor front end of the sm_100a kernel library.
+
+Every function launches on the current CUDA stream of the tensors' device and returns torch
+tensors; none of them synchronises.  Arguments are checked on the host (dtype, contiguity,
+alignment) so that a bad call raises in Python instead of faulting on the device.  The kernels
+record device-side problems (timeouts of bounded waits, out-of-range block-table entries) in a
+per-device error word that :func:`check_device_errors` reads.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional, Sequence
+
+import torch
+
+from . import _native as N
+
+_err_words: dict[int, torch.Tensor] = {}
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def err_word(device) -> torch.Tensor:
+    dev = torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    w = _err_words.get(idx)
+    if w is None:
+        w = torch.zeros(2, dtype=torch.int32, device=f"cuda:{idx}")
+        _err_words[idx] = w
+    return w
+
+
+def check_device_errors(device=None, reset: bool = True) -> None:
+    """Synchronises and raises if any kernel recorded an error since the last check."""
+    devs = [torch.device(device)] if device is not None else [torch.device(f"cuda:{i}") for i in _err_words]
+    for d in devs:
+        w = err_word(d)
+        code, detail = w.tolist()
+        if code != 0:
+            if reset:
+                w.zero_()
+            names = {1: "mbarrier wait timed out", 2: "flag wait timed out (peer or producer missing)",
+                     3: "index out of range", 4: "bad argument"}
+            raise RuntimeError(f"device error {code} ({names.get(code, '?')}), detail {detail} on {d}")
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _bf16c(t: torch.Tensor, name: str) -> None:
+    if t.dtype != torch.bfloat16:
+        raise TypeError(f"{name} must be bfloat16, got {t.dtype}")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor")
+
+
+# ---------------------------------------------------------------------------------------------
+# GEMM
+# ---------------------------------------------------------------------------------------------
+def gemm_tn(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
+            residual: Optional[torch.Tensor] = None, act: Optional[str] = None, out: Optional[torch.Tensor] = None,
+            out_dtype: torch.dtype = torch.bfloat16, out_scale: float = 1.0, tile_tokens: int = 0,
+            dual_rows: int = 0, rs: Optional[dict] = None, ag: Optional[dict] = None) -> torch.Tensor:
+    """``out[M, N] = act(x[M, K] @ w[N, K]^T * out_scale + bias) + residual`` on tcgen05 tensor cores.
+
+    ``dual_rows = I`` switches to the gated form: ``w`` is ``[2*I, K]`` with gate rows first and the
+    result is ``act(x @ w[:I]^T) * (x @ w[I:]^T)`` of shape ``[M, I]``.
+    ``rs`` / ``ag`` carry the peer pointers for the fused reduce-scatter / all-gather variants (see
+    :mod:`unillm_b200.dist.fused`).
+    """
+    _bf16c(x, "x"), _bf16c(w, "w")
+    if x.dim() != 2 or w.dim() != 2:
+        raise ValueError("gemm_tn takes 2-D operands")
+    if x.stride(1) != 1 or w.stride(1) != 1:
+        raise ValueError("operands must be K-contiguous")
+    M, K = x.shape
+    if w.shape[1] != K:
+        raise ValueError(f"K mismatch: x {tuple(x.shape)} vs w {tuple(w.shape)}")
+    dual = dual_rows > 0
+    Nn = dual_rows if dual else w.shape[0]
+    if dual and w.shape[0] < 2 * dual_rows:
+        raise ValueError("dual GEMM needs w with 2*I rows")
+    if out is None:
+        out = torch.empty((M, Nn), dtype=out_dtype, device=x.device)
+    if out.stride(-1) != 1:
+        raise ValueError("out must be row-major")
+    a = N.UbGemmArgs()
+    a.x, a.w, a.out = x.data_ptr(), w.data_ptr(), out.data_ptr()
+    a.bias = _p(bias)
+    a.residual = _p(residual)
+    a.err = err_word(x.device).data_ptr()
+    a.M, a.N, a.K = M, Nn, K
+    a.ldx, a.ldw, a.ldo = x.stride(0), w.stride(0), out.stride(0)
+    a.ldr = residual.stride(0) if residual is not None else 0
+    a.act = N.ACT[act]
+    a.dual = 1 if dual else 0
+    a.up_row_off = dual_rows
+    a.w_rows_total = w.shape[0]
+    a.out_f32 = 1 if out.dtype == torch.float32 else 0
+    a.out_scale = out_scale
+    a.tile_tokens = tile_tokens
+    if bias is not None:
+        _bf16c(bias, "bias")
+    if residual is not None:
+        _bf16c(residual, "residual")
+    if rs is not None:
+        a.rs_world, a.rs_rank, a.rs_rows_per_rank = rs["world"], rs["rank"], rs["rows_per_rank"]
+        for i in range(rs["world"]):
+            a.rs_peer_out[i] = rs["peer_out"][i]
+            a.rs_peer_flag[i] = rs["peer_flag"][i]
+    if ag is not None:
+        a.ag_world, a.ag_rows_per_rank = ag["world"], ag["rows_per_rank"]
+        a.ag_flags, a.ag_epoch, a.ag_signals_per_use = ag["flags"], ag["epoch"], ag["signals_per_use"]
+    N.check(N.cuda_lib().ub_gemm_tn(C.byref(a), _stream(x)), "ub_gemm_tn")
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, **kw) -> torch.Tensor:
+    """``x[..., K] @ w[N, K]^T`` for any leading shape."""
+    lead = x.shape[:-1]
+    y = gemm_tn(x.reshape(-1, x.shape[-1]), w, bias=bias, **kw)
+    return y.reshape(*lead, y.shape[-1])
+
+
+# ---------------------------------------------------------------------------------------------
+# Norm
+# ---------------------------------------------------------------------------------------------
+def norm(x: torch.Tensor, weight: Optional[torch.Tensor], *, bias: Optional[torch.Tensor] = None,
+         residual: Optional[torch.Tensor] = None, eps: float = 1e-5, kind: str = "rms",
+         weight_offset_one: bool = False, want_residual_out: bool = False,
+         out: Optional[torch.Tensor] = None, residual_out: Optional[torch.Tensor] = None,
+         rs: Optional[dict] = None, ag: Optional[dict] = None, T: Optional[int] = None):
+    """RMSNorm / LayerNorm over the last dim, with optional fused ``x + residual``.
+
+    Returns ``y`` or ``(y, h)`` when the residual stream ``h = x + residual`` is requested.
+    """
+    _bf16c(x, "x")
+    H = x.shape[-1]
+    if T is None:
+        T = x.numel() // H
+    if not x.is_contiguous():
+        x = x.contiguous()
+    if out is None:
+        out = torch.empty((T, H), dtype=torch.bfloat16, device=x.device)
+    if want_residual_out and residual_out is None:
+        residual_out = torch.empty((T, H), dtype=torch.bfloat16, device=x.device)
+    a = N.UbNormArgs()
+    a.x, a.residual, a.weight, a.bias = x.data_ptr(), _p(residual), _p(weight), _p(bias)
+    a.out, a.residual_out = out.data_ptr(), _p(residual_out)
+    a.err = err_word(x.device).data_ptr()
+    a.T, a.H, a.eps = T, H, eps
+    a.kind = 0 if kind == "rms" else 1
+    a.weight_offset_one = 1 if weight_offset_one else 0
+    if rs is not None:
+        a.rs_world, a.rs_flag, a.epoch, a.rs_signals_per_use = rs["world"], rs["flag"], rs["epoch"], rs["signals_per_use"]
+    if ag is not None:
+        a.ag_world, a.ag_rank = ag["world"], ag["rank"]
+        for i in range(ag["world"]):
+            a.ag_peer_out[i] = ag["peer_out"][i]
+            a.ag_peer_flag[i] = ag["peer_flag"][i]
+    N.check(N.cuda_lib().ub_norm(C.byref(a), _stream(x)), "ub_norm")
+    if residual_out is not None:
+        return out, residual_out
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# RoPE + KV append
+# ---------------------------------------------------------------------------------------------
+def rope_kv_append(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Optional[torch.Tensor],
+                   k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], *, num_q_heads: int,
+                   num_kv_heads: int, head_dim: int, rotary_dim: Optional[int] = None, theta: float = 10000.0,
+                   pos_scale: float = 1.0, interleaved: bool = False, q_norm_w: Optional[torch.Tensor] = None,
+                   k_norm_w: Optional[torch.Tensor] = None, norm_eps: float = 1e-6,
+                   llama3_scaling: Optional[Sequence[float]] = None) -> torch.Tensor:
+    """Rotates q and k inside ``qkv`` [T, (Hq+2Hkv)*D] in place and appends k, v to the paged cache."""
+    _bf16c(qkv, "qkv")
+    if not qkv.is_contiguous():
+        raise ValueError("qkv must be contiguous")
+    T = qkv.shape[0]
+    if positions.dtype != torch.int32 or (slot_mapping is not None and slot_mapping.dtype != torch.int32):
+        raise TypeError("positions / slot_mapping must be int32")
+    a = N.UbRopeArgs()
+    a.qkv, a.positions, a.slot_mapping = qkv.data_ptr(), positions.data_ptr(), _p(slot_mapping)
+    a.k_cache, a.v_cache = _p(k_cache), _p(v_cache)
+    a.q_norm_w, a.k_norm_w = _p(q_norm_w), _p(k_norm_w)
+    a.err = err_word(qkv.device).data_ptr()
+    a.T, a.Hq, a.Hkv, a.D = T, num_q_heads, num_kv_heads, head_dim
+    a.rotary_dim = head_dim if rotary_dim is None else rotary_dim
+    if k_cache is not None:
+        a.block_size = k_cache.shape[2]
+        a.num_slots = k_cache.shape[0] * k_cache.shape[2]
+    else:
+        a.block_size, a.num_slots = 16, 0
+        a.slot_mapping = None
+    a.theta, a.pos_scale, a.norm_eps = theta, pos_scale, norm_eps
+    a.interleaved = 1 if interleaved else 0
+    if llama3_scaling is not None:
+        a.l3_factor, a.l3_low_freq_factor, a.l3_high_freq_factor, a.l3_orig_ctx = llama3_scaling
+    N.check(N.cuda_lib().ub_rope_kv_append(C.byref(a), _stream(qkv)), "ub_rope_kv_append")
+    return qkv
+
+
+# ---------------------------------------------------------------------------------------------
+# Attention
+# ---------------------------------------------------------------------------------------------
+def _attn_args(q, k_cache, v_cache, out, lse, block_tables, seq_lens, Hq, Hkv, D, scale):
+    a = N.UbAttnArgs()
+    a.q, a.k_cache, a.v_cache, a.out, a.lse = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(lse)
+    a.block_tables, a.seq_lens = block_tables.data_ptr(), seq_lens.data_ptr()
+    a.err = err_word(q.device).data_ptr()
+    a.num_seqs, a.Hq, a.Hkv, a.D = seq_lens.shape[0], Hq, Hkv, D
+    a.block_size, a.max_blocks_per_seq, a.num_blocks = k_cache.shape[2], block_tables.shape[1], k_cache.shape[0]
+    a.q_stride, a.o_stride = q.stride(0), out.stride(0)
+    a.scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    return a
+
+
+def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
+                seq_lens: torch.Tensor, *, scale: Optional[float] = None, window: int = 0, kv_start: int = 0,
+                alibi_slopes: Optional[torch.Tensor] = None, splits: int = 0, scratch: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None, return_lse: bool = False, lse: Optional[torch.Tensor] = None,
+                max_seq_len: Optional[int] = None):
+    """One query token per sequence.  q: [B, Hq, D] (last two dims contiguous); caches [nb, Hkv, bs, D]."""
+    _bf16c(q, "q")
+    B, Hq, D = q.shape
+    Hkv = k_cache.shape[1]
+    if out is None:
+        out = torch.empty((B, Hq, D), dtype=torch.bfloat16, device=q.device)
+    if return_lse and lse is None:
+        lse = torch.empty((B, Hq), dtype=torch.float32, device=q.device)
+    if splits <= 0:
+        ctx = max_seq_len if max_seq_len is not None else block_tables.shape[1] * k_cache.shape[2]
+        ctas = B * Hkv
+        splits = 1
+        while ctas * splits < 2 * 148 and ctx // (splits * 2) >= 256 and splits < 16:
+            splits *= 2
+    a = _attn_args(q, k_cache, v_cache, out, lse, block_tables, seq_lens, Hq, Hkv, D, scale)
+    if splits > 1:
+        need = B * Hq * splits * (D + 2)
+        if scratch is None or scratch.numel() < need:
+            scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+        a.scratch = scratch.data_ptr()
+    a.window, a.splits, a.kv_start = window, splits, kv_start
+    a.alibi_slopes = _p(alibi_slopes)
+    N.check(N.cuda_lib().ub_attn_decode(C.byref(a), _stream(q)), "ub_attn_decode")
+    return (out, lse) if return_lse else out
+
+
+def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
+                 seq_lens: torch.Tensor, q_start: torch.Tensor, max_q_len: int, *, scale: Optional[float] = None,
+                 causal: bool = True, window: int = 0, kv_start: int = 0,
+                 alibi_slopes: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                 return_lse: bool = False, lse: Optional[torch.Tensor] = None):
+    """Ragged prefill: q [T, Hq, D]; sequence i owns query rows q_start[i]:q_start[i+1] and sees
+    seq_lens[i] keys, its last query at kv position seq_lens[i]-1."""
+    _bf16c(q, "q")
+    T, Hq, D = q.shape
+    Hkv = k_cache.shape[1]
+    if out is None:
+        out = torch.empty((T, Hq, D), dtype=torch.bfloat16, device=q.device)
+    if return_lse and lse is None:
+        lse = torch.empty((T, Hq), dtype=torch.float32, device=q.device)
+    a = _attn_args(q, k_cache, v_cache, out, lse, block_tables, seq_lens, Hq, Hkv, D, scale)
+    a.q_start = q_start.data_ptr()
+    a.causal, a.window, a.kv_start = (1 if causal else 0), window, kv_start
+    a.total_q, a.max_q_len = T, max_q_len
+    a.alibi_slopes = _p(alibi_slopes)
+    N.check(N.cuda_lib().ub_attn_prefill(C.byref(a), _stream(q)), "ub_attn_prefill")
+    return (out, lse) if return_lse else out
+
+
+def attn_merge(o_a: torch.Tensor, lse_a: torch.Tensor, o_b: torch.Tensor, lse_b: torch.Tensor,
+               out: Optional[torch.Tensor] = None, lse_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Combine two attention partials over disjoint key sets.  o_*: [T, Hq, D] contiguous, lse_*: [T, Hq]."""
+    if out is None:
+        out = torch.empty_like(o_a)
+    lib = N.cuda_lib()
+    lib.ub_attn_merge.restype = C.c_int
+    lib.ub_attn_merge.argtypes = [N.vp, N.vp, N.vp, N.vp, N.vp, N.vp, N.i64, N.i32, N.vp]
+    rows = o_a.shape[0] * o_a.shape[1]
+    N.check(lib.ub_attn_merge(o_a.data_ptr(), lse_a.data_ptr(), o_b.data_ptr(), lse_b.data_ptr(), out.data_ptr(),
+                              _p(lse_out), rows, o_a.shape[-1], _stream(o_a)), "ub_attn_merge")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# Sampling
+# ---------------------------------------------------------------------------------------------
+def sample(logits: torch.Tensor, *, temperature: Optional[torch.Tensor] = None, top_p: Optional[torch.Tensor] = None,
+           top_k: Optional[torch.Tensor] = None, rep_penalty: Optional[torch.Tensor] = None,
+           prev_ids: Optional[torch.Tensor] = None, seed: int = 0, step: int = 0, vocab_offset: int = 0,
+           out_ids: Optional[torch.Tensor] = None, out_vals: Optional[torch.Tensor] = None,
+           return_vals: bool = False):
+    """Greedy when ``temperature`` is None (or <= 0 for a row); otherwise temperature / top-k / top-p."""
+    if logits.dim() != 2 or logits.stride(1) != 1:
+        raise ValueError("logits must be [B, V] with contiguous rows")
+    if logits.dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError("logits must be bf16 or fp32")
+    B, V = logits.shape
+    if out_ids is None:
+        out_ids = torch.empty(B, dtype=torch.int32, device=logits.device)
+    if return_vals and out_vals is None:
+        out_vals = torch.empty(B, dtype=torch.float32, device=logits.device)
+    a = N.UbSampleArgs()
+    a.logits, a.ld, a.logits_f32 = logits.data_ptr(), logits.stride(0), int(logits.dtype == torch.float32)
+    a.out_ids, a.out_vals = out_ids.data_ptr(), _p(out_vals)
+    a.temperature, a.top_p, a.top_k, a.rep_penalty = _p(temperature), _p(top_p), _p(top_k), _p(rep_penalty)
+    if prev_ids is not None:
+        a.prev_ids, a.prev_ld = prev_ids.data_ptr(), prev_ids.shape[1]
+    a.seed, a.step, a.B, a.V, a.vocab_offset = seed & (2**64 - 1), step, B, V, vocab_offset
+    a.err = err_word(logits.device).data_ptr()
+    N.check(N.cuda_lib().ub_sample(C.byref(a), _stream(logits)), "ub_sample")
+    return (out_ids, out_vals) if return_vals else out_ids
+
+
+def argmax_merge(vals: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """vals/ids [world, B] per-shard greedy winners -> global winners [B]."""
+    world, B = vals.shape
+    if out is None:
+        out = torch.empty(B, dtype=torch.int32, device=vals.device)
+    lib = N.cuda_lib()
+    lib.ub_argmax_merge.restype = C.c_int
+    lib.ub_argmax_merge.argtypes = [N.vp, N.vp, N.i32, N.i32, N.vp, N.vp]
+    N.check(lib.ub_argmax_merge(vals.data_ptr(), ids.data_ptr(), world, B, out.data_ptr(), _stream(vals)),
+            "ub_argmax_merge")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# Element-wise
+# ---------------------------------------------------------------------------------------------
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _bf16c(table, "table")
+    if ids.dtype != torch.int32:
+        ids = ids.to(torch.int32)
+    ids = ids.contiguous()
+    T = ids.numel()
+    V, H = table.shape
+    if out is None:
+        out = torch.empty((T, H), dtype=torch.bfloat16, device=table.device)
+    lib = N.cuda_lib()
+    lib.ub_embed_gather.restype = C.c_int
+    lib.ub_embed_gather.argtypes = [N.vp, N.vp, N.vp, N.i32, N.i32, N.i32, N.f32, N.vp, N.vp]
+    N.check(lib.ub_embed_gather(ids.data_ptr(), table.data_ptr(), out.data_ptr(), T, H, V, scale,
+                                err_word(table.device).data_ptr(), _stream(table)), "ub_embed_gather")
+    return out
+
+
+def act_mul(gate_up: torch.Tensor, act: str = "silu", out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``act(gate) * up`` for gate_up [..., 2*I] (gate first)."""
+    _bf16c(gate_up, "gate_up")
+    gate_up = gate_up.contiguous()
+    I = gate_up.shape[-1] // 2
+    T = gate_up.numel() // (2 * I)
+    if out is None:
+        out = torch.empty((*gate_up.shape[:-1], I), dtype=torch.bfloat16, device=gate_up.device)
+    lib = N.cuda_lib()
+    lib.ub_act_mul.restype = C.c_int
+    lib.ub_act_mul.argtypes = [N.vp, N.vp, N.i64, N.i32, N.i32, N.vp]
+    N.check(lib.ub_act_mul(gate_up.data_ptr(), out.data_ptr(), T, I, N.ACT[act], _stream(gate_up)), "ub_act_mul")
+    return out
+
+
+def eltwise(x: torch.Tensor, act: Optional[str], alpha: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _bf16c(x, "x")
+    x = x.contiguous()
+    if out is None:
+        out = torch.empty_like(x)
+    lib = N.cuda_lib()
+    lib.ub_eltwise.restype = C.c_int
+    lib.ub_eltwise.argtypes = [N.vp, N.vp, N.i64, N.i32, N.f32, N.vp]
+    N.check(lib.ub_eltwise(x.data_ptr(), out.data_ptr(), x.numel(), N.ACT[act], alpha, _stream(x)), "ub_eltwise")
+    return out
+
+
+def add(a: torch.Tensor, b: torch.Tensor, sa: float = 1.0, sb: float = 1.0,
+        out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _bf16c(a, "a"), _bf16c(b, "b")
+    a, b = a.contiguous(), b.contiguous()
+    if a.shape != b.shape:
+        raise ValueError("add: shapes differ")
+    if out is None:
+        out = torch.empty_like(a)
+    lib = N.cuda_lib()
+    lib.ub_add.restype = C.c_int
+    lib.ub_add.argtypes = [N.vp, N.vp, N.vp, N.i64, N.f32, N.f32, N.vp]
+    N.check(lib.ub_add(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), sa, sb, _stream(a)), "ub_add")
+    return out
+
+
+def l2_normalize(x: torch.Tensor, eps: float = 1e-12) -> torch.Tensor:
+    _bf16c(x, "x")
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    H = x.shape[-1]
+    lib = N.cuda_lib()
+    lib.ub_l2_normalize.restype = C.c_int
+    lib.ub_l2_normalize.argtypes = [N.vp, N.vp, N.i32, N.i32, N.f32, N.vp]
+    N.check(lib.ub_l2_normalize(x.data_ptr(), out.data_ptr(), x.numel() // H, H, eps, _stream(x)), "ub_l2_normalize")
+    return out
