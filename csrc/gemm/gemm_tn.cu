@@ -8,13 +8,20 @@
 //    holds out^T: TMEM lane = output feature, TMEM column = token.
 //  * Warp roles: warp 0 = TMA producer, warp 1 = tcgen05.mma issuer and TMEM owner,
 //    warps 2..5 = epilogue (TMEM -> registers -> smem transpose -> 16-byte global stores).
+//  * Two scheduling modes share the main loop:
+//      - PERSISTENT: one CTA per SM walks a static list of output tiles; the accumulator is
+//        double-buffered in TMEM so the epilogue of tile i overlaps the MMAs of tile i+1.
+//      - SPLIT-K: when there are far fewer tiles than SMs (decode, tensor-parallel shards) a
+//        thread-block cluster of S CTAs shares one tile, each CTA reduces 1/S of K, and the
+//        partial accumulators are summed through distributed shared memory in a fixed order
+//        (deterministic, no global workspace, no atomics).  TMA loads are per-CTA (no multicast).
 //  * DUAL mode (K2): two weight tiles (gate rows, up rows) share one token tile and fill two
 //    accumulators; the epilogue writes act(gate) * up, so SwiGLU/GeGLU never touches HBM.
 //  * Collective fusion.  F1 (GEMM + reduce-scatter): the epilogue stores each output row straight
 //    into the symmetric receive buffer of the rank that owns that token (peer pointer, plain
-//    16-byte stores over NVLink), then bumps a counter on every peer.  F3 (all-gather + GEMM):
-//    the TMA producer waits (bounded) on the per-source counters before it loads token rows that
-//    another rank pushed into this rank's gather buffer.
+//    16-byte stores over NVLink), then every CTA bumps a counter on every peer.  F3 (all-gather +
+//    GEMM): the TMA producer waits (bounded) on the per-source counters before it loads token rows
+//    that another rank pushed into this rank's gather buffer.
 //  * Every wait is bounded; a timeout sets the error word and the kernel drains and frees TMEM.
 //
 // Replaces in the reference: ops_fn::matmul (crates/runtime/src/tensor_core.rs:843-892), the
@@ -27,6 +34,7 @@ namespace ub {
 constexpr int BM_W = 128;  // weight rows per tile (MMA M)
 constexpr int BK = 64;     // K elements per stage (one 128-byte swizzle atom of bf16)
 constexpr int UMMA_K = 16;
+constexpr int STAGING_BYTES = 16 * 1024;  // persistent-mode epilogue staging: 2 x [32][128] bf16 or 1 x [32][128] fp32
 
 struct GemmParams {
   int M, N, K;
@@ -37,9 +45,10 @@ struct GemmParams {
   long long ldr;
   int act;          // UB_ACT_*
   int up_row_off;   // DUAL: row offset of the "up" half inside w
-  int out_f32;      // 1: out is float* (ldo in floats), no residual/bias fusion restrictions
-  float out_scale;  // multiplies the result before bias/residual (1.0 = none)
+  int out_f32;      // 1: out is float* (ldo in floats)
+  float out_scale;  // multiplies the accumulator before bias / activation
   int* err;
+  int splits;       // SPLIT-K: cluster size
   // F1: reduce-scatter push.  rs_world == 0 disables.
   int rs_world, rs_rank, rs_rows_per_rank;
   __nv_bfloat16* rs_peer_out[UB_MAX_RANKS];  // each: [world][rows_per_rank][ldo]
@@ -47,7 +56,7 @@ struct GemmParams {
   // F3: all-gather wait.  ag_world == 0 disables.
   int ag_world, ag_rows_per_rank;
   const uint32_t* ag_flags;     // [world] counters in local memory, one per source rank
-  const uint32_t* ag_epoch;     // device word: number of completed uses + 1
+  const uint32_t* ag_epoch;     // device word: number of uses so far (this one included)
   uint32_t ag_signals_per_use;  // counter increments per source rank per use
 };
 
@@ -62,6 +71,8 @@ __device__ __forceinline__ float apply_act(float v, int act) {
     case UB_ACT_RELU: return fmaxf(v, 0.f);
     case UB_ACT_RELU2: { float r = fmaxf(v, 0.f); return r * r; }
     case UB_ACT_QUICK_GELU: return v / (1.f + __expf(-1.702f * v));
+    case UB_ACT_SIGMOID: return 1.f / (1.f + __expf(-v));
+    case UB_ACT_TANH: return tanhf(v);
     default: return v;
   }
 }
@@ -74,38 +85,115 @@ __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
 __device__ __forceinline__ void red_release_sys_add_u32(uint32_t* p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t cta_rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta_rank));
+  return r;
+}
+__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
+}
 
-template <int TN, int STAGES, bool DUAL>
+template <int TN, int STAGES, bool DUAL, bool SPLITK>
 struct GemmSmem {
   static constexpr int A_BYTES = BM_W * BK * 2;  // 16 KB
   static constexpr int B_BYTES = TN * BK * 2;
   static constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * A_BYTES + B_BYTES;
   static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int STAGING_BYTES = TN * BM_W * 4;  // worst case fp32 staging
-  static constexpr int DATA_BYTES = TILE_BYTES > STAGING_BYTES ? TILE_BYTES : STAGING_BYTES;
+  // SPLIT-K parks its fp32 partial tile on top of the (then idle) pipeline stages.
+  static constexpr int PARTIAL_BYTES = (DUAL ? 2 : 1) * TN * BM_W * 4;
+  static constexpr int DATA_BYTES = SPLITK ? (TILE_BYTES > PARTIAL_BYTES ? TILE_BYTES : PARTIAL_BYTES)
+                                           : TILE_BYTES + STAGING_BYTES;
   static constexpr int TOTAL = DATA_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+  static_assert(TOTAL <= 227 * 1024, "shared memory budget exceeded");
 };
 
-template <int TN, int STAGES, bool DUAL>
-__global__ void __launch_bounds__(192, (GemmSmem<TN, STAGES, DUAL>::TOTAL <= 112 * 1024) ? 2 : 1)
+// Final stage of every epilogue: 8 consecutive features of one token row.
+__device__ __forceinline__ void emit8(const GemmParams& p, int m, int nn, float (&v)[8], bool vec_ok) {
+  if (m >= p.M || nn >= p.N) return;
+  if (p.residual != nullptr) {
+    if (vec_ok) {
+      const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + (long long)m * p.ldr + nn);
+      const uint32_t* b = reinterpret_cast<const uint32_t*>(&rr);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { v[2 * e] += bf16_lo(b[e]); v[2 * e + 1] += bf16_hi(b[e]); }
+    } else {
+      for (int e = 0; e < 8 && nn + e < p.N; ++e) v[e] += __bfloat162float(p.residual[(long long)m * p.ldr + nn + e]);
+    }
+  }
+  if (p.out_f32) {
+    float* dst = reinterpret_cast<float*>(p.out) + (long long)m * p.ldo + nn;
+    if (nn + 8 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+      *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+      for (int e = 0; e < 8 && nn + e < p.N; ++e) dst[e] = v[e];
+    }
+    return;
+  }
+  __nv_bfloat16* dst_base = p.out;
+  long long row = m;
+  if (p.rs_world > 0) {
+    int owner = m / p.rs_rows_per_rank;
+    if (owner >= p.rs_world) owner = p.rs_world - 1;
+    dst_base = p.rs_peer_out[owner];
+    row = (long long)p.rs_rank * p.rs_rows_per_rank + (m - owner * p.rs_rows_per_rank);
+  }
+  __nv_bfloat16* dst = dst_base + row * p.ldo + nn;
+  if (vec_ok) {
+    *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
+                                                pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+  } else {
+    for (int e = 0; e < 8 && nn + e < p.N; ++e) dst[e] = __float2bfloat16(v[e]);
+  }
+}
+
+template <int TN, int STAGES, bool DUAL, bool SPLITK>
+__global__ void __launch_bounds__(192, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                const GemmParams p) {
-  using S = GemmSmem<TN, STAGES, DUAL>;
+  using S = GemmSmem<TN, STAGES, DUAL, SPLITK>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::DATA_BYTES);
   uint64_t* empty_bar = full_bar + STAGES;
-  uint64_t* tmem_full_bar = empty_bar + STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+  uint64_t* tmem_full_bar = empty_bar + STAGES;   // [2]
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;   // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * TN;     // first token of this tile
-  const int n0 = blockIdx.y * BM_W;   // first output feature of this tile
+  const int num_m = (p.M + TN - 1) / TN;
+  const int num_n = (p.N + BM_W - 1) / BM_W;
+  const int total_tiles = num_m * num_n;
   const int num_kb = (p.K + BK - 1) / BK;
-  constexpr uint32_t TMEM_COLS_NEEDED = (DUAL ? 2 : 1) * TN;
-  constexpr uint32_t TMEM_COLS = TMEM_COLS_NEEDED < 32 ? 32 : TMEM_COLS_NEEDED;
+  constexpr uint32_t ACC_COLS = (DUAL ? 2 : 1) * TN;
+  // Two accumulator buffers when they fit in the 512 TMEM columns (epilogue overlaps the next tile's MMAs).
+  constexpr int NBUF = (SPLITK || 2 * ACC_COLS > 512) ? 1 : 2;
+  constexpr uint32_t NEED_COLS = NBUF * ACC_COLS;
+  constexpr uint32_t TMEM_COLS = NEED_COLS < 32 ? 32 : NEED_COLS;
+  static_assert(TMEM_COLS <= 512, "TMEM budget exceeded");
+
+  // Work assignment.
+  int unit_begin, unit_step, kb0 = 0, kb1 = num_kb, crank = 0;
+  if (SPLITK) {
+    crank = blockIdx.x;  // cluster = (splits, 1, 1) and gridDim.x == splits
+    unit_begin = blockIdx.y;
+    unit_step = total_tiles;  // exactly one tile per cluster
+    const int per = (num_kb + p.splits - 1) / p.splits;
+    kb0 = crank * per;
+    kb1 = min(num_kb, kb0 + per);
+  } else {
+    unit_begin = blockIdx.x;
+    unit_step = gridDim.x;
+  }
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -113,7 +201,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(tmem_full_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full_bar[b], 1);
+      mbar_init(&tmem_empty_bar[b], 128);
+    }
     fence_mbar_init();
     tma_prefetch_desc(&tmap_w);
     tma_prefetch_desc(&tmap_x);
@@ -130,172 +221,242 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
-      if (p.ag_world > 0) {
-        // Token rows [m0, m0+TN) were pushed by the ranks that own them; wait for those sources.
-        const uint32_t want = (*p.ag_epoch) * p.ag_signals_per_use;
-        int r_lo = m0 / p.ag_rows_per_rank;
-        int m_hi = min(m0 + TN, p.M) - 1;
-        int r_hi = m_hi / p.ag_rows_per_rank;
-        if (r_hi >= p.ag_world) r_hi = p.ag_world - 1;
-        const uint64_t t0 = globaltimer_ns();
-        for (int r = r_lo; r <= r_hi; ++r) {
-          uint32_t it = 0;
-          while (int32_t(ld_acquire_sys_u32(p.ag_flags + r) - want) < 0) {
-            if ((++it & 31u) == 0 && (globaltimer_ns() - t0 > UB_WAIT_NS)) {
-              *abort_flag = 1;
-              set_err(p.err, ERR_FLAG_TIMEOUT, r);
-              break;
-            }
-          }
-        }
-        asm volatile("fence.proxy.async;" ::: "memory");
-      }
       const uint64_t pol_w = l2_policy_evict_first();
       const uint64_t pol_x = l2_policy_evict_last();
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err, 100 + s)) break;  // stop issuing copies
-        uint8_t* st = smem + s * S::STAGE_BYTES;
-        mbar_arrive_expect_tx(&full_bar[s], S::STAGE_BYTES);
-        tma_load_2d_hint(st, &tmap_w, &full_bar[s], kb * BK, n0, pol_w);
-        if (DUAL) tma_load_2d_hint(st + S::A_BYTES, &tmap_w, &full_bar[s], kb * BK, n0 + p.up_row_off, pol_w);
-        tma_load_2d_hint(st + (DUAL ? 2 : 1) * S::A_BYTES, &tmap_x, &full_bar[s], kb * BK, m0, pol_x);
+      uint32_t ag_ready = 0;  // bitmask of source ranks already seen complete
+      int it = 0;
+      bool dead = false;
+      for (int u = unit_begin; u < total_tiles && !dead; u += unit_step) {
+        const int m0 = (u % num_m) * TN, n0 = (u / num_m) * BM_W;
+        if (p.ag_world > 0) {
+          // Token rows [m0, m0+TN) were pushed by the ranks that own them; wait for those sources.
+          const uint32_t want = (*p.ag_epoch) * p.ag_signals_per_use;
+          const int r_lo = m0 / p.ag_rows_per_rank;
+          int r_hi = (min(m0 + TN, p.M) - 1) / p.ag_rows_per_rank;
+          if (r_hi >= p.ag_world) r_hi = p.ag_world - 1;
+          const uint64_t t0 = globaltimer_ns();
+          bool waited = false;
+          for (int r = r_lo; r <= r_hi; ++r) {
+            if (ag_ready >> r & 1u) continue;
+            uint32_t spin = 0;
+            while (int32_t(ld_acquire_sys_u32(p.ag_flags + r) - want) < 0) {
+              if ((++spin & 31u) == 0 && (globaltimer_ns() - t0 > UB_WAIT_NS)) {
+                *abort_flag = 1;
+                set_err(p.err, ERR_FLAG_TIMEOUT, r);
+                break;
+              }
+            }
+            ag_ready |= 1u << r;
+            waited = true;
+          }
+          if (waited) asm volatile("fence.proxy.async;" ::: "memory");
+        }
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err, 100 + s)) { dead = true; break; }
+          uint8_t* st = smem + s * S::STAGE_BYTES;
+          mbar_arrive_expect_tx(&full_bar[s], S::STAGE_BYTES);
+          tma_load_2d_hint(st, &tmap_w, &full_bar[s], kb * BK, n0, pol_w);
+          if (DUAL) tma_load_2d_hint(st + S::A_BYTES, &tmap_w, &full_bar[s], kb * BK, n0 + p.up_row_off, pol_w);
+          tma_load_2d_hint(st + (DUAL ? 2 : 1) * S::A_BYTES, &tmap_x, &full_bar[s], kb * BK, m0, pol_x);
+        }
       }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_bf16(BM_W, TN, 0, 0);
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        if (!mbar_wait(&full_bar[s], ph, abort_flag, p.err, 200 + s)) break;
+      int it = 0, ui = 0;
+      bool dead = false;
+      for (int u = unit_begin; u < total_tiles && !dead; u += unit_step, ++ui) {
+        const int ab = NBUF == 1 ? 0 : (ui & 1);
+        const uint32_t aph = NBUF == 1 ? (ui & 1) : ((ui >> 1) & 1);
+        if (!mbar_wait(&tmem_empty_bar[ab], aph ^ 1, abort_flag, p.err, 400 + ab)) break;
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(smem + s * S::STAGE_BYTES);
-        const uint32_t b_addr = a_addr + (DUAL ? 2 : 1) * S::A_BYTES;
+        const uint32_t d_tmem = tmem_base + ab * ACC_COLS;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, p.err, 200 + s)) { dead = true; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * S::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + (DUAL ? 2 : 1) * S::A_BYTES;
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          const uint64_t bdesc = make_smem_desc_sw128(b_addr + k * UMMA_K * 2, 16, 1024);
-          const uint64_t adesc = make_smem_desc_sw128(a_addr + k * UMMA_K * 2, 16, 1024);
-          const uint32_t acc = (kb | k) != 0 ? 1u : 0u;
-          umma_bf16_ss(tmem_base, adesc, bdesc, idesc, acc);
-          if (DUAL) {
-            const uint64_t a2desc = make_smem_desc_sw128(a_addr + S::A_BYTES + k * UMMA_K * 2, 16, 1024);
-            umma_bf16_ss(tmem_base + TN, a2desc, bdesc, idesc, acc);
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t bdesc = make_smem_desc_sw128(b_addr + k * UMMA_K * 2, 16, 1024);
+            const uint64_t adesc = make_smem_desc_sw128(a_addr + k * UMMA_K * 2, 16, 1024);
+            const uint32_t acc = (kb != kb0 || k != 0) ? 1u : 0u;
+            umma_bf16_ss(d_tmem, adesc, bdesc, idesc, acc);
+            if (DUAL) {
+              const uint64_t a2desc = make_smem_desc_sw128(a_addr + S::A_BYTES + k * UMMA_K * 2, 16, 1024);
+              umma_bf16_ss(d_tmem + TN, a2desc, bdesc, idesc, acc);
+            }
           }
+          umma_commit(&empty_bar[s]);  // stage is free once these MMAs have read it
         }
-        umma_commit(&empty_bar[s]);  // stage is free once these MMAs have read it
+        umma_commit(&tmem_full_bar[ab]);
       }
-      umma_commit(tmem_full_bar);
     }
   } else {
     // ------------------------------ epilogue (warps 2..5) ------------------------------
     const int q = warp & 3;           // TMEM lane quarter this warp may read
     const int et = q * 32 + lane;     // 0..127 : output feature inside the tile == TMEM lane
     const int tid_e = threadIdx.x - 64;
-    mbar_wait(tmem_full_bar, 0, abort_flag, p.err, 300);
-    tc_fence_after();
-    const int n = n0 + et;
-    float bias_v = 0.f;
-    if (p.bias != nullptr && n < p.N) bias_v = __bfloat162float(p.bias[n]);
-    // Staging tile in smem (aliases the pipeline stages, which are idle now): [TN][128] of bf16 or fp32.
-    __nv_bfloat16* stage_bf = reinterpret_cast<__nv_bfloat16*>(smem);
-    float* stage_f = reinterpret_cast<float*>(smem);
-    const uint32_t lane_addr = tmem_base + (uint32_t(q * 32) << 16);
     constexpr int CH = TN >= 32 ? 32 : 16;
+    const bool vec_ok = (p.N % 8 == 0) && (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
+                        (p.residual == nullptr ||
+                         ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
+    int ui = 0, chunk_ctr = 0;
+    for (int u = unit_begin; u < total_tiles; u += unit_step, ++ui) {
+      const int m0 = (u % num_m) * TN, n0 = (u / num_m) * BM_W;
+      const int ab = NBUF == 1 ? 0 : (ui & 1);
+      const uint32_t aph = NBUF == 1 ? (ui & 1) : ((ui >> 1) & 1);
+      mbar_wait(&tmem_full_bar[ab], aph, abort_flag, p.err, 300 + ab);
+      tc_fence_after();
+      const uint32_t lane_addr = tmem_base + ab * ACC_COLS + (uint32_t(q * 32) << 16);
+      if constexpr (SPLITK) {
+        // Park the raw fp32 partial tile in shared memory: [TN][128] (+ a second one for the up half).
+        float* part = reinterpret_cast<float*>(smem);
 #pragma unroll 1
-    for (int c = 0; c < TN / CH; ++c) {
-      uint32_t r[CH];
-      uint32_t r2[CH];
-      if constexpr (CH == 32) {
-        tmem_ld_32x32(lane_addr + c * CH, r);
-        if (DUAL) tmem_ld_32x32(lane_addr + TN + c * CH, r2);
-      } else {
-        tmem_ld_32x16(lane_addr + c * CH, r);
-        if (DUAL) tmem_ld_32x16(lane_addr + TN + c * CH, r2);
-      }
-      tmem_ld_wait();
-#pragma unroll
-      for (int j = 0; j < CH; ++j) {
-        float v = __uint_as_float(r[j]) * p.out_scale;
-        if (DUAL) {
-          v = apply_act(v, p.act) * (__uint_as_float(r2[j]) * p.out_scale);
-        } else {
-          v += bias_v;
-          v = apply_act(v, p.act);
-        }
-        const int tok = c * CH + j;
-        if (p.out_f32) stage_f[tok * BM_W + et] = v;
-        else stage_bf[tok * BM_W + et] = __float2bfloat16(v);
-      }
-    }
-    tc_fence_before();
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    // Coalesced write-out: each token row of the tile is 128 features.
-    if (p.out_f32) {
-      float* outf = reinterpret_cast<float*>(p.out);
-      for (int idx = tid_e; idx < TN * 32; idx += 128) {
-        const int tok = idx >> 5, c4 = idx & 31;
-        const int m = m0 + tok, nn = n0 + c4 * 4;
-        if (m < p.M && nn < p.N) {
-          float4 v = *reinterpret_cast<const float4*>(stage_f + tok * BM_W + c4 * 4);
-          float* dst = outf + (long long)m * p.ldo + nn;
-          if (nn + 4 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-            *reinterpret_cast<float4*>(dst) = v;
+        for (int c = 0; c < TN / CH; ++c) {
+          uint32_t r[CH], r2[CH];
+          if constexpr (CH == 32) {
+            tmem_ld_32x32(lane_addr + c * CH, r);
+            if (DUAL) tmem_ld_32x32(lane_addr + TN + c * CH, r2);
           } else {
-            const float vv[4] = {v.x, v.y, v.z, v.w};
-            for (int e = 0; e < 4 && nn + e < p.N; ++e) dst[e] = vv[e];
+            tmem_ld_32x16(lane_addr + c * CH, r);
+            if (DUAL) tmem_ld_32x16(lane_addr + TN + c * CH, r2);
           }
-        }
-      }
-    } else {
-      const bool vec_ok = (p.N % 8 == 0) && (p.ldo % 8 == 0) &&
-                          ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
-                          (p.residual == nullptr ||
-                           ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
-      for (int idx = tid_e; idx < TN * 16; idx += 128) {
-        const int tok = idx >> 4, c8 = idx & 15;
-        const int m = m0 + tok, nn = n0 + c8 * 8;
-        if (m >= p.M || nn >= p.N) continue;
-        uint4 v = *reinterpret_cast<const uint4*>(stage_bf + tok * BM_W + c8 * 8);
-        __nv_bfloat16* dst_base = p.out;
-        long long row = m;
-        if (p.rs_world > 0) {
-          int owner = m / p.rs_rows_per_rank;
-          if (owner >= p.rs_world) owner = p.rs_world - 1;
-          dst_base = p.rs_peer_out[owner];
-          row = (long long)p.rs_rank * p.rs_rows_per_rank + (m - owner * p.rs_rows_per_rank);
-        }
-        __nv_bfloat16* dst = dst_base + row * p.ldo + nn;
-        if (vec_ok) {
-          if (p.residual != nullptr) {
-            const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + (long long)m * p.ldr + nn);
-            const uint32_t* a = reinterpret_cast<const uint32_t*>(&v);
-            const uint32_t* b = reinterpret_cast<const uint32_t*>(&rr);
-            uint32_t o[4];
+          tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-              o[e] = pack_bf16x2(bf16_lo(a[e]) + bf16_lo(b[e]), bf16_hi(a[e]) + bf16_hi(b[e]));
-            v = make_uint4(o[0], o[1], o[2], o[3]);
+          for (int j = 0; j < CH; ++j) {
+            part[(c * CH + j) * BM_W + et] = __uint_as_float(r[j]);
+            if (DUAL) part[TN * BM_W + (c * CH + j) * BM_W + et] = __uint_as_float(r2[j]);
           }
-          *reinterpret_cast<uint4*>(dst) = v;
-        } else {
-          const __nv_bfloat16* sv = reinterpret_cast<const __nv_bfloat16*>(&v);
-          for (int e = 0; e < 8 && nn + e < p.N; ++e) {
-            float f = __bfloat162float(sv[e]);
-            if (p.residual != nullptr) f += __bfloat162float(p.residual[(long long)m * p.ldr + nn + e]);
-            dst[e] = __float2bfloat16(f);
+        }
+      } else {
+        const int n = n0 + et;
+        float bias_v = 0.f;
+        if (p.bias != nullptr && n < p.N) bias_v = __bfloat162float(p.bias[n]);
+        uint8_t* staging = smem + S::TILE_BYTES;
+#pragma unroll 1
+        for (int c = 0; c < TN / CH; ++c, ++chunk_ctr) {
+          uint32_t r[CH], r2[CH];
+          if constexpr (CH == 32) {
+            tmem_ld_32x32(lane_addr + c * CH, r);
+            if (DUAL) tmem_ld_32x32(lane_addr + TN + c * CH, r2);
+          } else {
+            tmem_ld_32x16(lane_addr + c * CH, r);
+            if (DUAL) tmem_ld_32x16(lane_addr + TN + c * CH, r2);
+          }
+          tmem_ld_wait();
+          if (c == TN / CH - 1) {
+            // Accumulator fully read: hand the TMEM buffer back to the MMA warp.
+            tc_fence_before();
+            mbar_arrive(&tmem_empty_bar[ab]);
+          }
+          if (p.out_f32) {
+            float* stf = reinterpret_cast<float*>(staging);
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+              float v = __uint_as_float(r[j]) * p.out_scale;
+              if (DUAL) v = apply_act(v, p.act) * (__uint_as_float(r2[j]) * p.out_scale);
+              else v = apply_act(v + bias_v, p.act);
+              stf[j * BM_W + et] = v;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            for (int idx = tid_e; idx < CH * 16; idx += 128) {
+              const int tok = idx >> 4, c8 = idx & 15;
+              const float4 lo = *reinterpret_cast<const float4*>(stf + tok * BM_W + c8 * 8);
+              const float4 hi = *reinterpret_cast<const float4*>(stf + tok * BM_W + c8 * 8 + 4);
+              float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+              emit8(p, m0 + c * CH + tok, n0 + c8 * 8, v, vec_ok);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+          } else {
+            __nv_bfloat16* stb = reinterpret_cast<__nv_bfloat16*>(staging + (chunk_ctr & 1) * (STAGING_BYTES / 2));
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+              float v = __uint_as_float(r[j]) * p.out_scale;
+              if (DUAL) v = apply_act(v, p.act) * (__uint_as_float(r2[j]) * p.out_scale);
+              else v = apply_act(v + bias_v, p.act);
+              stb[j * BM_W + et] = __float2bfloat16(v);
+            }
+            // One barrier per chunk: the two staging halves alternate, so the writers of chunk c+2
+            // have all passed the barrier of chunk c+1, i.e. finished reading chunk c.
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            for (int idx = tid_e; idx < CH * 16; idx += 128) {
+              const int tok = idx >> 4, c8 = idx & 15;
+              const uint4 raw = *reinterpret_cast<const uint4*>(stb + tok * BM_W + c8 * 8);
+              const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
+              float v[8];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) { v[2 * e] = bf16_lo(w[e]); v[2 * e + 1] = bf16_hi(w[e]); }
+              emit8(p, m0 + c * CH + tok, n0 + c8 * 8, v, vec_ok);
+            }
           }
         }
       }
     }
-    if (p.rs_world > 0) {
+    if (!SPLITK && p.rs_world > 0) {
       // Publish: every storing thread fences to system scope, then one thread per peer bumps its counter.
       __threadfence_system();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (tid_e < p.rs_world) red_release_sys_add_u32(p.rs_peer_flag[tid_e], 1u);
     }
+  }
+
+  if constexpr (SPLITK) {
+    // All CTAs of the cluster have parked their partials; reduce a slice of token rows each.
+    tc_fence_before();
+    cluster_sync_all();
+    if (warp >= 2 && blockIdx.y < total_tiles) {
+      const int u = blockIdx.y;
+      const int m0 = (u % num_m) * TN, n0 = (u / num_m) * BM_W;
+      const int tid_e = threadIdx.x - 64;
+      const int per = (TN + p.splits - 1) / p.splits;
+      const int r0 = crank * per, r1 = min(TN, r0 + per);
+      const bool vec_ok = (p.N % 8 == 0) && (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
+                          (p.residual == nullptr ||
+                           ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
+      const uint32_t base = smem_u32(smem);
+      for (int idx = tid_e; idx < (r1 - r0) * 16; idx += 128) {
+        const int tok = r0 + (idx >> 4), c8 = idx & 15;
+        const uint32_t off = uint32_t(tok * BM_W + c8 * 8) * 4u;
+        float g[8] = {0, 0, 0, 0, 0, 0, 0, 0}, up[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int s = 0; s < p.splits; ++s) {
+          const uint32_t ra = mapa_u32(base + off, (uint32_t)s);
+          const float4 a = ld_dsmem_f4(ra), b = ld_dsmem_f4(ra + 16);
+          g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w; g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
+          if (DUAL) {
+            const uint32_t rb = mapa_u32(base + uint32_t(TN * BM_W * 4) + off, (uint32_t)s);
+            const float4 c = ld_dsmem_f4(rb), d = ld_dsmem_f4(rb + 16);
+            up[0] += c.x; up[1] += c.y; up[2] += c.z; up[3] += c.w; up[4] += d.x; up[5] += d.y; up[6] += d.z; up[7] += d.w;
+          }
+        }
+        const int nn = n0 + c8 * 8;
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          float x = g[e] * p.out_scale;
+          if (DUAL) {
+            x = apply_act(x, p.act) * (up[e] * p.out_scale);
+          } else {
+            if (p.bias != nullptr && nn + e < p.N) x += __bfloat162float(p.bias[nn + e]);
+            x = apply_act(x, p.act);
+          }
+          v[e] = x;
+        }
+        emit8(p, m0 + tok, nn, v, vec_ok);
+      }
+      if (p.rs_world > 0) {
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (tid_e < p.rs_world) red_release_sys_add_u32(p.rs_peer_flag[tid_e], 1u);
+      }
+    }
+    cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
   }
 
   tc_fence_before();
@@ -329,7 +490,7 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 2-D bf16 tensor map, rows x cols (cols contiguous), box = box_rows x 64 columns, 128-byte swizzle.
+// 2-D bf16 tensor map, rows x cols (cols contiguous), box = box_rows x box_cols, 128-byte swizzle.
 int make_tmap_bf16_2d(CUtensorMap* out, const void* base, long long rows, long long cols, long long ld_elems,
                       int box_rows, int box_cols) {
   EncodeTiledFn fn = get_encode_fn();
@@ -344,25 +505,125 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, long long rows, long l
   return r == CUDA_SUCCESS ? 0 : -(int)r - 1000;
 }
 
-template <int TN, int STAGES, bool DUAL>
-static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
-  using S = GemmSmem<TN, STAGES, DUAL>;
+static int num_sms() {
+  static int sms[UB_MAX_DEVICES] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= UB_MAX_DEVICES) return 148;
+  if (sms[dev] == 0) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    sms[dev] = v;
+  }
+  return sms[dev];
+}
+
+struct GemmPlan { int tn, splits, ctas, tiles; };
+
+static GemmPlan plan_gemm(const UbGemmArgs* a) {
+  GemmPlan pl;
+  const bool dual = a->dual != 0;
+  int tn = a->tile_tokens;
+  if (tn <= 0) {
+    tn = 16;
+    while (tn < a->M && tn < 256) tn <<= 1;
+  }
+  pl.tn = tn;
+  const int num_m = (a->M + tn - 1) / tn, num_n = (a->N + BM_W - 1) / BM_W;
+  pl.tiles = num_m * num_n;
+  const int num_kb = (a->K + BK - 1) / BK;
+  const int sms = num_sms();
+  int splits = a->splits;
+  if (splits <= 0) {
+    splits = 1;
+    if (pl.tiles * 2 <= sms && num_kb >= 8) {
+      splits = sms / pl.tiles;
+      if (splits > 8) splits = 8;
+      if (splits > num_kb / 4) splits = num_kb / 4;
+      if (splits < 1) splits = 1;
+    }
+  }
+  if (splits > 8) splits = 8;
+  if (splits > num_kb) splits = num_kb;
+  while (splits & (splits - 1)) splits &= splits - 1;  // cluster sizes 1, 2, 4, 8
+  while (splits > 1 && (splits - 1) * ((num_kb + splits - 1) / splits) >= num_kb) --splits;  // no empty split
+  if (dual && tn == 256 && splits > 1) {
+    // the parked fp32 partials of a 2 x 256-token tile do not fit in shared memory
+    UbGemmArgs b = *a;
+    b.tile_tokens = 128;
+    return plan_gemm(&b);
+  }
+  pl.splits = splits;
+  pl.ctas = splits > 1 ? splits * pl.tiles : (pl.tiles < sms ? pl.tiles : sms);
+  return pl;
+}
+
+template <int TN, int STAGES, bool DUAL, bool SPLITK>
+static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, const GemmPlan& pl,
+                       cudaStream_t stream) {
+  using S = GemmSmem<TN, STAGES, DUAL, SPLITK>;
   static bool attr_set[UB_MAX_DEVICES] = {};
   int dev = 0;
   cudaGetDevice(&dev);
+  auto kern = gemm_tn_kernel<TN, STAGES, DUAL, SPLITK>;
   if (dev < UB_MAX_DEVICES && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tn_kernel<TN, STAGES, DUAL>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     if (e != cudaSuccess) return -(int)e;
     attr_set[dev] = true;
   }
-  dim3 grid((p.M + TN - 1) / TN, (p.N + BM_W - 1) / BM_W, 1);
-  gemm_tn_kernel<TN, STAGES, DUAL><<<grid, 192, S::TOTAL, stream>>>(tw, tx, p);
-  cudaError_t e = cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = S::TOTAL;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (SPLITK) {
+    cfg.gridDim = dim3(pl.splits, pl.tiles, 1);
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = pl.splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  } else {
+    cfg.gridDim = dim3(pl.ctas, 1, 1);
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, tx, p);
   return e == cudaSuccess ? 0 : -(int)e;
 }
 
+template <bool DUAL, bool SPLITK>
+static int dispatch_tn(int tn, const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p,
+                       const GemmPlan& pl, cudaStream_t st) {
+  // Stage counts fill the 227 KB of one resident CTA per SM.
+  if constexpr (!DUAL) {
+    switch (tn) {
+      case 16: return launch_gemm<16, 10, false, SPLITK>(tw, tx, p, pl, st);
+      case 32: return launch_gemm<32, 9, false, SPLITK>(tw, tx, p, pl, st);
+      case 64: return launch_gemm<64, 8, false, SPLITK>(tw, tx, p, pl, st);
+      case 128: return launch_gemm<128, 6, false, SPLITK>(tw, tx, p, pl, st);
+      case 256: return launch_gemm<256, 4, false, SPLITK>(tw, tx, p, pl, st);
+    }
+  } else {
+    switch (tn) {
+      case 16: return launch_gemm<16, 6, true, SPLITK>(tw, tx, p, pl, st);
+      case 32: return launch_gemm<32, 5, true, SPLITK>(tw, tx, p, pl, st);
+      case 64: return launch_gemm<64, 5, true, SPLITK>(tw, tx, p, pl, st);
+      case 128: return launch_gemm<128, 4, true, SPLITK>(tw, tx, p, pl, st);
+      case 256:
+        // 2 x 256 accumulator columns fill TMEM: single-buffered, and too large to park for split-K.
+        if constexpr (!SPLITK) return launch_gemm<256, 3, true, false>(tw, tx, p, pl, st);
+        else return -5;
+    }
+  }
+  return -4;
+}
+
 }  // namespace ub
+
+extern "C" int ub_gemm_num_ctas(const UbGemmArgs* a) {
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0) return 0;
+  return ub::plan_gemm(a).ctas;
+}
 
 extern "C" int ub_gemm_tn(const UbGemmArgs* a, void* stream_v) {
   using namespace ub;
@@ -371,11 +632,7 @@ extern "C" int ub_gemm_tn(const UbGemmArgs* a, void* stream_v) {
   if (a->K % 8 != 0 || a->ldx % 8 != 0 || a->ldw % 8 != 0) return -2;  // TMA strides must be 16-byte multiples
   if ((reinterpret_cast<uintptr_t>(a->x) & 15) || (reinterpret_cast<uintptr_t>(a->w) & 15)) return -3;
   const bool dual = a->dual != 0;
-  int tn = a->tile_tokens;
-  if (tn <= 0) {
-    tn = 16;
-    while (tn < a->M && tn < 256) tn <<= 1;
-  }
+  const GemmPlan pl = plan_gemm(a);
   GemmParams p;
   p.M = a->M; p.N = a->N; p.K = a->K;
   p.out = reinterpret_cast<__nv_bfloat16*>(a->out);
@@ -388,6 +645,7 @@ extern "C" int ub_gemm_tn(const UbGemmArgs* a, void* stream_v) {
   p.out_f32 = a->out_f32;
   p.out_scale = a->out_scale == 0.f ? 1.f : a->out_scale;
   p.err = a->err;
+  p.splits = pl.splits;
   p.rs_world = a->rs_world; p.rs_rank = a->rs_rank; p.rs_rows_per_rank = a->rs_rows_per_rank;
   p.ag_world = a->ag_world; p.ag_rows_per_rank = a->ag_rows_per_rank;
   p.ag_flags = a->ag_flags; p.ag_epoch = a->ag_epoch; p.ag_signals_per_use = a->ag_signals_per_use;
@@ -399,26 +657,12 @@ extern "C" int ub_gemm_tn(const UbGemmArgs* a, void* stream_v) {
   const long long w_rows = dual ? (long long)a->w_rows_total : (long long)a->N;
   int rc = make_tmap_bf16_2d(&tw, a->w, w_rows, a->K, a->ldw, BM_W, BK);
   if (rc != 0) return rc;
-  rc = make_tmap_bf16_2d(&tx, a->x, a->M, a->K, a->ldx, tn, BK);
+  rc = make_tmap_bf16_2d(&tx, a->x, a->M, a->K, a->ldx, pl.tn, BK);
   if (rc != 0) return rc;
-  if (!dual) {
-    switch (tn) {
-      // Stage counts: token tiles up to 128 keep two CTAs resident per SM (one CTA's epilogue hides
-      // behind the other's main loop); the 256-token tile owns the SM.
-      case 16: return launch_gemm<16, 6, false>(tw, tx, p, stream);
-      case 32: return launch_gemm<32, 5, false>(tw, tx, p, stream);
-      case 64: return launch_gemm<64, 4, false>(tw, tx, p, stream);
-      case 128: return launch_gemm<128, 3, false>(tw, tx, p, stream);
-      case 256: return launch_gemm<256, 4, false>(tw, tx, p, stream);
-    }
-  } else {
-    switch (tn) {
-      case 16: return launch_gemm<16, 3, true>(tw, tx, p, stream);
-      case 32: return launch_gemm<32, 3, true>(tw, tx, p, stream);
-      case 64: return launch_gemm<64, 5, true>(tw, tx, p, stream);
-      case 128: return launch_gemm<128, 4, true>(tw, tx, p, stream);
-      case 256: return launch_gemm<256, 3, true>(tw, tx, p, stream);
-    }
+  if (pl.splits > 1) {
+    return dual ? dispatch_tn<true, true>(pl.tn, tw, tx, p, pl, stream)
+                : dispatch_tn<false, true>(pl.tn, tw, tx, p, pl, stream);
   }
-  return -4;
+  return dual ? dispatch_tn<true, false>(pl.tn, tw, tx, p, pl, stream)
+              : dispatch_tn<false, false>(pl.tn, tw, tx, p, pl, stream);
 }

@@ -45,6 +45,7 @@ typedef struct UbGemmArgs {
   int out_f32;
   float out_scale;      /* 0 or 1 = none */
   int tile_tokens;      /* 0 = auto; else 16/32/64/128/256 */
+  int splits;           /* 0 = auto; 1 = no split-K; 2/4/8 = cluster size of the split-K reduction */
   /* F1: push rows to the rank that owns the token instead of writing `out`. */
   int rs_world, rs_rank, rs_rows_per_rank;
   void* rs_peer_out[UB_MAX_RANKS];
@@ -56,6 +57,8 @@ typedef struct UbGemmArgs {
   uint32_t ag_signals_per_use;
 } UbGemmArgs;
 int ub_gemm_tn(const UbGemmArgs* args, void* stream);
+/* Number of CTAs the launch for `args` will use; each CTA signals every peer once in F1 mode. */
+int ub_gemm_num_ctas(const UbGemmArgs* args);
 
 /* ---------------- K5 : normalisation ---------------- */
 typedef struct UbNormArgs {
@@ -155,6 +158,8 @@ typedef struct UbSampleArgs {
   int* err;
 } UbSampleArgs;
 int ub_sample(const UbSampleArgs* args, void* stream);
+/* vals/ids [world, B] per-shard greedy winners -> out_ids [B]; lowest id wins ties. */
+int ub_argmax_merge(const float* vals, const int* ids, int world, int B, int* out_ids, void* stream);
 
 /* ---------------- K9 / K10 / misc element-wise ---------------- */
 int ub_embed_gather(const int* ids, const void* table, void* out, int T, int H, int V, float scale, int* err,

@@ -53,6 +53,26 @@ def test_gemm_tile_variants(tile):
     _close(y, x.float() @ w.float().t())
 
 
+@pytest.mark.parametrize("splits", [2, 4, 8])
+@pytest.mark.parametrize("M,N,K,dual", [(256, 768, 4096, 0), (40, 512, 1792, 0), (256, 1792, 4096, 1), (16, 256, 8192, 1)])
+def test_gemm_splitk_cluster(splits, M, N, K, dual):
+    from unillm_b200.ops import cuda_ops
+
+    x = _rand(M, K, seed=21)
+    w = _rand(N * (2 if dual else 1), K, scale=1 / math.sqrt(K), seed=22)
+    b, r = _rand(N, seed=23), _rand(M, N, seed=24)
+    if dual:
+        y = cuda_ops.gemm_tn(x, w, dual_rows=N, act="silu", splits=splits, residual=r)
+        ref = torch.nn.functional.silu(x.float() @ w[:N].float().t()) * (x.float() @ w[N:].float().t()) + r.float()
+    else:
+        y = cuda_ops.gemm_tn(x, w, bias=b, residual=r, splits=splits)
+        ref = x.float() @ w.float().t() + b.float() + r.float()
+    _close(y, ref)
+    y2 = cuda_ops.gemm_tn(x, w, dual_rows=N, act="silu", splits=splits, residual=r) if dual else \
+        cuda_ops.gemm_tn(x, w, bias=b, residual=r, splits=splits)
+    assert torch.equal(y, y2)
+
+
 def test_gemm_bias_residual_act_f32():
     from unillm_b200.ops import cuda_ops
 

@@ -59,6 +59,8 @@ def bench_gemm(results):
         # (M, N, K, dual) : Llama-3-8B decode / prefill shapes
         (16, 6144, 4096, 0), (64, 6144, 4096, 0), (256, 6144, 4096, 0), (256, 4096, 4096, 0),
         (256, 14336, 4096, 1), (256, 4096, 14336, 0), (256, 128256, 4096, 0),
+        # tensor-parallel (TP=8) per-rank decode shapes: few tiles -> cluster split-K
+        (256, 768, 4096, 0), (256, 4096, 512, 0), (256, 1792, 4096, 1), (256, 4096, 1792, 0), (256, 16032, 4096, 0),
         (2048, 6144, 4096, 0), (2048, 14336, 4096, 1), (2048, 4096, 14336, 0), (8192, 8192, 8192, 0),
     ]
     for M, N, K, dual in shapes:

@@ -38,7 +38,7 @@ class UbGemmArgs(C.Structure):
         ("M", i32), ("N", i32), ("K", i32),
         ("ldx", i64), ("ldw", i64), ("ldo", i64), ("ldr", i64),
         ("act", i32), ("dual", i32), ("up_row_off", i32), ("w_rows_total", i32), ("out_f32", i32),
-        ("out_scale", f32), ("tile_tokens", i32),
+        ("out_scale", f32), ("tile_tokens", i32), ("splits", i32),
         ("rs_world", i32), ("rs_rank", i32), ("rs_rows_per_rank", i32),
         ("rs_peer_out", vp * UB_MAX_RANKS), ("rs_peer_flag", vp * UB_MAX_RANKS),
         ("ag_world", i32), ("ag_rows_per_rank", i32),
@@ -140,6 +140,8 @@ def cuda_lib() -> C.CDLL:
             if hasattr(lib, name):
                 getattr(lib, name).restype = i32
                 getattr(lib, name).argtypes = [vp, vp]
+        lib.ub_gemm_num_ctas.restype = i32
+        lib.ub_gemm_num_ctas.argtypes = [vp]
         lib.ub_cuda_error_string.restype = C.c_char_p
         _cuda = lib
         return lib

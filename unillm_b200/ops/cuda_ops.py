@@ -63,7 +63,7 @@ def _bf16c(t: torch.Tensor, name: str) -> None:
 # ---------------------------------------------------------------------------------------------
 def gemm_tn(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
             residual: Optional[torch.Tensor] = None, act: Optional[str] = None, out: Optional[torch.Tensor] = None,
-            out_dtype: torch.dtype = torch.bfloat16, out_scale: float = 1.0, tile_tokens: int = 0,
+            out_dtype: torch.dtype = torch.bfloat16, out_scale: float = 1.0, tile_tokens: int = 0, splits: int = 0,
             dual_rows: int = 0, rs: Optional[dict] = None, ag: Optional[dict] = None) -> torch.Tensor:
     """``out[M, N] = act(x[M, K] @ w[N, K]^T * out_scale + bias) + residual`` on tcgen05 tensor cores.
 
@@ -103,6 +103,7 @@ def gemm_tn(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = 
     a.out_f32 = 1 if out.dtype == torch.float32 else 0
     a.out_scale = out_scale
     a.tile_tokens = tile_tokens
+    a.splits = splits
     if bias is not None:
         _bf16c(bias, "bias")
     if residual is not None:
