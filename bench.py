@@ -1,0 +1,267 @@
+"""Headline benchmark: output tokens/s of the Llama-3-8B architecture served by the engine.
+
+``python bench.py --gpus N --steps K --warmup W`` (for N > 1 launched under ``torch.distributed.run``,
+one rank per GPU, tensor parallel over all N ranks).
+
+Workload (the prefix-sharing serving configuration, in steady state): ``--batch`` concurrent requests
+(default 256), every request = a 1024-token prefix shared by all requests + a unique 128-token suffix
+(random ids), 128 greedy output tokens, random-init bf16 weights, paged KV with 16-token blocks and the
+radix prefix cache on.  The request stream never dries up: whenever a request finishes a new one is
+queued, and the first wave gets staggered output budgets so that from the first timed step on, every
+step retires and admits about batch/128 requests.  One "step" is one engine iteration: decode of all
+running sequences + chunked prefill of the newly admitted suffixes + sampling.
+
+Two timings of the same K steps are reported:
+  * ``value``  : output tokens / device time, device time = sum over steps of the CUDA-event interval
+                 around the step's metadata upload + kernels, maximum over ranks;
+  * ``e2e``    : output tokens / wall time of ``LLMEngine.step()`` (scheduler, pinned-host -> device copy
+                 of the step's inputs, kernels, device -> host read of the sampled tokens), barrier and
+                 synchronize on both sides, maximum over ranks.
+Model weights (16 GB) are far larger than L2, so every step streams its inputs from HBM.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+MODELS = {
+    "llama3-8b": dict(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,
+                      num_attention_heads=32, num_key_value_heads=8, rope_theta=500000.0, rms_norm_eps=1e-5,
+                      max_position_embeddings=8192),
+    "llama2-7b": dict(vocab_size=32000, hidden_size=4096, intermediate_size=11008, num_hidden_layers=32,
+                      num_attention_heads=32, num_key_value_heads=32, rope_theta=10000.0, rms_norm_eps=1e-5,
+                      max_position_embeddings=4096),
+    "llama3-70b": dict(vocab_size=128256, hidden_size=8192, intermediate_size=28672, num_hidden_layers=80,
+                       num_attention_heads=64, num_key_value_heads=8, rope_theta=500000.0, rms_norm_eps=1e-5,
+                       max_position_embeddings=8192),
+    "tiny": dict(vocab_size=4096, hidden_size=1024, intermediate_size=2048, num_hidden_layers=4,
+                 num_attention_heads=8, num_key_value_heads=8, rope_theta=10000.0, rms_norm_eps=1e-5,
+                 max_position_embeddings=4096),
+}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=3)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = float(f[1])
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def reference_arm(args):
+    # The reference is a Rust workspace with no Python packaging: `pip install --no-index ... /root/reference`
+    # answers "neither setup.py nor pyproject.toml found", and there is no cargo/rustc on this machine or on
+    # the GPU box to build it another way.
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "reference is a Rust/Candle CPU workspace: not pip-installable (no setup.py/pyproject.toml) "
+                      "and no Rust toolchain offline; it has no GPU or multi-GPU path to run"}))
+    return 0
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="llama3-8b", choices=sorted(MODELS))
+    ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--prefix-len", type=int, default=1024)
+    ap.add_argument("--suffix-len", type=int, default=128)
+    ap.add_argument("--output-len", type=int, default=128)
+    ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--profile-ops", action="store_true", help="print device ms per op over the timed steps (eager mode)")
+    ap.add_argument("--baseline-collectives", action="store_true",
+                    help="tensor parallel with NCCL all-reduce between separate kernels instead of the fused path")
+    args = ap.parse_args(argv)
+    if args.impl == "reference":
+        return reference_arm(args)
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        args.gpus = world
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    group = None
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+        group = dist.group.WORLD
+
+    from unillm_b200.engine.llm_engine import LLMEngine
+    from unillm_b200.engine.runner import GpuModelRunner, RunnerWeights, TpContext
+    from unillm_b200.models import configs as C
+    from unillm_b200.models.families import LlamaModel
+    from unillm_b200.ops import cuda_ops
+    from unillm_b200.sampling import SamplingParams
+
+    cfg = C.LlamaConfig(**MODELS[args.model])
+    spec = LlamaModel.spec_from_config(cfg)
+    B, PL, SL, OL = args.batch, args.prefix_len, args.suffix_len, args.output_len
+    bs = 16
+    max_len = PL + SL + OL + bs
+    blocks_needed = PL // bs + (B + 8) * ((SL + OL) // bs + 2)
+    num_blocks = max(2 * blocks_needed, 1024)
+    tp = TpContext(rank, world, group, fused=not args.baseline_collectives)
+    weights = RunnerWeights.random(spec, dev, rank, world, seed=1234)
+    if tp.fused:
+        from unillm_b200.dist.fused import FusedComm
+
+        tp.comm = FusedComm.create(spec, rank, world, group, max_tokens=8192 + B, device=dev)
+    runner = GpuModelRunner(spec, weights, num_blocks=num_blocks, block_size=bs, max_num_seqs=B,
+                            max_num_batched_tokens=8192, max_model_len=max_len, tp=tp, device=dev,
+                            use_cuda_graphs=not args.no_graphs)
+    eng = LLMEngine(runner, num_blocks=num_blocks, block_size=bs, max_num_seqs=B, max_num_batched_tokens=8192,
+                    max_model_len=max_len, enable_prefix_caching=True)
+
+    g = torch.Generator().manual_seed(2024)
+    V = cfg.vocab_size
+    prefix = torch.randint(0, V, (PL,), generator=g).tolist()
+
+    def new_prompt():
+        return prefix + torch.randint(0, V, (SL,), generator=g).tolist()
+
+    # first wave: staggered budgets put the engine in steady state (about B/OL requests retire per step)
+    for i in range(B):
+        eng.add_request(new_prompt(), SamplingParams(temperature=0.0, max_tokens=1 + (i * OL) // B, ignore_eos=True))
+    params = SamplingParams(temperature=0.0, max_tokens=OL, ignore_eos=True)
+
+    def top_up():
+        while len(eng.waiting) < 8:
+            eng.add_request(new_prompt(), params)
+
+    top_up()
+    # setup (untimed): run until every request of the first wave has produced its first token
+    first_wave = [eng.seqs[i] for i in range(B)]
+    while any(s.first_token_time is None for s in first_wave) and eng.stats.steps < 400:
+        eng.step()
+        top_up()
+    for _ in range(args.warmup):
+        eng.step()
+        top_up()
+    torch.cuda.synchronize()
+    cuda_ops.check_device_errors()
+
+    if args.profile_ops:
+        runner.use_cuda_graphs = False
+        runner.profile = True
+    K = args.steps
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    sampler = ClockSampler(local)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    l0, h0, d0 = runner.launches, runner.h2d_bytes, runner.d2h_bytes
+    tokens = 0
+    t0 = time.perf_counter()
+    for k in range(K):
+        eng.step_events = evs[k]
+        outs = eng.step()
+        tokens += len(outs)
+        top_up()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    wall = time.perf_counter() - t0
+    clocks = sampler.stop()
+    eng.step_events = None
+    dev_ms = sum(a.elapsed_time(b) for a, b in evs)
+    cuda_ops.check_device_errors()
+    launches = runner.launches - l0
+    h2d = (runner.h2d_bytes - h0) / K
+    d2h = (runner.d2h_bytes - d0) / K
+    if world > 1:
+        t = torch.tensor([dev_ms, wall], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms, wall = t.tolist()
+    if args.profile_ops and rank == 0:
+        rep = runner.profile_report()
+        tot = sum(rep.values())
+        for name, ms in sorted(rep.items(), key=lambda kv: -kv[1]):
+            print(f"  {name:40s} {ms / K:9.3f} ms/step {100 * ms / tot:5.1f}%", file=sys.stderr)
+    if rank == 0:
+        value = tokens / (dev_ms / 1e3)
+        e2e = tokens / wall
+        out = {
+            "metric": "output tok/s, Llama-3-8B architecture, engine steady state (device-timed, max over ranks)",
+            "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": args.warmup,
+            "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (random token ids, random-init weights)",
+            "config": {"model": args.model, "global_batch": B, "seq_len": PL + SL + OL,
+                       "parallelism": f"tp{world}" + ("" if tp.fused or world == 1 else "-nccl-baseline"),
+                       "workload": f"{PL}-token shared prefix + {SL} unique + {OL} greedy outputs, continuous batching",
+                       "kv_block": bs, "prefix_cache": True, "cuda_graphs": not args.no_graphs,
+                       "l2": "inputs larger than L2: each step streams the model weights (>= 2 GB per GPU) from HBM",
+                       "output_tokens_timed": tokens},
+            "e2e": {"value": e2e, "unit": "tok/s", "ms_per_step": wall * 1e3 / K, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "engine": {"prefill_tokens": eng.stats.prefill_tokens, "decode_tokens": eng.stats.decode_tokens,
+                       "cached_tokens": eng.stats.cached_tokens, "preemptions": eng.stats.preemptions,
+                       "graphs": len(runner.graphs)},
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,400 @@
+"""``LLMEngine``: the iteration-level serving loop -- request queue, continuous batching with chunked
+prefill, radix prefix reuse over the paged block pool, preemption by recomputation, and one call into a
+model runner per step.
+
+The reference has the pieces but never connects them: its scheduler forms batches once
+(``crates/scheduler/src/lib.rs:271-323``), its KV crate only does bookkeeping and its engine sleeps
+instead of running a model (``crates/inference/src/engine.rs:322-379``).  Here every step:
+
+  1. running sequences that finished prefill get one decode token each (a new block when they cross a
+     block boundary; if the pool is empty the radix tree evicts unlocked leaves, then the youngest
+     running sequence is preempted and later recomputed);
+  2. the remaining token budget goes to prefill chunks -- first to sequences already in flight, then to
+     waiting requests in policy order, whose longest cached prefix (whole blocks) is taken from the radix
+     tree instead of being recomputed;
+  3. blocks that this step fills completely are published to the radix tree at scheduling time, so a
+     request admitted in the same step can already share them (the KV append of every layer runs before
+     that layer's attention);
+  4. the runner executes the packed step and returns one sampled token per finished prefill / decode row.
+
+Every rank of a tensor-parallel group runs this loop on the same request stream and takes identical
+decisions (it is deterministic), so no per-step control traffic is needed.
+"""
+from __future__ import annotations
+
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Callable, Deque, Dict, List, Optional, Sequence, Tuple
+
+from ..kv.block_pool import BlockPool, RadixTree
+from ..sampling import SamplingParams
+from ..types import InvalidInput, MemoryError_
+from .runner import StepBatch
+
+WAITING, RUNNING, FINISHED, ABORTED = "waiting", "running", "finished", "aborted"
+
+
+@dataclass
+class Sequence:
+    seq_id: int
+    prompt_ids: List[int]
+    params: SamplingParams
+    priority: int = 0
+    arrival: float = field(default_factory=time.perf_counter)
+    output_ids: List[int] = field(default_factory=list)
+    blocks: List[int] = field(default_factory=list)
+    num_computed: int = 0            # tokens whose KV is in the cache
+    num_cached: int = 0              # of those, how many came from the radix tree
+    published_blocks: int = 0        # leading blocks already offered to the radix tree
+    radix_node: int = 0
+    status: str = WAITING
+    finish_reason: Optional[str] = None
+    first_token_time: Optional[float] = None
+    finish_time: Optional[float] = None
+    token_times: List[float] = field(default_factory=list)
+    preemptions: int = 0
+
+    @property
+    def tokens(self) -> List[int]:
+        return self.prompt_ids + self.output_ids
+
+    @property
+    def total_len(self) -> int:
+        return len(self.prompt_ids) + len(self.output_ids)
+
+    @property
+    def prefill_done(self) -> bool:
+        return self.num_computed >= self.total_len - 1 and len(self.output_ids) > 0
+
+
+@dataclass
+class StepOutput:
+    seq_id: int
+    token: int
+    finished: bool
+    finish_reason: Optional[str] = None
+
+
+@dataclass
+class EngineStats:
+    steps: int = 0
+    prefill_tokens: int = 0
+    decode_tokens: int = 0
+    cached_tokens: int = 0
+    preemptions: int = 0
+    finished: int = 0
+    generated_tokens: int = 0
+
+
+class LLMEngine:
+    def __init__(self, runner, *, num_blocks: int, block_size: int = 16, max_num_seqs: int = 256,
+                 max_num_batched_tokens: int = 8192, max_model_len: int = 8192, enable_prefix_caching: bool = True,
+                 enable_chunked_prefill: bool = True, eos_token_id: Optional[int] = None,
+                 policy: Optional[Callable[[List[Sequence]], List[Sequence]]] = None, seed: int = 0):
+        self.runner = runner
+        self.block_size = block_size
+        self.pool = BlockPool(num_blocks, block_size)
+        self.radix = RadixTree(self.pool) if enable_prefix_caching else None
+        self.max_num_seqs, self.max_tokens, self.max_model_len = max_num_seqs, max_num_batched_tokens, max_model_len
+        self.chunked = enable_chunked_prefill
+        self.eos_token_id = eos_token_id
+        self.policy = policy
+        self.seed = seed
+        self.waiting: Deque[Sequence] = deque()
+        self.running: List[Sequence] = []
+        self.seqs: Dict[int, Sequence] = {}
+        self._next_id = 0
+        self.stats = EngineStats()
+        self.step_events = None     # optional (start, end) CUDA events recorded around the runner launch
+
+    # ------------------------------------------------------------------------------------------
+    def add_request(self, prompt_ids: Sequence[int], params: Optional[SamplingParams] = None, priority: int = 0,
+                    seq_id: Optional[int] = None) -> int:
+        if len(prompt_ids) == 0:
+            raise InvalidInput("empty prompt")
+        params = params or SamplingParams()
+        if len(prompt_ids) + params.max_tokens > self.max_model_len:
+            raise InvalidInput(f"prompt ({len(prompt_ids)}) + max_tokens ({params.max_tokens}) exceeds "
+                               f"max_model_len {self.max_model_len}")
+        sid = self._next_id if seq_id is None else seq_id
+        self._next_id = max(self._next_id, sid) + 1
+        s = Sequence(sid, list(prompt_ids), params, priority)
+        self.seqs[sid] = s
+        self.waiting.append(s)
+        return sid
+
+    def abort(self, seq_id: int) -> bool:
+        s = self.seqs.get(seq_id)
+        if s is None or s.status in (FINISHED, ABORTED):
+            return False
+        if s.status == RUNNING:
+            self.running.remove(s)
+        else:
+            self.waiting.remove(s)
+        self._release(s, publish=False)
+        s.status, s.finish_reason, s.finish_time = ABORTED, "aborted", time.perf_counter()
+        return True
+
+    def has_unfinished(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ------------------------------------------------------------------------------------------
+    # block management
+    # ------------------------------------------------------------------------------------------
+    def _alloc(self, n: int) -> Optional[List[int]]:
+        if n <= 0:
+            return []
+        got = self.pool.try_allocate(n)
+        if got is None and self.radix is not None:
+            self.radix.evict(n - self.pool.num_free())
+            got = self.pool.try_allocate(n)
+        return got
+
+    def _release(self, s: Sequence, publish: bool) -> None:
+        if publish and self.radix is not None:
+            self._publish(s, s.num_computed)
+        for b in s.blocks:
+            self.pool.free(b)
+        s.blocks = []
+        if self.radix is not None and s.radix_node:
+            self.radix.unlock(s.radix_node)
+        s.radix_node = 0
+        s.published_blocks = 0
+
+    def _publish(self, s: Sequence, upto_tokens: int) -> None:
+        """Offer the blocks that are completely filled by the first ``upto_tokens`` tokens to the radix tree."""
+        nb = min(upto_tokens // self.block_size, len(s.blocks))
+        if self.radix is None or nb <= s.published_blocks:
+            return
+        self.radix.insert(s.tokens[: nb * self.block_size], s.blocks[:nb])
+        s.published_blocks = nb
+
+    def _preempt_one(self, keep: Sequence) -> bool:
+        """Free the blocks of the youngest running sequence other than ``keep``; it is recomputed later."""
+        for cand in reversed(self.running):
+            if cand is not keep:
+                self.running.remove(cand)
+                self._release(cand, publish=True)
+                cand.num_computed = cand.num_cached = 0
+                cand.status = WAITING
+                cand.preemptions += 1
+                self.stats.preemptions += 1
+                self.waiting.appendleft(cand)
+                return True
+        return False
+
+    def _ensure_blocks(self, s: Sequence, upto_tokens: int) -> bool:
+        need = (upto_tokens + self.block_size - 1) // self.block_size - len(s.blocks)
+        while need > 0:
+            got = self._alloc(need)
+            if got is not None:
+                s.blocks.extend(got)
+                return True
+            if not self._preempt_one(s):
+                return False
+        return True
+
+    # ------------------------------------------------------------------------------------------
+    # scheduling
+    # ------------------------------------------------------------------------------------------
+    def _admit(self, s: Sequence) -> None:
+        """Look up the longest cached prefix of a waiting sequence and take references on its blocks."""
+        s.blocks, s.num_computed, s.num_cached, s.published_blocks = [], 0, 0, 0
+        if self.radix is None:
+            return
+        toks = s.tokens
+        blocks, node = self.radix.match_prefix(toks[: len(toks) - 1])   # at least one token is always computed
+        if blocks:
+            for b in blocks:
+                self.pool.incref(b)
+            self.radix.lock(node)
+            s.blocks = list(blocks)
+            s.radix_node = node
+            s.num_computed = s.num_cached = len(blocks) * self.block_size
+            s.published_blocks = len(blocks)
+
+    def schedule(self) -> Tuple[Optional[StepBatch], List[Tuple[Sequence, int, bool]]]:
+        """Returns the packed step and, per scheduled sequence, (sequence, tokens this step, samples?)."""
+        bs = self.block_size
+        decode: List[Sequence] = []
+        for s in list(self.running):
+            if s.status != RUNNING or not s.prefill_done:
+                continue
+            if s not in self.running:
+                continue                      # preempted while making room for an earlier one
+            if not self._ensure_blocks(s, s.total_len):
+                continue
+            decode.append(s)
+        decode = [s for s in decode if s in self.running]
+        budget = self.max_tokens - len(decode)
+        chunks: List[Tuple[Sequence, int]] = []
+        for s in list(self.running):
+            if s not in self.running or s.prefill_done or s in decode or budget <= 0:
+                continue
+            left = s.total_len - s.num_computed
+            n = min(left, budget) if self.chunked else left
+            if n <= 0 or n > budget:
+                continue
+            if self._ensure_blocks(s, s.num_computed + n):
+                chunks.append((s, n))
+                budget -= n
+        # making room may have preempted sequences that were already picked above
+        decode = [s for s in decode if s in self.running]
+        chunks = [(s, n) for s, n in chunks if s in self.running]
+        budget = self.max_tokens - len(decode) - sum(n for _, n in chunks)
+        # from here on nothing is preempted, so blocks filled by this step can be published now
+        for s, n in chunks:
+            self._publish(s, s.num_computed + n)
+        order = list(self.waiting)
+        if self.policy is not None:
+            order = self.policy(order)
+        for s in order:
+            if budget <= 0 or len(self.running) >= self.max_num_seqs:
+                break
+            self._admit(s)
+            remaining = s.total_len - s.num_computed
+            n = min(remaining, budget) if self.chunked else remaining
+            if n > budget or not self._ensure_blocks_no_preempt(s, s.num_computed + n):
+                self._release(s, publish=False)
+                s.num_computed = s.num_cached = 0
+                break
+            self.waiting.remove(s)
+            s.status = RUNNING
+            self.running.append(s)
+            self.stats.cached_tokens += s.num_cached
+            chunks.append((s, n))
+            budget -= n
+            self._publish(s, s.num_computed + n)
+        if not decode and not chunks:
+            return None, []
+        token_ids: List[int] = []
+        positions: List[int] = []
+        slots: List[int] = []
+        seq_lens: List[int] = []
+        tables: List[List[int]] = []
+        sample_rows: List[int] = []
+        plan: List[Tuple[Sequence, int, bool]] = []
+        for s in decode:
+            p = s.total_len - 1
+            token_ids.append(s.tokens[p])
+            positions.append(p)
+            slots.append(s.blocks[p // bs] * bs + p % bs)
+            seq_lens.append(p + 1)
+            tables.append(s.blocks)
+            sample_rows.append(len(token_ids) - 1)
+            plan.append((s, 1, True))
+        q_lens: List[int] = []
+        for s, n in chunks:
+            toks = s.tokens
+            for p in range(s.num_computed, s.num_computed + n):
+                token_ids.append(toks[p])
+                positions.append(p)
+                slots.append(s.blocks[p // bs] * bs + p % bs)
+            seq_lens.append(s.num_computed + n)
+            tables.append(s.blocks)
+            q_lens.append(n)
+            done = s.num_computed + n >= s.total_len
+            if done:
+                sample_rows.append(len(token_ids) - 1)
+            plan.append((s, n, done))
+        shared = self._shared_prefix(decode) if len(decode) >= 8 else 0
+        sampled = [s for s, _, smp in plan if smp]
+        greedy = all(s.params.greedy for s in sampled)
+        batch = StepBatch(token_ids, positions, slots, len(decode), seq_lens, tables, q_lens, sample_rows, shared,
+                          seed=self.seed, step=self.stats.steps)
+        if not greedy:
+            batch.temperature = [s.params.temperature for s in sampled]
+            batch.top_p = [s.params.top_p for s in sampled]
+            batch.top_k = [s.params.top_k or 0 for s in sampled]
+        return batch, plan
+
+    def _ensure_blocks_no_preempt(self, s: Sequence, upto_tokens: int) -> bool:
+        need = (upto_tokens + self.block_size - 1) // self.block_size - len(s.blocks)
+        if need <= 0:
+            return True
+        got = self._alloc(need)
+        if got is None:
+            return False
+        s.blocks.extend(got)
+        return True
+
+    def _shared_prefix(self, decode: List[Sequence]) -> int:
+        """Number of leading tokens (whole blocks) whose blocks are identical in all decode sequences."""
+        first = decode[0].blocks
+        n = min(min(len(s.blocks) for s in decode), min((s.total_len - 1) // self.block_size for s in decode))
+        lo = 0
+        while lo < n:
+            b = first[lo]
+            if any(s.blocks[lo] != b for s in decode):
+                break
+            lo += 1
+        return lo * self.block_size
+
+    # ------------------------------------------------------------------------------------------
+    # stepping
+    # ------------------------------------------------------------------------------------------
+    def step(self) -> List[StepOutput]:
+        batch, plan = self.schedule()
+        if batch is None:
+            if self.waiting and not self.running:
+                raise MemoryError_("a waiting request does not fit in the KV cache even when it is empty")
+            return []
+        ev = self.step_events
+        if ev is not None:
+            ev[0].record()
+        self.runner.launch(batch)
+        if ev is not None:
+            ev[1].record()
+        ids = self.runner.fetch()
+        return self._process(plan, ids)
+
+    def _process(self, plan, ids: List[int]) -> List[StepOutput]:
+        now = time.perf_counter()
+        outs: List[StepOutput] = []
+        k = 0
+        self.stats.steps += 1
+        for s, n, sampled in plan:
+            s.num_computed += n
+            if n == 1 and len(s.output_ids) > 0 and sampled:
+                self.stats.decode_tokens += 1
+            else:
+                self.stats.prefill_tokens += n
+            if not sampled:
+                continue
+            tok = int(ids[k])
+            k += 1
+            s.output_ids.append(tok)
+            s.token_times.append(now)
+            if s.first_token_time is None:
+                s.first_token_time = now
+            self.stats.generated_tokens += 1
+            reason = None
+            p = s.params
+            if not p.ignore_eos and self.eos_token_id is not None and tok == self.eos_token_id:
+                reason = "stop"
+            elif tok in p.stop_token_ids:
+                reason = "stop"
+            elif len(s.output_ids) >= p.max_tokens:
+                reason = "length"
+            elif s.total_len >= self.max_model_len:
+                reason = "length"
+            if reason is not None:
+                s.status, s.finish_reason, s.finish_time = FINISHED, reason, now
+                self.running.remove(s)
+                self._release(s, publish=True)
+                self.stats.finished += 1
+            outs.append(StepOutput(s.seq_id, tok, reason is not None, reason))
+        return outs
+
+    def run_to_completion(self, max_steps: int = 1 << 30) -> Dict[int, List[int]]:
+        n = 0
+        while self.has_unfinished() and n < max_steps:
+            self.step()
+            n += 1
+        return {sid: s.output_ids for sid, s in self.seqs.items()}
+
+    def generate(self, prompts: Sequence[Sequence[int]], params: Optional[SamplingParams] = None) -> List[List[int]]:
+        ids = [self.add_request(p, params) for p in prompts]
+        self.run_to_completion()
+        return [self.seqs[i].output_ids for i in ids]

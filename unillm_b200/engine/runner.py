@@ -1,0 +1,720 @@
+"""``GpuModelRunner``: executes one engine step of a decoder model on one B200 with the hand-written
+sm_100a kernels and a paged KV cache.
+
+Per layer (tensor-parallel rank view):
+
+    norm (K5)  ->  QKV GEMM (K1, tcgen05)  ->  RoPE + KV append (K6)  ->  paged attention (K3 prefill rows,
+    K4 decode rows, optional cascade over a radix-shared prefix)  ->  o_proj GEMM with the residual add in
+    its epilogue  ->  norm  ->  gate/up GEMM with SwiGLU in its epilogue (K2)  ->  down GEMM + residual
+
+then final norm on the rows that are sampled, the (vocab-parallel) lm_head GEMM and the device sampler
+(K8).  Token metadata for a step arrives as ONE packed int32 buffer copied from pinned host memory;
+pure-decode steps are captured in CUDA graphs keyed by (padded batch, shared-prefix length).
+
+Tensor parallelism (``TpContext``): column-parallel QKV / gate-up, row-parallel o / down, KV heads and
+the vocabulary sharded.  With ``fused=True`` the two reductions per layer run inside the GEMM and norm
+kernels over NVSwitch peer memory (GEMM epilogue pushes rows to the owning rank = reduce-scatter, the
+norm kernel sums the partials, normalises its token shard and pushes it to every rank = all-gather,
+and the next GEMM's TMA producer waits on the arrival counters); with ``fused=False`` the same math uses
+NCCL all-reduce between library-style separate kernels -- the measured baseline.
+
+Reference counterpart: the per-token loop of ``UniLLMBackend::generate`` / ``LlamaModelV2::forward_with_cache``
+(``crates/runtime/src/benchmark/unillm_backend.rs:69-211``, ``models_v2/llama.rs:421-464, 654-680,
+1027-1156``), which is batch-1, CPU-only and uses a contiguous cache.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..models.spec import DecoderSpec
+from ..ops import cuda_ops as K
+from ..precompute import alibi_slopes
+from ..types import InvalidInput, UnsupportedOperation
+
+
+@dataclass
+class StepBatch:
+    """Host-side description of one engine step (built by the scheduler).
+
+    Token rows are ordered: first the ``num_decode`` decode sequences (one row each), then the prefill
+    chunks.  ``seq_lens`` is the KV length of each sequence after this step's tokens are appended."""
+
+    token_ids: List[int]
+    positions: List[int]
+    slot_mapping: List[int]
+    num_decode: int
+    seq_lens: List[int]
+    block_tables: List[List[int]]
+    prefill_q_lens: List[int] = field(default_factory=list)
+    sample_rows: List[int] = field(default_factory=list)
+    shared_prefix_len: int = 0          # tokens of KV that ALL decode sequences share (whole blocks)
+    # sampling (per sampled row); None = greedy
+    temperature: Optional[List[float]] = None
+    top_p: Optional[List[float]] = None
+    top_k: Optional[List[int]] = None
+    seed: int = 0
+    step: int = 0
+
+
+def shard_rows(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    n = w.shape[0] // world
+    return w[rank * n:(rank + 1) * n]
+
+
+def shard_cols(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    n = w.shape[1] // world
+    return w[:, rank * n:(rank + 1) * n]
+
+
+class RunnerWeights:
+    """Device weights of one rank in kernel layout (bf16, fused QKV / gate-up, TP-sharded)."""
+
+    def __init__(self, spec: DecoderSpec, params: Dict[str, torch.Tensor], device, rank: int = 0, world: int = 1):
+        self.spec, self.rank, self.world = spec, rank, world
+        s = spec
+        if s.num_heads % world != 0:
+            raise InvalidInput(f"{s.num_heads} heads not divisible by tensor parallel size {world}")
+        if s.num_kv_heads % world != 0:
+            raise UnsupportedOperation(f"{s.num_kv_heads} KV heads with tensor parallel size {world}: "
+                                       "KV head replication is not implemented")
+        self.hq = s.num_heads // world
+        self.hkv = s.num_kv_heads // world
+        D = s.head_dim
+
+        def dev(t):
+            return t.to(device=device, dtype=torch.bfloat16).contiguous()
+
+        self.t: Dict[str, torch.Tensor] = {}
+        p = params
+        self.t["embed"] = dev(p["embed"])
+        for n in ("pos_embed", "embed_norm.w", "embed_norm.b", "final_norm.w", "final_norm.b", "project_in", "project_out"):
+            if n in p:
+                self.t[n] = dev(p[n])
+        lm = p["embed"] if s.tie_embeddings else p["lm_head"]
+        if s.vocab_size % world != 0:
+            raise InvalidInput(f"vocab {s.vocab_size} not divisible by tensor parallel size {world}")
+        self.vocab_shard = s.vocab_size // world
+        self.t["lm_head"] = dev(shard_rows(lm, rank, world)) if (world > 1 or not s.tie_embeddings) else self.t["embed"]
+        if "lm_head_bias" in p:
+            self.t["lm_head_bias"] = dev(shard_rows(p["lm_head_bias"], rank, world))
+        for i in range(s.num_layers):
+            L = f"layers.{i}."
+            for n in ("ln1.w", "ln1.b", "ln2.w", "ln2.b", "q_norm", "k_norm"):
+                if L + n in p:
+                    self.t[L + n] = dev(p[L + n])
+            wqkv = p[L + "wqkv"]
+            q, k, v = wqkv.split([s.q_size, s.kv_size, s.kv_size], dim=0)
+            self.t[L + "wqkv"] = dev(torch.cat([shard_rows(q, rank, world), shard_rows(k, rank, world),
+                                                shard_rows(v, rank, world)], 0))
+            if L + "bqkv" in p:
+                qb, kb, vb = p[L + "bqkv"].split([s.q_size, s.kv_size, s.kv_size])
+                self.t[L + "bqkv"] = dev(torch.cat([shard_rows(qb, rank, world), shard_rows(kb, rank, world),
+                                                    shard_rows(vb, rank, world)]))
+            self.t[L + "wo"] = dev(shard_cols(p[L + "wo"], rank, world))
+            if L + "bo" in p:
+                self.t[L + "bo"] = dev(p[L + "bo"] if rank == 0 else torch.zeros_like(p[L + "bo"]))
+            if L + "w_gate_up" in p:
+                g, u = p[L + "w_gate_up"].chunk(2, 0)
+                self.t[L + "w_gate_up"] = dev(torch.cat([shard_rows(g, rank, world), shard_rows(u, rank, world)], 0))
+            if L + "w_up" in p:
+                self.t[L + "w_up"] = dev(shard_rows(p[L + "w_up"], rank, world))
+                if L + "b_up" in p:
+                    self.t[L + "b_up"] = dev(shard_rows(p[L + "b_up"], rank, world))
+            if L + "w_down" in p:
+                self.t[L + "w_down"] = dev(shard_cols(p[L + "w_down"], rank, world))
+                if L + "b_down" in p:
+                    self.t[L + "b_down"] = dev(p[L + "b_down"] if rank == 0 else torch.zeros_like(p[L + "b_down"]))
+            if L + "router" in p:
+                # experts: tensor-parallel inside each expert here; expert-parallel layouts are built by MoeRunner
+                self.t[L + "router"] = dev(p[L + "router"])
+                gu = p[L + "experts_gate_up"]
+                E = gu.shape[0]
+                if s.moe.gated:
+                    g, u = gu.chunk(2, 1)
+                    n = g.shape[1] // world
+                    gu = torch.cat([g[:, rank * n:(rank + 1) * n], u[:, rank * n:(rank + 1) * n]], 1)
+                else:
+                    n = gu.shape[1] // world
+                    gu = gu[:, rank * n:(rank + 1) * n]
+                self.t[L + "experts_gate_up"] = dev(gu)
+                dn = p[L + "experts_down"]
+                n = dn.shape[2] // world
+                self.t[L + "experts_down"] = dev(dn[:, :, rank * n:(rank + 1) * n])
+                if L + "shared_gate_up" in p:
+                    g, u = p[L + "shared_gate_up"].chunk(2, 0)
+                    self.t[L + "shared_gate_up"] = dev(torch.cat([shard_rows(g, rank, world), shard_rows(u, rank, world)], 0))
+                    self.t[L + "shared_down"] = dev(shard_cols(p[L + "shared_down"], rank, world))
+
+    @staticmethod
+    def random(spec: DecoderSpec, device, rank: int = 0, world: int = 1, seed: int = 0) -> "RunnerWeights":
+        """Random-init weights generated directly on the device, shard by shard (no host copy): the
+        benchmark path for 8B-70B architectures.  Every rank draws the same full-size tensor for a given
+        name from a per-tensor seed and keeps its shard, so TP=1 and TP=N hold the same model."""
+        self = RunnerWeights.__new__(RunnerWeights)
+        self.spec, self.rank, self.world = spec, rank, world
+        s = spec
+        self.hq, self.hkv = s.num_heads // world, s.num_kv_heads // world
+        self.vocab_shard = s.vocab_size // world
+        self.t = {}
+        H, I = s.hidden_size, s.intermediate_size
+        std = s.initializer_range
+        counter = [0]
+
+        def rnd(rows, cols, row0=0, nrows=None, col0=0, ncols=None):
+            """Rows [row0, row0+nrows) x cols [col0, col0+ncols) of a virtual [rows, cols] N(0, std) matrix."""
+            counter[0] += 1
+            nrows = rows if nrows is None else nrows
+            ncols = cols if ncols is None else ncols
+            g = torch.Generator(device=device).manual_seed(seed * 1000003 + counter[0])
+            # generate in row blocks so that a shard equals the same rows of the full matrix
+            out = torch.empty(nrows, ncols, dtype=torch.bfloat16, device=device)
+            blk = 1024
+            for r in range(0, rows, blk):
+                rr = min(blk, rows - r)
+                lo, hi = max(r, row0), min(r + rr, row0 + nrows)
+                g.manual_seed((seed * 1000003 + counter[0]) * 65537 + r)
+                if lo >= hi:
+                    continue
+                full = torch.randn(rr, cols, generator=g, device=device, dtype=torch.float32) * std
+                out[lo - row0:hi - row0] = full[lo - r:hi - r, col0:col0 + ncols].to(torch.bfloat16)
+            return out
+
+        ones = lambda n: torch.ones(n, dtype=torch.bfloat16, device=device)
+        self.t["embed"] = rnd(s.vocab_size, H)
+        self.t["final_norm.w"] = ones(H)
+        vs = self.vocab_shard
+        if s.tie_embeddings:
+            self.t["lm_head"] = self.t["embed"][rank * vs:(rank + 1) * vs] if world > 1 else self.t["embed"]
+        else:
+            self.t["lm_head"] = rnd(s.vocab_size, H, rank * vs, vs)
+        qs, ks = s.q_size // world, s.kv_size // world
+        for i in range(s.num_layers):
+            L = f"layers.{i}."
+            self.t[L + "ln1.w"], self.t[L + "ln2.w"] = ones(H), ones(H)
+            q = rnd(s.q_size, H, rank * qs, qs)
+            k = rnd(s.kv_size, H, rank * ks, ks)
+            v = rnd(s.kv_size, H, rank * ks, ks)
+            self.t[L + "wqkv"] = torch.cat([q, k, v], 0)
+            self.t[L + "wo"] = rnd(H, s.q_size, 0, H, rank * qs, qs)
+            if s.layer_is_moe(i):
+                m = s.moe
+                Ie = m.intermediate_size // world
+                self.t[L + "router"] = rnd(m.num_experts, H)
+                gu = torch.empty(m.num_experts, 2 * Ie, H, dtype=torch.bfloat16, device=device)
+                dn = torch.empty(m.num_experts, H, Ie, dtype=torch.bfloat16, device=device)
+                for e in range(m.num_experts):
+                    gu[e, :Ie] = rnd(m.intermediate_size, H, rank * Ie, Ie)
+                    gu[e, Ie:] = rnd(m.intermediate_size, H, rank * Ie, Ie)
+                    dn[e] = rnd(H, m.intermediate_size, 0, H, rank * Ie, Ie)
+                self.t[L + "experts_gate_up"], self.t[L + "experts_down"] = gu, dn
+            else:
+                Is = I // world
+                g = rnd(I, H, rank * Is, Is)
+                u = rnd(I, H, rank * Is, Is)
+                self.t[L + "w_gate_up"] = torch.cat([g, u], 0)
+                self.t[L + "w_down"] = rnd(H, I, 0, H, rank * Is, Is)
+        return self
+
+    def nbytes(self) -> int:
+        seen, n = set(), 0
+        for t in self.t.values():
+            if t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                n += t.numel() * t.element_size()
+        return n
+
+
+class TpContext:
+    """Tensor-parallel plumbing of one rank: NCCL group for the baseline path, and (when fused) the
+    symmetric buffers + counters that the fused kernels use.  ``world == 1`` needs none of it."""
+
+    def __init__(self, rank: int = 0, world: int = 1, group=None, fused: bool = False):
+        self.rank, self.world, self.group, self.fused = rank, world, group, fused and world > 1
+        self.comm = None   # unillm_b200.dist.fused.FusedComm when fused
+
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(t, group=self.group)
+        return t
+
+    def all_gather_cat(self, t: torch.Tensor, dim: int = -1) -> torch.Tensor:
+        if self.world == 1:
+            return t
+        import torch.distributed as dist
+
+        outs = [torch.empty_like(t) for _ in range(self.world)]
+        dist.all_gather(outs, t.contiguous(), group=self.group)
+        return torch.cat(outs, dim=dim)
+
+
+class _OpTimer:
+    def __init__(self, runner, name):
+        self.r, self.name = runner, name
+
+    def __enter__(self):
+        if self.r.profile and not self.r._graph_mode:
+            self.a = torch.cuda.Event(enable_timing=True)
+            self.a.record()
+        else:
+            self.a = None
+
+    def __exit__(self, *exc):
+        if self.a is not None:
+            b = torch.cuda.Event(enable_timing=True)
+            b.record()
+            self.r._prof_events.append((self.name, self.a, b))
+        return False
+
+
+class GpuModelRunner:
+    META_INTS = 1 << 20   # capacity of the packed per-step metadata buffer (int32 words)
+
+    def __init__(self, spec: DecoderSpec, weights: RunnerWeights, *, num_blocks: int, block_size: int = 16,
+                 max_num_seqs: int = 256, max_num_batched_tokens: int = 8192, max_model_len: int = 8192,
+                 tp: Optional[TpContext] = None, device=None, use_cuda_graphs: bool = True):
+        if spec.norm not in ("rms", "layer") or spec.post_ln or spec.embed_proj_dim:
+            raise UnsupportedOperation("this spec is served by the generic model path, not the fused runner")
+        self.spec, self.w = spec, weights
+        self.tp = tp or TpContext()
+        self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        self.block_size, self.num_blocks = block_size, num_blocks
+        self.max_num_seqs, self.max_tokens, self.max_model_len = max_num_seqs, max_num_batched_tokens, max_model_len
+        self.max_blocks_per_seq = (max_model_len + block_size - 1) // block_size
+        self.use_cuda_graphs = use_cuda_graphs
+        s, dev = spec, self.device
+        hkv, D = weights.hkv, s.head_dim
+        self.k_cache = [torch.zeros(num_blocks, hkv, block_size, D, dtype=torch.bfloat16, device=dev)
+                        for _ in range(s.num_layers)]
+        self.v_cache = [torch.zeros(num_blocks, hkv, block_size, D, dtype=torch.bfloat16, device=dev)
+                        for _ in range(s.num_layers)]
+        self.alibi = None
+        if s.pos == "alibi":
+            sl = alibi_slopes(s.num_heads)
+            self.alibi = sl[weights.rank * weights.hq:(weights.rank + 1) * weights.hq].to(dev)
+        # packed metadata: pinned host staging + device mirror with fixed addresses (graph friendly)
+        self.meta_host = torch.empty(self.META_INTS, dtype=torch.int32, pin_memory=True)
+        self.meta_dev = torch.empty(self.META_INTS, dtype=torch.int32, device=dev)
+        self.fmeta_host = torch.empty(4 * max_num_seqs, dtype=torch.float32, pin_memory=True)
+        self.fmeta_dev = torch.empty(4 * max_num_seqs, dtype=torch.float32, device=dev)
+        self.out_ids_dev = torch.zeros(4 * max_num_seqs, dtype=torch.int32, device=dev)
+        self.out_ids_host = torch.zeros(4 * max_num_seqs, dtype=torch.int32, pin_memory=True)
+        self.attn_scratch = torch.empty(max_num_seqs * weights.hq * 16 * (D + 2), dtype=torch.float32, device=dev)
+        self.graphs: Dict[tuple, tuple] = {}
+        self.profile = False
+        self._prof_events = []
+        self._graph_mode = False
+        self.launches = 0          # kernels of this library launched so far (counted on the host)
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self._layout = None
+
+    # ------------------------------------------------------------------------------------------
+    # metadata packing
+    # ------------------------------------------------------------------------------------------
+    def _pack(self, b: StepBatch, bucketed: bool = False):
+        """Writes the step's integer metadata into the pinned buffer and returns the layout
+        (name -> (offset, length)); one H2D copy moves all of it.
+
+        With ``bucketed`` the batch is padded to a shape from a small set so that a captured CUDA graph
+        can be replayed: decode rows to a power of two, prefill tokens to a multiple of 128 (the padding
+        forms a dummy sequence that writes no KV), prefill sequences to a power of two (empty dummies),
+        and every decode row plus the last row of every prefill sequence is sampled."""
+        D = b.num_decode
+        nseq = len(b.seq_lens)
+        P = nseq - D
+        mb = self.max_blocks_per_seq
+        q_lens = list(b.prefill_q_lens)
+        p_lens = list(b.seq_lens[D:])
+        Tp = sum(q_lens)
+        Dp, Pp, tpad = D, P, 0
+        if bucketed:
+            Dp = self._bucket(D) if D else 0
+            if P:
+                tpad = (-Tp) % 128
+                Pp = self._bucket(P + (1 if tpad else 0))
+                if tpad:
+                    q_lens.append(tpad)
+                    p_lens.append(tpad)
+                q_lens += [0] * (Pp - len(q_lens))
+                p_lens += [0] * (Pp - len(p_lens))
+        pad = Dp - D
+        h = self.meta_host
+        off = 0
+        lay = {}
+
+        def put(name, vals, n=None, fill=0):
+            nonlocal off
+            n = len(vals) if n is None else n
+            if off + n > self.META_INTS:
+                raise InvalidInput("step metadata exceeds the staging buffer")
+            if len(vals):
+                h[off:off + len(vals)] = torch.as_tensor(vals, dtype=torch.int32)
+            if n > len(vals):
+                h[off + len(vals):off + n] = fill
+            lay[name] = (off, n)
+            off += (n + 3) // 4 * 4     # keep every array 16-byte aligned
+
+        # decode rows first (padded rows point at slot -1 / block 0 / length 1 so kernels stay in bounds)
+        put("token_ids", b.token_ids[:D] + [0] * pad + b.token_ids[D:] + [0] * tpad)
+        put("positions", b.positions[:D] + [0] * pad + b.positions[D:] + [0] * tpad)
+        put("slot_mapping", b.slot_mapping[:D] + [-1] * pad + b.slot_mapping[D:] + [-1] * tpad)
+        put("seq_lens_d", b.seq_lens[:D] + [1] * pad)
+        bt = torch.zeros((Dp + Pp, mb), dtype=torch.int32)
+        for i, row in enumerate(b.block_tables):
+            r = i if i < D else i + pad
+            bt[r, :len(row)] = torch.as_tensor(row, dtype=torch.int32)
+        put("block_tables", bt.reshape(-1))
+        put("seq_lens_p", p_lens)
+        qs = [0]
+        for ql in q_lens:
+            qs.append(qs[-1] + ql)
+        put("q_start", qs)
+        if bucketed:
+            rows = list(range(Dp)) + [Dp + max(qs[j + 1] - 1, 0) for j in range(Pp)]
+            sel = []
+            for r in b.sample_rows:
+                if r < D:
+                    sel.append(r)
+                else:
+                    # r is the last row of some prefill sequence j: find it from the unpadded prefix sums
+                    j = next(jj for jj in range(P) if D + qs[jj + 1] - 1 == r)
+                    sel.append(Dp + j)
+            lay["_sel"] = sel
+        else:
+            rows = [r if r < D else r + pad for r in b.sample_rows]
+            lay["_sel"] = list(range(len(rows)))
+        put("sample_rows", rows)
+        lay["_T"], lay["_D"], lay["_Dp"], lay["_P"], lay["_S"] = Dp + Tp + tpad, D, Dp, Pp, len(rows)
+        mq = max(q_lens) if q_lens else 0
+        lay["_max_q"] = self._bucket(mq) if (bucketed and mq) else mq
+        lay["_used"] = off
+        return lay
+
+    def _view(self, lay, name):
+        o, n = lay[name]
+        return self.meta_dev[o:o + n]
+
+    def _upload(self, lay):
+        n = lay["_used"]
+        self.meta_dev[:n].copy_(self.meta_host[:n], non_blocking=True)
+        self.h2d_bytes += n * 4
+
+    # ------------------------------------------------------------------------------------------
+    # layer math
+    # ------------------------------------------------------------------------------------------
+    def _prof(self, name: str):
+        """Context manager timing one op with CUDA events when profiling is on (eager mode only)."""
+        return _OpTimer(self, name)
+
+    def profile_report(self) -> Dict[str, float]:
+        """Milliseconds per op name accumulated since profiling was switched on (synchronises)."""
+        torch.cuda.synchronize()
+        out: Dict[str, float] = {}
+        for name, a, b in self._prof_events:
+            out[name] = out.get(name, 0.0) + a.elapsed_time(b)
+        self._prof_events = []
+        return out
+
+    def _norm(self, x, name, residual=None, want_h=False):
+        s, t = self.spec, self.w.t
+        self.launches += 1
+        with self._prof("norm"):
+            return self._norm_impl(x, name, residual, want_h)
+
+    def _norm_impl(self, x, name, residual=None, want_h=False):
+        s, t = self.spec, self.w.t
+        return K.norm(x, t[name + ".w"], bias=t.get(name + ".b"), residual=residual, eps=s.norm_eps,
+                      kind="rms" if s.norm == "rms" else "layer", weight_offset_one=s.norm_weight_offset_one,
+                      want_residual_out=want_h)
+
+    def _gemm(self, x, w, tag="gemm", **kw):
+        self.launches += 1
+        with self._prof(f"{tag}[{x.shape[0]}x{w.shape[0]}x{w.shape[1]}]"):
+            return K.gemm_tn(x, w, **kw)
+
+    def _attention(self, i, qkv, lay, shared_prefix_len):
+        """qkv [T, (hq + 2 hkv) * D] already rotated and appended -> attention output [T, hq * D]."""
+        s, w = self.spec, self.w
+        D, hq, hkv = s.head_dim, w.hq, w.hkv
+        T, Dp, P = lay["_T"], lay["_Dp"], lay["_P"]
+        q = qkv.view(T, hq + 2 * hkv, D)[:, :hq]           # strided view: row stride (hq + 2 hkv) * D
+        out = torch.empty(T, hq, D, dtype=torch.bfloat16, device=qkv.device)
+        kc, vc = self.k_cache[i], self.v_cache[i]
+        bt = self._view(lay, "block_tables").view(Dp + P, self.max_blocks_per_seq)
+        scale = s.attn_scale
+        if Dp > 0:
+            qd, od = q[:Dp], out[:Dp]
+            sl = self._view(lay, "seq_lens_d")
+            if shared_prefix_len >= 4 * self.block_size and Dp >= 8:
+                # cascade: one GEMM-shaped pass of all decode queries over the shared prefix blocks, one
+                # per-sequence pass over the unique suffixes, then a merge of the two partials
+                lse_a = torch.empty(Dp, hq, dtype=torch.float32, device=qkv.device)
+                lse_b = torch.empty(Dp, hq, dtype=torch.float32, device=qkv.device)
+                oa = torch.empty(Dp, hq, D, dtype=torch.bfloat16, device=qkv.device)
+                ob = torch.empty(Dp, hq, D, dtype=torch.bfloat16, device=qkv.device)
+                with self._prof("attn_shared_prefix"):
+                    K.attn_prefill(qd, kc, vc, bt[:1], self._prefix_len_dev(shared_prefix_len), self._q_start_all(Dp),
+                                   Dp, scale=scale, causal=False, window=0, alibi_slopes=None, out=oa, lse=lse_a,
+                                   return_lse=True)
+                with self._prof("attn_decode_suffix"):
+                    K.attn_decode(qd, kc, vc, bt[:Dp], sl, scale=scale, window=s.window, kv_start=shared_prefix_len,
+                                  alibi_slopes=self.alibi, out=ob, lse=lse_b, return_lse=True, splits=1)
+                with self._prof("attn_merge"):
+                    K.attn_merge(oa, lse_a, ob, lse_b, out=od)
+                self.launches += 3
+            else:
+                with self._prof("attn_decode"):
+                    K.attn_decode(qd, kc, vc, bt[:Dp], sl, scale=scale, window=s.window, alibi_slopes=self.alibi,
+                                  out=od, scratch=self.attn_scratch,
+                                  max_seq_len=self.max_model_len if self._graph_mode else int(self._max_len_d))
+                self.launches += 1
+        if P > 0:
+            with self._prof("attn_prefill"):
+                K.attn_prefill(q[Dp:], kc, vc, bt[Dp:], self._view(lay, "seq_lens_p"), self._view(lay, "q_start"),
+                               lay["_max_q"], scale=scale, causal=True, window=s.window, alibi_slopes=self.alibi,
+                               out=out[Dp:])
+            self.launches += 1
+        return out.view(T, hq * D)
+
+    def _prefix_len_dev(self, n: int) -> torch.Tensor:
+        c = getattr(self, "_plen_cache", None)
+        if c is None:
+            c = self._plen_cache = {}
+        if n not in c:
+            c[n] = torch.tensor([n], dtype=torch.int32, device=self.device)
+        return c[n]
+
+    def _q_start_all(self, n: int) -> torch.Tensor:
+        c = getattr(self, "_qsa_cache", None)
+        if c is None:
+            c = self._qsa_cache = {}
+        if n not in c:
+            c[n] = torch.tensor([0, n], dtype=torch.int32, device=self.device)
+        return c[n]
+
+    def _mlp(self, i, h, residual):
+        s, t = self.spec, self.w.t
+        L = f"layers.{i}."
+        tp = self.tp
+        if s.layer_is_moe(i):
+            from .moe_runner import moe_forward
+
+            return moe_forward(self, i, h, residual)
+        if s.mlp == "gated":
+            I = t[L + "w_gate_up"].shape[0] // 2
+            a = self._gemm(h, t[L + "w_gate_up"], dual_rows=I, act=s.act)
+        else:
+            a = self._gemm(h, t[L + "w_up"], bias=t.get(L + "b_up"), act=s.act)
+        if tp.world == 1:
+            return self._gemm(a, t[L + "w_down"], bias=t.get(L + "b_down"), residual=residual)
+        y = self._gemm(a, t[L + "w_down"], bias=t.get(L + "b_down"))
+        tp.all_reduce(y)
+        self.launches += 1
+        return K.add(y, residual)
+
+    def _forward_tokens(self, lay, shared_prefix_len: int) -> torch.Tensor:
+        """Runs all layers on the packed step; returns the sampled token ids tensor (device, [S])."""
+        s, t, tp = self.spec, self.w.t, self.tp
+        T = lay["_T"]
+        ids = self._view(lay, "token_ids")
+        pos = self._view(lay, "positions")
+        slots = self._view(lay, "slot_mapping")
+        x = K.embed_gather(ids, t["embed"], scale=s.embed_scale)
+        self.launches += 1
+        if s.pos == "learned":
+            x = x + t["pos_embed"][(pos + s.learned_pos_offset).long()]
+        if s.embed_norm:
+            x = K.norm(x, t["embed_norm.w"], bias=t["embed_norm.b"], eps=s.norm_eps, kind="layer")
+        rs = s.residual_scale
+        for i in range(s.num_layers):
+            L = f"layers.{i}."
+            h = self._norm(x, L + "ln1")
+            qkv = self._gemm(h, t[L + "wqkv"], bias=t.get(L + "bqkv"))
+            with self._prof("rope_kv_append"):
+                K.rope_kv_append(qkv, pos, slots, self.k_cache[i], self.v_cache[i], num_q_heads=self.w.hq,
+                                 num_kv_heads=self.w.hkv, head_dim=s.head_dim,
+                                 rotary_dim=s.rd if s.pos == "rope" else 0, theta=s.rope_theta,
+                                 pos_scale=s.rope_pos_scale, interleaved=s.rope_interleaved,
+                                 q_norm_w=t.get(L + "q_norm"), k_norm_w=t.get(L + "k_norm"), norm_eps=s.norm_eps,
+                                 llama3_scaling=s.rope_llama3)
+            self.launches += 1
+            a = self._attention(i, qkv, lay, shared_prefix_len)
+            if s.parallel_residual:
+                m_in = h if s.parallel_shared_norm else self._norm(x, L + "ln2")
+                o = self._gemm(a, t[L + "wo"], bias=t.get(L + "bo"))
+                m = self._mlp_noresid(i, m_in)
+                y = K.add(o, m)
+                if tp.world > 1:
+                    tp.all_reduce(y)
+                x = K.add(x, y, 1.0, rs)
+                self.launches += 2
+                continue
+            if tp.world == 1 and rs == 1.0:
+                x = self._gemm(a, t[L + "wo"], bias=t.get(L + "bo"), residual=x)
+            else:
+                o = self._gemm(a, t[L + "wo"], bias=t.get(L + "bo"))
+                tp.all_reduce(o)
+                x = K.add(x, o, 1.0, rs)
+                self.launches += 1
+            h2 = self._norm(x, L + "ln2")
+            if rs == 1.0:
+                x = self._mlp(i, h2, x)
+            else:
+                m = self._mlp_noresid(i, h2)
+                if tp.world > 1:
+                    tp.all_reduce(m)
+                x = K.add(x, m, 1.0, rs)
+                self.launches += 1
+        return x
+
+    def _mlp_noresid(self, i, h):
+        s, t = self.spec, self.w.t
+        L = f"layers.{i}."
+        if s.mlp == "gated":
+            I = t[L + "w_gate_up"].shape[0] // 2
+            a = self._gemm(h, t[L + "w_gate_up"], dual_rows=I, act=s.act)
+        else:
+            a = self._gemm(h, t[L + "w_up"], bias=t.get(L + "b_up"), act=s.act)
+        return self._gemm(a, t[L + "w_down"], bias=t.get(L + "b_down"))
+
+    def _logits_and_sample(self, x, lay, b: Optional[StepBatch], fl) -> torch.Tensor:
+        s, t, tp = self.spec, self.w.t, self.tp
+        S = lay["_S"]
+        rows = self._view(lay, "sample_rows")
+        xs = x.index_select(0, rows.long()) if S != x.shape[0] else x
+        if s.final_norm:
+            xs = self._norm(xs, "final_norm")
+        logits = self._gemm(xs, t["lm_head"], bias=t.get("lm_head_bias"), out_scale=s.logit_scale)
+        out = self.out_ids_dev[:S]
+        greedy = fl is None
+        if tp.world == 1:
+            if greedy:
+                K.sample(logits, out_ids=out)
+            else:
+                K.sample(logits, temperature=fl["temperature"], top_p=fl["top_p"], top_k=fl["top_k"],
+                         seed=fl["seed"], step=fl["step"], out_ids=out)
+            self.launches += 1
+            return out
+        if greedy:
+            ids, vals = K.sample(logits, vocab_offset=tp.rank * self.w.vocab_shard, return_vals=True)
+            allv = tp.all_gather_cat(vals[None], dim=0)
+            alli = tp.all_gather_cat(ids[None], dim=0)
+            K.argmax_merge(allv.contiguous(), alli.contiguous(), out=out)
+            self.launches += 2
+            return out
+        full = tp.all_gather_cat(logits, dim=-1)
+        K.sample(full, temperature=fl["temperature"], top_p=fl["top_p"], top_k=fl["top_k"], seed=fl["seed"],
+                 step=fl["step"], out_ids=out)
+        self.launches += 1
+        return out
+
+    # ------------------------------------------------------------------------------------------
+    # step execution
+    # ------------------------------------------------------------------------------------------
+    @staticmethod
+    def _bucket(n: int) -> int:
+        b = 1
+        while b < n:
+            b <<= 1
+        return b
+
+    def _sampling_tensors(self, b: StepBatch, S: int):
+        if b.temperature is None or all(t <= 0 for t in b.temperature):
+            return None
+        f = self.fmeta_host
+        f[:S] = torch.as_tensor(b.temperature, dtype=torch.float32)
+        f[S:2 * S] = torch.as_tensor(b.top_p if b.top_p is not None else [1.0] * S, dtype=torch.float32)
+        self.fmeta_dev[:2 * S].copy_(f[:2 * S], non_blocking=True)
+        self.h2d_bytes += 8 * S
+        tk = None
+        if b.top_k is not None and any(k and k > 0 for k in b.top_k):
+            tk = torch.as_tensor([k or 0 for k in b.top_k], dtype=torch.int32).to(self.device, non_blocking=True)
+            self.h2d_bytes += 4 * S
+        return {"temperature": self.fmeta_dev[:S], "top_p": self.fmeta_dev[S:2 * S], "top_k": tk, "seed": b.seed,
+                "step": b.step}
+
+    MAX_GRAPHS = 48
+
+    def launch(self, b: StepBatch) -> int:
+        """Uploads the step's metadata and enqueues all kernels on the current stream.  Returns the number of
+        sampled rows; ``fetch`` reads them back."""
+        D = b.num_decode
+        if len(b.token_ids) > self.max_tokens + self.max_num_seqs:
+            raise InvalidInput("step exceeds max_num_batched_tokens")
+        greedy = b.temperature is None or all(t <= 0 for t in b.temperature)
+        graphable = self.use_cuda_graphs and greedy and len(b.token_ids) > 0
+        self._max_len_d = max(b.seq_lens[:D]) if D else 0
+        if graphable:
+            lay = self._pack(b, bucketed=True)
+            key = (lay["_Dp"], lay["_P"], lay["_T"], lay["_max_q"], b.shared_prefix_len)
+            g = self.graphs.get(key)
+            if g is None and len(self.graphs) >= self.MAX_GRAPHS:
+                graphable = False
+        if graphable:
+            self._graph_mode = True
+            self._upload(lay)
+            if g is None:
+                # one eager run (sets kernel attributes, warms the allocator), then capture
+                self._forward_and_sample(lay, b.shared_prefix_len, None)
+                torch.cuda.current_stream().synchronize()
+                before = self.launches
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    self._forward_and_sample(lay, b.shared_prefix_len, None)
+                g = self.graphs[key] = (graph, self.launches - before)
+            g[0].replay()
+            self.launches += g[1]
+            self._sel = lay["_sel"]
+            return len(self._sel)
+        self._graph_mode = False
+        lay = self._pack(b, bucketed=False)
+        self._upload(lay)
+        fl = None if greedy else self._sampling_tensors(b, lay["_S"])
+        self._forward_and_sample(lay, b.shared_prefix_len, fl)
+        self._sel = lay["_sel"]
+        return len(self._sel)
+
+    def _forward_and_sample(self, lay, shared_prefix_len, fl):
+        x = self._forward_tokens(lay, shared_prefix_len)
+        if lay["_S"] > 0:
+            self._logits_and_sample(x, lay, None, fl)
+
+    def fetch(self) -> List[int]:
+        """Device -> pinned host copy of the sampled ids of the last ``launch`` and a stream sync."""
+        sel = self._sel
+        if not sel:
+            torch.cuda.current_stream().synchronize()
+            return []
+        n = max(sel) + 1
+        self.out_ids_host[:n].copy_(self.out_ids_dev[:n], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.d2h_bytes += 4 * n
+        vals = self.out_ids_host[:n].tolist()
+        return [vals[i] for i in sel]
+
+    def execute(self, b: StepBatch) -> List[int]:
+        self.launch(b)
+        return self.fetch()
+
+    def kv_cache_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.k_cache) * 2
+
+    def logits_for(self, b: StepBatch) -> torch.Tensor:
+        """Test hook: full logits [S, vocab_shard] of a step (eager, no sampling)."""
+        self._graph_mode = False
+        self._max_len_d = max(b.seq_lens[:b.num_decode]) if b.num_decode else 0
+        lay = self._pack(b, bucketed=False)
+        self._upload(lay)
+        x = self._forward_tokens(lay, b.shared_prefix_len)
+        rows = self._view(lay, "sample_rows")
+        xs = x.index_select(0, rows.long())
+        if self.spec.final_norm:
+            xs = self._norm(xs, "final_norm")
+        return self._gemm(xs, self.w.t["lm_head"], bias=self.w.t.get("lm_head_bias"), out_scale=self.spec.logit_scale,
+                          out_dtype=torch.float32)
