@@ -28,6 +28,7 @@
 // QMatMul call sites (models_v2/llama.rs:1184-1195) and fused_swiglu (tensor_core.rs:1385-1396).
 #include "../common/ptx.cuh"
 #include "../include/unillm_b200.h"
+#include <stdlib.h>
 
 namespace ub {
 
@@ -226,6 +227,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       uint32_t ag_ready = 0;  // bitmask of source ranks already seen complete
       int it = 0;
       bool dead = false;
+      constexpr int PF = 12;                 // L2 prefetch distance in k-blocks
+      int pf_issued = 0, pf_u = unit_begin, pf_kb = kb0;
       for (int u = unit_begin; u < total_tiles && !dead; u += unit_step) {
         const int m0 = (u % num_m) * TN, n0 = (u / num_m) * BM_W;
         if (p.ag_world > 0) {
@@ -252,6 +255,15 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
           if (waited) asm volatile("fence.proxy.async;" ::: "memory");
         }
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          // Weights come from HBM (about 2 us away under load) while the few smem stages cover far less
+          // time than that: ask L2 for the weight tile PF k-blocks ahead, so the smem copies hit in L2.
+          for (; pf_issued < it + PF + 1; ++pf_issued) {
+            if (pf_u >= total_tiles) break;
+            const int pn0 = (pf_u / num_m) * BM_W;
+            tma_prefetch_l2_2d(&tmap_w, pf_kb * BK, pn0);
+            if (DUAL) tma_prefetch_l2_2d(&tmap_w, pf_kb * BK, pn0 + p.up_row_off);
+            if (++pf_kb >= kb1) { pf_kb = kb0; pf_u += unit_step; }
+          }
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err, 100 + s)) { dead = true; break; }
@@ -499,8 +511,14 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, long long rows, long l
   cuuint64_t strides[1] = {(cuuint64_t)ld_elems * 2};
   cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
+  static int promo = -1;
+  if (promo < 0) {
+    const char* e = getenv("UB_TMAP_L2_PROMOTION");   // 0 none, 1 64B, 2 128B, 3 256B (default)
+    promo = e ? atoi(e) : 3;
+    if (promo < 0 || promo > 3) promo = 3;
+  }
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, (CUtensorMapL2promotion)promo,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -(int)r - 1000;
 }
@@ -526,7 +544,9 @@ static GemmPlan plan_gemm(const UbGemmArgs* a) {
   int tn = a->tile_tokens;
   if (tn <= 0) {
     tn = 16;
-    while (tn < a->M && tn < 256) tn <<= 1;
+    // gated GEMMs keep two 128-column accumulators double-buffered; the single-buffered 2 x 256 variant
+    // measured slower at every size
+    while (tn < a->M && tn < (dual ? 128 : 256)) tn <<= 1;
   }
   pl.tn = tn;
   const int num_m = (a->M + tn - 1) / tn, num_n = (a->N + BM_W - 1) / BM_W;

@@ -53,21 +53,23 @@ def time_ms(fn, iters=10, warmup=3, flush=True):
     return ts[len(ts) // 2], ts[0]
 
 
-def bench_gemm(results):
+def bench_gemm(results, only=None, tile=0):
     hbm, tf, how = _peaks()
-    shapes = [
+    shapes = [only] if only else [
         # (M, N, K, dual) : Llama-3-8B decode / prefill shapes
         (16, 6144, 4096, 0), (64, 6144, 4096, 0), (256, 6144, 4096, 0), (256, 4096, 4096, 0),
         (256, 14336, 4096, 1), (256, 4096, 14336, 0), (256, 128256, 4096, 0),
         # tensor-parallel (TP=8) per-rank decode shapes: few tiles -> cluster split-K
         (256, 768, 4096, 0), (256, 4096, 512, 0), (256, 1792, 4096, 1), (256, 4096, 1792, 0), (256, 16032, 4096, 0),
         (2048, 6144, 4096, 0), (2048, 14336, 4096, 1), (2048, 4096, 14336, 0), (8192, 8192, 8192, 0),
+        # mixed decode + prefill step of the serving benchmark (about 512 token rows)
+        (512, 6144, 4096, 0), (512, 4096, 4096, 0), (512, 14336, 4096, 1), (512, 4096, 14336, 0),
     ]
     for M, N, K, dual in shapes:
         x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
         w = torch.randn(N * (2 if dual else 1), K, device="cuda", dtype=torch.bfloat16) * 0.02
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-        fn = (lambda: cuda_ops.gemm_tn(x, w, dual_rows=N, act="silu", out=out)) if dual else (lambda: cuda_ops.gemm_tn(x, w, out=out))
+        fn = (lambda: cuda_ops.gemm_tn(x, w, dual_rows=N, act="silu", out=out, tile_tokens=tile)) if dual else (lambda: cuda_ops.gemm_tn(x, w, out=out, tile_tokens=tile))
         med, best = time_ms(fn)
         flops = 2.0 * M * N * K * (2 if dual else 1)
         byts = 2.0 * (w.numel() + x.numel() + out.numel())
@@ -135,10 +137,12 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("what", nargs="?", default="all", choices=["gemm", "attn", "norm", "all"])
     ap.add_argument("--json", default=None)
+    ap.add_argument("--shape", default=None, help="gemm only: M,N,K,dual -- run just this shape")
+    ap.add_argument("--tile", type=int, default=0, help="gemm only: force the token-tile width")
     a = ap.parse_args(argv)
     results = []
     if a.what in ("gemm", "all"):
-        bench_gemm(results)
+        bench_gemm(results, tuple(int(v) for v in a.shape.split(",")) if a.shape else None, a.tile)
     if a.what in ("attn", "all"):
         bench_attn(results)
     if a.what in ("norm", "all"):

@@ -35,7 +35,7 @@ from .runner import StepBatch
 WAITING, RUNNING, FINISHED, ABORTED = "waiting", "running", "finished", "aborted"
 
 
-@dataclass
+@dataclass(eq=False)
 class Sequence:
     seq_id: int
     prompt_ids: List[int]
@@ -277,7 +277,7 @@ class LLMEngine:
         plan: List[Tuple[Sequence, int, bool]] = []
         for s in decode:
             p = s.total_len - 1
-            token_ids.append(s.tokens[p])
+            token_ids.append(s.output_ids[-1])
             positions.append(p)
             slots.append(s.blocks[p // bs] * bs + p % bs)
             seq_lens.append(p + 1)
@@ -323,13 +323,15 @@ class LLMEngine:
         """Number of leading tokens (whole blocks) whose blocks are identical in all decode sequences."""
         first = decode[0].blocks
         n = min(min(len(s.blocks) for s in decode), min((s.total_len - 1) // self.block_size for s in decode))
-        lo = 0
-        while lo < n:
-            b = first[lo]
-            if any(s.blocks[lo] != b for s in decode):
+        for s in decode:
+            if n == 0:
                 break
-            lo += 1
-        return lo * self.block_size
+            if s.blocks[:n] != first[:n]:          # list slices compare at C speed; shrink only on mismatch
+                k = 0
+                while k < n and s.blocks[k] == first[k]:
+                    k += 1
+                n = k
+        return n * self.block_size
 
     # ------------------------------------------------------------------------------------------
     # stepping

@@ -253,6 +253,109 @@ class TpContext:
         return torch.cat(outs, dim=dim)
 
 
+class StepPacker:
+    """Packs a ``StepBatch`` into one int32 staging buffer (host-only logic, numpy views)."""
+
+    def __init__(self, buf: torch.Tensor, max_blocks_per_seq: int):
+        self.meta_host = buf
+        self.np = buf.numpy()
+        self.META_INTS = buf.numel()
+        self.max_blocks_per_seq = max_blocks_per_seq
+
+    @staticmethod
+    def _bucket(n: int) -> int:
+        b = 1
+        while b < n:
+            b <<= 1
+        return b
+
+    def pack(self, b: StepBatch, bucketed: bool = False):
+        """Writes the step's integer metadata into the pinned buffer and returns the layout
+        (name -> (offset, length)); one H2D copy moves all of it.
+
+        With ``bucketed`` the batch is padded to a shape from a small set so that a captured CUDA graph
+        can be replayed: decode rows to a power of two, prefill tokens to a multiple of 128 (the padding
+        forms a dummy sequence that writes no KV), prefill sequences to a power of two (empty dummies),
+        and every decode row plus the last row of every prefill sequence is sampled."""
+        D = b.num_decode
+        nseq = len(b.seq_lens)
+        P = nseq - D
+        mb = self.max_blocks_per_seq
+        q_lens = list(b.prefill_q_lens)
+        p_lens = list(b.seq_lens[D:])
+        Tp = sum(q_lens)
+        Dp, Pp, tpad = D, P, 0
+        if bucketed:
+            Dp = self._bucket(D) if D else 0
+            if P:
+                tpad = (-Tp) % 128
+                Pp = self._bucket(P + (1 if tpad else 0))
+                if tpad:
+                    q_lens.append(tpad)
+                    p_lens.append(tpad)
+                q_lens += [0] * (Pp - len(q_lens))
+                p_lens += [0] * (Pp - len(p_lens))
+        pad = Dp - D
+        h = self.np
+        off = 0
+        lay = {}
+
+        def put(name, vals):
+            nonlocal off
+            n = len(vals)
+            if off + n > self.META_INTS:
+                raise InvalidInput("step metadata exceeds the staging buffer")
+            if n:
+                h[off:off + n] = vals
+            lay[name] = (off, n)
+            off += (n + 3) // 4 * 4     # keep every array 16-byte aligned
+
+        # decode rows first (padded rows point at slot -1 / block 0 / length 1 so kernels stay in bounds)
+        put("token_ids", b.token_ids[:D] + [0] * pad + b.token_ids[D:] + [0] * tpad)
+        put("positions", b.positions[:D] + [0] * pad + b.positions[D:] + [0] * tpad)
+        put("slot_mapping", b.slot_mapping[:D] + [-1] * pad + b.slot_mapping[D:] + [-1] * tpad)
+        put("seq_lens_d", b.seq_lens[:D] + [1] * pad)
+        nbt = (Dp + Pp) * mb
+        if off + nbt > self.META_INTS:
+            raise InvalidInput("step metadata exceeds the staging buffer")
+        bt = h[off:off + nbt].reshape(Dp + Pp, mb)
+        # only the entries below each sequence's length are ever read; rows of padded sequences are zeroed
+        for i, row in enumerate(b.block_tables):
+            bt[i if i < D else i + pad, :len(row)] = row
+        if pad:
+            bt[D:Dp, 0] = 0
+        if Pp > P:
+            bt[Dp + P:, :(128 // 16) + 1] = 0      # the dummy sequence is shorter than 128 tokens
+        lay["block_tables"] = (off, nbt)
+        off += (nbt + 3) // 4 * 4
+        put("seq_lens_p", p_lens)
+        qs = [0]
+        for ql in q_lens:
+            qs.append(qs[-1] + ql)
+        put("q_start", qs)
+        if bucketed:
+            rows = list(range(Dp)) + [Dp + max(qs[j + 1] - 1, 0) for j in range(Pp)]
+            sel = []
+            for r in b.sample_rows:
+                if r < D:
+                    sel.append(r)
+                else:
+                    # r is the last row of some prefill sequence j: find it from the unpadded prefix sums
+                    j = next(jj for jj in range(P) if D + qs[jj + 1] - 1 == r)
+                    sel.append(Dp + j)
+            lay["_sel"] = sel
+        else:
+            rows = [r if r < D else r + pad for r in b.sample_rows]
+            lay["_sel"] = list(range(len(rows)))
+        put("sample_rows", rows)
+        lay["_T"], lay["_D"], lay["_Dp"], lay["_P"], lay["_S"] = Dp + Tp + tpad, D, Dp, Pp, len(rows)
+        mq = max(q_lens) if q_lens else 0
+        lay["_max_q"] = self._bucket(mq) if (bucketed and mq) else mq
+        lay["_used"] = off
+        return lay
+
+
+
 class _OpTimer:
     def __init__(self, runner, name):
         self.r, self.name = runner, name
@@ -298,7 +401,8 @@ class GpuModelRunner:
             sl = alibi_slopes(s.num_heads)
             self.alibi = sl[weights.rank * weights.hq:(weights.rank + 1) * weights.hq].to(dev)
         # packed metadata: pinned host staging + device mirror with fixed addresses (graph friendly)
-        self.meta_host = torch.empty(self.META_INTS, dtype=torch.int32, pin_memory=True)
+        self.meta_host = torch.zeros(self.META_INTS, dtype=torch.int32, pin_memory=True)
+        self.packer = StepPacker(self.meta_host, self.max_blocks_per_seq)
         self.meta_dev = torch.empty(self.META_INTS, dtype=torch.int32, device=dev)
         self.fmeta_host = torch.empty(4 * max_num_seqs, dtype=torch.float32, pin_memory=True)
         self.fmeta_dev = torch.empty(4 * max_num_seqs, dtype=torch.float32, device=dev)
@@ -318,83 +422,7 @@ class GpuModelRunner:
     # metadata packing
     # ------------------------------------------------------------------------------------------
     def _pack(self, b: StepBatch, bucketed: bool = False):
-        """Writes the step's integer metadata into the pinned buffer and returns the layout
-        (name -> (offset, length)); one H2D copy moves all of it.
-
-        With ``bucketed`` the batch is padded to a shape from a small set so that a captured CUDA graph
-        can be replayed: decode rows to a power of two, prefill tokens to a multiple of 128 (the padding
-        forms a dummy sequence that writes no KV), prefill sequences to a power of two (empty dummies),
-        and every decode row plus the last row of every prefill sequence is sampled."""
-        D = b.num_decode
-        nseq = len(b.seq_lens)
-        P = nseq - D
-        mb = self.max_blocks_per_seq
-        q_lens = list(b.prefill_q_lens)
-        p_lens = list(b.seq_lens[D:])
-        Tp = sum(q_lens)
-        Dp, Pp, tpad = D, P, 0
-        if bucketed:
-            Dp = self._bucket(D) if D else 0
-            if P:
-                tpad = (-Tp) % 128
-                Pp = self._bucket(P + (1 if tpad else 0))
-                if tpad:
-                    q_lens.append(tpad)
-                    p_lens.append(tpad)
-                q_lens += [0] * (Pp - len(q_lens))
-                p_lens += [0] * (Pp - len(p_lens))
-        pad = Dp - D
-        h = self.meta_host
-        off = 0
-        lay = {}
-
-        def put(name, vals, n=None, fill=0):
-            nonlocal off
-            n = len(vals) if n is None else n
-            if off + n > self.META_INTS:
-                raise InvalidInput("step metadata exceeds the staging buffer")
-            if len(vals):
-                h[off:off + len(vals)] = torch.as_tensor(vals, dtype=torch.int32)
-            if n > len(vals):
-                h[off + len(vals):off + n] = fill
-            lay[name] = (off, n)
-            off += (n + 3) // 4 * 4     # keep every array 16-byte aligned
-
-        # decode rows first (padded rows point at slot -1 / block 0 / length 1 so kernels stay in bounds)
-        put("token_ids", b.token_ids[:D] + [0] * pad + b.token_ids[D:] + [0] * tpad)
-        put("positions", b.positions[:D] + [0] * pad + b.positions[D:] + [0] * tpad)
-        put("slot_mapping", b.slot_mapping[:D] + [-1] * pad + b.slot_mapping[D:] + [-1] * tpad)
-        put("seq_lens_d", b.seq_lens[:D] + [1] * pad)
-        bt = torch.zeros((Dp + Pp, mb), dtype=torch.int32)
-        for i, row in enumerate(b.block_tables):
-            r = i if i < D else i + pad
-            bt[r, :len(row)] = torch.as_tensor(row, dtype=torch.int32)
-        put("block_tables", bt.reshape(-1))
-        put("seq_lens_p", p_lens)
-        qs = [0]
-        for ql in q_lens:
-            qs.append(qs[-1] + ql)
-        put("q_start", qs)
-        if bucketed:
-            rows = list(range(Dp)) + [Dp + max(qs[j + 1] - 1, 0) for j in range(Pp)]
-            sel = []
-            for r in b.sample_rows:
-                if r < D:
-                    sel.append(r)
-                else:
-                    # r is the last row of some prefill sequence j: find it from the unpadded prefix sums
-                    j = next(jj for jj in range(P) if D + qs[jj + 1] - 1 == r)
-                    sel.append(Dp + j)
-            lay["_sel"] = sel
-        else:
-            rows = [r if r < D else r + pad for r in b.sample_rows]
-            lay["_sel"] = list(range(len(rows)))
-        put("sample_rows", rows)
-        lay["_T"], lay["_D"], lay["_Dp"], lay["_P"], lay["_S"] = Dp + Tp + tpad, D, Dp, Pp, len(rows)
-        mq = max(q_lens) if q_lens else 0
-        lay["_max_q"] = self._bucket(mq) if (bucketed and mq) else mq
-        lay["_used"] = off
-        return lay
+        return self.packer.pack(b, bucketed)
 
     def _view(self, lay, name):
         o, n = lay[name]
