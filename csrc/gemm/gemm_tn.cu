@@ -57,7 +57,7 @@ struct GemmParams {
   // F3: all-gather wait.  ag_world == 0 disables.
   int ag_world, ag_rows_per_rank;
   const uint32_t* ag_flags;     // [world] counters in local memory, one per source rank
-  const uint32_t* ag_epoch;     // device word: number of uses so far (this one included)
+  const uint32_t* ag_epoch;     // unused (kept for ABI stability)
   uint32_t ag_signals_per_use;  // counter increments per source rank per use
 };
 
@@ -233,7 +233,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         const int m0 = (u % num_m) * TN, n0 = (u / num_m) * BM_W;
         if (p.ag_world > 0) {
           // Token rows [m0, m0+TN) were pushed by the ranks that own them; wait for those sources.
-          const uint32_t want = (*p.ag_epoch) * p.ag_signals_per_use;
+          // Counters are zeroed by the consumer side between uses (see csrc/norm/norm.cu), so the target is
+          // simply the number of producer CTAs of one use.
+          const uint32_t want = p.ag_signals_per_use;
           const int r_lo = m0 / p.ag_rows_per_rank;
           int r_hi = (min(m0 + TN, p.M) - 1) / p.ag_rows_per_rank;
           if (r_hi >= p.ag_world) r_hi = p.ag_world - 1;

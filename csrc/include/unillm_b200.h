@@ -76,12 +76,15 @@ typedef struct UbNormArgs {
   /* F1 consumer: sum `rs_world` partial slots [world][T][H] before the residual add (x is then the slot base). */
   int rs_world;
   const uint32_t* rs_flag;       /* local counter bumped by producers */
-  const uint32_t* epoch;         /* device word */
+  const uint32_t* epoch;         /* unused */
   uint32_t rs_signals_per_use;
   /* F3 producer: also push the normalised row into every peer's gather buffer at row (ag_rank*T + t). */
   int ag_world, ag_rank;
   void* ag_peer_out[UB_MAX_RANKS];
   uint32_t* ag_peer_flag[UB_MAX_RANKS]; /* peer's counter for source `ag_rank` */
+  /* up to 32 consecutive local counters that are idle during this kernel: block 0 zeroes them first */
+  uint32_t* reset_flags;
+  int reset_count;
 } UbNormArgs;
 int ub_norm(const UbNormArgs* args, void* stream);
 
@@ -222,6 +225,8 @@ typedef struct UbAllReduceArgs {
 int ub_allreduce_oneshot(const UbAllReduceArgs* args, void* stream);
 /* Wait until *flag (u32, wrap-safe) >= value; bounded (about 1 s), writes status 2 to err on timeout. */
 int ub_wait_flag(const uint32_t* flag, uint32_t value, int* err, void* stream);
+/* Same for n (<= 32) consecutive counters, one thread each. */
+int ub_wait_flags(const uint32_t* flags, int n, uint32_t value, int* err, void* stream);
 
 /* ---------------- device memory backend (kv/gpu_memory FFI surface) ---------------- */
 int ub_cuda_device_count(void);

@@ -33,6 +33,8 @@ struct NormParams {
   int ag_world, ag_rank;
   __nv_bfloat16* ag_peer_out[UB_MAX_RANKS];
   uint32_t* ag_peer_flag[UB_MAX_RANKS];
+  uint32_t* reset_flags;   // local counters that no kernel is using right now; zeroed by block 0 before it signals
+  int reset_count;
 };
 
 __device__ __forceinline__ float block_sum(float v, float* red) {
@@ -58,10 +60,16 @@ __global__ void __launch_bounds__(256) norm_kernel(const NormParams p) {
   const int H = p.H;
   const bool vec = (H % 8 == 0);
 
+  if (blockIdx.x == 0 && threadIdx.x < p.reset_count) {
+    // Flag hygiene: counters are reset to zero between uses by a kernel that is ordered (through the
+    // data dependencies of the layer pipeline) after their last reader and before their next writer.
+    p.reset_flags[threadIdx.x] = 0u;
+    __threadfence_system();
+  }
   if (p.rs_world > 0) {
     if (threadIdx.x == 0) {
       wait_failed = 0;
-      const uint32_t want = (*p.epoch) * p.rs_signals_per_use;
+      const uint32_t want = p.rs_signals_per_use;
       const uint64_t t0 = globaltimer_ns();
       uint32_t it = 0, v;
       while (true) {
@@ -193,7 +201,8 @@ __global__ void __launch_bounds__(256) norm_kernel(const NormParams p) {
 
 __global__ void bump_epoch_kernel(uint32_t* e) { *e = *e + 1; }
 
-__global__ void wait_flag_kernel(const uint32_t* flag, uint32_t value, int* err) {
+__global__ void wait_flag_kernel(const uint32_t* flags, uint32_t value, int* err) {
+  const uint32_t* flag = flags + threadIdx.x;   // one thread per counter
   const uint64_t t0 = globaltimer_ns();
   uint32_t it = 0, v;
   while (true) {
@@ -221,6 +230,7 @@ extern "C" int ub_norm(const UbNormArgs* a, void* stream_v) {
   p.rs_world = a->rs_world; p.rs_flag = a->rs_flag; p.epoch = a->epoch;
   p.rs_signals_per_use = a->rs_signals_per_use;
   p.ag_world = a->ag_world; p.ag_rank = a->ag_rank;
+  p.reset_flags = a->reset_flags; p.reset_count = a->reset_count;
   for (int i = 0; i < UB_MAX_RANKS; ++i) {
     p.ag_peer_out[i] = (__nv_bfloat16*)a->ag_peer_out[i];
     p.ag_peer_flag[i] = a->ag_peer_flag[i];
@@ -240,6 +250,13 @@ extern "C" int ub_norm(const UbNormArgs* a, void* stream_v) {
 
 extern "C" int ub_bump_epoch(uint32_t* epoch, void* stream_v) {
   ub::bump_epoch_kernel<<<1, 1, 0, (cudaStream_t)stream_v>>>(epoch);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+extern "C" int ub_wait_flags(const uint32_t* flags, int n, uint32_t value, int* err, void* stream_v) {
+  if (n < 1 || n > 32) return -2;
+  ub::wait_flag_kernel<<<1, n, 0, (cudaStream_t)stream_v>>>(flags, value, err);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }

@@ -1,0 +1,149 @@
+"""Fused compute + collective kernels.
+
+Single-GPU part: all ranks are emulated on one device with ``FusedComm.emulated`` (their "peer pointers"
+are ordinary buffers of the same GPU) and kernels are launched producer-before-consumer on one stream,
+so no kernel ever waits for a kernel that has not been launched yet.
+
+Multi-GPU part (needs >= 2 GPUs): a tiny LLaMA runs through the engine with tensor parallel 2 in child
+processes, once with the fused kernels and once with the NCCL baseline, and must produce the same
+tokens as the single-GPU run.
+"""
+import math
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16).cuda()
+
+
+@pytest.mark.parametrize("world,T", [(2, 64), (4, 256), (8, 512)])
+def test_gemm_rs_norm_ag_gemm_chain_emulated(world, T):
+    from unillm_b200.dist.fused import FusedComm
+    from unillm_b200.ops import cuda_ops as K
+
+    H, Kfull, I = 512, 1024, 768
+    R = T // world
+    comms = FusedComm.emulated(world, H, T, "cuda")
+    x = _rand(T, Kfull, seed=1)
+    wo = _rand(H, Kfull, scale=1 / math.sqrt(Kfull), seed=2)
+    res = _rand(T, H, seed=3)
+    ln = _rand(H, seed=4)
+    wup = _rand(I * world, H, scale=1 / math.sqrt(H), seed=5)
+    Kr = Kfull // world
+    for rep in range(2):      # twice: the counters must be reset correctly between uses
+        # ---- F1 producer on every rank: partial GEMM, rows pushed to their owner ----
+        n_ctas = None
+        for r, c in enumerate(comms):
+            xr = x[:, r * Kr:(r + 1) * Kr].contiguous()
+            wr = wo[:, r * Kr:(r + 1) * Kr].contiguous()
+            out = c.rs_local_tensor(0, R).view(world * R, H)
+            K.gemm_tn(xr, wr, out=out, rs=c.gemm_rs(0, R))
+            n_ctas = K.gemm_num_ctas(T, H, Kr)
+        # ---- F1 consumer + F3 producer on every rank ----
+        new_res = []
+        for r, c in enumerate(comms):
+            _, h = K.norm(c.rs_local_tensor(0, R), ln, residual=res[r * R:(r + 1) * R].contiguous(), eps=1e-5,
+                          want_residual_out=True, no_out=True, T=R, rs=c.norm_rs(0, n_ctas * world), ag=c.norm_ag(1),
+                          reset=c.reset_after_ag(1))
+            new_res.append(h)
+        # ---- F3 consumer: column-parallel GEMM on the gathered rows ----
+        ys = []
+        for r, c in enumerate(comms):
+            ys.append(K.gemm_tn(c.ag_local_tensor(1, T), wup[r * I:(r + 1) * I].contiguous(), ag=c.gemm_ag(1, R)))
+        # a second norm kernel (the "next layer" one) resets the counters used above, as in the layer pipeline
+        for r, c in enumerate(comms):
+            K.norm(new_res[r], ln, eps=1e-5, T=R, reset=c.reset_after_ag(0))
+        torch.cuda.synchronize()
+        K.check_device_errors()
+        hsum = (x.float() @ wo.float().t()).to(torch.bfloat16).float()   # order of rounding differs slightly
+        href = x.float() @ wo.float().t() + res.float()
+        got_res = torch.cat(new_res).float()
+        assert (got_res - href).abs().max().item() < 0.06 * max(1.0, href.abs().max().item())
+        hn = got_res * torch.rsqrt(got_res.pow(2).mean(-1, keepdim=True) + 1e-5) * ln.float()
+        yref = hn.to(torch.bfloat16).float() @ wup.float().t()
+        ygot = torch.cat(ys, dim=1).float()
+        assert (ygot - yref).abs().max().item() < 0.05 * max(1.0, yref.abs().max().item())
+        for c in comms:   # counters of the other phase were zeroed
+            flags = c.buf[c.flags.offset:c.flags.offset + 256].view(torch.int32)
+            assert int(flags[16:25].abs().sum()) == 0
+
+
+def test_flag_wait_times_out_without_hanging():
+    """A counter that nothing bumps: the bounded wait gives up, records status 2 and the context stays usable."""
+    from unillm_b200.ops import cuda_ops as K
+
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    K.wait_flags(flags.data_ptr(), 2, 5, "cuda")
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="flag wait timed out"):
+        K.check_device_errors()
+    K.check_device_errors()      # the word was cleared
+    assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0
+
+
+_CHILD = r"""
+import os, sys, json, torch
+import torch.distributed as dist
+sys.path.insert(0, os.environ["REPO"])
+from unillm_b200.engine.llm_engine import LLMEngine
+from unillm_b200.engine.runner import GpuModelRunner, RunnerWeights, TpContext
+from unillm_b200.models import configs as C
+from unillm_b200.models.families import LlamaModel
+from unillm_b200.ops import cuda_ops
+from unillm_b200.sampling import SamplingParams
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device(f"cuda:{rank}"))
+cfg = C.LlamaConfig(vocab_size=1024, hidden_size=512, intermediate_size=1024, num_hidden_layers=3,
+                    num_attention_heads=8, num_key_value_heads=4, rms_norm_eps=1e-5)
+spec = LlamaModel.spec_from_config(cfg)
+g = torch.Generator().manual_seed(0)
+shared = torch.randint(0, 1024, (48,), generator=g).tolist()
+prompts = [shared + torch.randint(0, 1024, (n,), generator=g).tolist() for n in (16, 48, 32, 64, 16, 80, 8, 24)]
+out = {}
+for mode in ("tp1", "nccl", "fused", "fused_graph"):
+    tpw = 1 if mode == "tp1" else world
+    tp = TpContext(rank if tpw > 1 else 0, tpw, dist.group.WORLD if tpw > 1 else None, fused=mode.startswith("fused"))
+    w = RunnerWeights.random(spec, f"cuda:{rank}", tp.rank, tp.world, seed=7)
+    if tp.fused:
+        from unillm_b200.dist.fused import FusedComm
+        tp.comm = FusedComm.create(spec, rank, world, dist.group.WORLD, max_tokens=512, device=f"cuda:{rank}")
+    runner = GpuModelRunner(spec, w, num_blocks=128, max_num_seqs=8, max_num_batched_tokens=256, max_model_len=256,
+                            tp=tp, use_cuda_graphs=(mode == "fused_graph"))
+    eng = LLMEngine(runner, num_blocks=128, max_num_seqs=8, max_num_batched_tokens=256, max_model_len=256)
+    out[mode] = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=10))
+    torch.cuda.synchronize()
+    cuda_ops.check_device_errors()
+    dist.barrier()
+if rank == 0:
+    print("RESULT " + json.dumps(out))
+dist.destroy_process_group()
+"""
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tensor_parallel_engine_fused_matches_baseline(tmp_path):
+    import json
+
+    script = tmp_path / "child.py"
+    script.write_text(_CHILD)
+    env = dict(os.environ, REPO=os.path.dirname(os.path.dirname(os.path.abspath(__file__))), NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29731", str(script)]
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    line = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")][-1]
+    out = json.loads(line[7:])
+    assert out["fused"] == out["fused_graph"]
+    for mode in ("nccl", "fused"):
+        agree = sum(a == b for ra, rb in zip(out["tp1"], out[mode]) for a, b in zip(ra, rb))
+        total = sum(len(r) for r in out["tp1"])
+        assert agree / total > 0.8, (mode, agree, total)

@@ -1,0 +1,140 @@
+"""Symmetric-memory plumbing for the fused tensor-parallel kernels.
+
+``FusedComm`` owns, on every rank, one symmetric allocation (same layout on all ranks, mapped into
+every peer's address space through ``torch.distributed._symmetric_memory``) that holds
+
+  * two reduce-scatter receive areas ``rs[k]``  : ``[world][rows_per_rank][H]`` bf16 -- slot ``[src]`` is
+    written by rank ``src``'s GEMM epilogue (F1), read by the local norm kernel;
+  * two all-gather areas ``ag[k]``              : ``[world * rows_per_rank][H]`` bf16 -- rows of rank
+    ``src`` are written by ``src``'s norm kernel (F3 producer), read by the local GEMM's TMA loads;
+  * the arrival counters of both.
+
+Counter protocol: counters only count up during a use and are zeroed between uses by a kernel that
+the layer pipeline orders after their last reader and before their next writer (the norm kernel
+that follows, see ``csrc/norm/norm.cu``).  The counters are laid out so that each norm kernel's reset
+set is one consecutive run: ``[ag0 x 8][rs1]`` and ``[ag1 x 8][rs0]``.  All device waits are bounded;
+after a reported timeout call :meth:`reset` on every rank before the next step.
+
+The reference has no collective or peer-memory code at all; the library baseline that this replaces
+is ``TpContext.all_reduce`` (NCCL) in ``unillm_b200/engine/runner.py``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List
+
+import torch
+
+MAXR = 8
+# counter indices (uint32 words) inside the flag area
+AG0, RS1, AG1, RS0 = 0, 8, 16, 24
+FLAG_WORDS = 64
+
+
+@dataclass
+class _Area:
+    offset: int      # bytes from the start of the symmetric buffer
+    nbytes: int
+
+
+class FusedComm:
+    def __init__(self, rank: int, world: int, hidden: int, max_tokens: int, buf: torch.Tensor, peer_ptrs: List[int],
+                 handle=None, group=None):
+        self.rank, self.world, self.H = rank, world, hidden
+        self.max_rows = (max_tokens + world - 1) // world
+        self.buf, self.peer_ptrs, self.handle, self.group = buf, peer_ptrs, handle, group
+        slot = world * self.max_rows * hidden * 2
+        self.rs = [_Area(0, slot), _Area(slot, slot)]
+        self.ag = [_Area(2 * slot, slot), _Area(3 * slot, slot)]
+        self.flags = _Area(4 * slot, FLAG_WORDS * 4)
+        self.device = buf.device
+
+    @staticmethod
+    def nbytes(world: int, hidden: int, max_tokens: int) -> int:
+        rows = (max_tokens + world - 1) // world
+        return 4 * world * rows * hidden * 2 + FLAG_WORDS * 4
+
+    @classmethod
+    def create(cls, spec, rank: int, world: int, group, max_tokens: int, device) -> "FusedComm":
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        n = cls.nbytes(world, spec.hidden_size, max_tokens)
+        buf = symm.empty(n, dtype=torch.uint8, device=device)
+        h = symm.rendezvous(buf, group if group is not None else dist.group.WORLD)
+        buf.zero_()
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+        return cls(rank, world, spec.hidden_size, max_tokens, buf, [int(p) for p in h.buffer_ptrs], h, group)
+
+    @classmethod
+    def emulated(cls, world: int, hidden: int, max_tokens: int, device) -> List["FusedComm"]:
+        """All ranks on ONE device (tests): plain buffers whose addresses stand in for peer mappings.  Kernels of
+        different emulated ranks must then be launched producer-before-consumer on one stream."""
+        n = cls.nbytes(world, hidden, max_tokens)
+        bufs = [torch.zeros(n, dtype=torch.uint8, device=device) for _ in range(world)]
+        ptrs = [b.data_ptr() for b in bufs]
+        return [cls(r, world, hidden, max_tokens, bufs[r], ptrs) for r in range(world)]
+
+    # ---- address helpers ----
+    def _peer(self, r: int, area: _Area, extra: int = 0) -> int:
+        return self.peer_ptrs[r] + area.offset + extra
+
+    def flag_ptr(self, r: int, word: int) -> int:
+        return self.peer_ptrs[r] + self.flags.offset + 4 * word
+
+    def local_flag_ptr(self, word: int) -> int:
+        return self.buf.data_ptr() + self.flags.offset + 4 * word
+
+    def rs_local(self, k: int) -> int:
+        return self.buf.data_ptr() + self.rs[k].offset
+
+    def ag_local_tensor(self, k: int, rows: int) -> torch.Tensor:
+        a = self.ag[k]
+        return self.buf[a.offset:a.offset + rows * self.H * 2].view(torch.bfloat16).view(rows, self.H)
+
+    def rs_local_tensor(self, k: int, rows_per_rank: int) -> torch.Tensor:
+        a = self.rs[k]
+        n = self.world * rows_per_rank * self.H
+        return self.buf[a.offset:a.offset + n * 2].view(torch.bfloat16).view(self.world, rows_per_rank, self.H)
+
+    # ---- kernel argument dicts ----
+    def gemm_rs(self, k: int, rows_per_rank: int) -> dict:
+        """F1 producer arguments: push rows into rank ``owner``'s ``rs[k]`` slot of this rank."""
+        return {"world": self.world, "rank": self.rank, "rows_per_rank": rows_per_rank,
+                "peer_out": [self._peer(r, self.rs[k]) for r in range(self.world)],
+                "peer_flag": [self.flag_ptr(r, RS0 if k == 0 else RS1) for r in range(self.world)]}
+
+    def norm_rs(self, k: int, signals: int) -> dict:
+        """F1 consumer arguments: wait for ``signals`` arrivals, sum the ``world`` slots of ``rs[k]``."""
+        return {"world": self.world, "flag": self.local_flag_ptr(RS0 if k == 0 else RS1), "signals_per_use": signals}
+
+    def norm_ag(self, k: int) -> dict:
+        """F3 producer arguments: push normalised rows into every rank's ``ag[k]`` and bump their counter for us."""
+        base = AG0 if k == 0 else AG1
+        return {"world": self.world, "rank": self.rank,
+                "peer_out": [self._peer(r, self.ag[k]) for r in range(self.world)],
+                "peer_flag": [self.flag_ptr(r, base + self.rank) for r in range(self.world)]}
+
+    def gemm_ag(self, k: int, rows_per_rank: int) -> dict:
+        """F3 consumer arguments: token rows of source rank ``s`` are ready when counter ``s`` reaches its row count."""
+        base = AG0 if k == 0 else AG1
+        return {"world": self.world, "rows_per_rank": rows_per_rank, "flags": self.local_flag_ptr(base),
+                "signals_per_use": rows_per_rank}
+
+    def reset_after_ag(self, k: int) -> tuple:
+        """Counters a norm kernel may zero: the all-gather counters it does NOT feed plus the reduce-scatter
+        counter it does NOT read -- ``k`` is the all-gather area this norm kernel pushes into."""
+        # norm pushing into ag1 (post-attention) resets [ag0 x 8][rs1]; norm pushing into ag0 resets [ag1 x 8][rs0]
+        base = AG0 if k == 1 else AG1
+        return (self.local_flag_ptr(base), 9)
+
+    def reset(self) -> None:
+        """Zero all counters (host side); call on every rank, then barrier, after a reported device timeout."""
+        a = self.flags
+        self.buf[a.offset:a.offset + a.nbytes].zero_()
+        torch.cuda.synchronize(self.device)
+        if self.group is not None:
+            import torch.distributed as dist
+
+            dist.barrier(self.group)

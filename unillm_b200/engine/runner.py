@@ -550,6 +550,9 @@ class GpuModelRunner:
         """Runs all layers on the packed step; returns the sampled token ids tensor (device, [S])."""
         s, t, tp = self.spec, self.w.t, self.tp
         T = lay["_T"]
+        self._final_norm_done = False
+        if self._fused_ok(T):
+            return self._forward_tokens_fused(lay, shared_prefix_len)
         ids = self._view(lay, "token_ids")
         pos = self._view(lay, "positions")
         slots = self._view(lay, "slot_mapping")
@@ -601,6 +604,84 @@ class GpuModelRunner:
                 self.launches += 1
         return x
 
+    # ------------------------------------------------------------------------------------------
+    # fused tensor-parallel path (F1 / F3)
+    # ------------------------------------------------------------------------------------------
+    def _fused_ok(self, T: int) -> bool:
+        s, tp = self.spec, self.tp
+        return (tp.fused and tp.comm is not None and T % tp.world == 0 and T // tp.world <= tp.comm.max_rows
+                and not s.parallel_residual and s.moe is None and s.residual_scale == 1.0 and s.pos != "learned"
+                and not s.embed_norm and s.final_norm)
+
+    def _forward_tokens_fused(self, lay, shared_prefix_len: int) -> torch.Tensor:
+        """Same math as ``_forward_tokens`` with the residual stream sharded by token rows between the two
+        GEMM pairs of every layer: o_proj / down_proj epilogues push rows to their owner (reduce-scatter),
+        the norm kernel sums, normalises and pushes to everyone (all-gather), and the next GEMM waits on
+        the arrival counters inside its TMA producer.  No NCCL call, no separate reduction kernel."""
+        s, t, tp = self.spec, self.w.t, self.tp
+        c, W, r = tp.comm, tp.world, tp.rank
+        T = lay["_T"]
+        R = T // W
+        H = s.hidden_size
+        ids = self._view(lay, "token_ids")
+        pos = self._view(lay, "positions")
+        slots = self._view(lay, "slot_mapping")
+        x_full = K.embed_gather(ids, t["embed"], scale=s.embed_scale)
+        self.launches += 1
+        xr = x_full[r * R:(r + 1) * R]                      # this rank's rows of the residual stream
+        h_full = self._norm(x_full, "layers.0.ln1")         # layer 0 normalises all rows locally
+        kind = "rms" if s.norm == "rms" else "layer"
+        n_o = K.gemm_num_ctas(T, H, self.w.hq * s.head_dim) * W
+        I_loc = (t["layers.0.w_gate_up"].shape[0] // 2) if s.mlp == "gated" else t["layers.0.w_up"].shape[0]
+        n_d = K.gemm_num_ctas(T, H, I_loc) * W
+        rs0_out = c.rs_local_tensor(0, R)
+        rs1_out = c.rs_local_tensor(1, R)
+        ag_args = None
+        for i in range(s.num_layers):
+            L = f"layers.{i}."
+            qkv = self._gemm(h_full, t[L + "wqkv"], bias=t.get(L + "bqkv"), ag=ag_args, tag="gemm_ag" if ag_args else "gemm")
+            with self._prof("rope_kv_append"):
+                K.rope_kv_append(qkv, pos, slots, self.k_cache[i], self.v_cache[i], num_q_heads=self.w.hq,
+                                 num_kv_heads=self.w.hkv, head_dim=s.head_dim,
+                                 rotary_dim=s.rd if s.pos == "rope" else 0, theta=s.rope_theta,
+                                 pos_scale=s.rope_pos_scale, interleaved=s.rope_interleaved,
+                                 q_norm_w=t.get(L + "q_norm"), k_norm_w=t.get(L + "k_norm"), norm_eps=s.norm_eps,
+                                 llama3_scaling=s.rope_llama3)
+            self.launches += 1
+            a = self._attention(i, qkv, lay, shared_prefix_len)
+            # o_proj: partial rows go straight to their owner's receive slot
+            self._gemm(a, t[L + "wo"], bias=t.get(L + "bo"), out=rs0_out.view(W * R, H)[:T], rs=c.gemm_rs(0, R),
+                       tag="gemm_rs")
+            # sum partials + residual, normalise own rows, push to every rank's gather area 1
+            with self._prof("norm_rs_ag"):
+                _, xr = K.norm(rs0_out, t[L + "ln2.w"], bias=t.get(L + "ln2.b"), residual=xr, eps=s.norm_eps, kind=kind,
+                               weight_offset_one=s.norm_weight_offset_one, want_residual_out=True, no_out=True, T=R,
+                               rs=c.norm_rs(0, n_o), ag=c.norm_ag(1), reset=c.reset_after_ag(1))
+            self.launches += 1
+            h2 = c.ag_local_tensor(1, T)
+            if s.mlp == "gated":
+                act = self._gemm(h2, t[L + "w_gate_up"], dual_rows=I_loc, act=s.act, ag=c.gemm_ag(1, R), tag="gemm_ag")
+            else:
+                act = self._gemm(h2, t[L + "w_up"], bias=t.get(L + "b_up"), act=s.act, ag=c.gemm_ag(1, R), tag="gemm_ag")
+            self._gemm(act, t[L + "w_down"], bias=t.get(L + "b_down"), out=rs1_out.view(W * R, H)[:T],
+                       rs=c.gemm_rs(1, R), tag="gemm_rs")
+            last = i == s.num_layers - 1
+            nname = "final_norm" if last else f"layers.{i + 1}.ln1"
+            with self._prof("norm_rs_ag"):
+                _, xr = K.norm(rs1_out, t[nname + ".w"], bias=t.get(nname + ".b"), residual=xr, eps=s.norm_eps, kind=kind,
+                               weight_offset_one=s.norm_weight_offset_one, want_residual_out=True, no_out=True, T=R,
+                               rs=c.norm_rs(1, n_d), ag=c.norm_ag(0), reset=c.reset_after_ag(0))
+            self.launches += 1
+            h_full = c.ag_local_tensor(0, T)
+            ag_args = c.gemm_ag(0, R)
+        # the final-normed rows of all ranks arrive in gather area 0; wait for them before the row gather
+        from ..dist.fused import AG0
+
+        K.wait_flags(c.local_flag_ptr(AG0), W, R, self.device)
+        self.launches += 1
+        self._final_norm_done = True
+        return h_full
+
     def _mlp_noresid(self, i, h):
         s, t = self.spec, self.w.t
         L = f"layers.{i}."
@@ -616,7 +697,7 @@ class GpuModelRunner:
         S = lay["_S"]
         rows = self._view(lay, "sample_rows")
         xs = x.index_select(0, rows.long()) if S != x.shape[0] else x
-        if s.final_norm:
+        if s.final_norm and not self._final_norm_done:
             xs = self._norm(xs, "final_norm")
         logits = self._gemm(xs, t["lm_head"], bias=t.get("lm_head_bias"), out_scale=s.logit_scale)
         out = self.out_ids_dev[:S]
@@ -742,7 +823,7 @@ class GpuModelRunner:
         x = self._forward_tokens(lay, b.shared_prefix_len)
         rows = self._view(lay, "sample_rows")
         xs = x.index_select(0, rows.long())
-        if self.spec.final_norm:
+        if self.spec.final_norm and not self._final_norm_done:
             xs = self._norm(xs, "final_norm")
         return self._gemm(xs, self.w.t["lm_head"], bias=self.w.t.get("lm_head_bias"), out_scale=self.spec.logit_scale,
                           out_dtype=torch.float32)

@@ -15,6 +15,7 @@ from typing import Optional, Sequence
 import torch
 
 from . import _native as N
+from . import _native as N_
 
 _err_words: dict[int, torch.Tensor] = {}
 
@@ -115,9 +116,25 @@ def gemm_tn(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = 
             a.rs_peer_flag[i] = rs["peer_flag"][i]
     if ag is not None:
         a.ag_world, a.ag_rows_per_rank = ag["world"], ag["rows_per_rank"]
-        a.ag_flags, a.ag_epoch, a.ag_signals_per_use = ag["flags"], ag["epoch"], ag["signals_per_use"]
+        a.ag_flags, a.ag_signals_per_use = ag["flags"], ag["signals_per_use"]
     N.check(N.cuda_lib().ub_gemm_tn(C.byref(a), _stream(x)), "ub_gemm_tn")
     return out
+
+
+def gemm_num_ctas(M: int, N: int, K: int, dual: bool = False, tile_tokens: int = 0, splits: int = 0) -> int:
+    """CTAs that ``gemm_tn`` launches for this problem (each signals every peer once in reduce-scatter mode)."""
+    a = N_.UbGemmArgs()
+    a.M, a.N, a.K, a.dual, a.tile_tokens, a.splits = M, N, K, int(dual), tile_tokens, splits
+    return N_.cuda_lib().ub_gemm_num_ctas(C.byref(a))
+
+
+def wait_flags(flags_ptr: int, n: int, value: int, device) -> None:
+    """Enqueue a one-block kernel that waits (bounded) until n consecutive u32 counters reach ``value``."""
+    lib = N_.cuda_lib()
+    lib.ub_wait_flags.restype = C.c_int
+    lib.ub_wait_flags.argtypes = [N_.vp, N_.i32, N_.u32, N_.vp, N_.vp]
+    N_.check(lib.ub_wait_flags(flags_ptr, n, value, err_word(device).data_ptr(),
+                               torch.cuda.current_stream(device).cuda_stream), "ub_wait_flags")
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, **kw) -> torch.Tensor:
@@ -134,7 +151,8 @@ def norm(x: torch.Tensor, weight: Optional[torch.Tensor], *, bias: Optional[torc
          residual: Optional[torch.Tensor] = None, eps: float = 1e-5, kind: str = "rms",
          weight_offset_one: bool = False, want_residual_out: bool = False,
          out: Optional[torch.Tensor] = None, residual_out: Optional[torch.Tensor] = None,
-         rs: Optional[dict] = None, ag: Optional[dict] = None, T: Optional[int] = None):
+         rs: Optional[dict] = None, ag: Optional[dict] = None, T: Optional[int] = None,
+         reset: Optional[tuple] = None, no_out: bool = False, x_ptr: Optional[int] = None):
     """RMSNorm / LayerNorm over the last dim, with optional fused ``x + residual``.
 
     Returns ``y`` or ``(y, h)`` when the residual stream ``h = x + residual`` is requested.
@@ -145,19 +163,21 @@ def norm(x: torch.Tensor, weight: Optional[torch.Tensor], *, bias: Optional[torc
         T = x.numel() // H
     if not x.is_contiguous():
         x = x.contiguous()
-    if out is None:
+    if out is None and not no_out:
         out = torch.empty((T, H), dtype=torch.bfloat16, device=x.device)
     if want_residual_out and residual_out is None:
         residual_out = torch.empty((T, H), dtype=torch.bfloat16, device=x.device)
     a = N.UbNormArgs()
-    a.x, a.residual, a.weight, a.bias = x.data_ptr(), _p(residual), _p(weight), _p(bias)
-    a.out, a.residual_out = out.data_ptr(), _p(residual_out)
+    a.x, a.residual, a.weight, a.bias = (x.data_ptr() if x_ptr is None else x_ptr), _p(residual), _p(weight), _p(bias)
+    a.out, a.residual_out = _p(out), _p(residual_out)
     a.err = err_word(x.device).data_ptr()
     a.T, a.H, a.eps = T, H, eps
     a.kind = 0 if kind == "rms" else 1
     a.weight_offset_one = 1 if weight_offset_one else 0
     if rs is not None:
-        a.rs_world, a.rs_flag, a.epoch, a.rs_signals_per_use = rs["world"], rs["flag"], rs["epoch"], rs["signals_per_use"]
+        a.rs_world, a.rs_flag, a.rs_signals_per_use = rs["world"], rs["flag"], rs["signals_per_use"]
+    if reset is not None:
+        a.reset_flags, a.reset_count = reset
     if ag is not None:
         a.ag_world, a.ag_rank = ag["world"], ag["rank"]
         for i in range(ag["world"]):
