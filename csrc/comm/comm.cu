@@ -78,3 +78,76 @@ extern "C" int ub_allreduce_oneshot(const UbAllReduceArgs* a, void* stream_v) {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }
+
+// ----------------------------------------------------------------------------------------------
+// F4: vocabulary-parallel greedy merge.  Every rank holds, per sampled row, the best (value, id) of its
+// vocabulary shard.  One single-block kernel pushes the pairs into every peer's slot [parity][rank],
+// bumps the peers' counters, waits (bounded) until all `world` ranks have arrived for this round and
+// picks the global winner (highest value, lowest id on ties) -- the same answer on every rank.
+// The round number lives in a device word that the kernel itself increments, so the launch can sit in
+// a CUDA graph; slots alternate by round parity because a fast rank may start round n+1 while a slow
+// one still reads round n.
+// ----------------------------------------------------------------------------------------------
+namespace ub {
+
+__global__ void __launch_bounds__(256) tp_argmax_merge_kernel(const UbArgmaxMergeArgs a) {
+  __shared__ uint32_t round_s;
+  __shared__ int failed;
+  if (threadIdx.x == 0) {
+    round_s = *a.round + 1;
+    *a.round = round_s;
+    failed = 0;
+  }
+  __syncthreads();
+  const uint32_t round = round_s;
+  const int par = round & 1u;
+  const long long slot = ((long long)par * a.world + a.rank) * a.max_rows;
+  for (int i = threadIdx.x; i < a.rows; i += blockDim.x) {
+    const float v = a.vals[i];
+    const int id = a.ids[i];
+    for (int r = 0; r < a.world; ++r) {
+      reinterpret_cast<float*>(a.peer_vals[r])[slot + i] = v;
+      reinterpret_cast<int*>(a.peer_ids[r])[slot + i] = id;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < a.world)
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(a.peer_flags[threadIdx.x]), "r"(1u) : "memory");
+  if (threadIdx.x == 0) {
+    const uint32_t want = round * (uint32_t)a.world;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t it = 0, v;
+    while (true) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a.my_flag) : "memory");
+      if (int32_t(v - want) >= 0) break;
+      if ((++it & 31u) == 0 && (globaltimer_ns() - t0 > UB_WAIT_NS)) {
+        set_err(a.err, ERR_FLAG_TIMEOUT, 4000);
+        failed = 1;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < a.rows; i += blockDim.x) {
+    float bv = -3.4e38f;
+    int bi = 0x7fffffff;
+    for (int r = 0; r < a.world; ++r) {
+      const long long s = ((long long)par * a.world + r) * a.max_rows + i;
+      const float v = __ldcg(a.my_vals + s);
+      const int id = __ldcg(a.my_ids + s);
+      if (v > bv || (v == bv && id < bi)) { bv = v; bi = id; }
+    }
+    a.out_ids[i] = bi;
+  }
+}
+
+}  // namespace ub
+
+extern "C" int ub_tp_argmax_merge(const UbArgmaxMergeArgs* a, void* stream_v) {
+  if (a->rows <= 0) return 0;
+  if (a->rows > a->max_rows || a->world < 1 || a->world > UB_MAX_RANKS) return -2;
+  ub::tp_argmax_merge_kernel<<<1, 256, 0, (cudaStream_t)stream_v>>>(*a);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}

@@ -223,6 +223,22 @@ typedef struct UbAllReduceArgs {
   int* err;
 } UbAllReduceArgs;
 int ub_allreduce_oneshot(const UbAllReduceArgs* args, void* stream);
+/* F4: merge per-shard greedy winners across tensor-parallel ranks over peer memory (see csrc/comm/comm.cu). */
+typedef struct UbArgmaxMergeArgs {
+  const float* vals;         /* [rows] best logit of this rank's vocabulary shard */
+  const int* ids;            /* [rows] its global token id */
+  int* out_ids;              /* [rows] global winners */
+  void* peer_vals[UB_MAX_RANKS];   /* each: float [2][world][max_rows] on that peer */
+  void* peer_ids[UB_MAX_RANKS];    /* each: int   [2][world][max_rows] */
+  uint32_t* peer_flags[UB_MAX_RANKS];
+  const float* my_vals;
+  const int* my_ids;
+  const uint32_t* my_flag;
+  uint32_t* round;           /* local device word, incremented by the kernel */
+  int world, rank, rows, max_rows;
+  int* err;
+} UbArgmaxMergeArgs;
+int ub_tp_argmax_merge(const UbArgmaxMergeArgs* args, void* stream);
 /* Wait until *flag (u32, wrap-safe) >= value; bounded (about 1 s), writes status 2 to err on timeout. */
 int ub_wait_flag(const uint32_t* flag, uint32_t value, int* err, void* stream);
 /* Same for n (<= 32) consecutive counters, one thread each. */

@@ -109,13 +109,14 @@ g = torch.Generator().manual_seed(0)
 shared = torch.randint(0, 1024, (48,), generator=g).tolist()
 prompts = [shared + torch.randint(0, 1024, (n,), generator=g).tolist() for n in (16, 48, 32, 64, 16, 80, 8, 24)]
 out = {}
+from unillm_b200.dist.fused import FusedComm
+comm = FusedComm.create(spec, rank, world, dist.group.WORLD, max_tokens=512, device=f"cuda:{rank}")
 for mode in ("tp1", "nccl", "fused", "fused_graph"):
     tpw = 1 if mode == "tp1" else world
     tp = TpContext(rank if tpw > 1 else 0, tpw, dist.group.WORLD if tpw > 1 else None, fused=mode.startswith("fused"))
     w = RunnerWeights.random(spec, f"cuda:{rank}", tp.rank, tp.world, seed=7)
     if tp.fused:
-        from unillm_b200.dist.fused import FusedComm
-        tp.comm = FusedComm.create(spec, rank, world, dist.group.WORLD, max_tokens=512, device=f"cuda:{rank}")
+        tp.comm = comm
     runner = GpuModelRunner(spec, w, num_blocks=128, max_num_seqs=8, max_num_batched_tokens=256, max_model_len=256,
                             tp=tp, use_cuda_graphs=(mode == "fused_graph"))
     eng = LLMEngine(runner, num_blocks=128, max_num_seqs=8, max_num_batched_tokens=256, max_model_len=256)
@@ -138,7 +139,7 @@ def test_tensor_parallel_engine_fused_matches_baseline(tmp_path):
     env = dict(os.environ, REPO=os.path.dirname(os.path.dirname(os.path.abspath(__file__))), NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", "29731", str(script)]
-    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
     line = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")][-1]
     out = json.loads(line[7:])

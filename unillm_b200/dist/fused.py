@@ -29,6 +29,8 @@ MAXR = 8
 # counter indices (uint32 words) inside the flag area
 AG0, RS1, AG1, RS0 = 0, 8, 16, 24
 FLAG_WORDS = 64
+ARGMAX_FLAG, ARGMAX_ROUND = 32, 33     # counter of the greedy merge and its (local) round word
+ARGMAX_ROWS = 2048                      # sampled rows per step the merge area can hold
 
 
 @dataclass
@@ -47,12 +49,15 @@ class FusedComm:
         self.rs = [_Area(0, slot), _Area(slot, slot)]
         self.ag = [_Area(2 * slot, slot), _Area(3 * slot, slot)]
         self.flags = _Area(4 * slot, FLAG_WORDS * 4)
+        am = 2 * world * ARGMAX_ROWS * 4
+        self.am_vals = _Area(4 * slot + FLAG_WORDS * 4, am)
+        self.am_ids = _Area(4 * slot + FLAG_WORDS * 4 + am, am)
         self.device = buf.device
 
     @staticmethod
     def nbytes(world: int, hidden: int, max_tokens: int) -> int:
         rows = (max_tokens + world - 1) // world
-        return 4 * world * rows * hidden * 2 + FLAG_WORDS * 4
+        return 4 * world * rows * hidden * 2 + FLAG_WORDS * 4 + 2 * (2 * world * ARGMAX_ROWS * 4)
 
     @classmethod
     def create(cls, spec, rank: int, world: int, group, max_tokens: int, device) -> "FusedComm":
@@ -128,6 +133,29 @@ class FusedComm:
         # norm pushing into ag1 (post-attention) resets [ag0 x 8][rs1]; norm pushing into ag0 resets [ag1 x 8][rs0]
         base = AG0 if k == 1 else AG1
         return (self.local_flag_ptr(base), 9)
+
+    def argmax_merge(self, vals: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """F4: global greedy winners from per-shard (value, id) pairs, exchanged through peer memory."""
+        import ctypes as C
+
+        from ..ops import _native as N
+        from ..ops import cuda_ops
+
+        rows = vals.numel()
+        a = N.UbArgmaxMergeArgs()
+        a.vals, a.ids, a.out_ids = vals.data_ptr(), ids.data_ptr(), out.data_ptr()
+        for r in range(self.world):
+            a.peer_vals[r] = self._peer(r, self.am_vals)
+            a.peer_ids[r] = self._peer(r, self.am_ids)
+            a.peer_flags[r] = self.flag_ptr(r, ARGMAX_FLAG)
+        a.my_vals = self.buf.data_ptr() + self.am_vals.offset
+        a.my_ids = self.buf.data_ptr() + self.am_ids.offset
+        a.my_flag, a.round = self.local_flag_ptr(ARGMAX_FLAG), self.local_flag_ptr(ARGMAX_ROUND)
+        a.world, a.rank, a.rows, a.max_rows = self.world, self.rank, rows, ARGMAX_ROWS
+        a.err = cuda_ops.err_word(self.device).data_ptr()
+        N.check(N.cuda_lib().ub_tp_argmax_merge(C.byref(a), torch.cuda.current_stream(self.device).cuda_stream),
+                "ub_tp_argmax_merge")
+        return out
 
     def reset(self) -> None:
         """Zero all counters (host side); call on every rank, then barrier, after a reported device timeout."""

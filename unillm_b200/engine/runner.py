@@ -389,7 +389,8 @@ class GpuModelRunner:
         self.block_size, self.num_blocks = block_size, num_blocks
         self.max_num_seqs, self.max_tokens, self.max_model_len = max_num_seqs, max_num_batched_tokens, max_model_len
         self.max_blocks_per_seq = (max_model_len + block_size - 1) // block_size
-        self.use_cuda_graphs = use_cuda_graphs
+        # NCCL collectives inside a captured graph stalled on this stack; the baseline path launches eagerly
+        self.use_cuda_graphs = use_cuda_graphs and (self.tp.world == 1 or self.tp.fused)
         s, dev = spec, self.device
         hkv, D = weights.hkv, s.head_dim
         self.k_cache = [torch.zeros(num_blocks, hkv, block_size, D, dtype=torch.bfloat16, device=dev)
@@ -712,6 +713,10 @@ class GpuModelRunner:
             return out
         if greedy:
             ids, vals = K.sample(logits, vocab_offset=tp.rank * self.w.vocab_shard, return_vals=True)
+            if tp.comm is not None and S <= 2048:
+                tp.comm.argmax_merge(vals, ids, out)     # F4: exchange over peer memory, no NCCL call
+                self.launches += 2
+                return out
             allv = tp.all_gather_cat(vals[None], dim=0)
             alli = tp.all_gather_cat(ids[None], dim=0)
             K.argmax_merge(allv.contiguous(), alli.contiguous(), out=out)

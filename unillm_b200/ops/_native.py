@@ -101,6 +101,14 @@ class UbAllReduceArgs(C.Structure):
     ]
 
 
+class UbArgmaxMergeArgs(C.Structure):
+    _fields_ = [
+        ("vals", vp), ("ids", vp), ("out_ids", vp), ("peer_vals", vp * UB_MAX_RANKS), ("peer_ids", vp * UB_MAX_RANKS),
+        ("peer_flags", vp * UB_MAX_RANKS), ("my_vals", vp), ("my_ids", vp), ("my_flag", vp), ("round", vp),
+        ("world", i32), ("rank", i32), ("rows", i32), ("max_rows", i32), ("err", vp),
+    ]
+
+
 class UbDeviceProps(C.Structure):
     _fields_ = [
         ("name", C.c_char * 128), ("total_mem", u64), ("sm_count", i32), ("cc_major", i32), ("cc_minor", i32),
@@ -136,7 +144,7 @@ def cuda_lib() -> C.CDLL:
         lib = C.CDLL(str(cuda_lib_path()))
         for name in (
             "ub_gemm_tn", "ub_norm", "ub_rope_kv_append", "ub_attn_decode", "ub_attn_prefill", "ub_sample",
-            "ub_moe_route", "ub_allreduce_oneshot",
+            "ub_moe_route", "ub_allreduce_oneshot", "ub_tp_argmax_merge",
         ):
             if hasattr(lib, name):
                 getattr(lib, name).restype = i32
