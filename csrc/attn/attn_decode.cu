@@ -305,3 +305,61 @@ extern "C" int ub_attn_merge(const void* o_a, const float* lse_a, const void* o_
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }
+
+// ----------------------------------------------------------------------------------------------
+// Allocation-free variant: the split-KV partials live in a fixed array inside the library image.
+// See attn_decode_static.h for who needs this and for the rules of use.
+// ----------------------------------------------------------------------------------------------
+#include "attn_decode_static.h"
+#include <mutex>
+#include <stdio.h>
+
+static __device__ __align__(256) float g_static_decode_scratch[UB_ATTN_STATIC_SCRATCH_FLOATS];
+
+namespace {
+std::mutex g_static_mu;
+float* g_static_ptr[UB_MAX_DEVICES] = {};   // device address of the array, per device, filled on first use
+thread_local char g_static_err[256] = "";
+}  // namespace
+
+extern "C" const char* ub_attn_decode_static_scratch_error(void) { return g_static_err; }
+
+extern "C" int ub_attn_decode_static_scratch(const UbAttnArgs* a, void* stream_v) {
+  g_static_err[0] = 0;
+  if (a->num_seqs <= 0) return 0;
+  if (a->splits < 1 || a->Hq <= 0 || a->D <= 0) {
+    snprintf(g_static_err, sizeof(g_static_err), "bad arguments: splits=%d Hq=%d D=%d", a->splits, a->Hq, a->D);
+    return -2;
+  }
+  const unsigned long long need = (unsigned long long)a->num_seqs * a->Hq * a->splits * (a->D + 2);
+  if (a->splits > 1 && need > UB_ATTN_STATIC_SCRATCH_FLOATS) {
+    snprintf(g_static_err, sizeof(g_static_err),
+             "split-KV partials need %llu floats but the built-in scratch holds %u; lower splits or the batch",
+             need, (unsigned)UB_ATTN_STATIC_SCRATCH_FLOATS);
+    return UB_ERR_STATIC_SCRATCH_TOO_SMALL;
+  }
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= UB_MAX_DEVICES) {
+    snprintf(g_static_err, sizeof(g_static_err), "no usable current device (index %d)", dev);
+    return UB_ERR_STATIC_SCRATCH_SETUP;
+  }
+  float* ptr;
+  {
+    std::lock_guard<std::mutex> g(g_static_mu);
+    if (g_static_ptr[dev] == nullptr) {
+      // In host code the array's name is only a handle; the address the kernel may use comes from here.
+      void* p = nullptr;
+      const cudaError_t e = cudaGetSymbolAddress(&p, g_static_decode_scratch);
+      if (e != cudaSuccess || p == nullptr) {
+        snprintf(g_static_err, sizeof(g_static_err), "cudaGetSymbolAddress failed on device %d: %s", dev,
+                 cudaGetErrorString(e));
+        return UB_ERR_STATIC_SCRATCH_SETUP;
+      }
+      g_static_ptr[dev] = static_cast<float*>(p);
+    }
+    ptr = g_static_ptr[dev];
+  }
+  UbAttnArgs b = *a;
+  b.scratch = ptr;
+  return ub_attn_decode(&b, stream_v);
+}
