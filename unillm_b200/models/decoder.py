@@ -139,11 +139,15 @@ class DecoderModel(Model):
     # ------------------------------------------------------------------------------------------
     @staticmethod
     def _find(w: ModelWeights, prefixes, names, suffix=".weight"):
+        """First present alias; block-quantised (GGUF) tensors are dequantised on the way in."""
         for pre in prefixes:
             for n in names:
                 t = w.get(pre + n + suffix)
                 if t is not None:
                     return t
+                q = w.get_quantized(pre + n + suffix)
+                if q is not None:
+                    return q.dequantize()
         return None
 
     def _load(self, weights: ModelWeights, dtype=None, device=None):
