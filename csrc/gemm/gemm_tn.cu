@@ -59,7 +59,28 @@ struct GemmParams {
   const uint32_t* ag_flags;     // [world] counters in local memory, one per source rank
   const uint32_t* ag_epoch;     // unused (kept for ABI stability)
   uint32_t ag_signals_per_use;  // counter increments per source rank per use
+  // K13 grouped mode (MoE experts).  grp_tiles == null disables.  One int4 per token tile:
+  // {expert (-1: no work), first row, end row, unused}; rows index the expert-sorted activation matrix.
+  const int4* grp_tiles;
+  int grp_max_tiles;  // token-tile slots in the table
+  int grp_w_rows;     // rows of w per expert; expert e's weights are rows [e*grp_w_rows, (e+1)*grp_w_rows)
 };
+
+// Coordinates of work unit u.  m0/m_end: token rows; nw: row of the weight tile in w; no: first output feature.
+struct TileCoord { int m0, m_end, nw, no; bool valid; };
+__device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int u, int num_m, int tn) {
+  TileCoord c;
+  const int mt = u % num_m, wn = u / num_m;
+  c.no = wn * BM_W;
+  if (p.grp_tiles == nullptr) {
+    c.m0 = mt * tn; c.m_end = p.M; c.nw = c.no; c.valid = true;
+  } else {
+    const int4 t = __ldg(p.grp_tiles + mt);
+    c.valid = t.x >= 0;
+    c.m0 = t.y; c.m_end = t.z; c.nw = t.x * p.grp_w_rows + c.no;
+  }
+  return c;
+}
 
 __device__ __forceinline__ float apply_act(float v, int act) {
   switch (act) {
@@ -116,8 +137,8 @@ struct GemmSmem {
 };
 
 // Final stage of every epilogue: 8 consecutive features of one token row.
-__device__ __forceinline__ void emit8(const GemmParams& p, int m, int nn, float (&v)[8], bool vec_ok) {
-  if (m >= p.M || nn >= p.N) return;
+__device__ __forceinline__ void emit8(const GemmParams& p, int m, int m_end, int nn, float (&v)[8], bool vec_ok) {
+  if (m >= m_end || nn >= p.N) return;
   if (p.residual != nullptr) {
     if (vec_ok) {
       const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + (long long)m * p.ldr + nn);
@@ -171,7 +192,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_m = (p.M + TN - 1) / TN;
+  const int num_m = p.grp_tiles != nullptr ? p.grp_max_tiles : (p.M + TN - 1) / TN;
   const int num_n = (p.N + BM_W - 1) / BM_W;
   const int total_tiles = num_m * num_n;
   const int num_kb = (p.K + BK - 1) / BK;
@@ -228,9 +249,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       int it = 0;
       bool dead = false;
       constexpr int PF = 12;                 // L2 prefetch distance in k-blocks
-      int pf_issued = 0, pf_u = unit_begin, pf_kb = kb0;
+      int pf_issued = 0, pf_u = unit_begin, pf_kb = kb0, pf_n0 = 0;
+      bool pf_valid = true;
       for (int u = unit_begin; u < total_tiles && !dead; u += unit_step) {
-        const int m0 = (u % num_m) * TN, n0 = (u / num_m) * BM_W;
+        const TileCoord tc = tile_coord(p, u, num_m, TN);
+        if (!tc.valid) continue;
+        const int m0 = tc.m0, n0 = tc.nw;
         if (p.ag_world > 0) {
           // Token rows [m0, m0+TN) were pushed by the ranks that own them; wait for those sources.
           // Counters are zeroed by the consumer side between uses (see csrc/norm/norm.cu), so the target is
@@ -261,9 +285,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
           // time than that: ask L2 for the weight tile PF k-blocks ahead, so the smem copies hit in L2.
           for (; pf_issued < it + PF + 1; ++pf_issued) {
             if (pf_u >= total_tiles) break;
-            const int pn0 = (pf_u / num_m) * BM_W;
-            tma_prefetch_l2_2d(&tmap_w, pf_kb * BK, pn0);
-            if (DUAL) tma_prefetch_l2_2d(&tmap_w, pf_kb * BK, pn0 + p.up_row_off);
+            if (pf_kb == kb0) {
+              const TileCoord pc = tile_coord(p, pf_u, num_m, TN);
+              pf_valid = pc.valid;
+              pf_n0 = pc.nw;
+              if (!pf_valid) { pf_u += unit_step; --pf_issued; continue; }
+            }
+            tma_prefetch_l2_2d(&tmap_w, pf_kb * BK, pf_n0);
+            if (DUAL) tma_prefetch_l2_2d(&tmap_w, pf_kb * BK, pf_n0 + p.up_row_off);
             if (++pf_kb >= kb1) { pf_kb = kb0; pf_u += unit_step; }
           }
           const int s = it % STAGES;
@@ -283,9 +312,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       constexpr uint32_t idesc = make_idesc_bf16(BM_W, TN, 0, 0);
       int it = 0, ui = 0;
       bool dead = false;
-      for (int u = unit_begin; u < total_tiles && !dead; u += unit_step, ++ui) {
+      for (int u = unit_begin; u < total_tiles && !dead; u += unit_step) {
+        if (p.grp_tiles != nullptr && __ldg(&p.grp_tiles[u % num_m].x) < 0) continue;
         const int ab = NBUF == 1 ? 0 : (ui & 1);
         const uint32_t aph = NBUF == 1 ? (ui & 1) : ((ui >> 1) & 1);
+        ++ui;
         if (!mbar_wait(&tmem_empty_bar[ab], aph ^ 1, abort_flag, p.err, 400 + ab)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + ab * ACC_COLS;
@@ -322,10 +353,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         (p.residual == nullptr ||
                          ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
     int ui = 0, chunk_ctr = 0;
-    for (int u = unit_begin; u < total_tiles; u += unit_step, ++ui) {
-      const int m0 = (u % num_m) * TN, n0 = (u / num_m) * BM_W;
+    for (int u = unit_begin; u < total_tiles; u += unit_step) {
+      const TileCoord tc = tile_coord(p, u, num_m, TN);
+      if (!tc.valid) continue;
+      const int m0 = tc.m0, n0 = tc.no, m_end = tc.m_end;
       const int ab = NBUF == 1 ? 0 : (ui & 1);
       const uint32_t aph = NBUF == 1 ? (ui & 1) : ((ui >> 1) & 1);
+      ++ui;
       mbar_wait(&tmem_full_bar[ab], aph, abort_flag, p.err, 300 + ab);
       tc_fence_after();
       const uint32_t lane_addr = tmem_base + ab * ACC_COLS + (uint32_t(q * 32) << 16);
@@ -385,7 +419,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
               const float4 lo = *reinterpret_cast<const float4*>(stf + tok * BM_W + c8 * 8);
               const float4 hi = *reinterpret_cast<const float4*>(stf + tok * BM_W + c8 * 8 + 4);
               float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-              emit8(p, m0 + c * CH + tok, n0 + c8 * 8, v, vec_ok);
+              emit8(p, m0 + c * CH + tok, m_end, n0 + c8 * 8, v, vec_ok);
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
           } else {
@@ -407,7 +441,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
               float v[8];
 #pragma unroll
               for (int e = 0; e < 4; ++e) { v[2 * e] = bf16_lo(w[e]); v[2 * e + 1] = bf16_hi(w[e]); }
-              emit8(p, m0 + c * CH + tok, n0 + c8 * 8, v, vec_ok);
+              emit8(p, m0 + c * CH + tok, m_end, n0 + c8 * 8, v, vec_ok);
             }
           }
         }
@@ -462,7 +496,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
           }
           v[e] = x;
         }
-        emit8(p, m0 + tok, nn, v, vec_ok);
+        emit8(p, m0 + tok, p.M, nn, v, vec_ok);
       }
       if (p.rs_world > 0) {
         __threadfence_system();
@@ -551,11 +585,12 @@ static GemmPlan plan_gemm(const UbGemmArgs* a) {
     while (tn < a->M && tn < (dual ? 128 : 256)) tn <<= 1;
   }
   pl.tn = tn;
-  const int num_m = (a->M + tn - 1) / tn, num_n = (a->N + BM_W - 1) / BM_W;
+  const bool grouped = a->grp_tiles != nullptr;
+  const int num_m = grouped ? a->grp_max_tiles : (a->M + tn - 1) / tn, num_n = (a->N + BM_W - 1) / BM_W;
   pl.tiles = num_m * num_n;
   const int num_kb = (a->K + BK - 1) / BK;
   const int sms = num_sms();
-  int splits = a->splits;
+  int splits = grouped ? 1 : a->splits;
   if (splits <= 0) {
     splits = 1;
     if (pl.tiles * 2 <= sms && num_kb >= 8) {
@@ -668,6 +703,12 @@ extern "C" int ub_gemm_tn(const UbGemmArgs* a, void* stream_v) {
   p.out_scale = a->out_scale == 0.f ? 1.f : a->out_scale;
   p.err = a->err;
   p.splits = pl.splits;
+  p.grp_tiles = reinterpret_cast<const int4*>(a->grp_tiles);
+  p.grp_max_tiles = a->grp_max_tiles;
+  p.grp_w_rows = a->grp_w_rows;
+  if (p.grp_tiles != nullptr && (a->tile_tokens <= 0 || a->grp_max_tiles <= 0 || a->grp_w_rows <= 0 || a->rs_world > 0 ||
+                                 a->ag_world > 0 || a->bias != nullptr))
+    return -6;  // grouped mode: fixed token tile, no bias, no fused collectives
   p.rs_world = a->rs_world; p.rs_rank = a->rs_rank; p.rs_rows_per_rank = a->rs_rows_per_rank;
   p.ag_world = a->ag_world; p.ag_rows_per_rank = a->ag_rows_per_rank;
   p.ag_flags = a->ag_flags; p.ag_epoch = a->ag_epoch; p.ag_signals_per_use = a->ag_signals_per_use;
@@ -676,7 +717,7 @@ extern "C" int ub_gemm_tn(const UbGemmArgs* a, void* stream_v) {
     p.rs_peer_flag[i] = a->rs_peer_flag[i];
   }
   CUtensorMap tw, tx;
-  const long long w_rows = dual ? (long long)a->w_rows_total : (long long)a->N;
+  const long long w_rows = (dual || a->grp_tiles != nullptr) ? (long long)a->w_rows_total : (long long)a->N;
   int rc = make_tmap_bf16_2d(&tw, a->w, w_rows, a->K, a->ldw, BM_W, BK);
   if (rc != 0) return rc;
   rc = make_tmap_bf16_2d(&tx, a->x, a->M, a->K, a->ldx, pl.tn, BK);

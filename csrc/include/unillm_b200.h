@@ -55,6 +55,12 @@ typedef struct UbGemmArgs {
   const uint32_t* ag_flags;
   const uint32_t* ag_epoch;
   uint32_t ag_signals_per_use;
+  /* K13 grouped mode (MoE): x is the expert-sorted activation matrix [M, K]; w stacks the experts' weights
+     row-wise ([num_experts * grp_w_rows, K], w_rows_total = that row count).  grp_tiles is the int4 table written
+     by ub_moe_route for token tile `tile_tokens`: {expert or -1, first row, end row, 0}.  NULL disables. */
+  const void* grp_tiles;
+  int grp_max_tiles;
+  int grp_w_rows;
 } UbGemmArgs;
 int ub_gemm_tn(const UbGemmArgs* args, void* stream);
 /* Number of CTAs the launch for `args` will use; each CTA signals every peer once in F1 mode. */
@@ -174,17 +180,24 @@ int ub_l2_normalize(const void* x, void* out, int T, int H, float eps, void* str
 
 /* ---------------- K7 / K13 : MoE ---------------- */
 typedef struct UbMoeRouteArgs {
-  const void* logits;       /* bf16 or fp32 [T, E] router logits */
-  int logits_f32;
-  int T, E, K;
-  int norm_topk;            /* 1: softmax over the K selected (Mixtral); 0: softmax over all E then pick (DeepSeek) */
+  const void* logits;       /* bf16 or fp32 [T, E] router logits; ignored when router_w is set */
+  const void* x;            /* bf16 [T, H] activations (router_w mode) */
+  const void* router_w;     /* bf16 [E, H] or NULL: the kernel computes logits = x router_w^T itself */
   int* topk_ids;            /* [T, K] */
   float* topk_w;            /* [T, K] */
-  int* expert_counts;       /* [E]   (zeroed by the kernel) */
+  int* expert_counts;       /* [E] */
   int* expert_offsets;      /* [E+1] exclusive prefix sums */
   int* sorted_rows;         /* [T*K] source row (t*K + k) for each expert-sorted slot */
   int* row_slot;            /* [T*K] inverse permutation */
+  void* tiles;              /* int4[max_tiles] token-tile table for the grouped GEMM, or NULL */
   int* err;
+  int logits_f32;
+  int T, E, K, H;
+  int norm_topk;            /* 1: softmax over the K selected (Mixtral); 0: softmax over all E, no renormalisation */
+  int round_logits_bf16;    /* router_w mode: round logits to bf16 first (what a bf16 linear layer produces) */
+  float weight_scale;       /* multiplies the routing weights (0 = 1) */
+  int tile_tokens;          /* token tile of the grouped GEMM that will consume `tiles` */
+  int max_tiles;            /* capacity of `tiles`; ceil(T*K / tile_tokens) + E always suffices */
 } UbMoeRouteArgs;
 int ub_moe_route(const UbMoeRouteArgs* args, void* stream);
 int ub_moe_gather(const void* x, const int* sorted_rows, void* out, int rows, int K, int H, void* stream);

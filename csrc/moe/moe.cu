@@ -1,0 +1,208 @@
+// K7: MoE routing (router GEMV + top-k + softmax), expert sort with the token-tile table that drives the grouped
+// GEMM, row gather and weighted combine.
+//
+// What the reference does (crates/runtime/src/model_core.rs:796-905, MoELayer::forward): a dense [T,E] router
+// matmul, softmax, per-token top-k on the host, then a Python-style loop "for each token, for each selected expert,
+// run that expert's MLP on one row".  Here the tokens are sorted by expert once and each expert's rows run as
+// tensor-core tiles of one grouped GEMM launch (csrc/gemm/gemm_tn.cu, grouped mode).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../common/ptx.cuh"
+#include "../include/unillm_b200.h"
+
+namespace ub {
+
+constexpr int MOE_MAX_E = 256;
+constexpr int MOE_MAX_K = 16;
+
+// One CTA of 128 threads per token: logits (from x and the router matrix, or given), top-k, weights.
+__global__ void __launch_bounds__(128) moe_route_kernel(const UbMoeRouteArgs a) {
+  __shared__ float logit[MOE_MAX_E];
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int E = a.E, K = a.K;
+  if (a.router_w != nullptr) {
+    const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(a.x) + (long long)t * a.H;
+    const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(a.router_w);
+    for (int e = warp; e < E; e += 4) {
+      const __nv_bfloat16* we = w + (long long)e * a.H;
+      float acc = 0.f;
+      for (int h = lane * 8; h < a.H; h += 256) {
+        const uint4 xv = *reinterpret_cast<const uint4*>(x + h);
+        const uint4 wv = __ldg(reinterpret_cast<const uint4*>(we + h));
+        const uint32_t* xs = reinterpret_cast<const uint32_t*>(&xv);
+        const uint32_t* ws = reinterpret_cast<const uint32_t*>(&wv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc += bf16_lo(xs[j]) * bf16_lo(ws[j]) + bf16_hi(xs[j]) * bf16_hi(ws[j]);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      // the reference model keeps router logits in the activation dtype: round like a bf16 linear layer would
+      if (lane == 0) logit[e] = a.round_logits_bf16 ? __bfloat162float(__float2bfloat16(acc)) : acc;
+    }
+  } else {
+    for (int e = threadIdx.x; e < E; e += 128)
+      logit[e] = a.logits_f32 ? reinterpret_cast<const float*>(a.logits)[(long long)t * E + e]
+                              : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.logits)[(long long)t * E + e]);
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  // Softmax statistics over all experts (used when the weights are not renormalised over the selection).
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, logit[e]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float den = 0.f;
+  for (int e = lane; e < E; e += 32) den += __expf(logit[e] - mx);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+  uint32_t taken = 0;  // bit j: expert lane + 32*j already selected
+  float sel_l[MOE_MAX_K];
+  int sel_e[MOE_MAX_K];
+  for (int k = 0; k < K; ++k) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane, j = 0; e < E; e += 32, ++j) {
+      if (taken >> j & 1u) continue;
+      const float v = logit[e];
+      if (v > best || (v == best && e < bi)) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if (bi < E && (bi & 31) == lane) taken |= 1u << (bi >> 5);
+    sel_l[k] = best;
+    sel_e[k] = bi < E ? bi : 0;
+  }
+  if (lane == 0) {
+    float s = 0.f;
+    for (int k = 0; k < K; ++k) { sel_l[k] = __expf(sel_l[k] - mx); s += sel_l[k]; }
+    const float inv = a.norm_topk ? 1.f / s : 1.f / den;
+    for (int k = 0; k < K; ++k) {
+      a.topk_ids[(long long)t * K + k] = sel_e[k];
+      a.topk_w[(long long)t * K + k] = sel_l[k] * inv * a.weight_scale;
+    }
+  }
+}
+
+// One CTA: counts, exclusive offsets, slot assignment and the token-tile table of the grouped GEMM.
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const UbMoeRouteArgs a) {
+  __shared__ int cnt[MOE_MAX_E], off[MOE_MAX_E + 1], cur[MOE_MAX_E];
+  const int E = a.E, n = a.T * a.K;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) { cnt[e] = 0; cur[e] = 0; }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&cnt[a.topk_ids[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0, tile = 0;
+    int4* tiles = reinterpret_cast<int4*>(a.tiles);
+    for (int e = 0; e < E; ++e) {
+      off[e] = acc;
+      if (tiles != nullptr) {
+        for (int r = 0; r < cnt[e] && tile < a.max_tiles; r += a.tile_tokens, ++tile)
+          tiles[tile] = make_int4(e, acc + r, acc + cnt[e], 0);
+      }
+      acc += cnt[e];
+    }
+    off[E] = acc;
+    if (tiles != nullptr)
+      for (; tile < a.max_tiles; ++tile) tiles[tile] = make_int4(-1, 0, 0, 0);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+    a.expert_offsets[e] = off[e];
+    if (e < E) a.expert_counts[e] = cnt[e];
+  }
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = a.topk_ids[i];
+    const int slot = off[e] + atomicAdd(&cur[e], 1);
+    a.sorted_rows[slot] = i;
+    a.row_slot[i] = slot;
+  }
+}
+
+// out[slot, :] = x[sorted_rows[slot] / K, :]
+__global__ void __launch_bounds__(256) moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ sorted_rows,
+                                                         __nv_bfloat16* __restrict__ out, int rows, int K, int H) {
+  const int vec = H / 8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < (long long)rows * vec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int slot = int(i / vec), c = int(i % vec);
+    const int src = sorted_rows[slot] / K;
+    reinterpret_cast<uint4*>(out + (long long)slot * H)[c] = __ldg(reinterpret_cast<const uint4*>(x + (long long)src * H) + c);
+  }
+}
+
+// out[t, :] = residual[t, :] + sum_k w[t,k] * y[row_slot[t*K+k], :]
+__global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ row_slot,
+                                                          const float* __restrict__ topk_w, const __nv_bfloat16* __restrict__ residual,
+                                                          __nv_bfloat16* __restrict__ out, int T, int K, int H) {
+  const int vec = H / 8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < (long long)T * vec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int t = int(i / vec), c = int(i % vec);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (residual != nullptr) {
+      const uint4 r = __ldg(reinterpret_cast<const uint4*>(residual + (long long)t * H) + c);
+      const uint32_t* rs = reinterpret_cast<const uint32_t*>(&r);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { acc[2 * j] = bf16_lo(rs[j]); acc[2 * j + 1] = bf16_hi(rs[j]); }
+    }
+    for (int k = 0; k < K; ++k) {
+      const float w = topk_w[(long long)t * K + k];
+      const int slot = row_slot[(long long)t * K + k];
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(y + (long long)slot * H) + c);
+      const uint32_t* vs = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { acc[2 * j] += w * bf16_lo(vs[j]); acc[2 * j + 1] += w * bf16_hi(vs[j]); }
+    }
+    reinterpret_cast<uint4*>(out + (long long)t * H)[c] =
+        make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+  }
+}
+
+}  // namespace ub
+
+extern "C" int ub_moe_route(const UbMoeRouteArgs* a, void* stream_v) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_v);
+  if (a->T <= 0) return 0;
+  if (a->E <= 0 || a->E > ub::MOE_MAX_E || a->K <= 0 || a->K > ub::MOE_MAX_K || a->K > a->E) return -2;
+  if (a->router_w != nullptr && (a->H % 8 != 0 || a->x == nullptr)) return -3;
+  if (a->tiles != nullptr && (a->tile_tokens <= 0 || a->max_tiles <= 0)) return -4;
+  UbMoeRouteArgs b = *a;
+  if (b.weight_scale == 0.f) b.weight_scale = 1.f;
+  ub::moe_route_kernel<<<a->T, 128, 0, st>>>(b);
+  ub::moe_sort_kernel<<<1, 1024, 0, st>>>(b);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+extern "C" int ub_moe_gather(const void* x, const int* sorted_rows, void* out, int rows, int K, int H, void* stream_v) {
+  if (rows <= 0) return 0;
+  if (H % 8 != 0) return -2;
+  const long long work = (long long)rows * (H / 8);
+  int blocks = int((work + 255) / 256);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  ub::moe_gather_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), sorted_rows, reinterpret_cast<__nv_bfloat16*>(out), rows, K, H);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+extern "C" int ub_moe_combine(const void* y, const int* row_slot, const float* topk_w, const void* residual, void* out, int T,
+                              int K, int H, void* stream_v) {
+  if (T <= 0) return 0;
+  if (H % 8 != 0) return -2;
+  const long long work = (long long)T * (H / 8);
+  int blocks = int((work + 255) / 256);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  ub::moe_combine_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(y), row_slot, topk_w, reinterpret_cast<const __nv_bfloat16*>(residual),
+      reinterpret_cast<__nv_bfloat16*>(out), T, K, H);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}

@@ -1,0 +1,59 @@
+"""Mixture-of-experts block of the GPU runner.
+
+Five launches for the routed experts: route (router GEMV + top-k + sort + tile table, 2 kernels), gather, grouped
+gate/up GEMM with the activation in its epilogue, grouped down GEMM, weighted combine with the residual.  The
+reference walks tokens and experts on the host (``crates/runtime/src/model_core.rs:796-905``); here nothing about
+the routing ever reaches the host, so the block sits inside a CUDA graph like any dense layer.
+
+Tensor parallelism shards every expert's FFN width across the ranks (each rank holds all experts), so the combine
+output is a partial sum that is all-reduced once, together with the shared experts / parallel dense MLP.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import cuda_ops as K
+
+
+def moe_partial(runner, i: int, h: torch.Tensor, residual=None) -> torch.Tensor:
+    """MoE output for hidden rows ``h`` ([T, H]).  With ``residual`` (single rank only) it is added in the combine."""
+    s, t = runner.spec, runner.w.t
+    m = s.moe
+    L = f"layers.{i}."
+    T = h.shape[0]
+    with runner._prof("moe_route"):
+        r = K.moe_route(h, t[L + "router"], m.top_k, norm_topk=m.normalize_topk, round_logits_bf16=False)
+        xs = K.moe_gather(h, r)
+    runner.launches += 3
+    gu, dn = t[L + "experts_gate_up"], t[L + "experts_down"]
+    with runner._prof(f"moe_gate_up[{T * m.top_k}x{gu.shape[1]}x{gu.shape[2]}]"):
+        if m.gated:
+            a = K.grouped_gemm(xs, gu, r, dual_rows=gu.shape[1] // 2, act=m.act)
+        else:
+            a = K.grouped_gemm(xs, gu, r, act=m.act)
+    with runner._prof(f"moe_down[{T * m.top_k}x{dn.shape[1]}x{dn.shape[2]}]"):
+        y = K.grouped_gemm(a, dn, r)
+    base = residual
+    if m.num_shared_experts:
+        Is = t[L + "shared_gate_up"].shape[0] // 2
+        sh = runner._gemm(h, t[L + "shared_gate_up"], dual_rows=Is, act=m.act)
+        base = runner._gemm(sh, t[L + "shared_down"], residual=residual)
+    if m.dense_parallel and (L + "w_down") in t:
+        d = runner._mlp_noresid(i, h, dense_only=True)
+        base = d if base is None else K.add(base, d)
+        runner.launches += 1
+    with runner._prof("moe_combine"):
+        out = K.moe_combine(y, r, residual=base)
+    runner.launches += 3
+    return out
+
+
+def moe_forward(runner, i: int, h: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+    """``residual + MoE(h)`` including the tensor-parallel reduction."""
+    tp = runner.tp
+    if tp.world == 1:
+        return moe_partial(runner, i, h, residual)
+    y = moe_partial(runner, i, h, None)
+    tp.all_reduce(y)
+    runner.launches += 1
+    return K.add(y, residual)

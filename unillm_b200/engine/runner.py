@@ -683,9 +683,13 @@ class GpuModelRunner:
         self._final_norm_done = True
         return h_full
 
-    def _mlp_noresid(self, i, h):
+    def _mlp_noresid(self, i, h, dense_only=False):
         s, t = self.spec, self.w.t
         L = f"layers.{i}."
+        if s.layer_is_moe(i) and not dense_only:
+            from .moe_runner import moe_partial
+
+            return moe_partial(self, i, h, None)
         if s.mlp == "gated":
             I = t[L + "w_gate_up"].shape[0] // 2
             a = self._gemm(h, t[L + "w_gate_up"], dual_rows=I, act=s.act)

@@ -43,6 +43,7 @@ class UbGemmArgs(C.Structure):
         ("rs_peer_out", vp * UB_MAX_RANKS), ("rs_peer_flag", vp * UB_MAX_RANKS),
         ("ag_world", i32), ("ag_rows_per_rank", i32),
         ("ag_flags", vp), ("ag_epoch", vp), ("ag_signals_per_use", u32),
+        ("grp_tiles", vp), ("grp_max_tiles", i32), ("grp_w_rows", i32),
     ]
 
 
@@ -88,9 +89,10 @@ class UbSampleArgs(C.Structure):
 
 class UbMoeRouteArgs(C.Structure):
     _fields_ = [
-        ("logits", vp), ("logits_f32", i32), ("T", i32), ("E", i32), ("K", i32), ("norm_topk", i32),
-        ("topk_ids", vp), ("topk_w", vp), ("expert_counts", vp), ("expert_offsets", vp),
-        ("sorted_rows", vp), ("row_slot", vp), ("err", vp),
+        ("logits", vp), ("x", vp), ("router_w", vp), ("topk_ids", vp), ("topk_w", vp), ("expert_counts", vp),
+        ("expert_offsets", vp), ("sorted_rows", vp), ("row_slot", vp), ("tiles", vp), ("err", vp),
+        ("logits_f32", i32), ("T", i32), ("E", i32), ("K", i32), ("H", i32), ("norm_topk", i32),
+        ("round_logits_bf16", i32), ("weight_scale", f32), ("tile_tokens", i32), ("max_tiles", i32),
     ]
 
 

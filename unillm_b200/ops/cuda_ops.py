@@ -65,7 +65,8 @@ def _bf16c(t: torch.Tensor, name: str) -> None:
 def gemm_tn(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
             residual: Optional[torch.Tensor] = None, act: Optional[str] = None, out: Optional[torch.Tensor] = None,
             out_dtype: torch.dtype = torch.bfloat16, out_scale: float = 1.0, tile_tokens: int = 0, splits: int = 0,
-            dual_rows: int = 0, rs: Optional[dict] = None, ag: Optional[dict] = None) -> torch.Tensor:
+            dual_rows: int = 0, rs: Optional[dict] = None, ag: Optional[dict] = None,
+            grouped: Optional[dict] = None) -> torch.Tensor:
     """``out[M, N] = act(x[M, K] @ w[N, K]^T * out_scale + bias) + residual`` on tcgen05 tensor cores.
 
     ``dual_rows = I`` switches to the gated form: ``w`` is ``[2*I, K]`` with gate rows first and the
@@ -117,6 +118,9 @@ def gemm_tn(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = 
     if ag is not None:
         a.ag_world, a.ag_rows_per_rank = ag["world"], ag["rows_per_rank"]
         a.ag_flags, a.ag_signals_per_use = ag["flags"], ag["signals_per_use"]
+    if grouped is not None:
+        a.grp_tiles, a.grp_max_tiles, a.grp_w_rows = grouped["tiles"], grouped["max_tiles"], grouped["w_rows"]
+        a.tile_tokens = grouped["tile_tokens"]
     N.check(N.cuda_lib().ub_gemm_tn(C.byref(a), _stream(x)), "ub_gemm_tn")
     return out
 
@@ -424,4 +428,131 @@ def l2_normalize(x: torch.Tensor, eps: float = 1e-12) -> torch.Tensor:
     lib.ub_l2_normalize.restype = C.c_int
     lib.ub_l2_normalize.argtypes = [N.vp, N.vp, N.i32, N.i32, N.f32, N.vp]
     N.check(lib.ub_l2_normalize(x.data_ptr(), out.data_ptr(), x.numel() // H, H, eps, _stream(x)), "ub_l2_normalize")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# Mixture of experts
+# ------------------------------------------------------------------------------------------------
+class MoeRouting:
+    """Device-side routing state of one MoE layer call (all int32 / fp32 tensors, sized from T, K, E)."""
+
+    __slots__ = ("T", "K", "E", "tile_tokens", "max_tiles", "topk_ids", "topk_w", "counts", "offsets", "sorted_rows",
+                 "row_slot", "tiles")
+
+    def __init__(self, T: int, K: int, E: int, tile_tokens: int, device):
+        self.T, self.K, self.E, self.tile_tokens = T, K, E, tile_tokens
+        self.max_tiles = (T * K + tile_tokens - 1) // tile_tokens + E
+        i32 = dict(dtype=torch.int32, device=device)
+        self.topk_ids = torch.empty(T, K, **i32)
+        self.topk_w = torch.empty(T, K, dtype=torch.float32, device=device)
+        self.counts = torch.empty(E, **i32)
+        self.offsets = torch.empty(E + 1, **i32)
+        self.sorted_rows = torch.empty(T * K, **i32)
+        self.row_slot = torch.empty(T * K, **i32)
+        self.tiles = torch.empty(self.max_tiles, 4, **i32)
+
+
+def moe_tile_tokens(T: int, K: int, E: int) -> int:
+    """Token tile for the grouped GEMM: the power of two covering the mean rows per expert, 16..128."""
+    avg = max(1, (T * K + E - 1) // E)
+    tn = 16
+    while tn < avg and tn < 128:
+        tn <<= 1
+    return tn
+
+
+def moe_route(x: Optional[torch.Tensor], router_w: Optional[torch.Tensor], top_k: int, *, norm_topk: bool = True,
+              logits: Optional[torch.Tensor] = None, weight_scale: float = 1.0, tile_tokens: int = 0,
+              round_logits_bf16: bool = True, routing: Optional[MoeRouting] = None) -> MoeRouting:
+    """Router GEMV + top-k + softmax weights + expert sort + grouped-GEMM tile table, two launches."""
+    if router_w is not None:
+        _bf16c(x, "x"), _bf16c(router_w, "router_w")
+        T, H = x.shape
+        E = router_w.shape[0]
+        dev = x.device
+    else:
+        T, E = logits.shape
+        H = 0
+        dev = logits.device
+        if not logits.is_contiguous():
+            raise ValueError("logits must be contiguous")
+    tn = tile_tokens or moe_tile_tokens(T, top_k, E)
+    r = routing if routing is not None else MoeRouting(T, top_k, E, tn, dev)
+    a = N.UbMoeRouteArgs()
+    a.logits, a.x, a.router_w = _p(logits), _p(x) if router_w is not None else None, _p(router_w)
+    a.topk_ids, a.topk_w = r.topk_ids.data_ptr(), r.topk_w.data_ptr()
+    a.expert_counts, a.expert_offsets = r.counts.data_ptr(), r.offsets.data_ptr()
+    a.sorted_rows, a.row_slot, a.tiles = r.sorted_rows.data_ptr(), r.row_slot.data_ptr(), r.tiles.data_ptr()
+    a.err = err_word(dev).data_ptr()
+    a.logits_f32 = 1 if (logits is not None and logits.dtype == torch.float32) else 0
+    a.T, a.E, a.K, a.H = T, E, top_k, H
+    a.norm_topk = 1 if norm_topk else 0
+    a.round_logits_bf16 = 1 if round_logits_bf16 else 0
+    a.weight_scale = weight_scale
+    a.tile_tokens, a.max_tiles = r.tile_tokens, r.max_tiles
+    N.check(N.cuda_lib().ub_moe_route(C.byref(a), torch.cuda.current_stream(dev).cuda_stream), "ub_moe_route")
+    return r
+
+
+def moe_gather(x: torch.Tensor, r: MoeRouting, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[slot] = x[sorted_rows[slot] // K]``: activations in expert order."""
+    _bf16c(x, "x")
+    T, H = x.shape
+    if out is None:
+        out = torch.empty(T * r.K, H, dtype=torch.bfloat16, device=x.device)
+    lib = N.cuda_lib()
+    lib.ub_moe_gather.restype = C.c_int
+    lib.ub_moe_gather.argtypes = [N.vp, N.vp, N.vp, N.i32, N.i32, N.i32, N.vp]
+    N.check(lib.ub_moe_gather(x.data_ptr(), r.sorted_rows.data_ptr(), out.data_ptr(), T * r.K, r.K, H, _stream(x)),
+            "ub_moe_gather")
+    return out
+
+
+def moe_combine(y: torch.Tensor, r: MoeRouting, residual: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[t] = residual[t] + sum_k w[t,k] * y[row_slot[t,k]]``."""
+    _bf16c(y, "y")
+    H = y.shape[1]
+    if out is None:
+        out = torch.empty(r.T, H, dtype=torch.bfloat16, device=y.device)
+    lib = N.cuda_lib()
+    lib.ub_moe_combine.restype = C.c_int
+    lib.ub_moe_combine.argtypes = [N.vp, N.vp, N.vp, N.vp, N.vp, N.i32, N.i32, N.i32, N.vp]
+    N.check(lib.ub_moe_combine(y.data_ptr(), r.row_slot.data_ptr(), r.topk_w.data_ptr(), _p(residual), out.data_ptr(),
+                               r.T, r.K, H, _stream(y)), "ub_moe_combine")
+    return out
+
+
+def grouped_gemm(x_sorted: torch.Tensor, w: torch.Tensor, r: MoeRouting, *, dual_rows: int = 0, act: Optional[str] = None,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Expert-grouped GEMM: rows of ``x_sorted`` that belong to expert e multiply ``w[e]`` (``[E, rows, K]``).
+
+    ``dual_rows = I``: ``w[e]`` is ``[2I, K]`` (gate rows then up rows) and the result is ``act(gate) * up``.
+    """
+    if w.dim() != 3 or not w.is_contiguous():
+        raise ValueError("grouped_gemm takes contiguous weights [E, rows, K]")
+    E, rows, Kd = w.shape
+    g = {"tiles": r.tiles.data_ptr(), "max_tiles": r.max_tiles, "w_rows": rows, "tile_tokens": r.tile_tokens}
+    n_out = dual_rows if dual_rows else rows
+    if out is None:
+        out = torch.empty(x_sorted.shape[0], n_out, dtype=torch.bfloat16, device=x_sorted.device)
+    w2 = w.view(E * rows, Kd)
+    if dual_rows:
+        return gemm_tn(x_sorted, w2, dual_rows=dual_rows, act=act, out=out, grouped=g)
+    # non-dual: N is the per-expert row count while w2 has E*rows rows
+    return _gemm_grouped_plain(x_sorted, w2, rows, act, out, g)
+
+
+def _gemm_grouped_plain(x, w2, rows, act, out, g):
+    a = N.UbGemmArgs()
+    a.x, a.w, a.out = x.data_ptr(), w2.data_ptr(), out.data_ptr()
+    a.err = err_word(x.device).data_ptr()
+    a.M, a.N, a.K = x.shape[0], rows, x.shape[1]
+    a.ldx, a.ldw, a.ldo = x.stride(0), w2.stride(0), out.stride(0)
+    a.act = N.ACT[act]
+    a.w_rows_total = w2.shape[0]
+    a.out_scale = 1.0
+    a.grp_tiles, a.grp_max_tiles, a.grp_w_rows, a.tile_tokens = g["tiles"], g["max_tiles"], g["w_rows"], g["tile_tokens"]
+    N.check(N.cuda_lib().ub_gemm_tn(C.byref(a), _stream(x)), "ub_gemm_tn(grouped)")
     return out
