@@ -208,17 +208,24 @@ int ub_moe_combine(const void* y, const int* row_slot, const float* topk_w, cons
 int ub_dequant(const void* blocks, void* out_bf16, long long n_elems, int qtype, void* stream); /* qtype: 2=Q4_0 8=Q8_0 12=Q4_K 14=Q6_K */
 int ub_qgemv(const void* blocks, const void* x, void* out, int M, int N, int K, int qtype, void* stream); /* out[M,N] = x[M,K] @ deq(w[N,K])^T, M <= 8 */
 
-/* ---------------- K11 / K14-K17 : conv and scans ---------------- */
-int ub_causal_dwconv1d(const void* x, const void* w, const void* b, void* out, void* state, int B, int L, int C,
-                       int Kw, int act_silu, void* stream);
-int ub_selective_scan(const void* u, const void* delta, const void* A, const void* Bm, const void* Cm, const void* Dv,
-                      const void* z, void* out, float* state, int B, int L, int Dm, int Ns, int delta_softplus,
-                      void* stream);
-int ub_linear_recurrence(const void* a, const void* x, void* out, float* state, int B, int L, int C, void* stream);
-int ub_wkv4(const void* k, const void* v, const float* w, const float* u, void* out, float* state, int B, int L,
-            int C, void* stream);
-int ub_wkv6(const void* r, const void* k, const void* v, const void* w, const float* u, void* out, float* state,
-            int B, int L, int H, int Dh, void* stream);
+/* ---------------- K14-K17, K15 : recurrences of the O(1)-state models ----------------
+   Activations are bf16 [B, L, C] (channel last); parameters and states are fp32 unless noted.  A NULL state means
+   "start from zero and do not store".  L = prompt length for prefill, 1 for decode. */
+/* state: bf16 [B, Kw-1, C], the inputs before this call; updated to the last Kw-1 inputs when update_state. */
+int ub_causal_dwconv1d(const void* x, const float* w /*[C,Kw]*/, const float* b /*[C] or NULL*/, void* out, void* state, int B,
+                       int L, int C, int Kw, int act_silu, int update_state, void* stream);
+/* A [Dm,Ns], Bm/Cm bf16 [B,L,Ns], Dv [Dm] or NULL, z bf16 [B,L,Dm] or NULL (gate: y *= silu(z)), state [B,Dm,Ns]. */
+int ub_selective_scan(const void* u, const void* delta, const float* A, const void* Bm, const void* Cm, const float* Dv,
+                      const void* z, void* out, float* state, int B, int L, int Dm, int Ns, int delta_softplus, void* stream);
+/* h = a*h + (one_minus ? 1-a : 1)*x;  a is [C] or, with a_per_step, [B,L,C];  state [B,C]. */
+int ub_linear_recurrence(const float* a, int a_per_step, const void* x, void* out, float* state, int B, int L, int C,
+                         int one_minus, void* stream);
+/* w = -exp(time_decay) [C], u = time_first [C], state [B,3,C] = (aa, bb, pp), fresh sequences start at (0, 0, -1e38). */
+int ub_wkv4(const void* k, const void* v, const float* w, const float* u, void* out, float* state, int B, int L, int C,
+            void* stream);
+/* w fp32 [B,L,H*Dh] pre-activation decay (decay = exp(-exp(w))), u [H*Dh], state [B,H,Dh,Dh]; Dh = 64 or 32. */
+int ub_wkv6(const void* r, const void* k, const void* v, const float* w, const float* u, void* out, float* state, int B,
+            int L, int H, int Dh, void* stream);
 
 /* ---------------- comm helpers ---------------- */
 int ub_bump_epoch(uint32_t* epoch, void* stream);

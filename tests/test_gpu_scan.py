@@ -1,0 +1,104 @@
+"""Recurrence kernels (conv, selective scan, linear recurrence, WKV-4, WKV-6) against the PyTorch fp32 oracle, including
+state carry-over across calls; Mamba and RWKV models in bf16 on the GPU against their fp32 CPU selves."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _bf(t):
+    return t.to(torch.bfloat16)
+
+
+def _close(got, ref, tol):
+    err = (got.float().cpu() - ref.float()).abs().max().item()
+    assert err < tol * max(1.0, ref.float().abs().max().item()), err
+
+
+@pytest.mark.parametrize("B,L,Cn,Kw", [(2, 37, 96, 4), (3, 1, 257, 4), (1, 600, 64, 3)])
+def test_dwconv1d(B, L, Cn, Kw):
+    from unillm_b200.ops import recurrent as R
+
+    g = torch.Generator().manual_seed(L)
+    x, w, b = _bf(torch.randn(B, L, Cn, generator=g)), torch.randn(Cn, Kw, generator=g), torch.randn(Cn, generator=g)
+    st0 = _bf(torch.randn(B, Kw - 1, Cn, generator=g))
+    st_ref, st_dev = st0.clone(), st0.clone().cuda()
+    ref = R.causal_dwconv1d(x, w, b, st_ref, act_silu=True)
+    got = R.causal_dwconv1d(x.cuda(), w.cuda(), b.cuda(), st_dev, act_silu=True)
+    _close(got, ref, 0.02)
+    assert torch.equal(st_dev.cpu(), st_ref)
+    x2 = _bf(torch.randn(B, 2, Cn, generator=g))
+    _close(R.causal_dwconv1d(x2.cuda(), w.cuda(), b.cuda(), st_dev), R.causal_dwconv1d(x2, w, b, st_ref), 0.02)
+    assert torch.equal(st_dev.cpu(), st_ref)
+
+
+@pytest.mark.parametrize("B,L,Dm,Ns", [(2, 50, 96, 16), (1, 1, 130, 16), (2, 33, 64, 8)])
+def test_selective_scan(B, L, Dm, Ns):
+    from unillm_b200.ops import recurrent as R
+
+    g = torch.Generator().manual_seed(Dm)
+    u, dt, z = (_bf(torch.randn(B, L, Dm, generator=g)) for _ in range(3))
+    Bm, Cm = (_bf(torch.randn(B, L, Ns, generator=g)) for _ in range(2))
+    A, Dv = -torch.rand(Dm, Ns, generator=g) * 2, torch.randn(Dm, generator=g)
+    st_ref = torch.randn(B, Dm, Ns, generator=g) * 0.1
+    st_dev = st_ref.clone().cuda()
+    ref = R.selective_scan(u, dt, A, Bm, Cm, Dv, z, st_ref)
+    got = R.selective_scan(u.cuda(), dt.cuda(), A.cuda(), Bm.cuda(), Cm.cuda(), Dv.cuda(), z.cuda(), st_dev)
+    _close(got, ref, 0.03)
+    _close(st_dev, st_ref, 0.01)
+
+
+def test_linear_recurrence_and_wkv():
+    from unillm_b200.ops import recurrent as R
+
+    g = torch.Generator().manual_seed(5)
+    B, L, Cn = 2, 70, 200
+    x, a = _bf(torch.randn(B, L, Cn, generator=g)), torch.rand(Cn, generator=g)
+    s_ref = torch.zeros(B, Cn)
+    s_dev = s_ref.clone().cuda()
+    _close(R.linear_recurrence(a.cuda(), x.cuda(), s_dev, True), R.linear_recurrence(a, x, s_ref, True), 0.02)
+    _close(s_dev, s_ref, 0.01)
+    ap = torch.rand(B, L, Cn, generator=g)
+    _close(R.linear_recurrence(ap.cuda(), x.cuda(), None, False), R.linear_recurrence(ap, x, None, False), 0.02)
+    k, v = _bf(torch.randn(B, L, Cn, generator=g)), _bf(torch.randn(B, L, Cn, generator=g))
+    wd, u = -torch.exp(torch.randn(Cn, generator=g)), torch.randn(Cn, generator=g)
+    s4r = R.wkv4_new_state(B, Cn, "cpu")
+    s4d = R.wkv4_new_state(B, Cn, "cuda")
+    _close(R.wkv4(k.cuda(), v.cuda(), wd.cuda(), u.cuda(), s4d), R.wkv4(k, v, wd, u, s4r), 0.02)
+    _close(s4d[:, :2], s4r[:, :2], 0.01)
+    for H, Dh in ((3, 64), (4, 32)):
+        r6, k6, v6 = (_bf(torch.randn(B, L, H * Dh, generator=g) * 0.5) for _ in range(3))
+        w6, u6 = torch.randn(B, L, H * Dh, generator=g) - 1.0, torch.randn(H * Dh, generator=g) * 0.3
+        s6r = torch.zeros(B, H, Dh, Dh)
+        s6d = s6r.clone().cuda()
+        _close(R.wkv6(r6.cuda(), k6.cuda(), v6.cuda(), w6.cuda(), u6.cuda(), H, s6d), R.wkv6(r6, k6, v6, w6, u6, H, s6r), 0.03)
+        _close(s6d, s6r, 0.02)
+
+
+@pytest.mark.parametrize("name", ["mamba", "rwkv4", "rwkv6", "recurrent_gemma"])
+def test_state_models_bf16_gpu_vs_fp32_cpu(name):
+    from unillm_b200.model_core import ModelInputs
+    from unillm_b200.models import ALL_MODELS, configs as C
+    from unillm_b200.ops import cuda_ops
+
+    cfgs = {
+        "mamba": C.MambaConfig(vocab_size=512, hidden_size=256, num_hidden_layers=2),
+        "rwkv4": C.Rwkv4Config(vocab_size=512, hidden_size=256, num_hidden_layers=2),
+        "rwkv6": C.Rwkv6Config(vocab_size=512, hidden_size=256, num_hidden_layers=2, head_size=64),
+        "recurrent_gemma": C.RecurrentGemmaConfig(vocab_size=512, hidden_size=256, num_hidden_layers=4, intermediate_size=512,
+                                                  num_attention_heads=4, num_key_value_heads=1, head_dim=64,
+                                                  max_position_embeddings=256),
+    }
+    cls = ALL_MODELS[name]
+    m = cls.new(cfgs[name], init="random", seed=4)
+    m.p = {k: v.to(torch.bfloat16).float() for k, v in m.p.items()}
+    ids = torch.randint(0, 512, (2, 40), generator=torch.Generator().manual_seed(0))
+    ref = m.forward(ModelInputs.text(ids)).main_tensor()
+    md = cls.from_weights(cfgs[name], m.export_hf(), dtype=torch.bfloat16, device="cuda")
+    cache = md.new_cache()
+    got = torch.cat([md.forward_with_cache(ids[:, :33].cuda(), cache)] +
+                    [md.forward_with_cache(ids[:, i:i + 1].cuda(), cache) for i in range(33, 40)], 1)
+    torch.cuda.synchronize()
+    cuda_ops.check_device_errors()
+    err = (got.float().cpu() - ref).abs().max().item()
+    assert err < 0.08 * max(1.0, ref.abs().max().item()), err

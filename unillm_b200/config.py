@@ -33,7 +33,7 @@ class ModelConfig:
     def hidden_size_(self) -> int:
         return int(getattr(self, "hidden_size"))
 
-    def num_layers(self) -> int:
+    def num_layers_(self) -> int:
         return int(getattr(self, "num_hidden_layers"))
 
     def validate(self, tp: int = 1) -> None:
@@ -41,7 +41,7 @@ class ModelConfig:
             raise ValidationFailed("vocab_size must be > 0")
         if self.hidden_size_() <= 0:
             raise ValidationFailed("hidden_size must be > 0")
-        if self.num_layers() <= 0:
+        if self.num_layers_() <= 0:
             raise ValidationFailed("num_layers must be > 0")
         nh = getattr(self, "num_attention_heads", None)
         nkv = getattr(self, "num_key_value_heads", None)
