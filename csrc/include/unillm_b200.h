@@ -205,8 +205,10 @@ int ub_moe_combine(const void* y, const int* row_slot, const float* topk_w, cons
                    int K, int H, void* stream);
 
 /* ---------------- K12 : GGUF-quantised weights ---------------- */
-int ub_dequant(const void* blocks, void* out_bf16, long long n_elems, int qtype, void* stream); /* qtype: 2=Q4_0 8=Q8_0 12=Q4_K 14=Q6_K */
-int ub_qgemv(const void* blocks, const void* x, void* out, int M, int N, int K, int qtype, void* stream); /* out[M,N] = x[M,K] @ deq(w[N,K])^T, M <= 8 */
+/* qtype is the ggml type id: 2 Q4_0, 3 Q4_1, 6 Q5_0, 8 Q8_0, 12 Q4_K, 14 Q6_K. */
+int ub_dequant(const void* blocks, void* out_bf16, long long n_elems, int qtype, void* stream);
+/* out[M,N] (bf16) = x[M,K] (bf16) @ dequant(w[N,K])^T for M <= 8 without materialising w. */
+int ub_qgemv(const void* blocks, const void* x, void* out, int M, int N, int K, int qtype, void* stream);
 
 /* ---------------- K14-K17, K15 : recurrences of the O(1)-state models ----------------
    Activations are bf16 [B, L, C] (channel last); parameters and states are fp32 unless noted.  A NULL state means
