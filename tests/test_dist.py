@@ -1,0 +1,209 @@
+"""Host-side distributed logic on CPU: heartbeat / watchdog / fault injection (threads and gloo-free TCPStore
+processes), tensor-parallel shard arithmetic over a gloo group, engine snapshot / restore."""
+import json
+import socket
+import time
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from unillm_b200.dist.health import (DictStore, FailureDetector, FaultInjector, Heartbeat, RankFailure, RecoveryPlan,
+                                     StepWatchdog)
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_heartbeat_watchdog_in_process():
+    store = DictStore()
+    hbs = [Heartbeat(store, r, 3, interval=0.02, timeout=0.25).start() for r in range(3)]
+    try:
+        for step in range(3):
+            for h in hbs:
+                h.set_step(step)
+        time.sleep(0.1)
+        det = FailureDetector(hbs[0], StepWatchdog(hbs[0], max_lag=1, stall_timeout=10))
+        rep = det.poll()
+        assert rep.healthy and rep.status() == "healthy" and not rep.dead
+        inj = FaultInjector(hbs[2])
+        inj.mute_heartbeat()
+        hbs[0].set_step(5), hbs[1].set_step(5)
+        time.sleep(0.4)
+        rep = det.poll()
+        assert rep.dead == [2] and rep.status() == "unhealthy"
+        with pytest.raises(RankFailure) as e:
+            det.check()
+        assert e.value.ranks == [2]
+        inj.mute_heartbeat(False)
+        time.sleep(0.1)
+        rep = det.poll()
+        assert rep.dead == [] and rep.lagging == [2] and rep.status() == "degraded"
+        det2 = FailureDetector(hbs[1], device_error_check=lambda: "flag wait timed out (peer 3)")
+        assert det2.poll().device_error and not det2.poll().healthy
+    finally:
+        for h in hbs:
+            h.stop()
+
+
+def test_fault_injector_and_recovery_plan():
+    inj = FaultInjector()
+    inj.fail_at_step(2)
+    inj.before_step(1, 0)
+    with pytest.raises(RankFailure):
+        inj.before_step(2, 0)
+    inj2 = FaultInjector()
+    inj2.exhaust_allocator_after(2)
+    assert [inj2.on_alloc() for _ in range(4)] == [False, False, True, True]
+    reqs = [{"id": 0, "prompt": [1, 2, 3], "output": [7, 8], "max_tokens": 5}, {"id": 1, "prompt": [4], "output": [9] * 4, "max_tokens": 4}]
+    plan = RecoveryPlan.make(8, dead=[5], num_heads=32, num_kv_heads=8, requests=reqs)
+    assert plan.new_world == 4 and plan.survivors == [0, 1, 2, 3, 4, 6, 7] and plan.new_ranks == {0: 0, 1: 1, 2: 2, 3: 3}
+    assert plan.requeue == [{"prompt": [1, 2, 3, 7, 8], "done": 2, "max_tokens": 3, "id": 0}]
+    assert RecoveryPlan.make(8, [0, 1, 2, 3, 4, 5], 32, 8).new_world == 2
+    assert RecoveryPlan.make(2, [1], 32, 8).new_world == 1
+
+
+def _hb_worker(rank, world, port, q):
+    from torch.distributed import TCPStore
+
+    store = TCPStore("127.0.0.1", port, world, is_master=(rank == 0), wait_for_workers=True, timeout=__import__("datetime").timedelta(seconds=30))
+    hb = Heartbeat(store, rank, world, interval=0.05, timeout=0.6).start()
+    inj = FaultInjector(hb)
+    if rank == 2:
+        inj.exit_at_step(3)
+    det = FailureDetector(hb, StepWatchdog(hb, max_lag=100))
+    try:
+        for step in range(200):
+            inj.before_step(step, rank)
+            hb.set_step(step)
+            time.sleep(0.02)            # the "step"
+            det.check()
+        q.put((rank, "no failure seen", None))
+    except RankFailure as e:
+        plan = RecoveryPlan.make(world, e.ranks, num_heads=4, num_kv_heads=2)
+        q.put((rank, "detected", (e.ranks, plan.new_world, hb._step)))
+        if rank == 0:
+            time.sleep(1.0)             # keep the store alive until the other observer has reported
+    except SystemExit:
+        q.put((rank, "exited", hb._step))
+    finally:
+        hb.stop()
+
+
+def test_rank_exit_is_detected_by_peers():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_hb_worker, args=(r, 3, port, q)) for r in range(3)]
+    for p in procs:
+        p.start()
+    got = {}
+    for _ in range(3):
+        r, what, info = q.get(timeout=60)
+        got[r] = (what, info)
+    for p in procs:
+        p.join(timeout=30)
+    assert got[2][0] == "exited"
+    for r in (0, 1):
+        assert got[r][0] == "detected", got
+        ranks, new_world, step = got[r][1]
+        assert ranks == [2] and new_world == 2 and step >= 3
+
+
+def _tp_worker(rank, world, port, q):
+    import torch.distributed as dist
+
+    from unillm_b200.engine.runner import RunnerWeights
+    from unillm_b200.models import configs as C
+    from unillm_b200.models.families import LlamaModel
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        cfg = C.LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=4,
+                            num_key_value_heads=2)
+        m = LlamaModel.new(cfg, init="random", seed=3)
+        m.p = {k: v.to(torch.bfloat16).float() for k, v in m.p.items()}
+        w = RunnerWeights(m.spec, m.p, "cpu", rank, world)
+        h = torch.randn(5, 32, generator=torch.Generator().manual_seed(0)).to(torch.bfloat16).float()
+        # column-parallel gate/up, row-parallel down, one all-reduce
+        gu = w.t["layers.0.w_gate_up"].float()
+        I = gu.shape[0] // 2
+        a = torch.nn.functional.silu(h @ gu[:I].t()) * (h @ gu[I:].t())
+        y = a @ w.t["layers.0.w_down"].float().t()
+        dist.all_reduce(y)
+        full = m.p["layers.0.w_gate_up"]
+        If = full.shape[0] // 2
+        ref = (torch.nn.functional.silu(h @ full[:If].t()) * (h @ full[If:].t())) @ m.p["layers.0.w_down"].t()
+        err_mlp = (y - ref).abs().max().item()
+        # head-parallel attention projections: q/k/v rows of this rank's heads, o columns
+        D = m.spec.head_dim
+        qkv = w.t["layers.0.wqkv"].float()
+        assert qkv.shape[0] == (w.hq + 2 * w.hkv) * D and w.hq == 2 and w.hkv == 1
+        o_part = (h @ qkv[:w.hq * D].t()) @ w.t["layers.0.wo"].float().t()
+        dist.all_reduce(o_part)
+        qfull = m.p["layers.0.wqkv"][:4 * D]
+        err_o = (o_part - (h @ qfull.t()) @ m.p["layers.0.wo"].t()).abs().max().item()
+        # vocab-parallel greedy sampling: local (max, argmax) pairs merged across ranks
+        logits = h @ w.t["lm_head"].float().t()
+        v, i = logits.max(-1)
+        pairs = torch.stack([v, (i + rank * w.vocab_shard).float()], -1)
+        allp = [torch.empty_like(pairs) for _ in range(world)]
+        dist.all_gather(allp, pairs)
+        st = torch.stack(allp)                         # [world, T, 2]
+        best = st[..., 0].argmax(0)
+        merged = st[best, torch.arange(5), 1].long()
+        ref_ids = (h @ m.p["lm_head"].t()).argmax(-1)
+        q.put((rank, err_mlp, err_o, bool((merged == ref_ids).all())))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tensor_parallel_shards_over_gloo():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=30)
+    for rank, e1, e2, ok in res:
+        assert e1 < 1e-4 and e2 < 1e-4 and ok, res
+
+
+def test_engine_snapshot_restore_continues_identically():
+    from unillm_b200.engine.cpu_runner import CpuModelRunner
+    from unillm_b200.engine.llm_engine import LLMEngine
+    from unillm_b200.models import configs as C
+    from unillm_b200.models.families import LlamaModel
+    from unillm_b200.sampling import SamplingParams
+
+    cfg = C.LlamaConfig(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2)
+    m = LlamaModel.new(cfg, init="random", seed=3)
+
+    def engine():
+        return LLMEngine(CpuModelRunner(m, num_blocks=64, block_size=4, max_model_len=128), num_blocks=64, block_size=4,
+                         max_num_seqs=4, max_num_batched_tokens=16, max_model_len=128)
+
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 128, (n,), generator=g).tolist() for n in (9, 14, 3, 21, 6)]
+    params = SamplingParams(temperature=0.0, max_tokens=10)
+    ref = engine().generate(prompts, params)
+    e1 = engine()
+    ids = [e1.add_request(p, params) for p in prompts]
+    for _ in range(6):
+        e1.step()
+    snap = json.loads(json.dumps(e1.snapshot()))
+    assert any(r["output"] for r in snap["requests"]) and any(r["status"] != "finished" for r in snap["requests"])
+    e2 = engine()
+    requeued = e2.restore(snap)
+    assert requeued
+    out = e2.run_to_completion()
+    assert [out[i] for i in ids] == ref
+    with pytest.raises(Exception):
+        e2.restore(snap)

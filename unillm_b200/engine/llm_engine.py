@@ -400,3 +400,43 @@ class LLMEngine:
         ids = [self.add_request(p, params) for p in prompts]
         self.run_to_completion()
         return [self.seqs[i].output_ids for i in ids]
+
+    # ------------------------------------------------------------------------------------------
+    # snapshot / restore: the request log is the durable state, KV is recomputed
+    # ------------------------------------------------------------------------------------------
+    def snapshot(self) -> dict:
+        """JSON-serialisable state of every unfinished request (prompt, tokens generated so far, sampling settings)
+        plus the finished ones' outputs.  The KV cache and the radix tree are not saved: after ``restore`` the
+        engine prefills prompt + generated tokens again (greedy requests then continue with identical tokens)."""
+        import dataclasses
+
+        reqs = []
+        for s in self.seqs.values():
+            reqs.append({"id": s.seq_id, "prompt": list(s.prompt_ids), "output": list(s.output_ids), "priority": s.priority,
+                         "params": dataclasses.asdict(s.params), "status": s.status, "finish_reason": s.finish_reason})
+        return {"version": 1, "next_id": self._next_id, "eos_token_id": self.eos_token_id, "seed": self.seed,
+                "stats": dataclasses.asdict(self.stats), "requests": reqs}
+
+    def restore(self, snap: dict) -> List[int]:
+        """Re-creates the requests of ``snapshot()`` in a fresh engine; returns the ids that were requeued."""
+        if snap.get("version") != 1:
+            raise InvalidInput("unknown snapshot version")
+        if self.seqs:
+            raise InvalidInput("restore needs an engine without requests")
+        self.eos_token_id = snap.get("eos_token_id", self.eos_token_id)
+        requeued = []
+        for r in snap["requests"]:
+            params = SamplingParams(**r["params"])
+            s = Sequence(r["id"], list(r["prompt"]), params, r.get("priority", 0))
+            s.output_ids = list(r["output"])
+            self.seqs[s.seq_id] = s
+            if r["status"] in (FINISHED, ABORTED):
+                s.status, s.finish_reason = r["status"], r.get("finish_reason")
+                continue
+            if s.output_ids:
+                # decode again from the full token history: the last generated token is the next input
+                s.num_computed = 0
+            self.waiting.append(s)
+            requeued.append(s.seq_id)
+        self._next_id = max(snap.get("next_id", 0), max(self.seqs, default=-1) + 1)
+        return requeued
