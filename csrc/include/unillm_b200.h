@@ -198,11 +198,20 @@ typedef struct UbMoeRouteArgs {
   float weight_scale;       /* multiplies the routing weights (0 = 1) */
   int tile_tokens;          /* token tile of the grouped GEMM that will consume `tiles` */
   int max_tiles;            /* capacity of `tiles`; ceil(T*K / tile_tokens) + E always suffices */
+  /* Expert parallelism: this rank owns experts [expert_lo, expert_lo + num_local_experts).  Pairs routed elsewhere
+     get row_slot = -1 and no tile; expert_counts/offsets/tiles use local expert indices.  0 = all experts local. */
+  int expert_lo;
+  int num_local_experts;
 } UbMoeRouteArgs;
 int ub_moe_route(const UbMoeRouteArgs* args, void* stream);
 int ub_moe_gather(const void* x, const int* sorted_rows, void* out, int rows, int K, int H, void* stream);
 int ub_moe_combine(const void* y, const int* row_slot, const float* topk_w, const void* residual, void* out, int T,
                    int K, int H, void* stream);
+/* F6: combine fused with the reduce-scatter: token t's partial row is stored into the receive slot
+   peer_out[owner(t)][rank][t - owner*rows_per_rank] and every CTA bumps every peer's counter once. */
+int ub_moe_combine_num_ctas(int T, int H);
+int ub_moe_combine_rs(const void* y, const int* row_slot, const float* topk_w, int T, int K, int H, int world, int rank,
+                      int rows_per_rank, void* const* peer_out, uint32_t* const* peer_flag, void* stream);
 
 /* ---------------- K12 : GGUF-quantised weights ---------------- */
 /* qtype is the ggml type id: 2 Q4_0, 3 Q4_1, 6 Q5_0, 8 Q8_0, 12 Q4_K, 14 Q6_K. */

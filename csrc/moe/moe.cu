@@ -92,10 +92,15 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const UbMoeRouteArgs a) 
 // One CTA: counts, exclusive offsets, slot assignment and the token-tile table of the grouped GEMM.
 __global__ void __launch_bounds__(1024) moe_sort_kernel(const UbMoeRouteArgs a) {
   __shared__ int cnt[MOE_MAX_E], off[MOE_MAX_E + 1], cur[MOE_MAX_E];
-  const int E = a.E, n = a.T * a.K;
+  const int E = a.num_local_experts > 0 ? a.num_local_experts : a.E, n = a.T * a.K;
   for (int e = threadIdx.x; e < E; e += blockDim.x) { cnt[e] = 0; cur[e] = 0; }
   __syncthreads();
-  for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&cnt[a.topk_ids[i]], 1);
+  // Expert parallelism: only experts [expert_lo, expert_lo + E) live on this rank; the rest get no slot.
+  const int lo = a.expert_lo;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = a.topk_ids[i] - lo;
+    if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
+  }
   __syncthreads();
   if (threadIdx.x == 0) {
     int acc = 0, tile = 0;
@@ -118,11 +123,13 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const UbMoeRouteArgs a) 
     if (e < E) a.expert_counts[e] = cnt[e];
   }
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int e = a.topk_ids[i];
+    const int e = a.topk_ids[i] - lo;
+    if (e < 0 || e >= E) { a.row_slot[i] = -1; continue; }
     const int slot = off[e] + atomicAdd(&cur[e], 1);
     a.sorted_rows[slot] = i;
     a.row_slot[i] = slot;
   }
+  for (int i = off[E] + threadIdx.x; i < n; i += blockDim.x) a.sorted_rows[i] = -1;   // unused tail
 }
 
 // out[slot, :] = x[sorted_rows[slot] / K, :]
@@ -132,15 +139,23 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(const __nv_bfloat16* __
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < (long long)rows * vec;
        i += (long long)gridDim.x * blockDim.x) {
     const int slot = int(i / vec), c = int(i % vec);
-    const int src = sorted_rows[slot] / K;
+    const int sr = sorted_rows[slot];
+    if (sr < 0) continue;                      // slot not used on this rank
+    const int src = sr / K;
     reinterpret_cast<uint4*>(out + (long long)slot * H)[c] = __ldg(reinterpret_cast<const uint4*>(x + (long long)src * H) + c);
   }
 }
 
 // out[t, :] = residual[t, :] + sum_k w[t,k] * y[row_slot[t*K+k], :]
+struct CombinePush {
+  int world, rank, rows_per_rank;            // world == 0: plain store to `out`
+  __nv_bfloat16* peer_out[UB_MAX_RANKS];     // each: [world][rows_per_rank][H] receive slots
+  uint32_t* peer_flag[UB_MAX_RANKS];
+};
+
 __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ row_slot,
                                                           const float* __restrict__ topk_w, const __nv_bfloat16* __restrict__ residual,
-                                                          __nv_bfloat16* __restrict__ out, int T, int K, int H) {
+                                                          __nv_bfloat16* __restrict__ out, int T, int K, int H, const CombinePush push) {
   const int vec = H / 8;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < (long long)T * vec;
        i += (long long)gridDim.x * blockDim.x) {
@@ -155,13 +170,28 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* _
     for (int k = 0; k < K; ++k) {
       const float w = topk_w[(long long)t * K + k];
       const int slot = row_slot[(long long)t * K + k];
+      if (slot < 0) continue;                  // expert lives on another rank
       const uint4 v = __ldg(reinterpret_cast<const uint4*>(y + (long long)slot * H) + c);
       const uint32_t* vs = reinterpret_cast<const uint32_t*>(&v);
 #pragma unroll
       for (int j = 0; j < 4; ++j) { acc[2 * j] += w * bf16_lo(vs[j]); acc[2 * j + 1] += w * bf16_hi(vs[j]); }
     }
-    reinterpret_cast<uint4*>(out + (long long)t * H)[c] =
+    __nv_bfloat16* dst = out + (long long)t * H;
+    if (push.world > 0) {
+      // F6: the partial row goes straight into the receive slot of the rank that owns token t
+      int owner = t / push.rows_per_rank;
+      if (owner >= push.world) owner = push.world - 1;
+      dst = push.peer_out[owner] + ((long long)push.rank * push.rows_per_rank + (t - owner * push.rows_per_rank)) * H;
+    }
+    reinterpret_cast<uint4*>(dst)[c] =
         make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+  }
+  if (push.world > 0) {
+    // publish: every storing thread fences to system scope, then one thread per peer bumps that peer's counter
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < push.world)
+      asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(push.peer_flag[threadIdx.x]), "r"(1u) : "memory");
   }
 }
 
@@ -193,16 +223,39 @@ extern "C" int ub_moe_gather(const void* x, const int* sorted_rows, void* out, i
   return e == cudaSuccess ? 0 : -(int)e;
 }
 
+static int combine_blocks(int T, int H) {
+  const long long work = (long long)T * (H / 8);
+  int blocks = int((work + 255) / 256);
+  return blocks > 148 * 4 ? 148 * 4 : blocks;
+}
+
+extern "C" int ub_moe_combine_num_ctas(int T, int H) { return T <= 0 ? 0 : combine_blocks(T, H); }
+
 extern "C" int ub_moe_combine(const void* y, const int* row_slot, const float* topk_w, const void* residual, void* out, int T,
                               int K, int H, void* stream_v) {
   if (T <= 0) return 0;
   if (H % 8 != 0) return -2;
-  const long long work = (long long)T * (H / 8);
-  int blocks = int((work + 255) / 256);
-  if (blocks > 148 * 8) blocks = 148 * 8;
-  ub::moe_combine_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
+  ub::CombinePush push = {};
+  ub::moe_combine_kernel<<<combine_blocks(T, H), 256, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
       reinterpret_cast<const __nv_bfloat16*>(y), row_slot, topk_w, reinterpret_cast<const __nv_bfloat16*>(residual),
-      reinterpret_cast<__nv_bfloat16*>(out), T, K, H);
+      reinterpret_cast<__nv_bfloat16*>(out), T, K, H, push);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+// F6: combine + reduce-scatter.  Every CTA (ub_moe_combine_num_ctas of them) signals every peer once.
+extern "C" int ub_moe_combine_rs(const void* y, const int* row_slot, const float* topk_w, int T, int K, int H, int world, int rank,
+                                 int rows_per_rank, void* const* peer_out, uint32_t* const* peer_flag, void* stream_v) {
+  if (T <= 0) return 0;
+  if (H % 8 != 0 || world <= 0 || world > UB_MAX_RANKS || rows_per_rank <= 0) return -2;
+  ub::CombinePush push = {};
+  push.world = world; push.rank = rank; push.rows_per_rank = rows_per_rank;
+  for (int i = 0; i < world; ++i) {
+    push.peer_out[i] = reinterpret_cast<__nv_bfloat16*>(peer_out[i]);
+    push.peer_flag[i] = peer_flag[i];
+  }
+  ub::moe_combine_kernel<<<combine_blocks(T, H), 256, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(y), row_slot, topk_w, nullptr, nullptr, T, K, H, push);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }

@@ -122,3 +122,53 @@ def test_moe_model_runner_vs_cpu(kind):
     assert outs["eager"] == outs["graph"]
     agree = sum(a == b for ra, rb in zip(outs["cpu"], outs["eager"]) for a, b in zip(ra, rb))
     assert agree / 40 > 0.6, agree
+
+
+def test_expert_parallel_partials_and_fused_combine():
+    """Expert parallelism emulated on one GPU: each 'rank' routes with its expert range; partial rows summed over the
+    ranks equal the single-rank result, both through plain combine and through the combine that pushes into the
+    owners' receive slots (all slots live on this GPU here; ranks run one after another on one stream)."""
+    from unillm_b200.ops import cuda_ops as ops
+
+    T, E, K, H, I, W = 96, 8, 2, 256, 128, 4
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16).cuda()
+    rw = (torch.randn(E, H, generator=g) * 0.2).to(torch.bfloat16).cuda()
+    gu = (torch.randn(E, 2 * I, H, generator=g) * H ** -0.5).to(torch.bfloat16).cuda()
+    dn = (torch.randn(E, H, I, generator=g) * I ** -0.5).to(torch.bfloat16).cuda()
+
+    def run(lo, n, rs=None):
+        r = ops.moe_route(x, rw, K, round_logits_bf16=False, expert_lo=lo, num_local_experts=n)
+        xs = ops.moe_gather(x, r)
+        a = ops.grouped_gemm(xs, gu[lo:lo + (n or E)].contiguous(), r, dual_rows=I, act="silu")
+        y = ops.grouped_gemm(a, dn[lo:lo + (n or E)].contiguous(), r)
+        if rs is None:
+            return ops.moe_combine(y, r), r
+        ops.moe_combine_rs(y, r, rs)
+        return None, r
+
+    full, r_full = run(0, 0)
+    parts = []
+    for rank in range(W):
+        out, r = run(rank * (E // W), E // W)
+        parts.append(out.float())
+        slots = r.row_slot.cpu()
+        ids = r.topk_ids.cpu().flatten()
+        local = (ids >= rank * (E // W)) & (ids < (rank + 1) * (E // W))
+        assert ((slots >= 0) == local).all()
+    total = torch.stack(parts).sum(0)
+    assert (total - full.float()).abs().max().item() < 0.03 * max(1.0, full.float().abs().max().item())
+    # fused combine + reduce-scatter: rows_per_rank R, owner o receives [W][R][H]
+    R = T // W
+    recv = [torch.zeros(W, R, H, dtype=torch.bfloat16, device="cuda") for _ in range(W)]
+    flags = torch.zeros(W, dtype=torch.int32, device="cuda")
+    n_ctas = ops.moe_combine_num_ctas(T, H)
+    for rank in range(W):
+        rs = {"world": W, "rank": rank, "rows_per_rank": R, "peer_out": [t.data_ptr() for t in recv],
+              "peer_flag": [flags[o:o + 1].data_ptr() for o in range(W)]}
+        run(rank * (E // W), E // W, rs)
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+    assert flags.cpu().tolist() == [W * n_ctas] * W
+    got = torch.cat([recv[o].float().sum(0) for o in range(W)], 0)
+    assert (got - full.float()).abs().max().item() < 0.05 * max(1.0, full.float().abs().max().item())

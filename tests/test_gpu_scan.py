@@ -102,3 +102,32 @@ def test_state_models_bf16_gpu_vs_fp32_cpu(name):
     cuda_ops.check_device_errors()
     err = (got.float().cpu() - ref).abs().max().item()
     assert err < 0.08 * max(1.0, ref.abs().max().item()), err
+
+
+def test_conv1d_as_gemm_and_whisper_bf16():
+    from unillm_b200.model_core import ModelInputs
+    from unillm_b200.models import ALL_MODELS, configs as C
+    from unillm_b200.models.simple import conv1d
+    from unillm_b200.ops import cuda_ops
+
+    g = torch.Generator().manual_seed(0)
+    for (B, Cc, L, O, k, st, pad) in ((2, 16, 50, 24, 3, 1, 1), (1, 8, 64, 32, 3, 2, 1), (2, 8, 40, 16, 7, 1, 0)):
+        x, w, b = _bf(torch.randn(B, Cc, L, generator=g)), _bf(torch.randn(O, Cc, k, generator=g) * 0.2), _bf(torch.randn(O, generator=g))
+        ref = torch.nn.functional.conv1d(x.float(), w.float(), b.float(), stride=st, padding=pad)
+        got = conv1d(x.cuda(), w.cuda(), b.cuda(), stride=st, padding=pad)
+        assert got.shape == ref.shape
+        _close(got, ref, 0.03)
+    cfg = C.WhisperConfig(vocab_size=512, d_model=128, encoder_layers=2, decoder_layers=2, encoder_attention_heads=4,
+                          decoder_attention_heads=4, encoder_ffn_dim=256, decoder_ffn_dim=256, max_source_positions=64,
+                          max_target_positions=32, num_mel_bins=16, hidden_size=128, decoder_start_token_id=1, eos_token_id=2)
+    cls = ALL_MODELS["whisper"]
+    m = cls.new(cfg, init="random", seed=3)
+    m.p = {k_: v.to(torch.bfloat16).float() for k_, v in m.p.items()}
+    mel = _bf(torch.randn(1, 16, 100, generator=g)).float()
+    dec = torch.tensor([[1, 7, 9, 30]])
+    ref = m.forward(ModelInputs.audio(mel, decoder_input_ids=dec)).logits
+    md = cls.from_weights(cfg, m.export_hf(), dtype=torch.bfloat16, device="cuda")
+    got = md.forward(ModelInputs.audio(mel.cuda().to(torch.bfloat16), decoder_input_ids=dec.cuda())).logits
+    torch.cuda.synchronize()
+    cuda_ops.check_device_errors()
+    _close(got, ref, 0.08)

@@ -5,8 +5,13 @@ gate/up GEMM with the activation in its epilogue, grouped down GEMM, weighted co
 reference walks tokens and experts on the host (``crates/runtime/src/model_core.rs:796-905``); here nothing about
 the routing ever reaches the host, so the block sits inside a CUDA graph like any dense layer.
 
-Tensor parallelism shards every expert's FFN width across the ranks (each rank holds all experts), so the combine
-output is a partial sum that is all-reduced once, together with the shared experts / parallel dense MLP.
+Two multi-GPU layouts.  Tensor parallelism shards every expert's FFN width across the ranks (each rank holds all
+experts).  Expert parallelism (``RunnerWeights(expert_parallel=True)``) keeps whole experts on their rank: the
+hidden rows are already replicated by the attention block's reduction (the dispatch), every rank routes all tokens
+identically, runs the grouped GEMMs for the pairs that picked one of its experts, and combines them into a partial
+row per token.  Either way the partial rows are summed across ranks once, together with the shared experts /
+parallel dense MLP: by an all-reduce, or (``combine_rs``) by the combine kernel storing straight into the owners'
+receive slots over NVLink, which the next norm kernel sums.
 """
 from __future__ import annotations
 
@@ -15,14 +20,18 @@ import torch
 from ..ops import cuda_ops as K
 
 
-def moe_partial(runner, i: int, h: torch.Tensor, residual=None) -> torch.Tensor:
-    """MoE output for hidden rows ``h`` ([T, H]).  With ``residual`` (single rank only) it is added in the combine."""
+def moe_partial(runner, i: int, h: torch.Tensor, residual=None, combine_rs=None) -> torch.Tensor:
+    """MoE output for hidden rows ``h`` ([T, H]).  With ``residual`` (single rank only) it is added in the combine.
+    ``combine_rs`` (peer pointers as for ``gemm_tn(rs=...)``) makes the combine kernel push its partial rows to the
+    ranks that own them instead of returning them."""
     s, t = runner.spec, runner.w.t
     m = s.moe
     L = f"layers.{i}."
     T = h.shape[0]
     with runner._prof("moe_route"):
-        r = K.moe_route(h, t[L + "router"], m.top_k, norm_topk=m.normalize_topk, round_logits_bf16=False)
+        r = K.moe_route(h, t[L + "router"], m.top_k, norm_topk=m.normalize_topk, round_logits_bf16=False,
+                        expert_lo=runner.w.expert_lo if runner.w.ep else 0,
+                        num_local_experts=runner.w.experts_local if runner.w.ep else 0)
         xs = K.moe_gather(h, r)
     runner.launches += 3
     gu, dn = t[L + "experts_gate_up"], t[L + "experts_down"]
@@ -43,7 +52,13 @@ def moe_partial(runner, i: int, h: torch.Tensor, residual=None) -> torch.Tensor:
         base = d if base is None else K.add(base, d)
         runner.launches += 1
     with runner._prof("moe_combine"):
-        out = K.moe_combine(y, r, residual=base)
+        if combine_rs is not None:
+            if base is not None:
+                raise ValueError("combine_rs pushes partial sums; shared experts / residual are added by the caller")
+            K.moe_combine_rs(y, r, combine_rs)
+            out = None
+        else:
+            out = K.moe_combine(y, r, residual=base)
     runner.launches += 3
     return out
 

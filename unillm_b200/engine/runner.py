@@ -73,9 +73,11 @@ def shard_cols(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
 class RunnerWeights:
     """Device weights of one rank in kernel layout (bf16, fused QKV / gate-up, TP-sharded)."""
 
-    def __init__(self, spec: DecoderSpec, params: Dict[str, torch.Tensor], device, rank: int = 0, world: int = 1):
+    def __init__(self, spec: DecoderSpec, params: Dict[str, torch.Tensor], device, rank: int = 0, world: int = 1,
+                 expert_parallel: bool = False):
         self.spec, self.rank, self.world = spec, rank, world
         s = spec
+        self._set_ep(expert_parallel)
         if s.num_heads % world != 0:
             raise InvalidInput(f"{s.num_heads} heads not divisible by tensor parallel size {world}")
         if s.num_kv_heads % world != 0:
@@ -133,30 +135,45 @@ class RunnerWeights:
                 self.t[L + "router"] = dev(p[L + "router"])
                 gu = p[L + "experts_gate_up"]
                 E = gu.shape[0]
-                if s.moe.gated:
+                if self.ep:
+                    # expert parallel: whole experts [expert_lo, expert_lo + experts_local) live here
+                    lo, hi = self.expert_lo, self.expert_lo + self.experts_local
+                    self.t[L + "experts_gate_up"] = dev(gu[lo:hi])
+                    self.t[L + "experts_down"] = dev(p[L + "experts_down"][lo:hi])
+                elif s.moe.gated:
                     g, u = gu.chunk(2, 1)
                     n = g.shape[1] // world
                     gu = torch.cat([g[:, rank * n:(rank + 1) * n], u[:, rank * n:(rank + 1) * n]], 1)
                 else:
                     n = gu.shape[1] // world
                     gu = gu[:, rank * n:(rank + 1) * n]
-                self.t[L + "experts_gate_up"] = dev(gu)
-                dn = p[L + "experts_down"]
-                n = dn.shape[2] // world
-                self.t[L + "experts_down"] = dev(dn[:, :, rank * n:(rank + 1) * n])
+                if not self.ep:
+                    self.t[L + "experts_gate_up"] = dev(gu)
+                    dn = p[L + "experts_down"]
+                    n = dn.shape[2] // world
+                    self.t[L + "experts_down"] = dev(dn[:, :, rank * n:(rank + 1) * n])
                 if L + "shared_gate_up" in p:
                     g, u = p[L + "shared_gate_up"].chunk(2, 0)
                     self.t[L + "shared_gate_up"] = dev(torch.cat([shard_rows(g, rank, world), shard_rows(u, rank, world)], 0))
                     self.t[L + "shared_down"] = dev(shard_cols(p[L + "shared_down"], rank, world))
 
+    def _set_ep(self, expert_parallel: bool) -> None:
+        """Expert parallelism applies when asked for, with more than one rank and an expert count the ranks divide."""
+        m = self.spec.moe
+        self.ep = bool(expert_parallel and self.world > 1 and m is not None and m.num_experts % self.world == 0)
+        self.experts_local = m.num_experts // self.world if self.ep else (m.num_experts if m is not None else 0)
+        self.expert_lo = self.rank * self.experts_local if self.ep else 0
+
     @staticmethod
-    def random(spec: DecoderSpec, device, rank: int = 0, world: int = 1, seed: int = 0) -> "RunnerWeights":
+    def random(spec: DecoderSpec, device, rank: int = 0, world: int = 1, seed: int = 0,
+               expert_parallel: bool = False) -> "RunnerWeights":
         """Random-init weights generated directly on the device, shard by shard (no host copy): the
         benchmark path for 8B-70B architectures.  Every rank draws the same full-size tensor for a given
         name from a per-tensor seed and keeps its shard, so TP=1 and TP=N hold the same model."""
         self = RunnerWeights.__new__(RunnerWeights)
         self.spec, self.rank, self.world = spec, rank, world
         s = spec
+        self._set_ep(expert_parallel)
         self.hq, self.hkv = s.num_heads // world, s.num_kv_heads // world
         self.vocab_shard = s.vocab_size // world
         self.t = {}
@@ -202,14 +219,21 @@ class RunnerWeights:
             self.t[L + "wo"] = rnd(H, s.q_size, 0, H, rank * qs, qs)
             if s.layer_is_moe(i):
                 m = s.moe
-                Ie = m.intermediate_size // world
                 self.t[L + "router"] = rnd(m.num_experts, H)
-                gu = torch.empty(m.num_experts, 2 * Ie, H, dtype=torch.bfloat16, device=device)
-                dn = torch.empty(m.num_experts, H, Ie, dtype=torch.bfloat16, device=device)
+                # tensor parallel inside every expert, or (expert parallel) whole experts of this rank
+                Ie = m.intermediate_size if self.ep else m.intermediate_size // world
+                c0 = 0 if self.ep else rank * Ie
+                gu = torch.empty(self.experts_local, 2 * Ie, H, dtype=torch.bfloat16, device=device)
+                dn = torch.empty(self.experts_local, H, Ie, dtype=torch.bfloat16, device=device)
                 for e in range(m.num_experts):
-                    gu[e, :Ie] = rnd(m.intermediate_size, H, rank * Ie, Ie)
-                    gu[e, Ie:] = rnd(m.intermediate_size, H, rank * Ie, Ie)
-                    dn[e] = rnd(H, m.intermediate_size, 0, H, rank * Ie, Ie)
+                    mine = self.expert_lo <= e < self.expert_lo + self.experts_local
+                    if not mine:
+                        counter[0] += 3           # keep the per-tensor seeds aligned across ranks
+                        continue
+                    j = e - self.expert_lo
+                    gu[j, :Ie] = rnd(m.intermediate_size, H, c0, Ie)
+                    gu[j, Ie:] = rnd(m.intermediate_size, H, c0, Ie)
+                    dn[j] = rnd(H, m.intermediate_size, 0, H, c0, Ie)
                 self.t[L + "experts_gate_up"], self.t[L + "experts_down"] = gu, dn
             else:
                 Is = I // world

@@ -175,6 +175,21 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, offset: in
 
 def conv1d(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None, stride: int = 1, padding: int = 0,
            groups: int = 1, dilation: int = 1) -> torch.Tensor:
-    """[B, C, L] convolution in fp32 (audio stems, positional convs)."""
+    """[B, C, L] convolution.  bf16 CUDA inputs with ``groups == 1`` run as a GEMM on the tensor cores: the input
+    windows are laid out as rows ``[B * L_out, C * k]`` and multiplied with the filter matrix ``[O, C * k]`` by the
+    tcgen05 GEMM (bias in its epilogue); everything else is an fp32 convolution (audio stems on CPU, grouped
+    positional convolutions)."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and groups == 1 and (w.shape[1] * w.shape[2]) % 8 == 0:
+        from ..ops import cuda_ops as K
+
+        B, Cc, L = x.shape
+        O, _, k = w.shape
+        xp = F.pad(x, (padding, padding)) if padding else x
+        span = dilation * (k - 1) + 1
+        Lo = (xp.shape[-1] - span) // stride + 1
+        idx = (torch.arange(Lo, device=x.device) * stride)[:, None] + (torch.arange(k, device=x.device) * dilation)[None]
+        cols = xp[:, :, idx].permute(0, 2, 1, 3).reshape(B * Lo, Cc * k).contiguous()      # [B*Lo, C*k]
+        y = K.linear(cols, w.reshape(O, Cc * k).to(torch.bfloat16).contiguous(), None if b is None else b.to(torch.bfloat16))
+        return y.view(B, Lo, O).transpose(1, 2).contiguous()
     return F.conv1d(_f(x), _f(w), None if b is None else _f(b), stride=stride, padding=padding, groups=groups,
                     dilation=dilation).to(x.dtype)

@@ -93,6 +93,7 @@ class UbMoeRouteArgs(C.Structure):
         ("expert_offsets", vp), ("sorted_rows", vp), ("row_slot", vp), ("tiles", vp), ("err", vp),
         ("logits_f32", i32), ("T", i32), ("E", i32), ("K", i32), ("H", i32), ("norm_topk", i32),
         ("round_logits_bf16", i32), ("weight_scale", f32), ("tile_tokens", i32), ("max_tiles", i32),
+        ("expert_lo", i32), ("num_local_experts", i32),
     ]
 
 

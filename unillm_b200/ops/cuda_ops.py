@@ -464,8 +464,12 @@ def moe_tile_tokens(T: int, K: int, E: int) -> int:
 
 def moe_route(x: Optional[torch.Tensor], router_w: Optional[torch.Tensor], top_k: int, *, norm_topk: bool = True,
               logits: Optional[torch.Tensor] = None, weight_scale: float = 1.0, tile_tokens: int = 0,
-              round_logits_bf16: bool = True, routing: Optional[MoeRouting] = None) -> MoeRouting:
-    """Router GEMV + top-k + softmax weights + expert sort + grouped-GEMM tile table, two launches."""
+              round_logits_bf16: bool = True, routing: Optional[MoeRouting] = None, expert_lo: int = 0,
+              num_local_experts: int = 0) -> MoeRouting:
+    """Router GEMV + top-k + softmax weights + expert sort + grouped-GEMM tile table, two launches.
+
+    ``expert_lo`` / ``num_local_experts`` restrict the sort to the experts of this rank (expert parallelism): pairs
+    routed to other ranks get ``row_slot = -1`` and take no part in the grouped GEMMs."""
     if router_w is not None:
         _bf16c(x, "x"), _bf16c(router_w, "router_w")
         T, H = x.shape
@@ -491,6 +495,7 @@ def moe_route(x: Optional[torch.Tensor], router_w: Optional[torch.Tensor], top_k
     a.round_logits_bf16 = 1 if round_logits_bf16 else 0
     a.weight_scale = weight_scale
     a.tile_tokens, a.max_tiles = r.tile_tokens, r.max_tiles
+    a.expert_lo, a.num_local_experts = expert_lo, num_local_experts
     N.check(N.cuda_lib().ub_moe_route(C.byref(a), torch.cuda.current_stream(dev).cuda_stream), "ub_moe_route")
     return r
 
@@ -522,6 +527,29 @@ def moe_combine(y: torch.Tensor, r: MoeRouting, residual: Optional[torch.Tensor]
     N.check(lib.ub_moe_combine(y.data_ptr(), r.row_slot.data_ptr(), r.topk_w.data_ptr(), _p(residual), out.data_ptr(),
                                r.T, r.K, H, _stream(y)), "ub_moe_combine")
     return out
+
+
+def moe_combine_num_ctas(T: int, H: int) -> int:
+    lib = N.cuda_lib()
+    lib.ub_moe_combine_num_ctas.restype = C.c_int
+    lib.ub_moe_combine_num_ctas.argtypes = [N.i32, N.i32]
+    return lib.ub_moe_combine_num_ctas(T, H)
+
+
+def moe_combine_rs(y: torch.Tensor, r: MoeRouting, rs: dict) -> None:
+    """Combine fused with the reduce-scatter: partial rows go into the owners' receive slots (``rs`` as for
+    ``gemm_tn``: world, rank, rows_per_rank, peer_out, peer_flag); each CTA signals each peer once."""
+    _bf16c(y, "y")
+    H = y.shape[1]
+    W = rs["world"]
+    outs = (C.c_void_p * W)(*[int(p) for p in rs["peer_out"][:W]])
+    flags = (C.c_void_p * W)(*[int(p) for p in rs["peer_flag"][:W]])
+    lib = N.cuda_lib()
+    lib.ub_moe_combine_rs.restype = C.c_int
+    lib.ub_moe_combine_rs.argtypes = [N.vp, N.vp, N.vp, N.i32, N.i32, N.i32, N.i32, N.i32, N.i32, N.vp, N.vp, N.vp]
+    N.check(lib.ub_moe_combine_rs(y.data_ptr(), r.row_slot.data_ptr(), r.topk_w.data_ptr(), r.T, r.K, H, W, rs["rank"],
+                                  rs["rows_per_rank"], C.cast(outs, C.c_void_p), C.cast(flags, C.c_void_p), _stream(y)),
+            "ub_moe_combine_rs")
 
 
 def grouped_gemm(x_sorted: torch.Tensor, w: torch.Tensor, r: MoeRouting, *, dual_rows: int = 0, act: Optional[str] = None,
