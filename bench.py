@@ -41,6 +41,12 @@ MODELS = {
     "llama3-70b": dict(vocab_size=128256, hidden_size=8192, intermediate_size=28672, num_hidden_layers=80,
                        num_attention_heads=64, num_key_value_heads=8, rope_theta=500000.0, rms_norm_eps=1e-5,
                        max_position_embeddings=8192),
+    "mixtral-8x7b": dict(vocab_size=32000, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,
+                         num_attention_heads=32, num_key_value_heads=8, rope_theta=1000000.0, rms_norm_eps=1e-5,
+                         max_position_embeddings=32768, num_experts=8, num_experts_per_tok=2, sliding_window=32768),
+    "tiny-moe": dict(vocab_size=4096, hidden_size=1024, intermediate_size=1024, num_hidden_layers=4,
+                     num_attention_heads=8, num_key_value_heads=8, rope_theta=10000.0, rms_norm_eps=1e-5,
+                     max_position_embeddings=4096, num_experts=8, num_experts_per_tok=2, sliding_window=4096),
     "tiny": dict(vocab_size=4096, hidden_size=1024, intermediate_size=2048, num_hidden_layers=4,
                  num_attention_heads=8, num_key_value_heads=8, rope_theta=10000.0, rms_norm_eps=1e-5,
                  max_position_embeddings=4096),
@@ -146,19 +152,25 @@ def main(argv=None) -> int:
     from unillm_b200.engine.llm_engine import LLMEngine
     from unillm_b200.engine.runner import GpuModelRunner, RunnerWeights, TpContext
     from unillm_b200.models import configs as C
-    from unillm_b200.models.families import LlamaModel
+    from unillm_b200.models.families import LlamaModel, MixtralModel
     from unillm_b200.ops import cuda_ops
     from unillm_b200.sampling import SamplingParams
 
-    cfg = C.LlamaConfig(**MODELS[args.model])
-    spec = LlamaModel.spec_from_config(cfg)
+    moe = "num_experts" in MODELS[args.model]
+    if moe:
+        cfg = C.MixtralConfig(**MODELS[args.model])
+        spec = MixtralModel.spec_from_config(cfg)
+    else:
+        cfg = C.LlamaConfig(**MODELS[args.model])
+        spec = LlamaModel.spec_from_config(cfg)
     B, PL, SL, OL = args.batch, args.prefix_len, args.suffix_len, args.output_len
     bs = 16
     max_len = PL + SL + OL + bs
     blocks_needed = PL // bs + (B + 8) * ((SL + OL) // bs + 2)
     num_blocks = max(2 * blocks_needed, 1024)
     tp = TpContext(rank, world, group, fused=not args.baseline_collectives)
-    weights = RunnerWeights.random(spec, dev, rank, world, seed=1234)
+    # MoE models: attention tensor parallel + expert parallel (whole experts per rank) when the ranks divide the experts
+    weights = RunnerWeights.random(spec, dev, rank, world, seed=1234, expert_parallel=moe)
     if tp.fused:
         from unillm_b200.dist.fused import FusedComm
 
@@ -248,12 +260,13 @@ def main(argv=None) -> int:
         value = tokens / (dev_ms / 1e3)
         e2e = tokens / wall
         out = {
-            "metric": "output tok/s, Llama-3-8B architecture, engine steady state (device-timed, max over ranks)",
+            "metric": f"output tok/s, {args.model} architecture, engine steady state (device-timed, max over ranks)",
             "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": args.warmup,
             "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic (random token ids, random-init weights)",
             "config": {"model": args.model, "global_batch": B, "seq_len": PL + SL + OL,
-                       "parallelism": f"tp{world}" + ("" if tp.fused or world == 1 else "-nccl-baseline"),
+                       "parallelism": f"tp{world}" + (f"+ep{world}" if weights.ep else "") +
+                       ("" if tp.fused or world == 1 else "-nccl-baseline"),
                        "workload": f"{PL}-token shared prefix + {SL} unique + {OL} greedy outputs, continuous batching",
                        "kv_block": bs, "prefix_cache": True, "cuda_graphs": not args.no_graphs,
                        "l2": "inputs larger than L2: each step streams the model weights (>= 2 GB per GPU) from HBM",

@@ -96,15 +96,21 @@ sys.path.insert(0, os.environ["REPO"])
 from unillm_b200.engine.llm_engine import LLMEngine
 from unillm_b200.engine.runner import GpuModelRunner, RunnerWeights, TpContext
 from unillm_b200.models import configs as C
-from unillm_b200.models.families import LlamaModel
+from unillm_b200.models.families import LlamaModel, MixtralModel
 from unillm_b200.ops import cuda_ops
 from unillm_b200.sampling import SamplingParams
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 torch.cuda.set_device(rank)
 dist.init_process_group("nccl", device_id=torch.device(f"cuda:{rank}"))
-cfg = C.LlamaConfig(vocab_size=1024, hidden_size=512, intermediate_size=1024, num_hidden_layers=3,
-                    num_attention_heads=8, num_key_value_heads=4, rms_norm_eps=1e-5)
-spec = LlamaModel.spec_from_config(cfg)
+moe = os.environ.get("MODEL", "llama") == "mixtral"
+if moe:
+    cfg = C.MixtralConfig(vocab_size=1024, hidden_size=512, intermediate_size=512, num_hidden_layers=3,
+                          num_attention_heads=8, num_key_value_heads=4, num_experts=4, sliding_window=4096)
+    spec = MixtralModel.spec_from_config(cfg)
+else:
+    cfg = C.LlamaConfig(vocab_size=1024, hidden_size=512, intermediate_size=1024, num_hidden_layers=3,
+                        num_attention_heads=8, num_key_value_heads=4, rms_norm_eps=1e-5)
+    spec = LlamaModel.spec_from_config(cfg)
 g = torch.Generator().manual_seed(0)
 shared = torch.randint(0, 1024, (48,), generator=g).tolist()
 prompts = [shared + torch.randint(0, 1024, (n,), generator=g).tolist() for n in (16, 48, 32, 64, 16, 80, 8, 24)]
@@ -114,7 +120,8 @@ comm = FusedComm.create(spec, rank, world, dist.group.WORLD, max_tokens=512, dev
 for mode in ("tp1", "nccl", "fused", "fused_graph"):
     tpw = 1 if mode == "tp1" else world
     tp = TpContext(rank if tpw > 1 else 0, tpw, dist.group.WORLD if tpw > 1 else None, fused=mode.startswith("fused"))
-    w = RunnerWeights.random(spec, f"cuda:{rank}", tp.rank, tp.world, seed=7)
+    w = RunnerWeights.random(spec, f"cuda:{rank}", tp.rank, tp.world, seed=7, expert_parallel=moe)
+    assert w.ep == (moe and tp.world > 1)
     if tp.fused:
         tp.comm = comm
     runner = GpuModelRunner(spec, w, num_blocks=128, max_num_seqs=8, max_num_batched_tokens=256, max_model_len=256,
@@ -131,14 +138,16 @@ dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_tensor_parallel_engine_fused_matches_baseline(tmp_path):
+@pytest.mark.parametrize("model", ["llama", "mixtral"])
+def test_tensor_parallel_engine_fused_matches_baseline(tmp_path, model):
+    """llama: tensor parallel 2.  mixtral: attention tensor parallel 2 + expert parallel 2 (two experts per rank)."""
     import json
 
     script = tmp_path / "child.py"
     script.write_text(_CHILD)
-    env = dict(os.environ, REPO=os.path.dirname(os.path.dirname(os.path.abspath(__file__))), NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, REPO=os.path.dirname(os.path.dirname(os.path.abspath(__file__))), NCCL_NVLS_ENABLE="0", MODEL=model)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29731", str(script)]
+           "127.0.0.1", "--master-port", "29731" if model == "llama" else "29741", str(script)]
     p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
     line = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")][-1]

@@ -635,8 +635,9 @@ class GpuModelRunner:
     def _fused_ok(self, T: int) -> bool:
         s, tp = self.spec, self.tp
         return (tp.fused and tp.comm is not None and T % tp.world == 0 and T // tp.world <= tp.comm.max_rows
-                and not s.parallel_residual and s.moe is None and s.residual_scale == 1.0 and s.pos != "learned"
-                and not s.embed_norm and s.final_norm)
+                and not s.parallel_residual and s.residual_scale == 1.0 and s.pos != "learned"
+                and not s.embed_norm and s.final_norm
+                and (s.moe is None or (s.moe.num_shared_experts == 0 and not s.moe.dense_parallel)))
 
     def _forward_tokens_fused(self, lay, shared_prefix_len: int) -> torch.Tensor:
         """Same math as ``_forward_tokens`` with the residual stream sharded by token rows between the two
@@ -657,8 +658,13 @@ class GpuModelRunner:
         h_full = self._norm(x_full, "layers.0.ln1")         # layer 0 normalises all rows locally
         kind = "rms" if s.norm == "rms" else "layer"
         n_o = K.gemm_num_ctas(T, H, self.w.hq * s.head_dim) * W
-        I_loc = (t["layers.0.w_gate_up"].shape[0] // 2) if s.mlp == "gated" else t["layers.0.w_up"].shape[0]
-        n_d = K.gemm_num_ctas(T, H, I_loc) * W
+        dense = [i for i in range(s.num_layers) if not s.layer_is_moe(i)]
+        I_loc = n_dense = 0
+        if dense:
+            L0 = f"layers.{dense[0]}."
+            I_loc = (t[L0 + "w_gate_up"].shape[0] // 2) if s.mlp == "gated" else t[L0 + "w_up"].shape[0]
+            n_dense = K.gemm_num_ctas(T, H, I_loc) * W
+        n_moe = K.moe_combine_num_ctas(T, H) * W
         rs0_out = c.rs_local_tensor(0, R)
         rs1_out = c.rs_local_tensor(1, R)
         ag_args = None
@@ -684,12 +690,24 @@ class GpuModelRunner:
                                rs=c.norm_rs(0, n_o), ag=c.norm_ag(1), reset=c.reset_after_ag(1))
             self.launches += 1
             h2 = c.ag_local_tensor(1, T)
-            if s.mlp == "gated":
-                act = self._gemm(h2, t[L + "w_gate_up"], dual_rows=I_loc, act=s.act, ag=c.gemm_ag(1, R), tag="gemm_ag")
+            if s.layer_is_moe(i):
+                # F5: the all-gather of the normalised rows is the dispatch (every rank sees every token and keeps
+                # the pairs of its own experts); F6: the combine kernel stores partial rows into their owners' slots
+                from ..dist.fused import AG1
+                from .moe_runner import moe_partial
+
+                K.wait_flags(c.local_flag_ptr(AG1), W, R, self.device)
+                self.launches += 1
+                moe_partial(self, i, h2, None, combine_rs=c.gemm_rs(1, R))
+                n_d = n_moe
             else:
-                act = self._gemm(h2, t[L + "w_up"], bias=t.get(L + "b_up"), act=s.act, ag=c.gemm_ag(1, R), tag="gemm_ag")
-            self._gemm(act, t[L + "w_down"], bias=t.get(L + "b_down"), out=rs1_out.view(W * R, H)[:T],
-                       rs=c.gemm_rs(1, R), tag="gemm_rs")
+                if s.mlp == "gated":
+                    act = self._gemm(h2, t[L + "w_gate_up"], dual_rows=I_loc, act=s.act, ag=c.gemm_ag(1, R), tag="gemm_ag")
+                else:
+                    act = self._gemm(h2, t[L + "w_up"], bias=t.get(L + "b_up"), act=s.act, ag=c.gemm_ag(1, R), tag="gemm_ag")
+                self._gemm(act, t[L + "w_down"], bias=t.get(L + "b_down"), out=rs1_out.view(W * R, H)[:T],
+                           rs=c.gemm_rs(1, R), tag="gemm_rs")
+                n_d = n_dense
             last = i == s.num_layers - 1
             nname = "final_norm" if last else f"layers.{i + 1}.ln1"
             with self._prof("norm_rs_ag"):
