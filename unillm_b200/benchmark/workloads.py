@@ -201,15 +201,16 @@ def config5(scale: float, env) -> List[Dict]:
     ctx, steps = (4096, 256) if not small else (256, 16)
     batches = [b for b in (1, 8, 32, 128, 256) if b <= max(1, int(256 * scale)) or small and b <= 8] or [1]
     bmax = max(batches)
-    blocks = bmax * ((ctx + steps) // 16 + 2) + 16
-    eng, runner, cfg, w = build_engine("llama3-70b", world, rank, group, device, max_seqs=bmax, max_len=ctx + steps + 16,
+    max_len = ctx + steps + 16
+    per = (max_len + 15) // 16                       # block-table width of the runner
+    blocks = bmax * per + 16
+    eng, runner, cfg, w = build_engine("llama3-70b", world, rank, group, device, max_seqs=bmax, max_len=max_len,
                                        blocks=blocks, small=small)
     for kc in runner.k_cache:
         kc.normal_(0, 0.5)
     for vc in runner.v_cache:
         vc.normal_(0, 0.5)
     out = []
-    per = (ctx + steps) // 16 + 2
     for B in batches:
         tables = [list(range(1 + i * per, 1 + (i + 1) * per)) for i in range(B)]
         toks = [1] * B
