@@ -18,6 +18,7 @@
 #include "../common/ptx.cuh"
 #include "../include/unillm_b200.h"
 #include <math_constants.h>
+#include <stdlib.h>
 
 namespace ub {
 
@@ -282,9 +283,30 @@ static int launch_prefill(const UbAttnArgs& a, cudaStream_t st) {
 
 }  // namespace ub
 
+extern "C" int ub_attn_prefill_tc_supported(const UbAttnArgs* a);
+extern "C" int ub_attn_prefill_tc(const UbAttnArgs* a, void* stream);
+
+// UB_ATTN_TC=0 keeps every problem on the warp-MMA kernel (A/B comparisons).
+static bool tc_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("UB_ATTN_TC");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+static int g_last_path = 0;   // 1: tcgen05 kernel, 2: warp-MMA kernel (what the last call on this host thread used)
+extern "C" int ub_attn_prefill_last_path() { return g_last_path; }
+
 extern "C" int ub_attn_prefill(const UbAttnArgs* a, void* stream_v) {
   using namespace ub;
   if (a->num_seqs <= 0 || a->max_q_len <= 0) return 0;
+  if (tc_enabled() && ub_attn_prefill_tc_supported(a)) {
+    g_last_path = 1;
+    return ub_attn_prefill_tc(a, stream_v);
+  }
+  g_last_path = 2;
   if (a->Hq % a->Hkv != 0) return -2;
   if (a->q_stride % 8 != 0) return -3;
   cudaStream_t st = (cudaStream_t)stream_v;

@@ -1,0 +1,421 @@
+// K3 on the 5th-generation tensor cores: paged prefill / shared-prefix attention with tcgen05.mma, accumulators
+// in TMEM and all operands staged by TMA.
+//
+// Work unit: 128 packed query rows of one (sequence, kv head); a packed row is (token, head of the GQA group),
+// so one K/V tile serves all G query heads of the group.  Per KV tile of 128 keys:
+//   S = Q K^T          tcgen05.mma 128x128x128, S in TMEM (double-buffered, so the next tile's QK^T overlaps the
+//                      softmax of this one)
+//   P = exp2(S - m)    four softmax warps, one query row per thread (tcgen05.ld, no shuffles), P written as bf16
+//                      into shared memory in the 128-byte-swizzled K-major layout the MMA reads
+//   O_j = P V          tcgen05.mma with V as an MN-major operand straight from the page layout [key][d]
+//   acc = acc * alpha + O_j   in registers of the softmax threads (read back from TMEM)
+// K and V pages (16 keys x 128 d) are gathered through the block table by TMA boxes of {64 d, 16 keys}; Q comes
+// in through a 3-D tensor map (d, head, token) so that the packed-row order is produced by the copy itself.
+//
+// Handles head_dim 128, page size 16, causal (with offset, for chunked prefill and prefix-cache hits) or
+// bidirectional masks, optional log-sum-exp output for merging partial results.  Sliding windows, ALiBi and other
+// head sizes stay on the warp-MMA kernel (attn_prefill.cu).
+//
+// Replaces in the reference: ops_fn::flash_attention (crates/runtime/src/tensor_core.rs:1318-1383).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdlib.h>
+
+#include "../common/ptx.cuh"
+#include "../include/unillm_b200.h"
+
+namespace ub {
+namespace atc {
+
+constexpr int BM = 128;           // packed query rows per CTA
+constexpr int BN = 128;           // keys per tile
+constexpr int HD = 128;           // head dim
+constexpr int PAGE = 16;
+constexpr int HALF_BYTES = BM * 128;            // one 64-column half of a 128-row operand: 16 KB
+constexpr int TILE_BYTES = 2 * HALF_BYTES;      // 32 KB
+constexpr int SMEM_Q = 0;
+constexpr int SMEM_K = SMEM_Q + TILE_BYTES;         // 2 stages
+constexpr int SMEM_V = SMEM_K + 2 * TILE_BYTES;     // 2 stages
+constexpr int SMEM_P = SMEM_V + 2 * TILE_BYTES;
+constexpr int SMEM_BAR = SMEM_P + TILE_BYTES;       // 192 KB of tiles, then barriers
+constexpr int SMEM_TOTAL = SMEM_BAR + 256 + 1024;   // + alignment slack
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(m), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+
+struct Params {
+  __nv_bfloat16* out;
+  float* lse;
+  const int* block_tables;
+  const int* seq_lens;
+  const int* q_start;
+  int* err;
+  int Hq, Hkv, G, max_blocks_per_seq, num_blocks;
+  long long o_stride;
+  float scale_log2;
+  int causal;
+};
+
+__global__ void __launch_bounds__(192, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                       const __grid_constant__ CUtensorMap tmap_v, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_BAR);
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;    // [2]
+  uint64_t* k_empty = bars + 3;   // [2]
+  uint64_t* v_full = bars + 5;    // [2]
+  uint64_t* v_empty = bars + 7;   // [2]
+  uint64_t* s_full = bars + 9;    // [2]
+  uint64_t* s_empty = bars + 11;  // [2]
+  uint64_t* p_full = bars + 13;
+  uint64_t* o_full = bars + 14;
+  uint64_t* o_empty = bars + 15;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seq = blockIdx.z, kh = blockIdx.y, G = p.G;
+  const int TOK = BM / G;                                   // query tokens per tile
+  const int q_begin = p.q_start[seq], q_end = p.q_start[seq + 1];
+  const int q_len = q_end - q_begin;
+  const int t0 = q_begin + blockIdx.x * TOK;                // first token of this tile (global token index)
+  if (t0 >= q_end) return;                                  // whole CTA leaves together, nothing allocated yet
+  const int kv_len = p.seq_lens[seq];
+  const int t_last = min(t0 + TOK, q_end) - 1;
+  int kv_hi = p.causal ? min(kv_len, kv_len - q_len + (t_last - q_begin) + 1) : kv_len;
+  if (kv_hi < 0) kv_hi = 0;
+  const int n_tiles = (kv_hi + BN - 1) / BN;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 128);
+    }
+    mbar_init(p_full, 128);
+    mbar_init(o_full, 1);
+    mbar_init(o_empty, 128);
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s = tmem_base;            // S buffers: columns [0,128) and [128,256)
+  const uint32_t tmem_o = tmem_base + 256;      // O tile: columns [256,384)
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0 && n_tiles > 0) {
+      mbar_arrive_expect_tx(q_full, TILE_BYTES);
+      tma_load_3d(smem + SMEM_Q, &tmap_q, q_full, 0, kh * G, t0);
+      tma_load_3d(smem + SMEM_Q + HALF_BYTES, &tmap_q, q_full, 64, kh * G, t0);
+      const int* bt = p.block_tables + (long long)seq * p.max_blocks_per_seq;
+      const int pages_valid = (kv_hi + PAGE - 1) / PAGE;
+      bool dead = false;
+      for (int j = 0; j < n_tiles && !dead; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        // K tile
+        if (!mbar_wait(&k_empty[s], ph ^ 1, abort_flag, p.err, 500 + s)) { dead = true; break; }
+        mbar_arrive_expect_tx(&k_full[s], TILE_BYTES);
+        for (int pg = 0; pg < BN / PAGE; ++pg) {
+          const int pi = j * (BN / PAGE) + pg;
+          int blk = (pi < pages_valid && pi < p.max_blocks_per_seq) ? bt[pi] : 0;   // pages past the end: any finite page
+          if (blk < 0 || blk >= p.num_blocks) { set_err(p.err, ERR_BOUNDS, blk); blk = 0; }
+          const int row = (blk * p.Hkv + kh) * PAGE;
+          uint8_t* dst = smem + SMEM_K + s * TILE_BYTES + pg * PAGE * 128;
+          tma_load_2d(dst, &tmap_k, &k_full[s], 0, row);
+          tma_load_2d(dst + HALF_BYTES, &tmap_k, &k_full[s], 64, row);
+        }
+        // V tile
+        if (!mbar_wait(&v_empty[s], ph ^ 1, abort_flag, p.err, 510 + s)) { dead = true; break; }
+        mbar_arrive_expect_tx(&v_full[s], TILE_BYTES);
+        for (int pg = 0; pg < BN / PAGE; ++pg) {
+          const int pi = j * (BN / PAGE) + pg;
+          int blk = (pi < pages_valid && pi < p.max_blocks_per_seq) ? bt[pi] : 0;
+          if (blk < 0 || blk >= p.num_blocks) blk = 0;
+          const int row = (blk * p.Hkv + kh) * PAGE;
+          uint8_t* dst = smem + SMEM_V + s * TILE_BYTES + pg * PAGE * 128;
+          tma_load_2d(dst, &tmap_v, &v_full[s], 0, row);
+          tma_load_2d(dst + HALF_BYTES, &tmap_v, &v_full[s], 64, row);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idesc_qk = make_idesc_bf16(BM, BN, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(BM, HD, 0, 1);   // B = V is MN-major ([key][d], d contiguous)
+      const uint32_t q_addr = smem_u32(smem + SMEM_Q), p_addr = smem_u32(smem + SMEM_P);
+      auto issue_qk = [&](int j) {
+        const uint32_t k_addr = smem_u32(smem + SMEM_K + (j & 1) * TILE_BYTES);
+        const uint32_t d = tmem_s + (j & 1) * BN;
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+          umma_bf16_ss(d, make_smem_desc_sw128(q_addr + off, 16, 1024), make_smem_desc_sw128(k_addr + off, 16, 1024),
+                       idesc_qk, k != 0);
+        }
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.err, 520);
+      if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag, p.err, 521);
+      if (ok) {
+        tc_fence_after();
+        issue_qk(0);
+        umma_commit(&s_full[0]);
+        umma_commit(&k_empty[0]);
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) {
+          const int jn = j + 1, sn = jn & 1;
+          const uint32_t phn = (jn >> 1) & 1;
+          if (!mbar_wait(&k_full[sn], phn, abort_flag, p.err, 522)) { ok = false; break; }
+          if (!mbar_wait(&s_empty[sn], phn ^ 1, abort_flag, p.err, 523)) { ok = false; break; }
+          tc_fence_after();
+          issue_qk(jn);
+          umma_commit(&s_full[sn]);
+          umma_commit(&k_empty[sn]);
+        }
+        const int s = j & 1;
+        if (!mbar_wait(p_full, j & 1, abort_flag, p.err, 524)) { ok = false; break; }
+        if (!mbar_wait(&v_full[s], (j >> 1) & 1, abort_flag, p.err, 525)) { ok = false; break; }
+        if (!mbar_wait(o_empty, (j & 1) ^ 1, abort_flag, p.err, 526)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(smem + SMEM_V + s * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < BN / 16; ++k) {
+          // A = P, K-major over keys: 64-key halves 16 KB apart, 16 keys = 32 B inside a 128-B row
+          const uint64_t a_desc = make_smem_desc_sw128(p_addr + (k >> 2) * HALF_BYTES + (k & 3) * 32, 16, 1024);
+          // B = V, MN-major: 16 keys = two 8-key groups (1024 B apart); the two 64-wide d blocks are 16 KB apart
+          const uint64_t b_desc = make_smem_desc_sw128(v_addr + k * 16 * 128, HALF_BYTES, 1024);
+          umma_bf16_ss(tmem_o, a_desc, b_desc, idesc_pv, k != 0);
+        }
+        umma_commit(o_full);
+        umma_commit(&v_empty[s]);
+      }
+    }
+  } else {
+    // ------------------------------ softmax + output (warps 2..5) ------------------------------
+    const int qd = warp & 3;                    // TMEM lane quarter this warp may read
+    const int row = qd * 32 + lane;             // packed query row == TMEM lane
+    const uint32_t lane_off = uint32_t(qd * 32) << 16;
+    const int tok = t0 + row / G, head = kh * G + row % G;
+    const bool row_valid = tok < q_end;
+    int limit = kv_len;
+    if (p.causal) limit = min(kv_len, kv_len - q_len + (tok - q_begin) + 1);
+    if (!row_valid || limit < 0) limit = 0;
+    float m = -CUDART_INF_F, l = 0.f;
+    float acc[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) acc[i] = 0.f;
+    uint8_t* p_row = smem + SMEM_P + row * 128;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int b = j & 1;
+      if (!mbar_wait(&s_full[b], (j >> 1) & 1, abort_flag, p.err, 530)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t s_addr = tmem_s + b * BN + lane_off;
+      const int key0 = j * BN;
+      // pass 1: row maximum
+      float mx = -CUDART_INF_F;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(s_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (key0 + c * 32 + i < limit) mx = fmaxf(mx, __uint_as_float(r[i]));
+      }
+      const float m_new = fmaxf(m, mx * p.scale_log2);
+      const float alpha = (m == -CUDART_INF_F) ? 0.f : exp2f(m - m_new);
+      const float m_use = (m_new == -CUDART_INF_F) ? 0.f : m_new;   // fully masked so far: every p is 0 anyway
+      // pass 2: probabilities -> bf16 -> swizzled shared memory
+      float psum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(s_addr + c * 32, r);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int k0 = key0 + c * 32 + 2 * i;
+          float p0 = (k0 < limit) ? exp2f(__uint_as_float(r[2 * i]) * p.scale_log2 - m_use) : 0.f;
+          float p1 = (k0 + 1 < limit) ? exp2f(__uint_as_float(r[2 * i + 1]) * p.scale_log2 - m_use) : 0.f;
+          // the MMA sees the rounded values: sum what it sees
+          const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+          packed[i] = *reinterpret_cast<const uint32_t*>(&pb);
+          const float2 back = __bfloat1622float2(pb);
+          psum += back.x + back.y;
+        }
+        // 32 keys = 4 chunks of 16 B; key half = c / 2, chunk index inside the 128-B row = (c & 1) * 4 + q
+        uint8_t* base = p_row + (c >> 1) * HALF_BYTES;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int chunk = (c & 1) * 4 + q4;
+          *reinterpret_cast<uint4*>(base + ((chunk ^ (row & 7)) << 4)) =
+              make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+        }
+      }
+      // S buffer fully read; P written
+      tc_fence_before();
+      mbar_arrive(&s_empty[b]);
+      fence_proxy_async_smem();
+      mbar_arrive(p_full);
+      l = l * alpha + psum;
+      m = m_new;
+      // O tile of this KV tile
+      if (!mbar_wait(o_full, j & 1, abort_flag, p.err, 531)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_o + lane_off + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[c * 32 + i] = acc[c * 32 + i] * alpha + __uint_as_float(r[i]);
+      }
+      tc_fence_before();
+      mbar_arrive(o_empty);
+    }
+    if (row_valid && ok) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* dst = p.out + (long long)tok * p.o_stride + (long long)head * HD;
+#pragma unroll
+      for (int i = 0; i < HD; i += 8) {
+        *reinterpret_cast<uint4*>(dst + i) =
+            make_uint4(pack_bf16x2(acc[i] * inv, acc[i + 1] * inv), pack_bf16x2(acc[i + 2] * inv, acc[i + 3] * inv),
+                       pack_bf16x2(acc[i + 4] * inv, acc[i + 5] * inv), pack_bf16x2(acc[i + 6] * inv, acc[i + 7] * inv));
+      }
+      if (p.lse != nullptr) p.lse[(long long)tok * p.Hq + head] = l > 0.f ? (m * LN2 + logf(l)) : -CUDART_INF_F;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(20000);   // let bulk copies in flight land before smem is reused
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+static int encode(CUtensorMap* out, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides_bytes,
+                  const cuuint32_t* box) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), dims, strides_bytes, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -(int)r - 1000;
+}
+
+}  // namespace atc
+}  // namespace ub
+
+// 1 when the tensor-core kernel can run this problem.
+extern "C" int ub_attn_prefill_tc_supported(const UbAttnArgs* a) {
+  if (a->D != 128 || a->block_size != 16 || a->window > 0 || a->alibi_slopes != nullptr || a->kv_start != 0) return 0;
+  if (a->Hkv <= 0 || a->Hq % a->Hkv != 0) return 0;
+  const int G = a->Hq / a->Hkv;
+  if (G > 128 || 128 % G != 0) return 0;
+  if (a->q_stride % 8 != 0 || a->o_stride % 8 != 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(a->q) & 15) || (reinterpret_cast<uintptr_t>(a->out) & 15) ||
+      (reinterpret_cast<uintptr_t>(a->k_cache) & 15) || (reinterpret_cast<uintptr_t>(a->v_cache) & 15))
+    return 0;
+  if (a->total_q <= 0) return 0;
+  return 1;
+}
+
+extern "C" int ub_attn_prefill_tc(const UbAttnArgs* a, void* stream_v) {
+  using namespace ub;
+  using namespace ub::atc;
+  if (a->num_seqs <= 0 || a->max_q_len <= 0) return 0;
+  if (!ub_attn_prefill_tc_supported(a)) return -4;
+  const int G = a->Hq / a->Hkv;
+  const int TOK = BM / G;
+  CUtensorMap tq, tk, tv;
+  {
+    // Q viewed as (d, head, token): box = 64 d x G heads x TOK tokens -> rows ordered (token, head in group)
+    cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)a->Hq, (cuuint64_t)a->total_q};
+    cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)a->q_stride * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)TOK};
+    int rc = encode(&tq, a->q, 3, dims, strides, box);
+    if (rc != 0) return rc;
+  }
+  {
+    // K / V caches viewed as rows of 128 d: row = (block * Hkv + kv head) * 16 + slot
+    cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)a->num_blocks * a->Hkv * PAGE};
+    cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+    cuuint32_t box[2] = {64, PAGE};
+    int rc = encode(&tk, a->k_cache, 2, dims, strides, box);
+    if (rc != 0) return rc;
+    rc = encode(&tv, a->v_cache, 2, dims, strides, box);
+    if (rc != 0) return rc;
+  }
+  Params p;
+  p.out = reinterpret_cast<__nv_bfloat16*>(a->out);
+  p.lse = a->lse;
+  p.block_tables = a->block_tables;
+  p.seq_lens = a->seq_lens;
+  p.q_start = a->q_start;
+  p.err = a->err;
+  p.Hq = a->Hq; p.Hkv = a->Hkv; p.G = G;
+  p.max_blocks_per_seq = a->max_blocks_per_seq;
+  p.num_blocks = a->num_blocks;
+  p.o_stride = a->o_stride;
+  p.scale_log2 = a->scale * LOG2E;
+  p.causal = a->causal;
+  static bool attr_set[UB_MAX_DEVICES] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < UB_MAX_DEVICES && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    if (e != cudaSuccess) return -(int)e;
+    attr_set[dev] = true;
+  }
+  dim3 grid((a->max_q_len + TOK - 1) / TOK, a->Hkv, a->num_seqs);
+  attn_prefill_tc_kernel<<<grid, 192, SMEM_TOTAL, reinterpret_cast<cudaStream_t>(stream_v)>>>(tq, tk, tv, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}

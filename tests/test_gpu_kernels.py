@@ -301,3 +301,35 @@ def test_eltwise_embed_actmul():
     gu = _rand(17, 2 * 384, seed=3)
     _close(cuda_ops.act_mul(gu, "silu"), torch.nn.functional.silu(gu[:, :384].float()) * gu[:, 384:].float())
     _close(cuda_ops.l2_normalize(x), torch.nn.functional.normalize(x.float(), dim=-1))
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(32, 8), (8, 8), (16, 2), (8, 1)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_attn_prefill_tensor_core_path(Hq, Hkv, causal):
+    """Head dim 128 without window / ALiBi runs on the tcgen05 kernel: long and short sequences, chunked prefill
+    with a cached prefix, tiles that end inside a page, more than two KV tiles (stage reuse)."""
+    from unillm_b200.ops import cuda_ops
+
+    kv_lens = [1100, 17, 300, 129, 640]
+    q_lens = [37, 17, 300, 1, 130]
+    kc, vc, bt, sl, dk, dv = make_paged_cache(len(kv_lens), kv_lens, Hkv, 128, seed=11)
+    qs = [0]
+    for l in q_lens:
+        qs.append(qs[-1] + l)
+    q = _rand(qs[-1], Hq, 128, seed=12)
+    q_start = torch.tensor(qs, dtype=torch.int32, device="cuda")
+    out, lse = cuda_ops.attn_prefill(q, kc, vc, bt, sl, q_start, max(q_lens), causal=causal, return_lse=True)
+    assert cuda_ops.attn_prefill_last_path() == "tcgen05"
+    torch.cuda.synchronize()
+    cuda_ops.check_device_errors()
+    for i, (kl, ql) in enumerate(zip(kv_lens, q_lens)):
+        ro, rl = ref_attention(q[qs[i]:qs[i + 1]].cpu(), dk[i], dv[i], causal_offset=(kl - ql) if causal else None)
+        _close(out[qs[i]:qs[i + 1]], ro)
+        _close(lse[qs[i]:qs[i + 1]], rl, rtol=1e-2, atol=1e-2)
+    # strided query view (rows of a fused QKV matrix), as the runner passes it
+    qkv = _rand(qs[-1], Hq + 2 * Hkv, 128, seed=13)
+    out2 = cuda_ops.attn_prefill(qkv[:, :Hq], kc, vc, bt, sl, q_start, max(q_lens), causal=causal)
+    for i, (kl, ql) in enumerate(zip(kv_lens, q_lens)):
+        ro, _ = ref_attention(qkv[qs[i]:qs[i + 1], :Hq].cpu(), dk[i], dv[i], causal_offset=(kl - ql) if causal else None)
+        _close(out2[qs[i]:qs[i + 1]], ro)
+    cuda_ops.check_device_errors()

@@ -100,7 +100,8 @@ def bench_attn(results):
                  frac_hbm=byts / med / 1e6 / hbm, peaks=how)
         results.append(r)
         print(json.dumps(r))
-    for T, ctx, Hq, Hkv, D in [(2048, 2048, 32, 8, 128), (8192, 8192, 4, 1, 128)]:
+    for T, ctx, Hq, Hkv, D, causal in [(2048, 2048, 32, 8, 128, True), (8192, 8192, 4, 1, 128, True),
+                                       (256, 1024, 32, 8, 128, False), (512, 1024, 32, 8, 128, False)]:
         bs = 16
         nblk = (ctx + bs - 1) // bs
         kc = torch.randn(nblk, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
@@ -110,10 +111,11 @@ def bench_attn(results):
         qs = torch.tensor([0, T], dtype=torch.int32, device="cuda")
         q = torch.randn(T, Hq, D, device="cuda", dtype=torch.bfloat16)
         out = torch.empty_like(q)
-        med, best = time_ms(lambda: cuda_ops.attn_prefill(q, kc, vc, bt, sl, qs, T, out=out))
-        flops = 4.0 * T * ctx * Hq * D / 2
-        r = dict(kind="attn_prefill", T=T, ctx=ctx, Hq=Hq, Hkv=Hkv, D=D, ms=med, best_ms=best,
-                 tflops=flops / med / 1e9, frac_tflops=flops / med / 1e9 / tf, peaks=how)
+        med, best = time_ms(lambda: cuda_ops.attn_prefill(q, kc, vc, bt, sl, qs, T, out=out, causal=causal))
+        flops = 4.0 * T * ctx * Hq * D / (2 if causal else 1)
+        r = dict(kind="attn_prefill", T=T, ctx=ctx, Hq=Hq, Hkv=Hkv, D=D, causal=causal, ms=med, best_ms=best,
+                 tflops=flops / med / 1e9, frac_tflops=flops / med / 1e9 / tf, path=cuda_ops.attn_prefill_last_path(),
+                 peaks=how)
         results.append(r)
         print(json.dumps(r))
 

@@ -299,6 +299,13 @@ def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     return (out, lse) if return_lse else out
 
 
+def attn_prefill_last_path() -> str:
+    """Which kernel the last ``attn_prefill`` call ran: ``"tcgen05"`` or ``"mma.sync"``."""
+    lib = N.cuda_lib()
+    lib.ub_attn_prefill_last_path.restype = C.c_int
+    return {1: "tcgen05", 2: "mma.sync"}.get(lib.ub_attn_prefill_last_path(), "none")
+
+
 def attn_merge(o_a: torch.Tensor, lse_a: torch.Tensor, o_b: torch.Tensor, lse_b: torch.Tensor,
                out: Optional[torch.Tensor] = None, lse_out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Combine two attention partials over disjoint key sets.  o_*: [T, Hq, D] contiguous, lse_*: [T, Hq]."""
