@@ -4,7 +4,9 @@
 // are processed together, so each K/V byte is fetched from HBM exactly once per step.  A group of
 // D/8 lanes owns one token: each lane loads one 16-byte chunk of the K row, partial dots are
 // reduced with xor-shuffles, and the same lanes own the matching 16-byte chunk of the output
-// accumulator for the P*V pass.  Four tokens per lane group are in flight per iteration and the
+// accumulator for the P*V pass.  K and V rows reach the lanes through a three-stage cp.async pipeline in shared
+// memory (tiles of 4 * (32 / (D/8)) * 4 tokens gathered page by page through the block table), so two tiles are
+// always in flight while one is consumed.  Four tokens per lane group are processed per iteration and the
 // online-softmax rescale runs once per four tokens.  Partial (O, lse) of each split go to a
 // scratch buffer and a second kernel merges them.  Sliding window, ALiBi and "suffix only"
 // (kv_start, for cascade attention after a shared radix prefix) are predicates on the kv index.
@@ -15,11 +17,32 @@
 #include "../common/ptx.cuh"
 #include "../include/unillm_b200.h"
 #include <math_constants.h>
+#include <stdlib.h>
+
+extern "C" int ub_attn_decode_mma_supported(const UbAttnArgs* a);
+extern "C" int ub_attn_decode_mma_main(const UbAttnArgs* a, void* stream);
 
 namespace ub {
 
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
+
+__device__ __forceinline__ void cp_async16_zfill(void* smem_dst, const void* gsrc, bool pred) {
+  const int sz = pred ? 16 : 0;         // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(sz) : "memory");
+}
+
+// Dynamic shared memory of the decode kernel: three K/V stages (reused by the cross-warp reduction), then q, then (m, l).
+template <int D, int G>
+struct DecodeSmem {
+  static constexpr int TILE = 4 * (32 / (D / 8)) * 4;
+  static constexpr int STAGE_BYTES = 2 * TILE * D * 2;
+  static constexpr int RED_BYTES = 4 * G * D * 4;
+  static constexpr int PIPE_BYTES = 3 * STAGE_BYTES > RED_BYTES ? 3 * STAGE_BYTES : RED_BYTES;
+  static constexpr int Q_OFF = PIPE_BYTES;
+  static constexpr int ML_OFF = Q_OFF + G * D * 4;
+  static constexpr int TOTAL = ML_OFF + 4 * G * 2 * 4;
+};
 
 template <int D, int G>
 __global__ void __launch_bounds__(128) attn_decode_kernel(const UbAttnArgs a, const int gchunks) {
@@ -36,9 +59,14 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const UbAttnArgs a, co
   const int h0 = kvh * Gtot + gc * G;     // first query head of this CTA
   const int gn = min(G, Gtot - gc * G);   // valid heads in this chunk
 
-  __shared__ float q_s[G][D];
-  __shared__ float red_o[4][G][D];
-  __shared__ float red_ml[4][G][2];
+  constexpr int TILE = 4 * TPW * UN;                 // tokens per pipeline stage
+  constexpr int STAGES = 3;
+  constexpr int STAGE_BYTES = 2 * TILE * D * 2;      // K tile then V tile
+  extern __shared__ __align__(16) uint8_t dsm[];
+  // the cross-warp reduction buffer reuses the pipeline stages (all copies have landed by then)
+  float (*red_o)[G][D] = reinterpret_cast<float (*)[G][D]>(dsm);
+  float (*q_s)[D] = reinterpret_cast<float (*)[D]>(dsm + DecodeSmem<D, G>::Q_OFF);
+  float (*red_ml)[G][2] = reinterpret_cast<float (*)[G][2]>(dsm + DecodeSmem<D, G>::ML_OFF);
 
   const int kv_len = a.seq_lens[seq];
   const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(a.q) + (long long)seq * a.q_stride;
@@ -73,26 +101,51 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const UbAttnArgs a, co
   const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(a.k_cache);
   const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(a.v_cache);
 
-  for (int base = kv_lo + warp * (TPW * UN); base < kv_hi; base += 4 * TPW * UN) {
-    long long off[UN];
+  const int n_tiles = kv_hi > kv_lo ? (kv_hi - kv_lo + TILE - 1) / TILE : 0;
+  // cooperative gather of one tile: TILE tokens x (D/8) 16-byte chunks for K and for V
+  auto issue_tile = [&](int t) {
+    if (t < n_tiles) {
+      uint8_t* st = dsm + (t % STAGES) * STAGE_BYTES;
+      const int tile_base = kv_lo + t * TILE;
+      for (int c = threadIdx.x; c < TILE * LPT; c += 128) {
+        const int tk = c / LPT, part = c % LPT;
+        const int pos = tile_base + tk;
+        bool okc = pos < kv_hi;
+        long long off = 0;
+        if (okc) {
+          const int bi = pos / a.block_size;
+          const int blk = bi < a.max_blocks_per_seq ? bt[bi] : -1;
+          if (blk < 0 || blk >= a.num_blocks) {
+            set_err(a.err, ERR_BOUNDS, seq);
+            okc = false;
+          } else {
+            off = (((long long)blk * a.Hkv + kvh) * a.block_size + (pos % a.block_size)) * D + part * 8;
+          }
+        }
+        cp_async16_zfill(st + c * 16, kc + off, okc);
+        cp_async16_zfill(st + TILE * D * 2 + c * 16, vc + off, okc);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  for (int t = 0; t < STAGES - 1; ++t) issue_tile(t);
+
+  for (int t = 0; t < n_tiles; ++t) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+    __syncthreads();                    // tile t is visible to everyone; everyone is done with tile t-1
+    issue_tile(t + STAGES - 1);         // goes into the stage tile t-1 used
+    const uint8_t* ks = dsm + (t % STAGES) * STAGE_BYTES;
+    const uint8_t* vs = ks + TILE * D * 2;
+    const int base = kv_lo + t * TILE + warp * (TPW * UN);
     bool ok[UN];
     uint4 kk[UN];
+    int srow[UN];
 #pragma unroll
     for (int u = 0; u < UN; ++u) {
       const int pos = base + u * TPW + grp;
       ok[u] = pos < kv_hi;
-      off[u] = 0;
-      if (ok[u]) {
-        const int bi = pos / a.block_size;
-        int blk = bi < a.max_blocks_per_seq ? bt[bi] : -1;
-        if (blk < 0 || blk >= a.num_blocks) {
-          set_err(a.err, ERR_BOUNDS, seq);
-          ok[u] = false;
-        } else {
-          off[u] = (((long long)blk * a.Hkv + kvh) * a.block_size + (pos % a.block_size)) * D + chunk * 8;
-        }
-      }
-      kk[u] = ok[u] ? *reinterpret_cast<const uint4*>(kc + off[u]) : make_uint4(0, 0, 0, 0);
+      srow[u] = (warp * (TPW * UN) + u * TPW + grp) * D * 2 + chunk * 16;
+      kk[u] = *reinterpret_cast<const uint4*>(ks + srow[u]);
     }
     float s[UN][G];
 #pragma unroll
@@ -118,11 +171,9 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const UbAttnArgs a, co
         const int pos = base + u * TPW + grp;
         s[u][g] = ok[u] ? s[u][g] + slope[g] * (float)(pos - (kv_len - 1)) : -CUDART_INF_F;
       }
-    // V loads issued before the softmax math so they overlap it
     uint4 vv[UN];
 #pragma unroll
-    for (int u = 0; u < UN; ++u)
-      vv[u] = ok[u] ? *reinterpret_cast<const uint4*>(vc + off[u]) : make_uint4(0, 0, 0, 0);
+    for (int u = 0; u < UN; ++u) vv[u] = *reinterpret_cast<const uint4*>(vs + srow[u]);
     float p[UN][G];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -153,6 +204,9 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const UbAttnArgs a, co
         for (int e = 0; e < 8; ++e) acc[g][e] += p[u][g] * vf[e];
     }
   }
+
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();                      // the stages are free: red_o lives there from here on
 
   // merge the token groups inside the warp (lanes that own the same chunk)
 #pragma unroll
@@ -253,8 +307,42 @@ __global__ void attn_merge2_kernel(const __nv_bfloat16* oa, const float* la, con
   if (threadIdx.x == 0 && lse_out != nullptr) lse_out[r] = den > 0.f ? mx + __logf(den) : -CUDART_INF_F;
 }
 
+template <int D, int G>
+static void launch_decode_g(const UbAttnArgs& a, dim3 grid, int gchunks, cudaStream_t st) {
+  constexpr int SMEM = DecodeSmem<D, G>::TOTAL;
+  static bool attr_set[UB_MAX_DEVICES] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < UB_MAX_DEVICES && !attr_set[dev]) {
+    cudaFuncSetAttribute(attn_decode_kernel<D, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    attr_set[dev] = true;
+  }
+  attn_decode_kernel<D, G><<<grid, 128, SMEM, st>>>(a, gchunks);
+}
+
+static bool decode_mma_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("UB_DECODE_MMA");     // UB_DECODE_MMA=0 keeps the CUDA-core kernel (A/B comparisons)
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
 template <int D>
 static int launch_decode(const UbAttnArgs& a, cudaStream_t st) {
+  if (D <= 128 && decode_mma_enabled() && ub_attn_decode_mma_supported(&a)) {
+    int rc = ub_attn_decode_mma_main(&a, st);
+    if (rc != 0) return rc;
+    if (a.splits > 1) {
+      dim3 g2(a.num_seqs, a.Hq);
+      attn_split_merge_kernel<<<g2, D <= 128 ? D : 128, 0, st>>>(a.scratch, reinterpret_cast<__nv_bfloat16*>(a.out),
+                                                                 a.lse, a.Hq, D, a.splits, a.o_stride);
+      cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) return -(int)e;
+    }
+    return 0;
+  }
   const int Gtot = a.Hq / a.Hkv;
   int G = 1;
   while (G < Gtot && G < 8) G <<= 1;
@@ -262,11 +350,11 @@ static int launch_decode(const UbAttnArgs& a, cudaStream_t st) {
   const int gchunks = (Gtot + G - 1) / G;
   dim3 grid(a.num_seqs, a.Hkv * gchunks, a.splits);
   switch (G) {
-    case 1: attn_decode_kernel<D, 1><<<grid, 128, 0, st>>>(a, gchunks); break;
-    case 2: attn_decode_kernel<D, 2><<<grid, 128, 0, st>>>(a, gchunks); break;
-    case 4: attn_decode_kernel<D, 4><<<grid, 128, 0, st>>>(a, gchunks); break;
+    case 1: launch_decode_g<D, 1>(a, grid, gchunks, st); break;
+    case 2: launch_decode_g<D, 2>(a, grid, gchunks, st); break;
+    case 4: launch_decode_g<D, 4>(a, grid, gchunks, st); break;
     default:
-      if constexpr (D <= 128) { attn_decode_kernel<D, 8><<<grid, 128, 0, st>>>(a, gchunks); }
+      if constexpr (D <= 128) { launch_decode_g<D, 8>(a, grid, gchunks, st); }
       break;
   }
   cudaError_t e = cudaGetLastError();

@@ -100,6 +100,13 @@ def bench_attn(results):
                  frac_hbm=byts / med / 1e6 / hbm, peaks=how)
         results.append(r)
         print(json.dumps(r))
+        # the same problem through the prefill kernels (one query token per sequence)
+        qs1 = torch.arange(B + 1, dtype=torch.int32, device="cuda")
+        med, best = time_ms(lambda: cuda_ops.attn_prefill(q, kc, vc, bt, sl, qs1, 1, out=out, causal=True))
+        r = dict(kind="attn_decode_via_prefill", B=B, ctx=ctx, Hq=Hq, Hkv=Hkv, D=D, ms=med, best_ms=best, gbs=byts / med / 1e6,
+                 frac_hbm=byts / med / 1e6 / hbm, path=cuda_ops.attn_prefill_last_path(), peaks=how)
+        results.append(r)
+        print(json.dumps(r))
     for T, ctx, Hq, Hkv, D, causal in [(2048, 2048, 32, 8, 128, True), (8192, 8192, 4, 1, 128, True),
                                        (256, 1024, 32, 8, 128, False), (512, 1024, 32, 8, 128, False)]:
         bs = 16
