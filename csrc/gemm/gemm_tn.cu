@@ -64,6 +64,7 @@ struct GemmParams {
   const int4* grp_tiles;
   int grp_max_tiles;  // token-tile slots in the table
   int grp_w_rows;     // rows of w per expert; expert e's weights are rows [e*grp_w_rows, (e+1)*grp_w_rows)
+  int tile_begin, tile_end;   // work units of this launch; tile_end == 0 means all
 };
 
 // Coordinates of work unit u.  m0/m_end: token rows; nw: row of the weight tile in w; no: first output feature.
@@ -194,7 +195,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   const int lane = threadIdx.x & 31;
   const int num_m = p.grp_tiles != nullptr ? p.grp_max_tiles : (p.M + TN - 1) / TN;
   const int num_n = (p.N + BM_W - 1) / BM_W;
-  const int total_tiles = num_m * num_n;
+  // [tile_begin, tile_end) is this launch's share of the num_m * num_n work units (two-phase schedule, see plan_gemm)
+  const int tile_begin = p.tile_begin;
+  const int total_tiles = p.tile_end > 0 ? p.tile_end : num_m * num_n;
   const int num_kb = (p.K + BK - 1) / BK;
   constexpr uint32_t ACC_COLS = (DUAL ? 2 : 1) * TN;
   // Two accumulator buffers when they fit in the 512 TMEM columns (epilogue overlaps the next tile's MMAs).
@@ -207,13 +210,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   int unit_begin, unit_step, kb0 = 0, kb1 = num_kb, crank = 0;
   if (SPLITK) {
     crank = blockIdx.x;  // cluster = (splits, 1, 1) and gridDim.x == splits
-    unit_begin = blockIdx.y;
-    unit_step = total_tiles;  // exactly one tile per cluster
+    unit_begin = tile_begin + blockIdx.y;
+    unit_step = 1 << 30;  // exactly one tile per cluster
     const int per = (num_kb + p.splits - 1) / p.splits;
     kb0 = crank * per;
     kb1 = min(num_kb, kb0 + per);
   } else {
-    unit_begin = blockIdx.x;
+    unit_begin = tile_begin + blockIdx.x;
     unit_step = gridDim.x;
   }
 
@@ -459,8 +462,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     // All CTAs of the cluster have parked their partials; reduce a slice of token rows each.
     tc_fence_before();
     cluster_sync_all();
-    if (warp >= 2 && blockIdx.y < total_tiles) {
-      const int u = blockIdx.y;
+    if (warp >= 2 && tile_begin + (int)blockIdx.y < total_tiles) {
+      const int u = tile_begin + blockIdx.y;
       const int m0 = (u % num_m) * TN, n0 = (u / num_m) * BM_W;
       const int tid_e = threadIdx.x - 64;
       const int per = (TN + p.splits - 1) / p.splits;
@@ -520,6 +523,302 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 }
 
 // ----------------------------------------------------------------------------
+// 2-CTA variant (tcgen05 cta_group::2).  A thread-block cluster of two CTAs on neighbouring SMs computes one tile of
+// 256 weight rows x TN tokens: every CTA stages its own 128 weight rows and HALF of the token tile, the leader CTA
+// issues MMAs that read both shared memories, and every CTA ends up with its 128 rows of the result in its own
+// TMEM.  Per MMA a CTA therefore moves 2/3 of the bytes of the 1-CTA kernel from L2 into shared memory, which is
+// what bounds large-token-count tiles.  Barrier protocol:
+//   full[s]  (leader's)  : both producers' TMA loads complete_tx on it (cta_group::2 loads, barrier address mapped
+//                          to CTA 0); the leader's producer arrives with the byte count of both CTAs
+//   empty[s] (each CTA's): the leader's tcgen05.commit arrives on its own and on the peer's barrier
+//   tmem_full (each CTA's): same, by commit;  tmem_empty (leader's): 256 arrivals, the peer's come over DSMEM
+// No load is multicast.  Plain, bias / residual / activation epilogues, the gated (dual) form and the F1 / F3
+// collective hooks are supported; split-K and the grouped mode stay on the 1-CTA kernel.
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void tmem_alloc_cg2(uint32_t* smem_slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_cg2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_cg2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// TMA tile load whose completion bytes go to a barrier that may live in the peer CTA (cluster address).
+__device__ __forceinline__ void tma_load_2d_cg2(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int x, int y,
+                                                uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, "
+      "{%3, %4}], [%2], %5;" ::"r"(smem_u32(smem_dst)),
+      "l"(m), "r"(bar_cluster_addr), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_ss_cg2(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the barrier at a cluster shared address once all MMAs issued so far by this thread are complete.
+__device__ __forceinline__ void umma_commit_cg2(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+template <int TN, int STAGES, bool DUAL>
+struct Gemm2Smem {
+  static constexpr int A_BYTES = BM_W * BK * 2;            // this CTA's 128 weight rows: 16 KB
+  static constexpr int B_BYTES = (TN / 2) * BK * 2;        // this CTA's half of the token tile
+  static constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * A_BYTES + B_BYTES;
+  static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int DATA_BYTES = TILE_BYTES + STAGING_BYTES;
+  static constexpr int TOTAL = DATA_BYTES + 1024 + 256;
+  static_assert(TOTAL <= 227 * 1024, "shared memory budget exceeded");
+};
+
+template <int TN, int STAGES, bool DUAL>
+__global__ void __launch_bounds__(192, 1)
+gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                    const GemmParams p) {
+  using S = Gemm2Smem<TN, STAGES, DUAL>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::DATA_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full_bar = empty_bar + STAGES;   // [2]
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;   // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();        // 0 = leader
+  const bool leader = rank == 0;
+  const int num_m = (p.M + TN - 1) / TN;
+  const int num_n = (p.N + 2 * BM_W - 1) / (2 * BM_W);
+  const int total_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+  constexpr uint32_t ACC_COLS = (DUAL ? 2 : 1) * TN;
+  constexpr int NBUF = (2 * ACC_COLS > 512) ? 1 : 2;
+  constexpr uint32_t NEED_COLS = NBUF * ACC_COLS;
+  constexpr uint32_t TMEM_COLS = NEED_COLS < 32 ? 32 : NEED_COLS;
+  static_assert(TMEM_COLS <= 512, "TMEM budget exceeded");
+  const int unit_begin = blockIdx.x >> 1, unit_step = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full_bar[b], 1);
+      mbar_init(&tmem_empty_bar[b], 256);       // epilogue threads of both CTAs (only the leader's copy is used)
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+  }
+  if (warp == 1) {
+    tmem_alloc_cg2(tmem_slot, TMEM_COLS);
+    tmem_relinquish_cg2();
+  }
+  tc_fence_before();
+  cluster_sync_all();                              // barriers of both CTAs are initialised before anyone uses them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    if (lane == 0) {
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_x = l2_policy_evict_last();
+      uint32_t ag_ready = 0;
+      int it = 0;
+      bool dead = false;
+      for (int u = unit_begin; u < total_tiles && !dead; u += unit_step) {
+        const int m0 = (u % num_m) * TN + int(rank) * (TN / 2);          // this CTA's half of the token tile
+        const int n0 = (u / num_m) * (2 * BM_W) + int(rank) * BM_W;      // this CTA's weight rows
+        if (p.ag_world > 0) {
+          const uint32_t want = p.ag_signals_per_use;
+          const int r_lo = m0 / p.ag_rows_per_rank;
+          int r_hi = (min(m0 + TN / 2, p.M) - 1) / p.ag_rows_per_rank;
+          if (r_hi >= p.ag_world) r_hi = p.ag_world - 1;
+          const uint64_t t0 = globaltimer_ns();
+          bool waited = false;
+          for (int r = r_lo; r <= r_hi; ++r) {
+            if (ag_ready >> r & 1u) continue;
+            uint32_t spin = 0;
+            while (int32_t(ld_acquire_sys_u32(p.ag_flags + r) - want) < 0) {
+              if ((++spin & 31u) == 0 && (globaltimer_ns() - t0 > UB_WAIT_NS)) {
+                *abort_flag = 1;
+                set_err(p.err, ERR_FLAG_TIMEOUT, r);
+                break;
+              }
+            }
+            ag_ready |= 1u << r;
+            waited = true;
+          }
+          if (waited) asm volatile("fence.proxy.async;" ::: "memory");
+        }
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err, 600 + s)) { dead = true; break; }
+          uint8_t* st = smem + s * S::STAGE_BYTES;
+          if (leader) mbar_arrive_expect_tx(&full_bar[s], 2 * S::STAGE_BYTES);   // bytes of both CTAs
+          const uint32_t fb = mapa_u32(smem_u32(&full_bar[s]), 0);              // the leader's barrier
+          tma_load_2d_cg2(st, &tmap_w, fb, kb * BK, n0, pol_w);
+          if (DUAL) tma_load_2d_cg2(st + S::A_BYTES, &tmap_w, fb, kb * BK, n0 + p.up_row_off, pol_w);
+          tma_load_2d_cg2(st + (DUAL ? 2 : 1) * S::A_BYTES, &tmap_x, fb, kb * BK, m0, pol_x);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (leader CTA only) ------------------------------
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc_bf16(2 * BM_W, TN, 0, 0);
+      int it = 0, ui = 0;
+      bool dead = false;
+      for (int u = unit_begin; u < total_tiles && !dead; u += unit_step) {
+        const int ab = NBUF == 1 ? 0 : (ui & 1);
+        const uint32_t aph = NBUF == 1 ? (ui & 1) : ((ui >> 1) & 1);
+        ++ui;
+        if (!mbar_wait(&tmem_empty_bar[ab], aph ^ 1, abort_flag, p.err, 610 + ab)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + ab * ACC_COLS;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, p.err, 620 + s)) { dead = true; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * S::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + (DUAL ? 2 : 1) * S::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t bdesc = make_smem_desc_sw128(b_addr + k * UMMA_K * 2, 16, 1024);
+            const uint64_t adesc = make_smem_desc_sw128(a_addr + k * UMMA_K * 2, 16, 1024);
+            const uint32_t acc = (kb != 0 || k != 0) ? 1u : 0u;
+            umma_bf16_ss_cg2(d_tmem, adesc, bdesc, idesc, acc);
+            if (DUAL) {
+              const uint64_t a2desc = make_smem_desc_sw128(a_addr + S::A_BYTES + k * UMMA_K * 2, 16, 1024);
+              umma_bf16_ss_cg2(d_tmem + TN, a2desc, bdesc, idesc, acc);
+            }
+          }
+          // the stage is free in BOTH CTAs once these MMAs have read it
+          const uint32_t eb = smem_u32(&empty_bar[s]);
+          umma_commit_cg2(mapa_u32(eb, 0));
+          umma_commit_cg2(mapa_u32(eb, 1));
+        }
+        const uint32_t tf = smem_u32(&tmem_full_bar[ab]);
+        umma_commit_cg2(mapa_u32(tf, 0));
+        umma_commit_cg2(mapa_u32(tf, 1));
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (warps 2..5, both CTAs) ------------------------------
+    const int q = warp & 3;
+    const int et = q * 32 + lane;
+    const int tid_e = threadIdx.x - 64;
+    constexpr int CH = 32;
+    const bool vec_ok = (p.N % 8 == 0) && (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
+                        (p.residual == nullptr ||
+                         ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
+    int ui = 0, chunk_ctr = 0;
+    for (int u = unit_begin; u < total_tiles; u += unit_step) {
+      const int m0 = (u % num_m) * TN;                                   // all TN tokens: the accumulator is 128 x TN
+      const int n0 = (u / num_m) * (2 * BM_W) + int(rank) * BM_W;
+      const int ab = NBUF == 1 ? 0 : (ui & 1);
+      const uint32_t aph = NBUF == 1 ? (ui & 1) : ((ui >> 1) & 1);
+      ++ui;
+      mbar_wait(&tmem_full_bar[ab], aph, abort_flag, p.err, 630 + ab);
+      tc_fence_after();
+      const uint32_t lane_addr = tmem_base + ab * ACC_COLS + (uint32_t(q * 32) << 16);
+      const int n = n0 + et;
+      float bias_v = 0.f;
+      if (p.bias != nullptr && n < p.N) bias_v = __bfloat162float(p.bias[n]);
+      uint8_t* staging = smem + S::TILE_BYTES;
+#pragma unroll 1
+      for (int c = 0; c < TN / CH; ++c, ++chunk_ctr) {
+        uint32_t r[CH], r2[CH];
+        tmem_ld_32x32(lane_addr + c * CH, r);
+        if (DUAL) tmem_ld_32x32(lane_addr + TN + c * CH, r2);
+        tmem_ld_wait();
+        if (c == TN / CH - 1) {
+          tc_fence_before();
+          mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty_bar[ab]), 0));   // hand the buffer back to the leader's MMA thread
+        }
+        if (p.out_f32) {
+          float* stf = reinterpret_cast<float*>(staging);
+#pragma unroll
+          for (int j = 0; j < CH; ++j) {
+            float v = __uint_as_float(r[j]) * p.out_scale;
+            if (DUAL) v = apply_act(v, p.act) * (__uint_as_float(r2[j]) * p.out_scale);
+            else v = apply_act(v + bias_v, p.act);
+            stf[j * BM_W + et] = v;
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          for (int idx = tid_e; idx < CH * 16; idx += 128) {
+            const int tok = idx >> 4, c8 = idx & 15;
+            const float4 lo = *reinterpret_cast<const float4*>(stf + tok * BM_W + c8 * 8);
+            const float4 hi = *reinterpret_cast<const float4*>(stf + tok * BM_W + c8 * 8 + 4);
+            float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+            emit8(p, m0 + c * CH + tok, p.M, n0 + c8 * 8, v, vec_ok);
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        } else {
+          __nv_bfloat16* stb = reinterpret_cast<__nv_bfloat16*>(staging + (chunk_ctr & 1) * (STAGING_BYTES / 2));
+#pragma unroll
+          for (int j = 0; j < CH; ++j) {
+            float v = __uint_as_float(r[j]) * p.out_scale;
+            if (DUAL) v = apply_act(v, p.act) * (__uint_as_float(r2[j]) * p.out_scale);
+            else v = apply_act(v + bias_v, p.act);
+            stb[j * BM_W + et] = __float2bfloat16(v);
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          for (int idx = tid_e; idx < CH * 16; idx += 128) {
+            const int tok = idx >> 4, c8 = idx & 15;
+            const uint4 raw = *reinterpret_cast<const uint4*>(stb + tok * BM_W + c8 * 8);
+            const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { v[2 * e] = bf16_lo(w[e]); v[2 * e + 1] = bf16_hi(w[e]); }
+            emit8(p, m0 + c * CH + tok, p.M, n0 + c8 * 8, v, vec_ok);
+          }
+        }
+      }
+    }
+    if (p.rs_world > 0) {
+      __threadfence_system();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (tid_e < p.rs_world) red_release_sys_add_u32(p.rs_peer_flag[tid_e], 1u);
+    }
+  }
+
+  tc_fence_before();
+  cluster_sync_all();       // nobody leaves while the peer may still touch its barriers, shared memory or TMEM
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(20000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_cg2(tmem_base, TMEM_COLS);
+  }
+}
+
+// ----------------------------------------------------------------------------
 // Host side
 // ----------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -572,7 +871,7 @@ static int num_sms() {
   return sms[dev];
 }
 
-struct GemmPlan { int tn, splits, ctas, tiles; };
+struct GemmPlan { int tn, splits, ctas, tiles; int tail_tiles, tail_splits; int pair; };
 
 static GemmPlan plan_gemm(const UbGemmArgs* a) {
   GemmPlan pl;
@@ -611,7 +910,47 @@ static GemmPlan plan_gemm(const UbGemmArgs* a) {
     return plan_gemm(&b);
   }
   pl.splits = splits;
-  pl.ctas = splits > 1 ? splits * pl.tiles : (pl.tiles < sms ? pl.tiles : sms);
+  pl.tail_tiles = 0;
+  pl.tail_splits = 1;
+  // Two-phase schedule: when the last round of a persistent launch would keep fewer than half of the SMs busy, those
+  // tiles run as a second launch with K split over clusters, so the tail costs 1/splits of a tile time.
+  if (splits == 1 && !grouped && a->tail_split != 1 && pl.tiles > sms && num_kb >= 16) {
+    const int r = pl.tiles % sms;
+    if (r > 0 && r * 2 <= sms && !(dual && tn == 256)) {
+      int ts = sms / r;
+      if (ts > 8) ts = 8;
+      while (ts & (ts - 1)) ts &= ts - 1;
+      while (ts > 1 && (ts - 1) * ((num_kb + ts - 1) / ts) >= num_kb) ts >>= 1;   // no empty K slice
+      if (ts >= 2) { pl.tail_tiles = r; pl.tail_splits = ts; }
+    }
+  }
+  const int main_tiles = pl.tiles - pl.tail_tiles;
+  pl.ctas = splits > 1 ? splits * pl.tiles : (main_tiles < sms ? main_tiles : sms) + pl.tail_tiles * pl.tail_splits;
+  // 2-CTA tiles (256 weight rows per CTA pair): for token counts that fill a wide tile and enough tiles to keep the
+  // SM pairs busy.  cta_pair: 0 auto, 1 never, 2 always (when the shape allows).
+  pl.pair = 0;
+  static int env_pair = -1;
+  if (env_pair < 0) {
+    const char* e = getenv("UB_GEMM_2CTA");
+    env_pair = e ? atoi(e) : 1;          // same meaning as cta_pair; the argument wins when it is not 0
+  }
+  const int want = a->cta_pair != 0 ? a->cta_pair : env_pair;
+  if (want != 1 && !grouped && splits == 1 && a->M >= 64 && a->N >= 2 * BM_W) {
+    int tn2 = a->tile_tokens > 0 ? a->tile_tokens : (dual ? 128 : 256);
+    if (tn2 < 64) tn2 = 64;
+    if (tn2 > 256) tn2 = 256;
+    while (tn2 > 64 && tn2 / 2 >= a->M) tn2 >>= 1;
+    const int tiles2 = ((a->M + tn2 - 1) / tn2) * ((a->N + 2 * BM_W - 1) / (2 * BM_W));
+    const bool enough = tiles2 * 4 >= (sms / 2) * 3;       // at least 3/4 of the SM pairs get a tile
+    if (want == 2 || (a->M >= 192 && enough)) {
+      pl.pair = 1;
+      pl.tn = tn2;
+      pl.tiles = tiles2;
+      pl.tail_tiles = 0;
+      pl.tail_splits = 1;
+      pl.ctas = 2 * (tiles2 < sms / 2 ? tiles2 : sms / 2);
+    }
+  }
   return pl;
 }
 
@@ -634,7 +973,7 @@ static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmP
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   if (SPLITK) {
-    cfg.gridDim = dim3(pl.splits, pl.tiles, 1);
+    cfg.gridDim = dim3(pl.splits, pl.tiles, 1);   // the caller passes a plan whose tiles/splits describe THIS launch
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = pl.splits;
     attr[0].val.clusterDim.y = 1;
@@ -646,6 +985,54 @@ static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmP
   }
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, tx, p);
   return e == cudaSuccess ? 0 : -(int)e;
+}
+
+template <int TN, int STAGES, bool DUAL>
+static int launch_gemm_2cta(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, const GemmPlan& pl,
+                            cudaStream_t stream) {
+  using S = Gemm2Smem<TN, STAGES, DUAL>;
+  static bool attr_set[UB_MAX_DEVICES] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  auto kern = gemm_tn_2cta_kernel<TN, STAGES, DUAL>;
+  if (dev < UB_MAX_DEVICES && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) return -(int)e;
+    attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.gridDim = dim3(pl.ctas, 1, 1);
+  cfg.dynamicSmemBytes = S::TOTAL;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, tx, p);
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+template <bool DUAL>
+static int dispatch_2cta(int tn, const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, const GemmPlan& pl,
+                         cudaStream_t st) {
+  if constexpr (!DUAL) {
+    switch (tn) {
+      case 64: return launch_gemm_2cta<64, 10, false>(tw, tx, p, pl, st);
+      case 128: return launch_gemm_2cta<128, 8, false>(tw, tx, p, pl, st);
+      case 256: return launch_gemm_2cta<256, 6, false>(tw, tx, p, pl, st);
+    }
+  } else {
+    switch (tn) {
+      case 64: return launch_gemm_2cta<64, 5, true>(tw, tx, p, pl, st);
+      case 128: return launch_gemm_2cta<128, 5, true>(tw, tx, p, pl, st);
+      case 256: return launch_gemm_2cta<256, 4, true>(tw, tx, p, pl, st);
+    }
+  }
+  return -4;
 }
 
 template <bool DUAL, bool SPLITK>
@@ -703,6 +1090,8 @@ extern "C" int ub_gemm_tn(const UbGemmArgs* a, void* stream_v) {
   p.out_scale = a->out_scale == 0.f ? 1.f : a->out_scale;
   p.err = a->err;
   p.splits = pl.splits;
+  p.tile_begin = 0;
+  p.tile_end = 0;
   p.grp_tiles = reinterpret_cast<const int4*>(a->grp_tiles);
   p.grp_max_tiles = a->grp_max_tiles;
   p.grp_w_rows = a->grp_w_rows;
@@ -720,12 +1109,34 @@ extern "C" int ub_gemm_tn(const UbGemmArgs* a, void* stream_v) {
   const long long w_rows = (dual || a->grp_tiles != nullptr) ? (long long)a->w_rows_total : (long long)a->N;
   int rc = make_tmap_bf16_2d(&tw, a->w, w_rows, a->K, a->ldw, BM_W, BK);
   if (rc != 0) return rc;
-  rc = make_tmap_bf16_2d(&tx, a->x, a->M, a->K, a->ldx, pl.tn, BK);
+  rc = make_tmap_bf16_2d(&tx, a->x, a->M, a->K, a->ldx, pl.pair ? pl.tn / 2 : pl.tn, BK);
   if (rc != 0) return rc;
+  if (pl.pair) return dual ? dispatch_2cta<true>(pl.tn, tw, tx, p, pl, stream) : dispatch_2cta<false>(pl.tn, tw, tx, p, pl, stream);
   if (pl.splits > 1) {
     return dual ? dispatch_tn<true, true>(pl.tn, tw, tx, p, pl, stream)
                 : dispatch_tn<false, true>(pl.tn, tw, tx, p, pl, stream);
   }
-  return dual ? dispatch_tn<true, false>(pl.tn, tw, tx, p, pl, stream)
-              : dispatch_tn<false, false>(pl.tn, tw, tx, p, pl, stream);
+  if (pl.tail_tiles == 0) {
+    return dual ? dispatch_tn<true, false>(pl.tn, tw, tx, p, pl, stream)
+                : dispatch_tn<false, false>(pl.tn, tw, tx, p, pl, stream);
+  }
+  // phase 1: full rounds, persistent
+  GemmPlan main_pl = pl;
+  main_pl.tiles = pl.tiles - pl.tail_tiles;
+  const int sms = num_sms();
+  main_pl.ctas = main_pl.tiles < sms ? main_pl.tiles : sms;
+  p.tile_begin = 0;
+  p.tile_end = main_pl.tiles;
+  rc = dual ? dispatch_tn<true, false>(pl.tn, tw, tx, p, main_pl, stream)
+            : dispatch_tn<false, false>(pl.tn, tw, tx, p, main_pl, stream);
+  if (rc != 0) return rc;
+  // phase 2: the leftover tiles, K split over clusters
+  GemmPlan tail_pl = pl;
+  tail_pl.tiles = pl.tail_tiles;
+  tail_pl.splits = pl.tail_splits;
+  p.tile_begin = main_pl.tiles;
+  p.tile_end = pl.tiles;
+  p.splits = pl.tail_splits;
+  return dual ? dispatch_tn<true, true>(pl.tn, tw, tx, p, tail_pl, stream)
+              : dispatch_tn<false, true>(pl.tn, tw, tx, p, tail_pl, stream);
 }

@@ -333,3 +333,31 @@ def test_attn_prefill_tensor_core_path(Hq, Hkv, causal):
         ro, _ = ref_attention(qkv[qs[i]:qs[i + 1], :Hq].cpu(), dk[i], dv[i], causal_offset=(kl - ql) if causal else None)
         _close(out2[qs[i]:qs[i + 1]], ro)
     cuda_ops.check_device_errors()
+
+
+@pytest.mark.parametrize("M,N,K,tile", [(256, 512, 512, 256), (512, 1024, 1024, 256), (300, 520, 264, 128), (1000, 2048, 4096, 256),
+                                        (128, 768, 1024, 64), (640, 4096, 4096, 0)])
+def test_gemm_2cta_pairs(M, N, K, tile):
+    """cta_group::2 kernel: tiles of 256 weight rows on CTA pairs; ragged M / N / K edges, several token tiles."""
+    from unillm_b200.ops import cuda_ops
+
+    x, w = _rand(M, K, seed=21), _rand(N, K, scale=1 / math.sqrt(K), seed=22)
+    out = cuda_ops.gemm_tn(x, w, tile_tokens=tile, cta_pair=2)
+    _close(out, x.float() @ w.float().t())
+    bias, res = _rand(N, seed=23), _rand(M, N, seed=24)
+    out2 = cuda_ops.gemm_tn(x, w, bias=bias, residual=res, act="gelu", tile_tokens=tile, cta_pair=2)
+    ref2 = torch.nn.functional.gelu(x.float() @ w.float().t() + bias.float()) + res.float()
+    _close(out2, ref2)
+    out3 = cuda_ops.gemm_tn(x, w, tile_tokens=tile, cta_pair=2, out_dtype=torch.float32)
+    _close(out3, x.float() @ w.float().t())
+    assert torch.equal(cuda_ops.gemm_tn(x, w, tile_tokens=tile, cta_pair=2), out)      # deterministic
+
+
+@pytest.mark.parametrize("M,I,K,tile", [(256, 512, 1024, 128), (500, 1408, 2048, 128), (512, 1024, 1024, 256), (200, 768, 512, 64)])
+def test_gemm_2cta_dual(M, I, K, tile):
+    from unillm_b200.ops import cuda_ops
+
+    x, w = _rand(M, K, seed=31), _rand(2 * I, K, scale=1 / math.sqrt(K), seed=32)
+    out = cuda_ops.gemm_tn(x, w, dual_rows=I, act="silu", tile_tokens=tile, cta_pair=2)
+    g, u = x.float() @ w[:I].float().t(), x.float() @ w[I:].float().t()
+    _close(out, torch.nn.functional.silu(g) * u)

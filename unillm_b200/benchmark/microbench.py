@@ -53,7 +53,7 @@ def time_ms(fn, iters=10, warmup=3, flush=True):
     return ts[len(ts) // 2], ts[0]
 
 
-def bench_gemm(results, only=None, tile=0):
+def bench_gemm(results, only=None, tile=0, pair=0):
     hbm, tf, how = _peaks()
     shapes = [only] if only else [
         # (M, N, K, dual) : Llama-3-8B decode / prefill shapes
@@ -69,7 +69,7 @@ def bench_gemm(results, only=None, tile=0):
         x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
         w = torch.randn(N * (2 if dual else 1), K, device="cuda", dtype=torch.bfloat16) * 0.02
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-        fn = (lambda: cuda_ops.gemm_tn(x, w, dual_rows=N, act="silu", out=out, tile_tokens=tile)) if dual else (lambda: cuda_ops.gemm_tn(x, w, out=out, tile_tokens=tile))
+        fn = (lambda: cuda_ops.gemm_tn(x, w, dual_rows=N, act="silu", out=out, tile_tokens=tile, cta_pair=pair)) if dual else (lambda: cuda_ops.gemm_tn(x, w, out=out, tile_tokens=tile, cta_pair=pair))
         med, best = time_ms(fn)
         flops = 2.0 * M * N * K * (2 if dual else 1)
         byts = 2.0 * (w.numel() + x.numel() + out.numel())
@@ -82,9 +82,10 @@ def bench_gemm(results, only=None, tile=0):
         print(json.dumps(r))
 
 
-def bench_attn(results):
+def bench_attn(results, case="all"):
     hbm, tf, how = _peaks()
-    for B, ctx, Hq, Hkv, D in [(256, 1152, 32, 8, 128), (64, 4096, 32, 8, 128), (256, 1152, 4, 1, 128), (8, 4096, 8, 1, 128)]:
+    decode_cases = [(256, 1152, 32, 8, 128), (64, 4096, 32, 8, 128), (256, 1152, 4, 1, 128), (8, 4096, 8, 1, 128)]
+    for B, ctx, Hq, Hkv, D in (decode_cases if case in ("all", "decode") else []):
         bs = 16
         nblk = B * ((ctx + bs - 1) // bs)
         kc = torch.randn(nblk, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
@@ -107,8 +108,9 @@ def bench_attn(results):
                  frac_hbm=byts / med / 1e6 / hbm, path=cuda_ops.attn_prefill_last_path(), peaks=how)
         results.append(r)
         print(json.dumps(r))
-    for T, ctx, Hq, Hkv, D, causal in [(2048, 2048, 32, 8, 128, True), (8192, 8192, 4, 1, 128, True),
-                                       (256, 1024, 32, 8, 128, False), (512, 1024, 32, 8, 128, False)]:
+    prefill_cases = [(2048, 2048, 32, 8, 128, True), (8192, 8192, 4, 1, 128, True), (256, 1024, 32, 8, 128, False),
+                     (512, 1024, 32, 8, 128, False)]
+    for T, ctx, Hq, Hkv, D, causal in (prefill_cases if case in ("all", "prefill") else []):
         bs = 16
         nblk = (ctx + bs - 1) // bs
         kc = torch.randn(nblk, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
@@ -145,15 +147,17 @@ def bench_norm(results):
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("what", nargs="?", default="all", choices=["gemm", "attn", "norm", "all"])
+    ap.add_argument("--attn-case", default="all", choices=["all", "decode", "prefill"], help="subset of the attention shapes")
     ap.add_argument("--json", default=None)
     ap.add_argument("--shape", default=None, help="gemm only: M,N,K,dual -- run just this shape")
     ap.add_argument("--tile", type=int, default=0, help="gemm only: force the token-tile width")
+    ap.add_argument("--pair", type=int, default=0, help="gemm only: 0 auto, 1 never, 2 always use the 2-CTA kernel")
     a = ap.parse_args(argv)
     results = []
     if a.what in ("gemm", "all"):
-        bench_gemm(results, tuple(int(v) for v in a.shape.split(",")) if a.shape else None, a.tile)
+        bench_gemm(results, tuple(int(v) for v in a.shape.split(",")) if a.shape else None, a.tile, a.pair)
     if a.what in ("attn", "all"):
-        bench_attn(results)
+        bench_attn(results, a.attn_case)
     if a.what in ("norm", "all"):
         bench_norm(results)
     if a.json:

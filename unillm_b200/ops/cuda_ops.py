@@ -66,7 +66,7 @@ def gemm_tn(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = 
             residual: Optional[torch.Tensor] = None, act: Optional[str] = None, out: Optional[torch.Tensor] = None,
             out_dtype: torch.dtype = torch.bfloat16, out_scale: float = 1.0, tile_tokens: int = 0, splits: int = 0,
             dual_rows: int = 0, rs: Optional[dict] = None, ag: Optional[dict] = None,
-            grouped: Optional[dict] = None) -> torch.Tensor:
+            grouped: Optional[dict] = None, cta_pair: int = 0) -> torch.Tensor:
     """``out[M, N] = act(x[M, K] @ w[N, K]^T * out_scale + bias) + residual`` on tcgen05 tensor cores.
 
     ``dual_rows = I`` switches to the gated form: ``w`` is ``[2*I, K]`` with gate rows first and the
@@ -106,6 +106,7 @@ def gemm_tn(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = 
     a.out_scale = out_scale
     a.tile_tokens = tile_tokens
     a.splits = splits
+    a.cta_pair = cta_pair
     if bias is not None:
         _bf16c(bias, "bias")
     if residual is not None:
@@ -125,10 +126,10 @@ def gemm_tn(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = 
     return out
 
 
-def gemm_num_ctas(M: int, N: int, K: int, dual: bool = False, tile_tokens: int = 0, splits: int = 0) -> int:
+def gemm_num_ctas(M: int, N: int, K: int, dual: bool = False, tile_tokens: int = 0, splits: int = 0, cta_pair: int = 0) -> int:
     """CTAs that ``gemm_tn`` launches for this problem (each signals every peer once in reduce-scatter mode)."""
     a = N_.UbGemmArgs()
-    a.M, a.N, a.K, a.dual, a.tile_tokens, a.splits = M, N, K, int(dual), tile_tokens, splits
+    a.M, a.N, a.K, a.dual, a.tile_tokens, a.splits, a.cta_pair = M, N, K, int(dual), tile_tokens, splits, cta_pair
     return N_.cuda_lib().ub_gemm_num_ctas(C.byref(a))
 
 
