@@ -65,6 +65,7 @@ struct GemmParams {
   int grp_max_tiles;  // token-tile slots in the table
   int grp_w_rows;     // rows of w per expert; expert e's weights are rows [e*grp_w_rows, (e+1)*grp_w_rows)
   int tile_begin, tile_end;   // work units of this launch; tile_end == 0 means all
+  int dbg;                    // UB_GEMM_DEBUG bits: 1 = no L2 prefetch, 2 = no L2 cache hints
 };
 
 // Coordinates of work unit u.  m0/m_end: token rows; nw: row of the weight tile in w; no: first output feature.
@@ -85,7 +86,12 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int u, int 
 
 __device__ __forceinline__ float apply_act(float v, int act) {
   switch (act) {
-    case UB_ACT_SILU: return v / (1.f + __expf(-v));
+    case UB_ACT_SILU: {
+      // v * sigmoid(v) with sigmoid(v) = 0.5 * (1 + tanh(v / 2)): one MUFU instruction, no division
+      float t;
+      asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * v));
+      return v * fmaf(0.5f, t, 0.5f);
+    }
     case UB_ACT_GELU: return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
     case UB_ACT_GELU_TANH: {
       float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
@@ -97,6 +103,34 @@ __device__ __forceinline__ float apply_act(float v, int act) {
     case UB_ACT_SIGMOID: return 1.f / (1.f + __expf(-v));
     case UB_ACT_TANH: return tanhf(v);
     default: return v;
+  }
+}
+
+// The activation is chosen ONCE per chunk of accumulator values: a switch inside the per-value loop makes the
+// compiler evaluate every branch (erf, tanh, exp ...) for every value, which dominated the epilogue.
+template <int N, bool DUAL, int ACT>
+__device__ __forceinline__ void epi_values_t(uint32_t (&r)[N], const uint32_t (&r2)[N], float scale, float bias_v) {
+#pragma unroll
+  for (int j = 0; j < N; ++j) {
+    float v = __uint_as_float(r[j]) * scale;
+    if (DUAL) v = apply_act(v, ACT) * (__uint_as_float(r2[j]) * scale);
+    else v = apply_act(v + bias_v, ACT);
+    r[j] = __float_as_uint(v);
+  }
+}
+template <int N, bool DUAL>
+__device__ __forceinline__ void epi_values(uint32_t (&r)[N], const uint32_t (&r2)[N], float scale, float bias_v, int act) {
+  switch (act) {
+    case UB_ACT_NONE: epi_values_t<N, DUAL, UB_ACT_NONE>(r, r2, scale, bias_v); break;
+    case UB_ACT_SILU: epi_values_t<N, DUAL, UB_ACT_SILU>(r, r2, scale, bias_v); break;
+    case UB_ACT_GELU: epi_values_t<N, DUAL, UB_ACT_GELU>(r, r2, scale, bias_v); break;
+    case UB_ACT_GELU_TANH: epi_values_t<N, DUAL, UB_ACT_GELU_TANH>(r, r2, scale, bias_v); break;
+    case UB_ACT_RELU: epi_values_t<N, DUAL, UB_ACT_RELU>(r, r2, scale, bias_v); break;
+    case UB_ACT_RELU2: epi_values_t<N, DUAL, UB_ACT_RELU2>(r, r2, scale, bias_v); break;
+    case UB_ACT_QUICK_GELU: epi_values_t<N, DUAL, UB_ACT_QUICK_GELU>(r, r2, scale, bias_v); break;
+    case UB_ACT_SIGMOID: epi_values_t<N, DUAL, UB_ACT_SIGMOID>(r, r2, scale, bias_v); break;
+    case UB_ACT_TANH: epi_values_t<N, DUAL, UB_ACT_TANH>(r, r2, scale, bias_v); break;
+    default: epi_values_t<N, DUAL, UB_ACT_NONE>(r, r2, scale, bias_v); break;
   }
 }
 
@@ -287,7 +321,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
           // Weights come from HBM (about 2 us away under load) while the few smem stages cover far less
           // time than that: ask L2 for the weight tile PF k-blocks ahead, so the smem copies hit in L2.
           for (; pf_issued < it + PF + 1; ++pf_issued) {
-            if (pf_u >= total_tiles) break;
+            if (pf_u >= total_tiles || (p.dbg & 1)) break;
             if (pf_kb == kb0) {
               const TileCoord pc = tile_coord(p, pf_u, num_m, TN);
               pf_valid = pc.valid;
@@ -303,9 +337,15 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err, 100 + s)) { dead = true; break; }
           uint8_t* st = smem + s * S::STAGE_BYTES;
           mbar_arrive_expect_tx(&full_bar[s], S::STAGE_BYTES);
-          tma_load_2d_hint(st, &tmap_w, &full_bar[s], kb * BK, n0, pol_w);
-          if (DUAL) tma_load_2d_hint(st + S::A_BYTES, &tmap_w, &full_bar[s], kb * BK, n0 + p.up_row_off, pol_w);
-          tma_load_2d_hint(st + (DUAL ? 2 : 1) * S::A_BYTES, &tmap_x, &full_bar[s], kb * BK, m0, pol_x);
+          if (p.dbg & 2) {
+            tma_load_2d(st, &tmap_w, &full_bar[s], kb * BK, n0);
+            if (DUAL) tma_load_2d(st + S::A_BYTES, &tmap_w, &full_bar[s], kb * BK, n0 + p.up_row_off);
+            tma_load_2d(st + (DUAL ? 2 : 1) * S::A_BYTES, &tmap_x, &full_bar[s], kb * BK, m0);
+          } else {
+            tma_load_2d_hint(st, &tmap_w, &full_bar[s], kb * BK, n0, pol_w);
+            if (DUAL) tma_load_2d_hint(st + S::A_BYTES, &tmap_w, &full_bar[s], kb * BK, n0 + p.up_row_off, pol_w);
+            tma_load_2d_hint(st + (DUAL ? 2 : 1) * S::A_BYTES, &tmap_x, &full_bar[s], kb * BK, m0, pol_x);
+          }
         }
       }
     }
@@ -407,14 +447,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             tc_fence_before();
             mbar_arrive(&tmem_empty_bar[ab]);
           }
+          epi_values<CH, DUAL>(r, r2, p.out_scale, bias_v, p.act);
           if (p.out_f32) {
             float* stf = reinterpret_cast<float*>(staging);
 #pragma unroll
             for (int j = 0; j < CH; ++j) {
-              float v = __uint_as_float(r[j]) * p.out_scale;
-              if (DUAL) v = apply_act(v, p.act) * (__uint_as_float(r2[j]) * p.out_scale);
-              else v = apply_act(v + bias_v, p.act);
-              stf[j * BM_W + et] = v;
+              stf[j * BM_W + et] = __uint_as_float(r[j]);
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
             for (int idx = tid_e; idx < CH * 16; idx += 128) {
@@ -429,10 +467,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             __nv_bfloat16* stb = reinterpret_cast<__nv_bfloat16*>(staging + (chunk_ctr & 1) * (STAGING_BYTES / 2));
 #pragma unroll
             for (int j = 0; j < CH; ++j) {
-              float v = __uint_as_float(r[j]) * p.out_scale;
-              if (DUAL) v = apply_act(v, p.act) * (__uint_as_float(r2[j]) * p.out_scale);
-              else v = apply_act(v + bias_v, p.act);
-              stb[j * BM_W + et] = __float2bfloat16(v);
+              stb[j * BM_W + et] = __float2bfloat16(__uint_as_float(r[j]));
             }
             // One barrier per chunk: the two staging halves alternate, so the writers of chunk c+2
             // have all passed the barrier of chunk c+1, i.e. finished reading chunk c.
@@ -487,18 +522,18 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
           }
         }
         const int nn = n0 + c8 * 8;
-        float v[8];
+        uint32_t gv[8], uv[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          float x = g[e] * p.out_scale;
-          if (DUAL) {
-            x = apply_act(x, p.act) * (up[e] * p.out_scale);
-          } else {
-            if (p.bias != nullptr && nn + e < p.N) x += __bfloat162float(p.bias[nn + e]);
-            x = apply_act(x, p.act);
-          }
-          v[e] = x;
+          float x = g[e];
+          if (!DUAL && p.bias != nullptr && nn + e < p.N) x += __bfloat162float(p.bias[nn + e]) / p.out_scale;
+          gv[e] = __float_as_uint(x);
+          uv[e] = __float_as_uint(up[e]);
         }
+        epi_values<8, DUAL>(gv, uv, p.out_scale, 0.f, p.act);
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(gv[e]);
         emit8(p, m0 + tok, p.M, nn, v, vec_ok);
       }
       if (p.rs_world > 0) {
@@ -760,14 +795,12 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           tc_fence_before();
           mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty_bar[ab]), 0));   // hand the buffer back to the leader's MMA thread
         }
+        epi_values<CH, DUAL>(r, r2, p.out_scale, bias_v, p.act);
         if (p.out_f32) {
           float* stf = reinterpret_cast<float*>(staging);
 #pragma unroll
           for (int j = 0; j < CH; ++j) {
-            float v = __uint_as_float(r[j]) * p.out_scale;
-            if (DUAL) v = apply_act(v, p.act) * (__uint_as_float(r2[j]) * p.out_scale);
-            else v = apply_act(v + bias_v, p.act);
-            stf[j * BM_W + et] = v;
+            stf[j * BM_W + et] = __uint_as_float(r[j]);
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
           for (int idx = tid_e; idx < CH * 16; idx += 128) {
@@ -782,10 +815,7 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           __nv_bfloat16* stb = reinterpret_cast<__nv_bfloat16*>(staging + (chunk_ctr & 1) * (STAGING_BYTES / 2));
 #pragma unroll
           for (int j = 0; j < CH; ++j) {
-            float v = __uint_as_float(r[j]) * p.out_scale;
-            if (DUAL) v = apply_act(v, p.act) * (__uint_as_float(r2[j]) * p.out_scale);
-            else v = apply_act(v + bias_v, p.act);
-            stb[j * BM_W + et] = __float2bfloat16(v);
+            stb[j * BM_W + et] = __float2bfloat16(__uint_as_float(r[j]));
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
           for (int idx = tid_e; idx < CH * 16; idx += 128) {
@@ -1092,6 +1122,11 @@ extern "C" int ub_gemm_tn(const UbGemmArgs* a, void* stream_v) {
   p.splits = pl.splits;
   p.tile_begin = 0;
   p.tile_end = 0;
+  {
+    static int dbg = -1;
+    if (dbg < 0) { const char* e = getenv("UB_GEMM_DEBUG"); dbg = e ? atoi(e) : 0; }
+    p.dbg = dbg;
+  }
   p.grp_tiles = reinterpret_cast<const int4*>(a->grp_tiles);
   p.grp_max_tiles = a->grp_max_tiles;
   p.grp_w_rows = a->grp_w_rows;
