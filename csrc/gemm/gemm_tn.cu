@@ -962,17 +962,19 @@ static GemmPlan plan_gemm(const UbGemmArgs* a) {
   static int env_pair = -1;
   if (env_pair < 0) {
     const char* e = getenv("UB_GEMM_2CTA");
-    env_pair = e ? atoi(e) : 1;          // same meaning as cta_pair; the argument wins when it is not 0
+    env_pair = e ? atoi(e) : 0;          // same meaning as cta_pair; the argument wins when it is not 0
   }
   const int want = a->cta_pair != 0 ? a->cta_pair : env_pair;
   if (want != 1 && !grouped && splits == 1 && a->M >= 64 && a->N >= 2 * BM_W) {
-    int tn2 = a->tile_tokens > 0 ? a->tile_tokens : (dual ? 128 : 256);
+    int tn2 = a->tile_tokens > 0 ? a->tile_tokens : 256;
     if (tn2 < 64) tn2 = 64;
     if (tn2 > 256) tn2 = 256;
     while (tn2 > 64 && tn2 / 2 >= a->M) tn2 >>= 1;
     const int tiles2 = ((a->M + tn2 - 1) / tn2) * ((a->N + 2 * BM_W - 1) / (2 * BM_W));
     const bool enough = tiles2 * 4 >= (sms / 2) * 3;       // at least 3/4 of the SM pairs get a tile
-    if (want == 2 || (a->M >= 192 && enough)) {
+    // measured: gated GEMMs gain from 256 tokens up (they beat the 1-CTA kernel by 15-20 %), plain ones from ~1024
+    const bool gains = dual ? a->M >= 256 : a->M >= 1024;
+    if (want == 2 || (gains && enough && a->tile_tokens <= 0)) {
       pl.pair = 1;
       pl.tn = tn2;
       pl.tiles = tiles2;

@@ -58,6 +58,9 @@ def test_gemm_rs_norm_ag_gemm_chain_emulated(world, T):
         ys = []
         for r, c in enumerate(comms):
             ys.append(K.gemm_tn(c.ag_local_tensor(1, T), wup[r * I:(r + 1) * I].contiguous(), ag=c.gemm_ag(1, R)))
+        # the gated GEMM waits on the same counters (for >= 256 tokens it runs on CTA pairs)
+        wgu = _rand(2 * 256, H, scale=1 / math.sqrt(H), seed=6)
+        act = K.gemm_tn(comms[0].ag_local_tensor(1, T), wgu, dual_rows=256, act="silu", ag=comms[0].gemm_ag(1, R))
         # a second norm kernel (the "next layer" one) resets the counters used above, as in the layer pipeline
         for r, c in enumerate(comms):
             K.norm(new_res[r], ln, eps=1e-5, T=R, reset=c.reset_after_ag(0))
@@ -71,6 +74,9 @@ def test_gemm_rs_norm_ag_gemm_chain_emulated(world, T):
         yref = hn.to(torch.bfloat16).float() @ wup.float().t()
         ygot = torch.cat(ys, dim=1).float()
         assert (ygot - yref).abs().max().item() < 0.05 * max(1.0, yref.abs().max().item())
+        hb = hn.to(torch.bfloat16).float()
+        aref = torch.nn.functional.silu(hb @ wgu[:256].float().t()) * (hb @ wgu[256:].float().t())
+        assert (act.float() - aref.cuda()).abs().max().item() < 0.05 * max(1.0, aref.abs().max().item())
         for c in comms:   # counters of the other phase were zeroed
             flags = c.buf[c.flags.offset:c.flags.offset + 256].view(torch.int32)
             assert int(flags[16:25].abs().sum()) == 0
