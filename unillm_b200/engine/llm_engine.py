@@ -218,19 +218,19 @@ class LLMEngine:
         """Returns the packed step and, per scheduled sequence, (sequence, tokens this step, samples?)."""
         bs = self.block_size
         decode: List[Sequence] = []
+        # membership in self.running is the same thing as status == RUNNING (preemption flips the status)
         for s in list(self.running):
             if s.status != RUNNING or not s.prefill_done:
-                continue
-            if s not in self.running:
-                continue                      # preempted while making room for an earlier one
+                continue                      # includes sequences preempted while making room for an earlier one
             if not self._ensure_blocks(s, s.total_len):
                 continue
             decode.append(s)
-        decode = [s for s in decode if s in self.running]
+        decode = [s for s in decode if s.status == RUNNING]
+        in_decode = {id(s) for s in decode}
         budget = self.max_tokens - len(decode)
         chunks: List[Tuple[Sequence, int]] = []
         for s in list(self.running):
-            if s not in self.running or s.prefill_done or s in decode or budget <= 0:
+            if s.status != RUNNING or budget <= 0 or id(s) in in_decode or s.prefill_done:
                 continue
             left = s.total_len - s.num_computed
             n = min(left, budget) if self.chunked else left
@@ -240,8 +240,8 @@ class LLMEngine:
                 chunks.append((s, n))
                 budget -= n
         # making room may have preempted sequences that were already picked above
-        decode = [s for s in decode if s in self.running]
-        chunks = [(s, n) for s, n in chunks if s in self.running]
+        decode = [s for s in decode if s.status == RUNNING]
+        chunks = [(s, n) for s, n in chunks if s.status == RUNNING]
         budget = self.max_tokens - len(decode) - sum(n for _, n in chunks)
         # from here on nothing is preempted, so blocks filled by this step can be published now
         for s, n in chunks:
@@ -275,22 +275,25 @@ class LLMEngine:
         tables: List[List[int]] = []
         sample_rows: List[int] = []
         plan: List[Tuple[Sequence, int, bool]] = []
-        for s in decode:
-            p = s.total_len - 1
-            token_ids.append(s.output_ids[-1])
-            positions.append(p)
-            slots.append(s.blocks[p // bs] * bs + p % bs)
-            seq_lens.append(p + 1)
-            tables.append(s.blocks)
-            sample_rows.append(len(token_ids) - 1)
-            plan.append((s, 1, True))
+        if decode:
+            positions = [len(s.prompt_ids) + len(s.output_ids) - 1 for s in decode]
+            token_ids = [s.output_ids[-1] for s in decode]
+            slots = [s.blocks[p // bs] * bs + p % bs for s, p in zip(decode, positions)]
+            seq_lens = [p + 1 for p in positions]
+            tables = [s.blocks for s in decode]
+            sample_rows = list(range(len(decode)))
+            plan = [(s, 1, True) for s in decode]
         q_lens: List[int] = []
         for s, n in chunks:
-            toks = s.tokens
-            for p in range(s.num_computed, s.num_computed + n):
-                token_ids.append(toks[p])
-                positions.append(p)
-                slots.append(s.blocks[p // bs] * bs + p % bs)
+            a, b = s.num_computed, s.num_computed + n
+            npr = len(s.prompt_ids)
+            if b <= npr:
+                token_ids.extend(s.prompt_ids[a:b])
+            else:
+                token_ids.extend(s.tokens[a:b])
+            positions.extend(range(a, b))
+            blk = s.blocks
+            slots.extend([blk[p // bs] * bs + p % bs for p in range(a, b)])
             seq_lens.append(s.num_computed + n)
             tables.append(s.blocks)
             q_lens.append(n)

@@ -10,6 +10,7 @@ on top of it and additionally exports block tables.  ``KvPage`` / ``KvBlock`` / 
 from __future__ import annotations
 
 import ctypes as C
+from array import array
 import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
@@ -120,7 +121,9 @@ class RadixTree:
 
     @staticmethod
     def _arr(tokens: Sequence[int]):
-        return (C.c_int32 * len(tokens))(*tokens)
+        # array('i') builds at C speed; the ctypes view shares its buffer (no per-element Python calls)
+        a = array("i", tokens)
+        return (C.c_int32 * len(a)).from_buffer(a)
 
     def match_prefix(self, tokens: Sequence[int]) -> Tuple[List[int], int]:
         """Longest cached prefix in whole blocks -> (block ids, node handle to lock)."""
