@@ -107,6 +107,7 @@ class LLMEngine:
         self._next_id = 0
         self.stats = EngineStats()
         self.step_events = None     # optional (start, end) CUDA events recorded around the runner launch
+        self.tracer = None          # optional unillm_b200.utils.Tracer: spans around schedule / launch / fetch / process
 
     # ------------------------------------------------------------------------------------------
     def add_request(self, prompt_ids: Sequence[int], params: Optional[SamplingParams] = None, priority: int = 0,
@@ -340,7 +341,18 @@ class LLMEngine:
     # stepping
     # ------------------------------------------------------------------------------------------
     def step(self) -> List[StepOutput]:
-        batch, plan = self.schedule()
+        tr = self.tracer
+        if tr is None:
+            return self._step()
+        with tr.span("engine.step"):
+            return self._step(tr)
+
+    def _step(self, tr=None) -> List[StepOutput]:
+        if tr is not None:
+            with tr.span("engine.schedule"):
+                batch, plan = self.schedule()
+        else:
+            batch, plan = self.schedule()
         if batch is None:
             if self.waiting and not self.running:
                 raise MemoryError_("a waiting request does not fit in the KV cache even when it is empty")
@@ -348,9 +360,18 @@ class LLMEngine:
         ev = self.step_events
         if ev is not None:
             ev[0].record()
-        self.runner.launch(batch)
+        if tr is not None:
+            with tr.span("engine.launch", tokens=len(batch.token_ids), decode=batch.num_decode):
+                self.runner.launch(batch)
+        else:
+            self.runner.launch(batch)
         if ev is not None:
             ev[1].record()
+        if tr is not None:
+            with tr.span("engine.fetch"):
+                ids = self.runner.fetch()
+            with tr.span("engine.process"):
+                return self._process(plan, ids)
         ids = self.runner.fetch()
         return self._process(plan, ids)
 
