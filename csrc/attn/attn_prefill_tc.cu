@@ -62,6 +62,7 @@ struct Params {
   long long o_stride;
   float scale_log2;
   int causal;
+  int kv_start;     // first key position to attend (suffix pass after a shared prefix); 0 = all
 };
 
 __global__ void __launch_bounds__(192, 1)
@@ -94,7 +95,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   const int t_last = min(t0 + TOK, q_end) - 1;
   int kv_hi = p.causal ? min(kv_len, kv_len - q_len + (t_last - q_begin) + 1) : kv_len;
   if (kv_hi < 0) kv_hi = 0;
-  const int n_tiles = (kv_hi + BN - 1) / BN;
+  const int kv_lo = max(p.kv_start, 0);
+  const int tile0 = kv_lo / BN;                             // first KV tile that holds a visible key
+  const int n_tiles = kv_hi > kv_lo ? (kv_hi + BN - 1) / BN - tile0 : 0;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -139,7 +142,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         if (!mbar_wait(&k_empty[s], ph ^ 1, abort_flag, p.err, 500 + s)) { dead = true; break; }
         mbar_arrive_expect_tx(&k_full[s], TILE_BYTES);
         for (int pg = 0; pg < BN / PAGE; ++pg) {
-          const int pi = j * (BN / PAGE) + pg;
+          const int pi = (tile0 + j) * (BN / PAGE) + pg;
           int blk = (pi < pages_valid && pi < p.max_blocks_per_seq) ? bt[pi] : 0;   // pages past the end: any finite page
           if (blk < 0 || blk >= p.num_blocks) { set_err(p.err, ERR_BOUNDS, blk); blk = 0; }
           const int row = (blk * p.Hkv + kh) * PAGE;
@@ -151,7 +154,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         if (!mbar_wait(&v_empty[s], ph ^ 1, abort_flag, p.err, 510 + s)) { dead = true; break; }
         mbar_arrive_expect_tx(&v_full[s], TILE_BYTES);
         for (int pg = 0; pg < BN / PAGE; ++pg) {
-          const int pi = j * (BN / PAGE) + pg;
+          const int pi = (tile0 + j) * (BN / PAGE) + pg;
           int blk = (pi < pages_valid && pi < p.max_blocks_per_seq) ? bt[pi] : 0;
           if (blk < 0 || blk >= p.num_blocks) blk = 0;
           const int row = (blk * p.Hkv + kh) * PAGE;
@@ -235,7 +238,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       if (!mbar_wait(&s_full[b], (j >> 1) & 1, abort_flag, p.err, 530)) { ok = false; break; }
       tc_fence_after();
       const uint32_t s_addr = tmem_s + b * BN + lane_off;
-      const int key0 = j * BN;
+      const int key0 = (tile0 + j) * BN;
       // pass 1: row maximum
       float mx = -CUDART_INF_F;
 #pragma unroll 1
@@ -245,7 +248,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i)
-          if (key0 + c * 32 + i < limit) mx = fmaxf(mx, __uint_as_float(r[i]));
+          if (key0 + c * 32 + i < limit && key0 + c * 32 + i >= kv_lo) mx = fmaxf(mx, __uint_as_float(r[i]));
       }
       const float m_new = fmaxf(m, mx * p.scale_log2);
       const float alpha = (m == -CUDART_INF_F) ? 0.f : exp2f(m - m_new);
@@ -261,8 +264,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const int k0 = key0 + c * 32 + 2 * i;
-          float p0 = (k0 < limit) ? exp2f(__uint_as_float(r[2 * i]) * p.scale_log2 - m_use) : 0.f;
-          float p1 = (k0 + 1 < limit) ? exp2f(__uint_as_float(r[2 * i + 1]) * p.scale_log2 - m_use) : 0.f;
+          float p0 = (k0 < limit && k0 >= kv_lo) ? exp2f(__uint_as_float(r[2 * i]) * p.scale_log2 - m_use) : 0.f;
+          float p1 = (k0 + 1 < limit && k0 + 1 >= kv_lo) ? exp2f(__uint_as_float(r[2 * i + 1]) * p.scale_log2 - m_use) : 0.f;
           // the MMA sees the rounded values: sum what it sees
           const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
           packed[i] = *reinterpret_cast<const uint32_t*>(&pb);
@@ -355,7 +358,7 @@ static int encode(CUtensorMap* out, const void* base, int rank, const cuuint64_t
 
 // 1 when the tensor-core kernel can run this problem.
 extern "C" int ub_attn_prefill_tc_supported(const UbAttnArgs* a) {
-  if (a->D != 128 || a->block_size != 16 || a->window > 0 || a->alibi_slopes != nullptr || a->kv_start != 0) return 0;
+  if (a->D != 128 || a->block_size != 16 || a->window > 0 || a->alibi_slopes != nullptr) return 0;
   if (a->Hkv <= 0 || a->Hq % a->Hkv != 0) return 0;
   const int G = a->Hq / a->Hkv;
   if (G > 128 || 128 % G != 0) return 0;
@@ -406,6 +409,7 @@ extern "C" int ub_attn_prefill_tc(const UbAttnArgs* a, void* stream_v) {
   p.o_stride = a->o_stride;
   p.scale_log2 = a->scale * LOG2E;
   p.causal = a->causal;
+  p.kv_start = a->kv_start;
   static bool attr_set[UB_MAX_DEVICES] = {};
   int dev = 0;
   cudaGetDevice(&dev);

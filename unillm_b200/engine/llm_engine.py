@@ -303,10 +303,14 @@ class LLMEngine:
                 sample_rows.append(len(token_ids) - 1)
             plan.append((s, n, done))
         shared = self._shared_prefix(decode) if len(decode) >= 8 else 0
+        # prefill chunks can join the shared-prefix pass when they start at or after the prefix and reuse its blocks
+        nshared = shared // bs
+        pfx_ok = bool(chunks) and shared > 0 and all(
+            s.num_computed >= shared and s.blocks[:nshared] == decode[0].blocks[:nshared] for s, _ in chunks)
         sampled = [s for s, _, smp in plan if smp]
         greedy = all(s.params.greedy for s in sampled)
         batch = StepBatch(token_ids, positions, slots, len(decode), seq_lens, tables, q_lens, sample_rows, shared,
-                          seed=self.seed, step=self.stats.steps)
+                          prefill_shares_prefix=pfx_ok, seed=self.seed, step=self.stats.steps)
         if not greedy:
             batch.temperature = [s.params.temperature for s in sampled]
             batch.top_p = [s.params.top_p for s in sampled]

@@ -52,6 +52,7 @@ class StepBatch:
     prefill_q_lens: List[int] = field(default_factory=list)
     sample_rows: List[int] = field(default_factory=list)
     shared_prefix_len: int = 0          # tokens of KV that ALL decode sequences share (whole blocks)
+    prefill_shares_prefix: bool = False  # the prefill chunks start at or after that prefix and share its blocks too
     # sampling (per sampled row); None = greedy
     temperature: Optional[List[float]] = None
     top_p: Optional[List[float]] = None
@@ -501,33 +502,41 @@ class GpuModelRunner:
         kc, vc = self.k_cache[i], self.v_cache[i]
         bt = self._view(lay, "block_tables").view(Dp + P, self.max_blocks_per_seq)
         scale = s.attn_scale
-        if Dp > 0:
-            qd, od = q[:Dp], out[:Dp]
-            sl = self._view(lay, "seq_lens_d")
-            if shared_prefix_len >= 4 * self.block_size and Dp >= 8:
-                # cascade: one GEMM-shaped pass of all decode queries over the shared prefix blocks, one
-                # per-sequence pass over the unique suffixes, then a merge of the two partials
-                lse_a = torch.empty(Dp, hq, dtype=torch.float32, device=qkv.device)
-                lse_b = torch.empty(Dp, hq, dtype=torch.float32, device=qkv.device)
-                oa = torch.empty(Dp, hq, D, dtype=torch.bfloat16, device=qkv.device)
-                ob = torch.empty(Dp, hq, D, dtype=torch.bfloat16, device=qkv.device)
-                with self._prof("attn_shared_prefix"):
-                    K.attn_prefill(qd, kc, vc, bt[:1], self._prefix_len_dev(shared_prefix_len), self._q_start_all(Dp),
-                                   Dp, scale=scale, causal=False, window=0, alibi_slopes=None, out=oa, lse=lse_a,
-                                   return_lse=True)
-                with self._prof("attn_decode_suffix"):
-                    K.attn_decode(qd, kc, vc, bt[:Dp], sl, scale=scale, window=s.window, kv_start=shared_prefix_len,
-                                  alibi_slopes=self.alibi, out=ob, lse=lse_b, return_lse=True, splits=1)
-                with self._prof("attn_merge"):
-                    K.attn_merge(oa, lse_a, ob, lse_b, out=od)
-                self.launches += 3
-            else:
-                with self._prof("attn_decode"):
-                    K.attn_decode(qd, kc, vc, bt[:Dp], sl, scale=scale, window=s.window, alibi_slopes=self.alibi,
-                                  out=od, scratch=self.attn_scratch,
-                                  max_seq_len=self.max_model_len if self._graph_mode else int(self._max_len_d))
+        cascade = shared_prefix_len >= 4 * self.block_size and Dp >= 8
+        # prefill rows join the cascade when their chunks start after the shared prefix and share its blocks
+        pp = cascade and P > 0 and lay.get("_pp", False) and s.window == 0 and self.alibi is None
+        if cascade:
+            # one GEMM-shaped pass of all queries over the shared prefix blocks, one pass per sequence over the
+            # unique suffixes, then a merge of the two partials
+            R = T if pp else Dp
+            lse_a = torch.empty(R, hq, dtype=torch.float32, device=qkv.device)
+            lse_b = torch.empty(R, hq, dtype=torch.float32, device=qkv.device)
+            oa = torch.empty(R, hq, D, dtype=torch.bfloat16, device=qkv.device)
+            ob = torch.empty(R, hq, D, dtype=torch.bfloat16, device=qkv.device)
+            with self._prof("attn_shared_prefix"):
+                K.attn_prefill(q[:R], kc, vc, bt[:1], self._prefix_len_dev(shared_prefix_len), self._q_start_all(R),
+                               R, scale=scale, causal=False, window=0, alibi_slopes=None, out=oa, lse=lse_a,
+                               return_lse=True)
+            with self._prof("attn_decode_suffix"):
+                K.attn_decode(q[:Dp], kc, vc, bt[:Dp], self._view(lay, "seq_lens_d"), scale=scale, window=s.window,
+                              kv_start=shared_prefix_len, alibi_slopes=self.alibi, out=ob[:Dp], lse=lse_b[:Dp],
+                              return_lse=True, splits=1)
+            if pp:
+                with self._prof("attn_prefill_suffix"):
+                    K.attn_prefill(q[Dp:], kc, vc, bt[Dp:], self._view(lay, "seq_lens_p"), self._view(lay, "q_start"),
+                                   lay["_max_q"], scale=scale, causal=True, kv_start=shared_prefix_len, out=ob[Dp:],
+                                   lse=lse_b[Dp:], return_lse=True)
                 self.launches += 1
-        if P > 0:
+            with self._prof("attn_merge"):
+                K.attn_merge(oa, lse_a, ob, lse_b, out=out[:R])
+            self.launches += 3
+        elif Dp > 0:
+            with self._prof("attn_decode"):
+                K.attn_decode(q[:Dp], kc, vc, bt[:Dp], self._view(lay, "seq_lens_d"), scale=scale, window=s.window,
+                              alibi_slopes=self.alibi, out=out[:Dp], scratch=self.attn_scratch,
+                              max_seq_len=self.max_model_len if self._graph_mode else int(self._max_len_d))
+            self.launches += 1
+        if P > 0 and not pp:
             with self._prof("attn_prefill"):
                 K.attn_prefill(q[Dp:], kc, vc, bt[Dp:], self._view(lay, "seq_lens_p"), self._view(lay, "q_start"),
                                lay["_max_q"], scale=scale, causal=True, window=s.window, alibi_slopes=self.alibi,
@@ -812,7 +821,8 @@ class GpuModelRunner:
         self._max_len_d = max(b.seq_lens[:D]) if D else 0
         if graphable:
             lay = self._pack(b, bucketed=True)
-            key = (lay["_Dp"], lay["_P"], lay["_T"], lay["_max_q"], b.shared_prefix_len)
+            lay["_pp"] = b.prefill_shares_prefix
+            key = (lay["_Dp"], lay["_P"], lay["_T"], lay["_max_q"], b.shared_prefix_len, b.prefill_shares_prefix)
             g = self.graphs.get(key)
             if g is None and len(self.graphs) >= self.MAX_GRAPHS:
                 graphable = False
@@ -834,6 +844,7 @@ class GpuModelRunner:
             return len(self._sel)
         self._graph_mode = False
         lay = self._pack(b, bucketed=False)
+        lay["_pp"] = b.prefill_shares_prefix
         self._upload(lay)
         fl = None if greedy else self._sampling_tensors(b, lay["_S"])
         self._forward_and_sample(lay, b.shared_prefix_len, fl)
@@ -870,6 +881,7 @@ class GpuModelRunner:
         self._graph_mode = False
         self._max_len_d = max(b.seq_lens[:b.num_decode]) if b.num_decode else 0
         lay = self._pack(b, bucketed=False)
+        lay["_pp"] = b.prefill_shares_prefix
         self._upload(lay)
         x = self._forward_tokens(lay, b.shared_prefix_len)
         rows = self._view(lay, "sample_rows")
