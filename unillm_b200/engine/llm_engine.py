@@ -54,6 +54,16 @@ class Sequence:
     finish_time: Optional[float] = None
     token_times: List[float] = field(default_factory=list)
     preemptions: int = 0
+    _blocks_np: Optional[object] = field(default=None, repr=False)
+
+    def blocks_array(self):
+        """Block table as an int32 array (the packer copies rows from it); every change of ``blocks`` drops it."""
+        c = self._blocks_np
+        if c is None or len(c) != len(self.blocks):
+            import numpy as np
+
+            c = self._blocks_np = np.asarray(self.blocks, dtype=np.int32)
+        return c
 
     @property
     def tokens(self) -> List[int]:
@@ -158,6 +168,7 @@ class LLMEngine:
         for b in s.blocks:
             self.pool.free(b)
         s.blocks = []
+        s._blocks_np = None
         if self.radix is not None and s.radix_node:
             self.radix.unlock(s.radix_node)
         s.radix_node = 0
@@ -191,6 +202,7 @@ class LLMEngine:
             got = self._alloc(need)
             if got is not None:
                 s.blocks.extend(got)
+                s._blocks_np = None
                 return True
             if not self._preempt_one(s):
                 return False
@@ -202,6 +214,7 @@ class LLMEngine:
     def _admit(self, s: Sequence) -> None:
         """Look up the longest cached prefix of a waiting sequence and take references on its blocks."""
         s.blocks, s.num_computed, s.num_cached, s.published_blocks = [], 0, 0, 0
+        s._blocks_np = None
         if self.radix is None:
             return
         toks = s.tokens
@@ -211,6 +224,7 @@ class LLMEngine:
                 self.pool.incref(b)
             self.radix.lock(node)
             s.blocks = list(blocks)
+            s._blocks_np = None
             s.radix_node = node
             s.num_computed = s.num_cached = len(blocks) * self.block_size
             s.published_blocks = len(blocks)
@@ -281,7 +295,7 @@ class LLMEngine:
             token_ids = [s.output_ids[-1] for s in decode]
             slots = [s.blocks[p // bs] * bs + p % bs for s, p in zip(decode, positions)]
             seq_lens = [p + 1 for p in positions]
-            tables = [s.blocks for s in decode]
+            tables = [s.blocks_array() for s in decode]
             sample_rows = list(range(len(decode)))
             plan = [(s, 1, True) for s in decode]
         q_lens: List[int] = []
@@ -296,7 +310,7 @@ class LLMEngine:
             blk = s.blocks
             slots.extend([blk[p // bs] * bs + p % bs for p in range(a, b)])
             seq_lens.append(s.num_computed + n)
-            tables.append(s.blocks)
+            tables.append(s.blocks_array())
             q_lens.append(n)
             done = s.num_computed + n >= s.total_len
             if done:
@@ -325,6 +339,7 @@ class LLMEngine:
         if got is None:
             return False
         s.blocks.extend(got)
+        s._blocks_np = None
         return True
 
     def _shared_prefix(self, decode: List[Sequence]) -> int:
