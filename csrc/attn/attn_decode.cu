@@ -331,7 +331,9 @@ static bool decode_mma_enabled() {
 
 template <int D>
 static int launch_decode(const UbAttnArgs& a, cudaStream_t st) {
-  if (D <= 128 && decode_mma_enabled() && ub_attn_decode_mma_supported(&a)) {
+  const bool mma_ok = D <= 128 && decode_mma_enabled() && ub_attn_decode_mma_supported(&a);
+  if (a.merge_o != nullptr && (!mma_ok || a.splits != 1)) return -7;   // fused merge lives in the warp-MMA kernel only
+  if (mma_ok) {
     int rc = ub_attn_decode_mma_main(&a, st);
     if (rc != 0) return rc;
     if (a.splits > 1) {

@@ -255,10 +255,22 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const UbAttnArgs a
       ov += red_o[w][g][d] * scw;
     }
     const float inv = lt > 0.f ? 1.f / lt : 0.f;
-    const float lse = lt > 0.f ? (mx + log2f(lt)) * LN2 : -CUDART_INF_F;
+    float lse = lt > 0.f ? (mx + log2f(lt)) * LN2 : -CUDART_INF_F;
     const int h = h0 + g;
     if (a.splits == 1) {
-      reinterpret_cast<__nv_bfloat16*>(a.out)[(long long)seq * a.o_stride + (long long)h * D + d] = __float2bfloat16(ov * inv);
+      float val = ov * inv;
+      if (a.merge_o != nullptr) {
+        // fold in the partial result over the other key set (shared prefix): weights exp(lse_x - max)
+        const float la = a.merge_lse[(long long)seq * a.Hq + h];
+        const float oa = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.merge_o)[((long long)seq * a.Hq + h) * D + d]);
+        const float mm = fmaxf(la, lse);
+        const float wa = (la == -CUDART_INF_F) ? 0.f : __expf(la - mm);
+        const float wb = (lse == -CUDART_INF_F) ? 0.f : __expf(lse - mm);
+        const float den = wa + wb;
+        val = den > 0.f ? (wa * oa + wb * val) / den : 0.f;
+        lse = den > 0.f ? mm + __logf(den) : -CUDART_INF_F;
+      }
+      reinterpret_cast<__nv_bfloat16*>(a.out)[(long long)seq * a.o_stride + (long long)h * D + d] = __float2bfloat16(val);
       if (d == 0 && a.lse != nullptr) a.lse[(long long)seq * a.Hq + h] = lse;
     } else {
       float* sp = a.scratch + (((long long)seq * a.Hq + h) * a.splits + split) * (D + 2);

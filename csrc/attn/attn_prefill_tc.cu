@@ -63,6 +63,8 @@ struct Params {
   float scale_log2;
   int causal;
   int kv_start;     // first key position to attend (suffix pass after a shared prefix); 0 = all
+  const __nv_bfloat16* merge_o;   // optional partial over a disjoint key set, [T, Hq, HD] contiguous
+  const float* merge_lse;         // its log-sum-exp, [T, Hq]
 };
 
 __global__ void __launch_bounds__(192, 1)
@@ -303,7 +305,30 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       mbar_arrive(o_empty);
     }
     if (row_valid && ok) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      float inv = l > 0.f ? 1.f / l : 0.f;
+      float lse_v = l > 0.f ? (m * LN2 + logf(l)) : -CUDART_INF_F;
+      if (p.merge_o != nullptr) {
+        // fold in the partial result over the other key set (shared prefix): weights exp(lse_x - max)
+        const float la = p.merge_lse[(long long)tok * p.Hq + head];
+        const float mm = fmaxf(la, lse_v);
+        const float wa = (la == -CUDART_INF_F) ? 0.f : __expf(la - mm);
+        const float wb = (lse_v == -CUDART_INF_F) ? 0.f : __expf(lse_v - mm);
+        const float den = wa + wb;
+        const float ca = den > 0.f ? wa / den : 0.f, cb = den > 0.f ? wb / den : 0.f;
+        const __nv_bfloat16* src = p.merge_o + ((long long)tok * p.Hq + head) * HD;
+#pragma unroll
+        for (int i = 0; i < HD; i += 8) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(src + i);
+          const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            acc[i + 2 * e] = acc[i + 2 * e] * inv * cb + bf16_lo(w[e]) * ca;
+            acc[i + 2 * e + 1] = acc[i + 2 * e + 1] * inv * cb + bf16_hi(w[e]) * ca;
+          }
+        }
+        inv = 1.f;
+        lse_v = den > 0.f ? mm + logf(den) : -CUDART_INF_F;
+      }
       __nv_bfloat16* dst = p.out + (long long)tok * p.o_stride + (long long)head * HD;
 #pragma unroll
       for (int i = 0; i < HD; i += 8) {
@@ -311,7 +336,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
             make_uint4(pack_bf16x2(acc[i] * inv, acc[i + 1] * inv), pack_bf16x2(acc[i + 2] * inv, acc[i + 3] * inv),
                        pack_bf16x2(acc[i + 4] * inv, acc[i + 5] * inv), pack_bf16x2(acc[i + 6] * inv, acc[i + 7] * inv));
       }
-      if (p.lse != nullptr) p.lse[(long long)tok * p.Hq + head] = l > 0.f ? (m * LN2 + logf(l)) : -CUDART_INF_F;
+      if (p.lse != nullptr) p.lse[(long long)tok * p.Hq + head] = lse_v;
     }
   }
 
@@ -410,6 +435,8 @@ extern "C" int ub_attn_prefill_tc(const UbAttnArgs* a, void* stream_v) {
   p.scale_log2 = a->scale * LOG2E;
   p.causal = a->causal;
   p.kv_start = a->kv_start;
+  p.merge_o = reinterpret_cast<const __nv_bfloat16*>(a->merge_o);
+  p.merge_lse = a->merge_lse;
   static bool attr_set[UB_MAX_DEVICES] = {};
   int dev = 0;
   cudaGetDevice(&dev);

@@ -142,6 +142,11 @@ typedef struct UbAttnArgs {
   int kv_start;              /* first kv position to attend (suffix attention after a shared prefix); 0 = all */
   int total_q;               /* prefill: total query tokens */
   int max_q_len;             /* prefill: max query tokens in one sequence (grid sizing) */
+  /* Optional partial result over a DISJOINT key set (e.g. a shared prefix), merged into the output by the kernel
+     itself: merge_o bf16 [T, Hq, D] contiguous and merge_lse fp32 [T, Hq].  Supported by the tensor-core prefill kernel
+     and the warp-MMA decode kernel with splits == 1; other paths answer -7. */
+  const void* merge_o;
+  const float* merge_lse;
 } UbAttnArgs;
 int ub_attn_decode(const UbAttnArgs* args, void* stream);
 int ub_attn_prefill(const UbAttnArgs* args, void* stream);

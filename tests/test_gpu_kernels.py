@@ -361,3 +361,47 @@ def test_gemm_2cta_dual(M, I, K, tile):
     out = cuda_ops.gemm_tn(x, w, dual_rows=I, act="silu", tile_tokens=tile, cta_pair=2)
     g, u = x.float() @ w[:I].float().t(), x.float() @ w[I:].float().t()
     _close(out, torch.nn.functional.silu(g) * u)
+
+
+def test_attention_fused_merge_matches_separate_merge():
+    """Suffix kernels that fold a prefix partial into their output == suffix partial + merge kernel == full attention."""
+    from unillm_b200.ops import cuda_ops
+
+    Hq, Hkv, D, P = 16, 4, 128, 256                       # P keys of shared prefix (here: simply the first P keys)
+    kv_lens = [300, 257, 512, 290, 400, 333, 270, 260]
+    kc, vc, bt, sl, dk, dv = make_paged_cache(len(kv_lens), kv_lens, Hkv, D, seed=41)
+    B = len(kv_lens)
+    q = _rand(B, Hq, D, seed=42)
+    plen = torch.tensor([P], dtype=torch.int32, device="cuda")
+    qs_all = torch.tensor([0, B], dtype=torch.int32, device="cuda")
+    # decode: the prefix partial uses sequence 0's first P keys for everybody, so build the reference the same way
+    oa, la = cuda_ops.attn_prefill(q, kc, vc, bt[:1], plen, qs_all, B, causal=False, return_lse=True)
+    ob, lb = cuda_ops.attn_decode(q, kc, vc, bt, sl, kv_start=P, splits=1, return_lse=True)
+    sep = cuda_ops.attn_merge(oa, la, ob, lb)
+    fused = cuda_ops.attn_decode(q, kc, vc, bt, sl, kv_start=P, splits=1, merge=(oa, la))
+    _close(fused, sep, rtol=2e-2, atol=1e-2)
+    for i, l in enumerate(kv_lens):
+        k = torch.cat([dk[0][:P], dk[i][P:l]])
+        v = torch.cat([dv[0][:P], dv[i][P:l]])
+        ro, _ = ref_attention(q[i:i + 1].cpu(), k, v, causal_offset=l - 1)
+        _close(fused[i:i + 1], ro)
+    # prefill chunks behind the prefix
+    q_lens = [44, 1, 130, 30, 64, 70, 9, 3]
+    qs = [0]
+    for n in q_lens:
+        qs.append(qs[-1] + n)
+    T = qs[-1]
+    qp = _rand(T, Hq, D, seed=43)
+    q_start = torch.tensor(qs, dtype=torch.int32, device="cuda")
+    oa2, la2 = cuda_ops.attn_prefill(qp, kc, vc, bt[:1], plen, torch.tensor([0, T], dtype=torch.int32, device="cuda"), T,
+                                     causal=False, return_lse=True)
+    ob2, lb2 = cuda_ops.attn_prefill(qp, kc, vc, bt, sl, q_start, max(q_lens), causal=True, kv_start=P, return_lse=True)
+    assert cuda_ops.attn_prefill_last_path() == "tcgen05"
+    sep2 = cuda_ops.attn_merge(oa2, la2, ob2, lb2)
+    fused2 = cuda_ops.attn_prefill(qp, kc, vc, bt, sl, q_start, max(q_lens), causal=True, kv_start=P, merge=(oa2, la2))
+    _close(fused2, sep2, rtol=2e-2, atol=1e-2)
+    for i, (l, n) in enumerate(zip(kv_lens, q_lens)):
+        k = torch.cat([dk[0][:P], dk[i][P:l]])
+        v = torch.cat([dv[0][:P], dv[i][P:l]])
+        ro, _ = ref_attention(qp[qs[i]:qs[i + 1]].cpu(), k, v, causal_offset=l - n)
+        _close(fused2[qs[i]:qs[i + 1]], ro)

@@ -509,27 +509,42 @@ class GpuModelRunner:
             # one GEMM-shaped pass of all queries over the shared prefix blocks, one pass per sequence over the
             # unique suffixes, then a merge of the two partials
             R = T if pp else Dp
+            # the suffix kernels fold the prefix partial into their output themselves (head dim 128, page 16, no
+            # window / ALiBi); otherwise a separate merge kernel combines the two partials
+            fused = D == 128 and self.block_size == 16 and s.window == 0 and self.alibi is None
             lse_a = torch.empty(R, hq, dtype=torch.float32, device=qkv.device)
-            lse_b = torch.empty(R, hq, dtype=torch.float32, device=qkv.device)
             oa = torch.empty(R, hq, D, dtype=torch.bfloat16, device=qkv.device)
-            ob = torch.empty(R, hq, D, dtype=torch.bfloat16, device=qkv.device)
             with self._prof("attn_shared_prefix"):
                 K.attn_prefill(q[:R], kc, vc, bt[:1], self._prefix_len_dev(shared_prefix_len), self._q_start_all(R),
                                R, scale=scale, causal=False, window=0, alibi_slopes=None, out=oa, lse=lse_a,
                                return_lse=True)
-            with self._prof("attn_decode_suffix"):
-                K.attn_decode(q[:Dp], kc, vc, bt[:Dp], self._view(lay, "seq_lens_d"), scale=scale, window=s.window,
-                              kv_start=shared_prefix_len, alibi_slopes=self.alibi, out=ob[:Dp], lse=lse_b[:Dp],
-                              return_lse=True, splits=1)
-            if pp:
-                with self._prof("attn_prefill_suffix"):
-                    K.attn_prefill(q[Dp:], kc, vc, bt[Dp:], self._view(lay, "seq_lens_p"), self._view(lay, "q_start"),
-                                   lay["_max_q"], scale=scale, causal=True, kv_start=shared_prefix_len, out=ob[Dp:],
-                                   lse=lse_b[Dp:], return_lse=True)
-                self.launches += 1
-            with self._prof("attn_merge"):
-                K.attn_merge(oa, lse_a, ob, lse_b, out=out[:R])
-            self.launches += 3
+            if fused:
+                with self._prof("attn_decode_suffix"):
+                    K.attn_decode(q[:Dp], kc, vc, bt[:Dp], self._view(lay, "seq_lens_d"), scale=scale,
+                                  kv_start=shared_prefix_len, out=out[:Dp], splits=1, merge=(oa[:Dp], lse_a[:Dp]))
+                if pp:
+                    with self._prof("attn_prefill_suffix"):
+                        K.attn_prefill(q[Dp:], kc, vc, bt[Dp:], self._view(lay, "seq_lens_p"), self._view(lay, "q_start"),
+                                       lay["_max_q"], scale=scale, causal=True, kv_start=shared_prefix_len, out=out[Dp:],
+                                       merge=(oa[Dp:], lse_a[Dp:]))
+                    self.launches += 1
+                self.launches += 2
+            else:
+                lse_b = torch.empty(R, hq, dtype=torch.float32, device=qkv.device)
+                ob = torch.empty(R, hq, D, dtype=torch.bfloat16, device=qkv.device)
+                with self._prof("attn_decode_suffix"):
+                    K.attn_decode(q[:Dp], kc, vc, bt[:Dp], self._view(lay, "seq_lens_d"), scale=scale, window=s.window,
+                                  kv_start=shared_prefix_len, alibi_slopes=self.alibi, out=ob[:Dp], lse=lse_b[:Dp],
+                                  return_lse=True, splits=1)
+                if pp:
+                    with self._prof("attn_prefill_suffix"):
+                        K.attn_prefill(q[Dp:], kc, vc, bt[Dp:], self._view(lay, "seq_lens_p"), self._view(lay, "q_start"),
+                                       lay["_max_q"], scale=scale, causal=True, kv_start=shared_prefix_len, out=ob[Dp:],
+                                       lse=lse_b[Dp:], return_lse=True)
+                    self.launches += 1
+                with self._prof("attn_merge"):
+                    K.attn_merge(oa, lse_a, ob, lse_b, out=out[:R])
+                self.launches += 3
         elif Dp > 0:
             with self._prof("attn_decode"):
                 K.attn_decode(q[:Dp], kc, vc, bt[:Dp], self._view(lay, "seq_lens_d"), scale=scale, window=s.window,

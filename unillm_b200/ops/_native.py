@@ -76,6 +76,7 @@ class UbAttnArgs(C.Structure):
         ("block_size", i32), ("max_blocks_per_seq", i32), ("num_blocks", i32),
         ("q_stride", i64), ("o_stride", i64), ("scale", f32),
         ("causal", i32), ("window", i32), ("splits", i32), ("kv_start", i32), ("total_q", i32), ("max_q_len", i32),
+        ("merge_o", vp), ("merge_lse", vp),
     ]
 
 

@@ -250,7 +250,7 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, b
                 seq_lens: torch.Tensor, *, scale: Optional[float] = None, window: int = 0, kv_start: int = 0,
                 alibi_slopes: Optional[torch.Tensor] = None, splits: int = 0, scratch: Optional[torch.Tensor] = None,
                 out: Optional[torch.Tensor] = None, return_lse: bool = False, lse: Optional[torch.Tensor] = None,
-                max_seq_len: Optional[int] = None):
+                max_seq_len: Optional[int] = None, merge: Optional[tuple] = None):
     """One query token per sequence.  q: [B, Hq, D] (last two dims contiguous); caches [nb, Hkv, bs, D]."""
     _bf16c(q, "q")
     B, Hq, D = q.shape
@@ -273,6 +273,8 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, b
         a.scratch = scratch.data_ptr()
     a.window, a.splits, a.kv_start = window, splits, kv_start
     a.alibi_slopes = _p(alibi_slopes)
+    if merge is not None:        # (o [B, Hq, D] bf16 contiguous, lse [B, Hq] fp32): partial over a disjoint key set
+        a.merge_o, a.merge_lse = merge[0].data_ptr(), merge[1].data_ptr()
     N.check(N.cuda_lib().ub_attn_decode(C.byref(a), _stream(q)), "ub_attn_decode")
     return (out, lse) if return_lse else out
 
@@ -281,7 +283,7 @@ def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
                  seq_lens: torch.Tensor, q_start: torch.Tensor, max_q_len: int, *, scale: Optional[float] = None,
                  causal: bool = True, window: int = 0, kv_start: int = 0,
                  alibi_slopes: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                 return_lse: bool = False, lse: Optional[torch.Tensor] = None):
+                 return_lse: bool = False, lse: Optional[torch.Tensor] = None, merge: Optional[tuple] = None):
     """Ragged prefill: q [T, Hq, D]; sequence i owns query rows q_start[i]:q_start[i+1] and sees
     seq_lens[i] keys, its last query at kv position seq_lens[i]-1."""
     _bf16c(q, "q")
@@ -296,6 +298,8 @@ def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     a.causal, a.window, a.kv_start = (1 if causal else 0), window, kv_start
     a.total_q, a.max_q_len = T, max_q_len
     a.alibi_slopes = _p(alibi_slopes)
+    if merge is not None:
+        a.merge_o, a.merge_lse = merge[0].data_ptr(), merge[1].data_ptr()
     N.check(N.cuda_lib().ub_attn_prefill(C.byref(a), _stream(q)), "ub_attn_prefill")
     return (out, lse) if return_lse else out
 
