@@ -119,3 +119,15 @@ def test_package_exports():
 
     for n in u.__all__:
         assert getattr(u, n) is not None
+
+
+def test_tensor_helpers_and_runtime():
+    import unillm_b200 as u
+
+    t = u.Tensor.from_f32_slice([1, 2, 3, 4, 5, 6], [2, 3])
+    assert u.Tensor.shape(t) == [2, 3] and u.Tensor.to_vec_f32(u.Tensor.transpose(t)) == [1, 4, 2, 5, 3, 6]
+    assert u.Tensor.narrow(t, 1, 1, 2).tolist() == [[2, 3], [5, 6]]
+    assert u.Tensor.from_i64_slice([1, 2], [2]).dtype == torch.int64
+    r = u.Runtime()
+    assert r.devices()[0].kind == "cpu" or str(r.devices()[0]).lower().startswith("cpu")
+    assert "unillm_b200" in r.describe()

@@ -17,7 +17,9 @@ __version__ = "0.1.0"
 
 _EXPORTS = {
     # core types and configs
-    "ModelError": "types", "DataType": "types", "Device": "types",
+    "ModelError": "types", "DataType": "types", "Device": "types", "ModelFeature": "types",
+    "Tensor": "tensor", "Runtime": "tensor",
+    "Tracer": "utils", "span": "utils", "ReplicaRouter": "engine.replica",
     "GenerationConfig": "config", "EngineConfig": "config", "model_config": "config",
     "Model": "model_core", "ModelInputs": "model_core", "ModelOutputs": "model_core", "ModelWeights": "model_core",
     "ModelRegistry": "model_core", "ModelFactory": "model_core", "registry": "model_core",
