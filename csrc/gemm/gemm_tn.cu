@@ -613,22 +613,25 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
-template <int TN, int STAGES, bool DUAL>
+template <int TN, int STAGES, bool DUAL, bool SPLITK = false>
 struct Gemm2Smem {
   static constexpr int A_BYTES = BM_W * BK * 2;            // this CTA's 128 weight rows: 16 KB
   static constexpr int B_BYTES = (TN / 2) * BK * 2;        // this CTA's half of the token tile
   static constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * A_BYTES + B_BYTES;
   static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
+  // split-K parks the fp32 partial tile [TN][128] on top of the (then idle) pipeline stages
+  static constexpr int PARTIAL_BYTES = (DUAL ? 2 : 1) * TN * BM_W * 4;
+  static_assert(!SPLITK || PARTIAL_BYTES <= TILE_BYTES, "partial tile does not fit in the stage memory");
   static constexpr int DATA_BYTES = TILE_BYTES + STAGING_BYTES;
   static constexpr int TOTAL = DATA_BYTES + 1024 + 256;
   static_assert(TOTAL <= 227 * 1024, "shared memory budget exceeded");
 };
 
-template <int TN, int STAGES, bool DUAL>
+template <int TN, int STAGES, bool DUAL, bool SPLITK>
 __global__ void __launch_bounds__(192, 1)
 gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                     const GemmParams p) {
-  using S = Gemm2Smem<TN, STAGES, DUAL>;
+  using S = Gemm2Smem<TN, STAGES, DUAL, SPLITK>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::DATA_BYTES);
@@ -639,18 +642,32 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_ctarank();        // 0 = leader
+  // Cluster = one CTA pair, or (split-K) `splits` pairs that share a tile and each reduce 1/splits of K.
+  const uint32_t crank = cluster_ctarank();
+  const uint32_t rank = crank & 1u;               // rank inside the pair; 0 = leader (issues the MMAs)
+  const uint32_t pidx = crank >> 1;               // pair index == K slice in split-K mode
+  const uint32_t lead = crank & ~1u;              // cluster rank of this pair's leader; the peer is lead + 1
   const bool leader = rank == 0;
   const int num_m = (p.M + TN - 1) / TN;
   const int num_n = (p.N + 2 * BM_W - 1) / (2 * BM_W);
   const int total_tiles = num_m * num_n;
   const int num_kb = (p.K + BK - 1) / BK;
   constexpr uint32_t ACC_COLS = (DUAL ? 2 : 1) * TN;
-  constexpr int NBUF = (2 * ACC_COLS > 512) ? 1 : 2;
+  constexpr int NBUF = (SPLITK || 2 * ACC_COLS > 512) ? 1 : 2;
   constexpr uint32_t NEED_COLS = NBUF * ACC_COLS;
   constexpr uint32_t TMEM_COLS = NEED_COLS < 32 ? 32 : NEED_COLS;
   static_assert(TMEM_COLS <= 512, "TMEM budget exceeded");
-  const int unit_begin = blockIdx.x >> 1, unit_step = gridDim.x >> 1;
+  int unit_begin, unit_step, kb0 = 0, kb1 = num_kb;
+  if (SPLITK) {
+    unit_begin = blockIdx.y;                      // grid = (2 * splits, tiles): one tile per cluster
+    unit_step = 1 << 30;
+    const int per = (num_kb + p.splits - 1) / p.splits;
+    kb0 = int(pidx) * per;
+    kb1 = min(num_kb, kb0 + per);
+  } else {
+    unit_begin = blockIdx.x >> 1;
+    unit_step = gridDim.x >> 1;
+  }
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -708,13 +725,13 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           }
           if (waited) asm volatile("fence.proxy.async;" ::: "memory");
         }
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err, 600 + s)) { dead = true; break; }
           uint8_t* st = smem + s * S::STAGE_BYTES;
           if (leader) mbar_arrive_expect_tx(&full_bar[s], 2 * S::STAGE_BYTES);   // bytes of both CTAs
-          const uint32_t fb = mapa_u32(smem_u32(&full_bar[s]), 0);              // the leader's barrier
+          const uint32_t fb = mapa_u32(smem_u32(&full_bar[s]), lead);           // the leader's barrier
           tma_load_2d_cg2(st, &tmap_w, fb, kb * BK, n0, pol_w);
           if (DUAL) tma_load_2d_cg2(st + S::A_BYTES, &tmap_w, fb, kb * BK, n0 + p.up_row_off, pol_w);
           tma_load_2d_cg2(st + (DUAL ? 2 : 1) * S::A_BYTES, &tmap_x, fb, kb * BK, m0, pol_x);
@@ -734,7 +751,7 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         if (!mbar_wait(&tmem_empty_bar[ab], aph ^ 1, abort_flag, p.err, 610 + ab)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + ab * ACC_COLS;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&full_bar[s], ph, abort_flag, p.err, 620 + s)) { dead = true; break; }
@@ -745,7 +762,7 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t bdesc = make_smem_desc_sw128(b_addr + k * UMMA_K * 2, 16, 1024);
             const uint64_t adesc = make_smem_desc_sw128(a_addr + k * UMMA_K * 2, 16, 1024);
-            const uint32_t acc = (kb != 0 || k != 0) ? 1u : 0u;
+            const uint32_t acc = (kb != kb0 || k != 0) ? 1u : 0u;
             umma_bf16_ss_cg2(d_tmem, adesc, bdesc, idesc, acc);
             if (DUAL) {
               const uint64_t a2desc = make_smem_desc_sw128(a_addr + S::A_BYTES + k * UMMA_K * 2, 16, 1024);
@@ -754,12 +771,12 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           }
           // the stage is free in BOTH CTAs once these MMAs have read it
           const uint32_t eb = smem_u32(&empty_bar[s]);
-          umma_commit_cg2(mapa_u32(eb, 0));
-          umma_commit_cg2(mapa_u32(eb, 1));
+          umma_commit_cg2(mapa_u32(eb, lead));
+          umma_commit_cg2(mapa_u32(eb, lead + 1));
         }
         const uint32_t tf = smem_u32(&tmem_full_bar[ab]);
-        umma_commit_cg2(mapa_u32(tf, 0));
-        umma_commit_cg2(mapa_u32(tf, 1));
+        umma_commit_cg2(mapa_u32(tf, lead));
+        umma_commit_cg2(mapa_u32(tf, lead + 1));
       }
     }
   } else {
@@ -781,6 +798,23 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       mbar_wait(&tmem_full_bar[ab], aph, abort_flag, p.err, 630 + ab);
       tc_fence_after();
       const uint32_t lane_addr = tmem_base + ab * ACC_COLS + (uint32_t(q * 32) << 16);
+      if constexpr (SPLITK) {
+        // park the raw fp32 partial tile in shared memory: [TN][128] (+ a second one for the up half)
+        float* part = reinterpret_cast<float*>(smem);
+#pragma unroll 1
+        for (int c = 0; c < TN / CH; ++c) {
+          uint32_t r[CH], r2[CH];
+          tmem_ld_32x32(lane_addr + c * CH, r);
+          if (DUAL) tmem_ld_32x32(lane_addr + TN + c * CH, r2);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < CH; ++j) {
+            part[(c * CH + j) * BM_W + et] = __uint_as_float(r[j]);
+            if (DUAL) part[TN * BM_W + (c * CH + j) * BM_W + et] = __uint_as_float(r2[j]);
+          }
+        }
+        continue;
+      }
       const int n = n0 + et;
       float bias_v = 0.f;
       if (p.bias != nullptr && n < p.N) bias_v = __bfloat162float(p.bias[n]);
@@ -793,7 +827,7 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         tmem_ld_wait();
         if (c == TN / CH - 1) {
           tc_fence_before();
-          mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty_bar[ab]), 0));   // hand the buffer back to the leader's MMA thread
+          mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty_bar[ab]), lead));   // hand the buffer back to the leader's MMA thread
         }
         epi_values<CH, DUAL>(r, r2, p.out_scale, bias_v, p.act);
         if (p.out_f32) {
@@ -830,10 +864,64 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         }
       }
     }
-    if (p.rs_world > 0) {
+    if (!SPLITK && p.rs_world > 0) {
       __threadfence_system();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (tid_e < p.rs_world) red_release_sys_add_u32(p.rs_peer_flag[tid_e], 1u);
+    }
+  }
+
+  if constexpr (SPLITK) {
+    // every CTA of the cluster has parked its partial; each pair finishes a slice of the token rows, and inside a
+    // pair each CTA owns its own 128 features: sum the partials of the CTAs with the same rank-in-pair
+    tc_fence_before();
+    cluster_sync_all();
+    if (warp >= 2 && (int)blockIdx.y < total_tiles) {
+      const int u = blockIdx.y;
+      const int m0 = (u % num_m) * TN;
+      const int n0 = (u / num_m) * (2 * BM_W) + int(rank) * BM_W;
+      const int tid_e = threadIdx.x - 64;
+      const int per = (TN + p.splits - 1) / p.splits;
+      const int r0 = int(pidx) * per, r1 = min(TN, r0 + per);
+      const bool vec_ok = (p.N % 8 == 0) && (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
+                          (p.residual == nullptr ||
+                           ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
+      const uint32_t base = smem_u32(smem);
+      for (int idx = tid_e; idx < (r1 - r0) * 16; idx += 128) {
+        const int tok = r0 + (idx >> 4), c8 = idx & 15;
+        const uint32_t off = uint32_t(tok * BM_W + c8 * 8) * 4u;
+        float g[8] = {0, 0, 0, 0, 0, 0, 0, 0}, up[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int sp = 0; sp < p.splits; ++sp) {
+          const uint32_t src = uint32_t(2 * sp) + rank;              // same rank-in-pair, pair sp
+          const uint32_t ra = mapa_u32(base + off, src);
+          const float4 a = ld_dsmem_f4(ra), b = ld_dsmem_f4(ra + 16);
+          g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w; g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
+          if (DUAL) {
+            const uint32_t rb = mapa_u32(base + uint32_t(TN * BM_W * 4) + off, src);
+            const float4 c = ld_dsmem_f4(rb), d = ld_dsmem_f4(rb + 16);
+            up[0] += c.x; up[1] += c.y; up[2] += c.z; up[3] += c.w; up[4] += d.x; up[5] += d.y; up[6] += d.z; up[7] += d.w;
+          }
+        }
+        const int nn = n0 + c8 * 8;
+        uint32_t gv[8], uv[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          float x = g[e];
+          if (!DUAL && p.bias != nullptr && nn + e < p.N) x += __bfloat162float(p.bias[nn + e]) / p.out_scale;
+          gv[e] = __float_as_uint(x);
+          uv[e] = __float_as_uint(up[e]);
+        }
+        epi_values<8, DUAL>(gv, uv, p.out_scale, 0.f, p.act);
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(gv[e]);
+        emit8(p, m0 + tok, p.M, nn, v, vec_ok);
+      }
+      if (p.rs_world > 0) {
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (tid_e < p.rs_world) red_release_sys_add_u32(p.rs_peer_flag[tid_e], 1u);
+      }
     }
   }
 
@@ -965,7 +1053,7 @@ static GemmPlan plan_gemm(const UbGemmArgs* a) {
     env_pair = e ? atoi(e) : 0;          // same meaning as cta_pair; the argument wins when it is not 0
   }
   const int want = a->cta_pair != 0 ? a->cta_pair : env_pair;
-  if (want != 1 && !grouped && splits == 1 && a->M >= 64 && a->N >= 2 * BM_W) {
+  if (want != 1 && !grouped && a->splits <= 1 && a->M >= 64 && a->N >= 2 * BM_W) {
     int tn2 = a->tile_tokens > 0 ? a->tile_tokens : 256;
     if (tn2 < 64) tn2 = 64;
     if (tn2 > 256) tn2 = 256;
@@ -974,13 +1062,23 @@ static GemmPlan plan_gemm(const UbGemmArgs* a) {
     const bool enough = tiles2 * 4 >= (sms / 2) * 3;       // at least 3/4 of the SM pairs get a tile
     // measured: gated GEMMs gain from 256 tokens up (they beat the 1-CTA kernel by 15-20 %), plain ones from ~1024
     const bool gains = dual ? a->M >= 256 : a->M >= 1024;
-    if (want == 2 || (gains && enough && a->tile_tokens <= 0)) {
+    // too few pair tiles for the machine: split K over 2 or 4 pairs per tile (clusters of 4 / 8 CTAs) when K is deep
+    int s2 = 1;
+    if (!enough && !dual && tn2 >= 128 && a->M >= 384) {
+      s2 = (sms / 2) / tiles2;
+      if (s2 > 4) s2 = 4;
+      while (s2 & (s2 - 1)) s2 &= s2 - 1;
+      while (s2 > 1 && (num_kb < 16 * s2 || (s2 - 1) * ((num_kb + s2 - 1) / s2) >= num_kb)) s2 >>= 1;
+    }
+    const int want_s = a->pair_splits > 0 ? a->pair_splits : s2;
+    if (want == 2 || (a->tile_tokens <= 0 && ((gains && enough) || want_s > 1))) {
       pl.pair = 1;
       pl.tn = tn2;
       pl.tiles = tiles2;
       pl.tail_tiles = 0;
       pl.tail_splits = 1;
-      pl.ctas = 2 * (tiles2 < sms / 2 ? tiles2 : sms / 2);
+      pl.splits = (!dual && tn2 >= 128 && want_s > 1) ? want_s : 1;
+      pl.ctas = pl.splits > 1 ? 2 * pl.splits * tiles2 : 2 * (tiles2 < sms / 2 ? tiles2 : sms / 2);
     }
   }
   return pl;
@@ -1019,14 +1117,14 @@ static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmP
   return e == cudaSuccess ? 0 : -(int)e;
 }
 
-template <int TN, int STAGES, bool DUAL>
+template <int TN, int STAGES, bool DUAL, bool SPLITK>
 static int launch_gemm_2cta(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, const GemmPlan& pl,
                             cudaStream_t stream) {
-  using S = Gemm2Smem<TN, STAGES, DUAL>;
+  using S = Gemm2Smem<TN, STAGES, DUAL, SPLITK>;
   static bool attr_set[UB_MAX_DEVICES] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kern = gemm_tn_2cta_kernel<TN, STAGES, DUAL>;
+  auto kern = gemm_tn_2cta_kernel<TN, STAGES, DUAL, SPLITK>;
   if (dev < UB_MAX_DEVICES && !attr_set[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     if (e != cudaSuccess) return -(int)e;
@@ -1034,12 +1132,12 @@ static int launch_gemm_2cta(const CUtensorMap& tw, const CUtensorMap& tx, const 
   }
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(192, 1, 1);
-  cfg.gridDim = dim3(pl.ctas, 1, 1);
+  cfg.gridDim = SPLITK ? dim3(2 * pl.splits, pl.tiles, 1) : dim3(pl.ctas, 1, 1);
   cfg.dynamicSmemBytes = S::TOTAL;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.x = SPLITK ? 2 * pl.splits : 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
@@ -1051,17 +1149,27 @@ static int launch_gemm_2cta(const CUtensorMap& tw, const CUtensorMap& tx, const 
 template <bool DUAL>
 static int dispatch_2cta(int tn, const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, const GemmPlan& pl,
                          cudaStream_t st) {
+  if (pl.splits > 1) {
+    // split-K over pairs: plain GEMMs with 128 / 256-token tiles (the gated form would not fit its partials)
+    if constexpr (!DUAL) {
+      switch (tn) {
+        case 128: return launch_gemm_2cta<128, 8, false, true>(tw, tx, p, pl, st);
+        case 256: return launch_gemm_2cta<256, 6, false, true>(tw, tx, p, pl, st);
+      }
+    }
+    return -4;
+  }
   if constexpr (!DUAL) {
     switch (tn) {
-      case 64: return launch_gemm_2cta<64, 10, false>(tw, tx, p, pl, st);
-      case 128: return launch_gemm_2cta<128, 8, false>(tw, tx, p, pl, st);
-      case 256: return launch_gemm_2cta<256, 6, false>(tw, tx, p, pl, st);
+      case 64: return launch_gemm_2cta<64, 10, false, false>(tw, tx, p, pl, st);
+      case 128: return launch_gemm_2cta<128, 8, false, false>(tw, tx, p, pl, st);
+      case 256: return launch_gemm_2cta<256, 6, false, false>(tw, tx, p, pl, st);
     }
   } else {
     switch (tn) {
-      case 64: return launch_gemm_2cta<64, 5, true>(tw, tx, p, pl, st);
-      case 128: return launch_gemm_2cta<128, 5, true>(tw, tx, p, pl, st);
-      case 256: return launch_gemm_2cta<256, 4, true>(tw, tx, p, pl, st);
+      case 64: return launch_gemm_2cta<64, 5, true, false>(tw, tx, p, pl, st);
+      case 128: return launch_gemm_2cta<128, 5, true, false>(tw, tx, p, pl, st);
+      case 256: return launch_gemm_2cta<256, 4, true, false>(tw, tx, p, pl, st);
     }
   }
   return -4;

@@ -63,6 +63,7 @@ typedef struct UbGemmArgs {
   int grp_w_rows;
   int tail_split;       /* 0 = auto (split K of a thin last round over clusters in a second launch), 1 = never */
   int cta_pair;         /* 0 = auto, 1 = never, 2 = always: tiles of 256 weight rows on pairs of CTAs (cta_group::2) */
+  int pair_splits;      /* 0 = auto; 1 / 2 / 4: K slices (pairs per tile) when the CTA-pair kernel is used */
 } UbGemmArgs;
 int ub_gemm_tn(const UbGemmArgs* args, void* stream);
 /* Number of CTAs the launch for `args` will use; each CTA signals every peer once in F1 mode. */

@@ -405,3 +405,16 @@ def test_attention_fused_merge_matches_separate_merge():
         v = torch.cat([dv[0][:P], dv[i][P:l]])
         ro, _ = ref_attention(qp[qs[i]:qs[i + 1]].cpu(), k, v, causal_offset=l - n)
         _close(fused2[qs[i]:qs[i + 1]], ro)
+
+
+@pytest.mark.parametrize("M,N,K,tile,ps", [(512, 1024, 4096, 256, 2), (510, 4096, 4096, 256, 2), (300, 768, 8192, 128, 4),
+                                           (512, 512, 2048, 256, 4)])
+def test_gemm_2cta_splitk(M, N, K, tile, ps):
+    """K split over 2 / 4 CTA pairs of one cluster, partial tiles reduced through distributed shared memory."""
+    from unillm_b200.ops import cuda_ops
+
+    x, w = _rand(M, K, seed=51), _rand(N, K, scale=1 / math.sqrt(K), seed=52)
+    bias, res = _rand(N, seed=53), _rand(M, N, seed=54)
+    out = cuda_ops.gemm_tn(x, w, bias=bias, residual=res, tile_tokens=tile, cta_pair=2, pair_splits=ps)
+    _close(out, x.float() @ w.float().t() + bias.float() + res.float())
+    assert torch.equal(cuda_ops.gemm_tn(x, w, bias=bias, residual=res, tile_tokens=tile, cta_pair=2, pair_splits=ps), out)

@@ -43,7 +43,7 @@ class UbGemmArgs(C.Structure):
         ("rs_peer_out", vp * UB_MAX_RANKS), ("rs_peer_flag", vp * UB_MAX_RANKS),
         ("ag_world", i32), ("ag_rows_per_rank", i32),
         ("ag_flags", vp), ("ag_epoch", vp), ("ag_signals_per_use", u32),
-        ("grp_tiles", vp), ("grp_max_tiles", i32), ("grp_w_rows", i32), ("tail_split", i32), ("cta_pair", i32),
+        ("grp_tiles", vp), ("grp_max_tiles", i32), ("grp_w_rows", i32), ("tail_split", i32), ("cta_pair", i32), ("pair_splits", i32),
     ]
 
 

@@ -66,7 +66,7 @@ def gemm_tn(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = 
             residual: Optional[torch.Tensor] = None, act: Optional[str] = None, out: Optional[torch.Tensor] = None,
             out_dtype: torch.dtype = torch.bfloat16, out_scale: float = 1.0, tile_tokens: int = 0, splits: int = 0,
             dual_rows: int = 0, rs: Optional[dict] = None, ag: Optional[dict] = None,
-            grouped: Optional[dict] = None, cta_pair: int = 0) -> torch.Tensor:
+            grouped: Optional[dict] = None, cta_pair: int = 0, pair_splits: int = 0) -> torch.Tensor:
     """``out[M, N] = act(x[M, K] @ w[N, K]^T * out_scale + bias) + residual`` on tcgen05 tensor cores.
 
     ``dual_rows = I`` switches to the gated form: ``w`` is ``[2*I, K]`` with gate rows first and the
@@ -107,6 +107,7 @@ def gemm_tn(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = 
     a.tile_tokens = tile_tokens
     a.splits = splits
     a.cta_pair = cta_pair
+    a.pair_splits = pair_splits
     if bias is not None:
         _bf16c(bias, "bias")
     if residual is not None:
