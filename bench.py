@@ -168,55 +168,83 @@ def main(argv=None) -> int:
     max_len = PL + SL + OL + bs
     blocks_needed = PL // bs + (B + 8) * ((SL + OL) // bs + 2)
     num_blocks = max(2 * blocks_needed, 1024)
-    tp = TpContext(rank, world, group, fused=not args.baseline_collectives)
     # MoE models: attention tensor parallel + expert parallel (whole experts per rank) when the ranks divide the experts
     weights = RunnerWeights.random(spec, dev, rank, world, seed=1234, expert_parallel=moe)
-    if tp.fused:
-        from unillm_b200.dist.fused import FusedComm
 
-        tp.comm = FusedComm.create(spec, rank, world, group, max_tokens=8192 + B, device=dev)
-    runner = GpuModelRunner(spec, weights, num_blocks=num_blocks, block_size=bs, max_num_seqs=B,
-                            max_num_batched_tokens=8192, max_model_len=max_len, tp=tp, device=dev,
-                            use_cuda_graphs=not args.no_graphs)
-    eng = LLMEngine(runner, num_blocks=num_blocks, block_size=bs, max_num_seqs=B, max_num_batched_tokens=8192,
-                    max_model_len=max_len, enable_prefix_caching=True)
+    def setup(fused: bool):
+        """Engine in steady state with its CUDA graphs captured (all untimed)."""
+        tp = TpContext(rank, world, group, fused=fused)
+        if tp.fused:
+            from unillm_b200.dist.fused import FusedComm
 
-    g = torch.Generator().manual_seed(2024)
-    V = cfg.vocab_size
-    prefix = torch.randint(0, V, (PL,), generator=g).tolist()
+            tp.comm = FusedComm.create(spec, rank, world, group, max_tokens=8192 + B, device=dev)
+        runner = GpuModelRunner(spec, weights, num_blocks=num_blocks, block_size=bs, max_num_seqs=B,
+                                max_num_batched_tokens=8192, max_model_len=max_len, tp=tp, device=dev,
+                                use_cuda_graphs=not args.no_graphs)
+        eng = LLMEngine(runner, num_blocks=num_blocks, block_size=bs, max_num_seqs=B, max_num_batched_tokens=8192,
+                        max_model_len=max_len, enable_prefix_caching=True)
 
-    def new_prompt():
-        return prefix + torch.randint(0, V, (SL,), generator=g).tolist()
+        g = torch.Generator().manual_seed(2024)
+        V = cfg.vocab_size
+        prefix = torch.randint(0, V, (PL,), generator=g).tolist()
 
-    # first wave: staggered budgets put the engine in steady state (about B/OL requests retire per step)
-    for i in range(B):
-        eng.add_request(new_prompt(), SamplingParams(temperature=0.0, max_tokens=1 + (i * OL) // B, ignore_eos=True))
-    params = SamplingParams(temperature=0.0, max_tokens=OL, ignore_eos=True)
+        def new_prompt():
+            return prefix + torch.randint(0, V, (SL,), generator=g).tolist()
 
-    def top_up():
-        while len(eng.waiting) < 8:
-            eng.add_request(new_prompt(), params)
+        # first wave: staggered budgets put the engine in steady state (about B/OL requests retire per step)
+        for i in range(B):
+            eng.add_request(new_prompt(), SamplingParams(temperature=0.0, max_tokens=1 + (i * OL) // B, ignore_eos=True))
+        params = SamplingParams(temperature=0.0, max_tokens=OL, ignore_eos=True)
 
-    top_up()
-    # setup (untimed): run until every request of the first wave has produced its first token
-    first_wave = [eng.seqs[i] for i in range(B)]
-    while any(s.first_token_time is None for s in first_wave) and eng.stats.steps < 400:
-        eng.step()
+        def top_up():
+            while len(eng.waiting) < 8:
+                eng.add_request(new_prompt(), params)
+
         top_up()
-    # setup (untimed): CUDA-graph capture is a one-time cost per step shape; run until the set of captured
-    # shapes has been stable for a while so that no capture falls into the timed steps
-    stable = guard = 0
-    while runner.use_cuda_graphs and stable < 48 and guard < 600:
-        n_graphs = len(runner.graphs)
-        eng.step()
-        top_up()
-        stable = stable + 1 if len(runner.graphs) == n_graphs else 0
-        guard += 1
-    for _ in range(args.warmup):
-        eng.step()
-        top_up()
-    torch.cuda.synchronize()
-    cuda_ops.check_device_errors()
+        # setup (untimed): run until every request of the first wave has produced its first token
+        first_wave = [eng.seqs[i] for i in range(B)]
+        while any(s.first_token_time is None for s in first_wave) and eng.stats.steps < 400:
+            eng.step()
+            top_up()
+            if fused:
+                cuda_ops.check_device_errors()      # a bounded wait that gave up: stop at once and fall back
+        # setup (untimed): CUDA-graph capture is a one-time cost per step shape; run until the set of captured
+        # shapes has been stable for a while so that no capture falls into the timed steps
+        stable = guard = 0
+        while runner.use_cuda_graphs and stable < 48 and guard < 600:
+            n_graphs = len(runner.graphs)
+            eng.step()
+            top_up()
+            stable = stable + 1 if len(runner.graphs) == n_graphs else 0
+            guard += 1
+        for _ in range(args.warmup):
+            eng.step()
+            top_up()
+        torch.cuda.synchronize()
+        cuda_ops.check_device_errors()
+        return tp, runner, eng, top_up
+
+    fused = world > 1 and not args.baseline_collectives
+    fallback_reason = None
+    state = None
+    if fused:
+        # The fused path is the product; if it cannot run on this box (a bounded device wait gave up, a peer mapping
+        # failed) every rank agrees to measure the NCCL path instead and the JSON line says so.
+        ok, why = 1, ""
+        try:
+            state = setup(True)
+        except Exception as e:          # noqa: BLE001 - any failure means "fall back", the reason is reported
+            ok, why = 0, repr(e)[:200]
+        flag = torch.tensor([ok], dtype=torch.int32, device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag[0]) == 0:
+            fallback_reason = why or "another rank failed in the fused path"
+            state = None
+            torch.cuda.empty_cache()
+            fused = False
+    if state is None:
+        state = setup(False)
+    tp, runner, eng, top_up = state
 
     if args.profile_ops:
         runner.use_cuda_graphs = False
@@ -267,6 +295,7 @@ def main(argv=None) -> int:
             "config": {"model": args.model, "global_batch": B, "seq_len": PL + SL + OL,
                        "parallelism": f"tp{world}" + (f"+ep{world}" if weights.ep else "") +
                        ("" if tp.fused or world == 1 else "-nccl-baseline"),
+                       "fused_fallback": fallback_reason,
                        "workload": f"{PL}-token shared prefix + {SL} unique + {OL} greedy outputs, continuous batching",
                        "kv_block": bs, "prefix_cache": True, "cuda_graphs": not args.no_graphs,
                        "l2": "inputs larger than L2: each step streams the model weights (>= 2 GB per GPU) from HBM",
