@@ -124,6 +124,8 @@ def main(argv=None) -> int:
     ap.add_argument("--suffix-len", type=int, default=128)
     ap.add_argument("--output-len", type=int, default=128)
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--sync-scheduling", action="store_true",
+                    help="read every step's tokens before scheduling the next one (default: the host runs one step ahead)")
     ap.add_argument("--profile-ops", action="store_true", help="print device ms per op over the timed steps (eager mode)")
     ap.add_argument("--baseline-collectives", action="store_true",
                     help="tensor parallel with NCCL all-reduce between separate kernels instead of the fused path")
@@ -182,7 +184,7 @@ def main(argv=None) -> int:
                                 max_num_batched_tokens=8192, max_model_len=max_len, tp=tp, device=dev,
                                 use_cuda_graphs=not args.no_graphs)
         eng = LLMEngine(runner, num_blocks=num_blocks, block_size=bs, max_num_seqs=B, max_num_batched_tokens=8192,
-                        max_model_len=max_len, enable_prefix_caching=True)
+                        max_model_len=max_len, enable_prefix_caching=True, async_scheduling=not args.sync_scheduling)
 
         g = torch.Generator().manual_seed(2024)
         V = cfg.vocab_size
@@ -220,6 +222,7 @@ def main(argv=None) -> int:
         for _ in range(args.warmup):
             eng.step()
             top_up()
+        eng.flush()                      # nothing launched before the timed steps is read inside them
         torch.cuda.synchronize()
         cuda_ops.check_device_errors()
         return tp, runner, eng, top_up
@@ -264,6 +267,7 @@ def main(argv=None) -> int:
         outs = eng.step()
         tokens += len(outs)
         top_up()
+    tokens += len(eng.flush())           # the last step's tokens are read inside the timed region as well
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
@@ -298,6 +302,7 @@ def main(argv=None) -> int:
                        "fused_fallback": fallback_reason,
                        "workload": f"{PL}-token shared prefix + {SL} unique + {OL} greedy outputs, continuous batching",
                        "kv_block": bs, "prefix_cache": True, "cuda_graphs": not args.no_graphs,
+                       "scheduling": "synchronous" if args.sync_scheduling else "host one step ahead of the device",
                        "l2": "inputs larger than L2: each step streams the model weights (>= 2 GB per GPU) from HBM",
                        "output_tokens_timed": tokens},
             "e2e": {"value": e2e, "unit": "tok/s", "ms_per_step": wall * 1e3 / K, "h2d_bytes_per_step": h2d,

@@ -51,6 +51,12 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct Params {
   __nv_bfloat16* out;
   float* lse;
@@ -67,6 +73,7 @@ struct Params {
   const float* merge_lse;         // its log-sum-exp, [T, Hq]
 };
 
+template <bool P_TMEM>
 __global__ void __launch_bounds__(192, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                        const __grid_constant__ CUtensorMap tmap_v, const Params p) {
@@ -82,7 +89,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   uint64_t* s_empty = bars + 11;  // [2]
   uint64_t* p_full = bars + 13;
   uint64_t* o_full = bars + 14;
-  uint64_t* o_empty = bars + 15;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -111,7 +117,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     }
     mbar_init(p_full, 128);
     mbar_init(o_full, 1);
-    mbar_init(o_empty, 128);
     fence_mbar_init();
     tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
@@ -195,7 +200,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           const int jn = j + 1, sn = jn & 1;
           const uint32_t phn = (jn >> 1) & 1;
           if (!mbar_wait(&k_full[sn], phn, abort_flag, p.err, 522)) { ok = false; break; }
-          if (!mbar_wait(&s_empty[sn], phn ^ 1, abort_flag, p.err, 523)) { ok = false; break; }
+          // S buffer sn: its last readers were the softmax loads of tile j - 1 and, when P lives in TMEM, P V of
+          // tile j - 1, which this thread issued before (the tensor pipe runs MMAs in issue order).
+          if (!P_TMEM && !mbar_wait(&s_empty[sn], phn ^ 1, abort_flag, p.err, 523)) { ok = false; break; }
           tc_fence_after();
           issue_qk(jn);
           umma_commit(&s_full[sn]);
@@ -204,16 +211,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         const int s = j & 1;
         if (!mbar_wait(p_full, j & 1, abort_flag, p.err, 524)) { ok = false; break; }
         if (!mbar_wait(&v_full[s], (j >> 1) & 1, abort_flag, p.err, 525)) { ok = false; break; }
-        if (!mbar_wait(o_empty, (j & 1) ^ 1, abort_flag, p.err, 526)) { ok = false; break; }
         tc_fence_after();
         const uint32_t v_addr = smem_u32(smem + SMEM_V + s * TILE_BYTES);
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k) {
-          // A = P, K-major over keys: 64-key halves 16 KB apart, 16 keys = 32 B inside a 128-B row
-          const uint64_t a_desc = make_smem_desc_sw128(p_addr + (k >> 2) * HALF_BYTES + (k & 3) * 32, 16, 1024);
           // B = V, MN-major: 16 keys = two 8-key groups (1024 B apart); the two 64-wide d blocks are 16 KB apart
           const uint64_t b_desc = make_smem_desc_sw128(v_addr + k * 16 * 128, HALF_BYTES, 1024);
-          umma_bf16_ss(tmem_o, a_desc, b_desc, idesc_pv, k != 0);
+          const uint32_t accumulate = (j > 0 || k != 0) ? 1u : 0u;     // O stays in TMEM over all KV tiles
+          if (P_TMEM) {
+            // A = P in tensor memory, packed bf16 pairs over the first 64 columns of this tile's S buffer
+            umma_bf16_ts(tmem_o, tmem_s + s * BN + k * 8, b_desc, idesc_pv, accumulate);
+          } else {
+            // A = P, K-major over keys: 64-key halves 16 KB apart, 16 keys = 32 B inside a 128-B row
+            const uint64_t a_desc = make_smem_desc_sw128(p_addr + (k >> 2) * HALF_BYTES + (k & 3) * 32, 16, 1024);
+            umma_bf16_ss(tmem_o, a_desc, b_desc, idesc_pv, accumulate);
+          }
         }
         umma_commit(o_full);
         umma_commit(&v_empty[s]);
@@ -229,114 +241,167 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     int limit = kv_len;
     if (p.causal) limit = min(kv_len, kv_len - q_len + (tok - q_begin) + 1);
     if (!row_valid || limit < 0) limit = 0;
+    // m is the exponent reference of this row (log2 domain).  It follows the running maximum lazily: it moves only
+    // when a tile's maximum exceeds it by more than 8, so probabilities stay below 2^8 and the O tile in TMEM is
+    // rescaled rarely.  The final O / l does not depend on the reference.
     float m = -CUDART_INF_F, l = 0.f;
-    float acc[HD];
-#pragma unroll
-    for (int i = 0; i < HD; ++i) acc[i] = 0.f;
     uint8_t* p_row = smem + SMEM_P + row * 128;
+    // every wait is agreed on by the whole warp: the TMEM loads and stores below are warp-wide instructions
+    auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) {
+      return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, p.err, code)) != 0;
+    };
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int b = j & 1;
-      if (!mbar_wait(&s_full[b], (j >> 1) & 1, abort_flag, p.err, 530)) { ok = false; break; }
+      if (!wait_all(&s_full[b], (j >> 1) & 1, 530)) { ok = false; break; }
       tc_fence_after();
       const uint32_t s_addr = tmem_s + b * BN + lane_off;
       const int key0 = (tile0 + j) * BN;
-      // pass 1: row maximum
-      float mx = -CUDART_INF_F;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(s_addr + c * 32, r);
-        tmem_ld_wait();
+      // Tiles that lie completely inside [kv_lo, limit) need no per-key predicate (all but the first and last ones).
+      const bool full = key0 >= kv_lo && key0 + BN <= limit;
+      // the whole S row of this thread: 128 fp32 in registers
+      uint32_t sv[4][32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (key0 + c * 32 + i < limit && key0 + c * 32 + i >= kv_lo) mx = fmaxf(mx, __uint_as_float(r[i]));
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(s_addr + c * 32, sv[c]);
+      tmem_ld_wait();
+      if (!P_TMEM) {
+        tc_fence_before();
+        mbar_arrive(&s_empty[b]);
       }
-      const float m_new = fmaxf(m, mx * p.scale_log2);
-      const float alpha = (m == -CUDART_INF_F) ? 0.f : exp2f(m - m_new);
-      const float m_use = (m_new == -CUDART_INF_F) ? 0.f : m_new;   // fully masked so far: every p is 0 anyway
-      // pass 2: probabilities -> bf16 -> swizzled shared memory
+      float mx = -CUDART_INF_F;
+      if (full) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int k = key0 + c * 32 + i;
+            if (k < limit && k >= kv_lo) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
+          }
+      }
+      const float m_tile = mx * p.scale_log2;
+      float alpha = 1.f;
+      if (m_tile > m + 8.f) {                       // also the first visible tile (m == -inf)
+        alpha = (m == -CUDART_INF_F) ? 0.f : ex2_approx(m - m_tile);
+        m = m_tile;
+      }
+      const float m_use = (m == -CUDART_INF_F) ? 0.f : m;   // nothing visible so far: every p is masked to 0
+      if (!P_TMEM && j > 0) {
+        // the single P buffer in shared memory is free once P V of the previous tile has completed
+        if (!wait_all(o_full, (j - 1) & 1, 531)) { ok = false; break; }
+      }
       float psum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(s_addr + c * 32, r);
-        tmem_ld_wait();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const int k0 = key0 + c * 32 + 2 * i;
-          float p0 = (k0 < limit && k0 >= kv_lo) ? exp2f(__uint_as_float(r[2 * i]) * p.scale_log2 - m_use) : 0.f;
-          float p1 = (k0 + 1 < limit && k0 + 1 >= kv_lo) ? exp2f(__uint_as_float(r[2 * i + 1]) * p.scale_log2 - m_use) : 0.f;
-          // the MMA sees the rounded values: sum what it sees
-          const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-          packed[i] = *reinterpret_cast<const uint32_t*>(&pb);
-          const float2 back = __bfloat1622float2(pb);
-          psum += back.x + back.y;
+          float p0 = ex2_approx(fmaf(__uint_as_float(sv[c][2 * i]), p.scale_log2, -m_use));
+          float p1 = ex2_approx(fmaf(__uint_as_float(sv[c][2 * i + 1]), p.scale_log2, -m_use));
+          if (!full) {
+            const int k0 = key0 + c * 32 + 2 * i;
+            if (!(k0 < limit && k0 >= kv_lo)) p0 = 0.f;
+            if (!(k0 + 1 < limit && k0 + 1 >= kv_lo)) p1 = 0.f;
+          }
+          psum += p0 + p1;
+          packed[i] = pack_bf16x2(p0, p1);
         }
-        // 32 keys = 4 chunks of 16 B; key half = c / 2, chunk index inside the 128-B row = (c & 1) * 4 + q
-        uint8_t* base = p_row + (c >> 1) * HALF_BYTES;
+        if (P_TMEM) {
+          // 32 keys = 16 packed columns; they overwrite the head of this tile's S buffer, already in registers
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = (c & 1) * 4 + q4;
-          *reinterpret_cast<uint4*>(base + ((chunk ^ (row & 7)) << 4)) =
-              make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+          for (int i = 0; i < 16; ++i) sv[c >> 1][(c & 1) * 16 + i] = packed[i];
+        } else {
+          // 32 keys = 4 chunks of 16 B; key half = c / 2, chunk index inside the 128-B row = (c & 1) * 4 + q
+          uint8_t* base = p_row + (c >> 1) * HALF_BYTES;
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const int chunk = (c & 1) * 4 + q4;
+            *reinterpret_cast<uint4*>(base + ((chunk ^ (row & 7)) << 4)) =
+                make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+          }
         }
       }
-      // S buffer fully read; P written
+      if (P_TMEM) {
+        tmem_st_32x32(s_addr, sv[0]);
+        tmem_st_32x32(s_addr + 32, sv[1]);
+        // O may only be touched (and the next P V issued) after P V of the previous tile; by now it has had the
+        // whole softmax of this tile to finish
+        if (j > 0 && !wait_all(o_full, (j - 1) & 1, 531)) { ok = false; break; }
+      }
+      l = l * alpha + psum;
+      // rescale the O rows whose reference moved (warp-uniform decision: the TMEM accesses are warp-wide)
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_o + lane_off + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st_32x32(tmem_o + lane_off + c * 32, r);
+        }
+      }
+      tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&s_empty[b]);
       fence_proxy_async_smem();
       mbar_arrive(p_full);
-      l = l * alpha + psum;
-      m = m_new;
-      // O tile of this KV tile
-      if (!mbar_wait(o_full, j & 1, abort_flag, p.err, 531)) { ok = false; break; }
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_o + lane_off + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) acc[c * 32 + i] = acc[c * 32 + i] * alpha + __uint_as_float(r[i]);
-      }
-      tc_fence_before();
-      mbar_arrive(o_empty);
     }
-    if (row_valid && ok) {
+    if (ok && n_tiles > 0) ok = wait_all(o_full, (n_tiles - 1) & 1, 532);
+    tc_fence_after();
+    if (ok) {
       float inv = l > 0.f ? 1.f / l : 0.f;
       float lse_v = l > 0.f ? (m * LN2 + logf(l)) : -CUDART_INF_F;
-      if (p.merge_o != nullptr) {
+      float ca = 0.f, cb = inv;
+      const __nv_bfloat16* src = nullptr;
+      if (p.merge_o != nullptr && row_valid) {
         // fold in the partial result over the other key set (shared prefix): weights exp(lse_x - max)
         const float la = p.merge_lse[(long long)tok * p.Hq + head];
         const float mm = fmaxf(la, lse_v);
         const float wa = (la == -CUDART_INF_F) ? 0.f : __expf(la - mm);
         const float wb = (lse_v == -CUDART_INF_F) ? 0.f : __expf(lse_v - mm);
         const float den = wa + wb;
-        const float ca = den > 0.f ? wa / den : 0.f, cb = den > 0.f ? wb / den : 0.f;
-        const __nv_bfloat16* src = p.merge_o + ((long long)tok * p.Hq + head) * HD;
-#pragma unroll
-        for (int i = 0; i < HD; i += 8) {
-          const uint4 raw = *reinterpret_cast<const uint4*>(src + i);
-          const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            acc[i + 2 * e] = acc[i + 2 * e] * inv * cb + bf16_lo(w[e]) * ca;
-            acc[i + 2 * e + 1] = acc[i + 2 * e + 1] * inv * cb + bf16_hi(w[e]) * ca;
-          }
-        }
-        inv = 1.f;
+        ca = den > 0.f ? wa / den : 0.f;
+        cb = den > 0.f ? inv * wb / den : 0.f;
+        src = p.merge_o + ((long long)tok * p.Hq + head) * HD;
         lse_v = den > 0.f ? mm + logf(den) : -CUDART_INF_F;
       }
       __nv_bfloat16* dst = p.out + (long long)tok * p.o_stride + (long long)head * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_o + lane_off + c * 32, r);      // never-written TMEM (no visible tile) is not used: l == 0
+        tmem_ld_wait();
+        if (row_valid) {
+        float o[32];
 #pragma unroll
-      for (int i = 0; i < HD; i += 8) {
-        *reinterpret_cast<uint4*>(dst + i) =
-            make_uint4(pack_bf16x2(acc[i] * inv, acc[i + 1] * inv), pack_bf16x2(acc[i + 2] * inv, acc[i + 3] * inv),
-                       pack_bf16x2(acc[i + 4] * inv, acc[i + 5] * inv), pack_bf16x2(acc[i + 6] * inv, acc[i + 7] * inv));
+        for (int i = 0; i < 32; ++i) o[i] = (l > 0.f) ? __uint_as_float(r[i]) * cb : 0.f;
+        if (src != nullptr) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(src + c * 32 + i);
+            const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              o[i + 2 * e] += bf16_lo(w[e]) * ca;
+              o[i + 2 * e + 1] += bf16_hi(w[e]) * ca;
+            }
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          *reinterpret_cast<uint4*>(dst + c * 32 + i) =
+              make_uint4(pack_bf16x2(o[i], o[i + 1]), pack_bf16x2(o[i + 2], o[i + 3]),
+                         pack_bf16x2(o[i + 4], o[i + 5]), pack_bf16x2(o[i + 6], o[i + 7]));
+        }
+        }
+        __syncwarp();
       }
-      if (p.lse != nullptr) p.lse[(long long)tok * p.Hq + head] = lse_v;
+      if (p.lse != nullptr && row_valid) p.lse[(long long)tok * p.Hq + head] = lse_v;
     }
   }
 
@@ -437,16 +502,27 @@ extern "C" int ub_attn_prefill_tc(const UbAttnArgs* a, void* stream_v) {
   p.kv_start = a->kv_start;
   p.merge_o = reinterpret_cast<const __nv_bfloat16*>(a->merge_o);
   p.merge_lse = a->merge_lse;
+  // P (the probabilities fed to the second MMA) lives in tensor memory by default; UB_ATTN_TC_P=smem stages it in
+  // shared memory instead (the A operand then comes through a shared-memory descriptor).
+  static const bool p_tmem = [] {
+    const char* e = getenv("UB_ATTN_TC_P");
+    return !(e != nullptr && e[0] == 's');
+  }();
   static bool attr_set[UB_MAX_DEVICES] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < UB_MAX_DEVICES && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
     if (e != cudaSuccess) return -(int)e;
     attr_set[dev] = true;
   }
   dim3 grid((a->max_q_len + TOK - 1) / TOK, a->Hkv, a->num_seqs);
-  attn_prefill_tc_kernel<<<grid, 192, SMEM_TOTAL, reinterpret_cast<cudaStream_t>(stream_v)>>>(tq, tk, tv, p);
+  if (p_tmem)
+    attn_prefill_tc_kernel<true><<<grid, 192, SMEM_TOTAL, reinterpret_cast<cudaStream_t>(stream_v)>>>(tq, tk, tv, p);
+  else
+    attn_prefill_tc_kernel<false><<<grid, 192, SMEM_TOTAL, reinterpret_cast<cudaStream_t>(stream_v)>>>(tq, tk, tv, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }

@@ -69,3 +69,64 @@ def test_engine_abort_and_limits():
         eng.add_request(list(range(60)), SamplingParams(max_tokens=10))
     with pytest.raises(InvalidInput):
         eng.add_request([], SamplingParams())
+
+
+def _run(async_scheduling, num_blocks, prompts, params, eos=None, prefix=True):
+    cls, cfg = CASES[0]
+    m = cls.new(cfg, init="random", seed=5)
+    runner = CpuModelRunner(m, num_blocks=num_blocks, block_size=4, max_model_len=96)
+    eng = LLMEngine(runner, num_blocks=num_blocks, block_size=4, max_num_seqs=4, max_num_batched_tokens=32,
+                    max_model_len=96, enable_prefix_caching=prefix, eos_token_id=eos, async_scheduling=async_scheduling)
+    ids = [eng.add_request(p, params) for p in prompts]
+    streamed = {i: [] for i in ids}
+    steps = 0
+    while eng.has_unfinished():
+        for o in eng.step():
+            streamed[o.seq_id].append(o.token)
+        steps += 1
+        assert steps < 500
+    outs = [eng.seqs[i].output_ids for i in ids]
+    assert [streamed[i] for i in ids] == outs          # every token is reported exactly once, in order
+    assert all(t >= 0 for o in outs for t in o)        # no placeholder survives
+    return eng, outs
+
+
+def test_async_scheduling_same_tokens():
+    """One-step-ahead scheduling gives the tokens of the synchronous loop: plain decode, a stop token noticed one step
+    late, and preemption while a step is in flight."""
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, 128, (n,), generator=g).tolist() for n in (18, 17, 19, 16, 5, 30)]
+    p = SamplingParams(temperature=0.0, max_tokens=12)
+    e0, sync = _run(False, 64, prompts, p)
+    e1, asyn = _run(True, 64, prompts, p)
+    assert sync == asyn
+    assert e1.pool.num_free() + e1.radix.stats()["cached_blocks"] == 64
+    assert e1.stats.generated_tokens == e0.stats.generated_tokens
+    # a stop token in the middle: take one that the greedy run produces
+    eos = sync[0][4]
+    _, s2 = _run(False, 64, prompts, p, eos=eos)
+    e3, a2 = _run(True, 64, prompts, p, eos=eos)
+    assert s2 == a2 and len(a2[0]) <= 5 and a2[0][-1] == eos
+    assert e3.pool.num_free() + e3.radix.stats()["cached_blocks"] == 64
+    # a small pool forces preemption
+    e4, s3 = _run(False, 24, prompts[:4], p, prefix=False)
+    e5, a3 = _run(True, 24, prompts[:4], p, prefix=False)
+    assert s3 == a3 and e5.stats.preemptions > 0 and e5.pool.num_free() == 24
+
+
+def test_async_scheduling_abort_and_snapshot():
+    cls, cfg = CASES[0]
+    m = cls.new(cfg, init="random", seed=5)
+    runner = CpuModelRunner(m, num_blocks=32, block_size=4, max_model_len=64)
+    eng = LLMEngine(runner, num_blocks=32, block_size=4, max_num_seqs=4, max_num_batched_tokens=32, max_model_len=64,
+                    async_scheduling=True)
+    a = eng.add_request([1, 2, 3, 4, 5], SamplingParams(temperature=0.0, max_tokens=20))
+    b = eng.add_request([1, 2, 3, 9], SamplingParams(temperature=0.0, max_tokens=5))
+    eng.step()
+    eng.step()
+    snap = eng.snapshot()
+    assert all(t >= 0 for r in snap["requests"] for t in r["output"])
+    assert eng.abort(a) and not eng.abort(a)
+    res = eng.run_to_completion()
+    assert len(res[b]) == 5 and all(t >= 0 for t in res[b])
+    assert eng.pool.num_free() + eng.radix.stats()["cached_blocks"] == 32

@@ -96,16 +96,19 @@ def test_engine_tokens_gpu_vs_cpu_and_graph_vs_eager():
     shared = torch.randint(0, 512, (70,), generator=g).tolist()
     prompts = [shared + torch.randint(0, 512, (n,), generator=g).tolist() for n in (3, 40, 17, 9, 25, 1, 33, 12, 5, 8)]
     results = {}
-    for name in ("cpu", "eager", "graph"):
-        cpu, gpu = _runners(m, graphs=(name == "graph"))
+    for name in ("cpu", "eager", "graph", "eager-async", "graph-async"):
+        cpu, gpu = _runners(m, graphs=name.startswith("graph"))
         eng = LLMEngine(cpu if name == "cpu" else gpu, num_blocks=128, block_size=16, max_num_seqs=16,
-                        max_num_batched_tokens=128, max_model_len=512)
+                        max_num_batched_tokens=128, max_model_len=512, async_scheduling=name.endswith("async"))
         results[name] = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12))
         if name != "cpu":
             torch.cuda.synchronize()
             cuda_ops.check_device_errors()
             assert eng.stats.cached_tokens > 0
     assert results["eager"] == results["graph"]
+    # the host running one step ahead (input tokens fed from the device buffer of the previous step's samples)
+    assert results["eager-async"] == results["eager"]
+    assert results["graph-async"] == results["graph"]
     agree = sum(a == b for ra, rb in zip(results["cpu"], results["eager"]) for a, b in zip(ra, rb))
     total = sum(len(r) for r in results["cpu"])
     assert agree / total > 0.7, (agree, total)

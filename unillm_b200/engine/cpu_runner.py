@@ -149,11 +149,20 @@ class CpuModelRunner:
         return out
 
     def launch(self, b: StepBatch) -> int:
+        if b.token_src is not None:
+            # input tokens that the previous step sampled and the engine has not read yet
+            prev = self._pending
+            for r, k in enumerate(b.token_src):
+                if k >= 0:
+                    b.token_ids[r] = prev[k]
         self._pending = self.execute(b)
         return len(self._pending)
 
-    def fetch(self) -> List[int]:
+    def pending(self):
         return self._pending
+
+    def fetch(self, handle=None) -> List[int]:
+        return self._pending if handle is None else handle
 
 
 def _draw_row(probs: torch.Tensor, seed: int, step: int, row: int) -> int:

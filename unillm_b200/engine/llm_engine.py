@@ -17,6 +17,13 @@ instead of running a model (``crates/inference/src/engine.rs:322-379``).  Here e
      that layer's attention);
   4. the runner executes the packed step and returns one sampled token per finished prefill / decode row.
 
+With ``async_scheduling`` the host runs one step ahead of the device: step N + 1 is scheduled, packed and launched
+while step N executes.  Lengths and block tables of N + 1 do not depend on the token values of N, so the engine
+appends a placeholder per sampled sequence, lets the runner feed the sampled ids from device memory into the
+next step, and reads the real values one step later.  Finishes by length are known in advance; a stop token is
+noticed one step late (that sequence's extra row is dropped).  Preemption, abort and snapshot first wait for
+the step in flight.
+
 Every rank of a tensor-parallel group runs this loop on the same request stream and takes identical
 decisions (it is deterministic), so no per-step control traffic is needed.
 """
@@ -54,6 +61,8 @@ class Sequence:
     finish_time: Optional[float] = None
     token_times: List[float] = field(default_factory=list)
     preemptions: int = 0
+    pending_src: int = -1            # sample index, in the step in flight, of the token that output_ids[pending_at] awaits
+    pending_at: int = -1
     _blocks_np: Optional[object] = field(default=None, repr=False)
 
     def blocks_array(self):
@@ -101,7 +110,8 @@ class LLMEngine:
     def __init__(self, runner, *, num_blocks: int, block_size: int = 16, max_num_seqs: int = 256,
                  max_num_batched_tokens: int = 8192, max_model_len: int = 8192, enable_prefix_caching: bool = True,
                  enable_chunked_prefill: bool = True, eos_token_id: Optional[int] = None,
-                 policy: Optional[Callable[[List[Sequence]], List[Sequence]]] = None, seed: int = 0):
+                 policy: Optional[Callable[[List[Sequence]], List[Sequence]]] = None, seed: int = 0,
+                 async_scheduling: bool = False):
         self.runner = runner
         self.block_size = block_size
         self.pool = BlockPool(num_blocks, block_size)
@@ -116,6 +126,9 @@ class LLMEngine:
         self.seqs: Dict[int, Sequence] = {}
         self._next_id = 0
         self.stats = EngineStats()
+        self.async_scheduling = async_scheduling
+        self._inflight = None       # (plan, runner handle) of the launched step whose samples are not read yet
+        self._late: List[StepOutput] = []   # outputs of a step that had to be waited for outside ``step``
         self.step_events = None     # optional (start, end) CUDA events recorded around the runner launch
         self.tracer = None          # optional unillm_b200.utils.Tracer: spans around schedule / launch / fetch / process
 
@@ -139,6 +152,9 @@ class LLMEngine:
         s = self.seqs.get(seq_id)
         if s is None or s.status in (FINISHED, ABORTED):
             return False
+        self._late.extend(self._drain())
+        if s.status in (FINISHED, ABORTED):
+            return False
         if s.status == RUNNING:
             self.running.remove(s)
         else:
@@ -148,7 +164,7 @@ class LLMEngine:
         return True
 
     def has_unfinished(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self.waiting or self.running or self._inflight is not None or self._late)
 
     # ------------------------------------------------------------------------------------------
     # block management
@@ -184,8 +200,11 @@ class LLMEngine:
 
     def _preempt_one(self, keep: Sequence) -> bool:
         """Free the blocks of the youngest running sequence other than ``keep``; it is recomputed later."""
+        if self._inflight is not None:
+            # a preempted sequence is recomputed from its token list: all of its tokens must be known first
+            self._late.extend(self._drain())
         for cand in reversed(self.running):
-            if cand is not keep:
+            if cand is not keep and cand.status == RUNNING:
                 self.running.remove(cand)
                 self._release(cand, publish=True)
                 cand.num_computed = cand.num_cached = 0
@@ -237,6 +256,8 @@ class LLMEngine:
         for s in list(self.running):
             if s.status != RUNNING or not s.prefill_done:
                 continue                      # includes sequences preempted while making room for an earlier one
+            if s.pending_src >= 0 and (len(s.output_ids) >= s.params.max_tokens or s.total_len >= self.max_model_len):
+                continue                      # its last token is in flight; it finishes when that step is read
             if not self._ensure_blocks(s, s.total_len):
                 continue
             decode.append(s)
@@ -290,9 +311,14 @@ class LLMEngine:
         tables: List[List[int]] = []
         sample_rows: List[int] = []
         plan: List[Tuple[Sequence, int, bool]] = []
+        token_src: Optional[List[int]] = None
         if decode:
             positions = [len(s.prompt_ids) + len(s.output_ids) - 1 for s in decode]
-            token_ids = [s.output_ids[-1] for s in decode]
+            if self._inflight is not None:
+                token_src = [s.pending_src for s in decode]
+                token_ids = [0 if s.pending_src >= 0 else s.output_ids[-1] for s in decode]
+            else:
+                token_ids = [s.output_ids[-1] for s in decode]
             slots = [s.blocks[p // bs] * bs + p % bs for s, p in zip(decode, positions)]
             seq_lens = [p + 1 for p in positions]
             tables = [s.blocks_array() for s in decode]
@@ -324,7 +350,7 @@ class LLMEngine:
         sampled = [s for s, _, smp in plan if smp]
         greedy = all(s.params.greedy for s in sampled)
         batch = StepBatch(token_ids, positions, slots, len(decode), seq_lens, tables, q_lens, sample_rows, shared,
-                          prefill_shares_prefix=pfx_ok, seed=self.seed, step=self.stats.steps)
+                          prefill_shares_prefix=pfx_ok, seed=self.seed, step=self.stats.steps, token_src=token_src)
         if not greedy:
             batch.temperature = [s.params.temperature for s in sampled]
             batch.top_p = [s.params.top_p for s in sampled]
@@ -373,9 +399,11 @@ class LLMEngine:
         else:
             batch, plan = self.schedule()
         if batch is None:
-            if self.waiting and not self.running:
+            outs = self._late + self._drain()
+            self._late = []
+            if not outs and self.waiting and not self.running:
                 raise MemoryError_("a waiting request does not fit in the KV cache even when it is empty")
-            return []
+            return outs
         ev = self.step_events
         if ev is not None:
             ev[0].record()
@@ -386,30 +414,76 @@ class LLMEngine:
             self.runner.launch(batch)
         if ev is not None:
             ev[1].record()
-        if tr is not None:
-            with tr.span("engine.fetch"):
-                ids = self.runner.fetch()
-            with tr.span("engine.process"):
-                return self._process(plan, ids)
-        ids = self.runner.fetch()
-        return self._process(plan, ids)
+        if not self.async_scheduling:
+            if tr is not None:
+                with tr.span("engine.fetch"):
+                    ids = self.runner.fetch()
+                with tr.span("engine.process"):
+                    return self._finalize(self._advance(plan), ids)
+            ids = self.runner.fetch()
+            return self._finalize(self._advance(plan), ids)
+        # one step ahead: this step is in flight; read the one launched before it
+        prev = self._inflight
+        self._inflight = (self._advance(plan), self.runner.pending())
+        outs, self._late = self._late, []
+        if prev is not None:
+            if tr is not None:
+                with tr.span("engine.fetch"):
+                    ids = self.runner.fetch(prev[1])
+                with tr.span("engine.process"):
+                    outs.extend(self._finalize(prev[0], ids))
+            else:
+                outs.extend(self._finalize(prev[0], self.runner.fetch(prev[1])))
+        return outs
 
-    def _process(self, plan, ids: List[int]) -> List[StepOutput]:
-        now = time.perf_counter()
-        outs: List[StepOutput] = []
-        k = 0
+    def flush(self) -> List[StepOutput]:
+        """Outputs of the step still in flight under ``async_scheduling`` (empty otherwise); afterwards every token
+        launched so far has been read back."""
+        outs, self._late = self._late + self._drain(), []
+        return outs
+
+    def _drain(self) -> List[StepOutput]:
+        """Waits for the step in flight (if any) and applies its results."""
+        prev, self._inflight = self._inflight, None
+        if prev is None:
+            return []
+        return self._finalize(prev[0], self.runner.fetch(prev[1]))
+
+    def _advance(self, plan) -> List[Tuple[Sequence, int, bool, int]]:
+        """Bookkeeping that does not need the sampled values: computed lengths move on and every sampled sequence
+        gets a placeholder token.  Returns the plan with the placeholder's index in ``output_ids``."""
         self.stats.steps += 1
+        out = []
+        k = 0
         for s, n, sampled in plan:
             s.num_computed += n
             if n == 1 and len(s.output_ids) > 0 and sampled:
                 self.stats.decode_tokens += 1
             else:
                 self.stats.prefill_tokens += n
+            at = -1
+            if sampled:
+                at = len(s.output_ids)
+                s.output_ids.append(-1)
+                s.pending_src, s.pending_at = k, at
+                k += 1
+            out.append((s, n, sampled, at))
+        return out
+
+    def _finalize(self, plan, ids: List[int]) -> List[StepOutput]:
+        now = time.perf_counter()
+        outs: List[StepOutput] = []
+        k = 0
+        for s, n, sampled, at in plan:
             if not sampled:
                 continue
             tok = int(ids[k])
             k += 1
-            s.output_ids.append(tok)
+            if s.status != RUNNING:
+                continue                  # stopped or aborted while this row was already in flight
+            s.output_ids[at] = tok
+            if s.pending_at == at:
+                s.pending_src = s.pending_at = -1
             s.token_times.append(now)
             if s.first_token_time is None:
                 s.first_token_time = now
@@ -420,11 +494,14 @@ class LLMEngine:
                 reason = "stop"
             elif tok in p.stop_token_ids:
                 reason = "stop"
-            elif len(s.output_ids) >= p.max_tokens:
+            elif at + 1 >= p.max_tokens:
                 reason = "length"
-            elif s.total_len >= self.max_model_len:
+            elif len(s.prompt_ids) + at + 1 >= self.max_model_len:
                 reason = "length"
             if reason is not None:
+                del s.output_ids[at + 1:]          # a placeholder of the step launched meanwhile
+                s.pending_src = s.pending_at = -1
+                s.num_computed = min(s.num_computed, s.total_len)
                 s.status, s.finish_reason, s.finish_time = FINISHED, reason, now
                 self.running.remove(s)
                 self._release(s, publish=True)
@@ -453,6 +530,7 @@ class LLMEngine:
         engine prefills prompt + generated tokens again (greedy requests then continue with identical tokens)."""
         import dataclasses
 
+        self._late.extend(self._drain())
         reqs = []
         for s in self.seqs.values():
             reqs.append({"id": s.seq_id, "prompt": list(s.prompt_ids), "output": list(s.output_ids), "priority": s.priority,

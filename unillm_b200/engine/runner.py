@@ -59,6 +59,10 @@ class StepBatch:
     top_k: Optional[List[int]] = None
     seed: int = 0
     step: int = 0
+    # per decode row: index (in sample order) of the PREVIOUS step's output that is this row's input token, or -1
+    # when ``token_ids`` already holds it.  Lets a step be launched before the host has read the previous
+    # step's samples.
+    token_src: Optional[List[int]] = None
 
 
 def shard_rows(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
@@ -294,7 +298,7 @@ class StepPacker:
             b <<= 1
         return b
 
-    def pack(self, b: StepBatch, bucketed: bool = False):
+    def pack(self, b: StepBatch, bucketed: bool = False, token_src: Optional[List[int]] = None):
         """Writes the step's integer metadata into the pinned buffer and returns the layout
         (name -> (offset, length)); one H2D copy moves all of it.
 
@@ -340,6 +344,9 @@ class StepPacker:
         put("positions", b.positions[:D] + [0] * pad + b.positions[D:] + [0] * tpad)
         put("slot_mapping", b.slot_mapping[:D] + [-1] * pad + b.slot_mapping[D:] + [-1] * tpad)
         put("seq_lens_d", b.seq_lens[:D] + [1] * pad)
+        if token_src is not None:
+            # device index of each decode row's input token inside the previous step's sampled ids (-1 = uploaded)
+            put("token_src", list(token_src[:D]) + [-1] * pad)
         nbt = (Dp + Pp) * mb
         if off + nbt > self.META_INTS:
             raise InvalidInput("step metadata exceeds the staging buffer")
@@ -427,13 +434,18 @@ class GpuModelRunner:
             sl = alibi_slopes(s.num_heads)
             self.alibi = sl[weights.rank * weights.hq:(weights.rank + 1) * weights.hq].to(dev)
         # packed metadata: pinned host staging + device mirror with fixed addresses (graph friendly)
-        self.meta_host = torch.zeros(self.META_INTS, dtype=torch.int32, pin_memory=True)
-        self.packer = StepPacker(self.meta_host, self.max_blocks_per_seq)
+        # two staging buffers: the next step may be packed while the copy of the previous one is still queued
+        self.meta_hosts = [torch.zeros(self.META_INTS, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.packers = [StepPacker(h, self.max_blocks_per_seq) for h in self.meta_hosts]
+        self._flip = 0
         self.meta_dev = torch.empty(self.META_INTS, dtype=torch.int32, device=dev)
-        self.fmeta_host = torch.empty(4 * max_num_seqs, dtype=torch.float32, pin_memory=True)
+        self.fmeta_hosts = [torch.empty(4 * max_num_seqs, dtype=torch.float32, pin_memory=True) for _ in range(2)]
         self.fmeta_dev = torch.empty(4 * max_num_seqs, dtype=torch.float32, device=dev)
         self.out_ids_dev = torch.zeros(4 * max_num_seqs, dtype=torch.int32, device=dev)
-        self.out_ids_host = torch.zeros(4 * max_num_seqs, dtype=torch.int32, pin_memory=True)
+        self.out_ids_hosts = [torch.zeros(4 * max_num_seqs, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._out_events = [torch.cuda.Event(), torch.cuda.Event()]
+        self._sel: List[int] = []
+        self._handle = None
         self.attn_scratch = torch.empty(max_num_seqs * weights.hq * 16 * (D + 2), dtype=torch.float32, device=dev)
         self.graphs: Dict[tuple, tuple] = {}
         self.profile = False
@@ -448,7 +460,26 @@ class GpuModelRunner:
     # metadata packing
     # ------------------------------------------------------------------------------------------
     def _pack(self, b: StepBatch, bucketed: bool = False):
-        return self.packer.pack(b, bucketed)
+        src = None
+        if b.token_src is not None:
+            prev = self._sel            # sample order -> index in out_ids_dev, of the step launched before this one
+            src = [prev[k] if k >= 0 else -1 for k in b.token_src]
+        self._flip ^= 1
+        pk = self.packers[self._flip]
+        lay = pk.pack(b, bucketed, token_src=src)
+        lay["_host"] = pk.meta_host
+        return lay
+
+    def _input_ids(self, lay) -> torch.Tensor:
+        """Token ids of the step; decode rows whose token was sampled by the previous step take it from the
+        device buffer of that step's samples (the host may not have read them yet)."""
+        ids = self._view(lay, "token_ids")
+        if "token_src" in lay:
+            src = self._view(lay, "token_src")
+            prev = self.out_ids_dev.index_select(0, src.clamp(min=0))
+            d = ids[:src.numel()]
+            d.copy_(torch.where(src >= 0, prev, d))
+        return ids
 
     def _view(self, lay, name):
         o, n = lay[name]
@@ -456,7 +487,7 @@ class GpuModelRunner:
 
     def _upload(self, lay):
         n = lay["_used"]
-        self.meta_dev[:n].copy_(self.meta_host[:n], non_blocking=True)
+        self.meta_dev[:n].copy_(lay["_host"][:n], non_blocking=True)
         self.h2d_bytes += n * 4
 
     # ------------------------------------------------------------------------------------------
@@ -602,7 +633,7 @@ class GpuModelRunner:
         self._final_norm_done = False
         if self._fused_ok(T):
             return self._forward_tokens_fused(lay, shared_prefix_len)
-        ids = self._view(lay, "token_ids")
+        ids = self._input_ids(lay)
         pos = self._view(lay, "positions")
         slots = self._view(lay, "slot_mapping")
         x = K.embed_gather(ids, t["embed"], scale=s.embed_scale)
@@ -673,7 +704,7 @@ class GpuModelRunner:
         T = lay["_T"]
         R = T // W
         H = s.hidden_size
-        ids = self._view(lay, "token_ids")
+        ids = self._input_ids(lay)
         pos = self._view(lay, "positions")
         slots = self._view(lay, "slot_mapping")
         x_full = K.embed_gather(ids, t["embed"], scale=s.embed_scale)
@@ -811,7 +842,7 @@ class GpuModelRunner:
     def _sampling_tensors(self, b: StepBatch, S: int):
         if b.temperature is None or all(t <= 0 for t in b.temperature):
             return None
-        f = self.fmeta_host
+        f = self.fmeta_hosts[self._flip]
         f[:S] = torch.as_tensor(b.temperature, dtype=torch.float32)
         f[S:2 * S] = torch.as_tensor(b.top_p if b.top_p is not None else [1.0] * S, dtype=torch.float32)
         self.fmeta_dev[:2 * S].copy_(f[:2 * S], non_blocking=True)
@@ -837,7 +868,8 @@ class GpuModelRunner:
         if graphable:
             lay = self._pack(b, bucketed=True)
             lay["_pp"] = b.prefill_shares_prefix
-            key = (lay["_Dp"], lay["_P"], lay["_T"], lay["_max_q"], b.shared_prefix_len, b.prefill_shares_prefix)
+            key = (lay["_Dp"], lay["_P"], lay["_T"], lay["_max_q"], b.shared_prefix_len, b.prefill_shares_prefix,
+                   b.token_src is not None)
             g = self.graphs.get(key)
             if g is None and len(self.graphs) >= self.MAX_GRAPHS:
                 graphable = False
@@ -855,33 +887,44 @@ class GpuModelRunner:
                 g = self.graphs[key] = (graph, self.launches - before)
             g[0].replay()
             self.launches += g[1]
-            self._sel = lay["_sel"]
-            return len(self._sel)
+            return self._queue_readback(lay["_sel"])
         self._graph_mode = False
         lay = self._pack(b, bucketed=False)
         lay["_pp"] = b.prefill_shares_prefix
         self._upload(lay)
         fl = None if greedy else self._sampling_tensors(b, lay["_S"])
         self._forward_and_sample(lay, b.shared_prefix_len, fl)
-        self._sel = lay["_sel"]
-        return len(self._sel)
+        return self._queue_readback(lay["_sel"])
+
+    def _queue_readback(self, sel: List[int]) -> int:
+        """Queues the device -> pinned host copy of the sampled ids behind the step and records an event; the
+        returned handle of ``pending()`` stays valid while one later step is launched."""
+        self._sel = sel
+        n = (max(sel) + 1) if sel else 0
+        host, ev = self.out_ids_hosts[self._flip], self._out_events[self._flip]
+        if n:
+            host[:n].copy_(self.out_ids_dev[:n], non_blocking=True)
+            self.d2h_bytes += 4 * n
+        ev.record()
+        self._handle = (ev, host, n, sel)
+        return len(sel)
+
+    def pending(self):
+        """Handle of the step launched last; pass it to ``fetch`` after launching the next step."""
+        return self._handle
 
     def _forward_and_sample(self, lay, shared_prefix_len, fl):
         x = self._forward_tokens(lay, shared_prefix_len)
         if lay["_S"] > 0:
             self._logits_and_sample(x, lay, None, fl)
 
-    def fetch(self) -> List[int]:
-        """Device -> pinned host copy of the sampled ids of the last ``launch`` and a stream sync."""
-        sel = self._sel
+    def fetch(self, handle=None) -> List[int]:
+        """Waits for a launched step (the last one by default) and returns its sampled ids from pinned memory."""
+        ev, host, n, sel = handle if handle is not None else self._handle
+        ev.synchronize()
         if not sel:
-            torch.cuda.current_stream().synchronize()
             return []
-        n = max(sel) + 1
-        self.out_ids_host[:n].copy_(self.out_ids_dev[:n], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        self.d2h_bytes += 4 * n
-        vals = self.out_ids_host[:n].tolist()
+        vals = host[:n].tolist()
         return [vals[i] for i in sel]
 
     def execute(self, b: StepBatch) -> List[int]:
