@@ -135,37 +135,56 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0 && n_tiles > 0) {
-      mbar_arrive_expect_tx(q_full, TILE_BYTES);
-      tma_load_3d(smem + SMEM_Q, &tmap_q, q_full, 0, kh * G, t0);
-      tma_load_3d(smem + SMEM_Q + HALF_BYTES, &tmap_q, q_full, 64, kh * G, t0);
+    // The whole warp takes part: lanes 0..7 each own one 16-key page of the tile.  They read their block-table entry
+    // one tile ahead (a dependent global load in front of every copy would otherwise serialise the pipeline) and each
+    // issues the copies of its page, so a tile costs a handful of issue slots instead of 64 single-thread copies.
+    if (n_tiles > 0) {
+      if (lane == 0) {
+        mbar_arrive_expect_tx(q_full, TILE_BYTES);
+        tma_load_3d(smem + SMEM_Q, &tmap_q, q_full, 0, kh * G, t0);
+        tma_load_3d(smem + SMEM_Q + HALF_BYTES, &tmap_q, q_full, 64, kh * G, t0);
+      }
       const int* bt = p.block_tables + (long long)seq * p.max_blocks_per_seq;
       const int pages_valid = (kv_hi + PAGE - 1) / PAGE;
-      bool dead = false;
-      for (int j = 0; j < n_tiles && !dead; ++j) {
+      constexpr int PPT = BN / PAGE;                       // pages per tile
+      auto page_block = [&](int j) {
+        int blk = 0;
+        if (lane < PPT) {
+          const int pi = (tile0 + j) * PPT + lane;
+          blk = (pi < pages_valid && pi < p.max_blocks_per_seq) ? bt[pi] : 0;   // pages past the end: any finite page
+          if (blk < 0 || blk >= p.num_blocks) { set_err(p.err, ERR_BOUNDS, blk); blk = 0; }
+        }
+        return blk;
+      };
+      int blk_next = page_block(0);
+      for (int j = 0; j < n_tiles; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
+        const int blk = blk_next;
+        if (j + 1 < n_tiles) blk_next = page_block(j + 1);
+        const int row = (blk * p.Hkv + kh) * PAGE;
         // K tile
-        if (!mbar_wait(&k_empty[s], ph ^ 1, abort_flag, p.err, 500 + s)) { dead = true; break; }
-        mbar_arrive_expect_tx(&k_full[s], TILE_BYTES);
-        for (int pg = 0; pg < BN / PAGE; ++pg) {
-          const int pi = (tile0 + j) * (BN / PAGE) + pg;
-          int blk = (pi < pages_valid && pi < p.max_blocks_per_seq) ? bt[pi] : 0;   // pages past the end: any finite page
-          if (blk < 0 || blk >= p.num_blocks) { set_err(p.err, ERR_BOUNDS, blk); blk = 0; }
-          const int row = (blk * p.Hkv + kh) * PAGE;
-          uint8_t* dst = smem + SMEM_K + s * TILE_BYTES + pg * PAGE * 128;
+        int ok = 1;
+        if (lane == 0) {
+          ok = mbar_wait(&k_empty[s], ph ^ 1, abort_flag, p.err, 500 + s) ? 1 : 0;
+          if (ok) mbar_arrive_expect_tx(&k_full[s], TILE_BYTES);
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        if (lane < PPT) {
+          uint8_t* dst = smem + SMEM_K + s * TILE_BYTES + lane * PAGE * 128;
           tma_load_2d(dst, &tmap_k, &k_full[s], 0, row);
           tma_load_2d(dst + HALF_BYTES, &tmap_k, &k_full[s], 64, row);
         }
         // V tile
-        if (!mbar_wait(&v_empty[s], ph ^ 1, abort_flag, p.err, 510 + s)) { dead = true; break; }
-        mbar_arrive_expect_tx(&v_full[s], TILE_BYTES);
-        for (int pg = 0; pg < BN / PAGE; ++pg) {
-          const int pi = (tile0 + j) * (BN / PAGE) + pg;
-          int blk = (pi < pages_valid && pi < p.max_blocks_per_seq) ? bt[pi] : 0;
-          if (blk < 0 || blk >= p.num_blocks) blk = 0;
-          const int row = (blk * p.Hkv + kh) * PAGE;
-          uint8_t* dst = smem + SMEM_V + s * TILE_BYTES + pg * PAGE * 128;
+        if (lane == 0) {
+          ok = mbar_wait(&v_empty[s], ph ^ 1, abort_flag, p.err, 510 + s) ? 1 : 0;
+          if (ok) mbar_arrive_expect_tx(&v_full[s], TILE_BYTES);
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        if (lane < PPT) {
+          uint8_t* dst = smem + SMEM_V + s * TILE_BYTES + lane * PAGE * 128;
           tma_load_2d(dst, &tmap_v, &v_full[s], 0, row);
           tma_load_2d(dst + HALF_BYTES, &tmap_v, &v_full[s], 64, row);
         }

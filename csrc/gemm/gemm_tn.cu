@@ -1060,13 +1060,17 @@ static GemmPlan plan_gemm(const UbGemmArgs* a) {
     while (tn2 > 64 && tn2 / 2 >= a->M) tn2 >>= 1;
     const int tiles2 = ((a->M + tn2 - 1) / tn2) * ((a->N + 2 * BM_W - 1) / (2 * BM_W));
     const bool enough = tiles2 * 4 >= (sms / 2) * 3;       // at least 3/4 of the SM pairs get a tile
-    // measured: gated GEMMs gain from 256 tokens up (they beat the 1-CTA kernel by 15-20 %), plain ones from ~1024
-    const bool gains = dual ? a->M >= 256 : a->M >= 1024;
-    // too few pair tiles for the machine: split K over 2 or 4 pairs per tile (clusters of 4 / 8 CTAs) when K is deep
+    // What bounds these kernels at a few hundred tokens is the rate at which one SM can fill its shared memory
+    // (measured: about 40 B/clk per SM, TMA without multicast).  Per k-block a 128 x 256 tile pulls 48 KB into one SM,
+    // a CTA pair 32 KB into each of two SMs for twice the math, so pairs win as soon as the tokens fill a 256-wide
+    // tile; gated GEMMs (two weight tiles per token tile) gain from 256 tokens up, plain ones from 384.
+    const bool gains = dual ? a->M >= 256 : a->M >= 384;
+    // pair tiles that cover at most half of the SM pairs: split K over 2 or 4 pairs per tile (clusters of 4 / 8 CTAs)
     int s2 = 1;
-    if (!enough && !dual && tn2 >= 128 && a->M >= 384) {
+    if (!dual && tn2 >= 128 && a->M >= 384) {
       s2 = (sms / 2) / tiles2;
       if (s2 > 4) s2 = 4;
+      if (s2 < 1) s2 = 1;
       while (s2 & (s2 - 1)) s2 &= s2 - 1;
       while (s2 > 1 && (num_kb < 16 * s2 || (s2 - 1) * ((num_kb + s2 - 1) / s2) >= num_kb)) s2 >>= 1;
     }

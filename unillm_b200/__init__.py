@@ -20,7 +20,7 @@ _EXPORTS = {
     "ModelError": "types", "DataType": "types", "Device": "types", "ModelFeature": "types",
     "Tensor": "tensor", "Runtime": "tensor",
     "Tracer": "utils", "span": "utils", "ReplicaRouter": "engine.replica",
-    "GenerationConfig": "config", "EngineConfig": "config", "model_config": "config",
+    "GenerationConfig": "config", "EngineConfig": "config", "model_config": "config", "ModelConfig": "config",
     "Model": "model_core", "ModelInputs": "model_core", "ModelOutputs": "model_core", "ModelWeights": "model_core",
     "ModelRegistry": "model_core", "ModelFactory": "model_core", "registry": "model_core",
     "TensorOps": "tensor_core", "ops_fn": "tensor_core",
@@ -35,6 +35,20 @@ _EXPORTS = {
     # engine and serving
     "LLMEngine": "engine.llm_engine", "GpuModelRunner": "engine.runner", "CpuModelRunner": "engine.cpu_runner",
     "UniLLMInferenceEngine": "inference", "InferenceRequest": "inference", "InferenceResponse": "inference",
+    "InferenceEngine": "inference", "RequestBuilder": "inference", "ChatMessage": "inference",
+    "ResponseStream": "inference", "StreamSender": "inference", "ResponseChunk": "inference",
+    "FinishReason": "inference", "BatchProcessor": "inference", "BatchOptimizer": "inference",
+    "BatchingStrategy": "inference", "PerformanceCollector": "inference", "EngineHealth": "inference",
+    "HealthStatus": "inference",
+    # KV bookkeeping
+    "PagedKvAllocator": "kv", "RadixCache": "kv", "HybridKVCache": "kv", "AdaptiveCachePolicy": "kv",
+    "CacheHandle": "kv", "CacheTier": "kv", "GpuIntegratedCache": "kv", "GpuIntegratedCacheBuilder": "kv",
+    # host-side scheduling policies
+    "ContinuousBatchingScheduler": "scheduler", "IntelligentScheduler": "scheduler", "SchedulingPolicy": "scheduler",
+    "ChunkedPrefillManager": "scheduler", "ChunkedPrefillConfig": "scheduler", "StreamOverlapManager": "scheduler",
+    "CacheAwareAnalyzer": "scheduler", "GpuMemoryTracker": "scheduler", "AdaptivePolicyEngine": "scheduler",
+    "AdmissionController": "scheduler", "Request": "scheduler", "RequestBatch": "scheduler",
+    "RequestPriority": "scheduler", "RequestState": "scheduler",
     # weights
     "ModelLoader": "weights", "UnifiedWeightLoader": "weights", "ConfigLoader": "weights",
     # benchmark

@@ -54,7 +54,8 @@ def percentile(xs: List[float], q: float) -> Optional[float]:
 
 
 def build_engine(arch_name: str, world: int, rank: int, group, device: str, *, max_seqs: int, max_len: int, blocks: int,
-                 max_tokens: int = 8192, small: bool = False, fused: bool = True, graphs: bool = True):
+                 max_tokens: int = 8192, small: bool = False, fused: bool = True, graphs: bool = True,
+                 async_scheduling: bool = True):
     from ..engine.llm_engine import LLMEngine
     from ..engine.runner import GpuModelRunner, RunnerWeights, TpContext
     from ..models import configs as C
@@ -73,7 +74,7 @@ def build_engine(arch_name: str, world: int, rank: int, group, device: str, *, m
     runner = GpuModelRunner(spec, w, num_blocks=blocks, block_size=16, max_num_seqs=max_seqs, max_num_batched_tokens=max_tokens,
                             max_model_len=max_len, tp=tp, device=device, use_cuda_graphs=graphs)
     eng = LLMEngine(runner, num_blocks=blocks, block_size=16, max_num_seqs=max_seqs, max_num_batched_tokens=max_tokens,
-                    max_model_len=max_len, enable_prefix_caching=True)
+                    max_model_len=max_len, enable_prefix_caching=True, async_scheduling=async_scheduling)
     return eng, runner, cfg, w
 
 

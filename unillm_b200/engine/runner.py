@@ -470,16 +470,17 @@ class GpuModelRunner:
         lay["_host"] = pk.meta_host
         return lay
 
-    def _input_ids(self, lay) -> torch.Tensor:
-        """Token ids of the step; decode rows whose token was sampled by the previous step take it from the
-        device buffer of that step's samples (the host may not have read them yet)."""
-        ids = self._view(lay, "token_ids")
-        if "token_src" in lay:
-            src = self._view(lay, "token_src")
-            prev = self.out_ids_dev.index_select(0, src.clamp(min=0))
-            d = ids[:src.numel()]
-            d.copy_(torch.where(src >= 0, prev, d))
-        return ids
+    def _feed_sampled_ids(self, lay) -> None:
+        """Decode rows whose input token was sampled by the previous step take it from the device buffer of that
+        step's samples (the host may not have read them yet).  Runs right after the upload and outside the captured
+        graph: the step itself then only reads its own metadata and can be replayed (graph capture runs it more
+        than once) without seeing the samples it has just written."""
+        if "token_src" not in lay:
+            return
+        src = self._view(lay, "token_src")
+        d = self._view(lay, "token_ids")[:src.numel()]
+        prev = self.out_ids_dev.index_select(0, src.clamp(min=0))
+        d.copy_(torch.where(src >= 0, prev, d))
 
     def _view(self, lay, name):
         o, n = lay[name]
@@ -489,6 +490,7 @@ class GpuModelRunner:
         n = lay["_used"]
         self.meta_dev[:n].copy_(lay["_host"][:n], non_blocking=True)
         self.h2d_bytes += n * 4
+        self._feed_sampled_ids(lay)
 
     # ------------------------------------------------------------------------------------------
     # layer math
@@ -633,7 +635,7 @@ class GpuModelRunner:
         self._final_norm_done = False
         if self._fused_ok(T):
             return self._forward_tokens_fused(lay, shared_prefix_len)
-        ids = self._input_ids(lay)
+        ids = self._view(lay, "token_ids")
         pos = self._view(lay, "positions")
         slots = self._view(lay, "slot_mapping")
         x = K.embed_gather(ids, t["embed"], scale=s.embed_scale)
@@ -704,7 +706,7 @@ class GpuModelRunner:
         T = lay["_T"]
         R = T // W
         H = s.hidden_size
-        ids = self._input_ids(lay)
+        ids = self._view(lay, "token_ids")
         pos = self._view(lay, "positions")
         slots = self._view(lay, "slot_mapping")
         x_full = K.embed_gather(ids, t["embed"], scale=s.embed_scale)
@@ -868,8 +870,7 @@ class GpuModelRunner:
         if graphable:
             lay = self._pack(b, bucketed=True)
             lay["_pp"] = b.prefill_shares_prefix
-            key = (lay["_Dp"], lay["_P"], lay["_T"], lay["_max_q"], b.shared_prefix_len, b.prefill_shares_prefix,
-                   b.token_src is not None)
+            key = (lay["_Dp"], lay["_P"], lay["_T"], lay["_max_q"], b.shared_prefix_len, b.prefill_shares_prefix)
             g = self.graphs.get(key)
             if g is None and len(self.graphs) >= self.MAX_GRAPHS:
                 graphable = False
