@@ -97,7 +97,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   const int TOK = BM / G;                                   // query tokens per tile
   const int q_begin = p.q_start[seq], q_end = p.q_start[seq + 1];
   const int q_len = q_end - q_begin;
-  const int t0 = q_begin + blockIdx.x * TOK;                // first token of this tile (global token index)
+  // causal: the last query tiles see the most keys; start them first so that the tail of the grid is made of short ones
+  const int qtile = p.causal ? int(gridDim.x) - 1 - int(blockIdx.x) : int(blockIdx.x);
+  const int t0 = q_begin + qtile * TOK;                     // first token of this tile (global token index)
   if (t0 >= q_end) return;                                  // whole CTA leaves together, nothing allocated yet
   const int kv_len = p.seq_lens[seq];
   const int t_last = min(t0 + TOK, q_end) - 1;
@@ -287,21 +289,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         tc_fence_before();
         mbar_arrive(&s_empty[b]);
       }
-      float mx = -CUDART_INF_F;
+      // one warp per scheduler has nobody to hide its ALU latency: keep four independent chains per reduction
+      float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
       if (full) {
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
+          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
       } else {
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int k = key0 + c * 32 + i;
-            if (k < limit && k >= kv_lo) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
+            if (k < limit && k >= kv_lo) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
           }
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_tile = mx * p.scale_log2;
       float alpha = 1.f;
       if (m_tile > m + 8.f) {                       // also the first visible tile (m == -inf)
@@ -313,7 +317,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         // the single P buffer in shared memory is free once P V of the previous tile has completed
         if (!wait_all(o_full, (j - 1) & 1, 531)) { ok = false; break; }
       }
-      float psum = 0.f;
+      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t packed[16];
@@ -326,7 +330,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
             if (!(k0 < limit && k0 >= kv_lo)) p0 = 0.f;
             if (!(k0 + 1 < limit && k0 + 1 >= kv_lo)) p1 = 0.f;
           }
-          psum += p0 + p1;
+          ps4[i & 3] += p0 + p1;
           packed[i] = pack_bf16x2(p0, p1);
         }
         if (P_TMEM) {
@@ -351,7 +355,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         // whole softmax of this tile to finish
         if (j > 0 && !wait_all(o_full, (j - 1) & 1, 531)) { ok = false; break; }
       }
-      l = l * alpha + psum;
+      l = l * alpha + ((ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
       // rescale the O rows whose reference moved (warp-uniform decision: the TMEM accesses are warp-wide)
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
         tc_fence_after();

@@ -211,6 +211,83 @@ __device__ __forceinline__ void emit8(const GemmParams& p, int m, int m_end, int
   }
 }
 
+// Split-K finish: sums the fp32 partial tiles that the CTAs of a cluster parked in their shared memory ([tokens][128]
+// floats, a second tile behind it for the up half of a gated GEMM) and runs the epilogue on token rows [r0, r1).
+// The partial of split sp lives in cluster rank sp * rank_stride + rank_off.  All remote loads of a batch of items
+// are issued before the first one is used: a distributed-shared-memory load takes several hundred cycles, and one
+// item at a time left the reduction latency-bound.
+template <int S, bool DUAL>
+__device__ __forceinline__ void splitk_reduce(const GemmParams& p, uint32_t base, int tn, int r0, int r1, int tid_e, int m0,
+                                              int n0, bool vec_ok, uint32_t rank_stride, uint32_t rank_off) {
+  constexpr int IT = (DUAL ? 4 : 8) / S > 0 ? (DUAL ? 4 : 8) / S : 1;     // items in flight per thread
+  const int n_items = (r1 - r0) * 16;
+  for (int idx0 = tid_e; idx0 < n_items; idx0 += 128 * IT) {
+    float4 ga[IT][S], gb[IT][S], ua[DUAL ? IT : 1][S], ub[DUAL ? IT : 1][S];
+#pragma unroll
+    for (int i = 0; i < IT; ++i) {
+      const int idx = idx0 + i * 128;
+      if (idx < n_items) {
+        const int tok = r0 + (idx >> 4), c8 = idx & 15;
+        const uint32_t off = uint32_t(tok * BM_W + c8 * 8) * 4u;
+#pragma unroll
+        for (int sp = 0; sp < S; ++sp) {
+          const uint32_t src = uint32_t(sp) * rank_stride + rank_off;
+          const uint32_t ra = mapa_u32(base + off, src);
+          ga[i][sp] = ld_dsmem_f4(ra);
+          gb[i][sp] = ld_dsmem_f4(ra + 16);
+          if (DUAL) {
+            const uint32_t rb = mapa_u32(base + uint32_t(tn * BM_W * 4) + off, src);
+            ua[i][sp] = ld_dsmem_f4(rb);
+            ub[i][sp] = ld_dsmem_f4(rb + 16);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < IT; ++i) {
+      const int idx = idx0 + i * 128;
+      if (idx < n_items) {
+        const int tok = r0 + (idx >> 4), c8 = idx & 15;
+        float g[8] = {0, 0, 0, 0, 0, 0, 0, 0}, up[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int sp = 0; sp < S; ++sp) {
+          const float4 a = ga[i][sp], b = gb[i][sp];
+          g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w; g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
+          if (DUAL) {
+            const float4 c = ua[i][sp], d = ub[i][sp];
+            up[0] += c.x; up[1] += c.y; up[2] += c.z; up[3] += c.w; up[4] += d.x; up[5] += d.y; up[6] += d.z; up[7] += d.w;
+          }
+        }
+        const int nn = n0 + c8 * 8;
+        uint32_t gv[8], uv[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          float x = g[e];
+          if (!DUAL && p.bias != nullptr && nn + e < p.N) x += __bfloat162float(p.bias[nn + e]) / p.out_scale;
+          gv[e] = __float_as_uint(x);
+          uv[e] = __float_as_uint(up[e]);
+        }
+        epi_values<8, DUAL>(gv, uv, p.out_scale, 0.f, p.act);
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(gv[e]);
+        emit8(p, m0 + tok, p.M, nn, v, vec_ok);
+      }
+    }
+  }
+}
+
+template <bool DUAL>
+__device__ __forceinline__ void splitk_reduce_any(const GemmParams& p, uint32_t base, int tn, int r0, int r1, int tid_e,
+                                                  int m0, int n0, bool vec_ok, uint32_t rank_stride, uint32_t rank_off) {
+  switch (p.splits) {
+    case 2: splitk_reduce<2, DUAL>(p, base, tn, r0, r1, tid_e, m0, n0, vec_ok, rank_stride, rank_off); break;
+    case 4: splitk_reduce<4, DUAL>(p, base, tn, r0, r1, tid_e, m0, n0, vec_ok, rank_stride, rank_off); break;
+    case 8: splitk_reduce<8, DUAL>(p, base, tn, r0, r1, tid_e, m0, n0, vec_ok, rank_stride, rank_off); break;
+    default: splitk_reduce<1, DUAL>(p, base, tn, r0, r1, tid_e, m0, n0, vec_ok, rank_stride, rank_off); break;
+  }
+}
+
 template <int TN, int STAGES, bool DUAL, bool SPLITK>
 __global__ void __launch_bounds__(192, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
@@ -507,35 +584,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                           (p.residual == nullptr ||
                            ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
       const uint32_t base = smem_u32(smem);
-      for (int idx = tid_e; idx < (r1 - r0) * 16; idx += 128) {
-        const int tok = r0 + (idx >> 4), c8 = idx & 15;
-        const uint32_t off = uint32_t(tok * BM_W + c8 * 8) * 4u;
-        float g[8] = {0, 0, 0, 0, 0, 0, 0, 0}, up[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int s = 0; s < p.splits; ++s) {
-          const uint32_t ra = mapa_u32(base + off, (uint32_t)s);
-          const float4 a = ld_dsmem_f4(ra), b = ld_dsmem_f4(ra + 16);
-          g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w; g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
-          if (DUAL) {
-            const uint32_t rb = mapa_u32(base + uint32_t(TN * BM_W * 4) + off, (uint32_t)s);
-            const float4 c = ld_dsmem_f4(rb), d = ld_dsmem_f4(rb + 16);
-            up[0] += c.x; up[1] += c.y; up[2] += c.z; up[3] += c.w; up[4] += d.x; up[5] += d.y; up[6] += d.z; up[7] += d.w;
-          }
-        }
-        const int nn = n0 + c8 * 8;
-        uint32_t gv[8], uv[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          float x = g[e];
-          if (!DUAL && p.bias != nullptr && nn + e < p.N) x += __bfloat162float(p.bias[nn + e]) / p.out_scale;
-          gv[e] = __float_as_uint(x);
-          uv[e] = __float_as_uint(up[e]);
-        }
-        epi_values<8, DUAL>(gv, uv, p.out_scale, 0.f, p.act);
-        float v[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(gv[e]);
-        emit8(p, m0 + tok, p.M, nn, v, vec_ok);
-      }
+      splitk_reduce_any<DUAL>(p, base, TN, r0, r1, tid_e, m0, n0, vec_ok, 1u, 0u);
       if (p.rs_world > 0) {
         __threadfence_system();
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -887,36 +936,7 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                           (p.residual == nullptr ||
                            ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
       const uint32_t base = smem_u32(smem);
-      for (int idx = tid_e; idx < (r1 - r0) * 16; idx += 128) {
-        const int tok = r0 + (idx >> 4), c8 = idx & 15;
-        const uint32_t off = uint32_t(tok * BM_W + c8 * 8) * 4u;
-        float g[8] = {0, 0, 0, 0, 0, 0, 0, 0}, up[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int sp = 0; sp < p.splits; ++sp) {
-          const uint32_t src = uint32_t(2 * sp) + rank;              // same rank-in-pair, pair sp
-          const uint32_t ra = mapa_u32(base + off, src);
-          const float4 a = ld_dsmem_f4(ra), b = ld_dsmem_f4(ra + 16);
-          g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w; g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
-          if (DUAL) {
-            const uint32_t rb = mapa_u32(base + uint32_t(TN * BM_W * 4) + off, src);
-            const float4 c = ld_dsmem_f4(rb), d = ld_dsmem_f4(rb + 16);
-            up[0] += c.x; up[1] += c.y; up[2] += c.z; up[3] += c.w; up[4] += d.x; up[5] += d.y; up[6] += d.z; up[7] += d.w;
-          }
-        }
-        const int nn = n0 + c8 * 8;
-        uint32_t gv[8], uv[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          float x = g[e];
-          if (!DUAL && p.bias != nullptr && nn + e < p.N) x += __bfloat162float(p.bias[nn + e]) / p.out_scale;
-          gv[e] = __float_as_uint(x);
-          uv[e] = __float_as_uint(up[e]);
-        }
-        epi_values<8, DUAL>(gv, uv, p.out_scale, 0.f, p.act);
-        float v[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(gv[e]);
-        emit8(p, m0 + tok, p.M, nn, v, vec_ok);
-      }
+      splitk_reduce_any<DUAL>(p, base, TN, r0, r1, tid_e, m0, n0, vec_ok, 2u, rank);
       if (p.rs_world > 0) {
         __threadfence_system();
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -991,6 +1011,39 @@ static int num_sms() {
 
 struct GemmPlan { int tn, splits, ctas, tiles; int tail_tiles, tail_splits; int pair; };
 
+// How many thread-block clusters of `csize` CTAs (one CTA per SM, ~200 KB of shared memory each) the device can run at
+// the same time.  A cluster lives inside one GPC, so this is less than SMs / csize: split-K launches that ask for
+// more clusters than this run in two waves and take twice as long.
+static int max_active_clusters(int csize) {
+  static int cache[UB_MAX_DEVICES][9] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (csize < 2) return num_sms();
+  if (csize > 8) csize = 8;
+  if (dev < UB_MAX_DEVICES && cache[dev][csize] > 0) return cache[dev][csize];
+  auto kern = gemm_tn_kernel<128, 6, false, true>;
+  using S = GemmSmem<128, 6, false, true>;
+  int n = 0;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL) == cudaSuccess) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(192, 1, 1);
+    cfg.gridDim = dim3(csize, 64, 1);
+    cfg.dynamicSmemBytes = S::TOTAL;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = csize;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) n = 0;
+  }
+  (void)cudaGetLastError();
+  if (n <= 0) n = (num_sms() / csize) * 7 / 8;      // the query failed: assume some GPCs do not divide evenly
+  if (dev < UB_MAX_DEVICES) cache[dev][csize] = n;
+  return n;
+}
+
 static GemmPlan plan_gemm(const UbGemmArgs* a) {
   GemmPlan pl;
   const bool dual = a->dual != 0;
@@ -1021,6 +1074,9 @@ static GemmPlan plan_gemm(const UbGemmArgs* a) {
   if (splits > num_kb) splits = num_kb;
   while (splits & (splits - 1)) splits &= splits - 1;  // cluster sizes 1, 2, 4, 8
   while (splits > 1 && (splits - 1) * ((num_kb + splits - 1) / splits) >= num_kb) --splits;  // no empty split
+  // an automatic split must fit in one wave of clusters
+  if (a->splits <= 0 && !grouped)
+    while (splits > 1 && pl.tiles > max_active_clusters(splits)) splits >>= 1;
   if (dual && tn == 256 && splits > 1) {
     // the parked fp32 partials of a 2 x 256-token tile do not fit in shared memory
     UbGemmArgs b = *a;
@@ -1073,16 +1129,20 @@ static GemmPlan plan_gemm(const UbGemmArgs* a) {
       if (s2 < 1) s2 = 1;
       while (s2 & (s2 - 1)) s2 &= s2 - 1;
       while (s2 > 1 && (num_kb < 16 * s2 || (s2 - 1) * ((num_kb + s2 - 1) / s2) >= num_kb)) s2 >>= 1;
+      while (s2 > 1 && tiles2 > max_active_clusters(2 * s2)) s2 >>= 1;      // one wave of clusters of 2 * s2 CTAs
     }
+    // tiles beyond one round of the SM pairs: the 1-CTA schedule splits its thin last round over K, pairs cannot
+    const int pairs_now = max_active_clusters(2);
+    const bool ragged = tiles2 > pairs_now && (tiles2 % pairs_now) * 2 <= pairs_now && (tiles2 % pairs_now) != 0;
     const int want_s = a->pair_splits > 0 ? a->pair_splits : s2;
-    if (want == 2 || (a->tile_tokens <= 0 && ((gains && enough) || want_s > 1))) {
+    if (want == 2 || (a->tile_tokens <= 0 && ((gains && enough && !(ragged && !dual)) || want_s > 1))) {
       pl.pair = 1;
       pl.tn = tn2;
       pl.tiles = tiles2;
       pl.tail_tiles = 0;
       pl.tail_splits = 1;
       pl.splits = (!dual && tn2 >= 128 && want_s > 1) ? want_s : 1;
-      pl.ctas = pl.splits > 1 ? 2 * pl.splits * tiles2 : 2 * (tiles2 < sms / 2 ? tiles2 : sms / 2);
+      pl.ctas = pl.splits > 1 ? 2 * pl.splits * tiles2 : 2 * (tiles2 < pairs_now ? tiles2 : pairs_now);
     }
   }
   return pl;
