@@ -21,7 +21,6 @@ namespace dmma {
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 constexpr int KT = 64;       // tokens per tile (16 per warp)
-constexpr int STAGES = 3;
 constexpr int ROWS = 16;     // query heads per CTA (MMA M)
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool pred) {
@@ -48,20 +47,27 @@ __device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
   return (uint32_t)(row * D * 2 + ((chunk ^ (row & 7)) << 4));
 }
 
-template <int D>
+// STAGES = 3 for long key ranges (two tiles in flight behind the one being used, two CTAs per SM); STAGES = 2 for
+// the short suffix ranges of the cascade, where a CTA has only two to four tiles and what hides the latency of its
+// dependent loads is a third resident CTA.
+template <int D, int STAGES>
 struct Smem {
   static constexpr int STAGE_BYTES = 2 * KT * D * 2;                 // K tile then V tile
   static constexpr int RED_BYTES = 4 * ROWS * D * 4;                 // per-warp partial outputs (fp32)
   static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES > RED_BYTES ? STAGES * STAGE_BYTES : RED_BYTES;
   static constexpr int Q_OFF = PIPE_BYTES;                           // [16][D] bf16, swizzled
   static constexpr int ML_OFF = Q_OFF + ROWS * D * 2;                // [4][16][2] floats
-  static constexpr int TOTAL = ML_OFF + 4 * ROWS * 2 * 4;
+  static constexpr int BT_OFF = ML_OFF + 4 * ROWS * 2 * 4;           // block-table entries of this CTA's key range
+  static constexpr int BT_MAX = 256;
+  static constexpr int TOTAL = BT_OFF + BT_MAX * 4;
 };
 
-template <int D>
+template <int D, int STAGES>
 __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const UbAttnArgs a, const int gchunks) {
+  pdl_launch_dependents();
+  pdl_wait();          // no global access before the previous kernel has completed
   constexpr int CPR = D / 8;
-  using S = Smem<D>;
+  using S = Smem<D, STAGES>;
   extern __shared__ __align__(128) uint8_t dsm[];
   uint8_t* q_sm = dsm + S::Q_OFF;
   float (*red_o)[ROWS][D] = reinterpret_cast<float (*)[ROWS][D]>(dsm);
@@ -102,6 +108,14 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const UbAttnArgs a
   const int bs_shift = 31 - __clz(a.block_size);
   const int tile_origin = kv_lo & ~(a.block_size - 1);
   const int n_tiles = kv_hi > tile_origin ? (kv_hi - tile_origin + KT - 1) / KT : 0;
+  // All block-table entries of the range are fetched at once, before the first copy: read one by one in front of
+  // each page they put a dependent global load (and its latency) in front of every group of copies.
+  int* bt_sm = reinterpret_cast<int*>(dsm + S::BT_OFF);
+  const int page0 = tile_origin >> bs_shift;
+  const int n_pages = kv_hi > tile_origin ? ((kv_hi - tile_origin + a.block_size - 1) >> bs_shift) : 0;
+  for (int i = threadIdx.x; i < min(n_pages, S::BT_MAX); i += 128)
+    bt_sm[i] = (page0 + i) < a.max_blocks_per_seq ? bt[page0 + i] : -1;
+  __syncthreads();                                       // q_sm and bt_sm complete
   const int pages_per_tile = KT >> bs_shift;
   const int chunks_per_page = CPR << bs_shift;
   auto issue_tile = [&](int t) {
@@ -114,7 +128,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const UbAttnArgs a
         long long base = 0;
         if (nvalid > 0) {
           const int bi = pos0 >> bs_shift;
-          const int blk = bi < a.max_blocks_per_seq ? bt[bi] : -1;
+          const int blk = (bi - page0) < S::BT_MAX ? bt_sm[bi - page0] : (bi < a.max_blocks_per_seq ? bt[bi] : -1);
           if (blk < 0 || blk >= a.num_blocks) set_err(a.err, ERR_BOUNDS, seq);
           else base = (((long long)blk * a.Hkv + kvh) << bs_shift) * D;
         }
@@ -131,7 +145,6 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const UbAttnArgs a
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
   for (int t = 0; t < STAGES - 1; ++t) issue_tile(t);
-  __syncthreads();                                       // q_sm complete
 
   uint32_t qf[D / 16][4];
 #pragma unroll
@@ -280,21 +293,21 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const UbAttnArgs a
   }
 }
 
-template <int D>
+template <int D, int STAGES>
 static int launch(const UbAttnArgs& a, cudaStream_t st) {
-  constexpr int SMEM = Smem<D>::TOTAL;
+  constexpr int SMEM = Smem<D, STAGES>::TOTAL;
   static bool attr_set[UB_MAX_DEVICES] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < UB_MAX_DEVICES && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return -(int)e;
     attr_set[dev] = true;
   }
   const int Gtot = a.Hq / a.Hkv;
   const int gchunks = (Gtot + ROWS - 1) / ROWS;
   dim3 grid(a.num_seqs, a.Hkv * gchunks, a.splits);
-  attn_decode_mma_kernel<D><<<grid, 128, SMEM, st>>>(a, gchunks);
+  ub::launch_pdl(attn_decode_mma_kernel<D, STAGES>, grid, dim3(128), (size_t)SMEM, st, a, gchunks);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }
@@ -315,5 +328,7 @@ extern "C" int ub_attn_decode_mma_supported(const UbAttnArgs* a) {
 
 extern "C" int ub_attn_decode_mma_main(const UbAttnArgs* a, void* stream) {
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  return a->D == 64 ? ub::dmma::launch<64>(*a, st) : ub::dmma::launch<128>(*a, st);
+  // suffix ranges after a shared prefix are short: favour a third resident CTA over a deeper ring
+  if (a->kv_start > 0) return a->D == 64 ? ub::dmma::launch<64, 2>(*a, st) : ub::dmma::launch<128, 2>(*a, st);
+  return a->D == 64 ? ub::dmma::launch<64, 3>(*a, st) : ub::dmma::launch<128, 3>(*a, st);
 }

@@ -40,7 +40,9 @@ constexpr int SMEM_K = SMEM_Q + TILE_BYTES;         // 2 stages
 constexpr int SMEM_V = SMEM_K + 2 * TILE_BYTES;     // 2 stages
 constexpr int SMEM_P = SMEM_V + 2 * TILE_BYTES;
 constexpr int SMEM_BAR = SMEM_P + TILE_BYTES;       // 192 KB of tiles, then barriers
-constexpr int SMEM_TOTAL = SMEM_BAR + 256 + 1024;   // + alignment slack
+constexpr int SMEM_XCH = SMEM_BAR + 256;            // row maxima exchanged between the two softmax warpgroups
+constexpr int SMEM_TOTAL = SMEM_XCH + 3072 + 1024;  // 2 KB of maxima + 1 KB of row sums, + alignment slack
+constexpr int THREADS = 320;                        // TMA warp, MMA warp, 2 x 4 softmax warps
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 
@@ -74,7 +76,7 @@ struct Params {
 };
 
 template <bool P_TMEM>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                        const __grid_constant__ CUtensorMap tmap_v, const Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -92,6 +94,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  pdl_wait();          // the sequence metadata read below may be written by earlier kernels of the stream
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seq = blockIdx.z, kh = blockIdx.y, G = p.G;
   const int TOK = BM / G;                                   // query tokens per tile
@@ -115,9 +118,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 128);
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 256);
     }
-    mbar_init(p_full, 128);
+    mbar_init(p_full, 256);
     mbar_init(o_full, 1);
     fence_mbar_init();
     tma_prefetch_desc(&tmap_q);
@@ -132,6 +135,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();     // only now: this CTA holds its TMEM columns before any CTA of the next kernel can exist
   const uint32_t tmem_s = tmem_base;            // S buffers: columns [0,128) and [128,256)
   const uint32_t tmem_o = tmem_base + 256;      // O tile: columns [256,384)
 
@@ -253,7 +257,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       }
     }
   } else {
-    // ------------------------------ softmax + output (warps 2..5) ------------------------------
+    // ------------------------------ softmax + output (warps 2..9) ------------------------------
+    // Two warpgroups share every query row: warps 2..5 take keys [0, 64) of a tile, warps 6..9 keys [64, 128) (a warp
+    // may read the TMEM lanes 32 * (warp % 4) .. + 32, at any column).  With two softmax warps per scheduler one
+    // warp's fixed-latency stalls are filled by the other.  The halves agree on the row maximum through shared
+    // memory (one named barrier per tile); each keeps its own partial row sum and its own 64 columns of O.
+    const int half = (warp - 2) >> 2;
     const int qd = warp & 3;                    // TMEM lane quarter this warp may read
     const int row = qd * 32 + lane;             // packed query row == TMEM lane
     const uint32_t lane_off = uint32_t(qd * 32) << 16;
@@ -267,45 +276,50 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     // rescaled rarely.  The final O / l does not depend on the reference.
     float m = -CUDART_INF_F, l = 0.f;
     uint8_t* p_row = smem + SMEM_P + row * 128;
+    float* xch = reinterpret_cast<float*>(smem + SMEM_XCH);       // [2 tile parities][2 halves][128 rows]
     // every wait is agreed on by the whole warp: the TMEM loads and stores below are warp-wide instructions
     auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) {
       return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, p.err, code)) != 0;
     };
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
+    for (int j = 0; j < n_tiles; ++j) {
       const int b = j & 1;
-      if (!wait_all(&s_full[b], (j >> 1) & 1, 530)) { ok = false; break; }
+      ok = ok && wait_all(&s_full[b], (j >> 1) & 1, 530);
       tc_fence_after();
       const uint32_t s_addr = tmem_s + b * BN + lane_off;
-      const int key0 = (tile0 + j) * BN;
+      const int key0 = (tile0 + j) * BN + half * 64;
       // Tiles that lie completely inside [kv_lo, limit) need no per-key predicate (all but the first and last ones).
-      const bool full = key0 >= kv_lo && key0 + BN <= limit;
-      // the whole S row of this thread: 128 fp32 in registers
-      uint32_t sv[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32(s_addr + c * 32, sv[c]);
+      const bool full = key0 >= kv_lo && key0 + 64 <= limit;
+      // this thread's half of the S row: 64 fp32 in registers
+      uint32_t sv[2][32];
+      tmem_ld_32x32(s_addr + half * 64, sv[0]);
+      tmem_ld_32x32(s_addr + half * 64 + 32, sv[1]);
       tmem_ld_wait();
       if (!P_TMEM) {
         tc_fence_before();
         mbar_arrive(&s_empty[b]);
       }
-      // one warp per scheduler has nobody to hide its ALU latency: keep four independent chains per reduction
       float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
       if (full) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
       } else {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int k = key0 + c * 32 + i;
             if (k < limit && k >= kv_lo) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
           }
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // both halves of the row must use the same reference: exchange the partial maxima.  The two parity slots
+      // alternate, and the barrier of tile j + 1 separates the reads of tile j from the writes of tile j + 2.
+      xch[(b * 2 + half) * 128 + row] = mx;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      mx = fmaxf(mx, xch[(b * 2 + (half ^ 1)) * 128 + row]);
       const float m_tile = mx * p.scale_log2;
       float alpha = 1.f;
       if (m_tile > m + 8.f) {                       // also the first visible tile (m == -inf)
@@ -315,12 +329,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       const float m_use = (m == -CUDART_INF_F) ? 0.f : m;   // nothing visible so far: every p is masked to 0
       if (!P_TMEM && j > 0) {
         // the single P buffer in shared memory is free once P V of the previous tile has completed
-        if (!wait_all(o_full, (j - 1) & 1, 531)) { ok = false; break; }
+        ok = ok && wait_all(o_full, (j - 1) & 1, 531);
       }
       float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t packed[32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t packed[16];
+      for (int c = 0; c < 2; ++c) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           float p0 = ex2_approx(fmaf(__uint_as_float(sv[c][2 * i]), p.scale_log2, -m_use));
@@ -331,42 +345,40 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
             if (!(k0 + 1 < limit && k0 + 1 >= kv_lo)) p1 = 0.f;
           }
           ps4[i & 3] += p0 + p1;
-          packed[i] = pack_bf16x2(p0, p1);
-        }
-        if (P_TMEM) {
-          // 32 keys = 16 packed columns; they overwrite the head of this tile's S buffer, already in registers
-#pragma unroll
-          for (int i = 0; i < 16; ++i) sv[c >> 1][(c & 1) * 16 + i] = packed[i];
-        } else {
-          // 32 keys = 4 chunks of 16 B; key half = c / 2, chunk index inside the 128-B row = (c & 1) * 4 + q
-          uint8_t* base = p_row + (c >> 1) * HALF_BYTES;
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            const int chunk = (c & 1) * 4 + q4;
-            *reinterpret_cast<uint4*>(base + ((chunk ^ (row & 7)) << 4)) =
-                make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
-          }
+          packed[c * 16 + i] = pack_bf16x2(p0, p1);
         }
       }
       if (P_TMEM) {
-        tmem_st_32x32(s_addr, sv[0]);
-        tmem_st_32x32(s_addr + 32, sv[1]);
+        // 64 keys = 32 packed columns; the two halves together overwrite the first 64 columns of this tile's S
+        // buffer.  The other half may still be reading its S columns [64, 128) when half 0 writes [0, 32), and
+        // half 1 writes [32, 64) which half 0 has read before the barrier above: no column is written before its
+        // reader has it in registers.
+        tmem_st_32x32(s_addr + half * 32, packed);
         // O may only be touched (and the next P V issued) after P V of the previous tile; by now it has had the
         // whole softmax of this tile to finish
-        if (j > 0 && !wait_all(o_full, (j - 1) & 1, 531)) { ok = false; break; }
+        if (j > 0) ok = ok && wait_all(o_full, (j - 1) & 1, 531);
+      } else {
+        // 64 keys = one 64-key half of the K-major P tile: 8 chunks of 16 B, swizzled by the row
+        uint8_t* base = p_row + half * HALF_BYTES;
+#pragma unroll
+        for (int q8 = 0; q8 < 8; ++q8) {
+          *reinterpret_cast<uint4*>(base + ((q8 ^ (row & 7)) << 4)) =
+              make_uint4(packed[4 * q8], packed[4 * q8 + 1], packed[4 * q8 + 2], packed[4 * q8 + 3]);
+        }
       }
       l = l * alpha + ((ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
-      // rescale the O rows whose reference moved (warp-uniform decision: the TMEM accesses are warp-wide)
+      // rescale the O rows whose reference moved (warp-uniform decision: the TMEM accesses are warp-wide); each half
+      // owns 64 of the 128 output columns
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
         tc_fence_after();
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t r[32];
-          tmem_ld_32x32(tmem_o + lane_off + c * 32, r);
+          tmem_ld_32x32(tmem_o + lane_off + half * 64 + c * 32, r);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st_32x32(tmem_o + lane_off + c * 32, r);
+          tmem_st_32x32(tmem_o + lane_off + half * 64 + c * 32, r);
         }
       }
       tmem_st_wait();
@@ -374,8 +386,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       fence_proxy_async_smem();
       mbar_arrive(p_full);
     }
-    if (ok && n_tiles > 0) ok = wait_all(o_full, (n_tiles - 1) & 1, 532);
+    if (n_tiles > 0) ok = ok && wait_all(o_full, (n_tiles - 1) & 1, 532);
     tc_fence_after();
+    // the row sum is the sum of the two halves' partial sums (same reference m in both)
+    float* lx = xch + 512;                                        // its own slots: a slow thread may still read a maximum
+    lx[half * 128 + row] = l;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    l += lx[(half ^ 1) * 128 + row];
     if (ok) {
       float inv = l > 0.f ? 1.f / l : 0.f;
       float lse_v = l > 0.f ? (m * LN2 + logf(l)) : -CUDART_INF_F;
@@ -395,36 +412,37 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       }
       __nv_bfloat16* dst = p.out + (long long)tok * p.o_stride + (long long)head * HD;
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = 0; c < 2; ++c) {
+        const int d0 = half * 64 + c * 32;
         uint32_t r[32];
-        tmem_ld_32x32(tmem_o + lane_off + c * 32, r);      // never-written TMEM (no visible tile) is not used: l == 0
+        tmem_ld_32x32(tmem_o + lane_off + d0, r);          // never-written TMEM (no visible tile) is not used: l == 0
         tmem_ld_wait();
         if (row_valid) {
-        float o[32];
+          float o[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = (l > 0.f) ? __uint_as_float(r[i]) * cb : 0.f;
-        if (src != nullptr) {
+          for (int i = 0; i < 32; ++i) o[i] = (l > 0.f) ? __uint_as_float(r[i]) * cb : 0.f;
+          if (src != nullptr) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(src + c * 32 + i);
-            const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
+            for (int i = 0; i < 32; i += 8) {
+              const uint4 raw = *reinterpret_cast<const uint4*>(src + d0 + i);
+              const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              o[i + 2 * e] += bf16_lo(w[e]) * ca;
-              o[i + 2 * e + 1] += bf16_hi(w[e]) * ca;
+              for (int e = 0; e < 4; ++e) {
+                o[i + 2 * e] += bf16_lo(w[e]) * ca;
+                o[i + 2 * e + 1] += bf16_hi(w[e]) * ca;
+              }
             }
           }
-        }
 #pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          *reinterpret_cast<uint4*>(dst + c * 32 + i) =
-              make_uint4(pack_bf16x2(o[i], o[i + 1]), pack_bf16x2(o[i + 2], o[i + 3]),
-                         pack_bf16x2(o[i + 4], o[i + 5]), pack_bf16x2(o[i + 6], o[i + 7]));
-        }
+          for (int i = 0; i < 32; i += 8) {
+            *reinterpret_cast<uint4*>(dst + d0 + i) =
+                make_uint4(pack_bf16x2(o[i], o[i + 1]), pack_bf16x2(o[i + 2], o[i + 3]),
+                           pack_bf16x2(o[i + 4], o[i + 5]), pack_bf16x2(o[i + 6], o[i + 7]));
+          }
         }
         __syncwarp();
       }
-      if (p.lse != nullptr && row_valid) p.lse[(long long)tok * p.Hq + head] = lse_v;
+      if (p.lse != nullptr && row_valid && half == 0) p.lse[(long long)tok * p.Hq + head] = lse_v;
     }
   }
 
@@ -543,9 +561,9 @@ extern "C" int ub_attn_prefill_tc(const UbAttnArgs* a, void* stream_v) {
   }
   dim3 grid((a->max_q_len + TOK - 1) / TOK, a->Hkv, a->num_seqs);
   if (p_tmem)
-    attn_prefill_tc_kernel<true><<<grid, 192, SMEM_TOTAL, reinterpret_cast<cudaStream_t>(stream_v)>>>(tq, tk, tv, p);
+    launch_pdl(attn_prefill_tc_kernel<true>, grid, dim3(THREADS), (size_t)SMEM_TOTAL, reinterpret_cast<cudaStream_t>(stream_v), tq, tk, tv, p);
   else
-    attn_prefill_tc_kernel<false><<<grid, 192, SMEM_TOTAL, reinterpret_cast<cudaStream_t>(stream_v)>>>(tq, tk, tv, p);
+    launch_pdl(attn_prefill_tc_kernel<false>, grid, dim3(THREADS), (size_t)SMEM_TOTAL, reinterpret_cast<cudaStream_t>(stream_v), tq, tk, tv, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }

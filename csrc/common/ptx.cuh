@@ -9,6 +9,7 @@
 // context stays usable.  Results of such a launch are garbage; the host checks
 // the word after the step.
 #pragma once
+#include "launch.cuh"
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>

@@ -164,7 +164,7 @@ struct GemmSmem {
   static constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * A_BYTES + B_BYTES;
   static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
   // SPLIT-K parks its fp32 partial tile on top of the (then idle) pipeline stages.
-  static constexpr int PARTIAL_BYTES = (DUAL ? 2 : 1) * TN * BM_W * 4;
+  static constexpr int PARTIAL_BYTES = (DUAL ? 2 : 1) * (TN + 8) * BM_W * 4;   // splits x ceil(TN / splits) rows, splits <= 8
   static constexpr int DATA_BYTES = SPLITK ? (TILE_BYTES > PARTIAL_BYTES ? TILE_BYTES : PARTIAL_BYTES)
                                            : TILE_BYTES + STAGING_BYTES;
   static constexpr int TOTAL = DATA_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
@@ -211,80 +211,102 @@ __device__ __forceinline__ void emit8(const GemmParams& p, int m, int m_end, int
   }
 }
 
-// Split-K finish: sums the fp32 partial tiles that the CTAs of a cluster parked in their shared memory ([tokens][128]
-// floats, a second tile behind it for the up half of a gated GEMM) and runs the epilogue on token rows [r0, r1).
-// The partial of split sp lives in cluster rank sp * rank_stride + rank_off.  All remote loads of a batch of items
-// are issued before the first one is used: a distributed-shared-memory load takes several hundred cycles, and one
-// item at a time left the reduction latency-bound.
-template <int S, bool DUAL>
-__device__ __forceinline__ void splitk_reduce(const GemmParams& p, uint32_t base, int tn, int r0, int r1, int tid_e, int m0,
-                                              int n0, bool vec_ok, uint32_t rank_stride, uint32_t rank_off) {
-  constexpr int IT = (DUAL ? 4 : 8) / S > 0 ? (DUAL ? 4 : 8) / S : 1;     // items in flight per thread
-  const int n_items = (r1 - r0) * 16;
-  for (int idx0 = tid_e; idx0 < n_items; idx0 += 128 * IT) {
-    float4 ga[IT][S], gb[IT][S], ua[DUAL ? IT : 1][S], ub[DUAL ? IT : 1][S];
-#pragma unroll
-    for (int i = 0; i < IT; ++i) {
-      const int idx = idx0 + i * 128;
-      if (idx < n_items) {
-        const int tok = r0 + (idx >> 4), c8 = idx & 15;
-        const uint32_t off = uint32_t(tok * BM_W + c8 * 8) * 4u;
-#pragma unroll
-        for (int sp = 0; sp < S; ++sp) {
-          const uint32_t src = uint32_t(sp) * rank_stride + rank_off;
-          const uint32_t ra = mapa_u32(base + off, src);
-          ga[i][sp] = ld_dsmem_f4(ra);
-          gb[i][sp] = ld_dsmem_f4(ra + 16);
-          if (DUAL) {
-            const uint32_t rb = mapa_u32(base + uint32_t(tn * BM_W * 4) + off, src);
-            ua[i][sp] = ld_dsmem_f4(rb);
-            ub[i][sp] = ld_dsmem_f4(rb + 16);
-          }
-        }
-      }
+// Optional timeline of one launch (UB_GEMM_DEBUG bit 4): each CTA of the 1-CTA kernel records the global timer at a few
+// points of its first tile; ub_gemm_debug_timeline copies the table out.  Slots: 0 kernel entry, 1 setup done,
+// 2 first operand stage landed, 3 last MMA of the first tile issued, 4 accumulator complete, 5 epilogue stores
+// issued, 6 split-K reduction done (or 0), 7 CTA exit.
+constexpr int TS_CTAS = 512;
+__device__ unsigned long long g_gemm_ts[TS_CTAS][8];
+__device__ __forceinline__ void ts_mark(const GemmParams& p, int slot) {
+  if (p.dbg & 4) {
+    const unsigned cta = blockIdx.x + gridDim.x * blockIdx.y;
+    if (cta < TS_CTAS) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+      g_gemm_ts[cta][slot] = t;
     }
+  }
+}
+
+// Split-K finish.  The CTAs of a cluster hold partial accumulators of the same tile; CTA d of the cluster finishes the
+// token rows [d * per, (d + 1) * per).  Every CTA PUSHES its partial rows into a slot of the owner's shared memory
+// (slot = sender's split index) with distributed-shared-memory stores, which are fire-and-forget; after one cluster
+// barrier each owner sums its slots with local loads and runs the epilogue.  (Pulling the partials with remote
+// loads instead cost 10 us per 128 x 256 tile: every load pays the SM-to-SM round trip.)  The slots overlay the
+// pipeline stages, so the pushes start only after a cluster barrier that follows everybody's last MMA.
+// Slot layout in the owner: [splits][per][128] floats, then the same again for the up half of a gated GEMM.
+__device__ __forceinline__ void st_dsmem_f32(uint32_t addr, uint32_t bits) {
+  asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(addr), "r"(bits) : "memory");
+}
+
+template <int TN, int CH, bool DUAL>
+__device__ __forceinline__ void splitk_scatter(const GemmParams& p, uint32_t smem_base, uint32_t lane_addr, int et,
+                                               int my_split, uint32_t rank_stride, uint32_t rank_off) {
+  const int S = p.splits, per = (TN + S - 1) / S;
+  const uint32_t up_off = uint32_t(S * per) * BM_W * 4u;
+#pragma unroll 1
+  for (int c = 0; c < TN / CH; ++c) {
+    uint32_t r[CH], r2[CH];
+    if constexpr (CH == 32) {
+      tmem_ld_32x32(lane_addr + c * CH, r);
+      if (DUAL) tmem_ld_32x32(lane_addr + TN + c * CH, r2);
+    } else {
+      tmem_ld_32x16(lane_addr + c * CH, r);
+      if (DUAL) tmem_ld_32x16(lane_addr + TN + c * CH, r2);
+    }
+    tmem_ld_wait();
+    int d = (c * CH) / per;
+    int next = (d + 1) * per;
+    uint32_t win = mapa_u32(smem_base, uint32_t(d) * rank_stride + rank_off);
 #pragma unroll
-    for (int i = 0; i < IT; ++i) {
-      const int idx = idx0 + i * 128;
-      if (idx < n_items) {
-        const int tok = r0 + (idx >> 4), c8 = idx & 15;
-        float g[8] = {0, 0, 0, 0, 0, 0, 0, 0}, up[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-        for (int sp = 0; sp < S; ++sp) {
-          const float4 a = ga[i][sp], b = gb[i][sp];
-          g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w; g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
-          if (DUAL) {
-            const float4 c = ua[i][sp], d = ub[i][sp];
-            up[0] += c.x; up[1] += c.y; up[2] += c.z; up[3] += c.w; up[4] += d.x; up[5] += d.y; up[6] += d.z; up[7] += d.w;
-          }
-        }
-        const int nn = n0 + c8 * 8;
-        uint32_t gv[8], uv[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          float x = g[e];
-          if (!DUAL && p.bias != nullptr && nn + e < p.N) x += __bfloat162float(p.bias[nn + e]) / p.out_scale;
-          gv[e] = __float_as_uint(x);
-          uv[e] = __float_as_uint(up[e]);
-        }
-        epi_values<8, DUAL>(gv, uv, p.out_scale, 0.f, p.act);
-        float v[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(gv[e]);
-        emit8(p, m0 + tok, p.M, nn, v, vec_ok);
+    for (int j = 0; j < CH; ++j) {
+      const int tok = c * CH + j;
+      if (tok >= next) {
+        ++d;
+        next += per;
+        win = mapa_u32(smem_base, uint32_t(d) * rank_stride + rank_off);
       }
+      const uint32_t off = uint32_t((my_split * per + (tok - (next - per))) * BM_W + et) * 4u;
+      st_dsmem_f32(win + off, r[j]);
+      if (DUAL) st_dsmem_f32(win + up_off + off, r2[j]);
     }
   }
 }
 
 template <bool DUAL>
-__device__ __forceinline__ void splitk_reduce_any(const GemmParams& p, uint32_t base, int tn, int r0, int r1, int tid_e,
-                                                  int m0, int n0, bool vec_ok, uint32_t rank_stride, uint32_t rank_off) {
-  switch (p.splits) {
-    case 2: splitk_reduce<2, DUAL>(p, base, tn, r0, r1, tid_e, m0, n0, vec_ok, rank_stride, rank_off); break;
-    case 4: splitk_reduce<4, DUAL>(p, base, tn, r0, r1, tid_e, m0, n0, vec_ok, rank_stride, rank_off); break;
-    case 8: splitk_reduce<8, DUAL>(p, base, tn, r0, r1, tid_e, m0, n0, vec_ok, rank_stride, rank_off); break;
-    default: splitk_reduce<1, DUAL>(p, base, tn, r0, r1, tid_e, m0, n0, vec_ok, rank_stride, rank_off); break;
+__device__ __forceinline__ void splitk_finish(const GemmParams& p, const uint8_t* smem, int tn, int r0, int r1, int tid_e,
+                                              int m0, int n0, bool vec_ok) {
+  const int S = p.splits, per = (tn + S - 1) / S;
+  const float* part = reinterpret_cast<const float*>(smem);
+  const float* part_up = part + (size_t)S * per * BM_W;
+  const int n_items = (r1 - r0) * 16;
+  for (int idx = tid_e; idx < n_items; idx += 128) {
+    const int lt = idx >> 4, c8 = idx & 15;
+    float g[8] = {0, 0, 0, 0, 0, 0, 0, 0}, up[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int sp = 0; sp < S; ++sp) {
+      const float* src = part + ((size_t)(sp * per + lt) * BM_W + c8 * 8);
+      const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+      g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w; g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
+      if (DUAL) {
+        const float* su = part_up + ((size_t)(sp * per + lt) * BM_W + c8 * 8);
+        const float4 c = *reinterpret_cast<const float4*>(su), d = *reinterpret_cast<const float4*>(su + 4);
+        up[0] += c.x; up[1] += c.y; up[2] += c.z; up[3] += c.w; up[4] += d.x; up[5] += d.y; up[6] += d.z; up[7] += d.w;
+      }
+    }
+    const int nn = n0 + c8 * 8;
+    uint32_t gv[8], uv[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float x = g[e];
+      if (!DUAL && p.bias != nullptr && nn + e < p.N) x += __bfloat162float(p.bias[nn + e]) / p.out_scale;
+      gv[e] = __float_as_uint(x);
+      uv[e] = __float_as_uint(up[e]);
+    }
+    epi_values<8, DUAL>(gv, uv, p.out_scale, 0.f, p.act);
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(gv[e]);
+    emit8(p, m0 + r0 + lt, p.M, nn, v, vec_ok);
   }
 }
 
@@ -332,6 +354,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   }
 
   if (threadIdx.x == 0) {
+    ts_mark(p, 0);
     *abort_flag = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -353,6 +376,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Programmatic dependent launch: this CTA owns its TMEM columns and barriers now, so the next kernel's CTAs may be
+  // scheduled; nothing global has been touched yet, and nothing is before the previous kernel has completed.
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x == 0) ts_mark(p, 1);
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -444,6 +472,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&full_bar[s], ph, abort_flag, p.err, 200 + s)) { dead = true; break; }
+          if (it == 0) ts_mark(p, 2);
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + s * S::STAGE_BYTES);
           const uint32_t b_addr = a_addr + (DUAL ? 2 : 1) * S::A_BYTES;
@@ -461,6 +490,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
           umma_commit(&empty_bar[s]);  // stage is free once these MMAs have read it
         }
         umma_commit(&tmem_full_bar[ab]);
+        if (ui == 1) ts_mark(p, 3);
       }
     }
   } else {
@@ -481,28 +511,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       const uint32_t aph = NBUF == 1 ? (ui & 1) : ((ui >> 1) & 1);
       ++ui;
       mbar_wait(&tmem_full_bar[ab], aph, abort_flag, p.err, 300 + ab);
+      if (ui == 1 && tid_e == 0) ts_mark(p, 4);
       tc_fence_after();
       const uint32_t lane_addr = tmem_base + ab * ACC_COLS + (uint32_t(q * 32) << 16);
       if constexpr (SPLITK) {
-        // Park the raw fp32 partial tile in shared memory: [TN][128] (+ a second one for the up half).
-        float* part = reinterpret_cast<float*>(smem);
-#pragma unroll 1
-        for (int c = 0; c < TN / CH; ++c) {
-          uint32_t r[CH], r2[CH];
-          if constexpr (CH == 32) {
-            tmem_ld_32x32(lane_addr + c * CH, r);
-            if (DUAL) tmem_ld_32x32(lane_addr + TN + c * CH, r2);
-          } else {
-            tmem_ld_32x16(lane_addr + c * CH, r);
-            if (DUAL) tmem_ld_32x16(lane_addr + TN + c * CH, r2);
-          }
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < CH; ++j) {
-            part[(c * CH + j) * BM_W + et] = __uint_as_float(r[j]);
-            if (DUAL) part[TN * BM_W + (c * CH + j) * BM_W + et] = __uint_as_float(r2[j]);
-          }
-        }
+        // the partial stays in TMEM until every CTA of the cluster has finished its MMAs (see below)
+        (void)lane_addr;
       } else {
         const int n = n0 + et;
         float bias_v = 0.f;
@@ -562,6 +576,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         }
       }
     }
+    if (tid_e == 0) ts_mark(p, 5);
     if (!SPLITK && p.rs_world > 0) {
       // Publish: every storing thread fences to system scope, then one thread per peer bumps its counter.
       __threadfence_system();
@@ -571,26 +586,36 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   }
 
   if constexpr (SPLITK) {
-    // All CTAs of the cluster have parked their partials; reduce a slice of token rows each.
+    // Every CTA's MMAs are complete (its epilogue warps have seen tmem_full), so the operand stages of all CTAs may be
+    // overwritten by the partial-tile slots.
     tc_fence_before();
     cluster_sync_all();
-    if (warp >= 2 && tile_begin + (int)blockIdx.y < total_tiles) {
+    const bool sk_valid = tile_begin + (int)blockIdx.y < total_tiles;
+    if (warp >= 2 && sk_valid) {
+      tc_fence_after();
+      constexpr int CHS = TN >= 32 ? 32 : 16;
+      const int q = warp & 3;
+      splitk_scatter<TN, CHS, DUAL>(p, smem_u32(smem), tmem_base + (uint32_t(q * 32) << 16), q * 32 + lane, crank, 1u, 0u);
+    }
+    tc_fence_before();
+    cluster_sync_all();                       // all slots are written (release / acquire at cluster scope)
+    if (warp >= 2 && sk_valid) {
       const int u = tile_begin + blockIdx.y;
       const int m0 = (u % num_m) * TN, n0 = (u / num_m) * BM_W;
       const int tid_e = threadIdx.x - 64;
       const int per = (TN + p.splits - 1) / p.splits;
-      const int r0 = crank * per, r1 = min(TN, r0 + per);
+      const int r0 = min(TN, crank * per), r1 = min(TN, r0 + per);
       const bool vec_ok = (p.N % 8 == 0) && (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
                           (p.residual == nullptr ||
                            ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
-      const uint32_t base = smem_u32(smem);
-      splitk_reduce_any<DUAL>(p, base, TN, r0, r1, tid_e, m0, n0, vec_ok, 1u, 0u);
+      splitk_finish<DUAL>(p, smem, TN, r0, r1, tid_e, m0, n0, vec_ok);
       if (p.rs_world > 0) {
         __threadfence_system();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (tid_e < p.rs_world) red_release_sys_add_u32(p.rs_peer_flag[tid_e], 1u);
       }
     }
+    if (threadIdx.x == 64) ts_mark(p, 6);
     cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
   }
 
@@ -604,6 +629,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if (threadIdx.x == 0) ts_mark(p, 7);
 }
 
 // ----------------------------------------------------------------------------
@@ -669,7 +695,7 @@ struct Gemm2Smem {
   static constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * A_BYTES + B_BYTES;
   static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
   // split-K parks the fp32 partial tile [TN][128] on top of the (then idle) pipeline stages
-  static constexpr int PARTIAL_BYTES = (DUAL ? 2 : 1) * TN * BM_W * 4;
+  static constexpr int PARTIAL_BYTES = (DUAL ? 2 : 1) * (TN + 8) * BM_W * 4;   // splits x ceil(TN / splits) rows, splits <= 8
   static_assert(!SPLITK || PARTIAL_BYTES <= TILE_BYTES, "partial tile does not fit in the stage memory");
   static constexpr int DATA_BYTES = TILE_BYTES + STAGING_BYTES;
   static constexpr int TOTAL = DATA_BYTES + 1024 + 256;
@@ -848,20 +874,8 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       tc_fence_after();
       const uint32_t lane_addr = tmem_base + ab * ACC_COLS + (uint32_t(q * 32) << 16);
       if constexpr (SPLITK) {
-        // park the raw fp32 partial tile in shared memory: [TN][128] (+ a second one for the up half)
-        float* part = reinterpret_cast<float*>(smem);
-#pragma unroll 1
-        for (int c = 0; c < TN / CH; ++c) {
-          uint32_t r[CH], r2[CH];
-          tmem_ld_32x32(lane_addr + c * CH, r);
-          if (DUAL) tmem_ld_32x32(lane_addr + TN + c * CH, r2);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < CH; ++j) {
-            part[(c * CH + j) * BM_W + et] = __uint_as_float(r[j]);
-            if (DUAL) part[TN * BM_W + (c * CH + j) * BM_W + et] = __uint_as_float(r2[j]);
-          }
-        }
+        // the partial stays in TMEM until every CTA of the cluster has finished its MMAs (see below)
+        (void)lane_addr;
         continue;
       }
       const int n = n0 + et;
@@ -921,22 +935,31 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   }
 
   if constexpr (SPLITK) {
-    // every CTA of the cluster has parked its partial; each pair finishes a slice of the token rows, and inside a
-    // pair each CTA owns its own 128 features: sum the partials of the CTAs with the same rank-in-pair
+    // Every pair's MMAs are complete, so the operand stages of all CTAs may be overwritten by the partial-tile slots.
+    // Pair d of the cluster finishes the token rows [d * per, (d + 1) * per); inside a pair each CTA owns its own 128
+    // features, so partial rows travel between the CTAs of equal rank in their pair.
     tc_fence_before();
     cluster_sync_all();
-    if (warp >= 2 && (int)blockIdx.y < total_tiles) {
+    const bool sk_valid = (int)blockIdx.y < total_tiles;
+    if (warp >= 2 && sk_valid) {
+      tc_fence_after();
+      const int q = warp & 3;
+      splitk_scatter<TN, 32, DUAL>(p, smem_u32(smem), tmem_base + (uint32_t(q * 32) << 16), q * 32 + lane, int(pidx), 2u,
+                                   uint32_t(rank));
+    }
+    tc_fence_before();
+    cluster_sync_all();                       // all slots are written (release / acquire at cluster scope)
+    if (warp >= 2 && sk_valid) {
       const int u = blockIdx.y;
       const int m0 = (u % num_m) * TN;
       const int n0 = (u / num_m) * (2 * BM_W) + int(rank) * BM_W;
       const int tid_e = threadIdx.x - 64;
       const int per = (TN + p.splits - 1) / p.splits;
-      const int r0 = int(pidx) * per, r1 = min(TN, r0 + per);
+      const int r0 = min(TN, int(pidx) * per), r1 = min(TN, r0 + per);
       const bool vec_ok = (p.N % 8 == 0) && (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
                           (p.residual == nullptr ||
                            ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
-      const uint32_t base = smem_u32(smem);
-      splitk_reduce_any<DUAL>(p, base, TN, r0, r1, tid_e, m0, n0, vec_ok, 2u, rank);
+      splitk_finish<DUAL>(p, smem, TN, r0, r1, tid_e, m0, n0, vec_ok);
       if (p.rs_world > 0) {
         __threadfence_system();
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -1165,18 +1188,20 @@ static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmP
   cfg.blockDim = dim3(192, 1, 1);
   cfg.dynamicSmemBytes = S::TOTAL;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  cfg.attrs = attr;
+  cfg.numAttrs = 0;
   if (SPLITK) {
     cfg.gridDim = dim3(pl.splits, pl.tiles, 1);   // the caller passes a plan whose tiles/splits describe THIS launch
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = pl.splits;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
     cfg.numAttrs = 1;
   } else {
     cfg.gridDim = dim3(pl.ctas, 1, 1);
   }
+  cfg.numAttrs += pdl_attr(&attr[cfg.numAttrs]);
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, tx, p);
   return e == cudaSuccess ? 0 : -(int)e;
 }
@@ -1199,13 +1224,13 @@ static int launch_gemm_2cta(const CUtensorMap& tw, const CUtensorMap& tx, const 
   cfg.gridDim = SPLITK ? dim3(2 * pl.splits, pl.tiles, 1) : dim3(pl.ctas, 1, 1);
   cfg.dynamicSmemBytes = S::TOTAL;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = SPLITK ? 2 * pl.splits : 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 1 + pdl_attr(&attr[1]);
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, tx, p);
   return e == cudaSuccess ? 0 : -(int)e;
 }
@@ -1348,4 +1373,10 @@ extern "C" int ub_gemm_tn(const UbGemmArgs* a, void* stream_v) {
   p.splits = pl.tail_splits;
   return dual ? dispatch_tn<true, true>(pl.tn, tw, tx, p, tail_pl, stream)
               : dispatch_tn<false, true>(pl.tn, tw, tx, p, tail_pl, stream);
+}
+
+// Copies the timeline table of the last 1-CTA launches (UB_GEMM_DEBUG bit 4) to `out` ([512][8] uint64, nanoseconds).
+extern "C" int ub_gemm_debug_timeline(unsigned long long* out) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, ub::g_gemm_ts, sizeof(unsigned long long) * ub::TS_CTAS * 8);
+  return e == cudaSuccess ? 0 : -(int)e;
 }

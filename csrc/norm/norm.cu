@@ -53,6 +53,8 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 __global__ void __launch_bounds__(256) norm_kernel(const NormParams p) {
+  pdl_launch_dependents();     // the next kernel may start its private set-up now
+  pdl_wait();                  // nothing global is touched before the previous kernel has completed
   extern __shared__ float row[];  // [H]
   __shared__ float red[32];
   __shared__ int wait_failed;
@@ -243,8 +245,8 @@ extern "C" int ub_norm(const UbNormArgs* a, void* stream_v) {
     cudaFuncSetAttribute(norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
     attr_set[dev] = true;
   }
-  norm_kernel<<<a->T, 256, smem, (cudaStream_t)stream_v>>>(p);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = ub::launch_pdl(norm_kernel, dim3(a->T), dim3(256), smem, (cudaStream_t)stream_v, p);
+  if (e == cudaSuccess) e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }
 

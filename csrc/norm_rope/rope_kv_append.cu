@@ -34,6 +34,8 @@ __device__ __forceinline__ float rope_inv_freq(int i, const UbRopeArgs& a) {
 }
 
 __global__ void __launch_bounds__(128) rope_kv_append_kernel(const UbRopeArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();          // no global access before the previous kernel has completed
   extern __shared__ float sm[];  // [4 warps][D]
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -112,7 +114,7 @@ __global__ void __launch_bounds__(128) rope_kv_append_kernel(const UbRopeArgs a)
 extern "C" int ub_rope_kv_append(const UbRopeArgs* a, void* stream_v) {
   if (a->T <= 0) return 0;
   if (a->D > 512 || (a->rotary_dim & 1) || a->rotary_dim > a->D) return -2;
-  ub::rope_kv_append_kernel<<<a->T, 128, 4 * a->D * sizeof(float), (cudaStream_t)stream_v>>>(*a);
+  ub::launch_pdl(ub::rope_kv_append_kernel, dim3(a->T), dim3(128), 4 * a->D * sizeof(float), (cudaStream_t)stream_v, *a);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }
