@@ -214,9 +214,10 @@ __device__ __forceinline__ void emit8(const GemmParams& p, int m, int m_end, int
 // Optional timeline of one launch (UB_GEMM_DEBUG bit 4): each CTA of the 1-CTA kernel records the global timer at a few
 // points of its first tile; ub_gemm_debug_timeline copies the table out.  Slots: 0 kernel entry, 1 setup done,
 // 2 first operand stage landed, 3 last MMA of the first tile issued, 4 accumulator complete, 5 epilogue stores
-// issued, 6 split-K reduction done (or 0), 7 CTA exit.
+// issued, 6 split-K reduction done (or 0), 7 CTA exit, 8 first cluster barrier passed, 9 partial rows pushed,
+// 10 second cluster barrier passed (8-10: split-K only).
 constexpr int TS_CTAS = 512;
-__device__ unsigned long long g_gemm_ts[TS_CTAS][8];
+__device__ unsigned long long g_gemm_ts[TS_CTAS][12];
 __device__ __forceinline__ void ts_mark(const GemmParams& p, int slot) {
   if (p.dbg & 4) {
     const unsigned cta = blockIdx.x + gridDim.x * blockIdx.y;
@@ -590,6 +591,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     // overwritten by the partial-tile slots.
     tc_fence_before();
     cluster_sync_all();
+    if (threadIdx.x == 64) ts_mark(p, 8);
     const bool sk_valid = tile_begin + (int)blockIdx.y < total_tiles;
     if (warp >= 2 && sk_valid) {
       tc_fence_after();
@@ -597,8 +599,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       const int q = warp & 3;
       splitk_scatter<TN, CHS, DUAL>(p, smem_u32(smem), tmem_base + (uint32_t(q * 32) << 16), q * 32 + lane, crank, 1u, 0u);
     }
+    if (threadIdx.x == 64) ts_mark(p, 9);
     tc_fence_before();
     cluster_sync_all();                       // all slots are written (release / acquire at cluster scope)
+    if (threadIdx.x == 64) ts_mark(p, 10);
     if (warp >= 2 && sk_valid) {
       const int u = tile_begin + blockIdx.y;
       const int m0 = (u % num_m) * TN, n0 = (u / num_m) * BM_W;
@@ -1375,8 +1379,8 @@ extern "C" int ub_gemm_tn(const UbGemmArgs* a, void* stream_v) {
               : dispatch_tn<false, true>(pl.tn, tw, tx, p, tail_pl, stream);
 }
 
-// Copies the timeline table of the last 1-CTA launches (UB_GEMM_DEBUG bit 4) to `out` ([512][8] uint64, nanoseconds).
+// Copies the timeline table of the last 1-CTA launches (UB_GEMM_DEBUG bit 4) to `out` ([512][12] uint64, nanoseconds).
 extern "C" int ub_gemm_debug_timeline(unsigned long long* out) {
-  cudaError_t e = cudaMemcpyFromSymbol(out, ub::g_gemm_ts, sizeof(unsigned long long) * ub::TS_CTAS * 8);
+  cudaError_t e = cudaMemcpyFromSymbol(out, ub::g_gemm_ts, sizeof(unsigned long long) * ub::TS_CTAS * 12);
   return e == cudaSuccess ? 0 : -(int)e;
 }
