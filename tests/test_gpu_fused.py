@@ -158,8 +158,11 @@ def test_tensor_parallel_engine_fused_matches_baseline(tmp_path, model):
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
     line = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")][-1]
     out = json.loads(line[7:])
-    assert out["fused"] == out["fused_graph"]
-    for mode in ("nccl", "fused"):
+    total = sum(len(r) for r in out["tp1"])
+    # The graph path pads the step to bucketed shapes, so its GEMMs may pick other tiles and K splits than the eager
+    # path: same math, different rounding, and greedy tokens of a random-weight model can flip on near-ties.
+    same = sum(a == b for ra, rb in zip(out["fused"], out["fused_graph"]) for a, b in zip(ra, rb))
+    assert same / total > 0.9, ("fused vs fused_graph", same, total)
+    for mode in ("nccl", "fused", "fused_graph"):
         agree = sum(a == b for ra, rb in zip(out["tp1"], out[mode]) for a, b in zip(ra, rb))
-        total = sum(len(r) for r in out["tp1"])
         assert agree / total > 0.8, (mode, agree, total)

@@ -86,7 +86,10 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(compile_one, jobs))
     if jobs or not lib.exists():
-        _run([nvcc, "-shared", "-o", str(lib), *map(str, objs), "-cudart", "static"])
+        # link beside the target and rename: a reader (another process, a snapshot) never sees a half-written library
+        tmp = lib.with_suffix(".so.tmp")
+        _run([nvcc, "-shared", "-o", str(tmp), *map(str, objs), "-cudart", "static"])
+        os.replace(tmp, lib)
     return lib
 
 
@@ -113,7 +116,9 @@ def build_host(force: bool = False, verbose: bool = False) -> Path:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(compile_one, jobs))
     if srcs and (jobs or not lib.exists()):
-        _run(["g++", "-shared", "-o", str(lib), *map(str, objs), "-pthread"])
+        tmp = lib.with_suffix(".so.tmp")
+        _run(["g++", "-shared", "-o", str(tmp), *map(str, objs), "-pthread"])
+        os.replace(tmp, lib)
     return lib
 
 

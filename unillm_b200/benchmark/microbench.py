@@ -146,6 +146,27 @@ def bench_attn(results, case="all"):
                  frac_hbm=byts / med / 1e6 / hbm, path=cuda_ops.attn_prefill_last_path(), peaks=how)
         results.append(r)
         print(json.dumps(r))
+    if case in ("all", "decode", "suffix"):
+        # the suffix pass of the cascade in the serving benchmark: 256 sequences, 1024 shared keys skipped, 128..256 own
+        # keys each, the shared-prefix partial folded into the output
+        B, Hq, Hkv, D, bs, pre = 256, 32, 8, 128, 16, 1024
+        lens = [pre + 128 + (i * 128) // B for i in range(B)]
+        per = (max(lens) + bs - 1) // bs
+        nblk = B * per
+        kc = torch.randn(nblk, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
+        vc = torch.randn_like(kc)
+        bt = torch.randperm(nblk, device="cuda").to(torch.int32).view(B, per)
+        sl = torch.tensor(lens, dtype=torch.int32, device="cuda")
+        q = torch.randn(B, Hq, D, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        oa = torch.randn(B, Hq, D, device="cuda", dtype=torch.bfloat16)
+        la = torch.randn(B, Hq, device="cuda", dtype=torch.float32)
+        med, best = time_ms(lambda: cuda_ops.attn_decode(q, kc, vc, bt, sl, out=out, kv_start=pre, splits=1, merge=(oa, la)))
+        byts = 2.0 * 2 * sum(l - pre for l in lens) * Hkv * D
+        r = dict(kind="attn_decode_suffix", B=B, prefix=pre, suffix="128..256", Hq=Hq, Hkv=Hkv, D=D, ms=med, best_ms=best,
+                 gbs=byts / med / 1e6, frac_hbm=byts / med / 1e6 / hbm, peaks=how)
+        results.append(r)
+        print(json.dumps(r))
     prefill_cases = [(2048, 2048, 32, 8, 128, True), (8192, 8192, 4, 1, 128, True), (256, 1024, 32, 8, 128, False),
                      (512, 1024, 32, 8, 128, False)]
     for T, ctx, Hq, Hkv, D, causal in (prefill_cases if case in ("all", "prefill") else []):
@@ -185,7 +206,7 @@ def bench_norm(results):
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("what", nargs="?", default="all", choices=["gemm", "attn", "norm", "all"])
-    ap.add_argument("--attn-case", default="all", choices=["all", "decode", "prefill"], help="subset of the attention shapes")
+    ap.add_argument("--attn-case", default="all", choices=["all", "decode", "prefill", "suffix"], help="subset of the attention shapes")
     ap.add_argument("--json", default=None)
     ap.add_argument("--shape", default=None, help="gemm only: M,N,K,dual -- run just this shape")
     ap.add_argument("--tile", type=int, default=0, help="gemm only: force the token-tile width")
