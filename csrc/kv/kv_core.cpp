@@ -253,6 +253,18 @@ int ubkv_radix_match(void* t, const int32_t* toks, int n, int* out_blocks, int m
   std::lock_guard<std::mutex> g(r->mu);
   return r->match(toks, n, out_blocks, max_out, last_node, true);
 }
+// match + lock the matched path + one reference per matched block, as one step with respect to eviction: between a
+// plain match and the caller's own incref / lock another thread could evict the leaf and hand its blocks out again
+int ubkv_radix_acquire(void* t, const int32_t* toks, int n, int* out_blocks, int max_out, int* last_node) {
+  RadixTree* r = static_cast<RadixTree*>(t);
+  std::lock_guard<std::mutex> g(r->mu);
+  const int m = r->match(toks, n, out_blocks, max_out, last_node, true);
+  if (m > 0) {
+    r->lock_path(*last_node, 1);
+    for (int i = 0; i < m && i < max_out; ++i) r->pool->incref(out_blocks[i]);
+  }
+  return m;
+}
 int ubkv_radix_insert(void* t, const int32_t* toks, int n, const int* blocks, int* last_node) {
   RadixTree* r = static_cast<RadixTree*>(t);
   std::lock_guard<std::mutex> g(r->mu);

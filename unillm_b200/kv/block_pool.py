@@ -36,6 +36,8 @@ def _lib():
         lib.ubkv_radix_destroy.argtypes = [C.c_void_p]
         lib.ubkv_radix_match.argtypes = [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.POINTER(C.c_int), C.c_int,
                                          C.POINTER(C.c_int)]
+        lib.ubkv_radix_acquire.argtypes = [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.POINTER(C.c_int), C.c_int,
+                                           C.POINTER(C.c_int)]
         lib.ubkv_radix_insert.argtypes = [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.POINTER(C.c_int),
                                           C.POINTER(C.c_int)]
         lib.ubkv_radix_lock.argtypes = [C.c_void_p, C.c_int, C.c_int]
@@ -135,6 +137,20 @@ class RadixTree:
         node = C.c_int(0)
         m = self._lib.ubkv_radix_match(self._h, self._arr(tokens[: nb * self.block_size]), nb * self.block_size, out,
                                        nb, C.byref(node))
+        return list(out[:m]), node.value
+
+    def acquire_prefix(self, tokens: Sequence[int]) -> Tuple[List[int], int]:
+        """``match_prefix`` that also locks the matched path and takes one pool reference per matched block, as one
+        step with respect to eviction (for callers on several threads).  Undo with ``unlock(node)`` and one
+        ``BlockPool.free`` per block."""
+        n = len(tokens)
+        nb = n // self.block_size
+        if nb == 0:
+            return [], 0
+        out = (C.c_int * nb)()
+        node = C.c_int(0)
+        m = self._lib.ubkv_radix_acquire(self._h, self._arr(tokens[: nb * self.block_size]), nb * self.block_size, out,
+                                         nb, C.byref(node))
         return list(out[:m]), node.value
 
     def insert(self, tokens: Sequence[int], blocks: Sequence[int]) -> Tuple[int, int]:
