@@ -104,6 +104,19 @@ def test_state_models_bf16_gpu_vs_fp32_cpu(name):
     assert err < 0.08 * max(1.0, ref.abs().max().item()), err
 
 
+def test_conv_transpose1d_as_gemm():
+    """Transposed convolution (EnCodec decoder upsampling) on the tcgen05 GEMM + overlap-add vs the fp32 operator."""
+    from unillm_b200.models.simple import conv_transpose1d
+
+    g = torch.Generator().manual_seed(1)
+    for (B, Ci, L, Co, k, st) in ((2, 32, 40, 16, 8, 4), (1, 64, 33, 32, 16, 8), (2, 16, 25, 8, 4, 2), (1, 8, 10, 8, 3, 1)):
+        x, w, b = _bf(torch.randn(B, Ci, L, generator=g)), _bf(torch.randn(Ci, Co, k, generator=g) * 0.2), _bf(torch.randn(Co, generator=g))
+        ref = torch.nn.functional.conv_transpose1d(x.float(), w.float(), b.float(), stride=st)
+        got = conv_transpose1d(x.cuda(), w.cuda(), b.cuda(), stride=st)
+        assert got.shape == ref.shape and got.dtype == torch.bfloat16
+        _close(got, ref, 0.03)
+
+
 def test_conv1d_as_gemm_and_whisper_bf16():
     from unillm_b200.model_core import ModelInputs
     from unillm_b200.models import ALL_MODELS, configs as C

@@ -27,7 +27,7 @@ from ..model_core import ModelInputs, ModelOutputs
 from ..tensor_core import ops_fn
 from ..types import InvalidInput, UnsupportedOperation
 from . import configs as C
-from .simple import ParamModel, _f, conv1d, mha
+from .simple import ParamModel, _f, conv1d, conv_transpose1d, mha
 
 
 class Wav2Vec2Model(ParamModel):
@@ -289,7 +289,7 @@ class EncodecModel(ParamModel):
 
     def _convT(self, x, name, stride):
         w = self.p[name + ".weight"]
-        y = F.conv_transpose1d(_f(x), _f(w), _f(self.p[name + ".bias"]), stride=stride)
+        y = conv_transpose1d(x, w, self.p[name + ".bias"], stride=stride)
         return y[..., :y.shape[-1] - (w.shape[-1] - stride)]                   # trim the right: causal
 
     def _res(self, x, pre):

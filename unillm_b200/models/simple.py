@@ -193,3 +193,25 @@ def conv1d(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None, s
         return y.view(B, Lo, O).transpose(1, 2).contiguous()
     return F.conv1d(_f(x), _f(w), None if b is None else _f(b), stride=stride, padding=padding, groups=groups,
                     dilation=dilation).to(x.dtype)
+
+
+def conv_transpose1d(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None, stride: int = 1) -> torch.Tensor:
+    """[B, C_in, L] transposed convolution with filters ``w [C_in, C_out, k]`` (torch layout), no padding:
+    output length ``(L - 1) * stride + k``.  bf16 CUDA inputs run as one tensor-core GEMM -- every input frame times
+    the filter matrix ``[C_out * k, C_in]`` gives that frame's ``k`` output taps for all channels -- followed by an
+    overlap-add of the taps (``F.fold``); everything else is the fp32 torch operator."""
+    Ci, Co, k = w.shape
+    if x.is_cuda and x.dtype == torch.bfloat16 and Ci % 8 == 0:
+        from ..ops import cuda_ops as K
+
+        B, _, L = x.shape
+        rows = x.transpose(1, 2).reshape(B * L, Ci).contiguous()                       # [B*L, C_in]
+        wm = w.permute(1, 2, 0).reshape(Co * k, Ci).to(torch.bfloat16).contiguous()    # row (o, t) = w[:, o, t]
+        taps = K.linear(rows, wm, None)                                                # [B*L, C_out*k]
+        cols = taps.view(B, L, Co * k).transpose(1, 2).float()                         # [B, C_out*k, L]
+        Lo = (L - 1) * stride + k
+        y = F.fold(cols, output_size=(1, Lo), kernel_size=(1, k), stride=(1, stride)).view(B, Co, Lo)
+        if b is not None:
+            y = y + b.float()[None, :, None]
+        return y.to(x.dtype)
+    return F.conv_transpose1d(_f(x), _f(w), None if b is None else _f(b), stride=stride).to(x.dtype)
