@@ -81,6 +81,16 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const UbAttnArgs a
   const int h0 = kvh * Gtot + gc * ROWS;
   const int gn = min(ROWS, Gtot - gc * ROWS);          // valid rows (heads) of this CTA
 
+  // Without a window or KV splits the first page of the range does not depend on the sequence length: fetch the
+  // block-table entries together with the length instead of behind it (one dependent global latency less).
+  int* bt_sm = reinterpret_cast<int*>(dsm + S::BT_OFF);
+  const int* bt = a.block_tables + (long long)seq * a.max_blocks_per_seq;
+  const bool bt_early = a.window == 0 && a.splits == 1;
+  const int bs_shift = 31 - __clz(a.block_size);
+  if (bt_early) {
+    const int first = max(a.kv_start, 0) >> bs_shift;
+    for (int i = threadIdx.x; i < min(S::BT_MAX, a.max_blocks_per_seq - first); i += 128) bt_sm[i] = bt[first + i];
+  }
   const int kv_len = a.seq_lens[seq];
   int lo = a.kv_start;
   if (a.window > 0) lo = max(lo, kv_len - a.window);
@@ -90,7 +100,6 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const UbAttnArgs a
   per = (per + a.block_size - 1) / a.block_size * a.block_size;
   const int kv_lo = lo + split * per;
   const int kv_hi = min(kv_len, kv_lo + per);
-  const int* bt = a.block_tables + (long long)seq * a.max_blocks_per_seq;
   const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(a.k_cache);
   const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(a.v_cache);
   const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(a.q) + (long long)seq * a.q_stride;
@@ -105,16 +114,15 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const UbAttnArgs a
 
   // Tiles start on a page boundary, so a tile is KT / block_size whole pages: one block-table lookup and one
   // base address per page, then 16-byte chunks at consecutive addresses (no per-chunk division).
-  const int bs_shift = 31 - __clz(a.block_size);
   const int tile_origin = kv_lo & ~(a.block_size - 1);
   const int n_tiles = kv_hi > tile_origin ? (kv_hi - tile_origin + KT - 1) / KT : 0;
   // All block-table entries of the range are fetched at once, before the first copy: read one by one in front of
   // each page they put a dependent global load (and its latency) in front of every group of copies.
-  int* bt_sm = reinterpret_cast<int*>(dsm + S::BT_OFF);
   const int page0 = tile_origin >> bs_shift;
   const int n_pages = kv_hi > tile_origin ? ((kv_hi - tile_origin + a.block_size - 1) >> bs_shift) : 0;
-  for (int i = threadIdx.x; i < min(n_pages, S::BT_MAX); i += 128)
-    bt_sm[i] = (page0 + i) < a.max_blocks_per_seq ? bt[page0 + i] : -1;
+  if (!bt_early)
+    for (int i = threadIdx.x; i < min(n_pages, S::BT_MAX); i += 128)
+      bt_sm[i] = (page0 + i) < a.max_blocks_per_seq ? bt[page0 + i] : -1;
   __syncthreads();                                       // q_sm and bt_sm complete
   const int pages_per_tile = KT >> bs_shift;
   const int chunks_per_page = CPR << bs_shift;
@@ -128,7 +136,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const UbAttnArgs a
         long long base = 0;
         if (nvalid > 0) {
           const int bi = pos0 >> bs_shift;
-          const int blk = (bi - page0) < S::BT_MAX ? bt_sm[bi - page0] : (bi < a.max_blocks_per_seq ? bt[bi] : -1);
+          const int blk = bi >= a.max_blocks_per_seq ? -1 : ((bi - page0) < S::BT_MAX ? bt_sm[bi - page0] : bt[bi]);
           if (blk < 0 || blk >= a.num_blocks) set_err(a.err, ERR_BOUNDS, seq);
           else base = (((long long)blk * a.Hkv + kvh) << bs_shift) * D;
         }
@@ -166,6 +174,22 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const UbAttnArgs a
 #pragma unroll
   for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
   float m_a = -CUDART_INF_F, m_b = -CUDART_INF_F, l_a = 0.f, l_b = 0.f;
+
+  // The partial over the shared prefix that the epilogue folds in: fetched now, so that its latency runs under the
+  // key / value copies instead of behind the last tile (first four output elements per thread = a GQA group of 4).
+  constexpr int PRE = 4;
+  float pre_la[PRE], pre_oa[PRE];
+#pragma unroll
+  for (int k = 0; k < PRE; ++k) {
+    const int i = threadIdx.x + k * 128;
+    pre_la[k] = 0.f;
+    pre_oa[k] = 0.f;
+    if (a.merge_o != nullptr && a.splits == 1 && i < gn * D) {
+      const int h = h0 + i / D;
+      pre_la[k] = a.merge_lse[(long long)seq * a.Hq + h];
+      pre_oa[k] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.merge_o)[((long long)seq * a.Hq + h) * D + i % D]);
+    }
+  }
 
   for (int t = 0; t < n_tiles; ++t) {
     asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
@@ -255,7 +279,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const UbAttnArgs a
     if (rb < gn) { red_ml[warp][rb][0] = m_b; red_ml[warp][rb][1] = l_b; }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < gn * D; i += 128) {
+  for (int i = threadIdx.x, it = 0; i < gn * D; i += 128, ++it) {
     const int g = i / D, d = i % D;
     float mx = -CUDART_INF_F;
 #pragma unroll
@@ -274,8 +298,15 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const UbAttnArgs a
       float val = ov * inv;
       if (a.merge_o != nullptr) {
         // fold in the partial result over the other key set (shared prefix): weights exp(lse_x - max)
-        const float la = a.merge_lse[(long long)seq * a.Hq + h];
-        const float oa = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.merge_o)[((long long)seq * a.Hq + h) * D + d]);
+        float la, oa;
+        if (it < PRE) {
+          // static indices keep the prefetched values in registers
+          la = it == 0 ? pre_la[0] : it == 1 ? pre_la[1] : it == 2 ? pre_la[2] : pre_la[3];
+          oa = it == 0 ? pre_oa[0] : it == 1 ? pre_oa[1] : it == 2 ? pre_oa[2] : pre_oa[3];
+        } else {
+          la = a.merge_lse[(long long)seq * a.Hq + h];
+          oa = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.merge_o)[((long long)seq * a.Hq + h) * D + d]);
+        }
         const float mm = fmaxf(la, lse);
         const float wa = (la == -CUDART_INF_F) ? 0.f : __expf(la - mm);
         const float wb = (lse == -CUDART_INF_F) ? 0.f : __expf(lse - mm);
@@ -328,7 +359,13 @@ extern "C" int ub_attn_decode_mma_supported(const UbAttnArgs* a) {
 
 extern "C" int ub_attn_decode_mma_main(const UbAttnArgs* a, void* stream) {
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  // suffix ranges after a shared prefix are short: favour a third resident CTA over a deeper ring
-  if (a->kv_start > 0) return a->D == 64 ? ub::dmma::launch<64, 2>(*a, st) : ub::dmma::launch<128, 2>(*a, st);
+  // suffix ranges after a shared prefix are short (two to four tiles): a third resident CTA per SM hides more of the
+  // chain of dependent latencies than a deeper ring does (68.8 us vs 83.3 us per layer on the serving step);
+  // UB_DECODE_STAGES=3 keeps the deep ring there
+  static const int suffix_stages = [] {
+    const char* e = getenv("UB_DECODE_STAGES");
+    return (e != nullptr && atoi(e) == 3) ? 3 : 2;
+  }();
+  if (a->kv_start > 0 && suffix_stages == 2) return a->D == 64 ? ub::dmma::launch<64, 2>(*a, st) : ub::dmma::launch<128, 2>(*a, st);
   return a->D == 64 ? ub::dmma::launch<64, 3>(*a, st) : ub::dmma::launch<128, 3>(*a, st);
 }

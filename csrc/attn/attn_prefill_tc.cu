@@ -83,15 +83,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_BAR);
   uint64_t* q_full = bars + 0;
-  uint64_t* k_full = bars + 1;    // [2]
-  uint64_t* k_empty = bars + 3;   // [2]
-  uint64_t* v_full = bars + 5;    // [2]
-  uint64_t* v_empty = bars + 7;   // [2]
-  uint64_t* s_full = bars + 9;    // [2]
-  uint64_t* s_empty = bars + 11;  // [2]
-  uint64_t* p_full = bars + 13;
-  uint64_t* o_full = bars + 14;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* k_full = bars + 1;    // [3]
+  uint64_t* k_empty = bars + 4;   // [3]
+  uint64_t* v_full = bars + 7;    // [2]
+  uint64_t* v_empty = bars + 9;   // [2]
+  uint64_t* s_full = bars + 11;   // [2]
+  uint64_t* s_empty = bars + 13;  // [2]
+  uint64_t* p_full = bars + 15;   // [2] one per key half
+  uint64_t* o_full = bars + 17;   // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
+  // K tiles: with P in tensor memory the shared-memory P buffer is free and serves as a third K stage, so the K copies
+  // run two tiles ahead of their use (the copy of a tile is gathered from 16 boxes and completes with its slowest).
+  constexpr int KST = P_TMEM ? 3 : 2;
+  auto k_stage = [&](int st) { return smem + (st < 2 ? SMEM_K + st * TILE_BYTES : SMEM_P); };
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   pdl_wait();          // the sequence metadata read below may be written by earlier kernels of the stream
@@ -117,11 +121,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+      if (i == 0) { mbar_init(&k_full[2], 1); mbar_init(&k_empty[2], 1); }
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 256);
     }
-    mbar_init(p_full, 256);
-    mbar_init(o_full, 1);
+    mbar_init(&p_full[0], 128);
+    mbar_init(&p_full[1], 128);
+    mbar_init(&o_full[0], 1);
+    mbar_init(&o_full[1], 1);
     fence_mbar_init();
     tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
@@ -137,7 +144,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   const uint32_t tmem_base = *tmem_slot;
   pdl_launch_dependents();     // only now: this CTA holds its TMEM columns before any CTA of the next kernel can exist
   const uint32_t tmem_s = tmem_base;            // S buffers: columns [0,128) and [128,256)
-  const uint32_t tmem_o = tmem_base + 256;      // O tile: columns [256,384)
+  const uint32_t tmem_o = tmem_base + 256;      // two O accumulators, one per key half: columns [256,384) and [384,512)
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -162,38 +169,43 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         }
         return blk;
       };
-      int blk_next = page_block(0);
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        const int blk = blk_next;
-        if (j + 1 < n_tiles) blk_next = page_block(j + 1);
-        const int row = (blk * p.Hkv + kh) * PAGE;
-        // K tile
+      // one tile of K or V: lane 0 waits for the stage and arms the barrier, lanes 0..7 copy one page each
+      auto load_tile = [&](uint8_t* dst_tile, const CUtensorMap* map, uint64_t* full, uint64_t* empty, uint32_t ph, int blk,
+                           int code) {
         int ok = 1;
         if (lane == 0) {
-          ok = mbar_wait(&k_empty[s], ph ^ 1, abort_flag, p.err, 500 + s) ? 1 : 0;
-          if (ok) mbar_arrive_expect_tx(&k_full[s], TILE_BYTES);
+          ok = mbar_wait(empty, ph ^ 1, abort_flag, p.err, code) ? 1 : 0;
+          if (ok) mbar_arrive_expect_tx(full, TILE_BYTES);
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
-        if (lane < PPT) {
-          uint8_t* dst = smem + SMEM_K + s * TILE_BYTES + lane * PAGE * 128;
-          tma_load_2d(dst, &tmap_k, &k_full[s], 0, row);
-          tma_load_2d(dst + HALF_BYTES, &tmap_k, &k_full[s], 64, row);
+        if (ok && lane < PPT) {
+          const int row = (blk * p.Hkv + kh) * PAGE;
+          uint8_t* dst = dst_tile + lane * PAGE * 128;
+          tma_load_2d(dst, map, full, 0, row);
+          tma_load_2d(dst + HALF_BYTES, map, full, 64, row);
         }
-        // V tile
-        if (lane == 0) {
-          ok = mbar_wait(&v_empty[s], ph ^ 1, abort_flag, p.err, 510 + s) ? 1 : 0;
-          if (ok) mbar_arrive_expect_tx(&v_full[s], TILE_BYTES);
-        }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
-        if (lane < PPT) {
-          uint8_t* dst = smem + SMEM_V + s * TILE_BYTES + lane * PAGE * 128;
-          tma_load_2d(dst, &tmap_v, &v_full[s], 0, row);
-          tma_load_2d(dst + HALF_BYTES, &tmap_v, &v_full[s], 64, row);
-        }
+        return ok != 0;
+      };
+      auto load_k = [&](int t, int blk) {
+        const int st = t % KST;
+        return load_tile(k_stage(st), &tmap_k, &k_full[st], &k_empty[st], (t / KST) & 1, blk, 500 + st);
+      };
+      auto load_v = [&](int t, int blk) {
+        const int st = t & 1;
+        return load_tile(smem + SMEM_V + st * TILE_BYTES, &tmap_v, &v_full[st], &v_empty[st], (t >> 1) & 1, blk, 510 + st);
+      };
+      // block ids of this lane's page in tiles j, j + 1 (and j + 2): K runs KST - 1 tiles ahead of V
+      int blk_v = page_block(0);
+      int blk_1 = n_tiles > 1 ? page_block(1) : 0;
+      int blk_2 = (KST == 3 && n_tiles > 2) ? page_block(2) : 0;
+      bool alive = load_k(0, blk_v);
+      if (alive && KST == 3 && n_tiles > 1) alive = load_k(1, blk_1);
+      for (int j = 0; j < n_tiles && alive; ++j) {
+        const int jk = j + KST - 1;
+        if (jk < n_tiles) alive = load_k(jk, KST == 3 ? blk_2 : blk_1);
+        const int blk_next = (jk + 1 < n_tiles) ? page_block(jk + 1) : 0;
+        if (alive) alive = load_v(j, blk_v);
+        if (KST == 3) { blk_v = blk_1; blk_1 = blk_2; blk_2 = blk_next; } else { blk_v = blk_1; blk_1 = blk_next; }
       }
     }
   } else if (warp == 1) {
@@ -203,7 +215,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       constexpr uint32_t idesc_pv = make_idesc_bf16(BM, HD, 0, 1);   // B = V is MN-major ([key][d], d contiguous)
       const uint32_t q_addr = smem_u32(smem + SMEM_Q), p_addr = smem_u32(smem + SMEM_P);
       auto issue_qk = [&](int j) {
-        const uint32_t k_addr = smem_u32(smem + SMEM_K + (j & 1) * TILE_BYTES);
+        const uint32_t k_addr = smem_u32(k_stage(j % KST));
         const uint32_t d = tmem_s + (j & 1) * BN;
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
@@ -224,44 +236,52 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         if (j + 1 < n_tiles) {
           const int jn = j + 1, sn = jn & 1;
           const uint32_t phn = (jn >> 1) & 1;
-          if (!mbar_wait(&k_full[sn], phn, abort_flag, p.err, 522)) { ok = false; break; }
+          if (!mbar_wait(&k_full[jn % KST], (jn / KST) & 1, abort_flag, p.err, 522)) { ok = false; break; }
           // S buffer sn: its last readers were the softmax loads of tile j - 1 and, when P lives in TMEM, P V of
           // tile j - 1, which this thread issued before (the tensor pipe runs MMAs in issue order).
           if (!P_TMEM && !mbar_wait(&s_empty[sn], phn ^ 1, abort_flag, p.err, 523)) { ok = false; break; }
           tc_fence_after();
           issue_qk(jn);
           umma_commit(&s_full[sn]);
-          umma_commit(&k_empty[sn]);
+          umma_commit(&k_empty[jn % KST]);
         }
         const int s = j & 1;
-        if (!mbar_wait(p_full, j & 1, abort_flag, p.err, 524)) { ok = false; break; }
         if (!mbar_wait(&v_full[s], (j >> 1) & 1, abort_flag, p.err, 525)) { ok = false; break; }
-        tc_fence_after();
         const uint32_t v_addr = smem_u32(smem + SMEM_V + s * TILE_BYTES);
+        // The two key halves of the tile are independent softmax streams with their own accumulators: P_h V_h is
+        // issued as soon as half h has delivered its probabilities.
 #pragma unroll
-        for (int k = 0; k < BN / 16; ++k) {
-          // B = V, MN-major: 16 keys = two 8-key groups (1024 B apart); the two 64-wide d blocks are 16 KB apart
-          const uint64_t b_desc = make_smem_desc_sw128(v_addr + k * 16 * 128, HALF_BYTES, 1024);
-          const uint32_t accumulate = (j > 0 || k != 0) ? 1u : 0u;     // O stays in TMEM over all KV tiles
-          if (P_TMEM) {
-            // A = P in tensor memory, packed bf16 pairs over the first 64 columns of this tile's S buffer
-            umma_bf16_ts(tmem_o, tmem_s + s * BN + k * 8, b_desc, idesc_pv, accumulate);
-          } else {
-            // A = P, K-major over keys: 64-key halves 16 KB apart, 16 keys = 32 B inside a 128-B row
-            const uint64_t a_desc = make_smem_desc_sw128(p_addr + (k >> 2) * HALF_BYTES + (k & 3) * 32, 16, 1024);
-            umma_bf16_ss(tmem_o, a_desc, b_desc, idesc_pv, accumulate);
+        for (int h = 0; h < 2; ++h) {
+          if (!mbar_wait(&p_full[h], j & 1, abort_flag, p.err, 524 + 10 * h)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int kk = h * 4 + k;                                    // 16-key step inside the tile
+            // B = V, MN-major: 16 keys = two 8-key groups (1024 B apart); the two 64-wide d blocks are 16 KB apart
+            const uint64_t b_desc = make_smem_desc_sw128(v_addr + kk * 16 * 128, HALF_BYTES, 1024);
+            const uint32_t accumulate = (j > 0 || k != 0) ? 1u : 0u;     // O stays in TMEM over all KV tiles
+            if (P_TMEM) {
+              // A = P in tensor memory: packed bf16 pairs over the first 32 columns of this half's S columns
+              umma_bf16_ts(tmem_o + h * HD, tmem_s + s * BN + h * 64 + k * 8, b_desc, idesc_pv, accumulate);
+            } else {
+              // A = P, K-major over keys: 64-key halves 16 KB apart, 16 keys = 32 B inside a 128-B row
+              const uint64_t a_desc = make_smem_desc_sw128(p_addr + h * HALF_BYTES + k * 32, 16, 1024);
+              umma_bf16_ss(tmem_o + h * HD, a_desc, b_desc, idesc_pv, accumulate);
+            }
           }
+          umma_commit(&o_full[h]);
         }
-        umma_commit(o_full);
+        if (!ok) break;
         umma_commit(&v_empty[s]);
       }
     }
   } else {
     // ------------------------------ softmax + output (warps 2..9) ------------------------------
-    // Two warpgroups share every query row: warps 2..5 take keys [0, 64) of a tile, warps 6..9 keys [64, 128) (a warp
-    // may read the TMEM lanes 32 * (warp % 4) .. + 32, at any column).  With two softmax warps per scheduler one
-    // warp's fixed-latency stalls are filled by the other.  The halves agree on the row maximum through shared
-    // memory (one named barrier per tile); each keeps its own partial row sum and its own 64 columns of O.
+    // Two warpgroups share every query row: warps 2..5 take keys [0, 64) of every tile, warps 6..9 keys [64, 128) (a
+    // warp may read the TMEM lanes 32 * (warp % 4) .. + 32, at any column).  The halves are two independent
+    // flash-attention streams over disjoint key sets: own exponent reference, own row sum, own O accumulator in
+    // TMEM, own barriers to the MMA warp -- nothing is exchanged per tile, so the two softmax warps of a scheduler
+    // drift freely and fill each other's stalls.  The streams are merged once, at the end.
     const int half = (warp - 2) >> 2;
     const int qd = warp & 3;                    // TMEM lane quarter this warp may read
     const int row = qd * 32 + lane;             // packed query row == TMEM lane
@@ -271,12 +291,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     int limit = kv_len;
     if (p.causal) limit = min(kv_len, kv_len - q_len + (tok - q_begin) + 1);
     if (!row_valid || limit < 0) limit = 0;
-    // m is the exponent reference of this row (log2 domain).  It follows the running maximum lazily: it moves only
-    // when a tile's maximum exceeds it by more than 8, so probabilities stay below 2^8 and the O tile in TMEM is
-    // rescaled rarely.  The final O / l does not depend on the reference.
+    // m is the exponent reference of this half row (log2 domain).  It follows the running maximum lazily: it moves
+    // only when a tile's maximum exceeds it by more than 8, so probabilities stay below 2^8 and the O rows in TMEM
+    // are rescaled rarely.  The final O / l does not depend on the reference.
     float m = -CUDART_INF_F, l = 0.f;
-    uint8_t* p_row = smem + SMEM_P + row * 128;
-    float* xch = reinterpret_cast<float*>(smem + SMEM_XCH);       // [2 tile parities][2 halves][128 rows]
+    uint8_t* p_row = smem + SMEM_P + row * 128 + half * HALF_BYTES;
+    const uint32_t o_mine = tmem_o + half * HD + lane_off, o_other = tmem_o + (half ^ 1) * HD + lane_off;
     // every wait is agreed on by the whole warp: the TMEM loads and stores below are warp-wide instructions
     auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) {
       return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, p.err, code)) != 0;
@@ -286,19 +306,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       const int b = j & 1;
       ok = ok && wait_all(&s_full[b], (j >> 1) & 1, 530);
       tc_fence_after();
-      const uint32_t s_addr = tmem_s + b * BN + lane_off;
+      const uint32_t s_addr = tmem_s + b * BN + half * 64 + lane_off;      // this half's 64 S columns
       const int key0 = (tile0 + j) * BN + half * 64;
       // Tiles that lie completely inside [kv_lo, limit) need no per-key predicate (all but the first and last ones).
       const bool full = key0 >= kv_lo && key0 + 64 <= limit;
-      // this thread's half of the S row: 64 fp32 in registers
       uint32_t sv[2][32];
-      tmem_ld_32x32(s_addr + half * 64, sv[0]);
-      tmem_ld_32x32(s_addr + half * 64 + 32, sv[1]);
+      tmem_ld_32x32(s_addr, sv[0]);
+      tmem_ld_32x32(s_addr + 32, sv[1]);
       tmem_ld_wait();
       if (!P_TMEM) {
         tc_fence_before();
         mbar_arrive(&s_empty[b]);
       }
+      // independent chains per reduction: a warp has to cover its own ALU latency
       float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
       if (full) {
 #pragma unroll
@@ -314,13 +334,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
             if (k < limit && k >= kv_lo) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
           }
       }
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // both halves of the row must use the same reference: exchange the partial maxima.  The two parity slots
-      // alternate, and the barrier of tile j + 1 separates the reads of tile j from the writes of tile j + 2.
-      xch[(b * 2 + half) * 128 + row] = mx;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      mx = fmaxf(mx, xch[(b * 2 + (half ^ 1)) * 128 + row]);
-      const float m_tile = mx * p.scale_log2;
+      const float m_tile = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
       float alpha = 1.f;
       if (m_tile > m + 8.f) {                       // also the first visible tile (m == -inf)
         alpha = (m == -CUDART_INF_F) ? 0.f : ex2_approx(m - m_tile);
@@ -328,8 +342,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       }
       const float m_use = (m == -CUDART_INF_F) ? 0.f : m;   // nothing visible so far: every p is masked to 0
       if (!P_TMEM && j > 0) {
-        // the single P buffer in shared memory is free once P V of the previous tile has completed
-        ok = ok && wait_all(o_full, (j - 1) & 1, 531);
+        // this half of the single P buffer in shared memory is free once P_h V_h of the previous tile has completed
+        ok = ok && wait_all(&o_full[half], (j - 1) & 1, 531);
       }
       float ps4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t packed[32];
@@ -349,78 +363,86 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         }
       }
       if (P_TMEM) {
-        // 64 keys = 32 packed columns; the two halves together overwrite the first 64 columns of this tile's S
-        // buffer.  The other half may still be reading its S columns [64, 128) when half 0 writes [0, 32), and
-        // half 1 writes [32, 64) which half 0 has read before the barrier above: no column is written before its
-        // reader has it in registers.
-        tmem_st_32x32(s_addr + half * 32, packed);
-        // O may only be touched (and the next P V issued) after P V of the previous tile; by now it has had the
-        // whole softmax of this tile to finish
-        if (j > 0) ok = ok && wait_all(o_full, (j - 1) & 1, 531);
+        // 64 keys = 32 packed columns, written over the head of this half's own S columns (already in registers)
+        tmem_st_32x32(s_addr, packed);
+        // O_h may only be touched (and the next P_h V_h issued) after P_h V_h of the previous tile; by now it has
+        // had the whole softmax of this tile to finish
+        if (j > 0) ok = ok && wait_all(&o_full[half], (j - 1) & 1, 531);
       } else {
         // 64 keys = one 64-key half of the K-major P tile: 8 chunks of 16 B, swizzled by the row
-        uint8_t* base = p_row + half * HALF_BYTES;
 #pragma unroll
         for (int q8 = 0; q8 < 8; ++q8) {
-          *reinterpret_cast<uint4*>(base + ((q8 ^ (row & 7)) << 4)) =
+          *reinterpret_cast<uint4*>(p_row + ((q8 ^ (row & 7)) << 4)) =
               make_uint4(packed[4 * q8], packed[4 * q8 + 1], packed[4 * q8 + 2], packed[4 * q8 + 3]);
         }
       }
       l = l * alpha + ((ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
-      // rescale the O rows whose reference moved (warp-uniform decision: the TMEM accesses are warp-wide); each half
-      // owns 64 of the 128 output columns
+      // rescale this half's O rows when the reference moved (warp-uniform decision: the TMEM accesses are warp-wide)
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
         tc_fence_after();
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < HD / 32; ++c) {
           uint32_t r[32];
-          tmem_ld_32x32(tmem_o + lane_off + half * 64 + c * 32, r);
+          tmem_ld_32x32(o_mine + c * 32, r);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st_32x32(tmem_o + lane_off + half * 64 + c * 32, r);
+          tmem_st_32x32(o_mine + c * 32, r);
         }
       }
       tmem_st_wait();
       tc_fence_before();
       fence_proxy_async_smem();
-      mbar_arrive(p_full);
+      mbar_arrive(&p_full[half]);
     }
-    if (n_tiles > 0) ok = ok && wait_all(o_full, (n_tiles - 1) & 1, 532);
+    // Merge of the two streams.  MMAs complete in issue order, so once this half's last P V has completed the other
+    // half's barrier is at most one phase behind and its parity wait cannot alias.
+    if (n_tiles > 0) {
+      ok = ok && wait_all(&o_full[half], (n_tiles - 1) & 1, 532);
+      ok = ok && wait_all(&o_full[half ^ 1], (n_tiles - 1) & 1, 533);
+    }
     tc_fence_after();
-    // the row sum is the sum of the two halves' partial sums (same reference m in both)
-    float* lx = xch + 512;                                        // its own slots: a slow thread may still read a maximum
-    lx[half * 128 + row] = l;
+    float* xch = reinterpret_cast<float*>(smem + SMEM_XCH);       // [2 halves][128 rows][m, l]
+    xch[(half * 128 + row) * 2] = m;
+    xch[(half * 128 + row) * 2 + 1] = l;
     asm volatile("bar.sync 1, 256;" ::: "memory");
-    l += lx[(half ^ 1) * 128 + row];
+    const float m_o = xch[((half ^ 1) * 128 + row) * 2], l_o = xch[((half ^ 1) * 128 + row) * 2 + 1];
+    const float mm_ = fmaxf(m, m_o);
+    const float w_mine = (m == -CUDART_INF_F) ? 0.f : ex2_approx(m - mm_);
+    const float w_other = (m_o == -CUDART_INF_F) ? 0.f : ex2_approx(m_o - mm_);
+    const float lt = l * w_mine + l_o * w_other;                  // row sum over all keys, reference mm_
     if (ok) {
-      float inv = l > 0.f ? 1.f / l : 0.f;
-      float lse_v = l > 0.f ? (m * LN2 + logf(l)) : -CUDART_INF_F;
+      const float inv = lt > 0.f ? 1.f / lt : 0.f;
+      float lse_v = lt > 0.f ? (mm_ * LN2 + logf(lt)) : -CUDART_INF_F;
       float ca = 0.f, cb = inv;
       const __nv_bfloat16* src = nullptr;
       if (p.merge_o != nullptr && row_valid) {
         // fold in the partial result over the other key set (shared prefix): weights exp(lse_x - max)
         const float la = p.merge_lse[(long long)tok * p.Hq + head];
-        const float mm = fmaxf(la, lse_v);
-        const float wa = (la == -CUDART_INF_F) ? 0.f : __expf(la - mm);
-        const float wb = (lse_v == -CUDART_INF_F) ? 0.f : __expf(lse_v - mm);
+        const float mx_ = fmaxf(la, lse_v);
+        const float wa = (la == -CUDART_INF_F) ? 0.f : __expf(la - mx_);
+        const float wb = (lse_v == -CUDART_INF_F) ? 0.f : __expf(lse_v - mx_);
         const float den = wa + wb;
         ca = den > 0.f ? wa / den : 0.f;
         cb = den > 0.f ? inv * wb / den : 0.f;
         src = p.merge_o + ((long long)tok * p.Hq + head) * HD;
-        lse_v = den > 0.f ? mm + logf(den) : -CUDART_INF_F;
+        lse_v = den > 0.f ? mx_ + logf(den) : -CUDART_INF_F;
       }
+      const float c_mine = (l > 0.f) ? cb * w_mine : 0.f, c_other = (l_o > 0.f) ? cb * w_other : 0.f;
       __nv_bfloat16* dst = p.out + (long long)tok * p.o_stride + (long long)head * HD;
+      // each half writes 64 of the 128 output columns, reading them from both accumulators
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
         const int d0 = half * 64 + c * 32;
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_o + lane_off + d0, r);          // never-written TMEM (no visible tile) is not used: l == 0
+        uint32_t r[32], r2[32];
+        tmem_ld_32x32(o_mine + d0, r);            // an accumulator that never saw a visible key is not used: l == 0
+        tmem_ld_32x32(o_other + d0, r2);
         tmem_ld_wait();
         if (row_valid) {
           float o[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = (l > 0.f) ? __uint_as_float(r[i]) * cb : 0.f;
+          for (int i = 0; i < 32; ++i)
+            o[i] = (c_mine != 0.f ? __uint_as_float(r[i]) * c_mine : 0.f) + (c_other != 0.f ? __uint_as_float(r2[i]) * c_other : 0.f);
           if (src != nullptr) {
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {

@@ -274,9 +274,9 @@ __device__ __forceinline__ void splitk_scatter(const GemmParams& p, uint32_t sme
   }
 }
 
-template <bool DUAL>
-__device__ __forceinline__ void splitk_finish(const GemmParams& p, const uint8_t* smem, int tn, int r0, int r1, int tid_e,
-                                              int m0, int n0, bool vec_ok) {
+template <bool DUAL, int ACT>
+__device__ __forceinline__ void splitk_finish_t(const GemmParams& p, const uint8_t* smem, int tn, int r0, int r1, int tid_e,
+                                                int m0, int n0, bool vec_ok) {
   const int S = p.splits, per = (tn + S - 1) / S;
   const float* part = reinterpret_cast<const float*>(smem);
   const float* part_up = part + (size_t)S * per * BM_W;
@@ -303,11 +303,29 @@ __device__ __forceinline__ void splitk_finish(const GemmParams& p, const uint8_t
       gv[e] = __float_as_uint(x);
       uv[e] = __float_as_uint(up[e]);
     }
-    epi_values<8, DUAL>(gv, uv, p.out_scale, 0.f, p.act);
+    epi_values_t<8, DUAL, ACT>(gv, uv, p.out_scale, 0.f);
     float v[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(gv[e]);
     emit8(p, m0 + r0 + lt, p.M, nn, v, vec_ok);
+  }
+}
+
+// The activation is chosen once, outside the loop over output rows: with the switch inside, the compiler turned the
+// eight-value bodies into predicated code that evaluated every activation for every value (880 cycles per 8 outputs).
+template <bool DUAL>
+__device__ __forceinline__ void splitk_finish(const GemmParams& p, const uint8_t* smem, int tn, int r0, int r1, int tid_e,
+                                              int m0, int n0, bool vec_ok) {
+  switch (p.act) {
+    case UB_ACT_SILU: splitk_finish_t<DUAL, UB_ACT_SILU>(p, smem, tn, r0, r1, tid_e, m0, n0, vec_ok); break;
+    case UB_ACT_GELU: splitk_finish_t<DUAL, UB_ACT_GELU>(p, smem, tn, r0, r1, tid_e, m0, n0, vec_ok); break;
+    case UB_ACT_GELU_TANH: splitk_finish_t<DUAL, UB_ACT_GELU_TANH>(p, smem, tn, r0, r1, tid_e, m0, n0, vec_ok); break;
+    case UB_ACT_RELU: splitk_finish_t<DUAL, UB_ACT_RELU>(p, smem, tn, r0, r1, tid_e, m0, n0, vec_ok); break;
+    case UB_ACT_RELU2: splitk_finish_t<DUAL, UB_ACT_RELU2>(p, smem, tn, r0, r1, tid_e, m0, n0, vec_ok); break;
+    case UB_ACT_QUICK_GELU: splitk_finish_t<DUAL, UB_ACT_QUICK_GELU>(p, smem, tn, r0, r1, tid_e, m0, n0, vec_ok); break;
+    case UB_ACT_SIGMOID: splitk_finish_t<DUAL, UB_ACT_SIGMOID>(p, smem, tn, r0, r1, tid_e, m0, n0, vec_ok); break;
+    case UB_ACT_TANH: splitk_finish_t<DUAL, UB_ACT_TANH>(p, smem, tn, r0, r1, tid_e, m0, n0, vec_ok); break;
+    default: splitk_finish_t<DUAL, UB_ACT_NONE>(p, smem, tn, r0, r1, tid_e, m0, n0, vec_ok); break;
   }
 }
 

@@ -95,11 +95,13 @@ def serve(eng, requests: List[dict], device: Optional[str], dist_group=None, wor
         if not eng.has_unfinished():
             time.sleep(min(0.001, max(0.0, pending[nxt]["arrival"] - now)))
             continue
+        e = None
         if cuda:
             e = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
             eng.step_events = e
-            evs.append(e)
         eng.step()
+        if e is not None and eng.step_events is None:
+            evs.append(e)                    # recorded: the step launched work (a drain-only step does not)
         steps += 1
     if cuda:
         torch.cuda.synchronize()

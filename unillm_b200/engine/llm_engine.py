@@ -414,6 +414,7 @@ class LLMEngine:
             self.runner.launch(batch)
         if ev is not None:
             ev[1].record()
+            self.step_events = None          # consumed: a caller that times steps sets a fresh pair per step
         if not self.async_scheduling:
             if tr is not None:
                 with tr.span("engine.fetch"):
