@@ -21,6 +21,8 @@
 
 extern "C" int ub_attn_decode_mma_supported(const UbAttnArgs* a);
 extern "C" int ub_attn_decode_mma_main(const UbAttnArgs* a, void* stream);
+extern "C" int ub_attn_decode_persist_supported(const UbAttnArgs* a);
+extern "C" int ub_attn_decode_persist(const UbAttnArgs* a, void* stream);
 
 namespace ub {
 
@@ -329,10 +331,23 @@ static bool decode_mma_enabled() {
   return v == 1;
 }
 
+// Short key ranges behind a shared prefix (kv_start > 0): the persistent kernel that overlaps one work item's tail with
+// the next one's copies.  UB_DECODE_PERSIST=0 keeps the one-item-per-CTA kernel.
+static bool decode_persist_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("UB_DECODE_PERSIST");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
 template <int D>
 static int launch_decode(const UbAttnArgs& a, cudaStream_t st) {
   const bool mma_ok = D <= 128 && decode_mma_enabled() && ub_attn_decode_mma_supported(&a);
-  if (a.merge_o != nullptr && (!mma_ok || a.splits != 1)) return -7;   // fused merge lives in the warp-MMA kernel only
+  if (a.merge_o != nullptr && (!mma_ok || a.splits != 1)) return -7;   // fused merge lives in the warp-MMA kernels only
+  if (mma_ok && a.kv_start > 0 && decode_persist_enabled() && ub_attn_decode_persist_supported(&a))
+    return ub_attn_decode_persist(&a, st);
   if (mma_ok) {
     int rc = ub_attn_decode_mma_main(&a, st);
     if (rc != 0) return rc;

@@ -1,0 +1,411 @@
+// K4, short key ranges: persistent paged decode attention with the copies of the NEXT work item in flight while the
+// current one is finished.
+//
+// The second pass of the cascade (every sequence attends to its own 128..256 keys behind a shared prefix) gives each
+// (sequence, kv head) work item only two to four 64-key tiles.  In attn_decode_mma.cu one CTA serves one item, so its
+// life is a chain of dependent latencies -- sequence length, block-table entries, keys / values, merge partial -- and
+// the kernel reaches 0.4 of the copy bandwidth.  Here a CTA walks over many items; while it computes the last tile
+// of an item and runs that item's epilogue, the first tile of the next item is already being copied, and the next
+// item's length, block-table entries, query rows and merge partial were requested one item earlier.
+//
+// Same math and layouts as attn_decode_mma.cu (warp-level m16n8k16 MMAs, the GQA group as the 16 MMA rows, 64-key
+// tiles gathered page by page with cp.async into XOR-swizzled shared memory, four warps with 16 keys each and their
+// own online-softmax state).  Restrictions: no sliding window, no ALiBi, no KV splits (the caller falls back to the
+// one-item-per-CTA kernel otherwise).
+//
+// Replaces in the reference: the cached attention path of LlamaAttention::forward_with_cache
+// (crates/runtime/src/models_v2/llama.rs:1027-1156) where q_len == 1.
+#include <math_constants.h>
+#include <stdlib.h>
+
+#include "../common/ptx.cuh"
+#include "../include/unillm_b200.h"
+
+namespace ub {
+namespace dper {
+
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+constexpr int KT = 64;       // keys per tile (16 per warp)
+constexpr int ROWS = 16;     // query heads per CTA (MMA M)
+constexpr int NST = 2;       // ring stages: one tile in use, one in flight
+constexpr int BT_MAX = 128;  // block-table entries kept in shared memory per item (one per thread)
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool pred) {
+  const int sz = pred ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// [rows][D] bf16 tile with 16-byte chunks XOR-swizzled by (row & 7)
+template <int D>
+__device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
+  return (uint32_t)(row * D * 2 + ((chunk ^ (row & 7)) << 4));
+}
+
+template <int D>
+struct Smem {
+  static constexpr int STAGE_BYTES = 2 * KT * D * 2;                 // K tile then V tile
+  static constexpr int RED_BYTES = 4 * ROWS * D * 4;                 // per-warp partial outputs (fp32): fits one stage
+  static_assert(RED_BYTES <= STAGE_BYTES, "the reduction buffer overlays one ring stage");
+  static constexpr int Q_OFF = NST * STAGE_BYTES;                    // 2 x [16][D] bf16, swizzled
+  static constexpr int ML_OFF = Q_OFF + 2 * ROWS * D * 2;            // [4][16][2] floats
+  static constexpr int BT_OFF = ML_OFF + 4 * ROWS * 2 * 4;           // 2 x BT_MAX block-table entries
+  static constexpr int TOTAL = BT_OFF + 2 * BT_MAX * 4;
+};
+
+// What the copy of a tile and the arithmetic on it need to know about a work item.
+struct Item {
+  int seq, kvh, gc;
+  int kv_len, kv_lo, kv_hi, tile_origin, n_tiles, page0;
+};
+
+template <int D>
+__global__ void __launch_bounds__(128, 3)
+attn_decode_persist_kernel(const UbAttnArgs a, const int gchunks, const int n_items) {
+  constexpr int CPR = D / 8;                 // 16-byte chunks per row
+  constexpr int QPT = ROWS * CPR / 128;      // query chunks per thread
+  constexpr int PRE = 4;                     // merge-partial elements per thread kept in registers (GQA group of 4)
+  using S = Smem<D>;
+  extern __shared__ __align__(128) uint8_t dsm[];
+  float (*red_ml)[ROWS][2] = reinterpret_cast<float (*)[ROWS][2]>(dsm + S::ML_OFF);
+
+  pdl_launch_dependents();
+  pdl_wait();          // no global access before the previous kernel has completed
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int Gtot = a.Hq / a.Hkv;
+  const int per_seq = a.Hkv * gchunks;
+  const int bs_shift = 31 - __clz(a.block_size);
+  const int kv_lo = max(a.kv_start, 0);                       // no window, no splits: the same for every item
+  const int tile_origin = kv_lo & ~(a.block_size - 1);
+  const int page0 = tile_origin >> bs_shift;
+  const int pages_per_tile = KT >> bs_shift;
+  const int chunks_per_page = CPR << bs_shift;
+  const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(a.k_cache);
+  const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(a.v_cache);
+  const __nv_bfloat16* mo = reinterpret_cast<const __nv_bfloat16*>(a.merge_o);
+  const float sc = a.scale * LOG2E;
+
+  // ---- the next item's metadata: requested one item ahead, held in registers until it is committed to shared memory
+  int nx_len = 0, nx_bt = -1;
+  uint4 nx_q[QPT];
+  float nx_la[PRE], nx_oa[PRE];
+  auto decode_item = [&](int item, int& seq, int& kvh, int& gc) {
+    seq = item / per_seq;
+    const int rem = item - seq * per_seq;
+    kvh = rem / gchunks;
+    gc = rem - kvh * gchunks;
+  };
+  auto request = [&](int item) {
+    int seq, kvh, gc;
+    decode_item(item, seq, kvh, gc);
+    const int h0 = kvh * Gtot + gc * ROWS;
+    const int gn = min(ROWS, Gtot - gc * ROWS);
+    nx_len = a.seq_lens[seq];
+    const int bi = page0 + (int)threadIdx.x;
+    nx_bt = bi < a.max_blocks_per_seq ? a.block_tables[(long long)seq * a.max_blocks_per_seq + bi] : -1;
+    const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(a.q) + (long long)seq * a.q_stride;
+#pragma unroll
+    for (int k = 0; k < QPT; ++k) {
+      const int i = threadIdx.x + k * 128, r = i / CPR, c = i % CPR;
+      nx_q[k] = make_uint4(0, 0, 0, 0);
+      if (r < gn) nx_q[k] = *reinterpret_cast<const uint4*>(qp + (long long)(h0 + r) * D + c * 8);
+    }
+#pragma unroll
+    for (int k = 0; k < PRE; ++k) {
+      const int i = threadIdx.x + k * 128;
+      nx_la[k] = 0.f;
+      nx_oa[k] = 0.f;
+      if (mo != nullptr && i < gn * D) {
+        const int h = h0 + i / D;
+        nx_la[k] = a.merge_lse[(long long)seq * a.Hq + h];
+        nx_oa[k] = __bfloat162float(mo[((long long)seq * a.Hq + h) * D + i % D]);
+      }
+    }
+  };
+  // writes the requested block-table entries and query rows into buffer `buf`, returns the item's key range
+  auto commit = [&](int item, int buf) {
+    int* bt_sm = reinterpret_cast<int*>(dsm + S::BT_OFF) + buf * BT_MAX;
+    uint8_t* q_sm = dsm + S::Q_OFF + buf * ROWS * D * 2;
+    bt_sm[threadIdx.x] = nx_bt;
+#pragma unroll
+    for (int k = 0; k < QPT; ++k) {
+      const int i = threadIdx.x + k * 128, r = i / CPR, c = i % CPR;
+      *reinterpret_cast<uint4*>(q_sm + tile_off<D>(r, c)) = nx_q[k];
+    }
+    Item it;
+    decode_item(item, it.seq, it.kvh, it.gc);
+    it.kv_len = nx_len;
+    it.kv_lo = kv_lo;
+    it.kv_hi = nx_len;
+    it.tile_origin = tile_origin;
+    it.page0 = page0;
+    const int nt = it.kv_hi > tile_origin ? (it.kv_hi - tile_origin + KT - 1) / KT : 0;
+    it.n_tiles = max(nt, 1);               // an empty range still runs one (fully masked, zero-filled) tile
+    return it;
+  };
+  // copies tile t of an item into ring stage `stage`: whole pages, 16-byte chunks at consecutive addresses
+  auto issue_tile = [&](const Item& it, int buf, int t, int stage) {
+    const int* bt_sm = reinterpret_cast<const int*>(dsm + S::BT_OFF) + buf * BT_MAX;
+    uint8_t* st = dsm + stage * S::STAGE_BYTES;
+    const int t0 = it.tile_origin + t * KT;
+    for (int pg = 0; pg < pages_per_tile; ++pg) {
+      const int pos0 = t0 + (pg << bs_shift);
+      const int nvalid = min(max(it.kv_hi - pos0, 0), a.block_size);       // keys of this page that exist
+      long long base = 0;
+      if (nvalid > 0) {
+        const int bi = pos0 >> bs_shift;
+        int blk = -1;
+        if (bi < a.max_blocks_per_seq)
+          blk = (bi - it.page0) < BT_MAX ? bt_sm[bi - it.page0] : a.block_tables[(long long)it.seq * a.max_blocks_per_seq + bi];
+        if (blk < 0 || blk >= a.num_blocks) set_err(a.err, ERR_BOUNDS, it.seq);
+        else base = (((long long)blk * a.Hkv + it.kvh) << bs_shift) * D;
+      }
+      for (int c = threadIdx.x; c < chunks_per_page; c += 128) {
+        const int tr = c / CPR;
+        const int r = (pg << bs_shift) + tr;
+        const bool ok = tr < nvalid;
+        const uint32_t dst = tile_off<D>(r, c % CPR);
+        cp_async16(st + dst, kc + base + c * 8, ok);
+        cp_async16(st + KT * D * 2 + dst, vc + base + c * 8, ok);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  int item = blockIdx.x;
+  if (item >= n_items) return;
+  request(item);
+  Item cur = commit(item, 0);
+  float cur_la[PRE], cur_oa[PRE];
+#pragma unroll
+  for (int k = 0; k < PRE; ++k) { cur_la[k] = nx_la[k]; cur_oa[k] = nx_oa[k]; }
+  __syncthreads();                                   // block-table entries and query rows of the first item are visible
+  int g = 0;                                         // flat tile counter over all items of this CTA: ring stage = g % NST
+  int buf = 0;
+  issue_tile(cur, buf, 0, 0);
+
+  const int ra = lane >> 2, rb = ra + 8;             // this thread's MMA rows (query heads of the group)
+  while (true) {
+    const int next_item = item + (int)gridDim.x;
+    const bool has_next = next_item < n_items;
+    if (has_next) request(next_item);                // its loads run under the wait for this item's first tile
+    const int h0 = cur.kvh * Gtot + cur.gc * ROWS;
+    const int gn = min(ROWS, Gtot - cur.gc * ROWS);
+    const uint8_t* q_sm = dsm + S::Q_OFF + buf * ROWS * D * 2;
+    uint32_t qf[D / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
+      const int c = ks * 2 + (lane >> 4);
+      ldsm_x4(smem_u32(q_sm + tile_off<D>(r, c)), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+    }
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_a = -CUDART_INF_F, m_b = -CUDART_INF_F, l_a = 0.f, l_b = 0.f;
+    Item nxt = cur;
+
+    for (int t = 0; t < cur.n_tiles; ++t, ++g) {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      __syncthreads();                     // flat tile g is visible; everyone is done with tile g - 1 and with the
+                                           // previous item's reduction buffer, which lived in the stage filled next
+      if (t == 0 && has_next) {
+        nxt = commit(next_item, buf ^ 1);
+        __syncthreads();                   // the next item's block-table entries are visible before its first copy
+      }
+      if (t + 1 < cur.n_tiles) issue_tile(cur, buf, t + 1, (g + 1) % NST);
+      else if (has_next) issue_tile(nxt, buf ^ 1, 0, (g + 1) % NST);
+      else asm volatile("cp.async.commit_group;" ::: "memory");
+
+      const uint8_t* kb = dsm + (g % NST) * S::STAGE_BYTES;
+      const uint8_t* vb = kb + KT * D * 2;
+      const int tw0 = warp * 16;           // this warp's 16 keys inside the tile
+      const int t0 = cur.tile_origin + t * KT + tw0;
+      if (t0 >= cur.kv_hi || t0 + 16 <= cur.kv_lo) continue;   // warp-uniform: nothing visible in this warp's slice
+
+      float s[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const int mi = lane >> 3;
+        const int r = tw0 + (mi >> 1) * 8 + (lane & 7);
+        const int c = ks * 2 + (mi & 1);
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(smem_u32(kb + tile_off<D>(r, c)), b0, b1, b2, b3);
+        mma_bf16(s[0], qf[ks], b0, b1);
+        mma_bf16(s[1], qf[ks], b2, b3);
+      }
+      float mx_a = m_a, mx_b = m_b;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int kpos = t0 + j * 8 + (lane & 3) * 2 + (e & 1);
+          float v = s[j][e] * sc;
+          v = (kpos < cur.kv_hi && kpos >= cur.kv_lo) ? v : -CUDART_INF_F;
+          s[j][e] = v;
+          if (e >= 2) mx_b = fmaxf(mx_b, v); else mx_a = fmaxf(mx_a, v);
+        }
+      }
+      mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+      mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+      const float al_a = (mx_a == -CUDART_INF_F) ? 1.f : exp2f(m_a - mx_a);
+      const float al_b = (mx_b == -CUDART_INF_F) ? 1.f : exp2f(m_b - mx_b);
+      m_a = mx_a; m_b = mx_b;
+      float ps_a = 0.f, ps_b = 0.f;
+      uint32_t pf[4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const float p0 = (s[j][0] == -CUDART_INF_F) ? 0.f : exp2f(s[j][0] - mx_a);
+        const float p1 = (s[j][1] == -CUDART_INF_F) ? 0.f : exp2f(s[j][1] - mx_a);
+        const float p2 = (s[j][2] == -CUDART_INF_F) ? 0.f : exp2f(s[j][2] - mx_b);
+        const float p3 = (s[j][3] == -CUDART_INF_F) ? 0.f : exp2f(s[j][3] - mx_b);
+        ps_a += p0 + p1; ps_b += p2 + p3;
+        pf[j * 2 + 0] = pack_bf16x2(p0, p1);     // accumulator layout of two adjacent n8 tiles == A fragment of a k16 step
+        pf[j * 2 + 1] = pack_bf16x2(p2, p3);
+      }
+      l_a = l_a * al_a + ps_a;
+      l_b = l_b * al_b + ps_b;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) { o[i][0] *= al_a; o[i][1] *= al_a; o[i][2] *= al_b; o[i][3] *= al_b; }
+#pragma unroll
+      for (int dp = 0; dp < D / 16; ++dp) {
+        const int mi = lane >> 3;
+        const int r = tw0 + (mi & 1) * 8 + (lane & 7);
+        const int c = dp * 2 + (mi >> 1);
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(smem_u32(vb + tile_off<D>(r, c)), b0, b1, b2, b3);
+        mma_bf16(o[dp * 2], pf, b0, b1);
+        mma_bf16(o[dp * 2 + 1], pf, b2, b3);
+      }
+    }
+
+    // ---- epilogue of the current item.  The stage of its last tile is free (the copy in flight, if any, fills the
+    // other one): the four warps' partial outputs are combined there.
+    __syncthreads();                           // every warp is done with the last tile
+    float (*red_o)[ROWS][D] = reinterpret_cast<float (*)[ROWS][D]>(dsm + ((g + NST - 1) % NST) * S::STAGE_BYTES);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      const int d = i * 8 + (lane & 3) * 2;
+      if (ra < gn) { red_o[warp][ra][d] = o[i][0]; red_o[warp][ra][d + 1] = o[i][1]; }
+      if (rb < gn) { red_o[warp][rb][d] = o[i][2]; red_o[warp][rb][d + 1] = o[i][3]; }
+    }
+    if ((lane & 3) == 0) {
+      if (ra < gn) { red_ml[warp][ra][0] = m_a; red_ml[warp][ra][1] = l_a; }
+      if (rb < gn) { red_ml[warp][rb][0] = m_b; red_ml[warp][rb][1] = l_b; }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x, it = 0; i < gn * D; i += 128, ++it) {
+      const int gq = i / D, d = i % D;
+      float mx = -CUDART_INF_F;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) mx = fmaxf(mx, red_ml[w][gq][0]);
+      float lt = 0.f, ov = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float scw = (red_ml[w][gq][0] == -CUDART_INF_F) ? 0.f : exp2f(red_ml[w][gq][0] - mx);
+        lt += red_ml[w][gq][1] * scw;
+        ov += red_o[w][gq][d] * scw;
+      }
+      const float inv = lt > 0.f ? 1.f / lt : 0.f;
+      float lse = lt > 0.f ? (mx + log2f(lt)) * LN2 : -CUDART_INF_F;
+      const int h = h0 + gq;
+      float val = ov * inv;
+      if (mo != nullptr) {
+        // fold in the partial result over the other key set (shared prefix): weights exp(lse_x - max)
+        float la, oa;
+        if (it < PRE) {
+          la = it == 0 ? cur_la[0] : it == 1 ? cur_la[1] : it == 2 ? cur_la[2] : cur_la[3];
+          oa = it == 0 ? cur_oa[0] : it == 1 ? cur_oa[1] : it == 2 ? cur_oa[2] : cur_oa[3];
+        } else {
+          la = a.merge_lse[(long long)cur.seq * a.Hq + h];
+          oa = __bfloat162float(mo[((long long)cur.seq * a.Hq + h) * D + d]);
+        }
+        const float mm = fmaxf(la, lse);
+        const float wa = (la == -CUDART_INF_F) ? 0.f : __expf(la - mm);
+        const float wb = (lse == -CUDART_INF_F) ? 0.f : __expf(lse - mm);
+        const float den = wa + wb;
+        val = den > 0.f ? (wa * oa + wb * val) / den : 0.f;
+        lse = den > 0.f ? mm + __logf(den) : -CUDART_INF_F;
+      }
+      reinterpret_cast<__nv_bfloat16*>(a.out)[(long long)cur.seq * a.o_stride + (long long)h * D + d] = __float2bfloat16(val);
+      if (d == 0 && a.lse != nullptr) a.lse[(long long)cur.seq * a.Hq + h] = lse;
+    }
+    if (!has_next) break;
+    // the reduction buffer is read above; the stage it lives in is refilled only after the barrier at the top of the
+    // next item's first tile
+    item = next_item;
+    cur = nxt;
+    buf ^= 1;
+#pragma unroll
+    for (int k = 0; k < PRE; ++k) { cur_la[k] = nx_la[k]; cur_oa[k] = nx_oa[k]; }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+template <int D>
+static int launch(const UbAttnArgs& a, cudaStream_t st) {
+  constexpr int SMEM = Smem<D>::TOTAL;
+  static bool attr_set[UB_MAX_DEVICES] = {};
+  static int sms[UB_MAX_DEVICES] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= UB_MAX_DEVICES) return -1;
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_persist_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return -(int)e;
+    cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+    attr_set[dev] = true;
+  }
+  const int Gtot = a.Hq / a.Hkv;
+  const int gchunks = (Gtot + ROWS - 1) / ROWS;
+  const int n_items = a.num_seqs * a.Hkv * gchunks;
+  if (n_items <= 0) return 0;
+  int grid = 3 * sms[dev];                       // three resident CTAs per SM
+  if (grid > n_items) grid = n_items;
+  cudaError_t e = ub::launch_pdl(attn_decode_persist_kernel<D>, dim3(grid), dim3(128), (size_t)SMEM, st, a, gchunks, n_items);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+}  // namespace dper
+}  // namespace ub
+
+// Persistent decode attention for short key ranges.  Supported: head size 64 / 128, page sizes 8..64, no sliding
+// window, no ALiBi, no KV splits; the caller checks with ub_attn_decode_persist_supported.
+extern "C" int ub_attn_decode_persist_supported(const UbAttnArgs* a) {
+  if (a->D != 64 && a->D != 128) return 0;
+  if (a->block_size < 8 || a->block_size > 64 || (a->block_size & (a->block_size - 1))) return 0;
+  if (a->Hkv <= 0 || a->Hq % a->Hkv != 0 || a->q_stride % 8 != 0) return 0;
+  if (a->window > 0 || a->alibi_slopes != nullptr || a->splits != 1) return 0;
+  if ((reinterpret_cast<uintptr_t>(a->q) & 15) || (reinterpret_cast<uintptr_t>(a->k_cache) & 15) ||
+      (reinterpret_cast<uintptr_t>(a->v_cache) & 15))
+    return 0;
+  return 1;
+}
+
+extern "C" int ub_attn_decode_persist(const UbAttnArgs* a, void* stream) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  return a->D == 64 ? ub::dper::launch<64>(*a, st) : ub::dper::launch<128>(*a, st);
+}

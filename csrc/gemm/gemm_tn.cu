@@ -1072,7 +1072,7 @@ static int max_active_clusters(int csize) {
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL) == cudaSuccess) {
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(192, 1, 1);
-    cfg.gridDim = dim3(csize, 64, 1);
+    cfg.gridDim = dim3(csize, 4096, 1);          // far more clusters than fit: the answer must not be capped by the grid
     cfg.dynamicSmemBytes = S::TOTAL;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;

@@ -363,6 +363,50 @@ def test_gemm_2cta_dual(M, I, K, tile):
     _close(out, torch.nn.functional.silu(g) * u)
 
 
+def test_decode_suffix_persistent_many_items():
+    """The persistent suffix-decode kernel with more work items than resident CTAs (every CTA walks over several
+    items with the next item's copies in flight), ragged suffix lengths, sequences that end before the suffix
+    starts, with and without the fused merge; oracle = fp32 attention over the visible keys."""
+    from unillm_b200.ops import cuda_ops
+
+    Hq, Hkv, D, P, B = 16, 4, 128, 64, 160                 # 160 x 4 = 640 items > 3 x 148 CTAs
+    g = torch.Generator().manual_seed(5)
+    kv_lens = [int(v) for v in torch.randint(P + 1, P + 200, (B,), generator=g)]
+    kv_lens[3], kv_lens[77] = P, P - 7                      # nothing behind the prefix
+    kc, vc, bt, sl, dk, dv = make_paged_cache(B, kv_lens, Hkv, D, seed=43)
+    q = _rand(B, Hq, D, seed=44)
+    out, lse = cuda_ops.attn_decode(q, kc, vc, bt, sl, kv_start=P, splits=1, return_lse=True)
+    oa = _rand(B, Hq, D, seed=45)
+    la = torch.randn(B, Hq, generator=torch.Generator().manual_seed(46)).cuda()
+    fused = cuda_ops.attn_decode(q, kc, vc, bt, sl, kv_start=P, splits=1, merge=(oa, la))
+    sep = cuda_ops.attn_merge(oa, la, out, lse)
+    torch.cuda.synchronize()
+    cuda_ops.check_device_errors()
+    for i in (0, 1, 2, 3, 50, 77, 78, 158, 159):
+        l = kv_lens[i]
+        if l <= P:
+            assert out[i].abs().max().item() == 0.0 and torch.isinf(lse[i]).all()
+            continue
+        ro, _ = ref_attention(q[i:i + 1].cpu(), dk[i], dv[i], causal_offset=l - 1, kv_start=P)
+        _close(out[i:i + 1], ro)
+    _close(fused, sep, rtol=2e-2, atol=1e-2)
+    # the one-item-per-CTA kernel gives the same answer
+    import os, subprocess, sys
+    code = ("import torch,sys;sys.path.insert(0,%r);from tests.test_gpu_kernels import make_paged_cache,_rand;"
+            "from unillm_b200.ops import cuda_ops;"
+            "kc,vc,bt,sl,dk,dv=make_paged_cache(%d,%r,%d,%d,seed=43);q=_rand(%d,%d,%d,seed=44);"
+            "o=cuda_ops.attn_decode(q,kc,vc,bt,sl,kv_start=%d,splits=1);torch.save(o.cpu(),sys.argv[1])"
+            % (os.path.dirname(os.path.dirname(os.path.abspath(__file__))), B, kv_lens, Hkv, D, B, Hq, D, P))
+    import tempfile
+    with tempfile.TemporaryDirectory() as td:
+        f = os.path.join(td, "o.pt")
+        r = subprocess.run([sys.executable, "-c", code, f], env=dict(os.environ, UB_DECODE_PERSIST="0"),
+                           capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr[-2000:]
+        ref = torch.load(f)
+    _close(out.cpu(), ref.float(), rtol=1e-2, atol=5e-3)
+
+
 def test_attention_fused_merge_matches_separate_merge():
     """Suffix kernels that fold a prefix partial into their output == suffix partial + merge kernel == full attention."""
     from unillm_b200.ops import cuda_ops
