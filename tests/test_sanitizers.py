@@ -23,6 +23,9 @@ def test_kv_core_under_sanitizer(tmp_path, flags, marker):
         pytest.skip("sanitizer runtime not installed")
     assert b.returncode == 0, b.stderr[-2000:]
     r = subprocess.run([exe, "150"], capture_output=True, text=True, timeout=300)
+    if r.returncode != 0 and ("unexpected memory mapping" in r.stderr or "Shadow memory range interleaves" in r.stderr
+                              or "failed to allocate" in r.stderr.lower() and "free 192" not in r.stdout):
+        pytest.skip("sanitizer runtime cannot start in this environment: " + r.stderr.strip().splitlines()[-1][:120])
     assert r.returncode == 0, r.stdout + r.stderr[-3000:]
     assert marker not in r.stderr, r.stderr[-3000:]
     assert "free 192 of 192" in r.stdout
