@@ -189,24 +189,28 @@ attn_decode_persist_kernel(const __grid_constant__ CUtensorMap tmk, const __grid
     uint8_t* st = dsm + stage * S::STAGE_BYTES;
     const int t0 = it.tile_origin + t * KT;
     if (TMA) {
-      // one thread: arm the stage's barrier with the bytes of the pages that exist, then one box per page and plane
+      // thread 0 arms the stage's barrier with the bytes of the pages that exist; lane 0 of every warp copies the
+      // pages pg = warp, warp + 4, ... (one box per page and plane), so no single warp carries all the issue work.
+      // A copy may complete before the barrier is armed: the phase cannot end while thread 0's arrival is pending.
+      // first global row of page pg in the cache view, or -1 when the page is past the end of the sequence
+      auto page_row = [&](int pg) {
+        const int pos0 = t0 + (pg << bs_shift);
+        if (pos0 >= it.kv_hi) return -1;
+        const int bi = pos0 >> bs_shift;
+        int blk = -1;
+        if (bi < a.max_blocks_per_seq)
+          blk = (bi - it.page0) < BT_MAX ? bt_sm[bi - it.page0] : a.block_tables[(long long)it.seq * a.max_blocks_per_seq + bi];
+        if (blk < 0 || blk >= a.num_blocks) { set_err(a.err, ERR_BOUNDS, it.seq); return -1; }
+        return (blk * a.Hkv + it.kvh) << bs_shift;
+      };
       if (threadIdx.x == 0) {
-        // first global row of page pg in the cache view, or -1 when the page is past the end of the sequence
-        auto page_row = [&](int pg) {
-          const int pos0 = t0 + (pg << bs_shift);
-          if (pos0 >= it.kv_hi) return -1;
-          const int bi = pos0 >> bs_shift;
-          int blk = -1;
-          if (bi < a.max_blocks_per_seq)
-            blk = (bi - it.page0) < BT_MAX ? bt_sm[bi - it.page0] : a.block_tables[(long long)it.seq * a.max_blocks_per_seq + bi];
-          if (blk < 0 || blk >= a.num_blocks) { set_err(a.err, ERR_BOUNDS, it.seq); return -1; }
-          return (blk * a.Hkv + it.kvh) << bs_shift;
-        };
         uint32_t bytes = 0;
         for (int pg = 0; pg < pages_per_tile; ++pg)
           if (page_row(pg) >= 0) bytes += 2u * (uint32_t)a.block_size * D * 2u;
         mbar_arrive_expect_tx(&bars[stage], bytes);
-        for (int pg = 0; pg < pages_per_tile; ++pg) {
+      }
+      if (lane == 0) {
+        for (int pg = warp; pg < pages_per_tile; pg += 4) {
           const int row = page_row(pg);
           if (row < 0) continue;
           uint8_t* dk = st + (pg << bs_shift) * 128;
