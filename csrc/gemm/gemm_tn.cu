@@ -1099,8 +1099,16 @@ static GemmPlan plan_gemm(const UbGemmArgs* a) {
     // measured slower at every size
     while (tn < a->M && tn < (dual ? 128 : 256)) tn <<= 1;
   }
-  pl.tn = tn;
   const bool grouped = a->grp_tiles != nullptr;
+  if (a->tile_tokens <= 0 && !grouped && !dual) {
+    // Short K (per-rank o / down projections under tensor parallelism): the main loop is a few microseconds and what
+    // the launch pays for is the exposed epilogue of its single tile per CTA (0.8 us per 32 token columns).  Narrower
+    // token tiles give more CTAs with shorter epilogues as long as everything still fits in one wave.
+    const int nn = (a->N + BM_W - 1) / BM_W, kb = (a->K + BK - 1) / BK, sm = num_sms();
+    auto tiles_of = [&](int t) { return ((a->M + t - 1) / t) * nn; };
+    while (kb <= 32 && tn > 64 && tiles_of(tn) * 2 <= sm && tiles_of(tn / 2) <= sm) tn >>= 1;
+  }
+  pl.tn = tn;
   const int num_m = grouped ? a->grp_max_tiles : (a->M + tn - 1) / tn, num_n = (a->N + BM_W - 1) / BM_W;
   pl.tiles = num_m * num_n;
   const int num_kb = (a->K + BK - 1) / BK;
@@ -1180,7 +1188,9 @@ static GemmPlan plan_gemm(const UbGemmArgs* a) {
     const int pairs_now = max_active_clusters(2);
     const bool ragged = tiles2 > pairs_now && (tiles2 % pairs_now) * 2 <= pairs_now && (tiles2 % pairs_now) != 0;
     const int want_s = a->pair_splits > 0 ? a->pair_splits : s2;
-    if (want == 2 || (a->tile_tokens <= 0 && ((gains && enough && !(ragged && !dual)) || want_s > 1))) {
+    // short K in a single wave: the narrow 1-CTA tiles chosen above (more CTAs, shorter exposed epilogues) win
+    const bool short_single = !dual && num_kb <= 32 && tiles2 <= pairs_now;
+    if (want == 2 || (a->tile_tokens <= 0 && !short_single && ((gains && enough && !(ragged && !dual)) || want_s > 1))) {
       pl.pair = 1;
       pl.tn = tn2;
       pl.tiles = tiles2;
