@@ -103,9 +103,9 @@ class ClockSampler:
 
 
 def reference_arm(args):
-    # The reference is a Rust workspace with no Python packaging: `pip install --no-index ... /root/reference`
-    # answers "neither setup.py nor pyproject.toml found", and there is no cargo/rustc on this machine or on
-    # the GPU box to build it another way.
+    # The reference is a Rust workspace with no Python packaging: an offline `pip install --no-index` of its source
+    # tree answers "neither setup.py nor pyproject.toml found", and there is no cargo / rustc available to build it
+    # another way.
     print(json.dumps({"impl": "reference", "unavailable":
                       "reference is a Rust/Candle CPU workspace: not pip-installable (no setup.py/pyproject.toml) "
                       "and no Rust toolchain offline; it has no GPU or multi-GPU path to run"}))

@@ -82,11 +82,11 @@ extern "C" int ub_allreduce_oneshot(const UbAllReduceArgs* a, void* stream_v) {
 // ----------------------------------------------------------------------------------------------
 // F4: vocabulary-parallel greedy merge.  Every rank holds, per sampled row, the best (value, id) of its
 // vocabulary shard.  One single-block kernel pushes the pairs into every peer's slot [parity][rank],
-// bumps the peers' counters, waits (bounded) until all `world` ranks have arrived for this round and
+// bumps the peers' counters, waits (bounded) until all `world` ranks have arrived for this exchange and
 // picks the global winner (highest value, lowest id on ties) -- the same answer on every rank.
-// The round number lives in a device word that the kernel itself increments, so the launch can sit in
-// a CUDA graph; slots alternate by round parity because a fast rank may start round n+1 while a slow
-// one still reads round n.
+// The exchange number lives in a device word that the kernel itself increments, so the launch can sit in
+// a CUDA graph; slots alternate by its parity because a fast rank may start exchange n+1 while a slow
+// one still reads exchange n.
 // ----------------------------------------------------------------------------------------------
 namespace ub {
 
