@@ -120,6 +120,46 @@ def bench_gemm(results, only=None, tile=0, pair=0):
         print(json.dumps(r))
 
 
+def gemm_timeline(shape: str, pair: int = 0, tile: int = 0):
+    """Per-CTA timeline of one 1-CTA GEMM launch (needs ``UB_GEMM_DEBUG=4`` in the environment before the library is
+    loaded): microseconds from the first CTA's entry to set-up done, first operand stage landed, last MMA issued,
+    accumulator complete, split-K barriers / pushes / finish, and exit; mean / min / max over the CTAs of the launch."""
+    import ctypes as C
+
+    import numpy as np
+
+    from ..ops._native import cuda_lib
+
+    M, N, K = [int(v) for v in shape.split(",")[:3]]
+    names = ["entry", "setup done", "1st stage landed", "last MMA issued", "accumulator ready", "epilogue stores issued",
+             "split-K finish done", "exit", "cluster barrier 1", "partials pushed", "cluster barrier 2"]
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(3):
+        flush.fill_(1)
+        cuda_ops.gemm_tn(x, w, out=out, tile_tokens=tile, cta_pair=pair or 1)
+        torch.cuda.synchronize()
+    buf = np.zeros((512, 12), dtype=np.uint64)
+    rc = cuda_lib().ub_gemm_debug_timeline(buf.ctypes.data_as(C.c_void_p))
+    if rc != 0 or not (buf[:, 0] > 0).any():
+        raise RuntimeError("no timeline recorded: set UB_GEMM_DEBUG=4 (the 2-CTA kernel records none: use --pair 1)")
+    t = buf.astype(np.float64)
+    used = (t[:, 0] > 0) & (t[:, 0] > t[:, 0].max() - 2e5)          # the CTAs of the last launch
+    t0 = t[used, 0].min()
+    rows = {}
+    for k in (0, 1, 2, 3, 4, 5, 8, 9, 10, 6, 7):
+        col = t[used, k]
+        ok = col > 0
+        if ok.any():
+            rows[names[k]] = [round(float((col[ok].mean() - t0) / 1e3), 2), round(float((col[ok].min() - t0) / 1e3), 2),
+                              round(float((col[ok].max() - t0) / 1e3), 2)]
+    r = dict(kind="gemm_timeline", M=M, N=N, K=K, ctas=int(used.sum()), us_mean_min_max=rows)
+    print(json.dumps(r))
+    return r
+
+
 def bench_attn(results, case="all"):
     hbm, tf, how = _peaks()
     decode_cases = [(256, 1152, 32, 8, 128), (64, 4096, 32, 8, 128), (256, 1152, 4, 1, 128), (8, 4096, 8, 1, 128)]
@@ -210,9 +250,13 @@ def main(argv=None):
     ap.add_argument("--json", default=None)
     ap.add_argument("--shape", default=None, help="gemm only: M,N,K,dual -- run just this shape")
     ap.add_argument("--tile", type=int, default=0, help="gemm only: force the token-tile width")
+    ap.add_argument("--timeline", default=None, help="gemm only: M,N,K -- per-CTA timeline of one launch (UB_GEMM_DEBUG=4)")
     ap.add_argument("--pair", type=int, default=0, help="gemm only: 0 auto, 1 never, 2 always use the 2-CTA kernel")
     a = ap.parse_args(argv)
     results = []
+    if a.timeline:
+        results.append(gemm_timeline(a.timeline, a.pair, a.tile))
+        return
     if a.what in ("gemm", "all"):
         bench_gemm(results, tuple(int(v) for v in a.shape.split(",")) if a.shape else None, a.tile, a.pair)
     if a.what in ("attn", "all"):
