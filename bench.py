@@ -106,6 +106,8 @@ def reference_arm(args):
     # The reference is a Rust workspace with no Python packaging: an offline `pip install --no-index` of its source
     # tree answers "neither setup.py nor pyproject.toml found", and there is no cargo / rustc available to build it
     # another way.
+    if int(os.environ.get("RANK", "0")) != 0:
+        return 0                                   # under torchrun only rank 0 reports
     print(json.dumps({"impl": "reference", "unavailable":
                       "reference is a Rust/Candle CPU workspace: not pip-installable (no setup.py/pyproject.toml) "
                       "and no Rust toolchain offline; it has no GPU or multi-GPU path to run"}))
