@@ -4,7 +4,7 @@
 one rank per GPU, tensor parallel over all N ranks).
 
 Workload (the prefix-sharing serving configuration, in steady state): ``--batch`` concurrent requests
-(default 256), every request = a 1024-token prefix shared by all requests + a unique 128-token suffix
+(default 512), every request = a 1024-token prefix shared by all requests + a unique 128-token suffix
 (random ids), 128 greedy output tokens, random-init bf16 weights, paged KV with 16-token blocks and the
 radix prefix cache on.  The request stream never dries up: whenever a request finishes a new one is
 queued, and the first wave gets staggered output budgets so that from the first timed step on, every
@@ -18,10 +18,17 @@ Two timings of the same K steps are reported:
                  of the step's inputs, kernels, device -> host read of the sampled tokens), barrier and
                  synchronize on both sides, maximum over ranks.
 Model weights (16 GB) are far larger than L2, so every step streams its inputs from HBM.
+
+Before the timed steps the engine runs untimed until every CUDA graph that the steady state needs has been
+captured (one whole output period without a new capture); during the timed steps a shape that still has no
+graph runs as plain launches instead of being captured, and the line says how many such steps there were.
+The line also carries the per-step device times (median / min / max), every rank's device and host time,
+the count of fused and NCCL-path steps, and the latency of the requests that lived inside the timed steps.
 """
 from __future__ import annotations
 
 import argparse
+import dataclasses
 import json
 import os
 import subprocess
@@ -54,29 +61,90 @@ MODELS = {
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    """SM clock and throttle reasons of one GPU, sampled every 20 ms while the timed region runs.
 
+    NVML is opened and the device handle looked up BEFORE the timed region (``prepare``), inside this process, so
+    that nothing but two cheap queries per sample happens while the steps are timed.  (Starting one ``nvidia-smi``
+    process per rank at the start of the timed region put eight NVML initialisations, each enumerating all GPUs of
+    the box, inside a window of a few hundred milliseconds.)  ``nvidia-smi`` remains the fallback when the NVML
+    binding cannot be imported; it is then started early, in ``prepare``."""
+
+    REASONS = ((0x8, "hw_slowdown"), (0x40, "hw_thermal_slowdown"), (0x20, "sw_thermal_slowdown"),
+               (0x4, "sw_power_cap"), (0x80, "hw_power_brake_slowdown"))
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index, self.proc, self.lines = index, None, []
+    def __init__(self, torch_index: int):
+        self.index, self.nvml, self.handle, self.proc = torch_index, None, None, None
+        self.samples, self.lines, self.max_mhz = [], [], None
+        self._stop = threading.Event()
+        self._on = False
+        self.thread = None
 
-    def start(self):
+    def prepare(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.t = threading.Thread(target=self._read, daemon=True)
-            self.t.start()
+            import pynvml
+            import torch
+
+            pynvml.nvmlInit()
+            h = None
+            try:
+                uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+                h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+            except Exception:
+                vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+                phys = self.index
+                if vis:
+                    try:
+                        phys = int(vis.split(",")[self.index])
+                    except ValueError:
+                        phys = self.index
+                h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            self.nvml, self.handle = pynvml, h
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
         except Exception:
-            self.proc = None
+            self.nvml = None
+            try:
+                self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                              "--format=csv,noheader,nounits", "-lms", "50"],
+                                             stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                self.thread = threading.Thread(target=self._read, daemon=True)
+                self.thread.start()
+            except Exception:
+                self.proc = None
+
+    def _poll(self):
+        n, h = self.nvml, self.handle
+        reasons = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or n.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self._stop.is_set():
+            if self._on:
+                try:
+                    self.samples.append((float(n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)), int(reasons(h))))
+                except Exception:
+                    pass
+            self._stop.wait(0.02)
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            if self._on:
+                self.lines.append(line.strip())
+
+    def start(self):
+        self._on = True
 
     def stop(self):
+        self._on = False
+        self._stop.set()
+        if self.nvml is not None:
+            sm = sorted(s for s, _ in self.samples)
+            bits = 0
+            for _, b in self.samples:
+                bits |= b
+            return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.max_mhz,
+                    "reasons": sorted(name for bit, name in self.REASONS if bits & bit), "samples": len(sm),
+                    "source": "nvml, sampled in-process every 20 ms during the timed steps"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -99,7 +167,7 @@ class ClockSampler:
                     reasons.add(name)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "source": "nvidia-smi -lms 50, started before the warm-up"}
 
 
 def reference_arm(args):
@@ -114,6 +182,14 @@ def reference_arm(args):
     return 0
 
 
+def _median(xs):
+    xs = sorted(xs)
+    n = len(xs)
+    if n == 0:
+        return None
+    return xs[n // 2] if n % 2 else 0.5 * (xs[n // 2 - 1] + xs[n // 2])
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -121,7 +197,7 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="llama3-8b", choices=sorted(MODELS))
-    ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--batch", type=int, default=512)
     ap.add_argument("--prefix-len", type=int, default=1024)
     ap.add_argument("--suffix-len", type=int, default=128)
     ap.add_argument("--output-len", type=int, default=128)
@@ -131,6 +207,13 @@ def main(argv=None) -> int:
     ap.add_argument("--profile-ops", action="store_true", help="print device ms per op over the timed steps (eager mode)")
     ap.add_argument("--baseline-collectives", action="store_true",
                     help="tensor parallel with NCCL all-reduce between separate kernels instead of the fused path")
+    ap.add_argument("--library-baseline", action="store_true",
+                    help="N > 1: also time the NCCL + separate-kernel path in the same process group (before the fused "
+                         "path) and report it under 'library_baseline'")
+    ap.add_argument("--emulate-shard", type=int, default=0, metavar="W",
+                    help="1 GPU: run the per-rank shapes of W-way tensor parallelism (heads, KV heads, MLP width and "
+                         "vocabulary divided by W) without any communication -- the compute floor of one rank; "
+                         "the token counts it prints are not a throughput of the full model")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return reference_arm(args)
@@ -167,6 +250,12 @@ def main(argv=None) -> int:
     else:
         cfg = C.LlamaConfig(**MODELS[args.model])
         spec = LlamaModel.spec_from_config(cfg)
+    if args.emulate_shard > 1:
+        if world > 1 or moe:
+            raise SystemExit("--emulate-shard is a 1-GPU mode for dense models")
+        W = args.emulate_shard
+        spec = dataclasses.replace(spec, num_heads=spec.num_heads // W, num_kv_heads=max(1, spec.num_kv_heads // W),
+                                   intermediate_size=spec.intermediate_size // W, vocab_size=spec.vocab_size // W)
     B, PL, SL, OL = args.batch, args.prefix_len, args.suffix_len, args.output_len
     bs = 16
     max_len = PL + SL + OL + bs
@@ -174,6 +263,9 @@ def main(argv=None) -> int:
     num_blocks = max(2 * blocks_needed, 1024)
     # MoE models: attention tensor parallel + expert parallel (whole experts per rank) when the ranks divide the experts
     weights = RunnerWeights.random(spec, dev, rank, world, seed=1234, expert_parallel=moe)
+    V = spec.vocab_size
+    sampler = ClockSampler(local)
+    sampler.prepare()
 
     def setup(fused: bool):
         """Engine in steady state with its CUDA graphs captured (all untimed)."""
@@ -189,7 +281,6 @@ def main(argv=None) -> int:
                         max_model_len=max_len, enable_prefix_caching=True, async_scheduling=not args.sync_scheduling)
 
         g = torch.Generator().manual_seed(2024)
-        V = cfg.vocab_size
         prefix = torch.randint(0, V, (PL,), generator=g).tolist()
 
         def new_prompt():
@@ -210,12 +301,13 @@ def main(argv=None) -> int:
         while any(s.first_token_time is None for s in first_wave) and eng.stats.steps < 400:
             eng.step()
             top_up()
-            if fused:
-                cuda_ops.check_device_errors()      # a bounded wait that gave up: stop at once and fall back
-        # setup (untimed): CUDA-graph capture is a one-time cost per step shape; run until the set of captured
-        # shapes has been stable for a while so that no capture falls into the timed steps
+        if eng.stats.device_errors:
+            raise RuntimeError(f"{eng.stats.device_errors} steps reported a device error during setup")
+        # setup (untimed): CUDA-graph capture is a one-time cost per step shape.  The workload repeats with the
+        # output length as its period, so the set of shapes is complete once a whole period (and a margin) has
+        # passed without a new capture.
         stable = guard = 0
-        while runner.use_cuda_graphs and stable < 48 and guard < 600:
+        while runner.use_cuda_graphs and stable < OL + 16 and guard < 6 * OL:
             n_graphs = len(runner.graphs)
             eng.step()
             top_up()
@@ -227,7 +319,79 @@ def main(argv=None) -> int:
         eng.flush()                      # nothing launched before the timed steps is read inside them
         torch.cuda.synchronize()
         cuda_ops.check_device_errors()
+        if eng.stats.device_errors:
+            raise RuntimeError(f"{eng.stats.device_errors} steps reported a device error during setup")
         return tp, runner, eng, top_up
+
+    def timed(state, K, clocks=None):
+        """K engine steps between barrier + synchronize on both sides; returns this job's numbers (max over ranks)."""
+        tp, runner, eng, top_up = state
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+        runner.capture_new_graphs = False          # an unseen shape runs as plain launches, never a capture, from here on
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        if clocks is not None:
+            clocks.start()
+        c0 = dict(l=runner.launches, h=runner.h2d_bytes, d=runner.d2h_bytes, cap=runner.captures, eag=runner.eager_steps,
+                  fu=runner.fused_steps, un=runner.unfused_steps, wait=runner.wait_s, err=eng.stats.device_errors)
+        tokens = 0
+        host_s = 0.0
+        t_first = time.perf_counter()
+        for k in range(K):
+            eng.step_events = evs[k]
+            ts = time.perf_counter()
+            outs = eng.step()
+            host_s += time.perf_counter() - ts
+            tokens += len(outs)
+            top_up()
+        tokens += len(eng.flush())           # the last step's tokens are read inside the timed region as well
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t_last = time.perf_counter()
+        wall = t_last - t_first
+        clk = clocks.stop() if clocks is not None else None
+        eng.step_events = None
+        runner.capture_new_graphs = True
+        per_step = [a.elapsed_time(b) for a, b in evs]
+        dev_ms = sum(per_step)
+        cuda_ops.check_device_errors()
+        host_busy_ms = (host_s - (runner.wait_s - c0["wait"])) * 1e3 / K     # scheduler + packing + launch, per step
+        res = {
+            "tokens": tokens, "dev_ms": dev_ms, "wall": wall, "per_step": per_step, "clocks": clk,
+            "launches": runner.launches - c0["l"], "h2d": (runner.h2d_bytes - c0["h"]) / K,
+            "d2h": (runner.d2h_bytes - c0["d"]) / K, "captures": runner.captures - c0["cap"],
+            "eager_steps": runner.eager_steps - c0["eag"], "fused_steps": runner.fused_steps - c0["fu"],
+            "unfused_steps": runner.unfused_steps - c0["un"], "device_errors": eng.stats.device_errors - c0["err"],
+            "host_busy_ms": host_busy_ms, "window": (t_first, t_last),
+        }
+        if world > 1:
+            # every rank's device time, host time and per-step maxima, so that a straggler is visible in the line
+            mine = torch.tensor([dev_ms, wall, host_busy_ms, max(per_step), _median(per_step)], dtype=torch.float64, device=dev)
+            allr = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(allr, mine)
+            allr = torch.stack(allr).tolist()
+            res["ranks"] = {"dev_ms": [r[0] for r in allr], "wall_s": [r[1] for r in allr],
+                            "host_busy_ms_per_step": [r[2] for r in allr], "step_ms_max": [r[3] for r in allr],
+                            "step_ms_p50": [r[4] for r in allr]}
+            res["dev_ms"] = max(r[0] for r in allr)
+            res["wall"] = max(r[1] for r in allr)
+            ps = torch.tensor(per_step, dtype=torch.float64, device=dev)
+            dist.all_reduce(ps, op=dist.ReduceOp.MAX)
+            res["per_step"] = ps.tolist()
+        return res
+
+    K = args.steps
+    library = None
+    if args.library_baseline and world > 1 and not args.baseline_collectives:
+        st = setup(False)
+        r = timed(st, K)
+        library = {"value": r["tokens"] / (r["dev_ms"] / 1e3), "unit": "tok/s", "ms_per_step": r["dev_ms"] / K,
+                   "ms_per_step_p50": _median(r["per_step"]),
+                   "what": "same engine and kernels, separate launches with NCCL all-reduce between them (no CUDA graph)"}
+        del st, r
+        torch.cuda.empty_cache()
 
     fused = world > 1 and not args.baseline_collectives
     fallback_reason = None
@@ -254,67 +418,64 @@ def main(argv=None) -> int:
     if args.profile_ops:
         runner.use_cuda_graphs = False
         runner.profile = True
-    K = args.steps
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
-    sampler = ClockSampler(local)
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    sampler.start()
-    l0, h0, d0 = runner.launches, runner.h2d_bytes, runner.d2h_bytes
-    tokens = 0
-    t0 = time.perf_counter()
-    for k in range(K):
-        eng.step_events = evs[k]
-        outs = eng.step()
-        tokens += len(outs)
-        top_up()
-    tokens += len(eng.flush())           # the last step's tokens are read inside the timed region as well
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    wall = time.perf_counter() - t0
-    clocks = sampler.stop()
-    eng.step_events = None
-    dev_ms = sum(a.elapsed_time(b) for a, b in evs)
-    cuda_ops.check_device_errors()
-    launches = runner.launches - l0
-    h2d = (runner.h2d_bytes - h0) / K
-    d2h = (runner.d2h_bytes - d0) / K
-    if world > 1:
-        t = torch.tensor([dev_ms, wall], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dev_ms, wall = t.tolist()
+    r = timed(state, K, sampler)
     if args.profile_ops and rank == 0:
         rep = runner.profile_report()
         tot = sum(rep.values())
         for name, ms in sorted(rep.items(), key=lambda kv: -kv[1]):
             print(f"  {name:40s} {ms / K:9.3f} ms/step {100 * ms / tot:5.1f}%", file=sys.stderr)
+    # latency of the requests that lived inside the timed steps (host clock, this rank)
+    t_first, t_last = r["window"]
+    ttft, tpot = [], []
+    for s in eng.seqs.values():
+        if s.first_token_time is not None and t_first <= s.first_token_time <= t_last and s.arrival >= t_first:
+            ttft.append((s.first_token_time - s.arrival) * 1e3)
+        tt = [t for t in s.token_times if t_first <= t <= t_last]
+        if len(tt) >= 2:
+            tpot.append((tt[-1] - tt[0]) * 1e3 / (len(tt) - 1))
     if rank == 0:
+        tokens, dev_ms, wall = r["tokens"], r["dev_ms"], r["wall"]
         value = tokens / (dev_ms / 1e3)
         e2e = tokens / wall
+        ps = r["per_step"]
+        par = f"tp{world}" + (f"+ep{world}" if weights.ep else "") + ("" if tp.fused or world == 1 else "-nccl-baseline")
+        if args.emulate_shard > 1:
+            par = f"1 GPU running the per-rank shapes of tp{args.emulate_shard} without communication"
         out = {
             "metric": f"output tok/s, {args.model} architecture, engine steady state (device-timed, max over ranks)",
             "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": args.warmup,
-            "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "ms_per_step": dev_ms / K, "ms_per_step_p50": _median(ps), "ms_per_step_min": min(ps),
+            "ms_per_step_max": max(ps), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic (random token ids, random-init weights)",
             "config": {"model": args.model, "global_batch": B, "seq_len": PL + SL + OL,
-                       "parallelism": f"tp{world}" + (f"+ep{world}" if weights.ep else "") +
-                       ("" if tp.fused or world == 1 else "-nccl-baseline"),
+                       "parallelism": par,
                        "fused_fallback": fallback_reason,
-                       "workload": f"{PL}-token shared prefix + {SL} unique + {OL} greedy outputs, continuous batching",
+                       "workload": f"{B} concurrent requests: {PL}-token shared prefix + {SL} unique + {OL} greedy outputs, "
+                                   "continuous batching in steady state",
                        "kv_block": bs, "prefix_cache": True, "cuda_graphs": not args.no_graphs,
                        "scheduling": "synchronous" if args.sync_scheduling else "host one step ahead of the device",
                        "l2": "inputs larger than L2: each step streams the model weights (>= 2 GB per GPU) from HBM",
                        "output_tokens_timed": tokens},
-            "e2e": {"value": e2e, "unit": "tok/s", "ms_per_step": wall * 1e3 / K, "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h},
-            "gpu_launches": launches,
-            "clocks": clocks,
+            "e2e": {"value": e2e, "unit": "tok/s", "ms_per_step": wall * 1e3 / K, "h2d_bytes_per_step": r["h2d"],
+                    "d2h_bytes_per_step": r["d2h"]},
+            "gpu_launches": r["launches"],
+            "clocks": r["clocks"],
+            "captures_in_timed_region": r["captures"], "eager_steps_in_timed_region": r["eager_steps"],
+            "fused_steps": r["fused_steps"], "unfused_steps": r["unfused_steps"],
+            "device_errors_in_timed_region": r["device_errors"],
+            "host_busy_ms_per_step": r["host_busy_ms"],
+            "latency": {"ttft_ms_p50": _median(ttft), "tpot_ms_p50": _median(tpot), "requests_admitted": len(ttft),
+                        "note": "requests inside the timed steps, host clock of rank 0; a request is queued when a "
+                                "slot of the closed loop is about to free up, so TTFT = queue wait + its prefill step"},
             "engine": {"prefill_tokens": eng.stats.prefill_tokens, "decode_tokens": eng.stats.decode_tokens,
                        "cached_tokens": eng.stats.cached_tokens, "preemptions": eng.stats.preemptions,
                        "graphs": len(runner.graphs)},
         }
+        if "ranks" in r:
+            out["ranks"] = r["ranks"]
+        if library is not None:
+            out["library_baseline"] = library
+            out["vs_library_baseline"] = value / library["value"]
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()

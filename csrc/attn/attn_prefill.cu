@@ -306,7 +306,7 @@ extern "C" int ub_attn_prefill(const UbAttnArgs* a, void* stream_v) {
     g_last_path = 1;
     return ub_attn_prefill_tc(a, stream_v);
   }
-  if (a->merge_o != nullptr) return -7;   // fused merge lives in the tensor-core kernel only
+  if (a->merge_o != nullptr || a->splits > 1) return -7;   // fused merge and key split live in the tensor-core kernel only
   g_last_path = 2;
   if (a->Hq % a->Hkv != 0) return -2;
   if (a->q_stride % 8 != 0) return -3;

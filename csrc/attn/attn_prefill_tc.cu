@@ -73,6 +73,12 @@ struct Params {
   int kv_start;     // first key position to attend (suffix pass after a shared prefix); 0 = all
   const __nv_bfloat16* merge_o;   // optional partial over a disjoint key set, [T, Hq, HD] contiguous
   const float* merge_lse;         // its log-sum-exp, [T, Hq]
+  // Key split: grid.z = num_seqs * kv_splits; CTA (seq, split) walks 1 / kv_splits of the visible KV tiles and writes
+  // its partial (O rows bf16, log-sum-exp) into slot [split] of the workspace; attn_merge_splits_kernel folds them.
+  int kv_splits;
+  __nv_bfloat16* part_o;          // [kv_splits][total_q][Hq][HD]
+  float* part_lse;                // [kv_splits][total_q][Hq]
+  int total_q;
 };
 
 template <bool P_TMEM>
@@ -100,7 +106,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 
   pdl_wait();          // the sequence metadata read below may be written by earlier kernels of the stream
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int seq = blockIdx.z, kh = blockIdx.y, G = p.G;
+  const int seq = int(blockIdx.z) / p.kv_splits, split = int(blockIdx.z) % p.kv_splits, kh = blockIdx.y, G = p.G;
   const int TOK = BM / G;                                   // query tokens per tile
   const int q_begin = p.q_start[seq], q_end = p.q_start[seq + 1];
   const int q_len = q_end - q_begin;
@@ -113,8 +119,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   int kv_hi = p.causal ? min(kv_len, kv_len - q_len + (t_last - q_begin) + 1) : kv_len;
   if (kv_hi < 0) kv_hi = 0;
   const int kv_lo = max(p.kv_start, 0);
-  const int tile0 = kv_lo / BN;                             // first KV tile that holds a visible key
-  const int n_tiles = kv_hi > kv_lo ? (kv_hi + BN - 1) / BN - tile0 : 0;
+  int tile0 = kv_lo / BN;                                   // first KV tile that holds a visible key
+  int n_tiles = kv_hi > kv_lo ? (kv_hi + BN - 1) / BN - tile0 : 0;
+  if (p.kv_splits > 1) {
+    // this CTA's share of the tiles; the masks below stay relative to the whole range [kv_lo, limit)
+    const int per = (n_tiles + p.kv_splits - 1) / p.kv_splits;
+    tile0 += split * per;
+    n_tiles = max(0, min(per, n_tiles - split * per));
+  }
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -430,6 +442,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       }
       const float c_mine = (l > 0.f) ? cb * w_mine : 0.f, c_other = (l_o > 0.f) ? cb * w_other : 0.f;
       __nv_bfloat16* dst = p.out + (long long)tok * p.o_stride + (long long)head * HD;
+      if (p.kv_splits > 1) dst = p.part_o + (((long long)split * p.total_q + tok) * p.Hq + head) * HD;
       // each half writes 64 of the 128 output columns, reading them from both accumulators
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
@@ -464,7 +477,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         }
         __syncwarp();
       }
-      if (p.lse != nullptr && row_valid && half == 0) p.lse[(long long)tok * p.Hq + head] = lse_v;
+      if (p.kv_splits > 1) {
+        if (row_valid && half == 0) p.part_lse[((long long)split * p.total_q + tok) * p.Hq + head] = lse_v;
+      } else if (p.lse != nullptr && row_valid && half == 0) {
+        p.lse[(long long)tok * p.Hq + head] = lse_v;
+      }
     }
   }
 
@@ -477,6 +494,36 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
+}
+
+// Folds the partials of a key-split launch: one warp per (token, head) row, 4 head-dim values per lane.
+// out = sum_s w_s O_s with w_s = exp(lse_s - max) / sum, lse = max + log(sum); a split that saw no key has lse = -inf.
+__global__ void __launch_bounds__(256) attn_merge_splits_kernel(const __nv_bfloat16* __restrict__ part_o,
+                                                                 const float* __restrict__ part_lse, int splits,
+                                                                 long long rows, int Hq, __nv_bfloat16* __restrict__ out,
+                                                                 long long o_stride, float* __restrict__ lse) {
+  pdl_wait();
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  float mx = -CUDART_INF_F;
+  for (int s = 0; s < splits; ++s) mx = fmaxf(mx, part_lse[(long long)s * rows + row]);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f}, den = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float l = part_lse[(long long)s * rows + row];
+    if (l == -CUDART_INF_F) continue;
+    const float w = __expf(l - mx);
+    den += w;
+    const uint2 raw = *reinterpret_cast<const uint2*>(part_o + ((long long)s * rows + row) * HD + lane * 4);
+    acc[0] += bf16_lo(raw.x) * w; acc[1] += bf16_hi(raw.x) * w;
+    acc[2] += bf16_lo(raw.y) * w; acc[3] += bf16_hi(raw.y) * w;
+  }
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+  const long long tok = row / Hq;
+  const int head = int(row % Hq);
+  *reinterpret_cast<uint2*>(out + tok * o_stride + (long long)head * HD + lane * 4) =
+      make_uint2(pack_bf16x2(acc[0] * inv, acc[1] * inv), pack_bf16x2(acc[2] * inv, acc[3] * inv));
+  if (lse != nullptr && lane == 0) lse[row] = den > 0.f ? mx + logf(den) : -CUDART_INF_F;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -565,6 +612,18 @@ extern "C" int ub_attn_prefill_tc(const UbAttnArgs* a, void* stream_v) {
   p.kv_start = a->kv_start;
   p.merge_o = reinterpret_cast<const __nv_bfloat16*>(a->merge_o);
   p.merge_lse = a->merge_lse;
+  // Key split (a->splits > 1): the caller provides the workspace in a->scratch, laid out as the log-sum-exps
+  // [splits][total_q][Hq] fp32 (rounded up to 16 bytes) followed by the partial rows [splits][total_q][Hq][128] bf16.
+  int S = a->splits > 1 ? a->splits : 1;
+  if (S > 16) S = 16;
+  if (S > 1 && (a->scratch == nullptr || a->merge_o != nullptr)) return -7;
+  p.kv_splits = S;
+  p.total_q = a->total_q;
+  p.part_lse = a->scratch;
+  {
+    const long long lse_floats = ((long long)S * a->total_q * a->Hq + 3) / 4 * 4;
+    p.part_o = S > 1 ? reinterpret_cast<__nv_bfloat16*>(a->scratch + lse_floats) : nullptr;
+  }
   // P (the probabilities fed to the second MMA) lives in tensor memory by default; UB_ATTN_TC_P=smem stages it in
   // shared memory instead (the A operand then comes through a shared-memory descriptor).
   static const bool p_tmem = [] {
@@ -581,11 +640,19 @@ extern "C" int ub_attn_prefill_tc(const UbAttnArgs* a, void* stream_v) {
     if (e != cudaSuccess) return -(int)e;
     attr_set[dev] = true;
   }
-  dim3 grid((a->max_q_len + TOK - 1) / TOK, a->Hkv, a->num_seqs);
+  dim3 grid((a->max_q_len + TOK - 1) / TOK, a->Hkv, a->num_seqs * S);
   if (p_tmem)
     launch_pdl(attn_prefill_tc_kernel<true>, grid, dim3(THREADS), (size_t)SMEM_TOTAL, reinterpret_cast<cudaStream_t>(stream_v), tq, tk, tv, p);
   else
     launch_pdl(attn_prefill_tc_kernel<false>, grid, dim3(THREADS), (size_t)SMEM_TOTAL, reinterpret_cast<cudaStream_t>(stream_v), tq, tk, tv, p);
   cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return -(int)e;
+  if (S > 1) {
+    const long long rows = (long long)a->total_q * a->Hq;
+    launch_pdl(attn_merge_splits_kernel, dim3((unsigned)((rows + 7) / 8)), dim3(256), (size_t)0,
+               reinterpret_cast<cudaStream_t>(stream_v), (const __nv_bfloat16*)p.part_o, (const float*)p.part_lse, S, rows,
+               a->Hq, p.out, (long long)a->o_stride, a->lse);
+    e = cudaGetLastError();
+  }
   return e == cudaSuccess ? 0 : -(int)e;
 }

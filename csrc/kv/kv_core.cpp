@@ -61,6 +61,10 @@ struct BlockPool {
     }
     return ref[b];
   }
+  int refcount(int b) {
+    std::lock_guard<std::mutex> g(mu);
+    return (b < 0 || b >= num_blocks) ? -1 : ref[b];
+  }
 };
 
 struct Node {
@@ -184,7 +188,9 @@ struct RadixTree {
       node = nodes[node].parent;
     }
   }
-  // Evict unlocked leaves, least recently used first, until `want` blocks were released.
+  // Evict unlocked leaves, least recently used first, until `want` blocks went back to the pool's free list.
+  // A leaf whose blocks are all still referenced by somebody else (a running sequence publishes its blocks while
+  // it holds them) would free nothing: it stays cached and is not counted.
   int evict(int want) {
     typedef std::pair<uint64_t, int> E;
     std::priority_queue<E, std::vector<E>, std::greater<E>> heap;
@@ -197,8 +203,11 @@ struct RadixTree {
       heap.pop();
       Node& nd = nodes[id];
       if (!nd.alive || !nd.children.empty() || nd.lock != 0) continue;
+      int freeable = 0;
+      for (int b : nd.blocks) freeable += pool->refcount(b) == 1 ? 1 : 0;
+      if (freeable == 0) continue;
       for (int b : nd.blocks) pool->decref(b);
-      released += (int)nd.blocks.size();
+      released += freeable;
       cached_blocks -= (int)nd.blocks.size();
       evicted_blocks += nd.blocks.size();
       const int par = nd.parent;

@@ -130,3 +130,81 @@ def test_async_scheduling_abort_and_snapshot():
     res = eng.run_to_completion()
     assert len(res[b]) == 5 and all(t >= 0 for t in res[b])
     assert eng.pool.num_free() + eng.radix.stats()["cached_blocks"] == 32
+
+
+def test_engine_allocates_from_finished_sequences_before_preempting():
+    """With a small pool, the blocks cached for a finished request are evicted for a new one; the running request
+    (whose published blocks are the oldest cache entries) is not preempted."""
+    cls, cfg = CASES[0]
+    m = cls.new(cfg, init="random", seed=5)
+    runner = CpuModelRunner(m, num_blocks=16, block_size=4, max_model_len=64)
+    eng = LLMEngine(runner, num_blocks=16, block_size=4, max_num_seqs=4, max_num_batched_tokens=64, max_model_len=64)
+    g = torch.Generator().manual_seed(9)
+    long_running = eng.add_request(torch.randint(0, 128, (17,), generator=g).tolist(),
+                                   SamplingParams(temperature=0.0, max_tokens=30, ignore_eos=True))
+    eng.step()                                     # prefill: 4 full blocks published while the sequence runs
+    short = eng.add_request(torch.randint(0, 128, (21,), generator=g).tolist(),
+                            SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True))
+    while eng.seqs[short].status != "finished":
+        eng.step()
+    third = eng.add_request(torch.randint(0, 128, (24,), generator=g).tolist(),
+                            SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True))
+    while eng.seqs[third].status != "finished":
+        eng.step()
+    assert eng.stats.preemptions == 0
+    assert eng.seqs[long_running].status == "running"
+
+
+class _FlakyRunner:
+    """Wraps a runner; ``fail_at`` lists the fetches (0-based) that report a device error instead of tokens."""
+
+    def __init__(self, inner, fail_at):
+        self.inner, self.fail_at, self.fetches, self.resets = inner, set(fail_at), 0, 0
+
+    def launch(self, b):
+        return self.inner.launch(b)
+
+    def pending(self):
+        return self.inner.pending()
+
+    def fetch(self, handle=None):
+        from unillm_b200.engine.runner import DeviceStepError
+
+        k, self.fetches = self.fetches, self.fetches + 1
+        if k in self.fail_at:
+            raise DeviceStepError(2, 4000)
+        return self.inner.fetch(handle)
+
+    def reset_after_error(self):
+        self.resets += 1
+
+
+@pytest.mark.parametrize("async_sched", [False, True])
+def test_engine_drops_a_step_whose_device_status_is_bad(async_sched):
+    """A step whose error word reads 'flag wait timed out' hands no token to anybody and publishes nothing: the
+    sequences are prefilled again from their history and the final outputs equal an undisturbed run."""
+    cls, cfg = CASES[0]
+    m = cls.new(cfg, init="random", seed=3)
+    prompts = _prompts()
+    ref = [m.generate_ids(p, GenerationConfig.greedy(8, eos_token_id=-1)) for p in prompts]
+    runner = _FlakyRunner(CpuModelRunner(m, num_blocks=64, block_size=4, max_model_len=128), fail_at=[2, 5])
+    eng = LLMEngine(runner, num_blocks=64, block_size=4, max_num_seqs=4, max_num_batched_tokens=16, max_model_len=128,
+                    async_scheduling=async_sched)
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8))
+    assert outs == ref
+    assert eng.stats.device_errors == 2 and runner.resets == 2
+    assert all(t >= 0 for o in outs for t in o)
+    assert eng.pool.num_free() + eng.radix.stats()["cached_blocks"] == 64
+
+
+def test_engine_raises_after_repeated_device_errors():
+    from unillm_b200.engine.runner import DeviceStepError
+
+    cls, cfg = CASES[0]
+    m = cls.new(cfg, init="random", seed=3)
+    runner = _FlakyRunner(CpuModelRunner(m, num_blocks=64, block_size=4, max_model_len=128), fail_at=range(100))
+    eng = LLMEngine(runner, num_blocks=64, block_size=4, max_num_seqs=4, max_num_batched_tokens=16, max_model_len=128)
+    eng.add_request([1, 2, 3], SamplingParams(temperature=0.0, max_tokens=4))
+    with pytest.raises(DeviceStepError):
+        for _ in range(10):
+            eng.step()

@@ -335,6 +335,45 @@ def test_attn_prefill_tensor_core_path(Hq, Hkv, causal):
     cuda_ops.check_device_errors()
 
 
+@pytest.mark.parametrize("Hq,Hkv,splits", [(4, 1, 4), (4, 1, 8), (32, 8, 3), (8, 2, 16)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_attn_prefill_key_split(Hq, Hkv, splits, causal):
+    """Key split of the tcgen05 prefill kernel: every CTA walks a share of the KV tiles and a second kernel folds the
+    partials.  Compared with the fp32 reference; includes sequences with fewer tiles than splits (empty shares), a
+    lower key bound (kv_start) and the strided output of a fused-QKV view."""
+    from unillm_b200.ops import cuda_ops
+
+    kv_lens = [1024, 17, 300, 1100]
+    q_lens = [260, 17, 40, 1]
+    kc, vc, bt, sl, dk, dv = make_paged_cache(len(kv_lens), kv_lens, Hkv, 128, seed=21)
+    qs = [0]
+    for l in q_lens:
+        qs.append(qs[-1] + l)
+    q = _rand(qs[-1], Hq, 128, seed=22)
+    q_start = torch.tensor(qs, dtype=torch.int32, device="cuda")
+    for kv_start in (0, 144):
+        out = torch.full((qs[-1], Hq, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+        out, lse = cuda_ops.attn_prefill(q, kc, vc, bt, sl, q_start, max(q_lens), causal=causal, return_lse=True,
+                                         kv_splits=splits, kv_start=kv_start, out=out)
+        assert cuda_ops.attn_prefill_last_path() == "tcgen05"
+        torch.cuda.synchronize()
+        cuda_ops.check_device_errors()
+        for i, (kl, ql) in enumerate(zip(kv_lens, q_lens)):
+            ro, rl = ref_attention(q[qs[i]:qs[i + 1]].cpu(), dk[i], dv[i], causal_offset=(kl - ql) if causal else None,
+                                   kv_start=kv_start)
+            seen = torch.isfinite(rl)                     # rows that see no key at all have lse = -inf and output 0
+            oc, lc = out[qs[i]:qs[i + 1]].cpu(), lse[qs[i]:qs[i + 1]].cpu()
+            _close(oc[seen], ro[seen])
+            _close(lc[seen], rl[seen], rtol=1e-2, atol=1e-2)
+            assert torch.all(oc[~seen] == 0)
+    # same answer as the unsplit kernel, bit for bit in the log-sum-exp up to fp32 rounding of the fold
+    a, la = cuda_ops.attn_prefill(q, kc, vc, bt, sl, q_start, max(q_lens), causal=causal, return_lse=True)
+    b, lb = cuda_ops.attn_prefill(q, kc, vc, bt, sl, q_start, max(q_lens), causal=causal, return_lse=True, kv_splits=splits)
+    _close(b, a.float(), rtol=2e-2, atol=2e-2)
+    _close(lb, la, rtol=1e-3, atol=1e-3)
+    cuda_ops.check_device_errors()
+
+
 @pytest.mark.parametrize("M,N,K,tile", [(256, 512, 512, 256), (512, 1024, 1024, 256), (300, 520, 264, 128), (1000, 2048, 4096, 256),
                                         (128, 768, 1024, 64), (640, 4096, 4096, 0)])
 def test_gemm_2cta_pairs(M, N, K, tile):

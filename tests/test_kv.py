@@ -162,3 +162,22 @@ def test_latency_budgets_of_the_reference_micro_benchmarks():
         t.match_prefix(seq)
     per = (time.perf_counter() - t0) / 2000
     assert per < 200e-6          # 1024-token lookup incl. ctypes marshalling of the token array
+
+
+def test_radix_evict_counts_only_blocks_that_return_to_the_pool():
+    """A running sequence publishes its full blocks while it still holds them: evicting that leaf frees nothing, so
+    it must neither be dropped nor be counted; the blocks of a finished sequence are what eviction has to find."""
+    p = BlockPool(12, 4)
+    t = RadixTree(p)
+    running = p.allocate(4)                       # older entry, still referenced by its sequence
+    t.insert(list(range(100, 116)), running)
+    finished = p.allocate(4)                      # newer entry, its sequence is gone
+    t.insert(list(range(200, 216)), finished)
+    p.free_many(finished)
+    assert p.num_free() == 4
+    assert t.evict(4) == 4                        # LRU order would pick the running sequence's leaf first
+    assert p.num_free() == 8
+    assert t.match_prefix(list(range(100, 116)))[0] == running       # still cached
+    assert t.evict(4) == 0 and p.num_free() == 8                     # nothing left that would free a block
+    p.free_many(running)
+    assert t.clear() == 4 and p.num_free() == 12 and t.stats()["cached_blocks"] == 0

@@ -4,8 +4,11 @@ Some callers of the kernel library may not allocate device memory (a fixed memor
 another allocator, a serving loop that bans driver allocations after start-up).  For them the split-KV
 partials live in an array inside the library image.  The test calls the function through its exported
 C symbol, twice in a row (the array is shared and keeps the previous call's contents), and compares
-with the regular entry point that takes a caller-provided scratch buffer.  It also checks that an
-oversized request is refused with a clear message instead of being launched.
+with the regular entry point that takes a caller-provided scratch buffer.  Two more properties are
+checked because they are what the entry point is for: the ``scratch`` field of the arguments is not
+used (it points at a sentinel buffer that must come back untouched), and the driver reports the same
+amount of free device memory before and after the calls.  An oversized request is refused with a clear
+message instead of being launched.
 This file sorts last on purpose: a run that stops at the first failure has then run everything else.
 """
 import ctypes as C
@@ -51,13 +54,32 @@ def test_static_scratch_decode_matches_regular_entry_point():
         g = torch.Generator().manual_seed(trial)
         q = (torch.randn(len(lens), Hq, D, generator=g)).to(torch.bfloat16).cuda()
         ref = cuda_ops.attn_decode(q, kc, vc, bt, sl, splits=splits)
-        out = torch.full_like(ref, float("nan"))
-        rc = fn(C.byref(_args(q, kc, vc, bt, sl, out, splits)), stream)
-        assert rc == 0, lib.ub_attn_decode_static_scratch_error()
+        outs = [torch.full_like(ref, float("nan")) for _ in range(3)]
+        # what a caller might leave in args.scratch: a buffer large enough for the partials, filled with a sentinel
+        sentinel = torch.full((len(lens) * Hq * splits * (D + 2),), -12345.0, dtype=torch.float32, device="cuda")
+
+        def call(out):
+            a = _args(q, kc, vc, bt, sl, out, splits)
+            a.scratch = sentinel.data_ptr()
+            rc = fn(C.byref(a), stream)
+            assert rc == 0, lib.ub_attn_decode_static_scratch_error()
+
+        # The first call on a device does the documented set-up (it looks up the array's address, which is also when
+        # the CUDA runtime loads the part of the library that holds the array); memory is compared around the calls
+        # after it.
+        call(outs[0])
         torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        for out in outs[1:]:                               # two calls in a row share the built-in array
+            call(out)
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after == free_before, (free_before, free_after)     # the driver handed out no device memory
         cuda_ops.check_device_errors()
-        err = (out.float() - ref.float()).abs().max().item()
-        assert err <= 2e-2, err
+        assert torch.all(sentinel == -12345.0)                          # args.scratch was never written
+        for out in outs:
+            err = (out.float() - ref.float()).abs().max().item()
+            assert err <= 2e-2, err
 
 
 def test_static_scratch_rejects_oversized_request():

@@ -37,7 +37,7 @@ from typing import Callable, Deque, Dict, List, Optional, Sequence, Tuple
 from ..kv.block_pool import BlockPool, RadixTree
 from ..sampling import SamplingParams
 from ..types import InvalidInput, MemoryError_
-from .runner import StepBatch
+from .runner import DeviceStepError, StepBatch
 
 WAITING, RUNNING, FINISHED, ABORTED = "waiting", "running", "finished", "aborted"
 
@@ -104,6 +104,7 @@ class EngineStats:
     preemptions: int = 0
     finished: int = 0
     generated_tokens: int = 0
+    device_errors: int = 0           # steps dropped because a kernel reported a problem in the device error word
 
 
 class LLMEngine:
@@ -129,6 +130,8 @@ class LLMEngine:
         self.async_scheduling = async_scheduling
         self._inflight = None       # (plan, runner handle) of the launched step whose samples are not read yet
         self._late: List[StepOutput] = []   # outputs of a step that had to be waited for outside ``step``
+        self.max_device_errors = 3  # consecutive failed steps after which the error is raised to the caller
+        self._consecutive_errors = 0
         self.step_events = None     # optional (start, end) CUDA events recorded around the runner launch
         self.tracer = None          # optional unillm_b200.utils.Tracer: spans around schedule / launch / fetch / process
 
@@ -418,10 +421,14 @@ class LLMEngine:
         if not self.async_scheduling:
             if tr is not None:
                 with tr.span("engine.fetch"):
-                    ids = self.runner.fetch()
+                    ids = self._fetch(None)
+                if ids is None:
+                    return []
                 with tr.span("engine.process"):
                     return self._finalize(self._advance(plan), ids)
-            ids = self.runner.fetch()
+            ids = self._fetch(None)
+            if ids is None:
+                return []
             return self._finalize(self._advance(plan), ids)
         # one step ahead: this step is in flight; read the one launched before it
         prev = self._inflight
@@ -430,12 +437,53 @@ class LLMEngine:
         if prev is not None:
             if tr is not None:
                 with tr.span("engine.fetch"):
-                    ids = self.runner.fetch(prev[1])
-                with tr.span("engine.process"):
-                    outs.extend(self._finalize(prev[0], ids))
+                    ids = self._fetch(prev[1])
+                if ids is not None:
+                    with tr.span("engine.process"):
+                        outs.extend(self._finalize(prev[0], ids))
             else:
-                outs.extend(self._finalize(prev[0], self.runner.fetch(prev[1])))
+                ids = self._fetch(prev[1])
+                if ids is not None:
+                    outs.extend(self._finalize(prev[0], ids))
         return outs
+
+    def _fetch(self, handle) -> Optional[List[int]]:
+        """Sampled ids of a launched step, or None when the device reported an error for it: then the step's
+        results are dropped and every running sequence is queued for recomputation (``_on_device_error``)."""
+        try:
+            ids = self.runner.fetch(handle) if handle is not None else self.runner.fetch()
+        except DeviceStepError as e:
+            self._on_device_error(e)
+            return None
+        self._consecutive_errors = 0
+        return ids
+
+    def _on_device_error(self, exc: DeviceStepError) -> None:
+        """A bounded device wait gave up or an index was out of range: nothing the failed step (or the step launched
+        after it, which consumed its samples) produced can be trusted.  Their tokens are dropped, the KV blocks of all
+        running sequences go back to the pool WITHOUT being offered to the prefix cache, the cache itself is emptied
+        (blocks were published at scheduling time), and the sequences wait to be prefilled again from their token
+        history.  The runner clears the error word and, under tensor parallelism, the arrival counters on every rank.
+        The reference only has request time-outs (``crates/inference/src/engine.rs:238-264``)."""
+        self.stats.device_errors += 1
+        self._consecutive_errors += 1
+        self._inflight = None
+        reset = getattr(self.runner, "reset_after_error", None)
+        if reset is not None:
+            reset()
+        for s in self.running:
+            while s.output_ids and s.output_ids[-1] < 0:      # placeholders of the dropped steps
+                s.output_ids.pop()
+            s.pending_src = s.pending_at = -1
+            self._release(s, publish=False)
+            s.num_computed = s.num_cached = 0
+            s.status = WAITING
+        self.waiting.extendleft(reversed(self.running))
+        self.running = []
+        if self.radix is not None:
+            self.radix.clear()
+        if self._consecutive_errors > self.max_device_errors:
+            raise exc
 
     def flush(self) -> List[StepOutput]:
         """Outputs of the step still in flight under ``async_scheduling`` (empty otherwise); afterwards every token
@@ -448,7 +496,8 @@ class LLMEngine:
         prev, self._inflight = self._inflight, None
         if prev is None:
             return []
-        return self._finalize(prev[0], self.runner.fetch(prev[1]))
+        ids = self._fetch(prev[1])
+        return [] if ids is None else self._finalize(prev[0], ids)
 
     def _advance(self, plan) -> List[Tuple[Sequence, int, bool, int]]:
         """Bookkeeping that does not need the sampled values: computed lengths move on and every sampled sequence

@@ -25,6 +25,7 @@ Reference counterpart: the per-token loop of ``UniLLMBackend::generate`` / ``Lla
 from __future__ import annotations
 
 import math
+import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Tuple
 
@@ -34,6 +35,18 @@ from ..models.spec import DecoderSpec
 from ..ops import cuda_ops as K
 from ..precompute import alibi_slopes
 from ..types import InvalidInput, UnsupportedOperation
+
+
+class DeviceStepError(RuntimeError):
+    """A kernel of a launched step recorded a problem in the device error word (a bounded wait that gave up, an
+    out-of-range block-table entry or slot): the step's sampled ids are garbage and must not be used."""
+
+    NAMES = {1: "mbarrier wait timed out", 2: "flag wait timed out (peer or producer missing)",
+             3: "index out of range", 4: "bad argument"}
+
+    def __init__(self, code: int, detail: int):
+        super().__init__(f"device error {code} ({self.NAMES.get(code, '?')}), detail {detail}")
+        self.code, self.detail = code, detail
 
 
 @dataclass
@@ -443,18 +456,28 @@ class GpuModelRunner:
         self.fmeta_dev = torch.empty(4 * max_num_seqs, dtype=torch.float32, device=dev)
         self.out_ids_dev = torch.zeros(4 * max_num_seqs, dtype=torch.int32, device=dev)
         self.out_ids_hosts = [torch.zeros(4 * max_num_seqs, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        # the per-device error word travels back with every step's sampled ids (same stream, no extra synchronisation)
+        self.err_hosts = [torch.zeros(2, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self._out_events = [torch.cuda.Event(), torch.cuda.Event()]
         self._sel: List[int] = []
         self._handle = None
         self.attn_scratch = torch.empty(max_num_seqs * weights.hq * 16 * (D + 2), dtype=torch.float32, device=dev)
+        self.prefix_scratch = None     # workspace of the key-split shared-prefix pass, allocated on first use
         self.graphs: Dict[tuple, tuple] = {}
         self.profile = False
         self._prof_events = []
         self._graph_mode = False
         self.launches = 0          # kernels of this library launched so far (counted on the host)
+        self.captures = 0          # CUDA-graph captures so far (each costs an eager run, a synchronize and the capture)
+        self.capture_new_graphs = True   # False: a step shape without a graph runs as plain launches instead
+        self.eager_steps = 0       # graphable steps that ran as plain launches for that reason
+        self.wait_s = 0.0          # host time spent blocked in fetch() waiting for the device
+        self.fused_steps = 0       # tensor-parallel steps that ran the fused (peer-memory) path / the NCCL path
+        self.unfused_steps = 0
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self._layout = None
+        self._last_fused = False
 
     # ------------------------------------------------------------------------------------------
     # metadata packing
@@ -547,10 +570,13 @@ class GpuModelRunner:
             fused = D == 128 and self.block_size == 16 and s.window == 0 and self.alibi is None
             lse_a = torch.empty(R, hq, dtype=torch.float32, device=qkv.device)
             oa = torch.empty(R, hq, D, dtype=torch.bfloat16, device=qkv.device)
+            kvs = self._prefix_splits(R, shared_prefix_len)
             with self._prof("attn_shared_prefix"):
                 K.attn_prefill(q[:R], kc, vc, bt[:1], self._prefix_len_dev(shared_prefix_len), self._q_start_all(R),
                                R, scale=scale, causal=False, window=0, alibi_slopes=None, out=oa, lse=lse_a,
-                               return_lse=True)
+                               return_lse=True, kv_splits=kvs, scratch=self.prefix_scratch if kvs > 1 else None)
+            if kvs > 1:
+                self.launches += 1
             if fused:
                 with self._prof("attn_decode_suffix"):
                     K.attn_decode(q[:Dp], kc, vc, bt[:Dp], self._view(lay, "seq_lens_d"), scale=scale,
@@ -591,6 +617,27 @@ class GpuModelRunner:
                                out=out[Dp:])
             self.launches += 1
         return out.view(T, hq * D)
+
+    PREFIX_SPLIT_ROWS = 160 * 128     # (query row, head) pairs x splits the key-split workspace can hold
+
+    def _prefix_splits(self, R: int, prefix_len: int) -> int:
+        """Key splits of the shared-prefix pass.  The pass has one CTA per 128 packed (token, head-of-group) rows and KV
+        head; a tensor-parallel rank with one KV head and a few hundred rows would keep a fraction of the SMs busy while
+        every CTA walks the whole prefix, so the key tiles are divided until about one wave of CTAs exists."""
+        s, w = self.spec, self.w
+        if s.head_dim != 128 or self.block_size != 16 or s.window or self.alibi is not None:
+            return 1
+        G = w.hq // w.hkv
+        if 128 % G:
+            return 1
+        ctas = -(-R // (128 // G)) * w.hkv
+        n = min(prefix_len // 128, 148 // max(ctas, 1), 8)
+        while n > 1 and n * R * w.hq > self.PREFIX_SPLIT_ROWS:
+            n -= 1
+        if n > 1 and self.prefix_scratch is None:
+            self.prefix_scratch = torch.empty(K.attn_prefill_split_scratch_floats(self.PREFIX_SPLIT_ROWS, 1, 128, 1),
+                                              dtype=torch.float32, device=self.device)
+        return max(n, 1)
 
     def _prefix_len_dev(self, n: int) -> torch.Tensor:
         c = getattr(self, "_plen_cache", None)
@@ -634,7 +681,9 @@ class GpuModelRunner:
         T = lay["_T"]
         self._final_norm_done = False
         if self._fused_ok(T):
+            self._last_fused = True
             return self._forward_tokens_fused(lay, shared_prefix_len)
+        self._last_fused = False
         ids = self._view(lay, "token_ids")
         pos = self._view(lay, "positions")
         slots = self._view(lay, "slot_mapping")
@@ -856,7 +905,7 @@ class GpuModelRunner:
         return {"temperature": self.fmeta_dev[:S], "top_p": self.fmeta_dev[S:2 * S], "top_k": tk, "seed": b.seed,
                 "step": b.step}
 
-    MAX_GRAPHS = 48
+    MAX_GRAPHS = 96
 
     def launch(self, b: StepBatch) -> int:
         """Uploads the step's metadata and enqueues all kernels on the current stream.  Returns the number of
@@ -872,12 +921,9 @@ class GpuModelRunner:
             lay["_pp"] = b.prefill_shares_prefix
             key = (lay["_Dp"], lay["_P"], lay["_T"], lay["_max_q"], b.shared_prefix_len, b.prefill_shares_prefix)
             g = self.graphs.get(key)
-            if g is None and len(self.graphs) >= self.MAX_GRAPHS:
-                graphable = False
-        if graphable:
             self._graph_mode = True
             self._upload(lay)
-            if g is None:
+            if g is None and self.capture_new_graphs and len(self.graphs) < self.MAX_GRAPHS:
                 # one eager run (sets kernel attributes, warms the allocator), then capture
                 self._forward_and_sample(lay, b.shared_prefix_len, None)
                 torch.cuda.current_stream().synchronize()
@@ -885,9 +931,18 @@ class GpuModelRunner:
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph):
                     self._forward_and_sample(lay, b.shared_prefix_len, None)
-                g = self.graphs[key] = (graph, self.launches - before)
-            g[0].replay()
-            self.launches += g[1]
+                g = self.graphs[key] = (graph, self.launches - before, self._last_fused)
+                self.captures += 1
+            if g is not None:
+                g[0].replay()
+                self.launches += g[1]
+                self._count_step(g[2])
+            else:
+                # a shape without a graph while captures are off (or the graph table is full): the padded step runs
+                # as plain launches -- slower than a replay, but without the synchronisation a capture needs
+                self._forward_and_sample(lay, b.shared_prefix_len, None)
+                self._count_step(self._last_fused)
+                self.eager_steps += 1
             return self._queue_readback(lay["_sel"])
         self._graph_mode = False
         lay = self._pack(b, bucketed=False)
@@ -895,19 +950,29 @@ class GpuModelRunner:
         self._upload(lay)
         fl = None if greedy else self._sampling_tensors(b, lay["_S"])
         self._forward_and_sample(lay, b.shared_prefix_len, fl)
+        self._count_step(self._last_fused)
         return self._queue_readback(lay["_sel"])
+
+    def _count_step(self, fused: bool) -> None:
+        if self.tp.world > 1:
+            if fused:
+                self.fused_steps += 1
+            else:
+                self.unfused_steps += 1
 
     def _queue_readback(self, sel: List[int]) -> int:
         """Queues the device -> pinned host copy of the sampled ids behind the step and records an event; the
         returned handle of ``pending()`` stays valid while one later step is launched."""
         self._sel = sel
         n = (max(sel) + 1) if sel else 0
-        host, ev = self.out_ids_hosts[self._flip], self._out_events[self._flip]
+        host, ev, err = self.out_ids_hosts[self._flip], self._out_events[self._flip], self.err_hosts[self._flip]
         if n:
             host[:n].copy_(self.out_ids_dev[:n], non_blocking=True)
             self.d2h_bytes += 4 * n
+        err.copy_(K.err_word(self.device), non_blocking=True)
+        self.d2h_bytes += 8
         ev.record()
-        self._handle = (ev, host, n, sel)
+        self._handle = (ev, host, n, sel, err)
         return len(sel)
 
     def pending(self):
@@ -921,8 +986,13 @@ class GpuModelRunner:
 
     def fetch(self, handle=None) -> List[int]:
         """Waits for a launched step (the last one by default) and returns its sampled ids from pinned memory."""
-        ev, host, n, sel = handle if handle is not None else self._handle
+        ev, host, n, sel, err = handle if handle is not None else self._handle
+        t0 = time.perf_counter()
         ev.synchronize()
+        self.wait_s += time.perf_counter() - t0
+        code, detail = err.tolist()
+        if code != 0:
+            raise DeviceStepError(code, detail)
         if not sel:
             return []
         vals = host[:n].tolist()
@@ -931,6 +1001,17 @@ class GpuModelRunner:
     def execute(self, b: StepBatch) -> List[int]:
         self.launch(b)
         return self.fetch()
+
+    def reset_after_error(self) -> None:
+        """After a ``DeviceStepError``: waits for the device, clears the error word and (tensor parallel, fused path)
+        zeroes the arrival counters on every rank -- a collective call, every rank of the group has to make it."""
+        torch.cuda.synchronize(self.device)
+        K.err_word(self.device).zero_()
+        for e in self.err_hosts:
+            e.zero_()
+        if self.tp.comm is not None:
+            self.tp.comm.reset()
+        torch.cuda.synchronize(self.device)
 
     def kv_cache_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.k_cache) * 2

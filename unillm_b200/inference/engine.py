@@ -79,6 +79,7 @@ class _Pending:
     seq_id: Optional[int] = None
     sent_tokens: int = 0
     text: str = ""
+    n_decoded: int = 0            # output tokens already turned into text
 
 
 class UniLLMInferenceEngine(InferenceEngine):
@@ -156,8 +157,12 @@ class UniLLMInferenceEngine(InferenceEngine):
             except Exception as e:                       # a failed step fails the requests in flight, not the engine
                 self._last_error = f"{type(e).__name__}: {e}"
                 self._device_errors += 1
+                eng._inflight = None                     # whatever was launched is not read back any more
                 for sid, p in list(self._active.items()):
-                    eng.abort(sid)
+                    try:
+                        eng.abort(sid)
+                    except Exception as e2:              # the abort must not take the worker thread down with it
+                        self._last_error = f"{type(e2).__name__}: {e2}"
                     self._finish_error(p, InternalError(self._last_error))
                 self._active.clear()
                 continue
@@ -185,10 +190,31 @@ class UniLLMInferenceEngine(InferenceEngine):
         seq = self.engine.seqs[p.seq_id]
         METRICS.token_generated()
         sp = p.request.sampling_params
-        new_text = self.tokenizer.decode(seq.output_ids)
-        delta = new_text[len(p.text):]
+        # tokens whose values are known: under one-step-ahead scheduling the tail may hold the placeholder of the
+        # step in flight
+        ids = seq.output_ids
+        n = len(ids)
+        while n > 0 and ids[n - 1] < 0:
+            n -= 1
+        if n < p.n_decoded:
+            p.n_decoded = n
+        # incremental detokenisation: only a window of the latest tokens is decoded, before and after the new ones
+        # (a token may complete a multi-byte piece), so the cost per token does not grow with the output length
+        w0 = max(0, p.n_decoded - 6)
+        old = self.tokenizer.decode(ids[w0:p.n_decoded]) if p.n_decoded > w0 else ""
+        new = self.tokenizer.decode(ids[w0:n])
+        k = len(old)
+        if not new.startswith(old):
+            k = 0
+            while k < min(len(old), len(new)) and old[k] == new[k]:
+                k += 1
+        delta = new[k:]
+        p.n_decoded = n
+        new_text = p.text + delta
         p.text = new_text
-        stop_hit = next((s for s in sp.stop_sequences if s and s in new_text), None)
+        stops = [s for s in sp.stop_sequences if s]
+        tail = new_text[-(len(delta) + max(map(len, stops))):] if stops else ""
+        stop_hit = next((s for s in stops if s in tail), None)
         if stop_hit is not None and not finished:
             self.engine.abort(p.seq_id)
             p.text = new_text[: new_text.index(stop_hit)]

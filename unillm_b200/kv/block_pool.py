@@ -176,6 +176,15 @@ class RadixTree:
     def evict(self, num_blocks: int) -> int:
         return self._lib.ubkv_radix_evict(self._h, num_blocks)
 
+    def clear(self) -> int:
+        """Drops every cache entry that no live sequence has locked (all of them once the sequences are released)."""
+        n = 0
+        while True:
+            k = self.evict(1 << 30)
+            if k <= 0:
+                return n
+            n += k
+
     def evictable_blocks(self) -> int:
         return self._lib.ubkv_radix_evictable(self._h)
 

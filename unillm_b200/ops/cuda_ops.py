@@ -284,9 +284,15 @@ def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
                  seq_lens: torch.Tensor, q_start: torch.Tensor, max_q_len: int, *, scale: Optional[float] = None,
                  causal: bool = True, window: int = 0, kv_start: int = 0,
                  alibi_slopes: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                 return_lse: bool = False, lse: Optional[torch.Tensor] = None, merge: Optional[tuple] = None):
+                 return_lse: bool = False, lse: Optional[torch.Tensor] = None, merge: Optional[tuple] = None,
+                 kv_splits: int = 1, scratch: Optional[torch.Tensor] = None):
     """Ragged prefill: q [T, Hq, D]; sequence i owns query rows q_start[i]:q_start[i+1] and sees
-    seq_lens[i] keys, its last query at kv position seq_lens[i]-1."""
+    seq_lens[i] keys, its last query at kv position seq_lens[i]-1.
+
+    ``kv_splits > 1`` (tensor-core kernel only, no ``merge``) divides every CTA's key tiles over that many CTAs and
+    folds the partial results with a second small kernel: for launches with few query tiles and many keys, such as
+    the shared-prefix pass of a tensor-parallel rank that holds one KV head.  ``scratch`` (fp32, at least
+    :func:`attn_prefill_split_scratch_floats` elements) holds the partials."""
     _bf16c(q, "q")
     T, Hq, D = q.shape
     Hkv = k_cache.shape[1]
@@ -301,8 +307,21 @@ def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     a.alibi_slopes = _p(alibi_slopes)
     if merge is not None:
         a.merge_o, a.merge_lse = merge[0].data_ptr(), merge[1].data_ptr()
+    if kv_splits > 1:
+        need = attn_prefill_split_scratch_floats(T, Hq, D, kv_splits)
+        if scratch is None or scratch.numel() < need:
+            scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+        if scratch.dtype != torch.float32:
+            raise TypeError("scratch must be float32")
+        a.splits, a.scratch = kv_splits, scratch.data_ptr()
     N.check(N.cuda_lib().ub_attn_prefill(C.byref(a), _stream(q)), "ub_attn_prefill")
     return (out, lse) if return_lse else out
+
+
+def attn_prefill_split_scratch_floats(T: int, Hq: int, D: int, kv_splits: int) -> int:
+    """fp32 elements of workspace that ``attn_prefill(kv_splits=...)`` needs: the log-sum-exps, then the bf16 rows."""
+    lse = (kv_splits * T * Hq + 3) // 4 * 4
+    return lse + (kv_splits * T * Hq * D + 1) // 2
 
 
 def attn_prefill_last_path() -> str:
