@@ -243,9 +243,116 @@ def bench_norm(results):
         print(json.dumps(r))
 
 
+def bench_tp_layer(results, world=8, batch=512, variants=False):
+    """Every kernel of one decoder layer at the per-rank shapes of ``world``-way tensor parallelism (Llama-3-8B
+    architecture, the serving benchmark's steady-state step: ``batch`` decode rows that share a 1024-token prefix +
+    batch/128 prefill chunks of 128 tokens), each timed alone through a CUDA graph with L2 flushed.  No communication:
+    this is the compute a rank has to get through per layer."""
+    hbm, tf, how = _peaks()
+    H, D, bs, pre = 4096, 128, 16, 1024
+    Hq, Hkv, I = 32 // world, max(1, 8 // world), 14336 // world
+    P = max(1, batch // 128)
+    T = batch - P + P * 128                     # rows of a steady-state step
+    dev = "cuda"
+
+    def rec(name, med, best, **kw):
+        r = dict(kind="tp_layer", world=world, batch=batch, op=name, us=med * 1e3, best_us=best * 1e3, **kw)
+        results.append(r)
+        print(json.dumps(r))
+
+    # ---- GEMMs ----
+    gem = [("qkv", T, (Hq + 2 * Hkv) * D, H, 0), ("o_proj", T, H, Hq * D, 0), ("gate_up", T, I, H, 1), ("down", T, H, I, 0)]
+    for name, M, N, K, dual in gem:
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(N * (2 if dual else 1), K, device=dev, dtype=torch.bfloat16) * 0.02
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        opts = [dict()]
+        if variants:
+            opts += [dict(tile_tokens=t, cta_pair=1) for t in (64, 128, 256)] + [dict(cta_pair=2)] + \
+                    [dict(tile_tokens=t, cta_pair=1, splits=sp) for t in (128, 256) for sp in (2, 4)]
+        for o in opts:
+            try:
+                fn = (lambda: cuda_ops.gemm_tn(x, w, dual_rows=N, act="silu", out=out, **o)) if dual else \
+                     (lambda: cuda_ops.gemm_tn(x, w, out=out, **o))
+                med, best = time_ms(fn)
+            except Exception as e:        # a variant the kernel does not have (e.g. split-K of a 2 x 256 gated tile)
+                print(json.dumps(dict(op=name, opts=o, error=str(e)[:80])))
+                continue
+            flops = 2.0 * M * N * K * (2 if dual else 1)
+            rec(name, med, best, M=M, N=N, K=K, dual=dual, opts=o, tflops=flops / med / 1e9,
+                ctas=cuda_ops.gemm_num_ctas(M, N, K, bool(dual), o.get("tile_tokens", 0), o.get("splits", 0), o.get("cta_pair", 0)))
+        ref = (lambda: torch.nn.functional.silu(x @ w[:N].t()) * (x @ w[N:].t())) if dual else (lambda: x @ w.t())
+        rmed, rbest = time_ms(ref)
+        rec(name + " (cuBLAS)", rmed, rbest, M=M, N=N, K=K, dual=dual)
+    # ---- attention ----
+    B = batch - P
+    lens = [pre + 128 + (i * 128) // max(B, 1) for i in range(B)]
+    per = (max(lens) + bs - 1) // bs
+    nblk = pre // bs + (B + P) * (per - pre // bs) + 8
+    kc = torch.randn(nblk, Hkv, bs, D, device=dev, dtype=torch.bfloat16)
+    vc = torch.randn_like(kc)
+    shared = torch.arange(pre // bs, dtype=torch.int32)
+    own = torch.randperm(nblk - pre // bs)[: (B + P) * (per - pre // bs)].to(torch.int32).view(B + P, -1) + pre // bs
+    bt = torch.cat([shared[None].expand(B + P, -1), own], 1).contiguous().to(dev)
+    qkv = torch.randn(T, Hq + 2 * Hkv, D, device=dev, dtype=torch.bfloat16)
+    q = qkv[:, :Hq]
+    out = torch.empty(T, Hq, D, device=dev, dtype=torch.bfloat16)
+    oa = torch.empty(T, Hq, D, device=dev, dtype=torch.bfloat16)
+    la = torch.empty(T, Hq, device=dev, dtype=torch.float32)
+    plen = torch.tensor([pre], dtype=torch.int32, device=dev)
+    qs_all = torch.tensor([0, T], dtype=torch.int32, device=dev)
+    G = Hq // Hkv
+    ctas = -(-T // (128 // G)) * Hkv
+    auto = max(1, min(pre // 128, 148 // ctas, 8))
+    for kvs in sorted({1, 2, 4, 8, auto}):
+        scratch = torch.empty(cuda_ops.attn_prefill_split_scratch_floats(T, Hq, D, kvs), dtype=torch.float32, device=dev)
+        med, best = time_ms(lambda: cuda_ops.attn_prefill(q, kc, vc, bt[:1], plen, qs_all, T, causal=False, out=oa, lse=la,
+                                                          return_lse=True, kv_splits=kvs, scratch=scratch))
+        rec("attn_shared_prefix", med, best, rows=T, keys=pre, kv_splits=kvs, ctas=ctas * kvs, auto=(kvs == auto),
+            tflops=4.0 * T * pre * Hq * D / med / 1e9)
+    sl_d = torch.tensor(lens, dtype=torch.int32, device=dev)
+    med, best = time_ms(lambda: cuda_ops.attn_decode(q[:B], kc, vc, bt[:B], sl_d, out=out[:B], kv_start=pre, splits=1,
+                                                     merge=(oa[:B], la[:B])))
+    byts = 2.0 * 2 * sum(l - pre for l in lens) * Hkv * D
+    rec("attn_decode_suffix", med, best, B=B, gbs=byts / med / 1e6, frac_hbm=byts / med / 1e6 / hbm)
+    sl_p = torch.full((P,), pre + 128, dtype=torch.int32, device=dev)
+    qs_p = (torch.arange(P + 1, dtype=torch.int32) * 128).to(dev)
+    med, best = time_ms(lambda: cuda_ops.attn_prefill(q[B:], kc, vc, bt[B:], sl_p, qs_p, 128, causal=True, kv_start=pre,
+                                                      out=out[B:], merge=(oa[B:], la[B:])))
+    rec("attn_prefill_suffix", med, best, seqs=P, q_len=128)
+    # ---- norm, RoPE + append ----
+    x = torch.randn(T, H, device=dev, dtype=torch.bfloat16)
+    r_ = torch.randn_like(x)
+    w = torch.ones(H, device=dev, dtype=torch.bfloat16)
+    o1, o2 = torch.empty_like(x), torch.empty_like(x)
+    med, best = time_ms(lambda: cuda_ops.norm(x, w, residual=r_, out=o1, residual_out=o2))
+    rec("rmsnorm_residual (all rows)", med, best, T=T, gbs=2.0 * 4 * T * H / med / 1e6)
+    R = -(-T // world)
+    med, best = time_ms(lambda: cuda_ops.norm(x[:R], w, residual=r_[:R], out=o1[:R], residual_out=o2[:R]))
+    rec("rmsnorm_residual (rows of one rank)", med, best, T=R)
+    pos = torch.randint(0, 1280, (T,), dtype=torch.int32, device=dev)
+    slots = torch.randperm(nblk * bs, device=dev)[:T].to(torch.int32)
+    qkv2 = qkv.view(T, -1).contiguous()
+    med, best = time_ms(lambda: cuda_ops.rope_kv_append(qkv2, pos, slots, kc, vc, num_q_heads=Hq, num_kv_heads=Hkv,
+                                                        head_dim=D, theta=500000.0))
+    rec("rope_kv_append", med, best, T=T)
+    tot = {}
+    for r in results:
+        if r.get("kind") == "tp_layer" and "cuBLAS" not in r["op"] and not r.get("opts") and r.get("auto", True) and \
+                "all rows" not in r["op"]:
+            tot[r["op"]] = r["us"]
+    norm_us = tot.pop("rmsnorm_residual (rows of one rank)", 0.0)
+    layer = sum(tot.values()) + 2 * norm_us
+    print(json.dumps(dict(kind="tp_layer_total", world=world, batch=batch, us_per_layer=layer, ms_per_32_layers=layer * 32e-3,
+                          ops=tot, norm_us_each=norm_us)))
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", nargs="?", default="all", choices=["gemm", "attn", "norm", "all"])
+    ap.add_argument("what", nargs="?", default="all", choices=["gemm", "attn", "norm", "tp", "all"])
+    ap.add_argument("--world", type=int, default=8, help="tp only: tensor-parallel size whose per-rank shapes are timed")
+    ap.add_argument("--batch", type=int, default=512, help="tp only: concurrent sequences of the serving step")
+    ap.add_argument("--variants", action="store_true", help="tp only: also time forced tile / pair / split-K choices")
     ap.add_argument("--attn-case", default="all", choices=["all", "decode", "prefill", "suffix"], help="subset of the attention shapes")
     ap.add_argument("--json", default=None)
     ap.add_argument("--shape", default=None, help="gemm only: M,N,K,dual -- run just this shape")
@@ -257,6 +364,8 @@ def main(argv=None):
     if a.timeline:
         results.append(gemm_timeline(a.timeline, a.pair, a.tile))
         return
+    if a.what == "tp":
+        bench_tp_layer(results, a.world, a.batch, a.variants)
     if a.what in ("gemm", "all"):
         bench_gemm(results, tuple(int(v) for v in a.shape.split(",")) if a.shape else None, a.tile, a.pair)
     if a.what in ("attn", "all"):

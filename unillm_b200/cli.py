@@ -49,8 +49,19 @@ def cmd_generate(a) -> int:
     from .config import GenerationConfig
     from .pipeline import InferencePipelineBuilder
 
-    model = _load(a.model, a.device)
-    pipe = InferencePipelineBuilder().model(model).use_engine(a.engine).build()
+    cuda = a.device.startswith("cuda")
+    # for a GPU run the weights are loaded on the host and handed to the kernel runner, which keeps its own bf16
+    # copy in kernel layout on the device; a model the runner does not cover is moved to the device as a whole
+    model = _load(a.model, "cpu" if cuda else a.device)
+    b = InferencePipelineBuilder().model(model).use_engine(a.engine)
+    if cuda:
+        b = b.device(a.device).engine_options(max_num_seqs=8, max_num_batched_tokens=2048)
+    pipe = b.build()
+    if cuda:
+        if pipe.engine_note is None:
+            print("engine: paged KV + sm_100a kernels", file=sys.stderr)
+        else:
+            print(f"engine: whole-model path on {a.device} ({pipe.engine_note})", file=sys.stderr)
     cfg = GenerationConfig(max_new_tokens=a.max_tokens, temperature=a.temperature, top_p=a.top_p, top_k=(a.top_k or None),
                            do_sample=a.temperature > 0, seed=a.seed)
     if a.stream:

@@ -25,6 +25,7 @@ Reference counterpart: the per-token loop of ``UniLLMBackend::generate`` / ``Lla
 from __future__ import annotations
 
 import math
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Tuple
@@ -463,6 +464,8 @@ class GpuModelRunner:
         self._handle = None
         self.attn_scratch = torch.empty(max_num_seqs * weights.hq * 16 * (D + 2), dtype=torch.float32, device=dev)
         self.prefix_scratch = None     # workspace of the key-split shared-prefix pass, allocated on first use
+        self.overlap_suffix = os.environ.get("UB_ATTN_OVERLAP", "1") != "0"
+        self._side = None
         self.graphs: Dict[tuple, tuple] = {}
         self.profile = False
         self._prof_events = []
@@ -578,10 +581,24 @@ class GpuModelRunner:
             if kvs > 1:
                 self.launches += 1
             if fused:
+                # The suffix pass of the prefill chunks is a handful of CTAs whose time is all latency; it runs beside
+                # the decode rows' suffix pass on a second stream (both only read the prefix partial).
+                side = self._side_stream() if (pp and self.overlap_suffix) else None
+                if side is not None:
+                    cur = torch.cuda.current_stream()
+                    side.wait_stream(cur)
+                    with torch.cuda.stream(side):
+                        with self._prof("attn_prefill_suffix"):
+                            K.attn_prefill(q[Dp:], kc, vc, bt[Dp:], self._view(lay, "seq_lens_p"),
+                                           self._view(lay, "q_start"), lay["_max_q"], scale=scale, causal=True,
+                                           kv_start=shared_prefix_len, out=out[Dp:], merge=(oa[Dp:], lse_a[Dp:]))
+                    self.launches += 1
                 with self._prof("attn_decode_suffix"):
                     K.attn_decode(q[:Dp], kc, vc, bt[:Dp], self._view(lay, "seq_lens_d"), scale=scale,
                                   kv_start=shared_prefix_len, out=out[:Dp], splits=1, merge=(oa[:Dp], lse_a[:Dp]))
-                if pp:
+                if side is not None:
+                    cur.wait_stream(side)
+                elif pp:
                     with self._prof("attn_prefill_suffix"):
                         K.attn_prefill(q[Dp:], kc, vc, bt[Dp:], self._view(lay, "seq_lens_p"), self._view(lay, "q_start"),
                                        lay["_max_q"], scale=scale, causal=True, kv_start=shared_prefix_len, out=out[Dp:],
@@ -617,6 +634,11 @@ class GpuModelRunner:
                                out=out[Dp:])
             self.launches += 1
         return out.view(T, hq * D)
+
+    def _side_stream(self):
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        return self._side
 
     PREFIX_SPLIT_ROWS = 160 * 128     # (query row, head) pairs x splits the key-split workspace can hold
 

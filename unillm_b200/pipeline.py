@@ -5,7 +5,9 @@ Parity with ``crates/runtime/src/inference.rs:159-388``: ``InferencePipeline(+Bu
 The reference is hard-wired to LLaMA and re-runs the whole sequence for every token; this one takes any
 ``Model``, uses its KV-cached path when it has one, offers ``generate_streaming`` (promised by the
 reference's docs, ``documentation/docs/api-reference/inference.md:10-34``) and can run on the paged engine
-(``use_engine=True``).
+(``use_engine=True``).  With ``device="cuda"`` the paged engine is the one on the sm_100a kernels
+(``engine.factory.build_engine``: radix-cached paged KV, tcgen05 GEMMs and attention, device sampling); a model
+that the kernel runner does not cover stays on the whole-model path and ``engine_note`` says why.
 """
 from __future__ import annotations
 
@@ -31,19 +33,40 @@ class InferenceMetrics:
 
 
 class InferencePipeline:
-    def __init__(self, model: Model, tokenizer: Tokenizer, use_engine: bool = False):
+    def __init__(self, model: Model, tokenizer: Tokenizer, use_engine: bool = False, device: Optional[str] = None,
+                 engine_options: Optional[dict] = None):
+        """``device``: ``None`` keeps the model where it is; ``"cuda"`` / ``"cuda:i"`` serves it from the paged engine on
+        the GPU kernels when the model qualifies (``use_engine`` is then implied), else moves the whole model there."""
         self.model, self.tokenizer, self.use_engine = model, tokenizer, use_engine
+        self.device = device
+        self.engine_options = dict(engine_options or {})
+        self.engine_kind = "none"        # "gpu-kernels" | "cpu-paged" | "none" once the engine exists
+        self.engine_note: Optional[str] = None
         self.last_metrics = InferenceMetrics()
         self._engine = None
+        if device is not None and str(device).startswith("cuda"):
+            from .engine.factory import why_not_gpu
+
+            self.engine_note = why_not_gpu(model)
+            if self.engine_note is None:
+                self.use_engine = True
+            else:
+                import torch
+
+                if torch.cuda.is_available():
+                    model.to_device(device)
 
     def _paged_engine(self):
         if self._engine is None:
-            from .engine.cpu_runner import CpuModelRunner
-            from .engine.llm_engine import LLMEngine
+            from .engine.factory import build_cpu_engine, build_engine
 
-            runner = CpuModelRunner(self.model, num_blocks=1024, block_size=16, max_model_len=8192)
-            self._engine = LLMEngine(runner, num_blocks=1024, block_size=16, max_num_seqs=8, max_num_batched_tokens=512,
-                                     max_model_len=8192)
+            want_gpu = self.device is not None and str(self.device).startswith("cuda") and self.engine_note is None
+            if want_gpu:
+                self._engine = build_engine(self.model, device=self.device, **self.engine_options)
+                self.engine_kind = "gpu-kernels"
+            else:
+                self._engine = build_cpu_engine(self.model)
+                self.engine_kind = "cpu-paged"
         return self._engine
 
     def generate_tokens(self, prompt_ids: List[int], cfg: GenerationConfig,
@@ -124,6 +147,8 @@ class InferencePipelineBuilder:
         self._model: Optional[Model] = None
         self._tok: Optional[Tokenizer] = None
         self._engine = False
+        self._device: Optional[str] = None
+        self._engine_options: dict = {}
 
     def model(self, m: Model) -> "InferencePipelineBuilder":
         self._model = m
@@ -137,7 +162,17 @@ class InferencePipelineBuilder:
         self._engine = flag
         return self
 
+    def device(self, device: Optional[str]) -> "InferencePipelineBuilder":
+        self._device = device
+        return self
+
+    def engine_options(self, **kw) -> "InferencePipelineBuilder":
+        """Keyword arguments of ``engine.factory.build_engine`` (max_num_seqs, max_model_len, num_blocks, ...)."""
+        self._engine_options.update(kw)
+        return self
+
     def build(self) -> InferencePipeline:
         if self._model is None:
             raise ConfigurationError("Model is required")
-        return InferencePipeline(self._model, self._tok or self._model.tokenizer(), self._engine)
+        return InferencePipeline(self._model, self._tok or self._model.tokenizer(), self._engine, self._device,
+                                 self._engine_options)
