@@ -261,6 +261,28 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ----------------------------------------------------------------------------
+// Publishing peer stores of a whole launch with ONE arrival per peer
+// ----------------------------------------------------------------------------
+// Every CTA of a producing launch stores rows into peers' memory.  Instead of each CTA bumping a counter on every
+// peer (ctas x world remote atomics on one hot address per peer and use), the CTAs arrive on a counter in LOCAL
+// memory and the last one to arrive bumps each peer's counter once.  Called by ONE thread per CTA, after a CTA-wide
+// barrier that follows the CTA's peer stores (the barrier orders the other threads' stores before this thread's
+// system-scope fence; the acquire-release chain through the local counter orders the other CTAs' stores before the
+// last CTA's remote arrivals).  The last CTA zeroes the local counter again, so the next launch in the stream can
+// reuse it; `total` is the number of CTAs that call this for one use (it may span two launches).
+__device__ __forceinline__ void publish_to_peers(uint32_t* local_count, uint32_t total, uint32_t* const* peer_flag, int world) {
+  asm volatile("fence.acq_rel.sys;" ::: "memory");
+  uint32_t old;
+  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(local_count) : "memory");
+  if (old + 1 == total) {
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(local_count), "r"(0u) : "memory");
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
+    for (int r = 0; r < world; ++r)
+      asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(peer_flag[r]), "r"(1u) : "memory");
+  }
+}
+
+// ----------------------------------------------------------------------------
 // Small numeric helpers
 // ----------------------------------------------------------------------------
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }

@@ -54,6 +54,8 @@ struct GemmParams {
   int rs_world, rs_rank, rs_rows_per_rank;
   __nv_bfloat16* rs_peer_out[UB_MAX_RANKS];  // each: [world][rows_per_rank][ldo]
   uint32_t* rs_peer_flag[UB_MAX_RANKS];      // counter to bump on each peer
+  uint32_t* rs_local_count;                  // local arrival counter of this use (see publish_to_peers)
+  uint32_t rs_total;                         // CTAs that arrive on it per use
   // F3: all-gather wait.  ag_world == 0 disables.
   int ag_world, ag_rows_per_rank;
   const uint32_t* ag_flags;     // [world] counters in local memory, one per source rank
@@ -597,10 +599,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     }
     if (tid_e == 0) ts_mark(p, 5);
     if (!SPLITK && p.rs_world > 0) {
-      // Publish: every storing thread fences to system scope, then one thread per peer bumps its counter.
-      __threadfence_system();
+      // Publish: the epilogue warps meet, then one thread arrives for the CTA (the last CTA of the launch tells the peers).
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (tid_e < p.rs_world) red_release_sys_add_u32(p.rs_peer_flag[tid_e], 1u);
+      if (tid_e == 0) publish_to_peers(p.rs_local_count, p.rs_total, p.rs_peer_flag, p.rs_world);
     }
   }
 
@@ -632,9 +633,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                            ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
       splitk_finish<DUAL>(p, smem, TN, r0, r1, tid_e, m0, n0, vec_ok);
       if (p.rs_world > 0) {
-        __threadfence_system();
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (tid_e < p.rs_world) red_release_sys_add_u32(p.rs_peer_flag[tid_e], 1u);
+        if (tid_e == 0) publish_to_peers(p.rs_local_count, p.rs_total, p.rs_peer_flag, p.rs_world);
       }
     }
     if (threadIdx.x == 64) ts_mark(p, 6);
@@ -950,9 +950,8 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       }
     }
     if (!SPLITK && p.rs_world > 0) {
-      __threadfence_system();
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (tid_e < p.rs_world) red_release_sys_add_u32(p.rs_peer_flag[tid_e], 1u);
+      if (tid_e == 0) publish_to_peers(p.rs_local_count, p.rs_total, p.rs_peer_flag, p.rs_world);
     }
   }
 
@@ -983,9 +982,8 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                            ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
       splitk_finish<DUAL>(p, smem, TN, r0, r1, tid_e, m0, n0, vec_ok);
       if (p.rs_world > 0) {
-        __threadfence_system();
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (tid_e < p.rs_world) red_release_sys_add_u32(p.rs_peer_flag[tid_e], 1u);
+        if (tid_e == 0) publish_to_peers(p.rs_local_count, p.rs_total, p.rs_peer_flag, p.rs_world);
       }
     }
   }
@@ -1371,6 +1369,9 @@ extern "C" int ub_gemm_tn(const UbGemmArgs* a, void* stream_v) {
     p.rs_peer_out[i] = reinterpret_cast<__nv_bfloat16*>(a->rs_peer_out[i]);
     p.rs_peer_flag[i] = a->rs_peer_flag[i];
   }
+  p.rs_local_count = a->rs_local_count;
+  p.rs_total = (uint32_t)pl.ctas;          // every CTA of this GEMM (both launches of a two-phase schedule) arrives once
+  if (p.rs_world > 0 && p.rs_local_count == nullptr) return -8;
   CUtensorMap tw, tx;
   const long long w_rows = (dual || a->grp_tiles != nullptr) ? (long long)a->w_rows_total : (long long)a->N;
   int rc = make_tmap_bf16_2d(&tw, a->w, w_rows, a->K, a->ldw, BM_W, BK);

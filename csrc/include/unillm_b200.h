@@ -64,6 +64,9 @@ typedef struct UbGemmArgs {
   int tail_split;       /* 0 = auto (split K of a thin last round over clusters in a second launch), 1 = never */
   int cta_pair;         /* 0 = auto, 1 = never, 2 = always: tiles of 256 weight rows on pairs of CTAs (cta_group::2) */
   int pair_splits;      /* 0 = auto; 1 / 2 / 4: K slices (pairs per tile) when the CTA-pair kernel is used */
+  /* F1: a zeroed u32 in LOCAL memory on which the CTAs of this GEMM arrive; the last one bumps every rs_peer_flag
+     once (one arrival per source rank and use at the consumer).  Required when rs_world > 0. */
+  uint32_t* rs_local_count;
 } UbGemmArgs;
 int ub_gemm_tn(const UbGemmArgs* args, void* stream);
 /* Number of CTAs the launch for `args` will use; each CTA signals every peer once in F1 mode. */
@@ -94,6 +97,9 @@ typedef struct UbNormArgs {
   /* up to 32 consecutive local counters that are idle during this kernel: block 0 zeroes them first */
   uint32_t* reset_flags;
   int reset_count;
+  /* F3 producer: a zeroed u32 in LOCAL memory on which the row CTAs arrive; the last one bumps every ag_peer_flag
+     once (the consumer waits for one arrival per source rank).  Required when ag_world > 0. */
+  uint32_t* ag_local_count;
 } UbNormArgs;
 int ub_norm(const UbNormArgs* args, void* stream);
 
@@ -216,10 +222,12 @@ int ub_moe_gather(const void* x, const int* sorted_rows, void* out, int rows, in
 int ub_moe_combine(const void* y, const int* row_slot, const float* topk_w, const void* residual, void* out, int T,
                    int K, int H, void* stream);
 /* F6: combine fused with the reduce-scatter: token t's partial row is stored into the receive slot
-   peer_out[owner(t)][rank][t - owner*rows_per_rank] and every CTA bumps every peer's counter once. */
+   peer_out[owner(t)][rank][t - owner*rows_per_rank]; the CTAs arrive on the zeroed LOCAL counter local_count and the
+   last one bumps every peer's counter once. */
 int ub_moe_combine_num_ctas(int T, int H);
 int ub_moe_combine_rs(const void* y, const int* row_slot, const float* topk_w, int T, int K, int H, int world, int rank,
-                      int rows_per_rank, void* const* peer_out, uint32_t* const* peer_flag, void* stream);
+                      int rows_per_rank, void* const* peer_out, uint32_t* const* peer_flag, uint32_t* local_count,
+                      void* stream);
 
 /* ---------------- K12 : GGUF-quantised weights ---------------- */
 /* qtype is the ggml type id: 2 Q4_0, 3 Q4_1, 6 Q5_0, 8 Q8_0, 12 Q4_K, 14 Q6_K. */

@@ -151,6 +151,7 @@ struct CombinePush {
   int world, rank, rows_per_rank;            // world == 0: plain store to `out`
   __nv_bfloat16* peer_out[UB_MAX_RANKS];     // each: [world][rows_per_rank][H] receive slots
   uint32_t* peer_flag[UB_MAX_RANKS];
+  uint32_t* local_count;                     // local arrival counter of the CTAs (see publish_to_peers)
 };
 
 __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ row_slot,
@@ -187,11 +188,9 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* _
         make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
   }
   if (push.world > 0) {
-    // publish: every storing thread fences to system scope, then one thread per peer bumps that peer's counter
-    __threadfence_system();
+    // publish: the CTAs arrive on the local counter; the last one bumps every peer's counter once
     __syncthreads();
-    if (threadIdx.x < push.world)
-      asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(push.peer_flag[threadIdx.x]), "r"(1u) : "memory");
+    if (threadIdx.x == 0) publish_to_peers(push.local_count, gridDim.x, push.peer_flag, push.world);
   }
 }
 
@@ -245,11 +244,13 @@ extern "C" int ub_moe_combine(const void* y, const int* row_slot, const float* t
 
 // F6: combine + reduce-scatter.  Every CTA (ub_moe_combine_num_ctas of them) signals every peer once.
 extern "C" int ub_moe_combine_rs(const void* y, const int* row_slot, const float* topk_w, int T, int K, int H, int world, int rank,
-                                 int rows_per_rank, void* const* peer_out, uint32_t* const* peer_flag, void* stream_v) {
+                                 int rows_per_rank, void* const* peer_out, uint32_t* const* peer_flag, uint32_t* local_count,
+                                 void* stream_v) {
   if (T <= 0) return 0;
-  if (H % 8 != 0 || world <= 0 || world > UB_MAX_RANKS || rows_per_rank <= 0) return -2;
+  if (H % 8 != 0 || world <= 0 || world > UB_MAX_RANKS || rows_per_rank <= 0 || local_count == nullptr) return -2;
   ub::CombinePush push = {};
   push.world = world; push.rank = rank; push.rows_per_rank = rows_per_rank;
+  push.local_count = local_count;
   for (int i = 0; i < world; ++i) {
     push.peer_out[i] = reinterpret_cast<__nv_bfloat16*>(peer_out[i]);
     push.peer_flag[i] = peer_flag[i];

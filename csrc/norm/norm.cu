@@ -35,6 +35,7 @@ struct NormParams {
   uint32_t* ag_peer_flag[UB_MAX_RANKS];
   uint32_t* reset_flags;   // local counters that no kernel is using right now; zeroed by block 0 before it signals
   int reset_count;
+  uint32_t* ag_local_count;   // local arrival counter of the row CTAs (see publish_to_peers)
 };
 
 __device__ __forceinline__ float block_sum(float v, float* red) {
@@ -193,11 +194,9 @@ __global__ void __launch_bounds__(256) norm_kernel(const NormParams p) {
     }
   }
   if (p.ag_world > 0) {
-    __threadfence_system();
+    // the row CTAs arrive locally; the last one tells every peer that ALL rows of this rank are there
     __syncthreads();
-    if (threadIdx.x < p.ag_world) {
-      asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.ag_peer_flag[threadIdx.x]), "r"(1u) : "memory");
-    }
+    if (threadIdx.x == 0) publish_to_peers(p.ag_local_count, gridDim.x, p.ag_peer_flag, p.ag_world);
   }
 }
 
@@ -233,6 +232,8 @@ extern "C" int ub_norm(const UbNormArgs* a, void* stream_v) {
   p.rs_signals_per_use = a->rs_signals_per_use;
   p.ag_world = a->ag_world; p.ag_rank = a->ag_rank;
   p.reset_flags = a->reset_flags; p.reset_count = a->reset_count;
+  p.ag_local_count = a->ag_local_count;
+  if (p.ag_world > 0 && p.ag_local_count == nullptr) return -8;
   for (int i = 0; i < UB_MAX_RANKS; ++i) {
     p.ag_peer_out[i] = (__nv_bfloat16*)a->ag_peer_out[i];
     p.ag_peer_flag[i] = a->ag_peer_flag[i];

@@ -20,7 +20,7 @@ def _free_port() -> int:
 
 def test_heartbeat_watchdog_in_process():
     store = DictStore()
-    hbs = [Heartbeat(store, r, 3, interval=0.02, timeout=0.25).start() for r in range(3)]
+    hbs = [Heartbeat(store, r, 3, interval=0.02, timeout=0.6).start() for r in range(3)]
     try:
         for step in range(3):
             for h in hbs:
@@ -32,7 +32,7 @@ def test_heartbeat_watchdog_in_process():
         inj = FaultInjector(hbs[2])
         inj.mute_heartbeat()
         hbs[0].set_step(5), hbs[1].set_step(5)
-        time.sleep(0.4)
+        time.sleep(0.9)
         rep = det.poll()
         assert rep.dead == [2] and rep.status() == "unhealthy"
         with pytest.raises(RankFailure) as e:
@@ -70,7 +70,7 @@ def _hb_worker(rank, world, port, q):
     from torch.distributed import TCPStore
 
     store = TCPStore("127.0.0.1", port, world, is_master=(rank == 0), wait_for_workers=True, timeout=__import__("datetime").timedelta(seconds=30))
-    hb = Heartbeat(store, rank, world, interval=0.05, timeout=0.6).start()
+    hb = Heartbeat(store, rank, world, interval=0.05, timeout=2.0).start()
     inj = FaultInjector(hb)
     if rank == 2:
         inj.exit_at_step(3)
@@ -207,3 +207,104 @@ def test_engine_snapshot_restore_continues_identically():
     assert [out[i] for i in ids] == ref
     with pytest.raises(Exception):
         e2.restore(snap)
+
+
+def _elastic_worker(rank, world, port, q, exit_rank, exit_step):
+    import datetime
+
+    from torch.distributed import TCPStore
+
+    from unillm_b200.dist.elastic import serve_elastic
+    from unillm_b200.engine.cpu_runner import TpCpuModelRunner
+    from unillm_b200.engine.llm_engine import LLMEngine
+    from unillm_b200.models import configs as C
+    from unillm_b200.models.families import LlamaModel
+    from unillm_b200.sampling import SamplingParams
+
+    torch.set_num_threads(1)
+    store = TCPStore("127.0.0.1", port, world, is_master=(rank == 0), wait_for_workers=True,
+                     timeout=datetime.timedelta(seconds=60))
+    cfg = C.LlamaConfig(vocab_size=96, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2)
+    m = LlamaModel.new(cfg, init="random", seed=11)
+    m.p = {k: v.to(torch.bfloat16).float() for k, v in m.p.items()}
+    g = torch.Generator().manual_seed(4)
+    params = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    reqs = [{"id": i, "prompt": torch.randint(0, 96, (n,), generator=g).tolist(), "params": params}
+            for i, n in enumerate((7, 12, 3, 9))]
+
+    def build_engine(g_rank, g_world, group):
+        runner = TpCpuModelRunner(m, g_rank, g_world, group, num_blocks=64, block_size=4, max_model_len=64)
+        return LLMEngine(runner, num_blocks=64, block_size=4, max_num_seqs=4, max_num_batched_tokens=16, max_model_len=64)
+
+    inj = FaultInjector()
+    if rank == exit_rank:
+        inj.exit_at_step(exit_step)
+    res = serve_elastic(rank, world, store, build_engine, reqs, num_heads=4, num_kv_heads=2, hb_interval=0.05,
+                        hb_timeout=1.5, injector=inj)
+    q.put((rank, res.role, res.outputs, res.generations, res.final_world, res.recovered_from, res.steps))
+    if rank == 0:
+        time.sleep(2.0)             # the store lives in this process: keep it until the others have reported
+
+
+def test_rank_loss_is_survived_at_a_smaller_tensor_parallel_size():
+    """Four CPU ranks serve four requests tensor parallel (4 query heads, 2 KV heads: every KV head is replicated on two
+    ranks); rank 3 exits between steps.  The others notice on the host (heartbeat + step gate) before their next
+    collective, re-form a 2-rank group (the largest size that divides the 4 heads), prefill the token history again
+    and finish with the tokens of an undisturbed single-rank run."""
+    from unillm_b200.engine.cpu_runner import CpuModelRunner
+    from unillm_b200.engine.llm_engine import LLMEngine
+    from unillm_b200.models import configs as C
+    from unillm_b200.models.families import LlamaModel
+    from unillm_b200.sampling import SamplingParams
+
+    cfg = C.LlamaConfig(vocab_size=96, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2)
+    m = LlamaModel.new(cfg, init="random", seed=11)
+    m.p = {k: v.to(torch.bfloat16).float() for k, v in m.p.items()}
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, 96, (n,), generator=g).tolist() for n in (7, 12, 3, 9)]
+    eng = LLMEngine(CpuModelRunner(m, num_blocks=64, block_size=4, max_model_len=64), num_blocks=64, block_size=4,
+                    max_num_seqs=4, max_num_batched_tokens=16, max_model_len=64)
+    ref = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_elastic_worker, args=(r, 4, port, q, 3, 4)) for r in range(4)]
+    for p in procs:
+        p.start()
+    got = {}
+    for _ in range(4):
+        r = q.get(timeout=180)
+        got[r[0]] = r[1:]
+    for p in procs:
+        p.join(timeout=60)
+    assert got[3][0] == "exited"
+    assert got[2][0] == "spare" and got[2][4] == [[3]]
+    for r in (0, 1):
+        role, outs, gens, final_world, recovered, steps = got[r]
+        assert role == "finished" and gens == 2 and final_world == 2 and recovered == [[3]], got[r]
+        assert [outs[i] for i in range(4)] == ref
+
+
+def test_kv_heads_are_replicated_when_ranks_outnumber_them():
+    from unillm_b200.engine.runner import RunnerWeights
+    from unillm_b200.models import configs as C
+    from unillm_b200.models.families import LlamaModel
+
+    cfg = C.LlamaConfig(vocab_size=64, hidden_size=64, intermediate_size=64, num_hidden_layers=1, num_attention_heads=8,
+                        num_key_value_heads=2)
+    m = LlamaModel.new(cfg, init="random", seed=1)
+    D = m.spec.head_dim
+    q, k, v = m.p["layers.0.wqkv"].split([8 * D, 2 * D, 2 * D], 0)
+    for rank in range(8):
+        w = RunnerWeights(m.spec, m.p, "cpu", rank, 8)
+        assert (w.hq, w.hkv, w.kv_lo) == (1, 1, rank // 4)
+        got = w.t["layers.0.wqkv"].float()
+        assert torch.equal(got[:D], q[rank * D:(rank + 1) * D].to(torch.bfloat16).float())
+        assert torch.equal(got[D:2 * D], k[w.kv_lo * D:(w.kv_lo + 1) * D].to(torch.bfloat16).float())
+        assert torch.equal(got[2 * D:], v[w.kv_lo * D:(w.kv_lo + 1) * D].to(torch.bfloat16).float())
+    assert RunnerWeights.kv_layout(8, 3, 4) == (2, 6)
+    with pytest.raises(Exception):
+        RunnerWeights.kv_layout(3, 0, 2)

@@ -40,18 +40,16 @@ def test_gemm_rs_norm_ag_gemm_chain_emulated(world, T):
     Kr = Kfull // world
     for rep in range(2):      # twice: the counters must be reset correctly between uses
         # ---- F1 producer on every rank: partial GEMM, rows pushed to their owner ----
-        n_ctas = None
         for r, c in enumerate(comms):
             xr = x[:, r * Kr:(r + 1) * Kr].contiguous()
             wr = wo[:, r * Kr:(r + 1) * Kr].contiguous()
             out = c.rs_local_tensor(0, R).view(world * R, H)
             K.gemm_tn(xr, wr, out=out, rs=c.gemm_rs(0, R))
-            n_ctas = K.gemm_num_ctas(T, H, Kr)
         # ---- F1 consumer + F3 producer on every rank ----
         new_res = []
         for r, c in enumerate(comms):
             _, h = K.norm(c.rs_local_tensor(0, R), ln, residual=res[r * R:(r + 1) * R].contiguous(), eps=1e-5,
-                          want_residual_out=True, no_out=True, T=R, rs=c.norm_rs(0, n_ctas * world), ag=c.norm_ag(1),
+                          want_residual_out=True, no_out=True, T=R, rs=c.norm_rs(0), ag=c.norm_ag(1),
                           reset=c.reset_after_ag(1))
             new_res.append(h)
         # ---- F3 consumer: column-parallel GEMM on the gathered rows ----
@@ -77,9 +75,10 @@ def test_gemm_rs_norm_ag_gemm_chain_emulated(world, T):
         hb = hn.to(torch.bfloat16).float()
         aref = torch.nn.functional.silu(hb @ wgu[:256].float().t()) * (hb @ wgu[256:].float().t())
         assert (act.float() - aref.cuda()).abs().max().item() < 0.05 * max(1.0, aref.abs().max().item())
-        for c in comms:   # counters of the other phase were zeroed
+        for c in comms:   # counters of the other phase were zeroed, and the last CTA of every launch zeroed its local one
             flags = c.buf[c.flags.offset:c.flags.offset + 256].view(torch.int32)
             assert int(flags[16:25].abs().sum()) == 0
+            assert int(flags[40:44].abs().sum()) == 0
 
 
 def test_flag_wait_times_out_without_hanging():

@@ -162,13 +162,14 @@ def test_expert_parallel_partials_and_fused_combine():
     R = T // W
     recv = [torch.zeros(W, R, H, dtype=torch.bfloat16, device="cuda") for _ in range(W)]
     flags = torch.zeros(W, dtype=torch.int32, device="cuda")
-    n_ctas = ops.moe_combine_num_ctas(T, H)
+    local = torch.zeros(W, dtype=torch.int32, device="cuda")          # one arrival counter per emulated rank
     for rank in range(W):
         rs = {"world": W, "rank": rank, "rows_per_rank": R, "peer_out": [t.data_ptr() for t in recv],
-              "peer_flag": [flags[o:o + 1].data_ptr() for o in range(W)]}
+              "peer_flag": [flags[o:o + 1].data_ptr() for o in range(W)], "local_count": local[rank:rank + 1].data_ptr()}
         run(rank * (E // W), E // W, rs)
     torch.cuda.synchronize()
     ops.check_device_errors()
-    assert flags.cpu().tolist() == [W * n_ctas] * W
+    assert flags.cpu().tolist() == [W] * W                            # one arrival per source rank
+    assert local.cpu().tolist() == [0] * W                            # the last CTA of each launch zeroed its counter
     got = torch.cat([recv[o].float().sum(0) for o in range(W)], 0)
     assert (got - full.float()).abs().max().item() < 0.05 * max(1.0, full.float().abs().max().item())

@@ -78,8 +78,11 @@ def build_engine(arch_name: str, world: int, rank: int, group, device: str, *, m
     return eng, runner, cfg, w
 
 
-def serve(eng, requests: List[dict], device: Optional[str], dist_group=None, world: int = 1) -> Dict:
-    """Runs the requests (dicts: prompt, max_tokens, arrival seconds) to completion; returns aggregate metrics."""
+def serve(eng, requests: List[dict], device: Optional[str], dist_group=None, world: int = 1, health=None) -> Dict:
+    """Runs the requests (dicts: prompt, max_tokens, arrival seconds) to completion; returns aggregate metrics.
+
+    ``health``: an optional ``dist.health.FailureDetector``; its ``check()`` runs on the host before every step, so a
+    peer whose heartbeat has stopped ends the run with ``RankFailure`` before the next launch."""
     from ..sampling import SamplingParams
 
     cuda = device is not None and device.startswith("cuda")
@@ -99,6 +102,8 @@ def serve(eng, requests: List[dict], device: Optional[str], dist_group=None, wor
         if cuda:
             e = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
             eng.step_events = e
+        if health is not None:
+            health.check()
         eng.step()
         if e is not None and eng.step_events is None:
             evs.append(e)                    # recorded: the step launched work (a drain-only step does not)
@@ -124,7 +129,7 @@ def serve(eng, requests: List[dict], device: Optional[str], dist_group=None, wor
             "ttft_p50_ms": 1e3 * percentile(ttft, 0.5) if ttft else None, "ttft_p99_ms": 1e3 * percentile(ttft, 0.99) if ttft else None,
             "tpot_p50_ms": 1e3 * percentile(tpot, 0.5) if tpot else None, "tpot_p99_ms": 1e3 * percentile(tpot, 0.99) if tpot else None,
             "prefill_tokens": st.prefill_tokens, "decode_tokens": st.decode_tokens, "prefix_hit_tokens": st.cached_tokens,
-            "preemptions": st.preemptions}
+            "preemptions": st.preemptions, "device_errors": st.device_errors}
 
 
 def rand_ids(g, n: int, vocab: int) -> List[int]:
@@ -155,14 +160,15 @@ def config1(scale: float) -> Dict:
     return res
 
 
-def gpu_config(n: int, scale: float, env) -> Dict:
+def gpu_config(n: int, scale: float, env, fused: bool = True, health=None, warm: bool = True) -> Dict:
     rank, world, group, device = env
     small = scale < 0.05
     g = torch.Generator().manual_seed(99)
+    build = lambda *a, **k: build_engine(*a, fused=fused, **k)      # noqa: E731
     if n == 2:
         nreq = max(8, int(1024 * scale))
         rate = 64.0                                    # requests per second
-        eng, runner, cfg, w = build_engine("llama2-7b", world, rank, group, device, max_seqs=256, max_len=2048 + 512 + 16,
+        eng, runner, cfg, w = build("llama2-7b", world, rank, group, device, max_seqs=256, max_len=2048 + 512 + 16,
                                            blocks=max(4096, min(60000, nreq * 170)), small=small)
         lens = torch.randint(128, 2049, (nreq,), generator=g).tolist()
         outs = torch.randint(64, 513, (nreq,), generator=g).tolist()
@@ -174,27 +180,47 @@ def gpu_config(n: int, scale: float, env) -> Dict:
     elif n == 3:
         nreq = max(8, int(256 * scale))
         pl, ol = (1024, 256) if not small else (128, 32)
-        eng, runner, cfg, w = build_engine("mixtral-8x7b", world, rank, group, device, max_seqs=256, max_len=pl + ol + 16,
+        eng, runner, cfg, w = build("mixtral-8x7b", world, rank, group, device, max_seqs=256, max_len=pl + ol + 16,
                                            blocks=nreq * ((pl + ol) // 16 + 2) + 64, small=small)
-        reqs = [{"prompt": rand_ids(g, pl, cfg.vocab_size), "max_tokens": ol} for _ in range(nreq)]
+        mk = lambda: [{"prompt": rand_ids(g, pl, cfg.vocab_size), "max_tokens": ol} for _ in range(nreq)]   # noqa: E731
+        reqs = mk()
         extra = {"model": "mixtral-8x7b", "requests": nreq, "prompt": pl, "output": ol, "expert_parallel": w.ep}
     elif n == 4:
         nreq = max(8, int(512 * scale))
         pl, sl, ol = (1024, 128, 128) if not small else (128, 32, 16)
-        eng, runner, cfg, w = build_engine("llama3-8b", world, rank, group, device, max_seqs=min(512, nreq),
+        eng, runner, cfg, w = build("llama3-8b", world, rank, group, device, max_seqs=min(512, nreq),
                                            max_len=pl + sl + ol + 16, blocks=pl // 16 + nreq * ((sl + ol) // 16 + 2) + 64, small=small)
-        prefix = rand_ids(g, pl, cfg.vocab_size)
-        reqs = [{"prompt": prefix + rand_ids(g, sl, cfg.vocab_size), "max_tokens": ol} for _ in range(nreq)]
+
+        def mk():
+            prefix = rand_ids(g, pl, cfg.vocab_size)
+            return [{"prompt": prefix + rand_ids(g, sl, cfg.vocab_size), "max_tokens": ol} for _ in range(nreq)]
+
+        reqs = mk()
         extra = {"model": "llama3-8b", "requests": nreq, "shared_prefix": pl, "suffix": sl, "output": ol}
     else:
         raise ValueError(n)
-    res = serve(eng, reqs, device, group, world)
-    res.update(extra, n_gpus=world, dtype="bf16", parallelism=f"tp{world}" + (f"+ep{world}" if w.ep else ""),
-               graphs=len(runner.graphs), small_model=small)
+    warmed = False
+    if warm and n in (3, 4) and runner.use_cuda_graphs:
+        # Fixed-length workloads walk through the same step shapes on every run: one untimed pass over requests of
+        # the same shape (other token ids, so nothing of it is a prefix-cache hit later) captures the CUDA graphs,
+        # and the timed pass then measures serving, not graph capture.
+        serve(eng, reqs, device, group, world, health)
+        import dataclasses
+
+        for f in dataclasses.fields(eng.stats):
+            setattr(eng.stats, f.name, 0)
+        reqs = mk()
+        warmed = True
+    cap0 = runner.captures
+    res = serve(eng, reqs, device, group, world, health)
+    res.update(extra, n_gpus=world, dtype="bf16",
+               parallelism=f"tp{world}" + (f"+ep{world}" if w.ep else "") + ("" if fused or world == 1 else "-nccl-baseline"),
+               graphs=len(runner.graphs), graph_captures_in_timed_run=runner.captures - cap0, warm_pass=warmed,
+               fused_steps=runner.fused_steps, unfused_steps=runner.unfused_steps, small_model=small)
     return res
 
 
-def config5(scale: float, env) -> List[Dict]:
+def config5(scale: float, env, fused: bool = True) -> List[Dict]:
     """Llama-3-70B decode sweep.  The KV cache is filled with random values at the target context (decode time does not
     depend on the values), then ``steps`` decode steps run through the runner with CUDA graphs."""
     from ..engine.runner import StepBatch
@@ -208,7 +234,7 @@ def config5(scale: float, env) -> List[Dict]:
     per = (max_len + 15) // 16                       # block-table width of the runner
     blocks = bmax * per + 16
     eng, runner, cfg, w = build_engine("llama3-70b", world, rank, group, device, max_seqs=bmax, max_len=max_len,
-                                       blocks=blocks, small=small)
+                                       blocks=blocks, small=small, fused=fused)
     for kc in runner.k_cache:
         kc.normal_(0, 0.5)
     for vc in runner.v_cache:
@@ -243,7 +269,8 @@ def config5(scale: float, env) -> List[Dict]:
             ms = float(t[0])
         out.append({"model": "llama3-70b", "n_gpus": world, "batch": B, "context": ctx, "decode_steps": steps,
                     "tpot_ms": ms / steps, "tok_s_device": B * steps / (ms / 1e3), "kv": "random values at the target context",
-                    "small_model": small, "dtype": "bf16", "parallelism": f"tp{world}"})
+                    "small_model": small, "dtype": "bf16",
+                    "parallelism": f"tp{world}" + ("" if fused or world == 1 else "-nccl-baseline")})
     return out
 
 
@@ -252,6 +279,11 @@ def main(argv=None) -> int:
     ap.add_argument("--config", type=int, required=True, choices=[1, 2, 3, 4, 5])
     ap.add_argument("--scale", type=float, default=1.0)
     ap.add_argument("--out", default=None, help="append JSON lines here")
+    ap.add_argument("--nccl-baseline", action="store_true",
+                    help="tensor parallel through NCCL all-reduce between separate kernels instead of the fused kernels")
+    ap.add_argument("--no-warm-pass", action="store_true", help="configs 3 / 4: time the first pass, graph captures included")
+    ap.add_argument("--health", action="store_true",
+                    help="start a heartbeat per rank (TCP store on MASTER_PORT + 17) and check the peers before every step")
     a = ap.parse_args(argv)
     if a.config == 1:
         results = [config1(a.scale)]
@@ -262,7 +294,31 @@ def main(argv=None) -> int:
         env = init_distributed(control_group=False)
         rank = env.rank
         e = (env.rank, env.world, env.group, env.device)
-        results = config5(a.scale, e) if a.config == 5 else [gpu_config(a.config, a.scale, e)]
+        health = hb = None
+        if a.health:
+            from ..dist.health import FailureDetector, Heartbeat, StepWatchdog
+
+            if env.world > 1:
+                import datetime
+
+                from torch.distributed import TCPStore
+
+                store = TCPStore(os.environ.get("MASTER_ADDR", "127.0.0.1"), int(os.environ.get("MASTER_PORT", "29500")) + 17,
+                                 env.world, is_master=(env.rank == 0), timeout=datetime.timedelta(seconds=120))
+            else:
+                from ..dist.health import DictStore
+
+                store = DictStore()
+            hb = Heartbeat(store, env.rank, env.world, interval=0.2, timeout=5.0).start()
+            health = FailureDetector(hb, StepWatchdog(hb, max_lag=1 << 30))
+        try:
+            if a.config == 5:
+                results = config5(a.scale, e, fused=not a.nccl_baseline)
+            else:
+                results = [gpu_config(a.config, a.scale, e, fused=not a.nccl_baseline, health=health, warm=not a.no_warm_pass)]
+        finally:
+            if hb is not None:
+                hb.stop()
         from ..ops import cuda_ops
 
         cuda_ops.check_device_errors()

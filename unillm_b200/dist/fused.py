@@ -9,9 +9,13 @@ every peer's address space through ``torch.distributed._symmetric_memory``) that
     ``src`` are written by ``src``'s norm kernel (F3 producer), read by the local GEMM's TMA loads;
   * the arrival counters of both.
 
-Counter protocol: counters only count up during a use and are zeroed between uses by a kernel that
+Counter protocol: a producing launch tells a peer ONCE that all of its rows have arrived: its CTAs arrive
+on a counter in local memory and the last one bumps the peer's counter (``publish_to_peers`` in
+``csrc/common/ptx.cuh``), so a consumer waits for ``world`` arrivals on a reduce-scatter counter and for one
+arrival on each per-source all-gather counter, and a use costs ``world`` remote atomics per rank instead of
+``CTAs x world``.  Peer counters only count up during a use and are zeroed between uses by a kernel that
 the layer pipeline orders after their last reader and before their next writer (the norm kernel
-that follows, see ``csrc/norm/norm.cu``).  The counters are laid out so that each norm kernel's reset
+that follows, see ``csrc/norm/norm.cu``); the local arrival counters are zeroed by the CTA that arrives last.  The counters are laid out so that each norm kernel's reset
 set is one consecutive run: ``[ag0 x 8][rs1]`` and ``[ag1 x 8][rs0]``.  All device waits are bounded;
 after a reported timeout call :meth:`reset` on every rank before the next step.
 
@@ -30,6 +34,7 @@ MAXR = 8
 AG0, RS1, AG1, RS0 = 0, 8, 16, 24
 FLAG_WORDS = 64
 ARGMAX_FLAG, ARGMAX_ROUND = 32, 33     # counter of the greedy merge and its (local) round word
+LOCAL_RS0, LOCAL_RS1, LOCAL_AG0, LOCAL_AG1 = 40, 41, 42, 43   # local arrival counters of the producing launches
 ARGMAX_ROWS = 2048                      # sampled rows per step the merge area can hold
 
 
@@ -108,24 +113,28 @@ class FusedComm:
         """F1 producer arguments: push rows into rank ``owner``'s ``rs[k]`` slot of this rank."""
         return {"world": self.world, "rank": self.rank, "rows_per_rank": rows_per_rank,
                 "peer_out": [self._peer(r, self.rs[k]) for r in range(self.world)],
-                "peer_flag": [self.flag_ptr(r, RS0 if k == 0 else RS1) for r in range(self.world)]}
+                "peer_flag": [self.flag_ptr(r, RS0 if k == 0 else RS1) for r in range(self.world)],
+                "local_count": self.local_flag_ptr(LOCAL_RS0 if k == 0 else LOCAL_RS1)}
 
-    def norm_rs(self, k: int, signals: int) -> dict:
-        """F1 consumer arguments: wait for ``signals`` arrivals, sum the ``world`` slots of ``rs[k]``."""
-        return {"world": self.world, "flag": self.local_flag_ptr(RS0 if k == 0 else RS1), "signals_per_use": signals}
+    def norm_rs(self, k: int, signals: int = 0) -> dict:
+        """F1 consumer arguments: wait for one arrival per source rank (``signals`` overrides the count), sum the
+        ``world`` slots of ``rs[k]``."""
+        return {"world": self.world, "flag": self.local_flag_ptr(RS0 if k == 0 else RS1),
+                "signals_per_use": signals or self.world}
 
     def norm_ag(self, k: int) -> dict:
         """F3 producer arguments: push normalised rows into every rank's ``ag[k]`` and bump their counter for us."""
         base = AG0 if k == 0 else AG1
         return {"world": self.world, "rank": self.rank,
                 "peer_out": [self._peer(r, self.ag[k]) for r in range(self.world)],
-                "peer_flag": [self.flag_ptr(r, base + self.rank) for r in range(self.world)]}
+                "peer_flag": [self.flag_ptr(r, base + self.rank) for r in range(self.world)],
+                "local_count": self.local_flag_ptr(LOCAL_AG0 if k == 0 else LOCAL_AG1)}
 
     def gemm_ag(self, k: int, rows_per_rank: int) -> dict:
-        """F3 consumer arguments: token rows of source rank ``s`` are ready when counter ``s`` reaches its row count."""
+        """F3 consumer arguments: the token rows of source rank ``s`` are ready when counter ``s`` shows its one arrival."""
         base = AG0 if k == 0 else AG1
         return {"world": self.world, "rows_per_rank": rows_per_rank, "flags": self.local_flag_ptr(base),
-                "signals_per_use": rows_per_rank}
+                "signals_per_use": 1}
 
     def reset_after_ag(self, k: int) -> tuple:
         """Counters a norm kernel may zero: the all-gather counters it does NOT feed plus the reduce-scatter

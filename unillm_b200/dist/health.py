@@ -76,9 +76,13 @@ class PeerView:
 
 
 class Heartbeat:
-    def __init__(self, store, rank: int, world: int, interval: float = 0.2, timeout: float = 1.0, prefix: str = "hb"):
+    def __init__(self, store, rank: int, world: int, interval: float = 0.2, timeout: float = 1.0, prefix: str = "hb",
+                 startup_grace: float = 30.0):
+        """``timeout``: a peer whose counter has not moved for this long is dead.  ``startup_grace``: a peer that has
+        never published a beat yet (its process is still starting) is given this long before it counts as dead."""
         self.store, self.rank, self.world = store, rank, world
         self.interval, self.timeout, self.prefix = interval, timeout, prefix
+        self.startup_grace = max(startup_grace, timeout)
         self.muted = False                      # fault injection: stop publishing
         self._stop = threading.Event()
         self._thread: Optional[threading.Thread] = None
@@ -127,7 +131,8 @@ class Heartbeat:
 
     def dead_ranks(self) -> List[int]:
         now = time.monotonic()
-        return [r for r, v in self.observe().items() if r != self.rank and now - v.last_change > self.timeout]
+        return [r for r, v in self.observe().items() if r != self.rank and
+                now - v.last_change > (self.timeout if v.ever_seen else self.startup_grace)]
 
     def steps(self) -> Dict[int, int]:
         return {r: v.step for r, v in self.observe().items()}

@@ -172,3 +172,64 @@ def _draw_row(probs: torch.Tensor, seed: int, step: int, row: int) -> int:
     cum = torch.cumsum(probs.double(), 0)
     idx = int(torch.searchsorted(cum, torch.tensor(u * float(cum[-1]), dtype=torch.float64), right=True))
     return min(idx, probs.numel() - 1)
+
+
+class TpCpuModelRunner(CpuModelRunner):
+    """The CPU runner, tensor parallel over a ``torch.distributed`` (gloo) group: attention heads, KV heads, the MLP
+    width and the vocabulary are divided over the ranks exactly as ``RunnerWeights`` divides them for the GPU runner,
+    the row-parallel outputs (attention output projection, MLP down projection) are summed with ``all_reduce`` and the
+    vocabulary shards' logits are gathered.  It exists for the host-side tests of the distributed engine (sharding
+    math, failure detection, recovery at a smaller tensor-parallel size): every rank runs the same ``LLMEngine`` on the
+    same request stream, like the GPU ranks do.  Dense decoder models with a sequential or parallel residual."""
+
+    def __init__(self, model: DecoderModel, rank: int, world: int, group=None, *, num_blocks: int, block_size: int = 16,
+                 max_model_len: int = 8192):
+        import copy
+        import dataclasses
+
+        from .runner import RunnerWeights
+
+        s = model.spec
+        if s.moe is not None or s.embed_proj_dim:
+            raise ValueError("TpCpuModelRunner covers dense decoder models")
+        self.rank, self.world, self.group = rank, world, group
+        w = RunnerWeights(s, model.p, "cpu", rank, world)
+        shard = copy.copy(model)
+        shard.spec = dataclasses.replace(s, num_heads=w.hq, num_kv_heads=w.hkv, tie_embeddings=False)
+        shard.p = {k: v.to(model.dtype) for k, v in w.t.items()}
+        shard._rope = shard._alibi = None
+        inner_mlp = shard._mlp
+
+        def mlp(i, x):
+            return self._sum(inner_mlp(i, x))
+
+        def lm_logits(x):
+            y = ops_fn.linear(x, shard.p["lm_head"], shard.p.get("lm_head_bias"))
+            if s.logit_scale != 1.0:
+                y = (y.float() * s.logit_scale).to(y.dtype)
+            return self._gather_cols(y)
+
+        shard._mlp, shard.lm_logits = mlp, lm_logits
+        super().__init__(shard, num_blocks=num_blocks, block_size=block_size, max_model_len=max_model_len)
+        if s.pos == "alibi":
+            self._alibi = alibi_slopes(s.num_heads)[rank * w.hq:(rank + 1) * w.hq].to(model.device)
+
+    def _sum(self, y: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            import torch.distributed as dist
+
+            y = y.contiguous()
+            dist.all_reduce(y, group=self.group)
+        return y
+
+    def _gather_cols(self, y: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return y
+        import torch.distributed as dist
+
+        parts = [torch.empty_like(y) for _ in range(self.world)]
+        dist.all_gather(parts, y.contiguous(), group=self.group)
+        return torch.cat(parts, dim=-1)
+
+    def _attention(self, i, h, b, pos, slots):
+        return self._sum(super()._attention(i, h, b, pos, slots))

@@ -99,12 +99,13 @@ class RunnerWeights:
         self._set_ep(expert_parallel)
         if s.num_heads % world != 0:
             raise InvalidInput(f"{s.num_heads} heads not divisible by tensor parallel size {world}")
-        if s.num_kv_heads % world != 0:
-            raise UnsupportedOperation(f"{s.num_kv_heads} KV heads with tensor parallel size {world}: "
-                                       "KV head replication is not implemented")
         self.hq = s.num_heads // world
-        self.hkv = s.num_kv_heads // world
+        self.hkv, self.kv_lo = self.kv_layout(s.num_kv_heads, rank, world)
         D = s.head_dim
+
+        def kv_rows(t):
+            """Rows (or elements) of this rank's KV heads inside a [num_kv_heads * D, ...] tensor."""
+            return t[self.kv_lo * D:(self.kv_lo + self.hkv) * D]
 
         def dev(t):
             return t.to(device=device, dtype=torch.bfloat16).contiguous()
@@ -129,12 +130,10 @@ class RunnerWeights:
                     self.t[L + n] = dev(p[L + n])
             wqkv = p[L + "wqkv"]
             q, k, v = wqkv.split([s.q_size, s.kv_size, s.kv_size], dim=0)
-            self.t[L + "wqkv"] = dev(torch.cat([shard_rows(q, rank, world), shard_rows(k, rank, world),
-                                                shard_rows(v, rank, world)], 0))
+            self.t[L + "wqkv"] = dev(torch.cat([shard_rows(q, rank, world), kv_rows(k), kv_rows(v)], 0))
             if L + "bqkv" in p:
                 qb, kb, vb = p[L + "bqkv"].split([s.q_size, s.kv_size, s.kv_size])
-                self.t[L + "bqkv"] = dev(torch.cat([shard_rows(qb, rank, world), shard_rows(kb, rank, world),
-                                                    shard_rows(vb, rank, world)]))
+                self.t[L + "bqkv"] = dev(torch.cat([shard_rows(qb, rank, world), kv_rows(kb), kv_rows(vb)]))
             self.t[L + "wo"] = dev(shard_cols(p[L + "wo"], rank, world))
             if L + "bo" in p:
                 self.t[L + "bo"] = dev(p[L + "bo"] if rank == 0 else torch.zeros_like(p[L + "bo"]))
@@ -176,6 +175,19 @@ class RunnerWeights:
                     self.t[L + "shared_gate_up"] = dev(torch.cat([shard_rows(g, rank, world), shard_rows(u, rank, world)], 0))
                     self.t[L + "shared_down"] = dev(shard_cols(p[L + "shared_down"], rank, world))
 
+    @staticmethod
+    def kv_layout(num_kv_heads: int, rank: int, world: int) -> Tuple[int, int]:
+        """(KV heads held by ``rank``, index of the first one).  When the ranks divide the KV heads every rank holds
+        its share; when there are more ranks than KV heads (``world`` a multiple of them) every KV head is replicated
+        on ``world / num_kv_heads`` consecutive ranks, whose query heads are exactly that head's group -- the
+        reference expands grouped heads by copying them (``crates/runtime/src/models_v2/llama.rs:1073-1087``)."""
+        if num_kv_heads % world == 0:
+            n = num_kv_heads // world
+            return n, rank * n
+        if world % num_kv_heads == 0:
+            return 1, rank // (world // num_kv_heads)
+        raise UnsupportedOperation(f"{num_kv_heads} KV heads cannot be divided over or replicated on {world} ranks")
+
     def _set_ep(self, expert_parallel: bool) -> None:
         """Expert parallelism applies when asked for, with more than one rank and an expert count the ranks divide."""
         m = self.spec.moe
@@ -193,7 +205,8 @@ class RunnerWeights:
         self.spec, self.rank, self.world = spec, rank, world
         s = spec
         self._set_ep(expert_parallel)
-        self.hq, self.hkv = s.num_heads // world, s.num_kv_heads // world
+        self.hq = s.num_heads // world
+        self.hkv, self.kv_lo = self.kv_layout(s.num_kv_heads, rank, world)
         self.vocab_shard = s.vocab_size // world
         self.t = {}
         H, I = s.hidden_size, s.intermediate_size
@@ -227,13 +240,14 @@ class RunnerWeights:
             self.t["lm_head"] = self.t["embed"][rank * vs:(rank + 1) * vs] if world > 1 else self.t["embed"]
         else:
             self.t["lm_head"] = rnd(s.vocab_size, H, rank * vs, vs)
-        qs, ks = s.q_size // world, s.kv_size // world
+        qs, ks = s.q_size // world, self.hkv * s.head_dim
+        k0 = self.kv_lo * s.head_dim
         for i in range(s.num_layers):
             L = f"layers.{i}."
             self.t[L + "ln1.w"], self.t[L + "ln2.w"] = ones(H), ones(H)
             q = rnd(s.q_size, H, rank * qs, qs)
-            k = rnd(s.kv_size, H, rank * ks, ks)
-            v = rnd(s.kv_size, H, rank * ks, ks)
+            k = rnd(s.kv_size, H, k0, ks)
+            v = rnd(s.kv_size, H, k0, ks)
             self.t[L + "wqkv"] = torch.cat([q, k, v], 0)
             self.t[L + "wo"] = rnd(H, s.q_size, 0, H, rank * qs, qs)
             if s.layer_is_moe(i):
@@ -785,14 +799,11 @@ class GpuModelRunner:
         xr = x_full[r * R:(r + 1) * R]                      # this rank's rows of the residual stream
         h_full = self._norm(x_full, "layers.0.ln1")         # layer 0 normalises all rows locally
         kind = "rms" if s.norm == "rms" else "layer"
-        n_o = K.gemm_num_ctas(T, H, self.w.hq * s.head_dim) * W
         dense = [i for i in range(s.num_layers) if not s.layer_is_moe(i)]
-        I_loc = n_dense = 0
+        I_loc = 0
         if dense:
             L0 = f"layers.{dense[0]}."
             I_loc = (t[L0 + "w_gate_up"].shape[0] // 2) if s.mlp == "gated" else t[L0 + "w_up"].shape[0]
-            n_dense = K.gemm_num_ctas(T, H, I_loc) * W
-        n_moe = K.moe_combine_num_ctas(T, H) * W
         rs0_out = c.rs_local_tensor(0, R)
         rs1_out = c.rs_local_tensor(1, R)
         ag_args = None
@@ -815,7 +826,7 @@ class GpuModelRunner:
             with self._prof("norm_rs_ag"):
                 _, xr = K.norm(rs0_out, t[L + "ln2.w"], bias=t.get(L + "ln2.b"), residual=xr, eps=s.norm_eps, kind=kind,
                                weight_offset_one=s.norm_weight_offset_one, want_residual_out=True, no_out=True, T=R,
-                               rs=c.norm_rs(0, n_o), ag=c.norm_ag(1), reset=c.reset_after_ag(1))
+                               rs=c.norm_rs(0), ag=c.norm_ag(1), reset=c.reset_after_ag(1))
             self.launches += 1
             h2 = c.ag_local_tensor(1, T)
             if s.layer_is_moe(i):
@@ -824,10 +835,9 @@ class GpuModelRunner:
                 from ..dist.fused import AG1
                 from .moe_runner import moe_partial
 
-                K.wait_flags(c.local_flag_ptr(AG1), W, R, self.device)
+                K.wait_flags(c.local_flag_ptr(AG1), W, 1, self.device)
                 self.launches += 1
                 moe_partial(self, i, h2, None, combine_rs=c.gemm_rs(1, R))
-                n_d = n_moe
             else:
                 if s.mlp == "gated":
                     act = self._gemm(h2, t[L + "w_gate_up"], dual_rows=I_loc, act=s.act, ag=c.gemm_ag(1, R), tag="gemm_ag")
@@ -835,20 +845,19 @@ class GpuModelRunner:
                     act = self._gemm(h2, t[L + "w_up"], bias=t.get(L + "b_up"), act=s.act, ag=c.gemm_ag(1, R), tag="gemm_ag")
                 self._gemm(act, t[L + "w_down"], bias=t.get(L + "b_down"), out=rs1_out.view(W * R, H)[:T],
                            rs=c.gemm_rs(1, R), tag="gemm_rs")
-                n_d = n_dense
             last = i == s.num_layers - 1
             nname = "final_norm" if last else f"layers.{i + 1}.ln1"
             with self._prof("norm_rs_ag"):
                 _, xr = K.norm(rs1_out, t[nname + ".w"], bias=t.get(nname + ".b"), residual=xr, eps=s.norm_eps, kind=kind,
                                weight_offset_one=s.norm_weight_offset_one, want_residual_out=True, no_out=True, T=R,
-                               rs=c.norm_rs(1, n_d), ag=c.norm_ag(0), reset=c.reset_after_ag(0))
+                               rs=c.norm_rs(1), ag=c.norm_ag(0), reset=c.reset_after_ag(0))
             self.launches += 1
             h_full = c.ag_local_tensor(0, T)
             ag_args = c.gemm_ag(0, R)
         # the final-normed rows of all ranks arrive in gather area 0; wait for them before the row gather
         from ..dist.fused import AG0
 
-        K.wait_flags(c.local_flag_ptr(AG0), W, R, self.device)
+        K.wait_flags(c.local_flag_ptr(AG0), W, 1, self.device)
         self.launches += 1
         self._final_norm_done = True
         return h_full

@@ -44,6 +44,7 @@ class UbGemmArgs(C.Structure):
         ("ag_world", i32), ("ag_rows_per_rank", i32),
         ("ag_flags", vp), ("ag_epoch", vp), ("ag_signals_per_use", u32),
         ("grp_tiles", vp), ("grp_max_tiles", i32), ("grp_w_rows", i32), ("tail_split", i32), ("cta_pair", i32), ("pair_splits", i32),
+        ("rs_local_count", vp),
     ]
 
 
@@ -54,7 +55,7 @@ class UbNormArgs(C.Structure):
         ("rs_world", i32), ("rs_flag", vp), ("epoch", vp), ("rs_signals_per_use", u32),
         ("ag_world", i32), ("ag_rank", i32),
         ("ag_peer_out", vp * UB_MAX_RANKS), ("ag_peer_flag", vp * UB_MAX_RANKS),
-        ("reset_flags", vp), ("reset_count", i32),
+        ("reset_flags", vp), ("reset_count", i32), ("ag_local_count", vp),
     ]
 
 

@@ -117,6 +117,7 @@ def gemm_tn(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = 
         for i in range(rs["world"]):
             a.rs_peer_out[i] = rs["peer_out"][i]
             a.rs_peer_flag[i] = rs["peer_flag"][i]
+        a.rs_local_count = rs["local_count"]
     if ag is not None:
         a.ag_world, a.ag_rows_per_rank = ag["world"], ag["rows_per_rank"]
         a.ag_flags, a.ag_signals_per_use = ag["flags"], ag["signals_per_use"]
@@ -189,6 +190,7 @@ def norm(x: torch.Tensor, weight: Optional[torch.Tensor], *, bias: Optional[torc
         for i in range(ag["world"]):
             a.ag_peer_out[i] = ag["peer_out"][i]
             a.ag_peer_flag[i] = ag["peer_flag"][i]
+        a.ag_local_count = ag["local_count"]
     N.check(N.cuda_lib().ub_norm(C.byref(a), _stream(x)), "ub_norm")
     if residual_out is not None:
         return out, residual_out
@@ -570,7 +572,7 @@ def moe_combine_num_ctas(T: int, H: int) -> int:
 
 def moe_combine_rs(y: torch.Tensor, r: MoeRouting, rs: dict) -> None:
     """Combine fused with the reduce-scatter: partial rows go into the owners' receive slots (``rs`` as for
-    ``gemm_tn``: world, rank, rows_per_rank, peer_out, peer_flag); each CTA signals each peer once."""
+    ``gemm_tn``: world, rank, rows_per_rank, peer_out, peer_flag, local_count); the last CTA signals each peer once."""
     _bf16c(y, "y")
     H = y.shape[1]
     W = rs["world"]
@@ -578,9 +580,10 @@ def moe_combine_rs(y: torch.Tensor, r: MoeRouting, rs: dict) -> None:
     flags = (C.c_void_p * W)(*[int(p) for p in rs["peer_flag"][:W]])
     lib = N.cuda_lib()
     lib.ub_moe_combine_rs.restype = C.c_int
-    lib.ub_moe_combine_rs.argtypes = [N.vp, N.vp, N.vp, N.i32, N.i32, N.i32, N.i32, N.i32, N.i32, N.vp, N.vp, N.vp]
+    lib.ub_moe_combine_rs.argtypes = [N.vp, N.vp, N.vp, N.i32, N.i32, N.i32, N.i32, N.i32, N.i32, N.vp, N.vp, N.vp, N.vp]
     N.check(lib.ub_moe_combine_rs(y.data_ptr(), r.row_slot.data_ptr(), r.topk_w.data_ptr(), r.T, r.K, H, W, rs["rank"],
-                                  rs["rows_per_rank"], C.cast(outs, C.c_void_p), C.cast(flags, C.c_void_p), _stream(y)),
+                                  rs["rows_per_rank"], C.cast(outs, C.c_void_p), C.cast(flags, C.c_void_p),
+                                  rs["local_count"], _stream(y)),
             "ub_moe_combine_rs")
 
 
