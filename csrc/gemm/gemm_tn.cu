@@ -7,7 +7,9 @@
 //    run the same kernel; only the token-tile width changes.  The accumulator in TMEM therefore
 //    holds out^T: TMEM lane = output feature, TMEM column = token.
 //  * Warp roles: warp 0 = TMA producer, warp 1 = tcgen05.mma issuer and TMEM owner,
-//    warps 2..5 = epilogue (TMEM -> registers -> smem transpose -> 16-byte global stores).
+//    warps 2..9 = epilogue (TMEM -> registers -> smem transpose -> 16-byte global stores) in two groups of four:
+//    a warp may read one quarter of the TMEM lanes, so two warps share every quarter and take alternate 32-token
+//    chunks of the accumulator (the exposed epilogue of a single-tile CTA halves).
 //  * Two scheduling modes share the main loop:
 //      - PERSISTENT: one CTA per SM walks a static list of output tiles; the accumulator is
 //        double-buffered in TMEM so the epilogue of tile i overlaps the MMAs of tile i+1.
@@ -35,7 +37,9 @@ namespace ub {
 constexpr int BM_W = 128;  // weight rows per tile (MMA M)
 constexpr int BK = 64;     // K elements per stage (one 128-byte swizzle atom of bf16)
 constexpr int UMMA_K = 16;
-constexpr int STAGING_BYTES = 16 * 1024;  // persistent-mode epilogue staging: 2 x [32][128] bf16 or 1 x [32][128] fp32
+constexpr int STAGING_BYTES = 16 * 1024;  // epilogue staging: one [32][128] bf16 (or [16][128] fp32) buffer per epilogue group
+constexpr int EPI_THREADS = 256;          // eight epilogue warps: two per TMEM lane quarter, taking alternate 32-token chunks
+constexpr int GEMM_THREADS = 64 + EPI_THREADS;
 
 struct GemmParams {
   int M, N, K;
@@ -244,11 +248,11 @@ __device__ __forceinline__ void st_dsmem_f32(uint32_t addr, uint32_t bits) {
 
 template <int TN, int CH, bool DUAL>
 __device__ __forceinline__ void splitk_scatter(const GemmParams& p, uint32_t smem_base, uint32_t lane_addr, int et,
-                                               int my_split, uint32_t rank_stride, uint32_t rank_off) {
+                                               int my_split, uint32_t rank_stride, uint32_t rank_off, int grp) {
   const int S = p.splits, per = (TN + S - 1) / S;
   const uint32_t up_off = uint32_t(S * per) * BM_W * 4u;
 #pragma unroll 1
-  for (int c = 0; c < TN / CH; ++c) {
+  for (int c = grp; c < TN / CH; c += 2) {
     uint32_t r[CH], r2[CH];
     if constexpr (CH == 32) {
       tmem_ld_32x32(lane_addr + c * CH, r);
@@ -283,7 +287,7 @@ __device__ __forceinline__ void splitk_finish_t(const GemmParams& p, const uint8
   const float* part = reinterpret_cast<const float*>(smem);
   const float* part_up = part + (size_t)S * per * BM_W;
   const int n_items = (r1 - r0) * 16;
-  for (int idx = tid_e; idx < n_items; idx += 128) {
+  for (int idx = tid_e; idx < n_items; idx += EPI_THREADS) {
     const int lt = idx >> 4, c8 = idx & 15;
     float g[8] = {0, 0, 0, 0, 0, 0, 0, 0}, up[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int sp = 0; sp < S; ++sp) {
@@ -332,7 +336,7 @@ __device__ __forceinline__ void splitk_finish(const GemmParams& p, const uint8_t
 }
 
 template <int TN, int STAGES, bool DUAL, bool SPLITK>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                const GemmParams p) {
   using S = GemmSmem<TN, STAGES, DUAL, SPLITK>;
@@ -383,7 +387,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full_bar[b], 1);
-      mbar_init(&tmem_empty_bar[b], 128);
+      mbar_init(&tmem_empty_bar[b], EPI_THREADS);
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmap_w);
@@ -515,15 +519,19 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       }
     }
   } else {
-    // ------------------------------ epilogue (warps 2..5) ------------------------------
+    // ------------------------------ epilogue (warps 2..9) ------------------------------
     const int q = warp & 3;           // TMEM lane quarter this warp may read
     const int et = q * 32 + lane;     // 0..127 : output feature inside the tile == TMEM lane
     const int tid_e = threadIdx.x - 64;
+    const int grp = tid_e >> 7;       // epilogue group: takes the chunks c with (c & 1) == grp
+    const int tid_g = tid_e & 127;
+    const int bar_id = 1 + grp;       // named barrier of the group (128 threads)
     constexpr int CH = TN >= 32 ? 32 : 16;
+    constexpr int NCH = TN / CH;
     const bool vec_ok = (p.N % 8 == 0) && (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
                         (p.residual == nullptr ||
                          ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
-    int ui = 0, chunk_ctr = 0;
+    int ui = 0;
     for (int u = unit_begin; u < total_tiles; u += unit_step) {
       const TileCoord tc = tile_coord(p, u, num_m, TN);
       if (!tc.valid) continue;
@@ -542,9 +550,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         const int n = n0 + et;
         float bias_v = 0.f;
         if (p.bias != nullptr && n < p.N) bias_v = __bfloat162float(p.bias[n]);
-        uint8_t* staging = smem + S::TILE_BYTES;
+        uint8_t* staging = smem + S::TILE_BYTES + grp * (STAGING_BYTES / 2);
+        if (grp >= NCH) {
+          // a tile of a single chunk: this group has nothing to read and hands the buffer back at once
+          tc_fence_before();
+          mbar_arrive(&tmem_empty_bar[ab]);
+        }
 #pragma unroll 1
-        for (int c = 0; c < TN / CH; ++c, ++chunk_ctr) {
+        for (int c = grp; c < NCH; c += 2) {
           uint32_t r[CH], r2[CH];
           if constexpr (CH == 32) {
             tmem_ld_32x32(lane_addr + c * CH, r);
@@ -554,37 +567,37 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             if (DUAL) tmem_ld_32x16(lane_addr + TN + c * CH, r2);
           }
           tmem_ld_wait();
-          if (c == TN / CH - 1) {
-            // Accumulator fully read: hand the TMEM buffer back to the MMA warp.
+          if (c + 2 >= NCH) {
+            // This group's share of the accumulator is read: hand the TMEM buffer back to the MMA warp.
             tc_fence_before();
             mbar_arrive(&tmem_empty_bar[ab]);
           }
           epi_values<CH, DUAL>(r, r2, p.out_scale, bias_v, p.act);
           if (p.out_f32) {
+            // fp32 rows are twice as wide: the group's 8 KB buffer holds 16 tokens at a time
             float* stf = reinterpret_cast<float*>(staging);
 #pragma unroll
-            for (int j = 0; j < CH; ++j) {
-              stf[j * BM_W + et] = __uint_as_float(r[j]);
+            for (int hh = 0; hh < CH / 16; ++hh) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) stf[j * BM_W + et] = __uint_as_float(r[hh * 16 + j]);
+              asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+              for (int idx = tid_g; idx < 16 * 16; idx += 128) {
+                const int tok = idx >> 4, c8 = idx & 15;
+                const float4 lo = *reinterpret_cast<const float4*>(stf + tok * BM_W + c8 * 8);
+                const float4 hi = *reinterpret_cast<const float4*>(stf + tok * BM_W + c8 * 8 + 4);
+                float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                emit8(p, m0 + c * CH + hh * 16 + tok, m_end, n0 + c8 * 8, v, vec_ok);
+              }
+              asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            for (int idx = tid_e; idx < CH * 16; idx += 128) {
-              const int tok = idx >> 4, c8 = idx & 15;
-              const float4 lo = *reinterpret_cast<const float4*>(stf + tok * BM_W + c8 * 8);
-              const float4 hi = *reinterpret_cast<const float4*>(stf + tok * BM_W + c8 * 8 + 4);
-              float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-              emit8(p, m0 + c * CH + tok, m_end, n0 + c8 * 8, v, vec_ok);
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
           } else {
-            __nv_bfloat16* stb = reinterpret_cast<__nv_bfloat16*>(staging + (chunk_ctr & 1) * (STAGING_BYTES / 2));
+            __nv_bfloat16* stb = reinterpret_cast<__nv_bfloat16*>(staging);
 #pragma unroll
             for (int j = 0; j < CH; ++j) {
               stb[j * BM_W + et] = __float2bfloat16(__uint_as_float(r[j]));
             }
-            // One barrier per chunk: the two staging halves alternate, so the writers of chunk c+2
-            // have all passed the barrier of chunk c+1, i.e. finished reading chunk c.
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            for (int idx = tid_e; idx < CH * 16; idx += 128) {
+            asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+            for (int idx = tid_g; idx < CH * 16; idx += 128) {
               const int tok = idx >> 4, c8 = idx & 15;
               const uint4 raw = *reinterpret_cast<const uint4*>(stb + tok * BM_W + c8 * 8);
               const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
@@ -593,6 +606,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
               for (int e = 0; e < 4; ++e) { v[2 * e] = bf16_lo(w[e]); v[2 * e + 1] = bf16_hi(w[e]); }
               emit8(p, m0 + c * CH + tok, m_end, n0 + c8 * 8, v, vec_ok);
             }
+            // the group's buffer is read: the next chunk may overwrite it
+            asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
           }
         }
       }
@@ -600,7 +615,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     if (tid_e == 0) ts_mark(p, 5);
     if (!SPLITK && p.rs_world > 0) {
       // Publish: the epilogue warps meet, then one thread arrives for the CTA (the last CTA of the launch tells the peers).
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 3, 256;" ::: "memory");
       if (tid_e == 0) publish_to_peers(p.rs_local_count, p.rs_total, p.rs_peer_flag, p.rs_world);
     }
   }
@@ -616,7 +631,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       tc_fence_after();
       constexpr int CHS = TN >= 32 ? 32 : 16;
       const int q = warp & 3;
-      splitk_scatter<TN, CHS, DUAL>(p, smem_u32(smem), tmem_base + (uint32_t(q * 32) << 16), q * 32 + lane, crank, 1u, 0u);
+      splitk_scatter<TN, CHS, DUAL>(p, smem_u32(smem), tmem_base + (uint32_t(q * 32) << 16), q * 32 + lane, crank, 1u, 0u,
+                                    (int(threadIdx.x) - 64) >> 7);
     }
     if (threadIdx.x == 64) ts_mark(p, 9);
     tc_fence_before();
@@ -633,7 +649,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                            ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
       splitk_finish<DUAL>(p, smem, TN, r0, r1, tid_e, m0, n0, vec_ok);
       if (p.rs_world > 0) {
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 3, 256;" ::: "memory");
         if (tid_e == 0) publish_to_peers(p.rs_local_count, p.rs_total, p.rs_peer_flag, p.rs_world);
       }
     }
@@ -725,7 +741,7 @@ struct Gemm2Smem {
 };
 
 template <int TN, int STAGES, bool DUAL, bool SPLITK>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                     const GemmParams p) {
   using S = Gemm2Smem<TN, STAGES, DUAL, SPLITK>;
@@ -774,7 +790,7 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full_bar[b], 1);
-      mbar_init(&tmem_empty_bar[b], 256);       // epilogue threads of both CTAs (only the leader's copy is used)
+      mbar_init(&tmem_empty_bar[b], 2 * EPI_THREADS);       // epilogue threads of both CTAs (only the leader's copy is used)
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmap_w);
@@ -877,15 +893,19 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       }
     }
   } else {
-    // ------------------------------ epilogue (warps 2..5, both CTAs) ------------------------------
+    // ------------------------------ epilogue (warps 2..9, both CTAs) ------------------------------
     const int q = warp & 3;
     const int et = q * 32 + lane;
     const int tid_e = threadIdx.x - 64;
+    const int grp = tid_e >> 7;       // epilogue group: takes the chunks c with (c & 1) == grp
+    const int tid_g = tid_e & 127;
+    const int bar_id = 1 + grp;
     constexpr int CH = 32;
+    constexpr int NCH = TN / CH;      // TN >= 64 here: both groups always have chunks
     const bool vec_ok = (p.N % 8 == 0) && (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
                         (p.residual == nullptr ||
                          ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
-    int ui = 0, chunk_ctr = 0;
+    int ui = 0;
     for (int u = unit_begin; u < total_tiles; u += unit_step) {
       const int m0 = (u % num_m) * TN;                                   // all TN tokens: the accumulator is 128 x TN
       const int n0 = (u / num_m) * (2 * BM_W) + int(rank) * BM_W;
@@ -903,14 +923,14 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       const int n = n0 + et;
       float bias_v = 0.f;
       if (p.bias != nullptr && n < p.N) bias_v = __bfloat162float(p.bias[n]);
-      uint8_t* staging = smem + S::TILE_BYTES;
+      uint8_t* staging = smem + S::TILE_BYTES + grp * (STAGING_BYTES / 2);
 #pragma unroll 1
-      for (int c = 0; c < TN / CH; ++c, ++chunk_ctr) {
+      for (int c = grp; c < NCH; c += 2) {
         uint32_t r[CH], r2[CH];
         tmem_ld_32x32(lane_addr + c * CH, r);
         if (DUAL) tmem_ld_32x32(lane_addr + TN + c * CH, r2);
         tmem_ld_wait();
-        if (c == TN / CH - 1) {
+        if (c + 2 >= NCH) {
           tc_fence_before();
           mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty_bar[ab]), lead));   // hand the buffer back to the leader's MMA thread
         }
@@ -918,26 +938,27 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         if (p.out_f32) {
           float* stf = reinterpret_cast<float*>(staging);
 #pragma unroll
-          for (int j = 0; j < CH; ++j) {
-            stf[j * BM_W + et] = __uint_as_float(r[j]);
+          for (int hh = 0; hh < CH / 16; ++hh) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) stf[j * BM_W + et] = __uint_as_float(r[hh * 16 + j]);
+            asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+            for (int idx = tid_g; idx < 16 * 16; idx += 128) {
+              const int tok = idx >> 4, c8 = idx & 15;
+              const float4 lo = *reinterpret_cast<const float4*>(stf + tok * BM_W + c8 * 8);
+              const float4 hi = *reinterpret_cast<const float4*>(stf + tok * BM_W + c8 * 8 + 4);
+              float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+              emit8(p, m0 + c * CH + hh * 16 + tok, p.M, n0 + c8 * 8, v, vec_ok);
+            }
+            asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
           }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          for (int idx = tid_e; idx < CH * 16; idx += 128) {
-            const int tok = idx >> 4, c8 = idx & 15;
-            const float4 lo = *reinterpret_cast<const float4*>(stf + tok * BM_W + c8 * 8);
-            const float4 hi = *reinterpret_cast<const float4*>(stf + tok * BM_W + c8 * 8 + 4);
-            float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-            emit8(p, m0 + c * CH + tok, p.M, n0 + c8 * 8, v, vec_ok);
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
         } else {
-          __nv_bfloat16* stb = reinterpret_cast<__nv_bfloat16*>(staging + (chunk_ctr & 1) * (STAGING_BYTES / 2));
+          __nv_bfloat16* stb = reinterpret_cast<__nv_bfloat16*>(staging);
 #pragma unroll
           for (int j = 0; j < CH; ++j) {
             stb[j * BM_W + et] = __float2bfloat16(__uint_as_float(r[j]));
           }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          for (int idx = tid_e; idx < CH * 16; idx += 128) {
+          asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+          for (int idx = tid_g; idx < CH * 16; idx += 128) {
             const int tok = idx >> 4, c8 = idx & 15;
             const uint4 raw = *reinterpret_cast<const uint4*>(stb + tok * BM_W + c8 * 8);
             const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
@@ -946,11 +967,12 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             for (int e = 0; e < 4; ++e) { v[2 * e] = bf16_lo(w[e]); v[2 * e + 1] = bf16_hi(w[e]); }
             emit8(p, m0 + c * CH + tok, p.M, n0 + c8 * 8, v, vec_ok);
           }
+          asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
         }
       }
     }
     if (!SPLITK && p.rs_world > 0) {
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 3, 256;" ::: "memory");
       if (tid_e == 0) publish_to_peers(p.rs_local_count, p.rs_total, p.rs_peer_flag, p.rs_world);
     }
   }
@@ -966,7 +988,7 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       tc_fence_after();
       const int q = warp & 3;
       splitk_scatter<TN, 32, DUAL>(p, smem_u32(smem), tmem_base + (uint32_t(q * 32) << 16), q * 32 + lane, int(pidx), 2u,
-                                   uint32_t(rank));
+                                   uint32_t(rank), (int(threadIdx.x) - 64) >> 7);
     }
     tc_fence_before();
     cluster_sync_all();                       // all slots are written (release / acquire at cluster scope)
@@ -982,7 +1004,7 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                            ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
       splitk_finish<DUAL>(p, smem, TN, r0, r1, tid_e, m0, n0, vec_ok);
       if (p.rs_world > 0) {
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 3, 256;" ::: "memory");
         if (tid_e == 0) publish_to_peers(p.rs_local_count, p.rs_total, p.rs_peer_flag, p.rs_world);
       }
     }
@@ -1069,7 +1091,7 @@ static int max_active_clusters(int csize) {
   int n = 0;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL) == cudaSuccess) {
     cudaLaunchConfig_t cfg = {};
-    cfg.blockDim = dim3(192, 1, 1);
+    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
     cfg.gridDim = dim3(csize, 4096, 1);          // far more clusters than fit: the answer must not be capped by the grid
     cfg.dynamicSmemBytes = S::TOTAL;
     cudaLaunchAttribute attr[1];
@@ -1215,7 +1237,7 @@ static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmP
     attr_set[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(192, 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = S::TOTAL;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -1250,7 +1272,7 @@ static int launch_gemm_2cta(const CUtensorMap& tw, const CUtensorMap& tx, const 
     attr_set[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(192, 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
   cfg.gridDim = SPLITK ? dim3(2 * pl.splits, pl.tiles, 1) : dim3(pl.ctas, 1, 1);
   cfg.dynamicSmemBytes = S::TOTAL;
   cfg.stream = stream;
