@@ -453,6 +453,8 @@ def main(argv=None) -> int:
                        "workload": f"{B} concurrent requests: {PL}-token shared prefix + {SL} unique + {OL} greedy outputs, "
                                    "continuous batching in steady state",
                        "kv_block": bs, "prefix_cache": True, "cuda_graphs": not args.no_graphs,
+                       "symmetric_heap": (None if tp.comm is None else ("own" if tp.comm.heap is not None else "torch")),
+                       "nvswitch_multicast": (None if tp.comm is None else bool(tp.comm.multimem)),
                        "scheduling": "synchronous" if args.sync_scheduling else "host one step ahead of the device",
                        "l2": "inputs larger than L2: each step streams the model weights (>= 2 GB per GPU) from HBM",
                        "output_tokens_timed": tokens},
@@ -478,6 +480,10 @@ def main(argv=None) -> int:
             out["vs_library_baseline"] = value / library["value"]
         print(json.dumps(out))
     if world > 1:
+        # orderly teardown: every rank unbinds its memory from the multicast object before any rank frees its block
+        torch.cuda.synchronize()
+        if tp.comm is not None:
+            tp.comm.close()
         dist.destroy_process_group()
     return 0
 

@@ -202,7 +202,8 @@ __device__ __forceinline__ void emit8(const GemmParams& p, int m, int m_end, int
   }
   __nv_bfloat16* dst_base = p.out;
   long long row = m;
-  if (p.rs_world > 0) {
+  if (p.rs_world > 0 && p.rs_peer_out[0] != nullptr) {
+    // (with a null rs_peer_out the partial rows stay in `out`, which the consumers read through the multicast address)
     int owner = m / p.rs_rows_per_rank;
     if (owner >= p.rs_world) owner = p.rs_world - 1;
     dst_base = p.rs_peer_out[owner];

@@ -100,6 +100,14 @@ typedef struct UbNormArgs {
   /* F3 producer: a zeroed u32 in LOCAL memory on which the row CTAs arrive; the last one bumps every ag_peer_flag
      once (the consumer waits for one arrival per source rank).  Required when ag_world > 0. */
   uint32_t* ag_local_count;
+  /* NVSwitch multicast variants (addresses inside the multicast mapping of a symmetric heap, see csrc/comm/symm_heap.cu):
+     rs_multimem = 1: x is the MULTICAST address of this rank's rows inside a [world * T, H] buffer in which every rank
+     holds its own partial result at the same offset; the rows are read with multimem.ld_reduce (summed in the switch,
+     fp32 accumulation) instead of summing rs_world local slots.
+     ag_mc_out != NULL: the normalised row goes to row (ag_rank * T + t) of this multicast address with ONE multimem.st
+     (the switch replicates it to every rank) instead of ag_world peer stores; ag_peer_out is then unused. */
+  int rs_multimem;
+  void* ag_mc_out;
 } UbNormArgs;
 int ub_norm(const UbNormArgs* args, void* stream);
 
@@ -223,11 +231,12 @@ int ub_moe_combine(const void* y, const int* row_slot, const float* topk_w, cons
                    int K, int H, void* stream);
 /* F6: combine fused with the reduce-scatter: token t's partial row is stored into the receive slot
    peer_out[owner(t)][rank][t - owner*rows_per_rank]; the CTAs arrive on the zeroed LOCAL counter local_count and the
-   last one bumps every peer's counter once. */
+   last one bumps every peer's counter once.  With null peer_out entries the rows go to local_out[t] instead (this
+   rank's partial buffer inside a multicast-bound heap; the owners read them summed by the switch). */
 int ub_moe_combine_num_ctas(int T, int H);
 int ub_moe_combine_rs(const void* y, const int* row_slot, const float* topk_w, int T, int K, int H, int world, int rank,
                       int rows_per_rank, void* const* peer_out, uint32_t* const* peer_flag, uint32_t* local_count,
-                      void* stream);
+                      void* local_out, void* stream);
 
 /* ---------------- K12 : GGUF-quantised weights ---------------- */
 /* qtype is the ggml type id: 2 Q4_0, 3 Q4_1, 6 Q5_0, 8 Q8_0, 12 Q4_K, 14 Q6_K. */
@@ -290,6 +299,22 @@ int ub_tp_argmax_merge(const UbArgmaxMergeArgs* args, void* stream);
 int ub_wait_flag(const uint32_t* flag, uint32_t value, int* err, void* stream);
 /* Same for n (<= 32) consecutive counters, one thread each. */
 int ub_wait_flags(const uint32_t* flags, int n, uint32_t value, int* err, void* stream);
+
+/* ---------------- symmetric heap + multicast (csrc/comm/symm_heap.cu) ---------------- */
+const char* ub_symm_error(void);
+int ub_symm_supported(int dev, int* vmm, int* multicast);
+int ub_symm_round_size(unsigned long long bytes, int dev, int world, unsigned long long* out);
+int ub_symm_alloc(unsigned long long bytes, int dev, unsigned long long* handle, int* fd, void** va);
+int ub_symm_map_peer(int fd, unsigned long long bytes, int dev, unsigned long long* handle, void** va);
+int ub_symm_unmap(void* va, unsigned long long bytes, unsigned long long handle);
+int ub_symm_mc_create(unsigned long long bytes, int world, unsigned long long* mc, int* fd);
+int ub_symm_mc_import(int fd, unsigned long long* mc);
+int ub_symm_mc_add_device(unsigned long long mc, int dev);
+int ub_symm_mc_bind(unsigned long long mc, unsigned long long local_handle, unsigned long long bytes);
+int ub_symm_mc_map(unsigned long long mc, unsigned long long bytes, int dev, void** va);
+int ub_symm_mc_release(unsigned long long mc, void* mc_va, unsigned long long bytes, int dev);
+/* One copy kernel for bandwidth probes: kind 0 plain copy (peer mappings allowed), 1 multimem.st, 2 multimem.ld_reduce. */
+int ub_symm_probe(int kind, const void* src, void* dst, long long bytes, int ctas, void* stream);
 
 /* ---------------- device memory backend (kv/gpu_memory FFI surface) ---------------- */
 int ub_cuda_device_count(void);

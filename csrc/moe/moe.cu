@@ -178,8 +178,10 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* _
       for (int j = 0; j < 4; ++j) { acc[2 * j] += w * bf16_lo(vs[j]); acc[2 * j + 1] += w * bf16_hi(vs[j]); }
     }
     __nv_bfloat16* dst = out + (long long)t * H;
-    if (push.world > 0) {
+    if (push.world > 0 && push.peer_out[0] != nullptr) {
       // F6: the partial row goes straight into the receive slot of the rank that owns token t
+      // (with null peer pointers it stays in `out`, this rank's own partial buffer, which the owners read summed
+      // through the multicast address)
       int owner = t / push.rows_per_rank;
       if (owner >= push.world) owner = push.world - 1;
       dst = push.peer_out[owner] + ((long long)push.rank * push.rows_per_rank + (t - owner * push.rows_per_rank)) * H;
@@ -245,9 +247,10 @@ extern "C" int ub_moe_combine(const void* y, const int* row_slot, const float* t
 // F6: combine + reduce-scatter.  Every CTA (ub_moe_combine_num_ctas of them) signals every peer once.
 extern "C" int ub_moe_combine_rs(const void* y, const int* row_slot, const float* topk_w, int T, int K, int H, int world, int rank,
                                  int rows_per_rank, void* const* peer_out, uint32_t* const* peer_flag, uint32_t* local_count,
-                                 void* stream_v) {
+                                 void* local_out, void* stream_v) {
   if (T <= 0) return 0;
   if (H % 8 != 0 || world <= 0 || world > UB_MAX_RANKS || rows_per_rank <= 0 || local_count == nullptr) return -2;
+  if (peer_out[0] == nullptr && local_out == nullptr) return -3;
   ub::CombinePush push = {};
   push.world = world; push.rank = rank; push.rows_per_rank = rows_per_rank;
   push.local_count = local_count;
@@ -256,7 +259,8 @@ extern "C" int ub_moe_combine_rs(const void* y, const int* row_slot, const float
     push.peer_flag[i] = peer_flag[i];
   }
   ub::moe_combine_kernel<<<combine_blocks(T, H), 256, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
-      reinterpret_cast<const __nv_bfloat16*>(y), row_slot, topk_w, nullptr, nullptr, T, K, H, push);
+      reinterpret_cast<const __nv_bfloat16*>(y), row_slot, topk_w, nullptr, reinterpret_cast<__nv_bfloat16*>(local_out), T, K, H,
+      push);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }

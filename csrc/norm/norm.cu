@@ -36,7 +36,24 @@ struct NormParams {
   uint32_t* reset_flags;   // local counters that no kernel is using right now; zeroed by block 0 before it signals
   int reset_count;
   uint32_t* ag_local_count;   // local arrival counter of the row CTAs (see publish_to_peers)
+  int rs_multimem;            // x is a multicast address: rows are read with multimem.ld_reduce (sum over all ranks)
+  __nv_bfloat16* ag_mc_out;   // multicast address of the gather buffer: one multimem.st per 16 bytes instead of peer stores
 };
+
+// 8 bf16 values, each the sum (fp32 accumulation inside the switch) of the values at this offset on every rank
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+// 16 bytes to the same offset on every rank
+__device__ __forceinline__ void multimem_st_16(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
 
 __device__ __forceinline__ float block_sum(float v, float* red) {
   v = warp_sum(v);
@@ -88,7 +105,7 @@ __global__ void __launch_bounds__(256) norm_kernel(const NormParams p) {
     __syncthreads();
   }
 
-  const int nslots = p.rs_world > 0 ? p.rs_world : 1;
+  const int nslots = (p.rs_world > 0 && !p.rs_multimem) ? p.rs_world : 1;
   const long long slot_stride = (long long)p.T * H;
   float ssum = 0.f, ssq = 0.f;
   if (vec) {
@@ -96,7 +113,8 @@ __global__ void __launch_bounds__(256) norm_kernel(const NormParams p) {
       float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
       for (int s = 0; s < nslots; ++s) {
         // L2-only load: with rs_world > 0 these rows were written by peers and L1 may hold a stale line
-        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(p.x + s * slot_stride + (long long)t * H + c * 8));
+        const uint4 v = p.rs_multimem ? multimem_ld_reduce_bf16x8(p.x + (long long)t * H + c * 8)
+                                      : __ldcg(reinterpret_cast<const uint4*>(p.x + s * slot_stride + (long long)t * H + c * 8));
         const uint32_t* a = reinterpret_cast<const uint32_t*>(&v);
 #pragma unroll
         for (int e = 0; e < 4; ++e) { f[2 * e] += bf16_lo(a[e]); f[2 * e + 1] += bf16_hi(a[e]); }
@@ -177,8 +195,12 @@ __global__ void __launch_bounds__(256) norm_kernel(const NormParams p) {
       if (p.out != nullptr) *reinterpret_cast<uint4*>(p.out + (long long)t * H + c * 8) = ov;
       if (p.ag_world > 0) {
         const long long grow = (long long)p.ag_rank * p.T + t;
-        for (int r = 0; r < p.ag_world; ++r)
-          *reinterpret_cast<uint4*>(p.ag_peer_out[r] + grow * H + c * 8) = ov;
+        if (p.ag_mc_out != nullptr) {
+          multimem_st_16(p.ag_mc_out + grow * H + c * 8, ov);
+        } else {
+          for (int r = 0; r < p.ag_world; ++r)
+            *reinterpret_cast<uint4*>(p.ag_peer_out[r] + grow * H + c * 8) = ov;
+        }
       }
     }
   } else {
@@ -234,6 +256,9 @@ extern "C" int ub_norm(const UbNormArgs* a, void* stream_v) {
   p.reset_flags = a->reset_flags; p.reset_count = a->reset_count;
   p.ag_local_count = a->ag_local_count;
   if (p.ag_world > 0 && p.ag_local_count == nullptr) return -8;
+  p.rs_multimem = a->rs_multimem;
+  p.ag_mc_out = (__nv_bfloat16*)a->ag_mc_out;
+  if ((p.rs_multimem || p.ag_mc_out != nullptr) && a->H % 8 != 0) return -9;   // the multicast paths are 16-byte vector only
   for (int i = 0; i < UB_MAX_RANKS; ++i) {
     p.ag_peer_out[i] = (__nv_bfloat16*)a->ag_peer_out[i];
     p.ag_peer_flag[i] = a->ag_peer_flag[i];

@@ -59,6 +59,107 @@ __global__ void __launch_bounds__(256) qgemv_kernel(const uint8_t* __restrict__ 
   }
 }
 
+// Q4_K fast path.  One warp owns RPW consecutive output rows; a lane takes one 64-value group of a block at a time
+// (32 bytes of nibbles: the low nibbles are the group's first 32 values, the high nibbles its last 32), so the block
+// header is decoded once per 64 weights and the activations of the group are loaded once for all RPW rows.  With
+// v = d*s*q - dmin*m the dot product over a 32-value sub-block is d*s * sum(q x) - dmin*m * sum(x); sum(x) is shared
+// by the rows.  MT is the activation-row count rounded up to a power of two (rows >= M repeat the last one).
+template <int MT, int RPW>
+__global__ void __launch_bounds__(256) qgemv_q4k_kernel(const uint8_t* __restrict__ w, const __nv_bfloat16* __restrict__ x,
+                                                        __nv_bfloat16* __restrict__ out, int M, int N, int K) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = (blockIdx.x * 8 + warp) * RPW;
+  if (n0 >= N) return;
+  const int nb = K >> 8, groups = nb << 2;
+  float acc[RPW][MT];
+#pragma unroll
+  for (int r = 0; r < RPW; ++r)
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[r][m] = 0.f;
+  for (int grp = lane; grp < groups; grp += 32) {
+    const int b = grp >> 2, g = grp & 3;
+    uint4 qa[RPW], qb[RPW];
+    float ds0[RPW], ds1[RPW], dm0[RPW], dm1[RPW];
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+      const int n = min(n0 + r, N - 1);
+      const uint8_t* blk = w + ((long long)n * nb + b) * 144;
+      const uint4 h = __ldg(reinterpret_cast<const uint4*>(blk));
+      qa[r] = __ldg(reinterpret_cast<const uint4*>(blk + 16 + g * 32));
+      qb[r] = __ldg(reinterpret_cast<const uint4*>(blk + 32 + g * 32));
+      const uint8_t* hb = reinterpret_cast<const uint8_t*>(&h);
+      const float d = ubq_f16(hb), dmin = ubq_f16(hb + 2);
+      const uint8_t* sc = hb + 4;
+      int s[2], mn[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int j = 2 * g + e;
+        if (j < 4) { s[e] = sc[j] & 63; mn[e] = sc[j + 4] & 63; }
+        else { s[e] = (sc[j + 4] & 0x0F) | ((sc[j - 4] >> 6) << 4); mn[e] = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4); }
+      }
+      ds0[r] = d * (float)s[0]; ds1[r] = d * (float)s[1];
+      dm0[r] = dmin * (float)mn[0]; dm1[r] = dmin * (float)mn[1];
+    }
+    float sx0[MT], sx1[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) sx0[m] = sx1[m] = 0.f;
+    const long long xoff = (long long)b * 256 + g * 64;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      // bytes 8c..8c+7 of the group's nibbles: values 8c..8c+7 of the first half (low nibbles) and of the second half
+      float ql[RPW][8], qh[RPW][8];
+#pragma unroll
+      for (int r = 0; r < RPW; ++r) {
+        const uint32_t* qw = (c < 2) ? reinterpret_cast<const uint32_t*>(&qa[r]) + 2 * c
+                                     : reinterpret_cast<const uint32_t*>(&qb[r]) + 2 * (c - 2);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t byte = (qw[j >> 2] >> (8 * (j & 3))) & 0xFFu;
+          ql[r][j] = (float)(byte & 0xFu);
+          qh[r][j] = (float)(byte >> 4);
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        const long long row = (long long)min(m, M - 1) * K + xoff;
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(x + row + 8 * c));
+        const uint4 bq = __ldg(reinterpret_cast<const uint4*>(x + row + 32 + 8 * c));
+        const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&bq);
+        float x0[8], x1[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 fa = __bfloat1622float2(ap[j]), fb = __bfloat1622float2(bp[j]);
+          x0[2 * j] = fa.x; x0[2 * j + 1] = fa.y;
+          x1[2 * j] = fb.x; x1[2 * j + 1] = fb.y;
+          sx0[m] += fa.x + fa.y;
+          sx1[m] += fb.x + fb.y;
+        }
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) {
+          float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { d0 += ql[r][j] * x0[j]; d1 += qh[r][j] * x1[j]; }
+          acc[r][m] += ds0[r] * d0 + ds1[r] * d1;
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < RPW; ++r)
+#pragma unroll
+      for (int m = 0; m < MT; ++m) acc[r][m] -= dm0[r] * sx0[m] + dm1[r] * sx1[m];
+  }
+#pragma unroll
+  for (int r = 0; r < RPW; ++r)
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      float a = acc[r][m];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+      if (lane == 0 && m < M && n0 + r < N) out[(long long)m * N + n0 + r] = __float2bfloat16(a);
+    }
+}
+
 }  // namespace ub
 
 extern "C" int ub_dequant(const void* blocks, void* out_bf16, long long n_elems, int qtype, void* stream) {
@@ -84,6 +185,15 @@ extern "C" int ub_qgemv(const void* blocks, const void* x, void* out, int M, int
   const uint8_t* w = reinterpret_cast<const uint8_t*>(blocks);
   const __nv_bfloat16* xp = reinterpret_cast<const __nv_bfloat16*>(x);
   __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(out);
+  if (qtype == UBQ_Q4_K && K % 256 == 0 && (reinterpret_cast<uintptr_t>(blocks) & 15) == 0) {
+    // specialised kernel: header decoded once per 64 weights, activations shared by 2 / 4 rows
+    if (M == 1) ub::qgemv_q4k_kernel<1, 2><<<(N + 15) / 16, 256, 0, st>>>(w, xp, op, M, N, K);
+    else if (M == 2) ub::qgemv_q4k_kernel<2, 2><<<(N + 15) / 16, 256, 0, st>>>(w, xp, op, M, N, K);
+    else if (M <= 4) ub::qgemv_q4k_kernel<4, 4><<<(N + 31) / 32, 256, 0, st>>>(w, xp, op, M, N, K);
+    else ub::qgemv_q4k_kernel<8, 4><<<(N + 31) / 32, 256, 0, st>>>(w, xp, op, M, N, K);
+    cudaError_t e4 = cudaGetLastError();
+    return e4 == cudaSuccess ? 0 : -(int)e4;
+  }
   const int grid = (N + 7) / 8;
 #define UB_QGEMV(MM) ub::qgemv_kernel<MM><<<grid, 256, 0, st>>>(w, xp, op, N, K, qtype, be, bb)
   switch (M) {

@@ -122,6 +122,23 @@ prompts = [shared + torch.randint(0, 1024, (n,), generator=g).tolist() for n in 
 out = {}
 from unillm_b200.dist.fused import FusedComm
 comm = FusedComm.create(spec, rank, world, dist.group.WORLD, max_tokens=512, device=f"cuda:{rank}")
+out["heap"] = "own" if comm.heap is not None else "torch"
+out["multimem"] = bool(comm.multimem)
+# one fixed prefill step for the logit comparison: 3 sequences, 112 token rows (a multiple of the world size)
+from unillm_b200.engine.runner import StepBatch
+def logit_batch():
+    toks, pos, slots, lens, tables, qlens, rows = [], [], [], [], [], [], []
+    nxt = 1
+    gg = torch.Generator().manual_seed(5)
+    for n in (40, 24, 48):
+        p = torch.randint(0, 1024, (n,), generator=gg).tolist()
+        nb = n // 16 + 2
+        blocks = list(range(nxt, nxt + nb)); nxt += nb
+        for i, t in enumerate(p):
+            toks.append(t); pos.append(i); slots.append(blocks[i // 16] * 16 + i % 16)
+        lens.append(n); tables.append(blocks); qlens.append(n); rows.append(len(toks) - 1)
+    return StepBatch(toks, pos, slots, 0, lens, tables, qlens, rows)
+logits = {}
 for mode in ("tp1", "nccl", "fused", "fused_graph"):
     tpw = 1 if mode == "tp1" else world
     tp = TpContext(rank if tpw > 1 else 0, tpw, dist.group.WORLD if tpw > 1 else None, fused=mode.startswith("fused"))
@@ -135,7 +152,22 @@ for mode in ("tp1", "nccl", "fused", "fused_graph"):
     out[mode] = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=10))
     torch.cuda.synchronize()
     cuda_ops.check_device_errors()
+    if mode != "fused_graph":
+        lg = runner.logits_for(logit_batch()).float()
+        if tpw > 1:                                  # vocabulary shards -> full rows
+            parts = [torch.empty_like(lg) for _ in range(world)]
+            dist.all_gather(parts, lg.contiguous())
+            lg = torch.cat(parts, dim=-1)
+        logits[mode] = lg
+        torch.cuda.synchronize()
+        cuda_ops.check_device_errors()
+        assert runner.fused_steps > 0 or mode != "fused"
     dist.barrier()
+ref = logits["tp1"]
+scale = float(ref.abs().max())
+out["logit_err"] = {m: float((logits[m] - ref).abs().max()) / scale for m in ("nccl", "fused")}
+out["argmax_agree"] = {m: float((logits[m].argmax(-1) == ref.argmax(-1)).float().mean()) for m in ("nccl", "fused")}
+comm.close()
 if rank == 0:
     print("RESULT " + json.dumps(out))
 dist.destroy_process_group()
@@ -143,16 +175,21 @@ dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("heap", ["own", "own-peer-only", "torch"])
 @pytest.mark.parametrize("model", ["llama", "mixtral"])
-def test_tensor_parallel_engine_fused_matches_baseline(tmp_path, model):
-    """llama: tensor parallel 2.  mixtral: attention tensor parallel 2 + expert parallel 2 (two experts per rank)."""
+def test_tensor_parallel_engine_fused_matches_baseline(tmp_path, model, heap):
+    """llama: tensor parallel 2.  mixtral: attention tensor parallel 2 + expert parallel 2 (two experts per rank).
+    ``heap``: the library's symmetric heap with the NVSwitch multicast paths (multimem.ld_reduce / multimem.st) when the
+    GPUs have multicast, the same heap with plain peer stores only, or torch's symmetric memory."""
     import json
 
     script = tmp_path / "child.py"
     script.write_text(_CHILD)
-    env = dict(os.environ, REPO=os.path.dirname(os.path.dirname(os.path.abspath(__file__))), NCCL_NVLS_ENABLE="0", MODEL=model)
+    env = dict(os.environ, REPO=os.path.dirname(os.path.dirname(os.path.abspath(__file__))), NCCL_NVLS_ENABLE="0", MODEL=model,
+               UB_SYMM_HEAP="torch" if heap == "torch" else "own", UB_MULTIMEM="0" if heap == "own-peer-only" else "1")
+    port = 29731 + 10 * ["llama", "mixtral"].index(model) + ["own", "own-peer-only", "torch"].index(heap)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29731" if model == "llama" else "29741", str(script)]
+           "127.0.0.1", "--master-port", str(port), str(script)]
     p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
     line = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")][-1]
@@ -165,3 +202,31 @@ def test_tensor_parallel_engine_fused_matches_baseline(tmp_path, model):
     for mode in ("nccl", "fused", "fused_graph"):
         agree = sum(a == b for ra, rb in zip(out["tp1"], out[mode]) for a, b in zip(ra, rb))
         assert agree / total > 0.8, (mode, agree, total)
+    assert out["heap"] == ("torch" if heap == "torch" else "own")
+    if heap != "own":
+        assert not out["multimem"]
+    # logits of one prefill step, every vocabulary column, against the single-GPU run: bf16 activations with other
+    # summation orders (K split over the ranks, partial sums rounded to bf16 before the reduction)
+    for mode in ("nccl", "fused"):
+        assert out["logit_err"][mode] < 0.04, out["logit_err"]
+        assert out["argmax_agree"][mode] == 1.0 or out["logit_err"][mode] < 0.02, (out["argmax_agree"], out["logit_err"])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_symmetric_heap_peer_and_multicast_access(tmp_path):
+    """The library's own symmetric heap on 2 GPUs: a peer sees what its neighbour stored, a multicast store lands on
+    every rank and a multicast load returns the sum of the ranks' copies (the last two where the GPUs support
+    multicast); the probe also reports the copy bandwidths."""
+    import json
+
+    out_file = tmp_path / "links.json"
+    env = dict(os.environ, PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))), NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29769", "-m", "unillm_b200.dist.probe_links", "--mb", "16", "--json", str(out_file)]
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    res = json.loads(out_file.read_text())
+    assert res["all_ranks_ok"] and res["checks"]["peer_store"] and res["checks"]["peer_load"]
+    if res["multicast"]:
+        assert res["checks"]["multimem_st"] and res["checks"]["multimem_ld_reduce"]
+    assert all(v["peer_store"] > 1.0 for v in res["gbs"].values())

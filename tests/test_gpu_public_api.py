@@ -121,3 +121,51 @@ def test_pipeline_names_the_reason_when_a_model_stays_off_the_kernel_runner():
     m = BertModel.new(C.BertConfig(vocab_size=128, hidden_size=64, num_hidden_layers=1, num_attention_heads=2,
                                    intermediate_size=128))
     assert "not a decoder-only model" in why_not_gpu(m)
+
+
+def test_block_quantised_weights_serve_like_their_bf16_expansion(tmp_path):
+    """Q4_K projection weights kept as blocks on the device: decode rows go through the quantised GEMV kernel, prefill
+    rows through dequantise + tensor-core GEMM.  The reference run uses the bf16 expansion of the same blocks, so
+    only summation order differs."""
+    from unillm_b200.engine.llm_engine import LLMEngine
+    from unillm_b200.engine.runner import GpuModelRunner, QWeight, RunnerWeights
+    from unillm_b200.models import configs as C
+    from unillm_b200.models.families import LlamaModel
+    from unillm_b200.ops import cuda_ops
+    from unillm_b200.ops import quant as Q
+    from unillm_b200.sampling import SamplingParams
+    from unillm_b200.weights.gguf import Q4_K, dequantize_blocks, quantize_blocks
+
+    # kernel level: the specialised Q4_K GEMV against the dequantised matrix, every row count it serves
+    g = torch.Generator().manual_seed(0)
+    N_, Kd = 1000, 1024
+    wf = torch.randn(N_, Kd, generator=g) * 0.05
+    raw = quantize_blocks(wf, Q4_K)
+    wd = dequantize_blocks(raw, Q4_K, (N_, Kd))
+    blocks = torch.from_numpy(raw.copy()).cuda()
+    for M in (1, 2, 3, 5, 8):
+        x = torch.randn(M, Kd, generator=g).to(torch.bfloat16).cuda()
+        got = Q.qgemv_cuda(blocks, x, N_, Q4_K).float().cpu()
+        ref = x.float().cpu() @ wd.t()
+        assert (got - ref).abs().max().item() < 0.02 * max(1.0, ref.abs().max().item()), M
+
+    cfg = C.LlamaConfig(vocab_size=512, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                        num_attention_heads=4, num_key_value_heads=2, rms_norm_eps=1e-5, max_position_embeddings=1024)
+    m = LlamaModel.new(cfg, init="random", seed=9)
+    wq = RunnerWeights(m.spec, m.p, "cuda").quantize("q4_k")
+    assert isinstance(wq.t["layers.0.wqkv"], QWeight) and isinstance(wq.t["lm_head"], QWeight)
+    dense_bytes = RunnerWeights(m.spec, m.p, "cuda").nbytes()
+    assert wq.nbytes() < 0.5 * dense_bytes
+    wref = wq.dequantized_copy()
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (33, 5, 70)]
+    outs = {}
+    for name, w in (("q", wq), ("ref", wref)):
+        runner = GpuModelRunner(m.spec, w, num_blocks=64, max_num_seqs=4, max_num_batched_tokens=256, max_model_len=256,
+                                use_cuda_graphs=False)
+        eng = LLMEngine(runner, num_blocks=64, max_num_seqs=4, max_num_batched_tokens=256, max_model_len=256)
+        outs[name] = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+        torch.cuda.synchronize()
+        cuda_ops.check_device_errors()
+    total = sum(len(o) for o in outs["ref"])
+    same = sum(a == b for x, y in zip(outs["q"], outs["ref"]) for a, b in zip(x, y))
+    assert same >= 0.9 * total, (same, total)

@@ -213,6 +213,11 @@ def gpu_config(n: int, scale: float, env, fused: bool = True, health=None, warm:
         warmed = True
     cap0 = runner.captures
     res = serve(eng, reqs, device, group, world, health)
+    comm = runner.tp.comm
+    if comm is not None:
+        torch.cuda.synchronize()
+        res.update(symmetric_heap="own" if comm.heap is not None else "torch", nvswitch_multicast=bool(comm.multimem))
+        comm.close()
     res.update(extra, n_gpus=world, dtype="bf16",
                parallelism=f"tp{world}" + (f"+ep{world}" if w.ep else "") + ("" if fused or world == 1 else "-nccl-baseline"),
                graphs=len(runner.graphs), graph_captures_in_timed_run=runner.captures - cap0, warm_pass=warmed,

@@ -55,7 +55,7 @@ def cmd_generate(a) -> int:
     model = _load(a.model, "cpu" if cuda else a.device)
     b = InferencePipelineBuilder().model(model).use_engine(a.engine)
     if cuda:
-        b = b.device(a.device).engine_options(max_num_seqs=8, max_num_batched_tokens=2048)
+        b = b.device(a.device).engine_options(max_num_seqs=8, max_num_batched_tokens=2048, quantize=a.quantize)
     pipe = b.build()
     if cuda:
         if pipe.engine_note is None:
@@ -141,6 +141,8 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--seed", type=int, default=None)
     g.add_argument("--device", default="cpu")
     g.add_argument("--engine", action="store_true", help="run on the paged continuous-batching engine")
+    g.add_argument("--quantize", default=None, choices=["q4_k", "q8_0", "q4_0"],
+                   help="--device cuda: keep the projection weights block-quantised on the device")
     g.add_argument("--stream", action="store_true")
     g.set_defaults(fn=cmd_generate)
     m = sub.add_parser("models", help="list architectures and cached models")

@@ -1,7 +1,9 @@
 """Symmetric-memory plumbing for the fused tensor-parallel kernels.
 
 ``FusedComm`` owns, on every rank, one symmetric allocation (same layout on all ranks, mapped into
-every peer's address space through ``torch.distributed._symmetric_memory``) that holds
+every peer's address space by ``dist.symm_heap.SymmetricHeap`` -- the library's own heap over the CUDA
+virtual-memory API, with an NVSwitch multicast view where the GPUs have one -- or, as a fallback,
+through ``torch.distributed._symmetric_memory``) that holds
 
   * two reduce-scatter receive areas ``rs[k]``  : ``[world][rows_per_rank][H]`` bf16 -- slot ``[src]`` is
     written by rank ``src``'s GEMM epilogue (F1), read by the local norm kernel;
@@ -24,8 +26,9 @@ is ``TpContext.all_reduce`` (NCCL) in ``unillm_b200/engine/runner.py``.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
-from typing import List
+from typing import List, Optional
 
 import torch
 
@@ -46,10 +49,16 @@ class _Area:
 
 class FusedComm:
     def __init__(self, rank: int, world: int, hidden: int, max_tokens: int, buf: torch.Tensor, peer_ptrs: List[int],
-                 handle=None, group=None):
+                 handle=None, group=None, mc_ptr: int = 0):
         self.rank, self.world, self.H = rank, world, hidden
         self.max_rows = (max_tokens + world - 1) // world
         self.buf, self.peer_ptrs, self.handle, self.group = buf, peer_ptrs, handle, group
+        # address of the NVSwitch multicast view of the buffer (0: none).  With it the reduce-scatter becomes "every
+        # rank keeps its partial rows in its own buffer, the owner reads them summed by the switch" and the all-gather
+        # one multimem.st per 16 bytes instead of `world` peer stores.
+        self.mc_ptr = mc_ptr
+        self.multimem = bool(mc_ptr) and os.environ.get("UB_MULTIMEM", "1") != "0"
+        self.heap = None
         slot = world * self.max_rows * hidden * 2
         self.rs = [_Area(0, slot), _Area(slot, slot)]
         self.ag = [_Area(2 * slot, slot), _Area(3 * slot, slot)]
@@ -65,17 +74,48 @@ class FusedComm:
         return 4 * world * rows * hidden * 2 + FLAG_WORDS * 4 + 2 * (2 * world * ARGMAX_ROWS * 4)
 
     @classmethod
-    def create(cls, spec, rank: int, world: int, group, max_tokens: int, device) -> "FusedComm":
+    def create(cls, spec, rank: int, world: int, group, max_tokens: int, device, heap: Optional[str] = None) -> "FusedComm":
+        """``heap``: "own" (the library's symmetric heap, multicast when available), "torch"
+        (``torch.distributed._symmetric_memory``) or None = "own" with "torch" as the fallback when the own heap
+        cannot be set up on this box; ``UB_SYMM_HEAP`` overrides.  All ranks take the same branch."""
         import torch.distributed as dist
+
+        group = group if group is not None else dist.group.WORLD
+        heap = os.environ.get("UB_SYMM_HEAP") or heap
+        n = cls.nbytes(world, spec.hidden_size, max_tokens)
+        if heap != "torch":
+            from .symm_heap import SymmetricHeap
+
+            ok, err, h = 1, "", None
+            try:
+                mc = None if os.environ.get("UB_MULTIMEM", "1") != "0" else False
+                h = SymmetricHeap.create(n, rank, world, group, device, multicast=mc)
+            except Exception as e:      # noqa: BLE001 - every rank has to learn about it and fall back together
+                ok, err = 0, repr(e)[:200]
+            flag = torch.tensor([ok], dtype=torch.int32, device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+            if int(flag[0]) == 1:
+                c = cls(rank, world, spec.hidden_size, max_tokens, h.tensor()[:n], list(h.peer_ptrs), None, group, h.mc_ptr)
+                c.heap = h
+                return c
+            if heap == "own":
+                raise RuntimeError(f"own symmetric heap unavailable: {err or 'another rank failed'}")
+            if h is not None:
+                h._closed = True         # a partial set-up on this rank: leave it to process exit
         import torch.distributed._symmetric_memory as symm
 
-        n = cls.nbytes(world, spec.hidden_size, max_tokens)
         buf = symm.empty(n, dtype=torch.uint8, device=device)
-        h = symm.rendezvous(buf, group if group is not None else dist.group.WORLD)
+        hd = symm.rendezvous(buf, group)
         buf.zero_()
         torch.cuda.synchronize(device)
         dist.barrier(group)
-        return cls(rank, world, spec.hidden_size, max_tokens, buf, [int(p) for p in h.buffer_ptrs], h, group)
+        return cls(rank, world, spec.hidden_size, max_tokens, buf, [int(p) for p in hd.buffer_ptrs], hd, group)
+
+    def close(self) -> None:
+        """Collective: releases the own heap (multicast binding first); a no-op for the torch-backed buffer."""
+        if self.heap is not None:
+            self.heap.close()
+            self.heap = None
 
     @classmethod
     def emulated(cls, world: int, hidden: int, max_tokens: int, device) -> List["FusedComm"]:
@@ -111,16 +151,24 @@ class FusedComm:
     # ---- kernel argument dicts ----
     def gemm_rs(self, k: int, rows_per_rank: int) -> dict:
         """F1 producer arguments: push rows into rank ``owner``'s ``rs[k]`` slot of this rank."""
-        return {"world": self.world, "rank": self.rank, "rows_per_rank": rows_per_rank,
-                "peer_out": [self._peer(r, self.rs[k]) for r in range(self.world)],
+        # multicast mode: the partial rows stay in this rank's own rs[k] area (peer_out all null); the owners read them
+        # summed through the multicast address
+        outs = [0] * self.world if self.multimem else [self._peer(r, self.rs[k]) for r in range(self.world)]
+        return {"world": self.world, "rank": self.rank, "rows_per_rank": rows_per_rank, "peer_out": outs,
                 "peer_flag": [self.flag_ptr(r, RS0 if k == 0 else RS1) for r in range(self.world)],
-                "local_count": self.local_flag_ptr(LOCAL_RS0 if k == 0 else LOCAL_RS1)}
+                "local_count": self.local_flag_ptr(LOCAL_RS0 if k == 0 else LOCAL_RS1), "local_out": self.rs_local(k)}
 
-    def norm_rs(self, k: int, signals: int = 0) -> dict:
-        """F1 consumer arguments: wait for one arrival per source rank (``signals`` overrides the count), sum the
-        ``world`` slots of ``rs[k]``."""
-        return {"world": self.world, "flag": self.local_flag_ptr(RS0 if k == 0 else RS1),
-                "signals_per_use": signals or self.world}
+    def norm_rs(self, k: int, signals: int = 0, rows_per_rank: int = 0) -> dict:
+        """F1 consumer arguments: wait for one arrival per source rank (``signals`` overrides the count), then sum the
+        ``world`` slots of ``rs[k]`` -- or, in multicast mode, read this rank's ``rows_per_rank`` rows of the partial
+        buffer through the multicast address (the switch sums the ranks' copies)."""
+        d = {"world": self.world, "flag": self.local_flag_ptr(RS0 if k == 0 else RS1),
+             "signals_per_use": signals or self.world}
+        if self.multimem:
+            if rows_per_rank <= 0:
+                raise ValueError("multicast reduce-scatter needs rows_per_rank")
+            d["multimem_x"] = self.mc_ptr + self.rs[k].offset + self.rank * rows_per_rank * self.H * 2
+        return d
 
     def norm_ag(self, k: int) -> dict:
         """F3 producer arguments: push normalised rows into every rank's ``ag[k]`` and bump their counter for us."""
@@ -128,7 +176,8 @@ class FusedComm:
         return {"world": self.world, "rank": self.rank,
                 "peer_out": [self._peer(r, self.ag[k]) for r in range(self.world)],
                 "peer_flag": [self.flag_ptr(r, base + self.rank) for r in range(self.world)],
-                "local_count": self.local_flag_ptr(LOCAL_AG0 if k == 0 else LOCAL_AG1)}
+                "local_count": self.local_flag_ptr(LOCAL_AG0 if k == 0 else LOCAL_AG1),
+                "mc_out": (self.mc_ptr + self.ag[k].offset) if self.multimem else 0}
 
     def gemm_ag(self, k: int, rows_per_rank: int) -> dict:
         """F3 consumer arguments: the token rows of source rank ``s`` are ready when counter ``s`` shows its one arrival."""

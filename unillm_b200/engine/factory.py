@@ -57,8 +57,11 @@ def build_engine(model, *, device="cuda", max_num_seqs: int = 64, max_num_batche
                  max_model_len: Optional[int] = None, block_size: int = 16, num_blocks: Optional[int] = None,
                  gpu_memory_fraction: float = 0.9, enable_prefix_caching: bool = True, async_scheduling: bool = False,
                  use_cuda_graphs: bool = True, eos_token_id: Optional[int] = None, rank: int = 0, world: int = 1,
-                 tp=None):
+                 tp=None, quantize: Optional[str] = None):
     """An ``LLMEngine`` that runs ``model`` on the hand-written kernels of ``device``.
+
+    ``quantize`` ("q4_k", "q8_0", "q4_0"): keep the projection matrices block-quantised on the device (4.5 - 8.5 bits
+    per weight, see ``RunnerWeights.quantize``) instead of bf16.
 
     Raises ``UnsupportedOperation`` (with the reason) when the model cannot take that path; see ``why_not_gpu``."""
     from .llm_engine import LLMEngine
@@ -74,6 +77,8 @@ def build_engine(model, *, device="cuda", max_num_seqs: int = 64, max_num_batche
     if max_model_len is None:
         max_model_len = min(spec.max_position_embeddings, 8192)
     weights = RunnerWeights(spec, model.p, dev, rank, world)
+    if quantize:
+        weights.quantize(quantize)
     if num_blocks is None:
         num_blocks = _auto_num_blocks(spec, weights, block_size, dev, gpu_memory_fraction, max_model_len, max_num_seqs)
     runner = GpuModelRunner(spec, weights, num_blocks=num_blocks, block_size=block_size, max_num_seqs=max_num_seqs,

@@ -89,6 +89,23 @@ def shard_cols(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
     return w[:, rank * n:(rank + 1) * n]
 
 
+class QWeight:
+    """A projection weight kept block-quantised on the device (ggml block layout, rows independent): what the
+    reference keeps as ``QMatMul`` for ``*_proj`` / ``lm_head`` tensors of a GGUF checkpoint
+    (``crates/runtime/src/weight_loader_core.rs:554-584``, used at ``models_v2/llama.rs:1184-1195``)."""
+
+    __slots__ = ("blocks", "qtype", "shape")
+
+    def __init__(self, blocks: torch.Tensor, qtype: int, shape):
+        self.blocks, self.qtype, self.shape = blocks, qtype, tuple(shape)
+
+    def nbytes(self) -> int:
+        return self.blocks.numel()
+
+
+QUANT_NAMES = {"q4_0": 2, "q8_0": 8, "q4_k": 12}
+
+
 class RunnerWeights:
     """Device weights of one rank in kernel layout (bf16, fused QKV / gate-up, TP-sharded)."""
 
@@ -276,9 +293,48 @@ class RunnerWeights:
                 self.t[L + "w_down"] = rnd(H, I, 0, H, rank * Is, Is)
         return self
 
+    def quantize(self, qtype="q4_k") -> "RunnerWeights":
+        """Re-encodes every projection matrix (QKV, attention output, MLP, ``lm_head``; not embeddings, norms, routers
+        or expert stacks) as ggml blocks of ``qtype`` on the device and drops the bf16 copy.  Decode-sized GEMMs
+        (<= 8 token rows) then stream the blocks through the quantised GEMV kernel; larger ones expand the matrix into
+        a scratch buffer first and run the tensor-core GEMM.  Rows are quantised independently along K, so sharded
+        and fused matrices quantise like their parts.  Returns self."""
+        from ..weights.gguf import BLOCK, quantize_blocks
+
+        qt = QUANT_NAMES[qtype] if isinstance(qtype, str) else int(qtype)
+        be = BLOCK[qt][0]
+        tied = self.t.get("lm_head") is self.t.get("embed")
+        for name, w in list(self.t.items()):
+            leaf = name.rsplit(".", 1)[-1]
+            if leaf not in ("wqkv", "wo", "w_gate_up", "w_up", "w_down", "lm_head") or isinstance(w, QWeight):
+                continue
+            if w.dim() != 2 or w.shape[1] % be or w.shape[1] % 8:
+                continue                     # K is not a whole number of blocks: this matrix stays bf16
+            if name == "lm_head" and tied:
+                w = w.clone()                # the embedding keeps its bf16 table
+            raw = quantize_blocks(w.float().cpu(), qt)
+            self.t[name] = QWeight(torch.from_numpy(raw.copy()).to(w.device), qt, w.shape)
+        self.quantized = qtype if isinstance(qtype, str) else str(qt)
+        return self
+
+    def dequantized_copy(self) -> "RunnerWeights":
+        """The same weights with every quantised matrix expanded to bf16 (the values the quantised kernels compute
+        with): the reference run for accuracy checks of the quantised path."""
+        import copy
+
+        from ..ops.quant import dequantize_cuda
+
+        o = copy.copy(self)
+        o.t = {k: (dequantize_cuda(v.blocks, v.qtype, v.shape) if isinstance(v, QWeight) else v) for k, v in self.t.items()}
+        o.quantized = None
+        return o
+
     def nbytes(self) -> int:
         seen, n = set(), 0
         for t in self.t.values():
+            if isinstance(t, QWeight):
+                n += t.nbytes()
+                continue
             if t.data_ptr() not in seen:
                 seen.add(t.data_ptr())
                 n += t.numel() * t.element_size()
@@ -478,6 +534,10 @@ class GpuModelRunner:
         self._handle = None
         self.attn_scratch = torch.empty(max_num_seqs * weights.hq * 16 * (D + 2), dtype=torch.float32, device=dev)
         self.prefix_scratch = None     # workspace of the key-split shared-prefix pass, allocated on first use
+        self._deq_scratch = None       # bf16 expansion of one quantised matrix at a time (quantised weights, > 8 rows)
+        if getattr(weights, "quantized", None):
+            big = max((int(v.shape[0]) * int(v.shape[1]) for v in weights.t.values() if isinstance(v, QWeight)), default=0)
+            self._deq_scratch = torch.empty(big, dtype=torch.bfloat16, device=dev) if big else None
         self.overlap_suffix = os.environ.get("UB_ATTN_OVERLAP", "1") != "0"
         self._side = None
         self.graphs: Dict[tuple, tuple] = {}
@@ -563,7 +623,46 @@ class GpuModelRunner:
     def _gemm(self, x, w, tag="gemm", **kw):
         self.launches += 1
         with self._prof(f"{tag}[{x.shape[0]}x{w.shape[0]}x{w.shape[1]}]"):
+            if isinstance(w, QWeight):
+                return self._qgemm(x, w, **kw)
             return K.gemm_tn(x, w, **kw)
+
+    def _qgemm(self, x, w: "QWeight", **kw):
+        """GEMM against a block-quantised matrix.  Up to 8 token rows: the quantised GEMV kernel (the weight stream is
+        4.5 - 8.5 bits per value) followed by the small epilogue kernels; more rows, or a fused collective: the matrix
+        is expanded into the runner's scratch buffer and the tensor-core GEMM runs on that."""
+        from ..ops import quant as Q
+
+        M = x.shape[0]
+        N_, Kd = w.shape
+        plain = kw.get("rs") is None and kw.get("ag") is None and kw.get("out") is None
+        if M <= 8 and plain and x.is_contiguous():
+            y = Q.qgemv_cuda(w.blocks, x, N_, w.qtype)
+            self.launches += 1
+            dual = kw.get("dual_rows", 0)
+            scale = kw.get("out_scale", 1.0)
+            if dual:
+                y = K.act_mul(y, kw.get("act") or "silu")
+            else:
+                if kw.get("bias") is not None or scale != 1.0:
+                    yf = y.float() * scale
+                    if kw.get("bias") is not None:
+                        yf = yf + kw["bias"].float()
+                    y = yf.to(torch.bfloat16)
+                if kw.get("act"):
+                    y = K.eltwise(y, kw["act"])
+            if kw.get("residual") is not None:
+                y = K.add(y, kw["residual"])
+            if kw.get("out_dtype", torch.bfloat16) == torch.float32:
+                y = y.float()
+            return y
+        need = N_ * Kd
+        if self._deq_scratch is None or self._deq_scratch.numel() < need:
+            self._deq_scratch = torch.empty(need, dtype=torch.bfloat16, device=self.device)
+        dense = self._deq_scratch[:need].view(N_, Kd)
+        Q.dequantize_cuda_into(w.blocks, w.qtype, dense)
+        self.launches += 1
+        return K.gemm_tn(x, dense, **kw)
 
     def _attention(self, i, qkv, lay, shared_prefix_len):
         """qkv [T, (hq + 2 hkv) * D] already rotated and appended -> attention output [T, hq * D]."""
@@ -826,7 +925,7 @@ class GpuModelRunner:
             with self._prof("norm_rs_ag"):
                 _, xr = K.norm(rs0_out, t[L + "ln2.w"], bias=t.get(L + "ln2.b"), residual=xr, eps=s.norm_eps, kind=kind,
                                weight_offset_one=s.norm_weight_offset_one, want_residual_out=True, no_out=True, T=R,
-                               rs=c.norm_rs(0), ag=c.norm_ag(1), reset=c.reset_after_ag(1))
+                               rs=c.norm_rs(0, rows_per_rank=R), ag=c.norm_ag(1), reset=c.reset_after_ag(1))
             self.launches += 1
             h2 = c.ag_local_tensor(1, T)
             if s.layer_is_moe(i):
@@ -850,7 +949,7 @@ class GpuModelRunner:
             with self._prof("norm_rs_ag"):
                 _, xr = K.norm(rs1_out, t[nname + ".w"], bias=t.get(nname + ".b"), residual=xr, eps=s.norm_eps, kind=kind,
                                weight_offset_one=s.norm_weight_offset_one, want_residual_out=True, no_out=True, T=R,
-                               rs=c.norm_rs(1), ag=c.norm_ag(0), reset=c.reset_after_ag(0))
+                               rs=c.norm_rs(1, rows_per_rank=R), ag=c.norm_ag(0), reset=c.reset_after_ag(0))
             self.launches += 1
             h_full = c.ag_local_tensor(0, T)
             ag_args = c.gemm_ag(0, R)

@@ -55,7 +55,7 @@ class UbNormArgs(C.Structure):
         ("rs_world", i32), ("rs_flag", vp), ("epoch", vp), ("rs_signals_per_use", u32),
         ("ag_world", i32), ("ag_rank", i32),
         ("ag_peer_out", vp * UB_MAX_RANKS), ("ag_peer_flag", vp * UB_MAX_RANKS),
-        ("reset_flags", vp), ("reset_count", i32), ("ag_local_count", vp),
+        ("reset_flags", vp), ("reset_count", i32), ("ag_local_count", vp), ("rs_multimem", i32), ("ag_mc_out", vp),
     ]
 
 

@@ -183,6 +183,8 @@ def norm(x: torch.Tensor, weight: Optional[torch.Tensor], *, bias: Optional[torc
     a.weight_offset_one = 1 if weight_offset_one else 0
     if rs is not None:
         a.rs_world, a.rs_flag, a.rs_signals_per_use = rs["world"], rs["flag"], rs["signals_per_use"]
+        if rs.get("multimem_x"):
+            a.x, a.rs_multimem = rs["multimem_x"], 1       # multicast address of this rank's rows of the partial buffer
     if reset is not None:
         a.reset_flags, a.reset_count = reset
     if ag is not None:
@@ -191,6 +193,7 @@ def norm(x: torch.Tensor, weight: Optional[torch.Tensor], *, bias: Optional[torc
             a.ag_peer_out[i] = ag["peer_out"][i]
             a.ag_peer_flag[i] = ag["peer_flag"][i]
         a.ag_local_count = ag["local_count"]
+        a.ag_mc_out = ag.get("mc_out") or None
     N.check(N.cuda_lib().ub_norm(C.byref(a), _stream(x)), "ub_norm")
     if residual_out is not None:
         return out, residual_out
@@ -576,14 +579,14 @@ def moe_combine_rs(y: torch.Tensor, r: MoeRouting, rs: dict) -> None:
     _bf16c(y, "y")
     H = y.shape[1]
     W = rs["world"]
-    outs = (C.c_void_p * W)(*[int(p) for p in rs["peer_out"][:W]])
+    outs = (C.c_void_p * W)(*[(int(p) or None) for p in rs["peer_out"][:W]])
     flags = (C.c_void_p * W)(*[int(p) for p in rs["peer_flag"][:W]])
     lib = N.cuda_lib()
     lib.ub_moe_combine_rs.restype = C.c_int
-    lib.ub_moe_combine_rs.argtypes = [N.vp, N.vp, N.vp, N.i32, N.i32, N.i32, N.i32, N.i32, N.i32, N.vp, N.vp, N.vp, N.vp]
+    lib.ub_moe_combine_rs.argtypes = [N.vp, N.vp, N.vp, N.i32, N.i32, N.i32, N.i32, N.i32, N.i32, N.vp, N.vp, N.vp, N.vp, N.vp]
     N.check(lib.ub_moe_combine_rs(y.data_ptr(), r.row_slot.data_ptr(), r.topk_w.data_ptr(), r.T, r.K, H, W, rs["rank"],
                                   rs["rows_per_rank"], C.cast(outs, C.c_void_p), C.cast(flags, C.c_void_p),
-                                  rs["local_count"], _stream(y)),
+                                  rs["local_count"], rs.get("local_out") or None, _stream(y)),
             "ub_moe_combine_rs")
 
 

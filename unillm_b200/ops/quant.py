@@ -194,6 +194,18 @@ def dequantize_cuda(blocks_dev: torch.Tensor, qtype: int, shape) -> torch.Tensor
     return out.view(*shape)
 
 
+def dequantize_cuda_into(blocks_dev: torch.Tensor, qtype: int, out: torch.Tensor) -> torch.Tensor:
+    """Expands raw blocks into the given contiguous bf16 tensor (no allocation: usable inside a captured graph)."""
+    n = out.numel()
+    _check(qtype, n)
+    if out.dtype != torch.bfloat16 or not out.is_contiguous():
+        raise ValueError("out must be a contiguous bfloat16 tensor")
+    lib, N = _cuda()
+    N.check(lib.ub_dequant(blocks_dev.data_ptr(), out.data_ptr(), n, qtype,
+                           torch.cuda.current_stream(blocks_dev.device).cuda_stream), "ub_dequant")
+    return out
+
+
 def qgemv_cuda(blocks_dev: torch.Tensor, x: torch.Tensor, N_: int, qtype: int) -> torch.Tensor:
     """``x`` bf16 [M <= 8, K] times the quantised [N, K] matrix -> bf16 [M, N]."""
     x = x.contiguous()

@@ -200,7 +200,8 @@ def dequantize_blocks(data, qtype: int, shape: Sequence[int]) -> torch.Tensor:
 
 
 def quantize_blocks(x: torch.Tensor, qtype: int) -> np.ndarray:
-    """float tensor -> raw block bytes (Q4_0, Q8_0, F16, F32, BF16): used to write test files and to re-quantise."""
+    """float tensor -> raw block bytes (Q4_0, Q8_0, Q4_K, F16, F32, BF16): used to write test files and to quantise
+    weights for the block-quantised serving mode."""
     a = x.detach().float().cpu().numpy().reshape(-1)
     if qtype == F32:
         return a.astype(np.float32).view(np.uint8)
@@ -228,6 +229,36 @@ def quantize_blocks(x: torch.Tensor, qtype: int) -> np.ndarray:
         out = np.empty((nb, 18), dtype=np.uint8)
         out[:, 0:2] = d.astype(np.float16).view(np.uint8).reshape(nb, 2)
         out[:, 2:] = q[:, :16] | (q[:, 16:] << 4)
+        return out.reshape(-1)
+    if qtype == Q4_K:
+        if a.size % 256:
+            raise LoadingError("Q4_K quantisation needs a multiple of 256 elements")
+        nb = a.size // 256
+        b = a.reshape(nb, 8, 32)
+        # per 32-value sub-block: value = scale * q - min with q in 0..15 (min >= 0 as ggml stores it)
+        lo = np.minimum(b.min(axis=2), 0.0)
+        hi = b.max(axis=2)
+        sub_scale = (hi - lo) / 15.0
+        sub_min = -lo
+        d = sub_scale.max(axis=1, keepdims=True) / 63.0
+        dmin = sub_min.max(axis=1, keepdims=True) / 63.0
+        d16, dmin16 = d.astype(np.float16), dmin.astype(np.float16)
+        df, dminf = d16.astype(np.float32), dmin16.astype(np.float32)
+        sc = np.where(df > 0, np.rint(sub_scale / np.where(df > 0, df, 1)), 0).clip(0, 63).astype(np.uint8)
+        mn = np.where(dminf > 0, np.rint(sub_min / np.where(dminf > 0, dminf, 1)), 0).clip(0, 63).astype(np.uint8)
+        eff_s = df * sc.astype(np.float32)
+        eff_m = dminf * mn.astype(np.float32)
+        q = np.where(eff_s[..., None] > 0, np.rint((b + eff_m[..., None]) / np.where(eff_s[..., None] > 0, eff_s[..., None], 1)), 0)
+        q = q.clip(0, 15).astype(np.uint8)
+        out = np.zeros((nb, 144), dtype=np.uint8)
+        out[:, 0:2] = d16.view(np.uint8).reshape(nb, 2)
+        out[:, 2:4] = dmin16.view(np.uint8).reshape(nb, 2)
+        for j in range(4):                       # 6-bit scales / mins packed as ggml's get_scale_min_k4 reads them
+            out[:, 4 + j] = (sc[:, j] & 63) | ((sc[:, j + 4] >> 4) << 6)
+            out[:, 8 + j] = (mn[:, j] & 63) | ((mn[:, j + 4] >> 4) << 6)
+            out[:, 12 + j] = (sc[:, j + 4] & 0x0F) | ((mn[:, j + 4] & 0x0F) << 4)
+        for g in range(4):                       # 64 values per group: low nibbles = first 32, high nibbles = next 32
+            out[:, 16 + g * 32:16 + (g + 1) * 32] = q[:, 2 * g] | (q[:, 2 * g + 1] << 4)
         return out.reshape(-1)
     raise LoadingError(f"quantisation to ggml type {qtype} is not implemented")
 
