@@ -279,6 +279,7 @@ def main(argv=None) -> int:
                                 use_cuda_graphs=not args.no_graphs)
         eng = LLMEngine(runner, num_blocks=num_blocks, block_size=bs, max_num_seqs=B, max_num_batched_tokens=8192,
                         max_model_len=max_len, enable_prefix_caching=True, async_scheduling=not args.sync_scheduling)
+        eng.max_device_errors = 0        # a step that reports a device error ends the run (or sends it to the fallback path)
 
         g = torch.Generator().manual_seed(2024)
         prefix = torch.randint(0, V, (PL,), generator=g).tolist()

@@ -1,46 +1,60 @@
-// C1 helpers: small-message one-shot all-reduce over NVSwitch peer memory.
+// C1 helpers: small-message one-shot all-reduce over NVSwitch peer memory (F1s).
 //
-// Every rank stores its vector into slot [rank] of every peer's symmetric receive buffer with
-// plain 16-byte peer stores, publishes with a release-add on the peer's counter, then waits
-// (bounded) until its own counter shows that all `world` ranks have arrived and sums the slots in
-// rank order (bitwise identical on every rank).  Latency-optimal for messages up to a few hundred
-// KB (each rank sends (world-1) * n bytes); larger tensors go through the GEMM-fused
-// reduce-scatter / all-gather path.  Counters are monotonic; the expected value is
-// epoch * world * gridDim.x, with the epoch read from a device word so the launch can live in a
-// CUDA graph.  The reference has no collective of any kind.
+// Every rank stores its vector into slot [parity][rank] of every peer's symmetric receive buffer with plain
+// 16-byte peer stores, then tells the peers, then waits (bounded) until all `world` ranks' data for this exchange
+// has arrived and sums the slots in rank order (bitwise identical on every rank).  Latency-optimal for messages up
+// to a few hundred KB (each rank sends (world-1) * n bytes); larger tensors go through the GEMM-fused
+// reduce-scatter / all-gather path.
+//
+// The vector is cut into one chunk per CTA (the same cut on every rank, the grid depends on n only); CTA c pushes
+// chunk c, bumps counter [c] on every peer and waits for its own counter [c] to show `world` more arrivals, so a
+// chunk is reduced as soon as ITS pieces are there and the remote atomics spread over up to 64 addresses.
+// Counters are monotonic: exchange number e (kept in a local device word that the last CTA to finish advances, so
+// the launch can sit in a CUDA graph) expects e * world on each.  Slots alternate by the parity of e: a fast rank
+// may start exchange e + 1 while a slow one still sums exchange e, but it cannot reach e + 2 before the slow rank
+// has pushed e + 1, which that rank does only after it has finished reading e.
+// The reference has no collective of any kind.
 #include "../common/ptx.cuh"
 #include "../include/unillm_b200.h"
 
 namespace ub {
 
 __global__ void __launch_bounds__(256) allreduce_oneshot_kernel(const UbAllReduceArgs a) {
-  const long long nv = a.n / 8;  // n must be a multiple of 8 (checked on the host)
-  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long nv = a.n / 8;  // n is a multiple of 8 (checked on the host)
+  const long long per = (nv + gridDim.x - 1) / gridDim.x;
+  const long long c0 = (long long)blockIdx.x * per, c1 = min(nv, c0 + per);
+  __shared__ uint32_t round_s;
+  __shared__ int failed;
+  if (threadIdx.x == 0) {
+    round_s = *a.round + 1;       // the word is advanced by the last CTA of this launch, after everyone has read it
+    failed = 0;
+  }
+  __syncthreads();
+  const uint32_t round = round_s;
+  const long long slot = (long long)(round & 1u) * a.world * a.n;
   const __nv_bfloat16* in = reinterpret_cast<const __nv_bfloat16*>(a.in);
-  // 1. push
-  for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < nv; c += stride) {
+  // 1. push this CTA's chunk into every rank's slot [parity][rank]
+  for (long long c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
     const uint4 v = *reinterpret_cast<const uint4*>(in + c * 8);
     for (int r = 0; r < a.world; ++r) {
-      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.peer_slots[r]) + (long long)a.rank * a.n + c * 8;
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.peer_slots[r]) + slot + (long long)a.rank * a.n + c * 8;
       *reinterpret_cast<uint4*>(dst) = v;
     }
   }
-  __threadfence_system();
   __syncthreads();
-  if (threadIdx.x < a.world)
-    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(a.peer_flags[threadIdx.x]), "r"(1u) : "memory");
-  // 2. wait for all ranks' CTAs
-  __shared__ int failed;
   if (threadIdx.x == 0) {
-    failed = 0;
-    const uint32_t want = (*a.epoch) * (uint32_t)a.world * gridDim.x;
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
+    for (int r = 0; r < a.world; ++r)
+      asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(a.peer_flags[r] + blockIdx.x), "r"(1u) : "memory");
+    // 2. wait for the same chunk of all ranks
+    const uint32_t want = round * (uint32_t)a.world;
     const uint64_t t0 = globaltimer_ns();
     uint32_t it = 0, v;
     while (true) {
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a.my_flag) : "memory");
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a.my_flags + blockIdx.x) : "memory");
       if (int32_t(v - want) >= 0) break;
-      if ((++it & 31u) == 0 && (globaltimer_ns() - t0 > UB_WAIT_NS)) {
-        set_err(a.err, ERR_FLAG_TIMEOUT, 3000);
+      if ((++it & 31u) == 0 && wait_expired(t0, a.err)) {
+        set_err(a.err, ERR_FLAG_TIMEOUT, 3000 + blockIdx.x);
         failed = 1;
         break;
       }
@@ -48,9 +62,9 @@ __global__ void __launch_bounds__(256) allreduce_oneshot_kernel(const UbAllReduc
   }
   __syncthreads();
   // 3. reduce in rank order
-  const __nv_bfloat16* slots = reinterpret_cast<const __nv_bfloat16*>(a.my_slots);
+  const __nv_bfloat16* slots = reinterpret_cast<const __nv_bfloat16*>(a.my_slots) + slot;
   __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.out);
-  for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < nv; c += stride) {
+  for (long long c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
     float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int r = 0; r < a.world; ++r) {
       const uint4 v = __ldcg(reinterpret_cast<const uint4*>(slots + (long long)r * a.n + c * 8));  // L2 only: peers wrote it
@@ -63,18 +77,30 @@ __global__ void __launch_bounds__(256) allreduce_oneshot_kernel(const UbAllReduc
     for (int e = 0; e < 4; ++e) o[e] = pack_bf16x2(f[2 * e], f[2 * e + 1]);
     *reinterpret_cast<uint4*>(out + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
   }
+  // 4. the last CTA to get here advances the exchange number for the next launch
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t old = atomicAdd(a.done_count, 1u);
+    if (old + 1 == gridDim.x) {
+      *a.done_count = 0u;
+      *a.round = round;
+    }
+  }
 }
 
 }  // namespace ub
 
+extern "C" int ub_allreduce_oneshot_ctas(long long n) {
+  // The grid must be co-resident (CTAs of different ranks wait on one another): stay well under one wave.
+  long long g = (n / 8 + 1023) / 1024;       // at least 16 KB per CTA
+  if (g > UB_AR_MAX_CTAS) g = UB_AR_MAX_CTAS;
+  return g < 1 ? 1 : (int)g;
+}
+
 extern "C" int ub_allreduce_oneshot(const UbAllReduceArgs* a, void* stream_v) {
   if (a->n <= 0) return 0;
-  if (a->n % 8 != 0 || a->world < 1 || a->world > UB_MAX_RANKS) return -2;
-  // The grid must be co-resident (CTAs of different ranks wait on one another): stay well under one wave.
-  long long g = (a->n / 8 + 255) / 256;
-  if (g > 64) g = 64;
-  if (g < 1) g = 1;
-  ub::allreduce_oneshot_kernel<<<(unsigned)g, 256, 0, (cudaStream_t)stream_v>>>(*a);
+  if (a->n % 8 != 0 || a->world < 1 || a->world > UB_MAX_RANKS || a->round == nullptr || a->done_count == nullptr) return -2;
+  ub::allreduce_oneshot_kernel<<<(unsigned)ub_allreduce_oneshot_ctas(a->n), 256, 0, (cudaStream_t)stream_v>>>(*a);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }
@@ -121,7 +147,7 @@ __global__ void __launch_bounds__(256) tp_argmax_merge_kernel(const UbArgmaxMerg
     while (true) {
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a.my_flag) : "memory");
       if (int32_t(v - want) >= 0) break;
-      if ((++it & 31u) == 0 && (globaltimer_ns() - t0 > UB_WAIT_NS)) {
+      if ((++it & 31u) == 0 && wait_expired(t0, a.err)) {
         set_err(a.err, ERR_FLAG_TIMEOUT, 4000);
         failed = 1;
         break;

@@ -94,6 +94,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 #ifndef UB_WAIT_NS
 #define UB_WAIT_NS 1500000000ull  // 1.5 s
 #endif
+// True when a bounded wait that started at t0 should give up: its deadline has passed, or an error is already
+// recorded in the device error word (by an earlier kernel of the step or another CTA) -- then nothing this launch
+// produces will be used, and sitting out one more deadline per wait would only make a broken step take minutes.
+__device__ __forceinline__ bool wait_expired(uint64_t t0, const int* err) {
+  if (err != nullptr && *reinterpret_cast<const volatile int*>(err) != 0) return true;
+  return globaltimer_ns() - t0 > UB_WAIT_NS;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err,
                                           int detail) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -104,7 +111,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     if (mbar_try_wait(bar, parity)) return true;
     if ((++it & 63u) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > UB_WAIT_NS) break;
+      if (wait_expired(t0, err)) break;
     }
   }
   *abort_flag = 1;

@@ -437,7 +437,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             if (ag_ready >> r & 1u) continue;
             uint32_t spin = 0;
             while (int32_t(ld_acquire_sys_u32(p.ag_flags + r) - want) < 0) {
-              if ((++spin & 31u) == 0 && (globaltimer_ns() - t0 > UB_WAIT_NS)) {
+              if ((++spin & 31u) == 0 && wait_expired(t0, p.err)) {
                 *abort_flag = 1;
                 set_err(p.err, ERR_FLAG_TIMEOUT, r);
                 break;
@@ -828,7 +828,7 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             if (ag_ready >> r & 1u) continue;
             uint32_t spin = 0;
             while (int32_t(ld_acquire_sys_u32(p.ag_flags + r) - want) < 0) {
-              if ((++spin & 31u) == 0 && (globaltimer_ns() - t0 > UB_WAIT_NS)) {
+              if ((++spin & 31u) == 0 && wait_expired(t0, p.err)) {
                 *abort_flag = 1;
                 set_err(p.err, ERR_FLAG_TIMEOUT, r);
                 break;

@@ -265,19 +265,23 @@ int ub_wkv6(const void* r, const void* k, const void* v, const float* w, const f
 
 /* ---------------- comm helpers ---------------- */
 int ub_bump_epoch(uint32_t* epoch, void* stream);
-/* One-shot all-reduce for tiny messages: every rank pushes its vector into each peer's slot, then sums. */
+/* One-shot all-reduce for small messages: every rank pushes its vector into each peer's slot, then sums.  May run in
+   place (out == in). */
+#define UB_AR_MAX_CTAS 64
 typedef struct UbAllReduceArgs {
   const void* in;           /* bf16 [n] local */
   void* out;                /* bf16 [n] */
-  void* peer_slots[UB_MAX_RANKS];     /* each: [world][n] bf16 on that peer */
-  uint32_t* peer_flags[UB_MAX_RANKS]; /* peer's counter */
-  const void* my_slots;     /* local [world][n] */
-  const uint32_t* my_flag;
-  const uint32_t* epoch;
+  void* peer_slots[UB_MAX_RANKS];     /* each: [2][world][n] bf16 on that peer (two slot sets, by exchange parity) */
+  uint32_t* peer_flags[UB_MAX_RANKS]; /* each: UB_AR_MAX_CTAS counters on that peer (one per CTA index) */
+  const void* my_slots;     /* local [2][world][n] */
+  const uint32_t* my_flags; /* local counters */
+  uint32_t* round;          /* local device word: number of exchanges completed (advanced by the kernel) */
+  uint32_t* done_count;     /* local device word, zero between launches */
   int world, rank;
   long long n;
   int* err;
 } UbAllReduceArgs;
+int ub_allreduce_oneshot_ctas(long long n);
 int ub_allreduce_oneshot(const UbAllReduceArgs* args, void* stream);
 /* F4: merge per-shard greedy winners across tensor-parallel ranks over peer memory (see csrc/comm/comm.cu). */
 typedef struct UbArgmaxMergeArgs {

@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(256) norm_kernel(const NormParams p) {
       while (true) {
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.rs_flag) : "memory");
         if (int32_t(v - want) >= 0) break;
-        if ((++it & 31u) == 0 && (globaltimer_ns() - t0 > UB_WAIT_NS)) {
+        if ((++it & 31u) == 0 && wait_expired(t0, p.err)) {
           set_err(p.err, ERR_FLAG_TIMEOUT, 1000 + t);
           wait_failed = 1;
           break;
@@ -231,7 +231,7 @@ __global__ void wait_flag_kernel(const uint32_t* flags, uint32_t value, int* err
   while (true) {
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
     if (int32_t(v - value) >= 0) return;
-    if ((++it & 31u) == 0 && (globaltimer_ns() - t0 > UB_WAIT_NS)) {
+    if ((++it & 31u) == 0 && wait_expired(t0, err)) {
       set_err(err, ERR_FLAG_TIMEOUT, 2000);
       return;
     }

@@ -61,6 +61,26 @@ def test_host_gemv_and_simd_gemm(qtype):
     assert torch.allclose(be.q_gemv(raw, x[0], N_, qtype), ref[0], atol=1e-3, rtol=1e-4)
 
 
+@pytest.mark.parametrize("qtype", [2, 8, 12])
+@pytest.mark.parametrize("level", [0, None])
+def test_tiled_parallel_quantised_gemm(qtype, level):
+    """Prefill-sized quantised GEMM: 64-row tiles of the weight handed to several threads; the vector row kernels
+    (Q4_0 / Q8_0 / Q4_K at level >= 1) and the portable ones must agree with the dequantised matrix product."""
+    be = Q.SimdBackend(force_level=level if level is not None else -1)
+    N_, K, M = 333, 1024, 19
+    raw = random_blocks(qtype, N_ * K, seed=3 + qtype)
+    w = dequantize_blocks(raw, qtype, (N_, K))
+    x = torch.randn(M, K, generator=torch.Generator().manual_seed(2))
+    ref = x @ w.t()
+    tol = 2e-3 * float(ref.abs().max())
+    for threads in (1, 4, 0):
+        be.set_threads(threads)
+        got = be.q_gemm(raw, x, N_, qtype)
+        assert float((got - ref).abs().max()) < tol, (threads, float((got - ref).abs().max()), tol)
+    be.set_threads(0)
+    Q.SimdBackend(force_level=-1)
+
+
 @pytest.mark.parametrize("level", [0, None])
 def test_simd_backend_ops(level):
     be = Q.SimdBackend(force_level=level if level is not None else -1)

@@ -35,7 +35,10 @@ import torch
 MAXR = 8
 # counter indices (uint32 words) inside the flag area
 AG0, RS1, AG1, RS0 = 0, 8, 16, 24
-FLAG_WORDS = 64
+FLAG_WORDS = 256
+AR_ROUND, AR_DONE = 44, 45               # one-shot all-reduce: exchanges completed, CTAs finished (both local)
+AR_FLAGS = 64                            # ... and its 64 per-CTA arrival counters (words 64..127)
+AR_ROWS = 32                             # token rows the one-shot all-reduce area holds (decode-sized messages)
 ARGMAX_FLAG, ARGMAX_ROUND = 32, 33     # counter of the greedy merge and its (local) round word
 LOCAL_RS0, LOCAL_RS1, LOCAL_AG0, LOCAL_AG1 = 40, 41, 42, 43   # local arrival counters of the producing launches
 ARGMAX_ROWS = 2048                      # sampled rows per step the merge area can hold
@@ -66,12 +69,15 @@ class FusedComm:
         am = 2 * world * ARGMAX_ROWS * 4
         self.am_vals = _Area(4 * slot + FLAG_WORDS * 4, am)
         self.am_ids = _Area(4 * slot + FLAG_WORDS * 4 + am, am)
+        self.ar_elems = AR_ROWS * hidden                       # bf16 elements per rank slot of the one-shot all-reduce
+        self.ar_slots = _Area(self.am_ids.offset + am, 2 * world * self.ar_elems * 2)
         self.device = buf.device
 
     @staticmethod
     def nbytes(world: int, hidden: int, max_tokens: int) -> int:
         rows = (max_tokens + world - 1) // world
-        return 4 * world * rows * hidden * 2 + FLAG_WORDS * 4 + 2 * (2 * world * ARGMAX_ROWS * 4)
+        return (4 * world * rows * hidden * 2 + FLAG_WORDS * 4 + 2 * (2 * world * ARGMAX_ROWS * 4) +
+                2 * world * AR_ROWS * hidden * 2)
 
     @classmethod
     def create(cls, spec, rank: int, world: int, group, max_tokens: int, device, heap: Optional[str] = None) -> "FusedComm":
@@ -214,6 +220,34 @@ class FusedComm:
         N.check(N.cuda_lib().ub_tp_argmax_merge(C.byref(a), torch.cuda.current_stream(self.device).cuda_stream),
                 "ub_tp_argmax_merge")
         return out
+
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        """F1s: in-place sum of a small contiguous bf16 tensor (at most ``AR_ROWS`` rows of the hidden size) over the
+        ranks, through peer memory -- no NCCL call, capturable in a CUDA graph."""
+        import ctypes as C
+
+        from ..ops import _native as N
+        from ..ops import cuda_ops
+
+        n = t.numel()
+        if t.dtype != torch.bfloat16 or not t.is_contiguous() or n % 8 or n > self.ar_elems:
+            raise ValueError("one-shot all-reduce takes a contiguous bf16 tensor of at most AR_ROWS x hidden elements")
+        a = N.UbAllReduceArgs()
+        a.in_, a.out = t.data_ptr(), t.data_ptr()
+        for r in range(self.world):
+            a.peer_slots[r] = self._peer(r, self.ar_slots)
+            a.peer_flags[r] = self.flag_ptr(r, AR_FLAGS)
+        a.my_slots = self.buf.data_ptr() + self.ar_slots.offset
+        a.my_flags = self.local_flag_ptr(AR_FLAGS)
+        a.round, a.done_count = self.local_flag_ptr(AR_ROUND), self.local_flag_ptr(AR_DONE)
+        a.world, a.rank, a.n = self.world, self.rank, n
+        a.err = cuda_ops.err_word(self.device).data_ptr()
+        N.check(N.cuda_lib().ub_allreduce_oneshot(C.byref(a), torch.cuda.current_stream(self.device).cuda_stream),
+                "ub_allreduce_oneshot")
+        return t
+
+    def can_all_reduce(self, t: torch.Tensor) -> bool:
+        return t.dtype == torch.bfloat16 and t.is_contiguous() and t.numel() % 8 == 0 and t.numel() <= self.ar_elems
 
     def reset(self) -> None:
         """Zero all counters (host side); call on every rank, then barrier, after a reported device timeout."""

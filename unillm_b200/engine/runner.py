@@ -351,6 +351,8 @@ class TpContext:
 
     def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
         if self.world > 1:
+            if self.comm is not None and self.comm.can_all_reduce(t):
+                return self.comm.all_reduce(t)        # decode-sized message: one-shot exchange over peer memory
             import torch.distributed as dist
 
             dist.all_reduce(t, group=self.group)

@@ -102,7 +102,8 @@ class UbMoeRouteArgs(C.Structure):
 class UbAllReduceArgs(C.Structure):
     _fields_ = [
         ("in_", vp), ("out", vp), ("peer_slots", vp * UB_MAX_RANKS), ("peer_flags", vp * UB_MAX_RANKS),
-        ("my_slots", vp), ("my_flag", vp), ("epoch", vp), ("world", i32), ("rank", i32), ("n", i64), ("err", vp),
+        ("my_slots", vp), ("my_flags", vp), ("round", vp), ("done_count", vp), ("world", i32), ("rank", i32), ("n", i64),
+        ("err", vp),
     ]
 
 

@@ -29,6 +29,7 @@ def _host():
         lib.ubs_backend_level.restype = i32
         lib.ubs_backend_name.restype = C.c_char_p
         lib.ubs_force_level.argtypes = [i32]
+        lib.ubs_set_threads.argtypes = [i32]
         lib.ubs_dot.argtypes, lib.ubs_dot.restype = [vp, vp, i64], f32
         for n in ("ubs_add", "ubs_mul", "ubs_fused_swiglu"):
             getattr(lib, n).argtypes = [vp, vp, vp, i64]
@@ -156,6 +157,10 @@ class SimdBackend:
 
     def q_gemv(self, blocks, x, N_: int, qtype: int):
         return self.q_gemm(blocks, x.reshape(1, -1), N_, qtype)[0]
+
+    def set_threads(self, n: int) -> None:
+        """Worker threads of the tiled quantised GEMM (0 = all hardware threads, at most 16)."""
+        self.lib.ubs_set_threads(int(n))
 
     q4_gemm, q4_gemv = q_gemm, q_gemv
 
