@@ -144,6 +144,25 @@ static inline int grid_for(long long n) {
   return (int)g;
 }
 
+// Row softmax over the last dimension (bf16 in / out, fp32 inside): one warp per row, three passes over the row kept
+// in L1 / L2.  Replaces ops_fn::softmax (crates/runtime/src/tensor_core.rs:1022-1036) and the SIMD softmax
+// (simd/arch/avx2.rs:246-307) outside attention, the router and the sampler, which have it fused.
+__global__ void __launch_bounds__(256) softmax_rows_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
+                                                           long long rows, int n) {
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const __nv_bfloat16* xr = x + row * n;
+  float mx = -3.4e38f;
+  for (int i = lane; i < n; i += 32) mx = fmaxf(mx, __bfloat162float(xr[i]));
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int i = lane; i < n; i += 32) sum += __expf(__bfloat162float(xr[i]) - mx);
+  sum = warp_sum(sum);
+  const float inv = 1.f / sum;
+  for (int i = lane; i < n; i += 32) out[row * n + i] = __float2bfloat16(__expf(__bfloat162float(xr[i]) - mx) * inv);
+}
+
 }  // namespace ub
 
 extern "C" int ub_embed_gather(const int* ids, const void* table, void* out, int T, int H, int V, float scale,
@@ -175,4 +194,12 @@ extern "C" int ub_l2_normalize(const void* x, void* out, int T, int H, float eps
   if (T <= 0) return 0;
   ub::l2norm_kernel<<<T, 256, 0, (cudaStream_t)st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, H, eps);
   return ub::last_err();
+}
+
+extern "C" int ub_softmax_rows(const void* x, void* out, long long rows, int n, void* stream) {
+  if (rows <= 0 || n <= 0) return 0;
+  ub::softmax_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<__nv_bfloat16*>(out), rows, n);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
 }

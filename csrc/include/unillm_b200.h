@@ -199,6 +199,7 @@ int ub_act_mul(const void* gate_up, void* out, long long T, int I, int act, void
 int ub_eltwise(const void* x, void* out, long long n, int act, float alpha, void* stream);  /* out = act(alpha * x) */
 int ub_add(const void* a, const void* b, void* out, long long n, float sa, float sb, void* stream);
 int ub_l2_normalize(const void* x, void* out, int T, int H, float eps, void* stream);
+int ub_softmax_rows(const void* x, void* out, long long rows, int n, void* stream);   /* bf16, softmax over the last dim */
 
 /* ---------------- K7 / K13 : MoE ---------------- */
 typedef struct UbMoeRouteArgs {
@@ -252,16 +253,23 @@ int ub_causal_dwconv1d(const void* x, const float* w /*[C,Kw]*/, const float* b 
                        int L, int C, int Kw, int act_silu, int update_state, void* stream);
 /* A [Dm,Ns], Bm/Cm bf16 [B,L,Ns], Dv [Dm] or NULL, z bf16 [B,L,Dm] or NULL (gate: y *= silu(z)), state [B,Dm,Ns]. */
 int ub_selective_scan(const void* u, const void* delta, const float* A, const void* Bm, const void* Cm, const float* Dv,
-                      const void* z, void* out, float* state, int B, int L, int Dm, int Ns, int delta_softplus, void* stream);
+                      const void* z, void* out, float* state, int B, int L, int Dm, int Ns, int delta_softplus,
+                      float* workspace, void* stream);
 /* h = a*h + (one_minus ? 1-a : 1)*x;  a is [C] or, with a_per_step, [B,L,C];  state [B,C]. */
 int ub_linear_recurrence(const float* a, int a_per_step, const void* x, void* out, float* state, int B, int L, int C,
-                         int one_minus, void* stream);
+                         int one_minus, float* workspace, void* stream);
 /* w = -exp(time_decay) [C], u = time_first [C], state [B,3,C] = (aa, bb, pp), fresh sequences start at (0, 0, -1e38). */
 int ub_wkv4(const void* k, const void* v, const float* w, const float* u, void* out, float* state, int B, int L, int C,
-            void* stream);
+            float* workspace, void* stream);
 /* w fp32 [B,L,H*Dh] pre-activation decay (decay = exp(-exp(w))), u [H*Dh], state [B,H,Dh,Dh]; Dh = 64 or 32. */
 int ub_wkv6(const void* r, const void* k, const void* v, const float* w, const float* u, void* out, float* state, int B,
-            int L, int H, int Dh, void* stream);
+            int L, int H, int Dh, float* workspace, void* stream);
+/* Long sequences run the four scans above in chunks that proceed in parallel (a summary pass, a short carry over the
+   chunks, an output pass).  That needs `workspace` (fp32, ub_scan_workspace_floats elements; kind: 0 selective scan
+   (n = Dm, m = Ns), 1 linear recurrence (n = C), 2 WKV-4 (n = C), 3 WKV-6 (n = H, m = Dh)); with a NULL workspace, or a
+   sequence for which ub_scan_chunks answers 1, the single sequential pass runs. */
+int ub_scan_chunks(int L);
+long long ub_scan_workspace_floats(int kind, int B, int L, int n, int m);
 
 /* ---------------- comm helpers ---------------- */
 int ub_bump_epoch(uint32_t* epoch, void* stream);

@@ -501,3 +501,56 @@ def test_gemm_2cta_splitk(M, N, K, tile, ps):
     out = cuda_ops.gemm_tn(x, w, bias=bias, residual=res, tile_tokens=tile, cta_pair=2, pair_splits=ps)
     _close(out, x.float() @ w.float().t() + bias.float() + res.float())
     assert torch.equal(cuda_ops.gemm_tn(x, w, bias=bias, residual=res, tile_tokens=tile, cta_pair=2, pair_splits=ps), out)
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,Sq,Sk,causal", [(128, 4, 2, 70, 70, True), (128, 4, 4, 33, 50, False), (64, 6, 2, 40, 40, False),
+                                                   (64, 4, 4, 1, 37, True), (128, 2, 1, 17, 64, True)])
+def test_dense_attention_on_the_paged_kernels(D, Hq, Hkv, Sq, Sk, causal):
+    """Dense [B, H, S, D] attention (encoders, cross-attention, the whole-model decoders) on identity-paged K/V."""
+    from unillm_b200.ops import cuda_ops as K
+
+    g = torch.Generator().manual_seed(D + Sq)
+    B = 3
+    q = torch.randn(B, Hq, Sq, D, generator=g).to(torch.bfloat16).cuda()
+    k = torch.randn(B, Hkv, Sk, D, generator=g).to(torch.bfloat16).cuda()
+    v = torch.randn(B, Hkv, Sk, D, generator=g).to(torch.bfloat16).cuda()
+    got = K.dense_attention(q, k, v, causal=causal).float().cpu()
+    rep = Hq // Hkv
+    kf, vf = k.float().cpu().repeat_interleave(rep, 1), v.float().cpu().repeat_interleave(rep, 1)
+    s = q.float().cpu() @ kf.transpose(-1, -2) * D ** -0.5
+    if causal:
+        i = torch.arange(Sq)[:, None] + (Sk - Sq)
+        s = s.masked_fill(torch.arange(Sk)[None] > i, float("-inf"))
+    ref = torch.softmax(s, -1) @ vf
+    assert (got - ref).abs().max().item() < 0.03
+    torch.cuda.synchronize()
+    K.check_device_errors()
+
+
+def test_softmax_rows_kernel():
+    from unillm_b200.ops import cuda_ops as K
+
+    x = (torch.randn(37, 5, 1000) * 3).to(torch.bfloat16).cuda()
+    got = K.softmax_rows(x).float().cpu()
+    ref = torch.softmax(x.float().cpu(), -1)
+    assert (got - ref).abs().max().item() < 4e-3
+    assert (got.sum(-1) - 1).abs().max().item() < 2e-2
+
+
+def test_encoder_attention_takes_the_kernel_path():
+    """A bf16 BERT on the GPU (bidirectional attention, head size 64) against its fp32 CPU copy."""
+    from unillm_b200.model_core import ModelInputs
+    from unillm_b200.models import configs as C
+    from unillm_b200.models.encoders import BertModel
+    from unillm_b200.ops import cuda_ops as K
+
+    cfg = C.BertConfig(vocab_size=200, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, intermediate_size=512)
+    m = BertModel.new(cfg, init="random", seed=2)
+    m.p = {k: v.to(torch.bfloat16).float() for k, v in m.p.items()}
+    ids = torch.randint(0, 200, (2, 45))
+    ref = m.forward(ModelInputs.text(ids)).main_tensor().float()
+    mg = BertModel.new(cfg, init="random", seed=2)
+    mg.p = {k: v.to(torch.bfloat16).cuda() for k, v in m.p.items()}
+    got = mg.forward(ModelInputs.text(ids.cuda())).main_tensor().float().cpu()
+    assert K.attn_prefill_last_path() in ("mma.sync", "tcgen05")
+    assert (got - ref).abs().max().item() < 0.08 * max(1.0, ref.abs().max().item())

@@ -144,3 +144,88 @@ def test_conv1d_as_gemm_and_whisper_bf16():
     torch.cuda.synchronize()
     cuda_ops.check_device_errors()
     _close(got, ref, 0.08)
+
+
+def test_chunked_scans_equal_the_single_pass_on_long_sequences():
+    """From 1024 steps on the scans run as parallel 256-step chunks (summary pass, carry over the chunks, output pass).
+    Same inputs through the single sequential pass of the same kernels: outputs and final states must agree up to the
+    rounding of a different summation order; a ragged last chunk and a non-zero starting state are included."""
+    from unillm_b200.ops import recurrent as R
+
+    g = torch.Generator().manual_seed(31)
+    L = 1024 + 256 + 77
+
+    def both(fn):
+        R.CHUNKED = False
+        a = fn()
+        R.CHUNKED = True
+        b = fn()
+        return a, b
+
+    # selective scan
+    B, Dm, Ns = 2, 160, 16
+    u, dt, z = (_bf(torch.randn(B, L, Dm, generator=g)).cuda() for _ in range(3))
+    Bm, Cm = (_bf(torch.randn(B, L, Ns, generator=g)).cuda() for _ in range(2))
+    A, Dv = (-torch.rand(Dm, Ns, generator=g) * 2).cuda(), torch.randn(Dm, generator=g).cuda()
+    st0 = (torch.randn(B, Dm, Ns, generator=g) * 0.1).cuda()
+    states = []
+
+    def run_ss():
+        st = st0.clone()
+        states.append(st)
+        return R.selective_scan(u, dt, A, Bm, Cm, Dv, z, st)
+
+    seq, chk = both(run_ss)
+    _close(chk, seq.cpu(), 0.02)
+    _close(states[1], states[0].cpu(), 1e-3)
+
+    # diagonal linear recurrence, per-step coefficients
+    Cn = 300
+    x = _bf(torch.randn(1, L, Cn, generator=g)).cuda()
+    a = torch.rand(1, L, Cn, generator=g).cuda() * 0.2 + 0.8
+    st0l = torch.randn(1, Cn, generator=g).cuda()
+    states.clear()
+
+    def run_lr():
+        st = st0l.clone()
+        states.append(st)
+        return R.linear_recurrence(a, x, st, True)
+
+    seq, chk = both(run_lr)
+    _close(chk, seq.cpu(), 0.02)
+    _close(states[1], states[0].cpu(), 1e-3)
+
+    # WKV-4
+    k, v = (_bf(torch.randn(2, L, Cn, generator=g)).cuda() for _ in range(2))
+    w, uu = (-torch.exp(torch.randn(Cn, generator=g) * 0.5 - 2)).cuda(), torch.randn(Cn, generator=g).cuda()
+    states.clear()
+
+    def run_w4():
+        st = R.wkv4_new_state(2, Cn, "cuda")
+        states.append(st)
+        return R.wkv4(k, v, w, uu, st)
+
+    seq, chk = both(run_w4)
+    _close(chk, seq.cpu(), 0.02)
+    true = lambda s: (s[:, 0] * torch.exp(s[:, 2] - s[:, 2].max()), s[:, 1] * torch.exp(s[:, 2] - s[:, 2].max()))  # noqa: E731
+    # the (aa, bb, pp) triple is not unique; the ratio aa / bb (the carried average) and pp + log(bb) are
+    r0, r1 = states[0][:, 0] / states[0][:, 1], states[1][:, 0] / states[1][:, 1]
+    _close(r1, r0.cpu(), 1e-3)
+    _close(states[1][:, 2] + torch.log(states[1][:, 1]), (states[0][:, 2] + torch.log(states[0][:, 1])).cpu(), 1e-3)
+
+    # WKV-6
+    H, Dh = 3, 64
+    r6, k6, v6 = (_bf(torch.randn(1, L, H * Dh, generator=g) * 0.5).cuda() for _ in range(3))
+    w6 = (torch.randn(1, L, H * Dh, generator=g) * 0.5 - 1.5).cuda()
+    u6 = torch.randn(H * Dh, generator=g).cuda() * 0.3
+    st06 = (torch.randn(1, H, Dh, Dh, generator=g) * 0.1).cuda()
+    states.clear()
+
+    def run_w6():
+        st = st06.clone()
+        states.append(st)
+        return R.wkv6(r6, k6, v6, w6, u6, H, st)
+
+    seq, chk = both(run_w6)
+    _close(chk, seq.cpu(), 0.02)
+    _close(states[1], states[0].cpu(), 2e-3)

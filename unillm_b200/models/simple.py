@@ -137,6 +137,15 @@ def mha(x_q: torch.Tensor, x_kv: torch.Tensor, wq, bq, wk, bk, wv, bv, wo, bo, n
             k = torch.cat([cache["k"], k], 2)
             v = torch.cat([cache["v"], v], 2)
         cache["k"], cache["v"] = k, v
+    if (q.is_cuda and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and D in (64, 128) and bias is None
+            and not window and num_heads % nkv == 0):
+        # bf16 on the GPU: the paged attention kernels of the serving engine on dense pages (tcgen05 for head size
+        # 128, warp MMA for 64), grouped heads indexed in the kernel instead of being copied
+        from ..ops import cuda_ops as K
+
+        o = K.dense_attention(q, k, v, causal=bool(causal), scale=scale if scale is not None else D ** -0.5)
+        o = o.transpose(1, 2).reshape(B, Tq, num_heads * D)
+        return ops_fn.linear(o, wo, bo)
     if nkv != num_heads:
         k = k.repeat_interleave(num_heads // nkv, 1)
         v = v.repeat_interleave(num_heads // nkv, 1)

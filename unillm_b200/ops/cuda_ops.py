@@ -329,6 +329,47 @@ def attn_prefill_split_scratch_floats(T: int, Hq: int, D: int, kv_splits: int) -
     return lse + (kv_splits * T * Hq * D + 1) // 2
 
 
+def dense_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = False,
+                    scale: Optional[float] = None) -> torch.Tensor:
+    """Attention over dense tensors on the paged prefill kernels: ``q`` [B, Hq, Sq, D], ``k`` / ``v`` [B, Hkv, Sk, D]
+    (bf16 CUDA, D = 64 or 128, Hq a multiple of Hkv) -> [B, Hq, Sq, D].  Keys and values are laid out as pages of 16
+    positions with an identity block table, so bidirectional encoders (BERT, ViT, Whisper, CLIP), cross-attention and
+    cached decoders share the kernels of the serving engine; with ``causal`` query i sees keys ``<= Sk - Sq + i``."""
+    _bf16c(q, "q"), _bf16c(k, "k"), _bf16c(v, "v")
+    B, Hq, Sq, D = q.shape
+    Hkv, Sk = k.shape[1], k.shape[2]
+    if D not in (64, 128) or Hq % Hkv:
+        raise ValueError("dense_attention: head size 64 or 128, query heads a multiple of KV heads")
+    nb = (Sk + 15) // 16
+    pad = nb * 16 - Sk
+
+    def pages(t):
+        if pad:
+            t = torch.nn.functional.pad(t, (0, 0, 0, pad))
+        return t.reshape(B, Hkv, nb, 16, D).permute(0, 2, 1, 3, 4).reshape(B * nb, Hkv, 16, D).contiguous()
+
+    kp, vp = pages(k), pages(v)
+    bt = torch.arange(B * nb, dtype=torch.int32, device=q.device).view(B, nb)
+    lens = torch.full((B,), Sk, dtype=torch.int32, device=q.device)
+    qs = torch.arange(B + 1, dtype=torch.int32, device=q.device) * Sq
+    qt = q.permute(0, 2, 1, 3).reshape(B * Sq, Hq, D).contiguous()
+    out = attn_prefill(qt, kp, vp, bt, lens, qs, Sq, scale=scale, causal=causal)
+    return out.view(B, Sq, Hq, D).permute(0, 2, 1, 3)
+
+
+def softmax_rows(x: torch.Tensor) -> torch.Tensor:
+    """Softmax over the last dimension of a bf16 CUDA tensor."""
+    _bf16c(x, "x")
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    n = x.shape[-1]
+    lib = N.cuda_lib()
+    lib.ub_softmax_rows.restype = C.c_int
+    lib.ub_softmax_rows.argtypes = [N.vp, N.vp, N.i64, N.i32, N.vp]
+    N.check(lib.ub_softmax_rows(x.data_ptr(), out.data_ptr(), x.numel() // n, n, _stream(x)), "ub_softmax_rows")
+    return out
+
+
 def attn_prefill_last_path() -> str:
     """Which kernel the last ``attn_prefill`` call ran: ``"tcgen05"`` or ``"mma.sync"``."""
     lib = N.cuda_lib()

@@ -2,7 +2,8 @@
 WKV-4, WKV-6.
 
 Every function has two implementations with one signature: a plain PyTorch fp32 loop over time (the oracle, used on
-CPU and by the tests) and the CUDA kernel of ``csrc/scan/scan.cu`` (used for bf16 CUDA tensors).  States are updated
+CPU and by the tests) and the CUDA kernel of ``csrc/scan/scan.cu`` (used for bf16 CUDA tensors).  From 1024 steps on
+the kernels run the sequence in 256-step chunks in parallel (chunk summaries, a short carry over the chunks, outputs).  States are updated
 in place when given, so prefill (``L`` = prompt length) and decode (``L`` = 1) chain naturally.
 
 Reference math: ``models_v2/mamba.rs:632-742`` (conv), ``:745-888`` (scan), ``rwkv4.rs:468-529``, ``rwkv6.rs:483-553``,
@@ -28,11 +29,14 @@ def _lib():
     if not getattr(lib, "_scan_bound", False):
         vp, i32 = N.vp, N.i32
         lib.ub_causal_dwconv1d.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
-        lib.ub_selective_scan.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
-        lib.ub_linear_recurrence.argtypes = [vp, i32, vp, vp, vp, i32, i32, i32, i32, vp]
-        lib.ub_wkv4.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]
-        lib.ub_wkv6.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]
-        for n in ("ub_causal_dwconv1d", "ub_selective_scan", "ub_linear_recurrence", "ub_wkv4", "ub_wkv6"):
+        lib.ub_selective_scan.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]
+        lib.ub_linear_recurrence.argtypes = [vp, i32, vp, vp, vp, i32, i32, i32, i32, vp, vp]
+        lib.ub_wkv4.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp]
+        lib.ub_wkv6.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp]
+        lib.ub_scan_chunks.argtypes = [i32]
+        lib.ub_scan_workspace_floats.argtypes = [i32, i32, i32, i32, i32]
+        lib.ub_scan_workspace_floats.restype = C.c_longlong
+        for n in ("ub_causal_dwconv1d", "ub_selective_scan", "ub_linear_recurrence", "ub_wkv4", "ub_wkv6", "ub_scan_chunks"):
             getattr(lib, n).restype = i32
         lib._scan_bound = True
     return lib, N
@@ -48,6 +52,15 @@ def _p(t: Optional[torch.Tensor]):
 
 def _f32c(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     return None if t is None else t.float().contiguous()
+
+
+CHUNKED = True      # long sequences run the scans in parallel chunks (tests switch it off to compare with the single pass)
+
+
+def _workspace(lib, kind: int, B: int, L: int, n: int, m: int, device) -> Optional[torch.Tensor]:
+    """fp32 workspace of the chunked form of a scan, or None when the single sequential pass is used."""
+    need = lib.ub_scan_workspace_floats(kind, B, L, n, m) if CHUNKED else 0
+    return torch.empty(need, dtype=torch.float32, device=device) if need > 0 else None
 
 
 # ------------------------------------------------------------------------------------------------
@@ -87,8 +100,9 @@ def selective_scan(u: torch.Tensor, delta: torch.Tensor, A: torch.Tensor, Bm: to
         z = None if z is None else z.contiguous()
         out = torch.empty_like(u)
         Af, Df = _f32c(A), _f32c(D)
+        ws = _workspace(lib, 0, Bn, L, Dm, Ns, u.device)
         N.check(lib.ub_selective_scan(u.data_ptr(), delta.data_ptr(), Af.data_ptr(), Bm.data_ptr(), Cm.data_ptr(), _p(Df),
-                                      _p(z), out.data_ptr(), _p(state), Bn, L, Dm, Ns, int(delta_softplus), _st(u)),
+                                      _p(z), out.data_ptr(), _p(state), Bn, L, Dm, Ns, int(delta_softplus), _p(ws), _st(u)),
                 "ub_selective_scan")
         return out
     uf, dt, Af = u.float(), delta.float(), A.float()
@@ -120,8 +134,9 @@ def linear_recurrence(a: torch.Tensor, x: torch.Tensor, state: Optional[torch.Te
         x = x.contiguous()
         af = _f32c(a)
         out = torch.empty_like(x)
+        ws = _workspace(lib, 1, Bn, L, Cn, 0, x.device)
         N.check(lib.ub_linear_recurrence(af.data_ptr(), int(per_step), x.data_ptr(), out.data_ptr(), _p(state), Bn, L, Cn,
-                                         int(one_minus), _st(x)), "ub_linear_recurrence")
+                                         int(one_minus), _p(ws), _st(x)), "ub_linear_recurrence")
         return out
     af, xf = a.float(), x.float()
     h = state.float().clone() if state is not None else torch.zeros(Bn, Cn, device=x.device)
@@ -150,8 +165,9 @@ def wkv4(k: torch.Tensor, v: torch.Tensor, w: torch.Tensor, u: torch.Tensor, sta
         k, v = k.contiguous(), v.contiguous()
         out = torch.empty_like(k)
         wf, uf = _f32c(w), _f32c(u)
+        ws = _workspace(lib, 2, Bn, L, Cn, 0, k.device)
         N.check(lib.ub_wkv4(k.data_ptr(), v.data_ptr(), wf.data_ptr(), uf.data_ptr(), out.data_ptr(), _p(state), Bn, L, Cn,
-                            _st(k)), "ub_wkv4")
+                            _p(ws), _st(k)), "ub_wkv4")
         return out
     kf, vf, wf, uf = k.float(), v.float(), w.float(), u.float()
     if state is not None:
@@ -188,8 +204,9 @@ def wkv6(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor, u: 
         r, k, v = r.contiguous(), k.contiguous(), v.contiguous()
         wf, uf = _f32c(w), _f32c(u)
         out = torch.empty_like(r)
+        ws = _workspace(lib, 3, Bn, L, H, Dh, r.device)
         N.check(lib.ub_wkv6(r.data_ptr(), k.data_ptr(), v.data_ptr(), wf.data_ptr(), uf.data_ptr(), out.data_ptr(), _p(state),
-                            Bn, L, H, Dh, _st(r)), "ub_wkv6")
+                            Bn, L, H, Dh, _p(ws), _st(r)), "ub_wkv6")
         return out
     rf, kf, vf = (t.float().view(Bn, L, H, Dh) for t in (r, k, v))
     dec = torch.exp(-torch.exp(w.float())).view(Bn, L, H, Dh)

@@ -227,6 +227,33 @@ class CudaTensorOps(CpuTensorOps):
             return self._k().l2_normalize(x)
         return super().normalize(x, p, dim)
 
+    def softmax(self, x, dim=-1):
+        if self._fast(x) and dim in (-1, x.dim() - 1):
+            return self._k().softmax_rows(x)
+        return super().softmax(x, dim)
+
+    def _attn_ok(self, q, k, v):
+        return (self._fast(q) and self._fast(k) and self._fast(v) and q.dim() == 4 and k.dim() == 4 and
+                q.shape[-1] in (64, 128) and q.shape[1] % k.shape[1] == 0 and k.shape == v.shape)
+
+    def attention(self, q, k, v, mask=None, scale=None):
+        # no mask: the paged attention kernels on dense pages; an explicit mask keeps the torch path
+        if mask is None and self._attn_ok(q, k, v):
+            return self._k().dense_attention(q, k, v, causal=False, scale=scale)
+        return super().attention(q, k, v, mask, scale)
+
+    def flash_attention(self, q, k, v, scale=None, causal=True):
+        if self._attn_ok(q, k, v):
+            return self._k().dense_attention(q, k, v, causal=causal, scale=scale)
+        return super().flash_attention(q, k, v, scale, causal)
+
+    def conv1d(self, x, w, b=None, stride=1, padding=0):
+        if self._fast(x):
+            from .models.simple import conv1d
+
+            return conv1d(x, w, b, stride=stride, padding=padding)      # window rows x filter matrix on the tcgen05 GEMM
+        return super().conv1d(x, w, b, stride, padding)
+
 
 _ACT_TORCH = {
     "silu": F.silu, "swish": F.silu, "gelu": F.gelu, "relu": F.relu, "sigmoid": torch.sigmoid, "tanh": torch.tanh,
