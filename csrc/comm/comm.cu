@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(256) allreduce_oneshot_kernel(const UbAllReduc
       asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(a.peer_flags[r] + blockIdx.x), "r"(1u) : "memory");
     // 2. wait for the same chunk of all ranks
     const uint32_t want = round * (uint32_t)a.world;
-    const uint64_t t0 = globaltimer_ns();
+    const uint64_t t0 = wait_ticks();
     uint32_t it = 0, v;
     while (true) {
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a.my_flags + blockIdx.x) : "memory");
@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(256) tp_argmax_merge_kernel(const UbArgmaxMerg
     asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(a.peer_flags[threadIdx.x]), "r"(1u) : "memory");
   if (threadIdx.x == 0) {
     const uint32_t want = round * (uint32_t)a.world;
-    const uint64_t t0 = globaltimer_ns();
+    const uint64_t t0 = wait_ticks();
     uint32_t it = 0, v;
     while (true) {
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a.my_flag) : "memory");

@@ -35,11 +35,11 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
-// Time base of the bounded waits.  The SM cycle counter is read instead of %globaltimer: the global timer is a
-// slow off-SM read, and a wait that polls it (even once per call) costs more than the event it waits for.  Only
-// differences inside one thread are used; cycles / 2 is within a factor of 1.5 of nanoseconds at 1.3 - 2 GHz, which
-// is all a 1.5 s deadline needs.
-__device__ __forceinline__ uint64_t globaltimer_ns() {
+// Time base of the bounded waits: SM cycles / 2 ("ticks").  The SM cycle counter is read instead of %globaltimer:
+// the global timer is a slow off-SM read, and a wait that polls it (even once per call) costs more than the event it
+// waits for.  Only differences inside one thread are used.  A tick is 1.0 ns at 2.0 GHz and 1.5 ns at 1.3 GHz, so a
+// limit stated in ticks is a time between those bounds -- all a give-up deadline needs.
+__device__ __forceinline__ uint64_t wait_ticks() {
   return (uint64_t)clock64() >> 1;
 }
 
@@ -91,21 +91,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait.  `abort_flag` is a CTA-shared int: once any wait of this CTA has
 // timed out, later waits give up at once so a broken launch drains quickly.
-#ifndef UB_WAIT_NS
-#define UB_WAIT_NS 1500000000ull  // 1.5 s
+#ifndef UB_WAIT_TICKS
+#define UB_WAIT_TICKS 1500000000ull  // 1.5 s at 2 GHz, 2.3 s at 1.3 GHz
 #endif
 // True when a bounded wait that started at t0 should give up: its deadline has passed, or an error is already
 // recorded in the device error word (by an earlier kernel of the step or another CTA) -- then nothing this launch
 // produces will be used, and sitting out one more deadline per wait would only make a broken step take minutes.
 __device__ __forceinline__ bool wait_expired(uint64_t t0, const int* err) {
   if (err != nullptr && *reinterpret_cast<const volatile int*>(err) != 0) return true;
-  return globaltimer_ns() - t0 > UB_WAIT_NS;
+  return wait_ticks() - t0 > UB_WAIT_TICKS;
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err,
                                           int detail) {
   if (mbar_try_wait(bar, parity)) return true;
   if (*abort_flag) return false;
-  const uint64_t t0 = globaltimer_ns();
+  const uint64_t t0 = wait_ticks();
   uint32_t it = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;

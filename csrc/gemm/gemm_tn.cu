@@ -431,7 +431,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
           const int r_lo = m0 / p.ag_rows_per_rank;
           int r_hi = (min(m0 + TN, p.M) - 1) / p.ag_rows_per_rank;
           if (r_hi >= p.ag_world) r_hi = p.ag_world - 1;
-          const uint64_t t0 = globaltimer_ns();
+          const uint64_t t0 = wait_ticks();
           bool waited = false;
           for (int r = r_lo; r <= r_hi; ++r) {
             if (ag_ready >> r & 1u) continue;
@@ -822,7 +822,7 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           const int r_lo = m0 / p.ag_rows_per_rank;
           int r_hi = (min(m0 + TN / 2, p.M) - 1) / p.ag_rows_per_rank;
           if (r_hi >= p.ag_world) r_hi = p.ag_world - 1;
-          const uint64_t t0 = globaltimer_ns();
+          const uint64_t t0 = wait_ticks();
           bool waited = false;
           for (int r = r_lo; r <= r_hi; ++r) {
             if (ag_ready >> r & 1u) continue;

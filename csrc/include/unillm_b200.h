@@ -239,6 +239,51 @@ int ub_moe_combine_rs(const void* y, const int* row_slot, const float* topk_w, i
                       int rows_per_rank, void* const* peer_out, uint32_t* const* peer_flag, uint32_t* local_count,
                       void* local_out, void* stream);
 
+/* F5 / F6: sparse expert-parallel dispatch / combine over peer memory (csrc/moe/moe.cu).  Rank r owns token rows
+   [r * R, (r + 1) * R) and experts [r * experts_local, (r + 1) * experts_local); cap = R * K rows per source region. */
+typedef struct UbMoeDispatchArgs {
+  const void* x;                     /* bf16 [R, H]: this rank's rows */
+  const int* topk_ids;               /* [R, K] global expert ids (ub_moe_route on the R rows) */
+  const float* topk_w;               /* [R, K] */
+  int* send_slot;                    /* scratch [R * K] */
+  int* send_counts;                  /* scratch [E] */
+  void* peer_rows[UB_MAX_RANKS];     /* per rank: bf16 [world][cap][H] receive rows */
+  void* peer_meta[UB_MAX_RANKS];     /* per rank: int4 [world][cap] (global pair id, local expert, weight bits, 0) */
+  int* peer_counts[UB_MAX_RANKS];    /* per rank: int [world][experts_local] rows sent per (source, local expert) */
+  uint32_t* peer_flag[UB_MAX_RANKS]; /* per rank: arrival counter of the dispatch (monotonic, one per source and use) */
+  uint32_t* local_count;             /* zeroed local word: arrival counter of this launch's CTAs */
+  int* err;
+  int R, K, H, E, world, rank, experts_local, cap;
+} UbMoeDispatchArgs;
+int ub_moe_dispatch(const UbMoeDispatchArgs* args, void* stream);
+
+typedef struct UbMoeRecvArgs {
+  const int* counts;                 /* local [world][experts_local] */
+  const void* meta;                  /* local int4 [world][cap] */
+  const uint32_t* flag;              /* local arrival counter; expects `world` more arrivals per use */
+  uint32_t* round;                   /* local word: uses so far (advanced by the kernel, so the launch can sit in a graph) */
+  int* sorted_rows;                  /* out [world * cap]: receive row of each expert-ordered slot, -1 past the end */
+  void* slot_meta;                   /* out int4 [world * cap]: (global pair id, owner rank, weight bits, 0) per slot */
+  int* expert_counts;                /* out [experts_local] */
+  int* expert_offsets;               /* out [experts_local + 1] */
+  void* tiles;                       /* out int4 [max_tiles]: tile table of the grouped GEMM */
+  int* err;
+  int world, experts_local, cap, tile_tokens, max_tiles;
+} UbMoeRecvArgs;
+int ub_moe_recv_build(const UbMoeRecvArgs* args, void* stream);
+
+typedef struct UbMoeReturnArgs {
+  const void* y;                     /* bf16 [slots, H] expert outputs in slot order */
+  const void* slot_meta;
+  const int* expert_offsets;         /* [experts_local + 1]; the last entry is the number of rows */
+  void* peer_comb[UB_MAX_RANKS];     /* per rank: bf16 [K][R][H] combine area, summed by the owner's norm kernel */
+  uint32_t* peer_flag[UB_MAX_RANKS];
+  uint32_t* local_count;
+  int* err;
+  int R, K, H, world, experts_local;
+} UbMoeReturnArgs;
+int ub_moe_combine_push(const UbMoeReturnArgs* args, int max_slots, void* stream);
+
 /* ---------------- K12 : GGUF-quantised weights ---------------- */
 /* qtype is the ggml type id: 2 Q4_0, 3 Q4_1, 6 Q5_0, 8 Q8_0, 12 Q4_K, 14 Q6_K. */
 int ub_dequant(const void* blocks, void* out_bf16, long long n_elems, int qtype, void* stream);

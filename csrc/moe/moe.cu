@@ -196,6 +196,180 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* _
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------------------
+// F5 / F6: sparse expert-parallel dispatch and combine over peer memory.
+//
+// Every rank owns R = T / world consecutive token rows (the rows its norm kernel has just produced), routes THEM
+// (1 / world of the router work), and sends each (token, choice) pair's row only to the rank that holds the chosen
+// expert: T * K / world rows leave a rank instead of (world - 1) * T / world for the all-gather, and T * K / world
+// come back instead of T.  No count exchange precedes the rows: rank `src` owns the fixed region
+// [src * cap, (src + 1) * cap), cap = R * K, of every destination's receive buffer, fills it front to back in expert
+// order, and writes how many rows of each local expert it sent into a small header.  One arrival per source tells
+// the destination that region and header are complete (publish_to_peers); the destination's build kernel turns the
+// world x experts_local count table into expert-contiguous row order, the tile table of the grouped GEMM and the
+// return address of every row.  The combine scales each expert output by its routing weight and stores it into
+// slot [choice k][row] of the token owner's combine area, one writer per (token, k), so the owner's norm kernel sums
+// K slots in a fixed order.  Replaces the host loop over tokens and experts at
+// crates/runtime/src/models_v2/mixtral.rs:639-662 / model_core.rs:796-905.
+// ------------------------------------------------------------------------------------------------------------
+
+// One CTA: pairs per global expert, and each pair's position inside its destination's region.
+__global__ void __launch_bounds__(1024) moe_dispatch_sort_kernel(const UbMoeDispatchArgs a) {
+  __shared__ int cnt[MOE_MAX_E], off[MOE_MAX_E], cur[MOE_MAX_E];
+  const int n = a.R * a.K;
+  for (int e = threadIdx.x; e < a.E; e += blockDim.x) { cnt[e] = 0; cur[e] = 0; }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = a.topk_ids[i];
+    if (e >= 0 && e < a.E) atomicAdd(&cnt[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x < a.world) {
+    // experts [d * experts_local, (d + 1) * experts_local) live on rank d: offsets restart at every destination
+    const int d = threadIdx.x;
+    int acc = 0;
+    for (int el = 0; el < a.experts_local; ++el) {
+      off[d * a.experts_local + el] = acc;
+      acc += cnt[d * a.experts_local + el];
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < a.E; e += blockDim.x) a.send_counts[e] = cnt[e];
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = a.topk_ids[i];
+    a.send_slot[i] = (e >= 0 && e < a.E) ? off[e] + atomicAdd(&cur[e], 1) : -1;
+  }
+}
+
+// Rows, their metadata and the count header go to the destinations; the last CTA signals every rank once.
+__global__ void __launch_bounds__(256) moe_dispatch_push_kernel(const UbMoeDispatchArgs a) {
+  const int vec = a.H / 8;
+  const long long work = (long long)a.R * a.K * vec;
+  const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(a.x);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < work; i += (long long)gridDim.x * blockDim.x) {
+    const int pair = int(i / vec), c = int(i % vec);
+    const int slot = a.send_slot[pair];
+    if (slot < 0 || slot >= a.cap) continue;
+    const int e = a.topk_ids[pair];
+    const int d = e / a.experts_local;
+    const long long row = (long long)a.rank * a.cap + slot;
+    const uint4 v = *reinterpret_cast<const uint4*>(x + (long long)(pair / a.K) * a.H + c * 8);
+    reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.peer_rows[d]) + row * a.H)[c] = v;
+    if (c == 0) {
+      // global pair id (token * K + k), local expert, routing weight
+      const int gp = (a.rank * a.R + pair / a.K) * a.K + pair % a.K;
+      reinterpret_cast<int4*>(a.peer_meta[d])[row] = make_int4(gp, e - d * a.experts_local, __float_as_int(a.topk_w[pair]), 0);
+    }
+  }
+  if (blockIdx.x == 0) {
+    for (int e = threadIdx.x; e < a.E; e += blockDim.x) {
+      const int d = e / a.experts_local;
+      a.peer_counts[d][a.rank * a.experts_local + (e - d * a.experts_local)] = a.send_counts[e];
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) publish_to_peers(a.local_count, gridDim.x, a.peer_flag, a.world);
+}
+
+// One CTA on the receiving rank: wait (bounded) for the arrival of every source, then expert-contiguous order.
+__global__ void __launch_bounds__(1024) moe_recv_build_kernel(const UbMoeRecvArgs a) {
+  __shared__ int cnt[MOE_MAX_E];     // [world][experts_local]; world * experts_local = E <= MOE_MAX_E (host check)
+  __shared__ int base[MOE_MAX_E];    // first compacted slot of (source, expert)
+  __shared__ int srcoff[MOE_MAX_E];  // first row of the expert inside the source's region
+  __shared__ int nsrc[UB_MAX_RANKS];
+  __shared__ int total_s;
+  const int W = a.world, EL = a.experts_local;
+  if (threadIdx.x == 0) {
+    const uint32_t round = *a.round + 1;                // exchanges are counted; the flag is never reset
+    const uint32_t want = round * (uint32_t)W;
+    const uint64_t t0 = wait_ticks();
+    uint32_t it = 0, v;
+    while (true) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a.flag) : "memory");
+      if (int32_t(v - want) >= 0) break;
+      if ((++it & 31u) == 0 && wait_expired(t0, a.err)) {
+        set_err(a.err, ERR_FLAG_TIMEOUT, 5000);
+        break;
+      }
+    }
+    *a.round = round;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < W * EL; i += blockDim.x) {
+    int c = __ldcg(a.counts + i);                       // written by peers: L2 only
+    if (c < 0 || c > a.cap) { set_err(a.err, ERR_BOUNDS, 5100 + i); c = 0; }
+    cnt[i] = c;
+  }
+  __syncthreads();
+  if (threadIdx.x < W) {
+    int acc = 0;
+    for (int el = 0; el < EL; ++el) { srcoff[threadIdx.x * EL + el] = acc; acc += cnt[threadIdx.x * EL + el]; }
+    if (acc > a.cap) { set_err(a.err, ERR_BOUNDS, 5200 + threadIdx.x); acc = 0; }
+    nsrc[threadIdx.x] = acc;
+  }
+  if (threadIdx.x == 0) {
+    int acc = 0, tile = 0;
+    int4* tiles = reinterpret_cast<int4*>(a.tiles);
+    for (int el = 0; el < EL; ++el) {
+      const int start = acc;
+      for (int s = 0; s < W; ++s) { base[s * EL + el] = acc; acc += cnt[s * EL + el]; }
+      a.expert_offsets[el] = start;
+      a.expert_counts[el] = acc - start;
+      for (int r = start; r < acc && tile < a.max_tiles; r += a.tile_tokens, ++tile) tiles[tile] = make_int4(el, r, acc, 0);
+    }
+    a.expert_offsets[EL] = acc;
+    for (; tile < a.max_tiles; ++tile) tiles[tile] = make_int4(-1, 0, 0, 0);
+    total_s = acc;
+  }
+  __syncthreads();
+  const int4* meta = reinterpret_cast<const int4*>(a.meta);
+  int4* slot_meta = reinterpret_cast<int4*>(a.slot_meta);
+  for (int i = threadIdx.x; i < W * a.cap; i += blockDim.x) {
+    const int s = i / a.cap, j = i - s * a.cap;
+    if (j >= nsrc[s]) continue;
+    const int4 m = __ldcg(meta + i);
+    const int el = m.y;
+    if (el < 0 || el >= EL || j < srcoff[s * EL + el] || j - srcoff[s * EL + el] >= cnt[s * EL + el]) {
+      set_err(a.err, ERR_BOUNDS, 5300 + s);
+      continue;
+    }
+    const int slot = base[s * EL + el] + (j - srcoff[s * EL + el]);
+    a.sorted_rows[slot] = i;
+    slot_meta[slot] = make_int4(m.x, s, m.z, 0);
+  }
+  for (int i = total_s + threadIdx.x; i < W * a.cap; i += blockDim.x) a.sorted_rows[i] = -1;
+}
+
+// Expert outputs go home: y[slot] * weight -> slot [k][token row] of the owner's combine area.
+__global__ void __launch_bounds__(256) moe_combine_push_kernel(const UbMoeReturnArgs a) {
+  const int vec = a.H / 8;
+  const int total = a.expert_offsets[a.experts_local];
+  const __nv_bfloat16* y = reinterpret_cast<const __nv_bfloat16*>(a.y);
+  const int4* slot_meta = reinterpret_cast<const int4*>(a.slot_meta);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < (long long)total * vec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int slot = int(i / vec), c = int(i % vec);
+    const int4 m = slot_meta[slot];
+    const int owner = m.y, tok = m.x / a.K, k = m.x - tok * a.K;
+    const int row = tok - owner * a.R;
+    if (owner < 0 || owner >= a.world || row < 0 || row >= a.R) {
+      if (c == 0) set_err(a.err, ERR_BOUNDS, 5400);
+      continue;
+    }
+    const float w = __int_as_float(m.z);
+    const uint4 v = *reinterpret_cast<const uint4*>(y + (long long)slot * a.H + c * 8);
+    const uint32_t* vs = reinterpret_cast<const uint32_t*>(&v);
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = pack_bf16x2(w * bf16_lo(vs[j]), w * bf16_hi(vs[j]));
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.peer_comb[owner]) + ((long long)k * a.R + row) * a.H;
+    reinterpret_cast<uint4*>(dst)[c] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) publish_to_peers(a.local_count, gridDim.x, a.peer_flag, a.world);
+}
+
 }  // namespace ub
 
 extern "C" int ub_moe_route(const UbMoeRouteArgs* a, void* stream_v) {
@@ -261,6 +435,42 @@ extern "C" int ub_moe_combine_rs(const void* y, const int* row_slot, const float
   ub::moe_combine_kernel<<<combine_blocks(T, H), 256, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
       reinterpret_cast<const __nv_bfloat16*>(y), row_slot, topk_w, nullptr, reinterpret_cast<__nv_bfloat16*>(local_out), T, K, H,
       push);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+// F5: route-local dispatch.  Two launches (sort, push); grid of the push as reported by ub_moe_dispatch_num_ctas.
+static int dispatch_blocks(int R, int K, int H) {
+  const long long work = (long long)R * K * (H / 8);
+  int blocks = int((work + 255) / 256);
+  return blocks > 148 * 4 ? 148 * 4 : (blocks < 1 ? 1 : blocks);
+}
+extern "C" int ub_moe_dispatch(const UbMoeDispatchArgs* a, void* stream_v) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_v);
+  if (a->R <= 0) return 0;
+  if (a->H % 8 != 0 || a->E <= 0 || a->E > ub::MOE_MAX_E || a->world <= 0 || a->world > UB_MAX_RANKS ||
+      a->experts_local * a->world != a->E || a->cap < a->R * a->K || a->local_count == nullptr)
+    return -2;
+  ub::moe_dispatch_sort_kernel<<<1, 1024, 0, st>>>(*a);
+  ub::moe_dispatch_push_kernel<<<dispatch_blocks(a->R, a->K, a->H), 256, 0, st>>>(*a);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+extern "C" int ub_moe_recv_build(const UbMoeRecvArgs* a, void* stream_v) {
+  if (a->world <= 0 || a->world > UB_MAX_RANKS || a->experts_local <= 0 ||
+      a->world * a->experts_local > ub::MOE_MAX_E || a->tile_tokens <= 0 || a->max_tiles <= 0 ||
+      a->round == nullptr || a->flag == nullptr)
+    return -2;
+  ub::moe_recv_build_kernel<<<1, 1024, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(*a);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+// F6: sparse combine.  max_slots bounds the grid (the true row count is read on the device).
+extern "C" int ub_moe_combine_push(const UbMoeReturnArgs* a, int max_slots, void* stream_v) {
+  if (a->H % 8 != 0 || a->world <= 0 || a->world > UB_MAX_RANKS || a->local_count == nullptr || a->R <= 0 || a->K <= 0) return -2;
+  ub::moe_combine_push_kernel<<<dispatch_blocks(max_slots, 1, a->H), 256, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(*a);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }

@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(256) norm_kernel(const NormParams p) {
     if (threadIdx.x == 0) {
       wait_failed = 0;
       const uint32_t want = p.rs_signals_per_use;
-      const uint64_t t0 = globaltimer_ns();
+      const uint64_t t0 = wait_ticks();
       uint32_t it = 0, v;
       while (true) {
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.rs_flag) : "memory");
@@ -226,7 +226,7 @@ __global__ void bump_epoch_kernel(uint32_t* e) { *e = *e + 1; }
 
 __global__ void wait_flag_kernel(const uint32_t* flags, uint32_t value, int* err) {
   const uint32_t* flag = flags + threadIdx.x;   // one thread per counter
-  const uint64_t t0 = globaltimer_ns();
+  const uint64_t t0 = wait_ticks();
   uint32_t it = 0, v;
   while (true) {
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");

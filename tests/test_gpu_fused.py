@@ -139,7 +139,11 @@ def logit_batch():
         lens.append(n); tables.append(blocks); qlens.append(n); rows.append(len(toks) - 1)
     return StepBatch(toks, pos, slots, 0, lens, tables, qlens, rows)
 logits = {}
-for mode in ("tp1", "nccl", "fused", "fused_graph"):
+modes = ("tp1", "nccl", "fused", "fused_graph") + (("fused_replicated",) if moe else ())
+for mode in modes:
+    # mixtral: "fused" sends each (token, expert) pair to the rank of its expert; "fused_replicated" is the layout in
+    # which every rank sees all rows after the all-gather and keeps the pairs of its experts
+    os.environ["UB_MOE_SPARSE"] = "0" if mode == "fused_replicated" else "1"
     tpw = 1 if mode == "tp1" else world
     tp = TpContext(rank if tpw > 1 else 0, tpw, dist.group.WORLD if tpw > 1 else None, fused=mode.startswith("fused"))
     w = RunnerWeights.random(spec, f"cuda:{rank}", tp.rank, tp.world, seed=7, expert_parallel=moe)
@@ -162,11 +166,20 @@ for mode in ("tp1", "nccl", "fused", "fused_graph"):
         torch.cuda.synchronize()
         cuda_ops.check_device_errors()
         assert runner.fused_steps > 0 or mode != "fused"
+        if moe and mode.startswith("fused"):
+            assert bool(getattr(runner, "_moe_sparse", False)) == (mode == "fused")
+        if moe and mode == "fused":
+            # token conservation: the pairs received over all ranks in the last MoE call are all pairs of the step
+            d = list(runner._moe_dispatch_state.values())[-1]
+            n = d.offsets[d.experts_local:d.experts_local + 1].clone().to(torch.int64)
+            dist.all_reduce(n)
+            out["pairs_received"], out["pairs_sent"] = int(n), d.R * world * d.K
     dist.barrier()
 ref = logits["tp1"]
 scale = float(ref.abs().max())
-out["logit_err"] = {m: float((logits[m] - ref).abs().max()) / scale for m in ("nccl", "fused")}
-out["argmax_agree"] = {m: float((logits[m].argmax(-1) == ref.argmax(-1)).float().mean()) for m in ("nccl", "fused")}
+cmp = ("nccl", "fused") + (("fused_replicated",) if moe else ())
+out["logit_err"] = {m: float((logits[m] - ref).abs().max()) / scale for m in cmp}
+out["argmax_agree"] = {m: float((logits[m].argmax(-1) == ref.argmax(-1)).float().mean()) for m in cmp}
 comm.close()
 if rank == 0:
     print("RESULT " + json.dumps(out))
@@ -190,7 +203,7 @@ def test_tensor_parallel_engine_fused_matches_baseline(tmp_path, model, heap):
     port = 29731 + 10 * ["llama", "mixtral"].index(model) + ["own", "own-peer-only", "torch"].index(heap)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", str(port), str(script)]
-    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
     line = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")][-1]
     out = json.loads(line[7:])
@@ -207,7 +220,9 @@ def test_tensor_parallel_engine_fused_matches_baseline(tmp_path, model, heap):
         assert not out["multimem"]
     # logits of one prefill step, every vocabulary column, against the single-GPU run: bf16 activations with other
     # summation orders (K split over the ranks, partial sums rounded to bf16 before the reduction)
-    for mode in ("nccl", "fused"):
+    if model == "mixtral":
+        assert out["pairs_received"] == out["pairs_sent"] > 0
+    for mode in out["logit_err"]:
         assert out["logit_err"][mode] < 0.04, out["logit_err"]
         assert out["argmax_agree"][mode] == 1.0 or out["logit_err"][mode] < 0.02, (out["argmax_agree"], out["logit_err"])
 

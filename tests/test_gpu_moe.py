@@ -173,3 +173,57 @@ def test_expert_parallel_partials_and_fused_combine():
     assert local.cpu().tolist() == [0] * W                            # the last CTA of each launch zeroed its counter
     got = torch.cat([recv[o].float().sum(0) for o in range(W)], 0)
     assert (got - full.float()).abs().max().item() < 0.05 * max(1.0, full.float().abs().max().item())
+
+
+@pytest.mark.parametrize("T,E,K,H,I,W", [(96, 8, 2, 256, 128, 4), (64, 4, 2, 512, 256, 2), (120, 64, 6, 256, 128, 8)])
+def test_sparse_dispatch_and_combine_emulated_ranks(T, E, K, H, I, W):
+    """Sparse expert-parallel dispatch / combine with all ranks emulated on one GPU (every sender runs before any
+    receiver on one stream, so each bounded wait finds its counter complete): every (token, expert) pair reaches
+    exactly one rank, the combine area of a token's owner ends up with the K weighted expert outputs, their sum equals
+    the single-rank MoE block, and a second exchange (counted, not reset, arrival words) works as well."""
+    from unillm_b200.dist.fused import RS1, FusedComm
+    from unillm_b200.ops import cuda_ops as ops
+
+    g = torch.Generator().manual_seed(T + E)
+    rw = (torch.randn(E, H, generator=g) * 0.2).to(torch.bfloat16).cuda()
+    gu = (torch.randn(E, 2 * I, H, generator=g) * H ** -0.5).to(torch.bfloat16).cuda()
+    dn = (torch.randn(E, H, I, generator=g) * I ** -0.5).to(torch.bfloat16).cuda()
+    comms = FusedComm.emulated(W, H, T, "cuda", moe_top_k=K, moe_experts=E)
+    R, EL = T // W, E // W
+    states = [ops.MoeDispatch(R, K, E, W, "cuda") for _ in range(W)]
+    for it in range(2):
+        x = torch.randn(T, H, generator=g).to(torch.bfloat16).cuda()
+        r_full = ops.moe_route(x, rw, K, round_logits_bf16=False)
+        xs = ops.moe_gather(x, r_full)
+        full = ops.moe_combine(ops.grouped_gemm(ops.grouped_gemm(xs, gu, r_full, dual_rows=I, act="silu"), dn, r_full), r_full)
+        for rank in range(W):                                   # senders
+            own = x[rank * R:(rank + 1) * R].contiguous()
+            ops.moe_route(own, rw, K, round_logits_bf16=False, routing=states[rank].route)
+            ops.moe_dispatch(own, states[rank], comms[rank].moe_dispatch_args())
+        received = 0
+        for rank in range(W):                                   # receivers: experts [rank * EL, (rank + 1) * EL)
+            d, c = states[rank], comms[rank]
+            ops.moe_recv_build(d, c.moe_recv_args(), "cuda")
+            rows = ops.gather_rows(c.moe_recv_rows(d.slots), d.sorted_rows)
+            a = ops.grouped_gemm(rows, gu[rank * EL:(rank + 1) * EL].contiguous(), d, dual_rows=I, act="silu")
+            y = ops.grouped_gemm(a, dn[rank * EL:(rank + 1) * EL].contiguous(), d)
+            ops.moe_combine_push(y, d, c.moe_return_args())
+            torch.cuda.synchronize()
+            ops.check_device_errors()
+            n = int(d.offsets[EL])
+            received += n
+            # the rows that arrived are the rows of the tokens that chose this rank's experts, in expert order
+            meta = d.slot_meta[:n].cpu()
+            pair = meta[:, 0].long()
+            ids = r_full.topk_ids.cpu().flatten()
+            assert ((ids[pair] >= rank * EL) & (ids[pair] < (rank + 1) * EL)).all()
+            assert (ids[pair][1:] >= ids[pair][:-1]).all()
+            assert torch.equal(rows[:n].cpu(), x.cpu()[pair // K])
+            assert torch.equal(meta[:, 1].long(), (pair // K) // R)            # return address: the token's owner
+        assert received == T * K                                               # token conservation
+        got = torch.cat([comms[o].moe_comb_tensor(R).float().sum(0) for o in range(W)], 0)
+        assert (got - full.float()).abs().max().item() < 0.05 * max(1.0, full.float().abs().max().item())
+        for o in range(W):
+            fl = comms[o].buf[comms[o].flags.offset:comms[o].flags.offset + 256].view(torch.int32)
+            assert int(fl[RS1]) == W                                           # one combine arrival per rank
+            fl[RS1] = 0                                                        # what the next norm kernel does in the pipeline

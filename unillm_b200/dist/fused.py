@@ -41,6 +41,7 @@ AR_FLAGS = 64                            # ... and its 64 per-CTA arrival counte
 AR_ROWS = 32                             # token rows the one-shot all-reduce area holds (decode-sized messages)
 ARGMAX_FLAG, ARGMAX_ROUND = 32, 33     # counter of the greedy merge and its (local) round word
 LOCAL_RS0, LOCAL_RS1, LOCAL_AG0, LOCAL_AG1 = 40, 41, 42, 43   # local arrival counters of the producing launches
+DISP_FLAG, DISP_ROUND, LOCAL_DISP = 46, 47, 48   # sparse MoE dispatch: arrivals (peers), uses so far and CTA counter (local)
 ARGMAX_ROWS = 2048                      # sampled rows per step the merge area can hold
 
 
@@ -52,7 +53,7 @@ class _Area:
 
 class FusedComm:
     def __init__(self, rank: int, world: int, hidden: int, max_tokens: int, buf: torch.Tensor, peer_ptrs: List[int],
-                 handle=None, group=None, mc_ptr: int = 0):
+                 handle=None, group=None, mc_ptr: int = 0, moe_top_k: int = 0, moe_experts: int = 0):
         self.rank, self.world, self.H = rank, world, hidden
         self.max_rows = (max_tokens + world - 1) // world
         self.buf, self.peer_ptrs, self.handle, self.group = buf, peer_ptrs, handle, group
@@ -71,13 +72,35 @@ class FusedComm:
         self.am_ids = _Area(4 * slot + FLAG_WORDS * 4 + am, am)
         self.ar_elems = AR_ROWS * hidden                       # bf16 elements per rank slot of the one-shot all-reduce
         self.ar_slots = _Area(self.am_ids.offset + am, 2 * world * self.ar_elems * 2)
+        # sparse expert-parallel MoE (F5 / F6): receive rows [world][cap][H] with their metadata and the count header,
+        # and the combine area [K][rows][H]; sized for cap = max_rows * K
+        self.moe_top_k, self.moe_experts = moe_top_k, moe_experts
+        end = self.ar_slots.offset + self.ar_slots.nbytes
+        if moe_top_k:
+            pairs = world * self.max_rows * moe_top_k
+            self.disp_rows = _Area(end, pairs * hidden * 2)
+            self.disp_meta = _Area(self.disp_rows.offset + self.disp_rows.nbytes, pairs * 16)
+            self.disp_counts = _Area(self.disp_meta.offset + self.disp_meta.nbytes, (max(moe_experts, 1) * 4 + 255) // 256 * 256)
+            self.comb = _Area(self.disp_counts.offset + self.disp_counts.nbytes, moe_top_k * self.max_rows * hidden * 2)
         self.device = buf.device
 
     @staticmethod
-    def nbytes(world: int, hidden: int, max_tokens: int) -> int:
+    def nbytes(world: int, hidden: int, max_tokens: int, moe_top_k: int = 0, moe_experts: int = 0) -> int:
         rows = (max_tokens + world - 1) // world
-        return (4 * world * rows * hidden * 2 + FLAG_WORDS * 4 + 2 * (2 * world * ARGMAX_ROWS * 4) +
-                2 * world * AR_ROWS * hidden * 2)
+        n = (4 * world * rows * hidden * 2 + FLAG_WORDS * 4 + 2 * (2 * world * ARGMAX_ROWS * 4) +
+             2 * world * AR_ROWS * hidden * 2)
+        if moe_top_k:
+            pairs = world * rows * moe_top_k
+            n += pairs * hidden * 2 + pairs * 16 + (max(moe_experts, 1) * 4 + 255) // 256 * 256 + moe_top_k * rows * hidden * 2
+        return n
+
+    @staticmethod
+    def _moe_shape(spec, world: int):
+        """(top_k, experts) when the model's routed experts can be spread whole over ``world`` ranks, else (0, 0)."""
+        m = getattr(spec, "moe", None)
+        if m is None or world < 2 or m.num_experts % world or m.num_experts > 256:
+            return 0, 0
+        return m.top_k, m.num_experts
 
     @classmethod
     def create(cls, spec, rank: int, world: int, group, max_tokens: int, device, heap: Optional[str] = None) -> "FusedComm":
@@ -88,7 +111,8 @@ class FusedComm:
 
         group = group if group is not None else dist.group.WORLD
         heap = os.environ.get("UB_SYMM_HEAP") or heap
-        n = cls.nbytes(world, spec.hidden_size, max_tokens)
+        mk, me = cls._moe_shape(spec, world)
+        n = cls.nbytes(world, spec.hidden_size, max_tokens, mk, me)
         if heap != "torch":
             from .symm_heap import SymmetricHeap
 
@@ -101,7 +125,8 @@ class FusedComm:
             flag = torch.tensor([ok], dtype=torch.int32, device=device)
             dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
             if int(flag[0]) == 1:
-                c = cls(rank, world, spec.hidden_size, max_tokens, h.tensor()[:n], list(h.peer_ptrs), None, group, h.mc_ptr)
+                c = cls(rank, world, spec.hidden_size, max_tokens, h.tensor()[:n], list(h.peer_ptrs), None, group, h.mc_ptr,
+                        moe_top_k=mk, moe_experts=me)
                 c.heap = h
                 return c
             if heap == "own":
@@ -115,7 +140,8 @@ class FusedComm:
         buf.zero_()
         torch.cuda.synchronize(device)
         dist.barrier(group)
-        return cls(rank, world, spec.hidden_size, max_tokens, buf, [int(p) for p in hd.buffer_ptrs], hd, group)
+        return cls(rank, world, spec.hidden_size, max_tokens, buf, [int(p) for p in hd.buffer_ptrs], hd, group,
+                   moe_top_k=mk, moe_experts=me)
 
     def close(self) -> None:
         """Collective: releases the own heap (multicast binding first); a no-op for the torch-backed buffer."""
@@ -124,13 +150,15 @@ class FusedComm:
             self.heap = None
 
     @classmethod
-    def emulated(cls, world: int, hidden: int, max_tokens: int, device) -> List["FusedComm"]:
+    def emulated(cls, world: int, hidden: int, max_tokens: int, device, moe_top_k: int = 0,
+                 moe_experts: int = 0) -> List["FusedComm"]:
         """All ranks on ONE device (tests): plain buffers whose addresses stand in for peer mappings.  Kernels of
         different emulated ranks must then be launched producer-before-consumer on one stream."""
-        n = cls.nbytes(world, hidden, max_tokens)
+        n = cls.nbytes(world, hidden, max_tokens, moe_top_k, moe_experts)
         bufs = [torch.zeros(n, dtype=torch.uint8, device=device) for _ in range(world)]
         ptrs = [b.data_ptr() for b in bufs]
-        return [cls(r, world, hidden, max_tokens, bufs[r], ptrs) for r in range(world)]
+        return [cls(r, world, hidden, max_tokens, bufs[r], ptrs, moe_top_k=moe_top_k, moe_experts=moe_experts)
+                for r in range(world)]
 
     # ---- address helpers ----
     def _peer(self, r: int, area: _Area, extra: int = 0) -> int:
@@ -190,6 +218,49 @@ class FusedComm:
         base = AG0 if k == 0 else AG1
         return {"world": self.world, "rows_per_rank": rows_per_rank, "flags": self.local_flag_ptr(base),
                 "signals_per_use": 1}
+
+    # ---- sparse expert-parallel MoE (F5 / F6) ----
+    @property
+    def has_moe_dispatch(self) -> bool:
+        return bool(self.moe_top_k)
+
+    def moe_dispatch_args(self) -> dict:
+        """Send side of the dispatch: every rank's receive rows, metadata, count header and arrival counter."""
+        W = self.world
+        return {"world": W, "rank": self.rank,
+                "peer_rows": [self._peer(r, self.disp_rows) for r in range(W)],
+                "peer_meta": [self._peer(r, self.disp_meta) for r in range(W)],
+                "peer_counts": [self._peer(r, self.disp_counts) for r in range(W)],
+                "peer_flag": [self.flag_ptr(r, DISP_FLAG) for r in range(W)],
+                "local_count": self.local_flag_ptr(LOCAL_DISP)}
+
+    def moe_recv_args(self) -> dict:
+        base = self.buf.data_ptr()
+        return {"counts": base + self.disp_counts.offset, "meta": base + self.disp_meta.offset,
+                "flag": self.local_flag_ptr(DISP_FLAG), "round": self.local_flag_ptr(DISP_ROUND)}
+
+    def moe_recv_rows(self, rows: int) -> torch.Tensor:
+        """This rank's receive buffer as ``[rows, H]`` (``rows = world * cap``)."""
+        a = self.disp_rows
+        return self.buf[a.offset:a.offset + rows * self.H * 2].view(torch.bfloat16).view(rows, self.H)
+
+    def moe_return_args(self) -> dict:
+        """Send side of the combine: every rank's combine area; arrivals count on the second reduce-scatter counter,
+        which the norm kernels already zero between uses."""
+        W = self.world
+        return {"world": W, "peer_comb": [self._peer(r, self.comb) for r in range(W)],
+                "peer_flag": [self.flag_ptr(r, RS1) for r in range(W)],
+                "local_count": self.local_flag_ptr(LOCAL_RS1)}
+
+    def moe_comb_tensor(self, rows_per_rank: int) -> torch.Tensor:
+        """This rank's combine area as ``[K, rows_per_rank, H]``: slot k holds every own token's k-th expert output."""
+        a = self.comb
+        n = self.moe_top_k * rows_per_rank * self.H
+        return self.buf[a.offset:a.offset + n * 2].view(torch.bfloat16).view(self.moe_top_k, rows_per_rank, self.H)
+
+    def norm_comb(self) -> dict:
+        """Consumer arguments for a norm kernel that sums the combine area: K slots, one arrival per rank."""
+        return {"world": self.moe_top_k, "flag": self.local_flag_ptr(RS1), "signals_per_use": self.world}
 
     def reset_after_ag(self, k: int) -> tuple:
         """Counters a norm kernel may zero: the all-gather counters it does NOT feed plus the reduce-scatter

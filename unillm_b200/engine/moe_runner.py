@@ -12,6 +12,10 @@ identically, runs the grouped GEMMs for the pairs that picked one of its experts
 row per token.  Either way the partial rows are summed across ranks once, together with the shared experts /
 parallel dense MLP: by an all-reduce, or (``combine_rs``) by the combine kernel storing straight into the owners'
 receive slots over NVLink, which the next norm kernel sums.
+
+``moe_sparse`` is the expert-parallel layout without the replication: every rank routes only the token rows it
+owns, each (token, expert) pair's row goes to the one rank that holds the expert, and the weighted expert output
+comes back into the token owner's combine area (see the F5 / F6 kernels in ``csrc/moe/moe.cu``).
 """
 from __future__ import annotations
 
@@ -61,6 +65,40 @@ def moe_partial(runner, i: int, h: torch.Tensor, residual=None, combine_rs=None)
             out = K.moe_combine(y, r, residual=base)
     runner.launches += 3
     return out
+
+
+def moe_sparse(runner, i: int, h_own: torch.Tensor, comm, R: int) -> None:
+    """Sparse expert-parallel MoE for this rank's ``R`` normalised rows ``h_own``.  Nothing is returned: the weighted
+    outputs of all ranks' experts for these rows arrive in ``comm.moe_comb_tensor(R)``, complete once the second
+    reduce-scatter counter shows one arrival per rank (the next norm kernel waits for exactly that)."""
+    s, t = runner.spec, runner.w.t
+    m = s.moe
+    L = f"layers.{i}."
+    W = comm.world
+    key = (R, m.top_k, m.num_experts)
+    d = runner._moe_dispatch_state.get(key) if hasattr(runner, "_moe_dispatch_state") else None
+    if d is None:
+        if not hasattr(runner, "_moe_dispatch_state"):
+            runner._moe_dispatch_state = {}
+        d = runner._moe_dispatch_state[key] = K.MoeDispatch(R, m.top_k, m.num_experts, W, h_own.device)
+    with runner._prof("moe_route_dispatch"):
+        K.moe_route(h_own, t[L + "router"], m.top_k, norm_topk=m.normalize_topk, round_logits_bf16=False, routing=d.route)
+        K.moe_dispatch(h_own, d, comm.moe_dispatch_args())
+    with runner._prof("moe_recv"):
+        K.moe_recv_build(d, comm.moe_recv_args(), h_own.device)
+        xs = K.gather_rows(comm.moe_recv_rows(d.slots), d.sorted_rows)
+    runner.launches += 6
+    gu, dn = t[L + "experts_gate_up"], t[L + "experts_down"]
+    with runner._prof(f"moe_gate_up[{d.slots}x{gu.shape[1]}x{gu.shape[2]}]"):
+        if m.gated:
+            a = K.grouped_gemm(xs, gu, d, dual_rows=gu.shape[1] // 2, act=m.act)
+        else:
+            a = K.grouped_gemm(xs, gu, d, act=m.act)
+    with runner._prof(f"moe_down[{d.slots}x{dn.shape[1]}x{dn.shape[2]}]"):
+        y = K.grouped_gemm(a, dn, d)
+    with runner._prof("moe_combine_push"):
+        K.moe_combine_push(y, d, comm.moe_return_args())
+    runner.launches += 3
 
 
 def moe_forward(runner, i: int, h: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:

@@ -908,6 +908,9 @@ class GpuModelRunner:
         rs0_out = c.rs_local_tensor(0, R)
         rs1_out = c.rs_local_tensor(1, R)
         ag_args = None
+        # whole experts per rank and a dispatch area in the symmetric buffer: route locally, send pairs, not all rows
+        self._moe_sparse = bool(s.moe is not None and self.w.ep and c.has_moe_dispatch and
+                                os.environ.get("UB_MOE_SPARSE", "1") != "0")
         for i in range(s.num_layers):
             L = f"layers.{i}."
             qkv = self._gemm(h_full, t[L + "wqkv"], bias=t.get(L + "bqkv"), ag=ag_args, tag="gemm_ag" if ag_args else "gemm")
@@ -923,6 +926,29 @@ class GpuModelRunner:
             # o_proj: partial rows go straight to their owner's receive slot
             self._gemm(a, t[L + "wo"], bias=t.get(L + "bo"), out=rs0_out.view(W * R, H)[:T], rs=c.gemm_rs(0, R),
                        tag="gemm_rs")
+            sparse = s.layer_is_moe(i) and self._moe_sparse
+            if sparse:
+                # F5 / F6: this rank normalises and routes its own rows only; each (token, expert) pair travels to the
+                # rank of its expert and its weighted output comes back into slot k of the combine area
+                from .moe_runner import moe_sparse
+
+                with self._prof("norm_rs"):
+                    h_own, xr = K.norm(rs0_out, t[L + "ln2.w"], bias=t.get(L + "ln2.b"), residual=xr, eps=s.norm_eps,
+                                       kind=kind, weight_offset_one=s.norm_weight_offset_one, want_residual_out=True, T=R,
+                                       rs=c.norm_rs(0, rows_per_rank=R), reset=c.reset_after_ag(1))
+                self.launches += 1
+                moe_sparse(self, i, h_own, c, R)
+                last = i == s.num_layers - 1
+                nname = "final_norm" if last else f"layers.{i + 1}.ln1"
+                with self._prof("norm_rs_ag"):
+                    _, xr = K.norm(c.moe_comb_tensor(R), t[nname + ".w"], bias=t.get(nname + ".b"), residual=xr,
+                                   eps=s.norm_eps, kind=kind, weight_offset_one=s.norm_weight_offset_one,
+                                   want_residual_out=True, no_out=True, T=R, rs=c.norm_comb(), ag=c.norm_ag(0),
+                                   reset=c.reset_after_ag(0))
+                self.launches += 1
+                h_full = c.ag_local_tensor(0, T)
+                ag_args = c.gemm_ag(0, R)
+                continue
             # sum partials + residual, normalise own rows, push to every rank's gather area 1
             with self._prof("norm_rs_ag"):
                 _, xr = K.norm(rs0_out, t[L + "ln2.w"], bias=t.get(L + "ln2.b"), residual=xr, eps=s.norm_eps, kind=kind,

@@ -99,6 +99,31 @@ class UbMoeRouteArgs(C.Structure):
     ]
 
 
+class UbMoeDispatchArgs(C.Structure):
+    _fields_ = [
+        ("x", vp), ("topk_ids", vp), ("topk_w", vp), ("send_slot", vp), ("send_counts", vp),
+        ("peer_rows", vp * UB_MAX_RANKS), ("peer_meta", vp * UB_MAX_RANKS), ("peer_counts", vp * UB_MAX_RANKS),
+        ("peer_flag", vp * UB_MAX_RANKS), ("local_count", vp), ("err", vp),
+        ("R", i32), ("K", i32), ("H", i32), ("E", i32), ("world", i32), ("rank", i32), ("experts_local", i32), ("cap", i32),
+    ]
+
+
+class UbMoeRecvArgs(C.Structure):
+    _fields_ = [
+        ("counts", vp), ("meta", vp), ("flag", vp), ("round", vp), ("sorted_rows", vp), ("slot_meta", vp),
+        ("expert_counts", vp), ("expert_offsets", vp), ("tiles", vp), ("err", vp),
+        ("world", i32), ("experts_local", i32), ("cap", i32), ("tile_tokens", i32), ("max_tiles", i32),
+    ]
+
+
+class UbMoeReturnArgs(C.Structure):
+    _fields_ = [
+        ("y", vp), ("slot_meta", vp), ("expert_offsets", vp), ("peer_comb", vp * UB_MAX_RANKS),
+        ("peer_flag", vp * UB_MAX_RANKS), ("local_count", vp), ("err", vp),
+        ("R", i32), ("K", i32), ("H", i32), ("world", i32), ("experts_local", i32),
+    ]
+
+
 class UbAllReduceArgs(C.Structure):
     _fields_ = [
         ("in_", vp), ("out", vp), ("peer_slots", vp * UB_MAX_RANKS), ("peer_flags", vp * UB_MAX_RANKS),

@@ -592,6 +592,20 @@ def moe_gather(x: torch.Tensor, r: MoeRouting, out: Optional[torch.Tensor] = Non
     return out
 
 
+def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[i] = x[rows[i]]`` for int32 ``rows`` (negative entries leave ``out[i]`` untouched)."""
+    _bf16c(x, "x")
+    H = x.shape[1]
+    n = rows.numel()
+    if out is None:
+        out = torch.empty(n, H, dtype=torch.bfloat16, device=x.device)
+    lib = N.cuda_lib()
+    lib.ub_moe_gather.restype = C.c_int
+    lib.ub_moe_gather.argtypes = [N.vp, N.vp, N.vp, N.i32, N.i32, N.i32, N.vp]
+    N.check(lib.ub_moe_gather(x.data_ptr(), rows.data_ptr(), out.data_ptr(), n, 1, H, _stream(x)), "ub_moe_gather")
+    return out
+
+
 def moe_combine(y: torch.Tensor, r: MoeRouting, residual: Optional[torch.Tensor] = None,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out[t] = residual[t] + sum_k w[t,k] * y[row_slot[t,k]]``."""
@@ -629,6 +643,79 @@ def moe_combine_rs(y: torch.Tensor, r: MoeRouting, rs: dict) -> None:
                                   rs["rows_per_rank"], C.cast(outs, C.c_void_p), C.cast(flags, C.c_void_p),
                                   rs["local_count"], rs.get("local_out") or None, _stream(y)),
             "ub_moe_combine_rs")
+
+
+class MoeDispatch:
+    """Device-side state of one sparse expert-parallel MoE call on one rank: the routing of this rank's own ``R`` rows
+    (``route``), the send scratch, and what the receive side builds (row order, return addresses, tile table).  The
+    attributes ``tiles`` / ``max_tiles`` / ``tile_tokens`` make it usable where ``grouped_gemm`` expects a routing."""
+
+    def __init__(self, R: int, K: int, E: int, world: int, device):
+        self.R, self.K, self.E, self.world = R, K, E, world
+        self.experts_local = E // world
+        self.cap = R * K
+        self.slots = world * self.cap                         # = T * K: every pair of the step could land here
+        self.tile_tokens = moe_tile_tokens(R * world, K, E)
+        self.max_tiles = (self.slots + self.tile_tokens - 1) // self.tile_tokens + self.experts_local
+        i32 = dict(dtype=torch.int32, device=device)
+        self.route = MoeRouting(R, K, E, self.tile_tokens, device)
+        self.send_slot = torch.empty(R * K, **i32)
+        self.send_counts = torch.empty(E, **i32)
+        self.sorted_rows = torch.empty(self.slots, **i32)
+        self.slot_meta = torch.empty(self.slots, 4, **i32)
+        self.counts = torch.empty(self.experts_local, **i32)
+        self.offsets = torch.empty(self.experts_local + 1, **i32)
+        self.tiles = torch.empty(self.max_tiles, 4, **i32)
+
+
+def moe_dispatch(x: torch.Tensor, d: MoeDispatch, comm: dict) -> None:
+    """F5 send side: rows of ``x`` ([R, H], this rank's tokens, routed in ``d.route``) go to the ranks of their
+    experts.  ``comm``: world, rank, peer_rows / peer_meta / peer_counts / peer_flag (one address per rank) and
+    local_count, as ``FusedComm.moe_dispatch_args`` builds them."""
+    _bf16c(x, "x")
+    a = N.UbMoeDispatchArgs()
+    a.x, a.topk_ids, a.topk_w = x.data_ptr(), d.route.topk_ids.data_ptr(), d.route.topk_w.data_ptr()
+    a.send_slot, a.send_counts = d.send_slot.data_ptr(), d.send_counts.data_ptr()
+    for r in range(comm["world"]):
+        a.peer_rows[r], a.peer_meta[r] = comm["peer_rows"][r], comm["peer_meta"][r]
+        a.peer_counts[r], a.peer_flag[r] = comm["peer_counts"][r], comm["peer_flag"][r]
+    a.local_count = comm["local_count"]
+    a.err = err_word(x.device).data_ptr()
+    a.R, a.K, a.H, a.E = d.R, d.K, x.shape[1], d.E
+    a.world, a.rank, a.experts_local, a.cap = comm["world"], comm["rank"], d.experts_local, d.cap
+    lib = N.cuda_lib()
+    lib.ub_moe_dispatch.restype = C.c_int
+    N.check(lib.ub_moe_dispatch(C.byref(a), _stream(x)), "ub_moe_dispatch")
+
+
+def moe_recv_build(d: MoeDispatch, comm: dict, device) -> None:
+    """F5 receive side: waits (bounded, on the device) for every source's arrival, then orders the received rows by
+    expert: ``d.sorted_rows`` (receive row per slot), ``d.slot_meta`` (return address), ``d.tiles``."""
+    a = N.UbMoeRecvArgs()
+    a.counts, a.meta, a.flag, a.round = comm["counts"], comm["meta"], comm["flag"], comm["round"]
+    a.sorted_rows, a.slot_meta = d.sorted_rows.data_ptr(), d.slot_meta.data_ptr()
+    a.expert_counts, a.expert_offsets, a.tiles = d.counts.data_ptr(), d.offsets.data_ptr(), d.tiles.data_ptr()
+    a.err = err_word(device).data_ptr()
+    a.world, a.experts_local, a.cap = d.world, d.experts_local, d.cap
+    a.tile_tokens, a.max_tiles = d.tile_tokens, d.max_tiles
+    lib = N.cuda_lib()
+    lib.ub_moe_recv_build.restype = C.c_int
+    N.check(lib.ub_moe_recv_build(C.byref(a), torch.cuda.current_stream(device).cuda_stream), "ub_moe_recv_build")
+
+
+def moe_combine_push(y: torch.Tensor, d: MoeDispatch, comm: dict) -> None:
+    """F6: ``y[slot] * weight`` goes into slot ``[k][row]`` of the token owner's combine area; one arrival per rank."""
+    _bf16c(y, "y")
+    a = N.UbMoeReturnArgs()
+    a.y, a.slot_meta, a.expert_offsets = y.data_ptr(), d.slot_meta.data_ptr(), d.offsets.data_ptr()
+    for r in range(comm["world"]):
+        a.peer_comb[r], a.peer_flag[r] = comm["peer_comb"][r], comm["peer_flag"][r]
+    a.local_count = comm["local_count"]
+    a.err = err_word(y.device).data_ptr()
+    a.R, a.K, a.H, a.world, a.experts_local = d.R, d.K, y.shape[1], comm["world"], d.experts_local
+    lib = N.cuda_lib()
+    lib.ub_moe_combine_push.restype = C.c_int
+    N.check(lib.ub_moe_combine_push(C.byref(a), d.slots, _stream(y)), "ub_moe_combine_push")
 
 
 def grouped_gemm(x_sorted: torch.Tensor, w: torch.Tensor, r: MoeRouting, *, dual_rows: int = 0, act: Optional[str] = None,
