@@ -208,13 +208,29 @@ def test_tensor_parallel_engine_fused_matches_baseline(tmp_path, model, heap):
     line = [l for l in p.stdout.splitlines() if l.startswith("RESULT ")][-1]
     out = json.loads(line[7:])
     total = sum(len(r) for r in out["tp1"])
+
+    def agreement(a, b):
+        """Greedy tokens of a random-weight model flip on near-ties, and everything after a flip differs: count the
+        sequences that agree on their first tokens and the tokens that agree overall."""
+        first = sum(ra[:3] == rb[:3] for ra, rb in zip(out[a], out[b]))
+        same = sum(x == y for ra, rb in zip(out[a], out[b]) for x, y in zip(ra, rb))
+        return first, same
+
+    summary = {k: out[k] for k in ("logit_err", "argmax_agree", "heap", "multimem")}
+    summary["agreement"] = {f"{a}/{b}": agreement(a, b) for a, b in
+                            [("fused", "fused_graph"), ("tp1", "nccl"), ("tp1", "fused"), ("tp1", "fused_graph")]}
+    print(summary)
     # The graph path pads the step to bucketed shapes, so its GEMMs may pick other tiles and K splits than the eager
-    # path: same math, different rounding, and greedy tokens of a random-weight model can flip on near-ties.
-    same = sum(a == b for ra, rb in zip(out["fused"], out["fused_graph"]) for a, b in zip(ra, rb))
-    assert same / total > 0.9, ("fused vs fused_graph", same, total)
+    # path: same math, different rounding.  With routed experts a near-tie in the router moves a token to another
+    # expert, which changes its row by far more than rounding does, hence the wider margin there.
+    # The logit comparison below is the numerical check; the token comparison guards against a path that derails.
+    floor = 0.75 if model == "mixtral" else 0.9
+    slack = 2 if model == "mixtral" else 1
+    first, same = agreement("fused", "fused_graph")
+    assert first >= len(out["tp1"]) - slack and same / total > floor, summary
     for mode in ("nccl", "fused", "fused_graph"):
-        agree = sum(a == b for ra, rb in zip(out["tp1"], out[mode]) for a, b in zip(ra, rb))
-        assert agree / total > 0.8, (mode, agree, total)
+        first, agree = agreement("tp1", mode)
+        assert first >= len(out["tp1"]) - slack and agree / total > min(floor, 0.8), (mode, summary)
     assert out["heap"] == ("torch" if heap == "torch" else "own")
     if heap != "own":
         assert not out["multimem"]
@@ -223,8 +239,8 @@ def test_tensor_parallel_engine_fused_matches_baseline(tmp_path, model, heap):
     if model == "mixtral":
         assert out["pairs_received"] == out["pairs_sent"] > 0
     for mode in out["logit_err"]:
-        assert out["logit_err"][mode] < 0.04, out["logit_err"]
-        assert out["argmax_agree"][mode] == 1.0 or out["logit_err"][mode] < 0.02, (out["argmax_agree"], out["logit_err"])
+        assert out["logit_err"][mode] < 0.04, summary
+        assert out["argmax_agree"][mode] == 1.0 or out["logit_err"][mode] < 0.02, summary
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
