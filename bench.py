@@ -456,6 +456,9 @@ def main(argv=None) -> int:
                        "kv_block": bs, "prefix_cache": True, "cuda_graphs": not args.no_graphs,
                        "symmetric_heap": (None if tp.comm is None else ("own" if tp.comm.heap is not None else "torch")),
                        "nvswitch_multicast": (None if tp.comm is None else bool(tp.comm.multimem)),
+                       "reduce_scatter": (None if tp.comm is None else
+                                          "owner reads rows summed by the switch (multimem.ld_reduce)" if tp.comm.multimem_rs
+                                          else "GEMM epilogue stores rows into the owners' slots (peer stores)"),
                        "scheduling": "synchronous" if args.sync_scheduling else "host one step ahead of the device",
                        "l2": "inputs larger than L2: each step streams the model weights (>= 2 GB per GPU) from HBM",
                        "output_tokens_timed": tokens},

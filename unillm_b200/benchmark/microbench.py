@@ -269,7 +269,9 @@ def bench_tp_layer(results, world=8, batch=512, variants=False):
         opts = [dict()]
         if variants:
             opts += [dict(tile_tokens=t, cta_pair=1) for t in (64, 128, 256)] + [dict(cta_pair=2)] + \
-                    [dict(tile_tokens=t, cta_pair=1, splits=sp) for t in (128, 256) for sp in (2, 4)]
+                    [dict(tile_tokens=t, cta_pair=1, splits=sp) for t in (128, 256) for sp in (2, 4)] + \
+                    [dict(cta_pair=2, pair_splits=sp) for sp in (2, 4)] + \
+                    [dict(cta_pair=2, tile_tokens=128), dict(cta_pair=2, tile_tokens=128, pair_splits=2)]
         for o in opts:
             try:
                 fn = (lambda: cuda_ops.gemm_tn(x, w, dual_rows=N, act="silu", out=out, **o)) if dual else \

@@ -62,6 +62,11 @@ class FusedComm:
         # one multimem.st per 16 bytes instead of `world` peer stores.
         self.mc_ptr = mc_ptr
         self.multimem = bool(mc_ptr) and os.environ.get("UB_MULTIMEM", "1") != "0"
+        # The reduce-scatter has two forms on a multicast heap.  "pull" (default): partial rows stay local and the owner
+        # reads them summed by the switch, all of the NVLink time sits in the consumer.  "push" (UB_MULTIMEM_RS=0): the
+        # GEMM epilogue stores rows into the owners' slots as its tiles finish, so the transfer overlaps the tiles
+        # still being computed; the all-gather keeps its multicast stores either way.
+        self.multimem_rs = self.multimem and os.environ.get("UB_MULTIMEM_RS", "1") != "0"
         self.heap = None
         slot = world * self.max_rows * hidden * 2
         self.rs = [_Area(0, slot), _Area(slot, slot)]
@@ -187,7 +192,7 @@ class FusedComm:
         """F1 producer arguments: push rows into rank ``owner``'s ``rs[k]`` slot of this rank."""
         # multicast mode: the partial rows stay in this rank's own rs[k] area (peer_out all null); the owners read them
         # summed through the multicast address
-        outs = [0] * self.world if self.multimem else [self._peer(r, self.rs[k]) for r in range(self.world)]
+        outs = [0] * self.world if self.multimem_rs else [self._peer(r, self.rs[k]) for r in range(self.world)]
         return {"world": self.world, "rank": self.rank, "rows_per_rank": rows_per_rank, "peer_out": outs,
                 "peer_flag": [self.flag_ptr(r, RS0 if k == 0 else RS1) for r in range(self.world)],
                 "local_count": self.local_flag_ptr(LOCAL_RS0 if k == 0 else LOCAL_RS1), "local_out": self.rs_local(k)}
@@ -198,7 +203,7 @@ class FusedComm:
         buffer through the multicast address (the switch sums the ranks' copies)."""
         d = {"world": self.world, "flag": self.local_flag_ptr(RS0 if k == 0 else RS1),
              "signals_per_use": signals or self.world}
-        if self.multimem:
+        if self.multimem_rs:
             if rows_per_rank <= 0:
                 raise ValueError("multicast reduce-scatter needs rows_per_rank")
             d["multimem_x"] = self.mc_ptr + self.rs[k].offset + self.rank * rows_per_rank * self.H * 2
