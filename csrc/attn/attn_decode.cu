@@ -23,6 +23,8 @@ extern "C" int ub_attn_decode_mma_supported(const UbAttnArgs* a);
 extern "C" int ub_attn_decode_mma_main(const UbAttnArgs* a, void* stream);
 extern "C" int ub_attn_decode_persist_supported(const UbAttnArgs* a);
 extern "C" int ub_attn_decode_persist(const UbAttnArgs* a, void* stream);
+extern "C" int ub_attn_decode_warp_supported(const UbAttnArgs* a);
+extern "C" int ub_attn_decode_warp(const UbAttnArgs* a, void* stream);
 
 namespace ub {
 
@@ -342,10 +344,25 @@ static bool decode_persist_enabled() {
   return v == 1;
 }
 
+// Unsplit ranges with 16-key pages: the kernel with one independent copy / MMA pipeline per warp
+// (attn_decode_warp.cu).  UB_DECODE_WARP=0 keeps the CTA-per-item kernels.
+static bool decode_warp_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("UB_DECODE_WARP");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
 template <int D>
 static int launch_decode(const UbAttnArgs& a, cudaStream_t st) {
   const bool mma_ok = D <= 128 && decode_mma_enabled() && ub_attn_decode_mma_supported(&a);
   if (a.merge_o != nullptr && (!mma_ok || a.splits != 1)) return -7;   // fused merge lives in the warp-MMA kernels only
+  // one warp per item needs enough items to keep every SM's copy engines busy; with fewer, an item is better served by
+  // the four warps of a CTA
+  if (mma_ok && a.splits == 1 && a.num_seqs * a.Hkv >= 256 && decode_warp_enabled() && ub_attn_decode_warp_supported(&a))
+    return ub_attn_decode_warp(&a, st);
   if (mma_ok && a.kv_start > 0 && decode_persist_enabled() && ub_attn_decode_persist_supported(&a))
     return ub_attn_decode_persist(&a, st);
   if (mma_ok) {

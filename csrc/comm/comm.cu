@@ -106,6 +106,87 @@ extern "C" int ub_allreduce_oneshot(const UbAllReduceArgs* a, void* stream_v) {
 }
 
 // ----------------------------------------------------------------------------------------------
+// F4s: one-shot all-gather of (value, id) pairs, the exchange of vocabulary-parallel top-k / top-p sampling.  Every
+// rank holds, per sampled row, the k best (scaled logit, global id) pairs of its vocabulary shard; after the exchange
+// every rank has all world * k pairs of every row, in rank order, and draws the same token from them.  The rows are cut
+// into one chunk per CTA (the same cut on every rank); CTA c stores its chunk into slot [parity][row][rank] of every
+// rank, bumps counter [c] on every rank, waits (bounded) for `world` arrivals on its own counter [c] and copies the
+// chunk's gathered pairs into the caller's buffers.  Parity and exchange number as in the all-reduce above.
+// ----------------------------------------------------------------------------------------------
+namespace ub {
+
+__global__ void __launch_bounds__(256) pair_gather_oneshot_kernel(const UbPairGatherArgs a) {
+  const int per = (a.rows + gridDim.x - 1) / gridDim.x;
+  const int r0 = blockIdx.x * per, r1 = min(a.rows, r0 + per);
+  __shared__ uint32_t round_s;
+  if (threadIdx.x == 0) round_s = *a.round + 1;
+  __syncthreads();
+  const uint32_t round = round_s;
+  const long long slot = (long long)(round & 1u) * a.cap * a.world;
+  const int k = a.k, W = a.world;
+  // 1. this CTA's rows into slot [parity][row][rank][0..k) of every rank
+  for (long long i = (long long)r0 * k + threadIdx.x; i < (long long)r1 * k; i += blockDim.x) {
+    const long long row = i / k;
+    const int j = int(i - row * k);
+    const float v = a.vals[i];
+    const int id = a.ids[i];
+    const long long dst = slot + (row * W + a.rank) * k + j;
+    for (int r = 0; r < W; ++r) {
+      reinterpret_cast<float*>(a.peer_vals[r])[dst] = v;
+      reinterpret_cast<int*>(a.peer_ids[r])[dst] = id;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
+    for (int r = 0; r < W; ++r)
+      asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(a.peer_flags[r] + blockIdx.x), "r"(1u) : "memory");
+    const uint32_t want = round * (uint32_t)W;
+    const uint64_t t0 = wait_ticks();
+    uint32_t it = 0, v;
+    while (true) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a.my_flags + blockIdx.x) : "memory");
+      if (int32_t(v - want) >= 0) break;
+      if ((++it & 31u) == 0 && wait_expired(t0, a.err)) {
+        set_err(a.err, ERR_FLAG_TIMEOUT, 6000 + blockIdx.x);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  // 2. the gathered pairs of this CTA's rows -> [row][world * k]
+  for (long long i = (long long)r0 * W * k + threadIdx.x; i < (long long)r1 * W * k; i += blockDim.x) {
+    a.out_vals[i] = __ldcg(a.my_vals + slot + i);      // L2 only: peers wrote it
+    a.out_ids[i] = __ldcg(a.my_ids + slot + i);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t old = atomicAdd(a.done_count, 1u);
+    if (old + 1 == gridDim.x) {
+      *a.done_count = 0u;
+      *a.round = round;
+    }
+  }
+}
+
+}  // namespace ub
+
+extern "C" int ub_pair_gather_oneshot(const UbPairGatherArgs* a, void* stream_v) {
+  if (a->rows <= 0) return 0;
+  if (a->k <= 0 || a->world < 1 || a->world > UB_MAX_RANKS || (long long)a->rows * a->k > a->cap || a->round == nullptr ||
+      a->done_count == nullptr)
+    return -2;
+  // The grid must be co-resident (CTAs of different ranks wait on one another): at most UB_AR_MAX_CTAS.
+  int g = (int)(((long long)a->rows * a->k + 4095) / 4096);
+  if (g > UB_AR_MAX_CTAS) g = UB_AR_MAX_CTAS;
+  if (g > a->rows) g = a->rows;
+  if (g < 1) g = 1;
+  ub::pair_gather_oneshot_kernel<<<g, 256, 0, (cudaStream_t)stream_v>>>(*a);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+// ----------------------------------------------------------------------------------------------
 // F4: vocabulary-parallel greedy merge.  Every rank holds, per sampled row, the best (value, id) of its
 // vocabulary shard.  One single-block kernel pushes the pairs into every peer's slot [parity][rank],
 // bumps the peers' counters, waits (bounded) until all `world` ranks have arrived for this exchange and

@@ -1207,7 +1207,11 @@ static GemmPlan plan_gemm(const UbGemmArgs* a) {
     }
     // tiles beyond one round of the SM pairs: the 1-CTA schedule splits its thin last round over K, pairs cannot
     const int pairs_now = max_active_clusters(2);
-    const bool ragged = tiles2 > pairs_now && (tiles2 % pairs_now) * 2 <= pairs_now && (tiles2 % pairs_now) != 0;
+    // ... but a pair tile moves a third less data into shared memory per FLOP, so the pairs still win unless the last
+    // round wastes more than 0.4 of the launch (1020 x 6144 x 4096: 96 pair tiles in two rounds, 56.7 us against 63.6 us)
+    const int rounds2 = (tiles2 + pairs_now - 1) / pairs_now;
+    const bool ragged = tiles2 > pairs_now && (tiles2 % pairs_now) != 0 &&
+                        (rounds2 * pairs_now - tiles2) * 10 > rounds2 * pairs_now * 4;
     const int want_s = a->pair_splits > 0 ? a->pair_splits : s2;
     // short K in a single wave: the narrow 1-CTA tiles chosen above (more CTAs, shorter exposed epilogues) win
     const bool short_single = !dual && num_kb <= 32 && tiles2 <= pairs_now;

@@ -187,8 +187,38 @@ typedef struct UbSampleArgs {
   int B, V;
   int vocab_offset;          /* added to the returned ids (vocab-parallel shards) */
   int* err;
+  /* Vocabulary-parallel sampling in two stages.  Stage 1 (cand_vals != NULL, on every shard): instead of drawing, the
+     row's best min(k, cand_k) entries after penalty and temperature go to cand_vals / cand_ids [B, cand_k] (value
+     descending, global id = index + vocab_offset, unused slots -inf / -1); rows need top_k > 0 or top_p < 1.
+     Stage 2 (id_map != NULL, identical on every rank): `logits` holds the gathered fp32 candidates [B, V = world * cand_k]
+     (already scaled), id_map [B, ld] their global ids: top-k / top-p / draw as usual, out_ids = id_map[picked]. */
+  float* cand_vals;
+  int* cand_ids;
+  int cand_k;
+  const int* id_map;
 } UbSampleArgs;
 int ub_sample(const UbSampleArgs* args, void* stream);
+/* One-shot all-gather of (value, id) pairs through peer memory: every rank contributes `rows` x `k` pairs; row s of
+   out_vals / out_ids ([rows, world * k], local) receives the ranks' pairs in rank order.  Same protocol as the one-shot
+   all-reduce (parity slots, one arrival counter per CTA, bounded waits, exchange number in a device word). */
+typedef struct UbPairGatherArgs {
+  const float* vals;          /* [rows, k] */
+  const int* ids;
+  float* out_vals;            /* [rows, world * k] */
+  int* out_ids;
+  void* peer_vals[UB_MAX_RANKS];   /* per rank: fp32 [2][cap pairs * world] receive slots */
+  void* peer_ids[UB_MAX_RANKS];
+  uint32_t* peer_flags[UB_MAX_RANKS];
+  const float* my_vals;
+  const int* my_ids;
+  const uint32_t* my_flags;
+  uint32_t* round;
+  uint32_t* done_count;
+  int world, rank, rows, k;
+  long long cap;              /* pairs per rank the slots can hold (rows * k <= cap) */
+  int* err;
+} UbPairGatherArgs;
+int ub_pair_gather_oneshot(const UbPairGatherArgs* args, void* stream);
 /* vals/ids [world, B] per-shard greedy winners -> out_ids [B]; lowest id wins ties. */
 int ub_argmax_merge(const float* vals, const int* ids, int world, int B, int* out_ids, void* stream);
 

@@ -49,7 +49,7 @@ __device__ __forceinline__ uint32_t f2key(float f) {  // order-preserving float 
 }
 
 struct RowReader {
-  const void* base; int f32; const uint32_t* bitmap; float pen; float inv_t;
+  const void* base; int f32; const uint32_t* bitmap; float pen; float inv_t;   // inv_t = 1 for pre-scaled candidates
   __device__ __forceinline__ float operator()(int i) const {
     float v = f32 ? reinterpret_cast<const float*>(base)[i]
                   : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[i]);
@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(SB) sample_kernel(const UbSampleArgs a) {
   RowReader rd;
   rd.base = a.logits_f32 ? (const void*)(reinterpret_cast<const float*>(a.logits) + (long long)row * a.ld)
                          : (const void*)(reinterpret_cast<const __nv_bfloat16*>(a.logits) + (long long)row * a.ld);
-  rd.f32 = a.logits_f32; rd.bitmap = bitmap; rd.pen = pen; rd.inv_t = greedy ? 1.f : 1.f / temp;
+  rd.f32 = a.logits_f32; rd.bitmap = bitmap; rd.pen = pen; rd.inv_t = (greedy || a.id_map != nullptr) ? 1.f : 1.f / temp;
 
   // ---- max / argmax ----
   float best = -CUDART_INF_F; int best_i = 0x7fffffff;
@@ -161,16 +161,25 @@ __global__ void __launch_bounds__(SB) sample_kernel(const UbSampleArgs a) {
   const int imax = red_i[0];
   if (greedy) {
     if (tid == 0) {
-      a.out_ids[row] = (imax == 0x7fffffff ? 0 : imax) + a.vocab_offset;
+      const int pick = imax == 0x7fffffff ? 0 : imax;
+      a.out_ids[row] = a.id_map != nullptr ? a.id_map[(long long)row * a.ld + pick] : pick + a.vocab_offset;
       if (a.out_vals != nullptr) a.out_vals[row] = vmax;
+    }
+    if (a.cand_vals != nullptr) {
+      // stage 1 of a vocabulary-parallel draw, greedy row: the shard's winner is its only candidate
+      for (int j = tid; j < a.cand_k; j += SB) {
+        a.cand_vals[(long long)row * a.cand_k + j] = j == 0 ? vmax : -CUDART_INF_F;
+        a.cand_ids[(long long)row * a.cand_k + j] = j == 0 ? (imax == 0x7fffffff ? 0 : imax) + a.vocab_offset : -1;
+      }
     }
     return;
   }
   const float u = philox_uniform(a.seed, a.step, (uint32_t)row);
   int k = a.top_k != nullptr ? a.top_k[row] : 0;
   const float top_p = a.top_p != nullptr ? a.top_p[row] : 1.f;
-  if (k <= 0 && top_p < 1.f) k = SB;
+  if (k <= 0 && (top_p < 1.f || a.cand_vals != nullptr)) k = SB;
   if (k > SB) k = SB;
+  if (a.cand_vals != nullptr && k > a.cand_k) k = a.cand_k;
   if (k > V) k = V;
 
   if (k <= 0) {
@@ -191,7 +200,8 @@ __global__ void __launch_bounds__(SB) sample_kernel(const UbSampleArgs a) {
     }
     __syncthreads();
     if (tid == 0) {
-      a.out_ids[row] = (sh_pick < 0 ? imax : sh_pick) + a.vocab_offset;
+      const int pick = sh_pick < 0 ? imax : sh_pick;
+      a.out_ids[row] = a.id_map != nullptr ? a.id_map[(long long)row * a.ld + pick] : pick + a.vocab_offset;
       if (a.out_vals != nullptr) a.out_vals[row] = vmax;
     }
     return;
@@ -258,6 +268,15 @@ __global__ void __launch_bounds__(SB) sample_kernel(const UbSampleArgs a) {
       __syncthreads();
     }
   }
+  if (a.cand_vals != nullptr) {
+    // stage 1 of a vocabulary-parallel draw: hand the sorted survivors to the merge
+    for (int j = tid; j < a.cand_k; j += SB) {
+      const bool ok = j < ncand && cand_i[j] != 0x7fffffff;
+      a.cand_vals[(long long)row * a.cand_k + j] = ok ? cand_v[j] : -CUDART_INF_F;
+      a.cand_ids[(long long)row * a.cand_k + j] = ok ? cand_i[j] + a.vocab_offset : -1;
+    }
+    return;
+  }
   // ---- softmax over survivors, nucleus cut, draw ----
   const float pv = tid < ncand ? __expf(cand_v[tid] - vmax) : 0.f;
   float total;
@@ -276,7 +295,8 @@ __global__ void __launch_bounds__(SB) sample_kernel(const UbSampleArgs a) {
   if (tid <= cut && incl > target && excl <= target) atomicMin(&sh_pick, tid);
   __syncthreads();
   if (tid == 0) {
-    a.out_ids[row] = cand_i[sh_pick] + a.vocab_offset;
+    const int pick = cand_i[sh_pick];
+    a.out_ids[row] = a.id_map != nullptr ? a.id_map[(long long)row * a.ld + pick] : pick + a.vocab_offset;
     if (a.out_vals != nullptr) a.out_vals[row] = vmax;
   }
 }
@@ -297,6 +317,8 @@ __global__ void argmax_merge_kernel(const float* vals, const int* ids, int world
 
 extern "C" int ub_sample(const UbSampleArgs* a, void* stream_v) {
   if (a->B <= 0) return 0;
+  if (a->cand_vals != nullptr && (a->cand_ids == nullptr || a->cand_k <= 0 || a->cand_k > ub::SB)) return -2;
+  if (a->id_map != nullptr && (!a->logits_f32 || a->cand_vals != nullptr)) return -2;
   size_t dyn = 0;
   if (a->rep_penalty != nullptr && a->prev_ids != nullptr && a->V <= ub::MAXV_BITMAP) dyn = ((size_t)a->V + 31) / 32 * 4;
   ub::sample_kernel<<<a->B, ub::SB, dyn, (cudaStream_t)stream_v>>>(*a);

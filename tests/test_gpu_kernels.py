@@ -554,3 +554,113 @@ def test_encoder_attention_takes_the_kernel_path():
     got = mg.forward(ModelInputs.text(ids.cuda())).main_tensor().float().cpu()
     assert K.attn_prefill_last_path() in ("mma.sync", "tcgen05")
     assert (got - ref).abs().max().item() < 0.08 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,P,B", [(16, 4, 128, 64, 700), (4, 1, 128, 1024, 130), (8, 8, 64, 0, 90), (24, 2, 128, 48, 40),
+                                         (40, 2, 64, 16, 33)])
+def test_decode_warp_pipelines(Hq, Hkv, D, P, B):
+    """The decode kernel with one copy / MMA pipeline per warp: more items than warps (a warp walks over several, with the
+    next one's length and block-table entries requested early), fewer items than warps (deep ring), GQA groups of 1, 4,
+    12 and 20 heads (MMA rows 8..15 in use, two row chunks per KV head), ranges longer than 32 pages (block-table
+    entries reloaded), ranges that end before they start, first pages that start inside a page, with and without the
+    fused merge; oracle = fp32 attention over the visible keys."""
+    from unillm_b200.ops import cuda_ops
+
+    g = torch.Generator().manual_seed(B + Hq)
+    kv_lens = [int(v) for v in torch.randint(P + 1, P + 230, (B,), generator=g)]
+    kv_lens[1] = P + 700                                    # 44 pages: more than one round of block-table entries
+    kv_lens[2] = max(P, 1)
+    if P >= 7:
+        kv_lens[3] = P - 7
+    kc, vc, bt, sl, dk, dv = make_paged_cache(B, kv_lens, Hkv, D, seed=51)
+    q = _rand(B, Hq, D, seed=52)
+    start = P if P != 48 else 43                            # a range that starts in the middle of a page
+    out, lse = cuda_ops.attn_decode(q, kc, vc, bt, sl, kv_start=start, splits=1, return_lse=True, kernel="warp")
+    oa = _rand(B, Hq, D, seed=53)
+    la = torch.randn(B, Hq, generator=torch.Generator().manual_seed(54)).cuda()
+    fused = cuda_ops.attn_decode(q, kc, vc, bt, sl, kv_start=start, splits=1, merge=(oa, la), kernel="warp")
+    sep = cuda_ops.attn_merge(oa, la, out, lse)
+    torch.cuda.synchronize()
+    cuda_ops.check_device_errors()
+    for i in sorted({0, 1, 2, 3, 4, B // 2, B - 2, B - 1}):
+        l = kv_lens[i]
+        if l <= start:
+            assert out[i].abs().max().item() == 0.0 and torch.isinf(lse[i]).all()
+            continue
+        ro, rl = ref_attention(q[i:i + 1].cpu(), dk[i], dv[i], causal_offset=l - 1, kv_start=start)
+        _close(out[i:i + 1], ro)
+        _close(lse[i:i + 1], rl, rtol=1e-2, atol=1e-2)
+    _close(fused, sep, rtol=2e-2, atol=1e-2)
+    # and it agrees with the dispatcher's default kernel on every row
+    ref = cuda_ops.attn_decode(q, kc, vc, bt, sl, kv_start=start, splits=1)
+    _close(out, ref.float(), rtol=1e-2, atol=5e-3)
+
+
+def test_vocab_parallel_sampling_in_two_stages_equals_the_single_shard_draw():
+    """Top-k / top-p draws over a vocabulary cut into shards: every shard hands in its best candidates after penalty
+    and temperature, the merge over all shards' candidates (here: concatenated by hand, as the pair gather delivers them)
+    draws the same token as the kernel that sees the whole row -- for top-k rows, top-p rows, rows with both, greedy rows
+    in the same batch and a repetition penalty."""
+    from unillm_b200.ops import cuda_ops as K
+
+    B, V, W = 12, 4096, 4
+    g = torch.Generator().manual_seed(9)
+    logits = (torch.randn(B, V, generator=g) * 3).to(torch.bfloat16).cuda()
+    temp = torch.tensor([0.7, 1.0, 1.3, 0.0, 0.9, 1.0, 0.5, 2.0, 1.0, 0.0, 1.1, 0.8]).cuda()
+    top_p = torch.tensor([1.0, 0.9, 0.5, 1.0, 0.95, 1.0, 0.3, 0.99, 0.8, 1.0, 1.0, 0.6]).cuda()
+    top_k = torch.tensor([40, 0, 0, 0, 64, 1, 5, 0, 17, 0, 3, 0], dtype=torch.int32).cuda()
+    pen = torch.full((B,), 1.2).cuda()
+    prev = torch.randint(0, V, (B, 9), generator=g).to(torch.int32).cuda()
+    for step in range(4):
+        ref = K.sample(logits, temperature=temp, top_p=top_p, top_k=top_k, rep_penalty=pen, prev_ids=prev, seed=123, step=step)
+        kc = 1024
+        cvs, cis = [], []
+        for r in range(W):
+            shard = logits[:, r * (V // W):(r + 1) * (V // W)].contiguous()
+            pr = prev - r * (V // W)                  # history in shard coordinates (out-of-range ids are ignored)
+            cv, ci = K.sample(shard, temperature=temp, top_p=top_p, top_k=top_k, rep_penalty=pen, prev_ids=pr.contiguous(),
+                              seed=123, step=step, vocab_offset=r * (V // W), candidates=kc)
+            cvs.append(cv)
+            cis.append(ci)
+        av = torch.cat(cvs, 1).contiguous()
+        ai = torch.cat(cis, 1).contiguous()
+        got = K.sample(av, temperature=temp, top_p=top_p, top_k=top_k, seed=123, step=step, id_map=ai)
+        assert torch.equal(got.cpu(), ref.cpu()), (step, got.cpu().tolist(), ref.cpu().tolist())
+    # the candidate lists are sorted, global ids, padded with -inf / -1
+    assert bool((cvs[1][:, :-1] >= cvs[1][:, 1:]).all())
+    ok = cis[1] >= 0
+    assert bool(((cis[1] >= V // W) & (cis[1] < 2 * (V // W)))[ok].all())
+
+
+def test_pair_gather_emulated_ranks():
+    """The one-shot (value, id) all-gather with all ranks emulated on one GPU.  Kernels of different emulated ranks
+    cannot wait for one another on one stream, so every rank's counters are credited up front with the arrivals of the
+    ranks that launch after it; the last launch sees all data and its result is checked.  Two exchanges in a row
+    cover the parity slots and the counted (never reset) arrival words."""
+    from unillm_b200.dist.fused import SG_FLAGS, FusedComm
+
+    W, rows, k = 4, 37, 24
+    comms = FusedComm.emulated(W, 256, 64, "cuda")
+    g = torch.Generator().manual_seed(1)
+    vals = [torch.randn(rows, k, generator=g).cuda() for _ in range(W)]
+    ids = [torch.randint(0, 1 << 20, (rows, k), generator=g).to(torch.int32).cuda() for _ in range(W)]
+    for rnd in range(1, 3):
+        outs = None
+        for r in range(W):
+            c = comms[r]
+            fl = c.buf[c.flags.offset:c.flags.offset + 1024].view(torch.int32)
+            fl[SG_FLAGS:SG_FLAGS + 64] += (W - 1 - r)
+        for r in range(W):
+            outs = comms[r].gather_pairs(vals[r], ids[r])
+        torch.cuda.synchronize()
+        from unillm_b200.ops import cuda_ops as K
+        K.check_device_errors()
+        ov, oi = outs
+        assert torch.equal(ov, torch.cat(vals, 1)) and torch.equal(oi, torch.cat(ids, 1))
+        for r in range(W):
+            c = comms[r]
+            fl = c.buf[c.flags.offset:c.flags.offset + 1024].view(torch.int32)
+            # every rank's counters end at rnd * W plus its pre-credit: remove the credit so both rounds start alike
+            fl[SG_FLAGS:SG_FLAGS + 64] -= (W - 1 - r)
+            assert int(fl[SG_FLAGS]) == rnd * W
+        vals = [v + 1 for v in vals]

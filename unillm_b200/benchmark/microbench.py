@@ -179,6 +179,12 @@ def bench_attn(results, case="all"):
                  frac_hbm=byts / med / 1e6 / hbm, peaks=how)
         results.append(r)
         print(json.dumps(r))
+        # one pipeline per warp, no KV split
+        med, best = time_ms(lambda: cuda_ops.attn_decode(q, kc, vc, bt, sl, out=out, splits=1, kernel="warp"))
+        r = dict(kind="attn_decode", kernel="warp", B=B, ctx=ctx, Hq=Hq, Hkv=Hkv, D=D, ms=med, best_ms=best,
+                 gbs=byts / med / 1e6, frac_hbm=byts / med / 1e6 / hbm, peaks=how)
+        results.append(r)
+        print(json.dumps(r))
         # the same problem through the prefill kernels (one query token per sequence)
         qs1 = torch.arange(B + 1, dtype=torch.int32, device="cuda")
         med, best = time_ms(lambda: cuda_ops.attn_prefill(q, kc, vc, bt, sl, qs1, 1, out=out, causal=True))
@@ -205,6 +211,12 @@ def bench_attn(results, case="all"):
         byts = 2.0 * 2 * sum(l - pre for l in lens) * Hkv * D
         r = dict(kind="attn_decode_suffix", B=B, prefix=pre, suffix="128..256", Hq=Hq, Hkv=Hkv, D=D, ms=med, best_ms=best,
                  gbs=byts / med / 1e6, frac_hbm=byts / med / 1e6 / hbm, peaks=how)
+        results.append(r)
+        print(json.dumps(r))
+        med, best = time_ms(lambda: cuda_ops.attn_decode(q, kc, vc, bt, sl, out=out, kv_start=pre, splits=1, merge=(oa, la),
+                                                         kernel="warp"))
+        r = dict(kind="attn_decode_suffix", kernel="warp", B=B, prefix=pre, suffix="128..256", Hq=Hq, Hkv=Hkv, D=D, ms=med,
+                 best_ms=best, gbs=byts / med / 1e6, frac_hbm=byts / med / 1e6 / hbm, peaks=how)
         results.append(r)
         print(json.dumps(r))
     prefill_cases = [(2048, 2048, 32, 8, 128, True), (8192, 8192, 4, 1, 128, True), (256, 1024, 32, 8, 128, False),
@@ -317,6 +329,10 @@ def bench_tp_layer(results, world=8, batch=512, variants=False):
                                                      merge=(oa[:B], la[:B])))
     byts = 2.0 * 2 * sum(l - pre for l in lens) * Hkv * D
     rec("attn_decode_suffix", med, best, B=B, gbs=byts / med / 1e6, frac_hbm=byts / med / 1e6 / hbm)
+    for kern in ("warp",) if variants else ():
+        med, best = time_ms(lambda: cuda_ops.attn_decode(q[:B], kc, vc, bt[:B], sl_d, out=out[:B], kv_start=pre, splits=1,
+                                                         merge=(oa[:B], la[:B]), kernel=kern))
+        rec("attn_decode_suffix", med, best, B=B, kernel=kern, gbs=byts / med / 1e6, frac_hbm=byts / med / 1e6 / hbm)
     sl_p = torch.full((P,), pre + 128, dtype=torch.int32, device=dev)
     qs_p = (torch.arange(P + 1, dtype=torch.int32) * 128).to(dev)
     med, best = time_ms(lambda: cuda_ops.attn_prefill(q[B:], kc, vc, bt[B:], sl_p, qs_p, 128, causal=True, kv_start=pre,

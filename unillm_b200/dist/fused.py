@@ -41,6 +41,9 @@ AR_FLAGS = 64                            # ... and its 64 per-CTA arrival counte
 AR_ROWS = 32                             # token rows the one-shot all-reduce area holds (decode-sized messages)
 ARGMAX_FLAG, ARGMAX_ROUND = 32, 33     # counter of the greedy merge and its (local) round word
 LOCAL_RS0, LOCAL_RS1, LOCAL_AG0, LOCAL_AG1 = 40, 41, 42, 43   # local arrival counters of the producing launches
+SG_ROUND, SG_DONE = 49, 50               # pair gather of vocabulary-parallel sampling: exchanges completed, CTAs finished
+SG_FLAGS = 128                           # ... and its 64 per-CTA arrival counters (words 128..191)
+SG_PAIRS = 32768                         # (value, id) pairs per rank and exchange the gather area holds (rows x k)
 DISP_FLAG, DISP_ROUND, LOCAL_DISP = 46, 47, 48   # sparse MoE dispatch: arrivals (peers), uses so far and CTA counter (local)
 ARGMAX_ROWS = 2048                      # sampled rows per step the merge area can hold
 
@@ -77,10 +80,14 @@ class FusedComm:
         self.am_ids = _Area(4 * slot + FLAG_WORDS * 4 + am, am)
         self.ar_elems = AR_ROWS * hidden                       # bf16 elements per rank slot of the one-shot all-reduce
         self.ar_slots = _Area(self.am_ids.offset + am, 2 * world * self.ar_elems * 2)
+        end0 = self.ar_slots.offset + self.ar_slots.nbytes
+        sg = 2 * world * SG_PAIRS * 4
+        self.sg_vals = _Area(end0, sg)
+        self.sg_ids = _Area(end0 + sg, sg)
         # sparse expert-parallel MoE (F5 / F6): receive rows [world][cap][H] with their metadata and the count header,
         # and the combine area [K][rows][H]; sized for cap = max_rows * K
         self.moe_top_k, self.moe_experts = moe_top_k, moe_experts
-        end = self.ar_slots.offset + self.ar_slots.nbytes
+        end = self.sg_ids.offset + self.sg_ids.nbytes
         if moe_top_k:
             pairs = world * self.max_rows * moe_top_k
             self.disp_rows = _Area(end, pairs * hidden * 2)
@@ -93,7 +100,7 @@ class FusedComm:
     def nbytes(world: int, hidden: int, max_tokens: int, moe_top_k: int = 0, moe_experts: int = 0) -> int:
         rows = (max_tokens + world - 1) // world
         n = (4 * world * rows * hidden * 2 + FLAG_WORDS * 4 + 2 * (2 * world * ARGMAX_ROWS * 4) +
-             2 * world * AR_ROWS * hidden * 2)
+             2 * world * AR_ROWS * hidden * 2 + 2 * (2 * world * SG_PAIRS * 4))
         if moe_top_k:
             pairs = world * rows * moe_top_k
             n += pairs * hidden * 2 + pairs * 16 + (max(moe_experts, 1) * 4 + 255) // 256 * 256 + moe_top_k * rows * hidden * 2
@@ -321,6 +328,41 @@ class FusedComm:
         N.check(N.cuda_lib().ub_allreduce_oneshot(C.byref(a), torch.cuda.current_stream(self.device).cuda_stream),
                 "ub_allreduce_oneshot")
         return t
+
+    def can_gather_pairs(self, rows: int, k: int) -> bool:
+        return 0 < rows * k <= SG_PAIRS
+
+    def gather_pairs(self, vals: torch.Tensor, ids: torch.Tensor):
+        """F4s: ``vals`` / ``ids`` [rows, k] (fp32 / int32) of every rank -> ([rows, world * k], [rows, world * k]) in rank
+        order, identical on every rank, through peer memory (no NCCL call)."""
+        import ctypes as C
+
+        from ..ops import _native as N
+        from ..ops import cuda_ops
+
+        rows, k = vals.shape
+        if vals.dtype != torch.float32 or ids.dtype != torch.int32 or not vals.is_contiguous() or not ids.is_contiguous() \
+                or not self.can_gather_pairs(rows, k):
+            raise ValueError("gather_pairs takes contiguous fp32 / int32 [rows, k] with rows * k <= SG_PAIRS")
+        ov = torch.empty(rows, self.world * k, dtype=torch.float32, device=self.device)
+        oi = torch.empty(rows, self.world * k, dtype=torch.int32, device=self.device)
+        a = N.UbPairGatherArgs()
+        a.vals, a.ids, a.out_vals, a.out_ids = vals.data_ptr(), ids.data_ptr(), ov.data_ptr(), oi.data_ptr()
+        for r in range(self.world):
+            a.peer_vals[r] = self._peer(r, self.sg_vals)
+            a.peer_ids[r] = self._peer(r, self.sg_ids)
+            a.peer_flags[r] = self.flag_ptr(r, SG_FLAGS)
+        a.my_vals = self.buf.data_ptr() + self.sg_vals.offset
+        a.my_ids = self.buf.data_ptr() + self.sg_ids.offset
+        a.my_flags = self.local_flag_ptr(SG_FLAGS)
+        a.round, a.done_count = self.local_flag_ptr(SG_ROUND), self.local_flag_ptr(SG_DONE)
+        a.world, a.rank, a.rows, a.k, a.cap = self.world, self.rank, rows, k, SG_PAIRS
+        a.err = cuda_ops.err_word(self.device).data_ptr()
+        lib = N.cuda_lib()
+        lib.ub_pair_gather_oneshot.restype = C.c_int
+        N.check(lib.ub_pair_gather_oneshot(C.byref(a), torch.cuda.current_stream(self.device).cuda_stream),
+                "ub_pair_gather_oneshot")
+        return ov, oi
 
     def can_all_reduce(self, t: torch.Tensor) -> bool:
         return t.dtype == torch.bfloat16 and t.is_contiguous() and t.numel() % 8 == 0 and t.numel() <= self.ar_elems

@@ -1032,6 +1032,17 @@ class GpuModelRunner:
             K.argmax_merge(allv.contiguous(), alli.contiguous(), out=out)
             self.launches += 2
             return out
+        kc = fl.get("cand_k", 0)
+        if tp.comm is not None and kc and tp.comm.can_gather_pairs(S, kc):
+            # F4s: every shard hands in the best `kc` entries of each row (after temperature), the pairs are gathered
+            # over peer memory and every rank draws the same token from them -- the whole-vocabulary logits stay put
+            cv, ci = K.sample(logits, temperature=fl["temperature"], top_p=fl["top_p"], top_k=fl["top_k"], seed=fl["seed"],
+                              step=fl["step"], vocab_offset=tp.rank * self.w.vocab_shard, candidates=kc)
+            av, ai = tp.comm.gather_pairs(cv, ci)
+            K.sample(av, temperature=fl["temperature"], top_p=fl["top_p"], top_k=fl["top_k"], seed=fl["seed"],
+                     step=fl["step"], out_ids=out, id_map=ai)
+            self.launches += 3
+            return out
         full = tp.all_gather_cat(logits, dim=-1)
         K.sample(full, temperature=fl["temperature"], top_p=fl["top_p"], top_k=fl["top_k"], seed=fl["seed"],
                  step=fl["step"], out_ids=out)
@@ -1060,8 +1071,21 @@ class GpuModelRunner:
         if b.top_k is not None and any(k and k > 0 for k in b.top_k):
             tk = torch.as_tensor([k or 0 for k in b.top_k], dtype=torch.int32).to(self.device, non_blocking=True)
             self.h2d_bytes += 4 * S
+        # candidates per row and shard that a vocabulary-parallel draw has to exchange: the row's top_k, or the 1024
+        # survivors that a top-p draw keeps; 0 = some row samples from the whole vocabulary (logits are gathered then)
+        cand = 1
+        for i, t in enumerate(b.temperature):
+            if t <= 0:
+                continue
+            k = b.top_k[i] if b.top_k is not None and b.top_k[i] else 0
+            p = b.top_p[i] if b.top_p is not None else 1.0
+            k = min(k, 1024) if k > 0 else (1024 if p < 1.0 else 0)
+            if k == 0:
+                cand = 0
+                break
+            cand = max(cand, k)
         return {"temperature": self.fmeta_dev[:S], "top_p": self.fmeta_dev[S:2 * S], "top_k": tk, "seed": b.seed,
-                "step": b.step}
+                "step": b.step, "cand_k": cand}
 
     MAX_GRAPHS = 96
 

@@ -86,6 +86,16 @@ class UbSampleArgs(C.Structure):
         ("logits", vp), ("ld", i64), ("logits_f32", i32), ("out_ids", vp), ("out_vals", vp),
         ("temperature", vp), ("top_p", vp), ("top_k", vp), ("rep_penalty", vp), ("prev_ids", vp), ("prev_ld", i32),
         ("seed", u64), ("step", u64), ("B", i32), ("V", i32), ("vocab_offset", i32), ("err", vp),
+        ("cand_vals", vp), ("cand_ids", vp), ("cand_k", i32), ("id_map", vp),
+    ]
+
+
+class UbPairGatherArgs(C.Structure):
+    _fields_ = [
+        ("vals", vp), ("ids", vp), ("out_vals", vp), ("out_ids", vp), ("peer_vals", vp * UB_MAX_RANKS),
+        ("peer_ids", vp * UB_MAX_RANKS), ("peer_flags", vp * UB_MAX_RANKS), ("my_vals", vp), ("my_ids", vp),
+        ("my_flags", vp), ("round", vp), ("done_count", vp), ("world", i32), ("rank", i32), ("rows", i32), ("k", i32),
+        ("cap", i64), ("err", vp),
     ]
 
 

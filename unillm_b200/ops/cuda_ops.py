@@ -256,8 +256,11 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, b
                 seq_lens: torch.Tensor, *, scale: Optional[float] = None, window: int = 0, kv_start: int = 0,
                 alibi_slopes: Optional[torch.Tensor] = None, splits: int = 0, scratch: Optional[torch.Tensor] = None,
                 out: Optional[torch.Tensor] = None, return_lse: bool = False, lse: Optional[torch.Tensor] = None,
-                max_seq_len: Optional[int] = None, merge: Optional[tuple] = None):
-    """One query token per sequence.  q: [B, Hq, D] (last two dims contiguous); caches [nb, Hkv, bs, D]."""
+                max_seq_len: Optional[int] = None, merge: Optional[tuple] = None, kernel: Optional[str] = None):
+    """One query token per sequence.  q: [B, Hq, D] (last two dims contiguous); caches [nb, Hkv, bs, D].
+
+    ``kernel="warp"`` calls the warp-per-item kernel directly (page size 16, head size 64 / 128, ``splits == 1``, no
+    window, no ALiBi) instead of going through the dispatcher's choice."""
     _bf16c(q, "q")
     B, Hq, D = q.shape
     Hkv = k_cache.shape[1]
@@ -281,7 +284,13 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, b
     a.alibi_slopes = _p(alibi_slopes)
     if merge is not None:        # (o [B, Hq, D] bf16 contiguous, lse [B, Hq] fp32): partial over a disjoint key set
         a.merge_o, a.merge_lse = merge[0].data_ptr(), merge[1].data_ptr()
-    N.check(N.cuda_lib().ub_attn_decode(C.byref(a), _stream(q)), "ub_attn_decode")
+    if kernel == "warp":
+        lib = N.cuda_lib()
+        if not lib.ub_attn_decode_warp_supported(C.byref(a)):
+            raise ValueError("attn_decode(kernel='warp'): page size 16, head size 64 / 128, one split, no window / ALiBi")
+        N.check(lib.ub_attn_decode_warp(C.byref(a), _stream(q)), "ub_attn_decode_warp")
+    else:
+        N.check(N.cuda_lib().ub_attn_decode(C.byref(a), _stream(q)), "ub_attn_decode")
     return (out, lse) if return_lse else out
 
 
@@ -398,8 +407,13 @@ def sample(logits: torch.Tensor, *, temperature: Optional[torch.Tensor] = None, 
            top_k: Optional[torch.Tensor] = None, rep_penalty: Optional[torch.Tensor] = None,
            prev_ids: Optional[torch.Tensor] = None, seed: int = 0, step: int = 0, vocab_offset: int = 0,
            out_ids: Optional[torch.Tensor] = None, out_vals: Optional[torch.Tensor] = None,
-           return_vals: bool = False):
-    """Greedy when ``temperature`` is None (or <= 0 for a row); otherwise temperature / top-k / top-p."""
+           return_vals: bool = False, candidates: int = 0, id_map: Optional[torch.Tensor] = None):
+    """Greedy when ``temperature`` is None (or <= 0 for a row); otherwise temperature / top-k / top-p.
+
+    Vocabulary-parallel draws run in two stages.  ``candidates = k`` (on every shard, with ``vocab_offset``): returns
+    ``(vals [B, k] fp32, ids [B, k] int32)``, the row's best entries after penalty and temperature, instead of drawing.
+    ``id_map`` (identical on every rank): ``logits`` are the gathered fp32 candidates ``[B, world * k]`` and ``id_map``
+    their global ids; the usual top-k / top-p / draw runs over them and returns global ids."""
     if logits.dim() != 2 or logits.stride(1) != 1:
         raise ValueError("logits must be [B, V] with contiguous rows")
     if logits.dtype not in (torch.bfloat16, torch.float32):
@@ -417,7 +431,19 @@ def sample(logits: torch.Tensor, *, temperature: Optional[torch.Tensor] = None, 
         a.prev_ids, a.prev_ld = prev_ids.data_ptr(), prev_ids.shape[1]
     a.seed, a.step, a.B, a.V, a.vocab_offset = seed & (2**64 - 1), step, B, V, vocab_offset
     a.err = err_word(logits.device).data_ptr()
+    cv = ci = None
+    if candidates:
+        cv = torch.empty(B, candidates, dtype=torch.float32, device=logits.device)
+        ci = torch.empty(B, candidates, dtype=torch.int32, device=logits.device)
+        a.cand_vals, a.cand_ids, a.cand_k = cv.data_ptr(), ci.data_ptr(), candidates
+    if id_map is not None:
+        if id_map.dtype != torch.int32 or id_map.shape != logits.shape or not id_map.is_contiguous() or \
+                logits.dtype != torch.float32 or not logits.is_contiguous():
+            raise ValueError("id_map: int32, contiguous, same shape as the contiguous fp32 candidate values")
+        a.id_map = id_map.data_ptr()
     N.check(N.cuda_lib().ub_sample(C.byref(a), _stream(logits)), "ub_sample")
+    if candidates:
+        return cv, ci
     return (out_ids, out_vals) if return_vals else out_ids
 
 
