@@ -70,10 +70,14 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return red[0];
 }
 
+// CH > 0: H is a multiple of 8 and at most 2048 * CH, every thread keeps its (at most CH) 16-byte chunks of the row in
+// registers between the two passes; CH == 0: any H, the row is staged in shared memory as fp32.
+template <int CH>
 __global__ void __launch_bounds__(256) norm_kernel(const NormParams p) {
   pdl_launch_dependents();     // the next kernel may start its private set-up now
   pdl_wait();                  // nothing global is touched before the previous kernel has completed
-  extern __shared__ float row[];  // [H]
+  extern __shared__ float row[];  // [H] (CH == 0 only)
+  float fr[CH > 0 ? CH : 1][8];
   __shared__ float red[32];
   __shared__ int wait_failed;
   const int t = blockIdx.x;
@@ -109,7 +113,7 @@ __global__ void __launch_bounds__(256) norm_kernel(const NormParams p) {
   const long long slot_stride = (long long)p.T * H;
   float ssum = 0.f, ssq = 0.f;
   if (vec) {
-    for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
+    auto load_chunk = [&](int c, float* keep) {
       float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
       for (int s = 0; s < nslots; ++s) {
         // L2-only load: with rs_world > 0 these rows were written by peers and L1 may hold a stale line
@@ -136,7 +140,16 @@ __global__ void __launch_bounds__(256) norm_kernel(const NormParams p) {
         *reinterpret_cast<uint4*>(p.residual_out + (long long)t * H + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
       }
 #pragma unroll
-      for (int e = 0; e < 8; ++e) { row[c * 8 + e] = f[e]; ssum += f[e]; ssq += f[e] * f[e]; }
+      for (int e = 0; e < 8; ++e) { keep[e] = f[e]; ssum += f[e]; ssq += f[e] * f[e]; }
+    };
+    if constexpr (CH > 0) {
+#pragma unroll
+      for (int k = 0; k < CH; ++k) {
+        const int c = threadIdx.x + k * 256;
+        if (c < H / 8) load_chunk(c, fr[k]);
+      }
+    } else {
+      for (int c = threadIdx.x; c < H / 8; c += blockDim.x) load_chunk(c, row + c * 8);
     }
   } else {
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
@@ -156,7 +169,16 @@ __global__ void __launch_bounds__(256) norm_kernel(const NormParams p) {
     mean = block_sum(ssum, red) / H;
     // two-pass variance for accuracy
     float sv = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) { float d = row[i] - mean; sv += d * d; }
+    if constexpr (CH > 0) {
+#pragma unroll
+      for (int k = 0; k < CH; ++k)
+        if (threadIdx.x + k * 256 < H / 8) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) { const float d = fr[k][e] - mean; sv += d * d; }
+        }
+    } else {
+      for (int i = threadIdx.x; i < H; i += blockDim.x) { float d = row[i] - mean; sv += d * d; }
+    }
     rstd = rsqrtf(block_sum(sv, red) / H + p.eps);
   } else {
     rstd = rsqrtf(block_sum(ssq, red) / H + p.eps);
@@ -164,7 +186,7 @@ __global__ void __launch_bounds__(256) norm_kernel(const NormParams p) {
 
   const float woff = p.weight_offset_one ? 1.f : 0.f;
   if (vec) {
-    for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
+    auto store_chunk = [&](int c, const float* kept) {
       float w[8], b[8];
       if (p.weight != nullptr) {
         const uint4 v = *reinterpret_cast<const uint4*>(p.weight + c * 8);
@@ -187,8 +209,8 @@ __global__ void __launch_bounds__(256) norm_kernel(const NormParams p) {
       uint32_t o[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float y0 = (row[c * 8 + 2 * e] - mean) * rstd * w[2 * e] + b[2 * e];
-        const float y1 = (row[c * 8 + 2 * e + 1] - mean) * rstd * w[2 * e + 1] + b[2 * e + 1];
+        const float y0 = (kept[2 * e] - mean) * rstd * w[2 * e] + b[2 * e];
+        const float y1 = (kept[2 * e + 1] - mean) * rstd * w[2 * e + 1] + b[2 * e + 1];
         o[e] = pack_bf16x2(y0, y1);
       }
       const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
@@ -202,6 +224,15 @@ __global__ void __launch_bounds__(256) norm_kernel(const NormParams p) {
             *reinterpret_cast<uint4*>(p.ag_peer_out[r] + grow * H + c * 8) = ov;
         }
       }
+    };
+    if constexpr (CH > 0) {
+#pragma unroll
+      for (int k = 0; k < CH; ++k) {
+        const int c = threadIdx.x + k * 256;
+        if (c < H / 8) store_chunk(c, fr[k]);
+      }
+    } else {
+      for (int c = threadIdx.x; c < H / 8; c += blockDim.x) store_chunk(c, row + c * 8);
     }
   } else {
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
@@ -263,15 +294,22 @@ extern "C" int ub_norm(const UbNormArgs* a, void* stream_v) {
     p.ag_peer_out[i] = (__nv_bfloat16*)a->ag_peer_out[i];
     p.ag_peer_flag[i] = a->ag_peer_flag[i];
   }
-  const size_t smem = (size_t)a->H * 4;
-  static bool attr_set[UB_MAX_DEVICES] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (smem > 48 * 1024 && dev < UB_MAX_DEVICES && !attr_set[dev]) {
-    cudaFuncSetAttribute(norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-    attr_set[dev] = true;
+  cudaError_t e;
+  if (a->H % 8 == 0 && a->H <= 2048 * 2) {
+    e = ub::launch_pdl(norm_kernel<2>, dim3(a->T), dim3(256), (size_t)0, (cudaStream_t)stream_v, p);
+  } else if (a->H % 8 == 0 && a->H <= 2048 * 4) {
+    e = ub::launch_pdl(norm_kernel<4>, dim3(a->T), dim3(256), (size_t)0, (cudaStream_t)stream_v, p);
+  } else {
+    const size_t smem = (size_t)a->H * 4;
+    static bool attr_set[UB_MAX_DEVICES] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (smem > 48 * 1024 && dev < UB_MAX_DEVICES && !attr_set[dev]) {
+      cudaFuncSetAttribute(norm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      attr_set[dev] = true;
+    }
+    e = ub::launch_pdl(norm_kernel<0>, dim3(a->T), dim3(256), smem, (cudaStream_t)stream_v, p);
   }
-  cudaError_t e = ub::launch_pdl(norm_kernel, dim3(a->T), dim3(256), smem, (cudaStream_t)stream_v, p);
   if (e == cudaSuccess) e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }
