@@ -1355,10 +1355,20 @@ extern "C" int ub_gemm_num_ctas(const UbGemmArgs* a) {
   return ub::plan_gemm(a).ctas;
 }
 
+extern "C" int ub_gemv_supported(const UbGemmArgs* a);
+extern "C" int ub_gemv(const UbGemmArgs* a, void* stream);
+
 extern "C" int ub_gemm_tn(const UbGemmArgs* a, void* stream_v) {
   using namespace ub;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   if (a->M <= 0 || a->N <= 0 || a->K <= 0) return 0;
+  {
+    // up to 16 tokens: the weight-streaming kernel (csrc/gemm/gemv.cu); UB_GEMV=0 keeps the tcgen05 tiles
+    static int gemv = -1;
+    if (gemv < 0) { const char* e = getenv("UB_GEMV"); gemv = (e != nullptr && e[0] == '0') ? 0 : 1; }
+    if (gemv && a->M <= 16 && a->tile_tokens <= 0 && a->splits <= 0 && a->cta_pair == 0 && ub_gemv_supported(a))
+      return ub_gemv(a, stream_v);
+  }
   if (a->K % 8 != 0 || a->ldx % 8 != 0 || a->ldw % 8 != 0) return -2;  // TMA strides must be 16-byte multiples
   if ((reinterpret_cast<uintptr_t>(a->x) & 15) || (reinterpret_cast<uintptr_t>(a->w) & 15)) return -3;
   const bool dual = a->dual != 0;

@@ -664,3 +664,31 @@ def test_pair_gather_emulated_ranks():
             fl[SG_FLAGS:SG_FLAGS + 64] -= (W - 1 - r)
             assert int(fl[SG_FLAGS]) == rnd * W
         vals = [v + 1 for v in vals]
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K,dual", [(6144, 4096, False), (1000, 520, False), (1792, 4096, True), (37, 264, True)])
+def test_gemv_small_token_counts(M, N, K, dual):
+    """Up to 16 tokens take the weight-streaming kernel (one or two token tiles of 8): plain and gated form, bias, activation, residual, scale,
+    fp32 output, column counts that do not divide by the CTA's eight columns, K that leaves warps without work."""
+    from unillm_b200.ops import cuda_ops as K_
+
+    g = torch.Generator().manual_seed(M * 7 + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(N * (2 if dual else 1), K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+    xf, wf = x.float(), w.float()
+    if dual:
+        got = K_.gemm_tn(x, w, dual_rows=N, act="silu")
+        ref = torch.nn.functional.silu(xf @ wf[:N].t()) * (xf @ wf[N:].t())
+        _close(got, ref, rtol=2e-2, atol=2e-2)
+        return
+    bias = torch.randn(N, generator=g).to(torch.bfloat16).cuda()
+    res = torch.randn(M, N, generator=g).to(torch.bfloat16).cuda()
+    got = K_.gemm_tn(x, w, bias=bias, residual=res, act="gelu", out_scale=0.5)
+    ref = torch.nn.functional.gelu(xf @ wf.t() * 0.5 + bias.float()) + res.float()
+    _close(got, ref, rtol=2e-2, atol=2e-2)
+    got32 = K_.gemm_tn(x, w, out_dtype=torch.float32)
+    _close(got32, xf @ wf.t(), rtol=1e-3, atol=1e-3)
+    # and the tensor-core tiles agree on the same inputs (tile width forced, so the dispatcher does not divert)
+    tc = K_.gemm_tn(x, w, tile_tokens=16)
+    _close(tc, got32, rtol=2e-2, atol=2e-2)

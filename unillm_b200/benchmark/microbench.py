@@ -94,8 +94,12 @@ def time_ms(fn, iters=10, warmup=3, flush=True, reps=8):
 def bench_gemm(results, only=None, tile=0, pair=0):
     hbm, tf, how = _peaks()
     shapes = [only] if only else [
+        # up to 16 tokens: the weight-streaming kernel (Llama-3-8B layer shapes, 70B shard of 8-way tensor parallelism)
+        (1, 6144, 4096, 0), (1, 14336, 4096, 1), (1, 4096, 14336, 0), (4, 6144, 4096, 0), (8, 6144, 4096, 0),
+        (8, 14336, 4096, 1), (16, 6144, 4096, 0), (16, 14336, 4096, 1), (16, 4096, 14336, 0), (32, 6144, 4096, 0),
+        (1, 1280, 8192, 0), (1, 3584, 8192, 1), (1, 8192, 3584, 0), (1, 128256, 4096, 0),
         # (M, N, K, dual) : Llama-3-8B decode / prefill shapes
-        (16, 6144, 4096, 0), (64, 6144, 4096, 0), (256, 6144, 4096, 0), (256, 4096, 4096, 0),
+        (64, 6144, 4096, 0), (256, 6144, 4096, 0), (256, 4096, 4096, 0),
         (256, 14336, 4096, 1), (256, 4096, 14336, 0), (256, 128256, 4096, 0),
         # tensor-parallel (TP=8) per-rank decode shapes: few tiles -> cluster split-K
         (256, 768, 4096, 0), (256, 4096, 512, 0), (256, 1792, 4096, 1), (256, 4096, 1792, 0), (256, 16032, 4096, 0),
