@@ -175,6 +175,26 @@ for mode in modes:
             dist.all_reduce(n)
             out["pairs_received"], out["pairs_sent"] = int(n), d.R * world * d.K
     dist.barrier()
+# top-k / top-p sampling over vocabulary shards: candidate pairs gathered through peer memory against whole rows of
+# logits gathered by NCCL -- same logits, same Philox draws, so the tokens have to be identical
+tp = TpContext(rank, world, dist.group.WORLD, fused=True)
+tp.comm = comm
+w = RunnerWeights.random(spec, f"cuda:{rank}", rank, world, seed=7, expert_parallel=moe)
+sampled = {}
+for how in ("pairs", "nccl"):
+    os.environ["UB_SAMPLE_PAIRS"] = "1" if how == "pairs" else "0"
+    runner = GpuModelRunner(spec, w, num_blocks=128, max_num_seqs=8, max_num_batched_tokens=256, max_model_len=256,
+                            tp=tp, use_cuda_graphs=False)
+    eng = LLMEngine(runner, num_blocks=128, max_num_seqs=8, max_num_batched_tokens=256, max_model_len=256)
+    sps = [SamplingParams(temperature=0.8, top_k=40, max_tokens=6, seed=11), SamplingParams(temperature=1.0, top_p=0.9, max_tokens=6, seed=12),
+           SamplingParams(temperature=0.0, max_tokens=6), SamplingParams(temperature=1.2, top_k=5, top_p=0.7, max_tokens=6, seed=13)]
+    ids = [eng.add_request(p, sp) for p, sp in zip(prompts[:4], sps)]
+    eng.run_to_completion()
+    sampled[how] = [list(eng.seqs[i].output_ids) for i in ids]
+    torch.cuda.synchronize()
+    cuda_ops.check_device_errors()
+    dist.barrier()
+out["sampled"] = sampled
 ref = logits["tp1"]
 scale = float(ref.abs().max())
 cmp = ("nccl", "fused") + (("fused_replicated",) if moe else ())
@@ -236,6 +256,8 @@ def test_tensor_parallel_engine_fused_matches_baseline(tmp_path, model, heap):
         assert not out["multimem"]
     # logits of one prefill step, every vocabulary column, against the single-GPU run: bf16 activations with other
     # summation orders (K split over the ranks, partial sums rounded to bf16 before the reduction)
+    assert out["sampled"]["pairs"] == out["sampled"]["nccl"], out["sampled"]
+    assert all(len(t) == 6 for t in out["sampled"]["pairs"])
     if model == "mixtral":
         assert out["pairs_received"] == out["pairs_sent"] > 0
     for mode in out["logit_err"]:

@@ -225,20 +225,21 @@ def gpu_config(n: int, scale: float, env, fused: bool = True, health=None, warm:
     return res
 
 
-def config5(scale: float, env, fused: bool = True) -> List[Dict]:
+def config5(scale: float, env, fused: bool = True, model: str = "llama3-70b", context: int = 4096) -> List[Dict]:
     """Llama-3-70B decode sweep.  The KV cache is filled with random values at the target context (decode time does not
-    depend on the values), then ``steps`` decode steps run through the runner with CUDA graphs."""
+    depend on the values), then ``steps`` decode steps run through the runner with CUDA graphs.  ``model`` / ``context``
+    run the same sweep on another architecture (e.g. ``llama3-8b`` on one GPU: single-stream decode latency)."""
     from ..engine.runner import StepBatch
 
     rank, world, group, device = env
     small = scale < 0.05
-    ctx, steps = (4096, 256) if not small else (256, 16)
+    ctx, steps = (context, 256) if not small else (256, 16)
     batches = [b for b in (1, 8, 32, 128, 256) if b <= max(1, int(256 * scale)) or small and b <= 8] or [1]
     bmax = max(batches)
     max_len = ctx + steps + 16
     per = (max_len + 15) // 16                       # block-table width of the runner
     blocks = bmax * per + 16
-    eng, runner, cfg, w = build_engine("llama3-70b", world, rank, group, device, max_seqs=bmax, max_len=max_len,
+    eng, runner, cfg, w = build_engine(model, world, rank, group, device, max_seqs=bmax, max_len=max_len,
                                        blocks=blocks, small=small, fused=fused)
     for kc in runner.k_cache:
         kc.normal_(0, 0.5)
@@ -272,7 +273,9 @@ def config5(scale: float, env, fused: bool = True) -> List[Dict]:
             t = torch.tensor([ms], dtype=torch.float64, device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
             ms = float(t[0])
-        out.append({"model": "llama3-70b", "n_gpus": world, "batch": B, "context": ctx, "decode_steps": steps,
+        wbytes = w.nbytes()
+        out.append({"model": model, "weight_gb_per_gpu": round(wbytes / 1e9, 2),
+                    "weight_stream_floor_ms": round(wbytes / 6.54e12 * 1e3, 3), "n_gpus": world, "batch": B, "context": ctx, "decode_steps": steps,
                     "tpot_ms": ms / steps, "tok_s_device": B * steps / (ms / 1e3), "kv": "random values at the target context",
                     "small_model": small, "dtype": "bf16",
                     "parallelism": f"tp{world}" + ("" if fused or world == 1 else "-nccl-baseline")})
@@ -283,6 +286,8 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", type=int, required=True, choices=[1, 2, 3, 4, 5])
     ap.add_argument("--scale", type=float, default=1.0)
+    ap.add_argument("--model", default="llama3-70b", help="config 5: architecture of the decode sweep")
+    ap.add_argument("--context", type=int, default=4096, help="config 5: context length of the decode sweep")
     ap.add_argument("--out", default=None, help="append JSON lines here")
     ap.add_argument("--nccl-baseline", action="store_true",
                     help="tensor parallel through NCCL all-reduce between separate kernels instead of the fused kernels")
@@ -318,7 +323,7 @@ def main(argv=None) -> int:
             health = FailureDetector(hb, StepWatchdog(hb, max_lag=1 << 30))
         try:
             if a.config == 5:
-                results = config5(a.scale, e, fused=not a.nccl_baseline)
+                results = config5(a.scale, e, fused=not a.nccl_baseline, model=a.model, context=a.context)
             else:
                 results = [gpu_config(a.config, a.scale, e, fused=not a.nccl_baseline, health=health, warm=not a.no_warm_pass)]
         finally:

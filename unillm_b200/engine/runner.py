@@ -1033,7 +1033,7 @@ class GpuModelRunner:
             self.launches += 2
             return out
         kc = fl.get("cand_k", 0)
-        if tp.comm is not None and kc and tp.comm.can_gather_pairs(S, kc):
+        if tp.comm is not None and kc and tp.comm.can_gather_pairs(S, kc) and os.environ.get("UB_SAMPLE_PAIRS", "1") != "0":
             # F4s: every shard hands in the best `kc` entries of each row (after temperature), the pairs are gathered
             # over peer memory and every rank draws the same token from them -- the whole-vocabulary logits stay put
             cv, ci = K.sample(logits, temperature=fl["temperature"], top_p=fl["top_p"], top_k=fl["top_k"], seed=fl["seed"],
