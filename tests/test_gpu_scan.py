@@ -124,12 +124,21 @@ def test_conv1d_as_gemm_and_whisper_bf16():
     from unillm_b200.ops import cuda_ops
 
     g = torch.Generator().manual_seed(0)
-    for (B, Cc, L, O, k, st, pad) in ((2, 16, 50, 24, 3, 1, 1), (1, 8, 64, 32, 3, 2, 1), (2, 8, 40, 16, 7, 1, 0)):
+    from unillm_b200.models import simple
+
+    # implicit GEMM (overlapping strided window view): strides 1 / 2 / 3, odd lengths, several batch elements whose
+    # straddling windows are dropped, long inputs (tcgen05 tiles) and short ones (weight-streaming kernel)
+    for (B, Cc, L, O, k, st, pad) in ((2, 16, 50, 24, 3, 1, 1), (1, 8, 64, 32, 3, 2, 1), (2, 8, 40, 16, 7, 1, 0),
+                                       (3, 80, 301, 96, 3, 2, 1), (1, 384, 1500, 384, 3, 1, 1), (2, 24, 9, 8, 5, 3, 2)):
         x, w, b = _bf(torch.randn(B, Cc, L, generator=g)), _bf(torch.randn(O, Cc, k, generator=g) * 0.2), _bf(torch.randn(O, generator=g))
         ref = torch.nn.functional.conv1d(x.float(), w.float(), b.float(), stride=st, padding=pad)
         got = conv1d(x.cuda(), w.cuda(), b.cuda(), stride=st, padding=pad)
         assert got.shape == ref.shape
-        _close(got, ref, 0.03)
+        _close(got, ref, 0.03 * max(1.0, float(ref.abs().max()) / 8))
+    assert simple._IMPLICIT_CONV["ok"], "the overlapping window descriptor was refused; conv1d fell back to the window matrix"
+    # dilation keeps the window-matrix path
+    x, w = _bf(torch.randn(1, 16, 70, generator=g)), _bf(torch.randn(8, 16, 3, generator=g) * 0.2)
+    _close(conv1d(x.cuda(), w.cuda(), None, dilation=3), torch.nn.functional.conv1d(x.float(), w.float(), dilation=3), 0.03)
     cfg = C.WhisperConfig(vocab_size=512, d_model=128, encoder_layers=2, decoder_layers=2, encoder_attention_heads=4,
                           decoder_attention_heads=4, encoder_ffn_dim=256, decoder_ffn_dim=256, max_source_positions=64,
                           max_target_positions=32, num_mel_bins=16, hidden_size=128, decoder_start_token_id=1, eos_token_id=2)

@@ -182,23 +182,57 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, offset: in
     return torch.cat([out, rest], -1) if rest.shape[-1] else out
 
 
+_IMPLICIT_CONV = {"ok": True}
+_CONV_FILTERS: dict = {}
+
+
+def _filter_matrix(w: torch.Tensor) -> torch.Tensor:
+    """``w [O, C, k]`` as the GEMM operand ``[O, k * C]`` whose columns run tap-major (tap j, channel c), cached per
+    weight tensor."""
+    key = (w.data_ptr(), tuple(w.shape), w.dtype, str(w.device))
+    m = _CONV_FILTERS.get(key)
+    if m is None:
+        if len(_CONV_FILTERS) > 256:
+            _CONV_FILTERS.clear()
+        m = _CONV_FILTERS[key] = w.permute(0, 2, 1).reshape(w.shape[0], -1).to(torch.bfloat16).contiguous()
+    return m
+
+
 def conv1d(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None, stride: int = 1, padding: int = 0,
            groups: int = 1, dilation: int = 1) -> torch.Tensor:
-    """[B, C, L] convolution.  bf16 CUDA inputs with ``groups == 1`` run as a GEMM on the tensor cores: the input
-    windows are laid out as rows ``[B * L_out, C * k]`` and multiplied with the filter matrix ``[O, C * k]`` by the
-    tcgen05 GEMM (bias in its epilogue); everything else is an fp32 convolution (audio stems on CPU, grouped
-    positional convolutions)."""
+    """[B, C, L] convolution.
+
+    bf16 CUDA inputs with ``groups == 1``, ``dilation == 1`` and a channel count that is a multiple of 8 run as an
+    IMPLICIT GEMM on the tcgen05 kernel: the input is laid out once channel-last and zero-padded, and the window matrix
+    ``[windows, k * C]`` is never built -- window t is the ``k * C`` consecutive elements that start at row ``t * stride``,
+    so the matrix is an overlapping strided view (row stride ``stride * C``) that the GEMM's TMA descriptor walks
+    directly.  Batch elements are padded to a whole number of windows; the few windows that straddle two batch elements
+    are computed and dropped.  Dilated convolutions still build the window matrix before the GEMM; everything else is an
+    fp32 convolution (audio stems on CPU, grouped positional convolutions, single-channel waveforms)."""
     if x.is_cuda and x.dtype == torch.bfloat16 and groups == 1 and (w.shape[1] * w.shape[2]) % 8 == 0:
         from ..ops import cuda_ops as K
 
         B, Cc, L = x.shape
         O, _, k = w.shape
+        bias = None if b is None else b.to(torch.bfloat16)
+        if dilation == 1 and Cc % 8 == 0 and _IMPLICIT_CONV["ok"]:
+            Lp = L + 2 * padding
+            Lo = (Lp - k) // stride + 1
+            R = -(-Lp // stride)                                   # windows per batch element, the straddling ones included
+            buf = x.new_zeros(B * R * stride + k, Cc)              # channel-last, padded; k spare rows behind the last window
+            buf[:B * R * stride].view(B, R * stride, Cc)[:, padding:padding + L] = x.transpose(1, 2)
+            win = buf.as_strided((B * R, k * Cc), (stride * Cc, 1))
+            try:
+                y = K.gemm_tn(win, _filter_matrix(w), bias=bias)
+                return y.view(B, R, O)[:, :Lo].transpose(1, 2).contiguous()
+            except RuntimeError:
+                _IMPLICIT_CONV["ok"] = False                       # the descriptor was refused: window matrix from here on
         xp = F.pad(x, (padding, padding)) if padding else x
         span = dilation * (k - 1) + 1
         Lo = (xp.shape[-1] - span) // stride + 1
         idx = (torch.arange(Lo, device=x.device) * stride)[:, None] + (torch.arange(k, device=x.device) * dilation)[None]
         cols = xp[:, :, idx].permute(0, 2, 1, 3).reshape(B * Lo, Cc * k).contiguous()      # [B*Lo, C*k]
-        y = K.linear(cols, w.reshape(O, Cc * k).to(torch.bfloat16).contiguous(), None if b is None else b.to(torch.bfloat16))
+        y = K.linear(cols, w.reshape(O, Cc * k).to(torch.bfloat16).contiguous(), bias)
         return y.view(B, Lo, O).transpose(1, 2).contiguous()
     return F.conv1d(_f(x), _f(w), None if b is None else _f(b), stride=stride, padding=padding, groups=groups,
                     dilation=dilation).to(x.dtype)
