@@ -136,6 +136,12 @@ def test_conv1d_as_gemm_and_whisper_bf16():
         assert got.shape == ref.shape
         _close(got, ref, 0.03 * max(1.0, float(ref.abs().max()) / 8))
     assert simple._IMPLICIT_CONV["ok"], "the overlapping window descriptor was refused; conv1d fell back to the window matrix"
+    # grouped: one implicit GEMM per group (the positional convolution of wav2vec2: even kernel, padding k // 2)
+    x, w, b = _bf(torch.randn(2, 64, 90, generator=g)), _bf(torch.randn(64, 16, 8, generator=g) * 0.1), _bf(torch.randn(64, generator=g))
+    ref = torch.nn.functional.conv1d(x.float(), w.float(), b.float(), padding=4, groups=4)
+    got = conv1d(x.cuda(), w.cuda(), b.cuda(), padding=4, groups=4)
+    assert got.shape == ref.shape
+    _close(got, ref, 0.03)
     # dilation keeps the window-matrix path
     x, w = _bf(torch.randn(1, 16, 70, generator=g)), _bf(torch.randn(8, 16, 3, generator=g) * 0.2)
     _close(conv1d(x.cuda(), w.cuda(), None, dilation=3), torch.nn.functional.conv1d(x.float(), w.float(), dilation=3), 0.03)

@@ -207,8 +207,18 @@ def conv1d(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None, s
     ``[windows, k * C]`` is never built -- window t is the ``k * C`` consecutive elements that start at row ``t * stride``,
     so the matrix is an overlapping strided view (row stride ``stride * C``) that the GEMM's TMA descriptor walks
     directly.  Batch elements are padded to a whole number of windows; the few windows that straddle two batch elements
-    are computed and dropped.  Dilated convolutions still build the window matrix before the GEMM; everything else is an
-    fp32 convolution (audio stems on CPU, grouped positional convolutions, single-channel waveforms)."""
+    are computed and dropped.  Grouped convolutions run one such GEMM per group; dilated convolutions still build the
+    window matrix before the GEMM; everything else is an fp32 convolution (audio stems on CPU, single-channel
+    waveforms, depthwise filters)."""
+    if (x.is_cuda and x.dtype == torch.bfloat16 and groups > 1 and dilation == 1 and w.shape[1] % 8 == 0
+            and x.shape[1] == groups * w.shape[1] and w.shape[0] % groups == 0 and _IMPLICIT_CONV["ok"]):
+        # grouped (e.g. the positional convolution of wav2vec2 / HuBERT: 16 groups of 48 channels, 128 taps): one implicit
+        # GEMM per group over that group's channels
+        Og = w.shape[0] // groups
+        outs = [conv1d(x[:, gi * w.shape[1]:(gi + 1) * w.shape[1]], w[gi * Og:(gi + 1) * Og],
+                       None if b is None else b[gi * Og:(gi + 1) * Og], stride=stride, padding=padding)
+                for gi in range(groups)]
+        return torch.cat(outs, dim=1)
     if x.is_cuda and x.dtype == torch.bfloat16 and groups == 1 and (w.shape[1] * w.shape[2]) % 8 == 0:
         from ..ops import cuda_ops as K
 
