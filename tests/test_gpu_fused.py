@@ -175,6 +175,25 @@ for mode in modes:
             dist.all_reduce(n)
             out["pairs_received"], out["pairs_sent"] = int(n), d.R * world * d.K
     dist.barrier()
+# one-shot all-reduce and pair gather over peer memory against NCCL, three exchanges each (parity slots alternate)
+ar_err = 0.0
+for it in range(3):
+    t = (torch.randn(16 + it, spec.hidden_size, generator=torch.Generator().manual_seed(100 * rank + it)) * 2).to(torch.bfloat16).cuda()
+    ref_t = t.float().clone()
+    dist.all_reduce(ref_t)
+    got_t = comm.all_reduce(t.clone())
+    torch.cuda.synchronize()
+    ar_err = max(ar_err, float((got_t.float() - ref_t).abs().max()) / max(1.0, float(ref_t.abs().max())))
+    pv = torch.randn(5 + it, 24, generator=torch.Generator().manual_seed(7 * rank + it)).cuda()
+    pi = torch.randint(0, 1000, (5 + it, 24), generator=torch.Generator().manual_seed(9 * rank + it)).to(torch.int32).cuda()
+    gv, gi = comm.gather_pairs(pv, pi)
+    lv = [torch.empty_like(pv) for _ in range(world)]
+    li = [torch.empty_like(pi) for _ in range(world)]
+    dist.all_gather(lv, pv)
+    dist.all_gather(li, pi)
+    assert torch.equal(gv, torch.cat(lv, 1)) and torch.equal(gi, torch.cat(li, 1))
+cuda_ops.check_device_errors()
+out["all_reduce_err"] = ar_err
 # top-k / top-p sampling over vocabulary shards: candidate pairs gathered through peer memory against whole rows of
 # logits gathered by NCCL -- same logits, same Philox draws, so the tokens have to be identical
 tp = TpContext(rank, world, dist.group.WORLD, fused=True)
@@ -256,6 +275,7 @@ def test_tensor_parallel_engine_fused_matches_baseline(tmp_path, model, heap):
         assert not out["multimem"]
     # logits of one prefill step, every vocabulary column, against the single-GPU run: bf16 activations with other
     # summation orders (K split over the ranks, partial sums rounded to bf16 before the reduction)
+    assert out["all_reduce_err"] < 0.01, out["all_reduce_err"]        # bf16 rounding of the sum
     assert out["sampled"]["pairs"] == out["sampled"]["nccl"], out["sampled"]
     assert all(len(t) == 6 for t in out["sampled"]["pairs"])
     if model == "mixtral":

@@ -692,3 +692,32 @@ def test_gemv_small_token_counts(M, N, K, dual):
     # and the tensor-core tiles agree on the same inputs (tile width forced, so the dispatcher does not divert)
     tc = K_.gemm_tn(x, w, tile_tokens=16)
     _close(tc, got32, rtol=2e-2, atol=2e-2)
+
+
+def test_oneshot_all_reduce_emulated_ranks_two_exchanges():
+    """The one-shot all-reduce with all ranks emulated on one GPU, two exchanges in a row (parity slots, counted arrival
+    words).  Kernels of different emulated ranks cannot wait for one another on one stream, so every rank's per-CTA
+    counters are credited up front with the arrivals of the ranks that launch after it; the last launch sees every
+    rank's data and its sum is checked against fp32."""
+    from unillm_b200.dist.fused import AR_FLAGS, FusedComm
+    from unillm_b200.ops import cuda_ops as K
+
+    W, H, rows = 4, 512, 24
+    comms = FusedComm.emulated(W, H, 64, "cuda")
+    g = torch.Generator().manual_seed(3)
+    for rnd in range(1, 3):
+        xs = [torch.randn(rows, H, generator=g).to(torch.bfloat16).cuda() for _ in range(W)]
+        want = torch.stack([x.float() for x in xs]).sum(0)
+        for r in range(W):
+            c = comms[r]
+            fl = c.buf[c.flags.offset:c.flags.offset + 1024].view(torch.int32)
+            fl[AR_FLAGS:AR_FLAGS + 64] += (W - 1 - r)
+        outs = [comms[r].all_reduce(xs[r].clone()) for r in range(W)]
+        torch.cuda.synchronize()
+        K.check_device_errors()
+        assert (outs[-1].float() - want).abs().max().item() < 0.06 * max(1.0, want.abs().max().item())
+        for r in range(W):
+            c = comms[r]
+            fl = c.buf[c.flags.offset:c.flags.offset + 1024].view(torch.int32)
+            fl[AR_FLAGS:AR_FLAGS + 64] -= (W - 1 - r)
+            assert int(fl[AR_FLAGS]) == rnd * W
