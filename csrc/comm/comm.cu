@@ -9,8 +9,10 @@
 // The vector is cut into one chunk per CTA (the same cut on every rank, the grid depends on n only); CTA c pushes
 // chunk c, bumps counter [c] on every peer and waits for its own counter [c] to show `world` more arrivals, so a
 // chunk is reduced as soon as ITS pieces are there and the remote atomics spread over up to 64 addresses.
-// Counters are monotonic: exchange number e (kept in a local device word that the last CTA to finish advances, so
-// the launch can sit in a CUDA graph) expects e * world on each.  Slots alternate by the parity of e: a fast rank
+// Counters are monotonic.  A launch uses as many CTAs as its size asks for, so every CTA keeps its own count of the
+// exchanges it took part in (a local word per CTA) and expects `world` arrivals more per exchange on ITS counter; the
+// number of the exchange itself (a local word that the last CTA to finish advances, so the launch can sit in a CUDA
+// graph) only selects the slot.  Slots alternate by the parity of that number e: a fast rank
 // may start exchange e + 1 while a slow one still sums exchange e, but it cannot reach e + 2 before the slow rank
 // has pushed e + 1, which that rank does only after it has finished reading e.
 // The reference has no collective of any kind.
@@ -31,23 +33,26 @@ __global__ void __launch_bounds__(256) allreduce_oneshot_kernel(const UbAllReduc
   }
   __syncthreads();
   const uint32_t round = round_s;
-  const long long slot = (long long)(round & 1u) * a.world * a.n;
+  const long long slot = (long long)(round & 1u) * a.world * a.max_n;
   const __nv_bfloat16* in = reinterpret_cast<const __nv_bfloat16*>(a.in);
   // 1. push this CTA's chunk into every rank's slot [parity][rank]
   for (long long c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
     const uint4 v = *reinterpret_cast<const uint4*>(in + c * 8);
     for (int r = 0; r < a.world; ++r) {
-      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.peer_slots[r]) + slot + (long long)a.rank * a.n + c * 8;
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.peer_slots[r]) + slot + (long long)a.rank * a.max_n + c * 8;
       *reinterpret_cast<uint4*>(dst) = v;
     }
   }
+  __threadfence_system();       // every thread's own peer stores are performed before the CTA meets
   __syncthreads();
   if (threadIdx.x == 0) {
     asm volatile("fence.acq_rel.sys;" ::: "memory");
     for (int r = 0; r < a.world; ++r)
       asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(a.peer_flags[r] + blockIdx.x), "r"(1u) : "memory");
-    // 2. wait for the same chunk of all ranks
-    const uint32_t want = round * (uint32_t)a.world;
+    // 2. wait for the same chunk of all ranks: `world` arrivals more than after this CTA's previous exchange
+    const uint32_t mine = a.cta_rounds[blockIdx.x] + 1;
+    a.cta_rounds[blockIdx.x] = mine;
+    const uint32_t want = mine * (uint32_t)a.world;
     const uint64_t t0 = wait_ticks();
     uint32_t it = 0, v;
     while (true) {
@@ -67,7 +72,7 @@ __global__ void __launch_bounds__(256) allreduce_oneshot_kernel(const UbAllReduc
   for (long long c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
     float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int r = 0; r < a.world; ++r) {
-      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(slots + (long long)r * a.n + c * 8));  // L2 only: peers wrote it
+      const uint4 v = ld_sys_u128(slots + (long long)r * a.max_n + c * 8);     // peers wrote it: read at the point of coherence
       const uint32_t* w = reinterpret_cast<const uint32_t*>(&v);
 #pragma unroll
       for (int e = 0; e < 4; ++e) { f[2 * e] += bf16_lo(w[e]); f[2 * e + 1] += bf16_hi(w[e]); }
@@ -99,7 +104,9 @@ extern "C" int ub_allreduce_oneshot_ctas(long long n) {
 
 extern "C" int ub_allreduce_oneshot(const UbAllReduceArgs* a, void* stream_v) {
   if (a->n <= 0) return 0;
-  if (a->n % 8 != 0 || a->world < 1 || a->world > UB_MAX_RANKS || a->round == nullptr || a->done_count == nullptr) return -2;
+  if (a->n % 8 != 0 || a->world < 1 || a->world > UB_MAX_RANKS || a->round == nullptr || a->done_count == nullptr ||
+      a->cta_rounds == nullptr || a->max_n < a->n || a->max_n % 8 != 0)
+    return -2;
   ub::allreduce_oneshot_kernel<<<(unsigned)ub_allreduce_oneshot_ctas(a->n), 256, 0, (cudaStream_t)stream_v>>>(*a);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
@@ -136,12 +143,15 @@ __global__ void __launch_bounds__(256) pair_gather_oneshot_kernel(const UbPairGa
       reinterpret_cast<int*>(a.peer_ids[r])[dst] = id;
     }
   }
+  __threadfence_system();       // every thread's own peer stores are performed before the CTA meets ...
   __syncthreads();
   if (threadIdx.x == 0) {
-    asm volatile("fence.acq_rel.sys;" ::: "memory");
+    asm volatile("fence.acq_rel.sys;" ::: "memory");     // ... and before the arrival that thread 0 sends for all of them
     for (int r = 0; r < W; ++r)
       asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(a.peer_flags[r] + blockIdx.x), "r"(1u) : "memory");
-    const uint32_t want = round * (uint32_t)W;
+    const uint32_t mine = a.cta_rounds[blockIdx.x] + 1;       // exchanges this CTA index has taken part in (grids vary)
+    a.cta_rounds[blockIdx.x] = mine;
+    const uint32_t want = mine * (uint32_t)W;
     const uint64_t t0 = wait_ticks();
     uint32_t it = 0, v;
     while (true) {
@@ -156,8 +166,8 @@ __global__ void __launch_bounds__(256) pair_gather_oneshot_kernel(const UbPairGa
   __syncthreads();
   // 2. the gathered pairs of this CTA's rows -> [row][world * k]
   for (long long i = (long long)r0 * W * k + threadIdx.x; i < (long long)r1 * W * k; i += blockDim.x) {
-    a.out_vals[i] = __ldcg(a.my_vals + slot + i);      // L2 only: peers wrote it
-    a.out_ids[i] = __ldcg(a.my_ids + slot + i);
+    a.out_vals[i] = ld_sys_f32(a.my_vals + slot + i);      // peers wrote it: read at the point of coherence
+    a.out_ids[i] = (int)ld_sys_u32(a.my_ids + slot + i);
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -174,7 +184,7 @@ __global__ void __launch_bounds__(256) pair_gather_oneshot_kernel(const UbPairGa
 extern "C" int ub_pair_gather_oneshot(const UbPairGatherArgs* a, void* stream_v) {
   if (a->rows <= 0) return 0;
   if (a->k <= 0 || a->world < 1 || a->world > UB_MAX_RANKS || (long long)a->rows * a->k > a->cap || a->round == nullptr ||
-      a->done_count == nullptr)
+      a->done_count == nullptr || a->cta_rounds == nullptr)
     return -2;
   // The grid must be co-resident (CTAs of different ranks wait on one another): at most UB_AR_MAX_CTAS.
   int g = (int)(((long long)a->rows * a->k + 4095) / 4096);
@@ -241,8 +251,8 @@ __global__ void __launch_bounds__(256) tp_argmax_merge_kernel(const UbArgmaxMerg
     int bi = 0x7fffffff;
     for (int r = 0; r < a.world; ++r) {
       const long long s = ((long long)par * a.world + r) * a.max_rows + i;
-      const float v = __ldcg(a.my_vals + s);
-      const int id = __ldcg(a.my_ids + s);
+      const float v = ld_sys_f32(a.my_vals + s);      // peers wrote it: read at the point of coherence
+      const int id = (int)ld_sys_u32(a.my_ids + s);
       if (v > bv || (v == bv && id < bi)) { bv = v; bi = id; }
     }
     a.out_ids[i] = bi;

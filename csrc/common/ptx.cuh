@@ -43,6 +43,21 @@ __device__ __forceinline__ uint64_t wait_ticks() {
   return (uint64_t)clock64() >> 1;
 }
 
+// Loads of data that a PEER GPU has written into this GPU's memory, issued after the arrival counter has been
+// acquired: relaxed at system scope, i.e. served from the point of coherence.  (A weak ld.global.cg after another
+// thread's acquire returned stale zeros from a line that had been cached before the peer's stores landed.)
+__device__ __forceinline__ uint32_t ld_sys_u32(const void* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_sys_f32(const void* p) { return __uint_as_float(ld_sys_u32(p)); }
+__device__ __forceinline__ uint4 ld_sys_u128(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile(

@@ -217,6 +217,7 @@ typedef struct UbPairGatherArgs {
   int world, rank, rows, k;
   long long cap;              /* pairs per rank the slots can hold (rows * k <= cap) */
   int* err;
+  uint32_t* cta_rounds;       /* local, UB_AR_MAX_CTAS words: exchanges each CTA index has taken part in */
 } UbPairGatherArgs;
 int ub_pair_gather_oneshot(const UbPairGatherArgs* args, void* stream);
 /* vals/ids [world, B] per-shard greedy winners -> out_ids [B]; lowest id wins ties. */
@@ -354,15 +355,17 @@ int ub_bump_epoch(uint32_t* epoch, void* stream);
 typedef struct UbAllReduceArgs {
   const void* in;           /* bf16 [n] local */
   void* out;                /* bf16 [n] */
-  void* peer_slots[UB_MAX_RANKS];     /* each: [2][world][n] bf16 on that peer (two slot sets, by exchange parity) */
+  void* peer_slots[UB_MAX_RANKS];     /* each: [2][world][max_n] bf16 on that peer (two slot sets, by exchange parity) */
   uint32_t* peer_flags[UB_MAX_RANKS]; /* each: UB_AR_MAX_CTAS counters on that peer (one per CTA index) */
-  const void* my_slots;     /* local [2][world][n] */
+  const void* my_slots;     /* local [2][world][max_n] */
   const uint32_t* my_flags; /* local counters */
   uint32_t* round;          /* local device word: number of exchanges completed (advanced by the kernel) */
   uint32_t* done_count;     /* local device word, zero between launches */
   int world, rank;
   long long n;
   int* err;
+  uint32_t* cta_rounds;     /* local, UB_AR_MAX_CTAS words: exchanges each CTA index has taken part in (grids vary with n) */
+  long long max_n;          /* elements per rank slot (capacity); n <= max_n */
 } UbAllReduceArgs;
 int ub_allreduce_oneshot_ctas(long long n);
 int ub_allreduce_oneshot(const UbAllReduceArgs* args, void* stream);

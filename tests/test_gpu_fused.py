@@ -175,10 +175,11 @@ for mode in modes:
             dist.all_reduce(n)
             out["pairs_received"], out["pairs_sent"] = int(n), d.R * world * d.K
     dist.barrier()
-# one-shot all-reduce and pair gather over peer memory against NCCL, three exchanges each (parity slots alternate)
+# one-shot all-reduce and pair gather over peer memory against NCCL: exchanges of different sizes, i.e. with different
+# numbers of CTAs (each CTA index keeps its own arrival count), parity slots alternating
 ar_err = 0.0
-for it in range(3):
-    t = (torch.randn(16 + it, spec.hidden_size, generator=torch.Generator().manual_seed(100 * rank + it)) * 2).to(torch.bfloat16).cuda()
+for it in range(5):
+    t = (torch.randn((16, 17, 4, 30, 9)[it], spec.hidden_size, generator=torch.Generator().manual_seed(100 * rank + it)) * 2).to(torch.bfloat16).cuda()
     ref_t = t.float().clone()
     dist.all_reduce(ref_t)
     got_t = comm.all_reduce(t.clone())
@@ -191,7 +192,11 @@ for it in range(3):
     li = [torch.empty_like(pi) for _ in range(world)]
     dist.all_gather(lv, pv)
     dist.all_gather(li, pi)
-    assert torch.equal(gv, torch.cat(lv, 1)) and torch.equal(gi, torch.cat(li, 1))
+    ev, ei = torch.cat(lv, 1), torch.cat(li, 1)
+    if not (torch.equal(gv, ev) and torch.equal(gi, ei)):
+        bad = ((gv != ev) | (gi != ei)).nonzero()
+        raise AssertionError(f"pair gather differs from NCCL on rank {rank}, exchange {it}: {bad.shape[0]} of {gv.numel()} "
+                             f"entries, first {bad[:4].tolist()}, got {gv[tuple(bad[0].tolist())].item()} want {ev[tuple(bad[0].tolist())].item()}")
 cuda_ops.check_device_errors()
 out["all_reduce_err"] = ar_err
 # top-k / top-p sampling over vocabulary shards: candidate pairs gathered through peer memory against whole rows of

@@ -695,17 +695,17 @@ def test_gemv_small_token_counts(M, N, K, dual):
 
 
 def test_oneshot_all_reduce_emulated_ranks_two_exchanges():
-    """The one-shot all-reduce with all ranks emulated on one GPU, two exchanges in a row (parity slots, counted arrival
-    words).  Kernels of different emulated ranks cannot wait for one another on one stream, so every rank's per-CTA
+    """The one-shot all-reduce with all ranks emulated on one GPU, four exchanges of different sizes in a row (parity
+    slots, counted arrival words, grids of one and two CTAs).  Kernels of different emulated ranks cannot wait for one another on one stream, so every rank's per-CTA
     counters are credited up front with the arrivals of the ranks that launch after it; the last launch sees every
     rank's data and its sum is checked against fp32."""
     from unillm_b200.dist.fused import AR_FLAGS, FusedComm
     from unillm_b200.ops import cuda_ops as K
 
-    W, H, rows = 4, 512, 24
+    W, H = 4, 512
     comms = FusedComm.emulated(W, H, 64, "cuda")
     g = torch.Generator().manual_seed(3)
-    for rnd in range(1, 3):
+    for rnd, rows in ((1, 24), (2, 8), (3, 32), (4, 24)):      # 2, 1, 2, 2 CTAs: every CTA index counts its own exchanges
         xs = [torch.randn(rows, H, generator=g).to(torch.bfloat16).cuda() for _ in range(W)]
         want = torch.stack([x.float() for x in xs]).sum(0)
         for r in range(W):

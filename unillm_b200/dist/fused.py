@@ -35,12 +35,13 @@ import torch
 MAXR = 8
 # counter indices (uint32 words) inside the flag area
 AG0, RS1, AG1, RS0 = 0, 8, 16, 24
-FLAG_WORDS = 256
+FLAG_WORDS = 512
 AR_ROUND, AR_DONE = 44, 45               # one-shot all-reduce: exchanges completed, CTAs finished (both local)
 AR_FLAGS = 64                            # ... and its 64 per-CTA arrival counters (words 64..127)
 AR_ROWS = 32                             # token rows the one-shot all-reduce area holds (decode-sized messages)
 ARGMAX_FLAG, ARGMAX_ROUND = 32, 33     # counter of the greedy merge and its (local) round word
 LOCAL_RS0, LOCAL_RS1, LOCAL_AG0, LOCAL_AG1 = 40, 41, 42, 43   # local arrival counters of the producing launches
+AR_CTA_ROUNDS, SG_CTA_ROUNDS = 192, 256  # per-CTA exchange counts of the two one-shot kernels (local, 64 words each)
 SG_ROUND, SG_DONE = 49, 50               # pair gather of vocabulary-parallel sampling: exchanges completed, CTAs finished
 SG_FLAGS = 128                           # ... and its 64 per-CTA arrival counters (words 128..191)
 SG_PAIRS = 32768                         # (value, id) pairs per rank and exchange the gather area holds (rows x k)
@@ -323,6 +324,7 @@ class FusedComm:
         a.my_slots = self.buf.data_ptr() + self.ar_slots.offset
         a.my_flags = self.local_flag_ptr(AR_FLAGS)
         a.round, a.done_count = self.local_flag_ptr(AR_ROUND), self.local_flag_ptr(AR_DONE)
+        a.cta_rounds, a.max_n = self.local_flag_ptr(AR_CTA_ROUNDS), self.ar_elems
         a.world, a.rank, a.n = self.world, self.rank, n
         a.err = cuda_ops.err_word(self.device).data_ptr()
         N.check(N.cuda_lib().ub_allreduce_oneshot(C.byref(a), torch.cuda.current_stream(self.device).cuda_stream),
@@ -356,6 +358,7 @@ class FusedComm:
         a.my_ids = self.buf.data_ptr() + self.sg_ids.offset
         a.my_flags = self.local_flag_ptr(SG_FLAGS)
         a.round, a.done_count = self.local_flag_ptr(SG_ROUND), self.local_flag_ptr(SG_DONE)
+        a.cta_rounds = self.local_flag_ptr(SG_CTA_ROUNDS)
         a.world, a.rank, a.rows, a.k, a.cap = self.world, self.rank, rows, k, SG_PAIRS
         a.err = cuda_ops.err_word(self.device).data_ptr()
         lib = N.cuda_lib()

@@ -95,7 +95,7 @@ class UbPairGatherArgs(C.Structure):
         ("vals", vp), ("ids", vp), ("out_vals", vp), ("out_ids", vp), ("peer_vals", vp * UB_MAX_RANKS),
         ("peer_ids", vp * UB_MAX_RANKS), ("peer_flags", vp * UB_MAX_RANKS), ("my_vals", vp), ("my_ids", vp),
         ("my_flags", vp), ("round", vp), ("done_count", vp), ("world", i32), ("rank", i32), ("rows", i32), ("k", i32),
-        ("cap", i64), ("err", vp),
+        ("cap", i64), ("err", vp), ("cta_rounds", vp),
     ]
 
 
@@ -138,7 +138,7 @@ class UbAllReduceArgs(C.Structure):
     _fields_ = [
         ("in_", vp), ("out", vp), ("peer_slots", vp * UB_MAX_RANKS), ("peer_flags", vp * UB_MAX_RANKS),
         ("my_slots", vp), ("my_flags", vp), ("round", vp), ("done_count", vp), ("world", i32), ("rank", i32), ("n", i64),
-        ("err", vp),
+        ("err", vp), ("cta_rounds", vp), ("max_n", i64),
     ]
 
 
