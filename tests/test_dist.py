@@ -308,3 +308,46 @@ def test_kv_heads_are_replicated_when_ranks_outnumber_them():
     assert RunnerWeights.kv_layout(8, 3, 4) == (2, 6)
     with pytest.raises(Exception):
         RunnerWeights.kv_layout(3, 0, 2)
+
+
+def test_fused_comm_layout_has_no_overlap_and_matches_its_size():
+    """The symmetric buffer of the fused tensor-parallel kernels: every area (reduce-scatter / all-gather rows, counters,
+    greedy-merge pairs, one-shot all-reduce slots, sampling pair slots, MoE dispatch / combine areas) lies inside the
+    allocation, none overlaps another, and ``nbytes`` is exactly the end of the last one."""
+    import torch
+
+    from unillm_b200.dist import fused as F
+
+    for world, hidden, max_tokens, k, e in ((2, 512, 512, 0, 0), (8, 4096, 8704, 0, 0), (8, 4096, 2304, 2, 8), (4, 1024, 100, 6, 64)):
+        n = F.FusedComm.nbytes(world, hidden, max_tokens, k, e)
+        c = F.FusedComm(0, world, hidden, max_tokens, torch.empty(0, dtype=torch.uint8), [0] * world, moe_top_k=k, moe_experts=e)
+        names = ["flags", "am_vals", "am_ids", "ar_slots", "sg_vals", "sg_ids"] + (["disp_rows", "disp_meta", "disp_counts", "comb"] if k else [])
+        areas = list(c.rs) + list(c.ag) + [getattr(c, nm) for nm in names]
+        spans = sorted((a.offset, a.offset + a.nbytes) for a in areas)
+        assert spans[0][0] == 0 and spans[-1][1] == n
+        for (a0, a1), (b0, b1) in zip(spans, spans[1:]):
+            assert a1 <= b0, (world, hidden, (a0, a1), (b0, b1))
+        assert all(a.offset % 16 == 0 for a in areas)
+        words = [F.AG0, F.RS1, F.AG1, F.RS0, F.ARGMAX_FLAG, F.ARGMAX_ROUND, F.LOCAL_RS0, F.LOCAL_RS1, F.LOCAL_AG0, F.LOCAL_AG1,
+                 F.AR_ROUND, F.AR_DONE, F.DISP_FLAG, F.DISP_ROUND, F.LOCAL_DISP, F.SG_ROUND, F.SG_DONE]
+        ranges = [(F.AG0, 8), (F.AG1, 8), (F.AR_FLAGS, 64), (F.SG_FLAGS, 64), (F.AR_CTA_ROUNDS, 64), (F.SG_CTA_ROUNDS, 64)]
+        used = set()
+        for w_ in words:
+            if not any(lo <= w_ < lo + cnt for lo, cnt in ranges):
+                assert w_ not in used, w_
+                used.add(w_)
+        for lo, cnt in ranges:
+            for w_ in range(lo, lo + cnt):
+                assert w_ not in used and w_ < F.FLAG_WORDS, w_
+                used.add(w_)
+
+
+def test_candidate_count_of_a_tensor_parallel_draw():
+    from unillm_b200.engine.runner import GpuModelRunner as R
+
+    assert R.candidate_count([0.0, 0.0], None, None) == 1                       # greedy rows: the shard's winner
+    assert R.candidate_count([0.7, 0.0, 1.0], [40, 0, 8], [1.0, 1.0, 1.0]) == 40
+    assert R.candidate_count([0.7, 1.0], [0, 5], [0.9, 1.0]) == 1024               # top-p keeps 1024 survivors
+    assert R.candidate_count([0.7, 1.0], [5000, 5], None) == 1024                  # capped like the sampler
+    assert R.candidate_count([0.7, 1.0], None, None) == 0                          # whole-vocabulary draw: gather logits
+    assert R.candidate_count([0.7, 1.0], [0, 5], [1.0, 0.5]) == 0

@@ -1059,6 +1059,23 @@ class GpuModelRunner:
             b <<= 1
         return b
 
+    @staticmethod
+    def candidate_count(temperature, top_k, top_p) -> int:
+        """Candidates per row and vocabulary shard that a tensor-parallel draw has to exchange: the largest ``top_k`` of
+        the batch, or the 1024 survivors that a top-p draw keeps; greedy rows need one.  0 = some row samples from the
+        whole vocabulary (pure temperature), so the logits have to be gathered."""
+        cand = 1
+        for i, t in enumerate(temperature):
+            if t <= 0:
+                continue
+            k = top_k[i] if top_k is not None and top_k[i] else 0
+            p = top_p[i] if top_p is not None else 1.0
+            k = min(k, 1024) if k > 0 else (1024 if p < 1.0 else 0)
+            if k == 0:
+                return 0
+            cand = max(cand, k)
+        return cand
+
     def _sampling_tensors(self, b: StepBatch, S: int):
         if b.temperature is None or all(t <= 0 for t in b.temperature):
             return None
@@ -1071,19 +1088,7 @@ class GpuModelRunner:
         if b.top_k is not None and any(k and k > 0 for k in b.top_k):
             tk = torch.as_tensor([k or 0 for k in b.top_k], dtype=torch.int32).to(self.device, non_blocking=True)
             self.h2d_bytes += 4 * S
-        # candidates per row and shard that a vocabulary-parallel draw has to exchange: the row's top_k, or the 1024
-        # survivors that a top-p draw keeps; 0 = some row samples from the whole vocabulary (logits are gathered then)
-        cand = 1
-        for i, t in enumerate(b.temperature):
-            if t <= 0:
-                continue
-            k = b.top_k[i] if b.top_k is not None and b.top_k[i] else 0
-            p = b.top_p[i] if b.top_p is not None else 1.0
-            k = min(k, 1024) if k > 0 else (1024 if p < 1.0 else 0)
-            if k == 0:
-                cand = 0
-                break
-            cand = max(cand, k)
+        cand = self.candidate_count(b.temperature, b.top_k, b.top_p)
         return {"temperature": self.fmeta_dev[:S], "top_p": self.fmeta_dev[S:2 * S], "top_k": tk, "seed": b.seed,
                 "step": b.step, "cand_k": cand}
 
