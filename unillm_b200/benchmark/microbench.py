@@ -244,6 +244,30 @@ def bench_attn(results, case="all"):
         print(json.dumps(r))
 
 
+def bench_quant(results):
+    """Block-quantised weights: the GEMV on Q4_K / Q8_0 blocks (1 - 8 tokens) and dequantise + tcgen05 GEMM (more tokens),
+    against the bf16 kernels on the expanded matrix.  Bytes = the quantised blocks."""
+    from ..ops import quant as Q
+    from ..weights.gguf import Q4_K, Q8_0, quantize_blocks
+
+    hbm, tf, how = _peaks()
+    for qname, qt, bits in (("q4_k", Q4_K, 4.5), ("q8_0", Q8_0, 8.5)):
+        for M, N, K in ((1, 4096, 4096), (1, 14336, 4096), (8, 6144, 4096), (1, 4096, 14336)):
+            w = torch.randn(N, K) * 0.05
+            raw = quantize_blocks(w, qt)
+            blocks = torch.from_numpy(raw.copy()).cuda()
+            x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+            med, best = time_ms(lambda: Q.qgemv_cuda(blocks, x, N, qt))
+            wd = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+            out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            dmed, _ = time_ms(lambda: cuda_ops.gemm_tn(x, wd, out=out))
+            byts = float(blocks.numel() * blocks.element_size())
+            r = dict(kind="qgemv", qtype=qname, M=M, N=N, K=K, ms=med, best_ms=best, gbs=byts / med / 1e6,
+                     frac_hbm=byts / med / 1e6 / hbm, bf16_ms=dmed, speedup_vs_bf16=dmed / med, bits_per_weight=bits, peaks=how)
+            results.append(r)
+            print(json.dumps(r))
+
+
 def bench_norm(results):
     hbm, tf, how = _peaks()
     for T, H in [(256, 4096), (8192, 4096), (8192, 8192)]:
@@ -371,7 +395,7 @@ def bench_tp_layer(results, world=8, batch=512, variants=False):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", nargs="?", default="all", choices=["gemm", "attn", "norm", "tp", "all"])
+    ap.add_argument("what", nargs="?", default="all", choices=["gemm", "attn", "norm", "tp", "quant", "all"])
     ap.add_argument("--world", type=int, default=8, help="tp only: tensor-parallel size whose per-rank shapes are timed")
     ap.add_argument("--batch", type=int, default=512, help="tp only: concurrent sequences of the serving step")
     ap.add_argument("--variants", action="store_true", help="tp only: also time forced tile / pair / split-K choices")
@@ -394,6 +418,8 @@ def main(argv=None):
         bench_attn(results, a.attn_case)
     if a.what in ("norm", "all"):
         bench_norm(results)
+    if a.what == "quant":
+        bench_quant(results)
     if a.json:
         os.makedirs(os.path.dirname(a.json) or ".", exist_ok=True)
         Path(a.json).write_text(json.dumps(results, indent=1))
