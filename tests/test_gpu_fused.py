@@ -308,3 +308,104 @@ def test_symmetric_heap_peer_and_multicast_access(tmp_path):
     if res["multicast"]:
         assert res["checks"]["multimem_st"] and res["checks"]["multimem_ld_reduce"]
     assert all(v["peer_store"] > 1.0 for v in res["gbs"].values())
+
+
+def _gpu_elastic_worker(rank, world, port, q, exit_rank, exit_step):
+    """One rank of the GPU recovery test: fused tensor parallelism over the own symmetric heap WITHOUT a multicast
+    binding, a gloo control group (no NCCL anywhere), failures made on the host only."""
+    import datetime
+    import time
+
+    os.environ.update(UB_SYMM_HEAP="own", UB_MULTIMEM="0", NCCL_NVLS_ENABLE="0")
+    import torch
+    from torch.distributed import TCPStore
+
+    from unillm_b200.dist.elastic import serve_elastic
+    from unillm_b200.dist.fused import FusedComm
+    from unillm_b200.dist.health import FaultInjector
+    from unillm_b200.engine.llm_engine import LLMEngine
+    from unillm_b200.engine.runner import GpuModelRunner, RunnerWeights, TpContext
+    from unillm_b200.models import configs as C
+    from unillm_b200.models.families import LlamaModel
+    from unillm_b200.ops import cuda_ops
+    from unillm_b200.sampling import SamplingParams
+
+    torch.cuda.set_device(rank)
+    dev = f"cuda:{rank}"
+    store = TCPStore("127.0.0.1", port, world, is_master=(rank == 0), wait_for_workers=True,
+                     timeout=datetime.timedelta(seconds=120))
+    cfg = C.LlamaConfig(vocab_size=1024, hidden_size=512, intermediate_size=1024, num_hidden_layers=3,
+                        num_attention_heads=8, num_key_value_heads=4, rms_norm_eps=1e-5)
+    spec = LlamaModel.spec_from_config(cfg)
+    g = torch.Generator().manual_seed(0)
+    params = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    reqs = [{"id": i, "prompt": torch.randint(0, 1024, (n,), generator=g).tolist(), "params": params}
+            for i, n in enumerate((16, 48, 32, 64))]
+    built = []
+
+    def build_engine(g_rank, g_world, group):
+        tp = TpContext(g_rank, g_world, group if g_world > 1 else None, fused=g_world > 1)
+        w = RunnerWeights.random(spec, dev, g_rank, g_world, seed=7)
+        if tp.fused:
+            tp.comm = FusedComm.create(spec, g_rank, g_world, group, max_tokens=512, device=dev, heap="own")
+            assert tp.comm.heap is not None and not tp.comm.multimem        # plain peer stores / loads only
+        runner = GpuModelRunner(spec, w, num_blocks=128, max_num_seqs=8, max_num_batched_tokens=256, max_model_len=256,
+                                tp=tp, use_cuda_graphs=False, device=dev)
+        built.append((g_world, runner))
+        return LLMEngine(runner, num_blocks=128, max_num_seqs=8, max_num_batched_tokens=256, max_model_len=256)
+
+    ref = None
+    if rank == 0:                                   # the undisturbed single-GPU tokens, for the comparison at the end
+        ref = build_engine(0, 1, None).generate([r["prompt"] for r in reqs], params)
+        built.clear()
+    inj = FaultInjector()
+    if rank == exit_rank:
+        inj.exit_at_step(exit_step)
+    res = serve_elastic(rank, world, store, build_engine, reqs, num_heads=8, num_kv_heads=4, hb_interval=0.05,
+                        hb_timeout=1.5, injector=inj, backend="gloo")
+    torch.cuda.synchronize()
+    err = None
+    try:
+        cuda_ops.check_device_errors()
+    except RuntimeError as e:       # noqa: BLE001 - reported to the parent
+        err = str(e)
+    fused_steps = [(wd, r.fused_steps, r.unfused_steps) for wd, r in built]
+    q.put((rank, res.role, res.outputs, res.generations, res.final_world, res.recovered_from, res.steps, ref, fused_steps, err))
+    if rank == 0:
+        time.sleep(2.0)             # the store lives in this process: keep it until the other rank has reported
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_gpu_rank_leaves_between_steps_and_the_survivor_finishes():
+    """Two GPU ranks serve four requests with the fused tensor-parallel kernels (own symmetric heap, no multicast
+    binding, gloo control group, no NCCL); rank 1 exits between steps with nothing of its own in flight.  Rank 0 learns of
+    it on the host (heartbeat + step gate) before its next launch, so none of its kernels ever waits for the dead peer;
+    it rebuilds a single-GPU engine, restores the request log and finishes.  No device wait times out."""
+    import multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    import socket
+
+    with socket.socket() as s_:
+        s_.bind(("127.0.0.1", 0))
+        port = s_.getsockname()[1]
+    procs = [ctx.Process(target=_gpu_elastic_worker, args=(r, 2, port, q, 1, 5)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = {}
+    for _ in range(2):
+        r = q.get(timeout=240)
+        got[r[0]] = r[1:]
+    for p in procs:
+        p.join(timeout=60)
+    assert got[1][0] == "exited"
+    role, outs, gens, final_world, recovered, steps, ref, fused_steps, err = got[0]
+    assert err is None and got[1][8] is None, (err, got[1][8])
+    assert role == "finished" and gens == 2 and final_world == 1 and recovered == [[1]], got[0][:6]
+    assert fused_steps[0][0] == 2 and fused_steps[0][1] > 0              # the first generation ran the fused kernels
+    assert all(len(outs[i]) == 12 for i in range(4))
+    # tensor parallel 2 rounds differently from 1 GPU, so a near-tie may flip a token; the history up to the failure was
+    # generated at TP 2, the rest on one GPU
+    agree = sum(a == b for i in range(4) for a, b in zip(outs[i], ref[i]))
+    assert agree >= 0.7 * 48, (agree, outs, ref)

@@ -135,7 +135,8 @@ class FusedComm:
                 h = SymmetricHeap.create(n, rank, world, group, device, multicast=mc)
             except Exception as e:      # noqa: BLE001 - every rank has to learn about it and fall back together
                 ok, err = 0, repr(e)[:200]
-            flag = torch.tensor([ok], dtype=torch.int32, device=device)
+            # the agreement runs on the group's own kind of tensor (a gloo control group takes host tensors)
+            flag = torch.tensor([ok], dtype=torch.int32, device=device if dist.get_backend(group) == "nccl" else "cpu")
             dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
             if int(flag[0]) == 1:
                 c = cls(rank, world, spec.hidden_size, max_tokens, h.tensor()[:n], list(h.peer_ptrs), None, group, h.mc_ptr,
