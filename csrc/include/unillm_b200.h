@@ -196,6 +196,12 @@ typedef struct UbSampleArgs {
   int* cand_ids;
   int cand_k;
   const int* id_map;
+  /* Vocabulary-parallel draw from the WHOLE vocabulary (temperature only), again in two stages.  stats_out != NULL: no
+     draw; stats_out[2 * row] = the shard's largest scaled logit, [2 * row + 1] = sum of exp(logit - that maximum).
+     target_in != NULL: the inverse-CDF target for this shard in the same units (a negative value = another shard owns
+     the draw: out_ids = -1, out_vals = -inf; otherwise out_vals = 1). */
+  float* stats_out;
+  const float* target_in;
 } UbSampleArgs;
 int ub_sample(const UbSampleArgs* args, void* stream);
 /* One-shot all-gather of (value, id) pairs through peer memory: every rank contributes `rows` x `k` pairs; row s of

@@ -190,7 +190,20 @@ __global__ void __launch_bounds__(SB) sample_kernel(const UbSampleArgs a) {
     for (int i = lo; i < hi; ++i) s += __expf(rd(i) - vmax);
     float total;
     const float excl = blk_excl_scan(s, red, &total);
-    const float target = u * total;
+    if (a.stats_out != nullptr) {
+      // stage 1 of a vocabulary-parallel draw from the whole vocabulary: this shard's maximum and mass
+      if (tid == 0) { a.stats_out[2 * row] = vmax; a.stats_out[2 * row + 1] = total; }
+      return;
+    }
+    float target = u * total;
+    if (a.target_in != nullptr) {
+      // stage 2: the target inside this shard was worked out from all shards' masses; negative = not this shard's draw
+      target = a.target_in[row];
+      if (target < 0.f) {
+        if (tid == 0) { a.out_ids[row] = -1; if (a.out_vals != nullptr) a.out_vals[row] = -CUDART_INF_F; }
+        return;
+      }
+    }
     if (tid == 0) sh_pick = -1;
     __syncthreads();
     if (lo < hi && target >= excl && (target < excl + s || hi == V)) {
@@ -202,7 +215,7 @@ __global__ void __launch_bounds__(SB) sample_kernel(const UbSampleArgs a) {
     if (tid == 0) {
       const int pick = sh_pick < 0 ? imax : sh_pick;
       a.out_ids[row] = a.id_map != nullptr ? a.id_map[(long long)row * a.ld + pick] : pick + a.vocab_offset;
-      if (a.out_vals != nullptr) a.out_vals[row] = vmax;
+      if (a.out_vals != nullptr) a.out_vals[row] = a.target_in != nullptr ? 1.f : vmax;
     }
     return;
   }

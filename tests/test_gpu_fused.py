@@ -215,6 +215,10 @@ for how in ("pairs", "nccl"):
     ids = [eng.add_request(p, sp) for p, sp in zip(prompts[:4], sps)]
     eng.run_to_completion()
     sampled[how] = [list(eng.seqs[i].output_ids) for i in ids]
+    # temperature only: the draw from the whole vocabulary, split over the shards
+    ids = [eng.add_request(p, SamplingParams(temperature=0.9, max_tokens=6)) for p in prompts[4:8]]
+    eng.run_to_completion()
+    sampled[how + "_whole"] = [list(eng.seqs[i].output_ids) for i in ids]
     torch.cuda.synchronize()
     cuda_ops.check_device_errors()
     dist.barrier()
@@ -283,6 +287,11 @@ def test_tensor_parallel_engine_fused_matches_baseline(tmp_path, model, heap):
     assert out["all_reduce_err"] < 0.01, out["all_reduce_err"]        # bf16 rounding of the sum
     assert out["sampled"]["pairs"] == out["sampled"]["nccl"], out["sampled"]
     assert all(len(t) == 6 for t in out["sampled"]["pairs"])
+    wa, wb = out["sampled"]["pairs_whole"], out["sampled"]["nccl_whole"]
+    assert all(len(t) == 6 for t in wa)
+    # same logits and uniform numbers; shard-wise and whole-row sums round differently, so allow one boundary flip
+    # (everything after a flip in that sequence differs)
+    assert sum(a == b for a, b in zip(wa, wb)) >= 3, (wa, wb)
     if model == "mixtral":
         assert out["pairs_received"] == out["pairs_sent"] > 0
     for mode in out["logit_err"]:

@@ -721,3 +721,38 @@ def test_oneshot_all_reduce_emulated_ranks_two_exchanges():
             fl = c.buf[c.flags.offset:c.flags.offset + 1024].view(torch.int32)
             fl[AR_FLAGS:AR_FLAGS + 64] -= (W - 1 - r)
             assert int(fl[AR_FLAGS]) == rnd * W
+
+
+def test_whole_vocabulary_draw_over_shards_equals_the_single_kernel_draw():
+    """Temperature-only sampling with the vocabulary cut into shards: per-shard (maximum, mass), the shard and in-shard
+    target worked out from all of them, the owner's pick merged like a greedy winner -- the token of the kernel that
+    sees the whole row, for several Philox steps."""
+    from unillm_b200.ops import cuda_ops as K
+    from unillm_b200.sampling import philox_uniform
+
+    B, V, W = 16, 4096, 4
+    g = torch.Generator().manual_seed(21)
+    logits = (torch.randn(B, V, generator=g) * 2.5).to(torch.bfloat16).cuda()
+    temp = (torch.rand(B, generator=g) * 1.5 + 0.3).cuda()
+    same = 0
+    for step in range(6):
+        ref = K.sample(logits, temperature=temp, seed=77, step=step).cpu()
+        stats = [K.sample(logits[:, r * (V // W):(r + 1) * (V // W)].contiguous(), temperature=temp, seed=77, step=step, stats=True)
+                 for r in range(W)]
+        maxes = torch.stack([s_[:, 0] for s_ in stats], 1)
+        masses = torch.stack([s_[:, 1] for s_ in stats], 1)
+        uni = torch.tensor([philox_uniform(77, step, r) for r in range(B)], dtype=torch.float32).cuda()
+        owner, local = K.vocab_shard_targets(maxes, masses, uni)
+        vals, ids = [], []
+        for r in range(W):
+            tgt = torch.where(owner == r, local, torch.full_like(local, -1.0)).contiguous()
+            i_, v_ = K.sample(logits[:, r * (V // W):(r + 1) * (V // W)].contiguous(), temperature=temp, seed=77, step=step,
+                              vocab_offset=r * (V // W), target=tgt, return_vals=True)
+            ids.append(i_)
+            vals.append(v_)
+        got = K.argmax_merge(torch.stack(vals).contiguous(), torch.stack(ids).contiguous()).cpu()
+        assert ((torch.stack(ids) >= 0).sum(0) == 1).all()                     # exactly one shard draws every row
+        same += int((got == ref).sum())
+    # sums over shards and over the whole row round differently: a target that sits within rounding of a token's
+    # boundary may land on its neighbour
+    assert same >= 6 * B - 2, same

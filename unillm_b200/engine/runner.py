@@ -1043,6 +1043,19 @@ class GpuModelRunner:
                      step=fl["step"], out_ids=out, id_map=ai)
             self.launches += 3
             return out
+        if (tp.comm is not None and fl.get("whole_vocab") and tp.comm.can_gather_pairs(S, 1) and S <= 2048
+                and os.environ.get("UB_SAMPLE_PAIRS", "1") != "0"):
+            # F4s, temperature only: every shard reports its maximum and its mass, all ranks work out which shard the
+            # draw falls into and where, that shard picks the token and the winner is merged like a greedy one
+            st = K.sample(logits, temperature=fl["temperature"], seed=fl["seed"], step=fl["step"], stats=True)
+            mv, sv = tp.comm.gather_pairs(st[:, :1].contiguous(), st[:, 1:].contiguous().view(torch.int32))
+            owner, local = K.vocab_shard_targets(mv, sv.view(torch.float32), fl["uniform"])
+            local = torch.where(owner == tp.rank, local, torch.full_like(local, -1.0)).contiguous()
+            ids, vals = K.sample(logits, temperature=fl["temperature"], seed=fl["seed"], step=fl["step"],
+                                 vocab_offset=tp.rank * self.w.vocab_shard, target=local, return_vals=True)
+            tp.comm.argmax_merge(vals, ids, out)
+            self.launches += 4
+            return out
         full = tp.all_gather_cat(logits, dim=-1)
         K.sample(full, temperature=fl["temperature"], top_p=fl["top_p"], top_k=fl["top_k"], seed=fl["seed"],
                  step=fl["step"], out_ids=out)
@@ -1089,8 +1102,17 @@ class GpuModelRunner:
             tk = torch.as_tensor([k or 0 for k in b.top_k], dtype=torch.int32).to(self.device, non_blocking=True)
             self.h2d_bytes += 4 * S
         cand = self.candidate_count(b.temperature, b.top_k, b.top_p)
+        # temperature-only rows everywhere: the draw from the whole vocabulary can be split over the shards; it needs the
+        # uniform number of every row (the device sampler's Philox stream, evaluated here)
+        whole = cand == 0 and all(t > 0 for t in b.temperature) and (b.top_k is None or not any(b.top_k)) and \
+            (b.top_p is None or all(p >= 1.0 for p in b.top_p)) and self.tp.world > 1
+        uni = None
+        if whole:
+            from ..sampling import philox_uniform
+
+            uni = torch.tensor([philox_uniform(b.seed, b.step, r) for r in range(S)], dtype=torch.float32).to(self.device)
         return {"temperature": self.fmeta_dev[:S], "top_p": self.fmeta_dev[S:2 * S], "top_k": tk, "seed": b.seed,
-                "step": b.step, "cand_k": cand}
+                "step": b.step, "cand_k": cand, "whole_vocab": whole, "uniform": uni}
 
     MAX_GRAPHS = 96
 

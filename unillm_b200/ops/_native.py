@@ -86,7 +86,7 @@ class UbSampleArgs(C.Structure):
         ("logits", vp), ("ld", i64), ("logits_f32", i32), ("out_ids", vp), ("out_vals", vp),
         ("temperature", vp), ("top_p", vp), ("top_k", vp), ("rep_penalty", vp), ("prev_ids", vp), ("prev_ld", i32),
         ("seed", u64), ("step", u64), ("B", i32), ("V", i32), ("vocab_offset", i32), ("err", vp),
-        ("cand_vals", vp), ("cand_ids", vp), ("cand_k", i32), ("id_map", vp),
+        ("cand_vals", vp), ("cand_ids", vp), ("cand_k", i32), ("id_map", vp), ("stats_out", vp), ("target_in", vp),
     ]
 
 

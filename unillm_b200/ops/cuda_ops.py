@@ -407,13 +407,18 @@ def sample(logits: torch.Tensor, *, temperature: Optional[torch.Tensor] = None, 
            top_k: Optional[torch.Tensor] = None, rep_penalty: Optional[torch.Tensor] = None,
            prev_ids: Optional[torch.Tensor] = None, seed: int = 0, step: int = 0, vocab_offset: int = 0,
            out_ids: Optional[torch.Tensor] = None, out_vals: Optional[torch.Tensor] = None,
-           return_vals: bool = False, candidates: int = 0, id_map: Optional[torch.Tensor] = None):
+           return_vals: bool = False, candidates: int = 0, id_map: Optional[torch.Tensor] = None,
+           stats: bool = False, target: Optional[torch.Tensor] = None):
     """Greedy when ``temperature`` is None (or <= 0 for a row); otherwise temperature / top-k / top-p.
 
     Vocabulary-parallel draws run in two stages.  ``candidates = k`` (on every shard, with ``vocab_offset``): returns
     ``(vals [B, k] fp32, ids [B, k] int32)``, the row's best entries after penalty and temperature, instead of drawing.
     ``id_map`` (identical on every rank): ``logits`` are the gathered fp32 candidates ``[B, world * k]`` and ``id_map``
-    their global ids; the usual top-k / top-p / draw runs over them and returns global ids."""
+    their global ids; the usual top-k / top-p / draw runs over them and returns global ids.
+
+    Whole-vocabulary (temperature only) draws over shards: ``stats=True`` returns ``[B, 2]`` fp32 (the shard's largest
+    scaled logit, the sum of ``exp(logit - max)``) instead of drawing; ``target`` ([B] fp32, in those units, negative =
+    another shard draws) makes the shard that owns the draw pick the token, the others return -1."""
     if logits.dim() != 2 or logits.stride(1) != 1:
         raise ValueError("logits must be [B, V] with contiguous rows")
     if logits.dtype not in (torch.bfloat16, torch.float32):
@@ -441,10 +446,35 @@ def sample(logits: torch.Tensor, *, temperature: Optional[torch.Tensor] = None, 
                 logits.dtype != torch.float32 or not logits.is_contiguous():
             raise ValueError("id_map: int32, contiguous, same shape as the contiguous fp32 candidate values")
         a.id_map = id_map.data_ptr()
+    st = None
+    if stats:
+        st = torch.empty(B, 2, dtype=torch.float32, device=logits.device)
+        a.stats_out = st.data_ptr()
+    if target is not None:
+        a.target_in = target.data_ptr()
     N.check(N.cuda_lib().ub_sample(C.byref(a), _stream(logits)), "ub_sample")
+    if stats:
+        return st
     if candidates:
         return cv, ci
     return (out_ids, out_vals) if return_vals else out_ids
+
+
+def vocab_shard_targets(maxes: torch.Tensor, masses: torch.Tensor, uniform: torch.Tensor):
+    """Where a draw from the whole vocabulary falls when the vocabulary is cut into shards.  ``maxes`` / ``masses``
+    ([B, W] fp32: every shard's largest scaled logit and its sum of ``exp(logit - max)``, as ``sample(stats=True)`` reports
+    them) and the row's uniform number give ``(owner [B], target [B])``: the shard whose running mass passes
+    ``uniform * total`` (shards in vocabulary order, like the single-kernel inverse CDF) and the target inside that shard
+    in the shard's own units."""
+    gmax = maxes.max(dim=1, keepdim=True).values
+    mass = masses * torch.exp(maxes - gmax)
+    cum = mass.cumsum(dim=1)
+    tgt = uniform * cum[:, -1]
+    owner = (cum > tgt[:, None]).float().argmax(dim=1)
+    owner = torch.where(cum[:, -1] > tgt, owner, torch.full_like(owner, maxes.shape[1] - 1))
+    before = (cum - mass).gather(1, owner[:, None])[:, 0]
+    local = (tgt - before) * torch.exp(gmax[:, 0] - maxes.gather(1, owner[:, None])[:, 0])
+    return owner, local.clamp_min(0.0)
 
 
 def argmax_merge(vals: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
