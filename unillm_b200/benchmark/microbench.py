@@ -244,6 +244,88 @@ def bench_attn(results, case="all"):
         print(json.dumps(r))
 
 
+def bench_fused_emulated(results, world=8, batch=512, only=None):
+    """The fused tensor-parallel kernels of one layer at the serving step's per-rank shapes, with all ``world`` ranks
+    emulated on ONE GPU: the peers' buffers are plain local tensors, the chain runs once for every rank (producers before
+    consumers, one stream), then rank 0's kernels are timed alone -- their counters stay satisfied, so no kernel waits.
+    What this measures is the kernels' own cost with the peer stores landing in local HBM instead of crossing NVLink;
+    beside each one the same shape without the collective part.  ``only``: run just that kernel a few times (for ncu)."""
+    from ..dist.fused import FusedComm
+
+    hbm, tf, how = _peaks()
+    H, I = 4096, 14336 // world
+    Kq = (32 // world) * 128                    # o_proj: this rank's slice of the attention output
+    P = max(1, batch // 128)
+    T = (batch - P + P * 128) // world * world  # rows of a steady-state step, a multiple of the world size
+    R = T // world
+    comms = FusedComm.emulated(world, H, T, "cuda")
+    g = torch.Generator(device="cpu").manual_seed(0)
+    rnd = lambda *sh, sc=1.0: (torch.randn(*sh, generator=g) * sc).to(torch.bfloat16).cuda()   # noqa: E731
+    a_o, w_o = rnd(T, Kq), rnd(H, Kq, sc=Kq ** -0.5)
+    a_d, w_d = rnd(T, I), rnd(H, I, sc=I ** -0.5)
+    w_qkv, w_gu = rnd(Kq + 2 * max(1, 8 // world) * 128, H, sc=H ** -0.5), rnd(2 * I, H, sc=H ** -0.5)
+    ln = torch.ones(H, dtype=torch.bfloat16, device="cuda")
+    res = rnd(R, H)
+    # one pass of the whole chain for every rank: every counter that rank 0's kernels wait on is satisfied afterwards
+    for c in comms:
+        cuda_ops.gemm_tn(a_o, w_o, out=c.rs_local_tensor(0, R).view(world * R, H), rs=c.gemm_rs(0, R))
+    for c in comms:
+        cuda_ops.norm(c.rs_local_tensor(0, R), ln, residual=res, eps=1e-5, want_residual_out=True, no_out=True, T=R,
+                      rs=c.norm_rs(0), ag=c.norm_ag(1), reset=c.reset_after_ag(1))
+    for c in comms:
+        cuda_ops.gemm_tn(a_d, w_d, out=c.rs_local_tensor(1, R).view(world * R, H), rs=c.gemm_rs(1, R))
+    for c in comms:
+        cuda_ops.norm(c.rs_local_tensor(1, R), ln, residual=res, eps=1e-5, want_residual_out=True, no_out=True, T=R,
+                      rs=c.norm_rs(1), ag=c.norm_ag(0), reset=c.reset_after_ag(0))
+    torch.cuda.synchronize()
+    cuda_ops.check_device_errors()
+    c0 = comms[0]
+    # the pipeline zeroes every counter after its use; leave rank 0's satisfied so that each kernel can be timed alone
+    from ..dist.fused import AG0, AG1, RS0, RS1
+
+    fl = c0.buf[c0.flags.offset:c0.flags.offset + 1024].view(torch.int32)
+    fl[RS0], fl[RS1] = world, world
+    fl[AG0:AG0 + world] = 1
+    fl[AG1:AG1 + world] = 1
+    out_o = c0.rs_local_tensor(0, R).view(world * R, H)
+    out_d = c0.rs_local_tensor(1, R).view(world * R, H)
+    plain = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+    x1 = c0.ag_local_tensor(1, T)
+    x0 = c0.ag_local_tensor(0, T)
+    cases = {
+        "o_proj + reduce-scatter push": (lambda: cuda_ops.gemm_tn(a_o, w_o, out=out_o, rs=c0.gemm_rs(0, R)),
+                                         lambda: cuda_ops.gemm_tn(a_o, w_o, out=plain), 2.0 * T * H * Kq),
+        "down + reduce-scatter push": (lambda: cuda_ops.gemm_tn(a_d, w_d, out=out_d, rs=c0.gemm_rs(1, R)),
+                                       lambda: cuda_ops.gemm_tn(a_d, w_d, out=plain), 2.0 * T * H * I),
+        "all-gather wait + QKV": (lambda: cuda_ops.gemm_tn(x0, w_qkv, ag=c0.gemm_ag(0, R)),
+                                  lambda: cuda_ops.gemm_tn(x0, w_qkv), 2.0 * T * w_qkv.shape[0] * H),
+        "all-gather wait + gate/up": (lambda: cuda_ops.gemm_tn(x1, w_gu, dual_rows=I, act="silu", ag=c0.gemm_ag(1, R)),
+                                      lambda: cuda_ops.gemm_tn(x1, w_gu, dual_rows=I, act="silu"), 4.0 * T * I * H),
+        "norm: sum 8 slots + residual, all-gather push": (
+            lambda: cuda_ops.norm(c0.rs_local_tensor(0, R), ln, residual=res, eps=1e-5, want_residual_out=True, no_out=True,
+                                  T=R, rs=c0.norm_rs(0), ag=c0.norm_ag(1)),
+            lambda: cuda_ops.norm(c0.rs_local_tensor(0, R)[0], ln, residual=res, eps=1e-5, want_residual_out=True, T=R), 0.0),
+    }
+    if only is not None:
+        fn = cases[only][0]
+        for _ in range(6):
+            flush_l2()
+            fn()
+        torch.cuda.synchronize()
+        cuda_ops.check_device_errors()
+        print(json.dumps(dict(kind="fused_emulated_once", case=only, world=world, T=T)))
+        return
+    for name, (fused, base, flops) in cases.items():
+        med, best = time_ms(fused)
+        bmed, _ = time_ms(base)
+        r = dict(kind="fused_emulated", world=world, T=T, rows_per_rank=R, case=name, us=med * 1e3, best_us=best * 1e3,
+                 unfused_us=bmed * 1e3, tflops=(flops / med / 1e9 if flops else None), peaks=how)
+        results.append(r)
+        print(json.dumps(r))
+    torch.cuda.synchronize()
+    cuda_ops.check_device_errors()
+
+
 def bench_quant(results):
     """Block-quantised weights: the GEMV on Q4_K / Q8_0 blocks (1 - 8 tokens) and dequantise + tcgen05 GEMM (more tokens),
     against the bf16 kernels on the expanded matrix.  Bytes = the quantised blocks."""
@@ -395,7 +477,8 @@ def bench_tp_layer(results, world=8, batch=512, variants=False):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", nargs="?", default="all", choices=["gemm", "attn", "norm", "tp", "quant", "all"])
+    ap.add_argument("what", nargs="?", default="all", choices=["gemm", "attn", "norm", "tp", "quant", "fused", "all"])
+    ap.add_argument("--fused-case", default=None, help="fused only: run just this kernel a few times (for a profiler)")
     ap.add_argument("--world", type=int, default=8, help="tp only: tensor-parallel size whose per-rank shapes are timed")
     ap.add_argument("--batch", type=int, default=512, help="tp only: concurrent sequences of the serving step")
     ap.add_argument("--variants", action="store_true", help="tp only: also time forced tile / pair / split-K choices")
@@ -420,6 +503,8 @@ def main(argv=None):
         bench_norm(results)
     if a.what == "quant":
         bench_quant(results)
+    if a.what == "fused":
+        bench_fused_emulated(results, a.world, a.batch, a.fused_case)
     if a.json:
         os.makedirs(os.path.dirname(a.json) or ".", exist_ok=True)
         Path(a.json).write_text(json.dumps(results, indent=1))
