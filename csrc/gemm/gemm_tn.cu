@@ -764,7 +764,9 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   const bool leader = rank == 0;
   const int num_m = (p.M + TN - 1) / TN;
   const int num_n = (p.N + 2 * BM_W - 1) / (2 * BM_W);
-  const int total_tiles = num_m * num_n;
+  // [tile_begin, tile_end) is this launch's share of the pair tiles (two-phase schedule, see plan_gemm)
+  const int tile_begin = p.tile_begin;
+  const int total_tiles = p.tile_end > 0 ? p.tile_end : num_m * num_n;
   const int num_kb = (p.K + BK - 1) / BK;
   constexpr uint32_t ACC_COLS = (DUAL ? 2 : 1) * TN;
   constexpr int NBUF = (SPLITK || 2 * ACC_COLS > 512) ? 1 : 2;
@@ -773,13 +775,13 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   static_assert(TMEM_COLS <= 512, "TMEM budget exceeded");
   int unit_begin, unit_step, kb0 = 0, kb1 = num_kb;
   if (SPLITK) {
-    unit_begin = blockIdx.y;                      // grid = (2 * splits, tiles): one tile per cluster
+    unit_begin = tile_begin + blockIdx.y;         // grid = (2 * splits, tiles): one tile per cluster
     unit_step = 1 << 30;
     const int per = (num_kb + p.splits - 1) / p.splits;
     kb0 = int(pidx) * per;
     kb1 = min(num_kb, kb0 + per);
   } else {
-    unit_begin = blockIdx.x >> 1;
+    unit_begin = tile_begin + (blockIdx.x >> 1);
     unit_step = gridDim.x >> 1;
   }
 
@@ -984,7 +986,7 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     // features, so partial rows travel between the CTAs of equal rank in their pair.
     tc_fence_before();
     cluster_sync_all();
-    const bool sk_valid = (int)blockIdx.y < total_tiles;
+    const bool sk_valid = tile_begin + (int)blockIdx.y < total_tiles;
     if (warp >= 2 && sk_valid) {
       tc_fence_after();
       const int q = warp & 3;
@@ -994,7 +996,7 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     tc_fence_before();
     cluster_sync_all();                       // all slots are written (release / acquire at cluster scope)
     if (warp >= 2 && sk_valid) {
-      const int u = blockIdx.y;
+      const int u = tile_begin + blockIdx.y;
       const int m0 = (u % num_m) * TN;
       const int n0 = (u / num_m) * (2 * BM_W) + int(rank) * BM_W;
       const int tid_e = threadIdx.x - 64;
@@ -1075,7 +1077,12 @@ static int num_sms() {
   return sms[dev];
 }
 
-struct GemmPlan { int tn, splits, ctas, tiles; int tail_tiles, tail_splits; int pair; };
+struct GemmPlan {
+  int tn, splits, ctas, tiles;
+  int tail_tiles, tail_splits;
+  int pair;
+  int tail_units;     // pair plans of a gated GEMM: 1-CTA tiles (128 tokens) that cover the tail's pair tiles
+};
 
 // How many thread-block clusters of `csize` CTAs (one CTA per SM, ~200 KB of shared memory each) the device can run at
 // the same time.  A cluster lives inside one GPC, so this is less than SMs / csize: split-K launches that ask for
@@ -1160,6 +1167,7 @@ static GemmPlan plan_gemm(const UbGemmArgs* a) {
   pl.splits = splits;
   pl.tail_tiles = 0;
   pl.tail_splits = 1;
+  pl.tail_units = 0;
   // Two-phase schedule: when the last round of a persistent launch would keep fewer than half of the SMs busy, those
   // tiles run as a second launch with K split over clusters, so the tail costs 1/splits of a tile time.
   if (splits == 1 && !grouped && a->tail_split != 1 && pl.tiles > sms && num_kb >= 16) {
@@ -1223,6 +1231,37 @@ static GemmPlan plan_gemm(const UbGemmArgs* a) {
       pl.tail_splits = 1;
       pl.splits = (!dual && tn2 >= 128 && want_s > 1) ? want_s : 1;
       pl.ctas = pl.splits > 1 ? 2 * pl.splits * tiles2 : 2 * (tiles2 < pairs_now ? tiles2 : pairs_now);
+      // Two-phase schedule for gated GEMMs on pairs: the full rounds run as one persistent launch, the weight rows of a
+      // thin last round as a second launch of 1-CTA tiles (128 tokens) with K split over a cluster, because a pair
+      // tile of 2 x 256 accumulator columns cannot park its partials (1020 x 14336 x 4096 gated: 224 pair tiles =
+      // 3 x 74 + 2; 186.9 -> 164.3 us).  Plain GEMMs gain nothing from it: the split launch's fixed cost (cold
+      // start, reduction through distributed shared memory, exposed epilogue) is a full round of their shorter tiles
+      // (1020 x 6144 x 4096: 54.3 -> 60.2 us).
+      static int env_tail = -1;
+      if (env_tail < 0) { const char* e = getenv("UB_GEMM_PAIR_TAIL"); env_tail = (e != nullptr && e[0] == '0') ? 0 : 1; }
+      if (env_tail && pl.splits == 1 && a->tile_tokens <= 0 && a->tail_split != 1 && a->rs_world == 0 &&
+          tiles2 > pairs_now && num_kb >= 32) {
+        const int num_m2 = (a->M + tn2 - 1) / tn2;
+        const int main_t = (((tiles2 / pairs_now) * pairs_now) / num_m2) * num_m2;
+        const int tail_t = tiles2 - main_t;
+        if (main_t > 0 && tail_t > 0 && (main_t + pairs_now - 1) / pairs_now < rounds2) {
+          if (dual && tn2 == 256) {
+            const int num_m1 = (a->M + 127) / 128, num_n1 = (a->N + BM_W - 1) / BM_W;
+            const int units = num_m1 * num_n1 - (main_t / num_m2) * 2 * num_m1;
+            int ts = units > 0 ? sms / units : 0;
+            if (ts > 8) ts = 8;
+            while (ts & (ts - 1)) ts &= ts - 1;
+            while (ts > 1 && (num_kb < 8 * ts || (ts - 1) * ((num_kb + ts - 1) / ts) >= num_kb)) ts >>= 1;
+            while (ts > 1 && units > max_active_clusters(ts)) ts >>= 1;
+            if (ts >= 2) {
+              pl.tail_tiles = tail_t;
+              pl.tail_splits = ts;
+              pl.tail_units = units;
+              pl.ctas = 2 * pairs_now + ts * units;
+            }
+          }
+        }
+      }
     }
   }
   return pl;
@@ -1415,7 +1454,37 @@ extern "C" int ub_gemm_tn(const UbGemmArgs* a, void* stream_v) {
   if (rc != 0) return rc;
   rc = make_tmap_bf16_2d(&tx, a->x, a->M, a->K, a->ldx, pl.pair ? pl.tn / 2 : pl.tn, BK);
   if (rc != 0) return rc;
-  if (pl.pair) return dual ? dispatch_2cta<true>(pl.tn, tw, tx, p, pl, stream) : dispatch_2cta<false>(pl.tn, tw, tx, p, pl, stream);
+  if (pl.pair && pl.tail_tiles == 0)
+    return dual ? dispatch_2cta<true>(pl.tn, tw, tx, p, pl, stream) : dispatch_2cta<false>(pl.tn, tw, tx, p, pl, stream);
+  if (pl.pair) {
+    // phase 1: the full rounds on CTA pairs, persistent
+    GemmPlan main_pl = pl;
+    main_pl.tiles = pl.tiles - pl.tail_tiles;
+    main_pl.splits = 1;
+    const int pairs_now = max_active_clusters(2);
+    main_pl.ctas = 2 * (main_pl.tiles < pairs_now ? main_pl.tiles : pairs_now);
+    p.splits = 1;
+    p.tile_begin = 0;
+    p.tile_end = main_pl.tiles;
+    if (!dual) return -4;                      // the planner makes this plan for gated GEMMs only
+    rc = dispatch_2cta<true>(pl.tn, tw, tx, p, main_pl, stream);
+    if (rc != 0) return rc;
+    // phase 2: the thin last round, K split
+    GemmPlan tail_pl = pl;
+    tail_pl.splits = pl.tail_splits;
+    p.splits = pl.tail_splits;
+    // gated: the tail's weight rows as 1-CTA tiles of 128 tokens (pair row r = 1-CTA weight tiles 2r and 2r + 1)
+    CUtensorMap tx1;
+    rc = make_tmap_bf16_2d(&tx1, a->x, a->M, a->K, a->ldx, 128, BK);
+    if (rc != 0) return rc;
+    const int num_m1 = (a->M + 127) / 128, num_n1 = (a->N + BM_W - 1) / BM_W;
+    tail_pl.pair = 0;
+    tail_pl.tn = 128;
+    tail_pl.tiles = pl.tail_units;
+    p.tile_end = num_m1 * num_n1;
+    p.tile_begin = p.tile_end - pl.tail_units;
+    return dispatch_tn<true, true>(128, tw, tx1, p, tail_pl, stream);
+  }
   if (pl.splits > 1) {
     return dual ? dispatch_tn<true, true>(pl.tn, tw, tx, p, pl, stream)
                 : dispatch_tn<false, true>(pl.tn, tw, tx, p, pl, stream);

@@ -503,6 +503,33 @@ def test_gemm_2cta_splitk(M, N, K, tile, ps):
     assert torch.equal(cuda_ops.gemm_tn(x, w, bias=bias, residual=res, tile_tokens=tile, cta_pair=2, pair_splits=ps), out)
 
 
+@pytest.mark.parametrize("M,N,K,dual", [(1020, 6144, 4096, False), (1020, 6272, 2048, False), (1020, 4864, 2048, True),
+                                        (1000, 4992, 2048, True), (1020, 14336, 4096, True)])
+def test_gemm_pair_two_phase(M, N, K, dual):
+    """The planner's own choice for shapes whose CTA-pair tiles leave a thin last round.  Gated: full rounds on pairs, the
+    weight rows of the rest as 1-CTA tiles of 128 tokens with K split; plain: ragged rounds on pairs.  Ragged token and
+    feature edges; against fp32."""
+    from unillm_b200.ops import cuda_ops
+
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    x = _rand(M, K, seed=61)
+    if dual:
+        w = _rand(2 * N, K, scale=1 / math.sqrt(K), seed=62)
+        if sms >= 132:
+            assert cuda_ops.gemm_num_ctas(M, N, K, True) > sms          # both launches counted
+        out = cuda_ops.gemm_tn(x, w, dual_rows=N, act="silu")
+        g, u = x.float() @ w[:N].float().t(), x.float() @ w[N:].float().t()
+        _close(out, torch.nn.functional.silu(g) * u)
+        assert torch.equal(cuda_ops.gemm_tn(x, w, dual_rows=N, act="silu"), out)
+    else:
+        w = _rand(N, K, scale=1 / math.sqrt(K), seed=62)
+        bias, res = _rand(N, seed=63), _rand(M, N, seed=64)
+        out = cuda_ops.gemm_tn(x, w, bias=bias, residual=res)
+        _close(out, x.float() @ w.float().t() + bias.float() + res.float())
+        assert torch.equal(cuda_ops.gemm_tn(x, w, bias=bias, residual=res), out)
+    cuda_ops.check_device_errors()
+
+
 @pytest.mark.parametrize("D,Hq,Hkv,Sq,Sk,causal", [(128, 4, 2, 70, 70, True), (128, 4, 4, 33, 50, False), (64, 6, 2, 40, 40, False),
                                                    (64, 4, 4, 1, 37, True), (128, 2, 1, 17, 64, True)])
 def test_dense_attention_on_the_paged_kernels(D, Hq, Hkv, Sq, Sk, causal):
