@@ -31,6 +31,7 @@
 #include "../common/ptx.cuh"
 #include "../include/unillm_b200.h"
 #include <stdlib.h>
+#include <mutex>
 
 namespace ub {
 
@@ -71,6 +72,11 @@ struct GemmParams {
   int grp_max_tiles;  // token-tile slots in the table
   int grp_w_rows;     // rows of w per expert; expert e's weights are rows [e*grp_w_rows, (e+1)*grp_w_rows)
   int tile_begin, tile_end;   // work units of this launch; tile_end == 0 means all
+  // Stream-K schedule of the CTA-pair kernel (sk_on != 0): the (tile, k-block) space is cut into one contiguous range
+  // per pair; partial tiles are summed through sk_ws (fp32, one slot per CTA) under the flags sk_flags (one per CTA).
+  int sk_on;
+  float* sk_ws;
+  uint32_t* sk_flags;
   int dbg;                    // UB_GEMM_DEBUG bits: 1 = no L2 prefetch, 2 = no L2 cache hints
 };
 
@@ -727,6 +733,35 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
+// Work of one CTA pair, segment by segment.  Tile mode: whole tiles u, u + step, ... with the K range [kb0, kb1) fixed.
+// Stream-K mode (nkb > 0): the pairs form teams of num_m (one member per token tile); a team takes the units
+// [pos, pos_end) of the linear (row of weight tiles, k-block) space, cut at row boundaries, and its members walk them in
+// lockstep, each on its own token tile -- so a weight k-block is still pulled by num_m pairs at the same time and
+// comes from HBM once (with one range per pair the pairs of a weight row drift apart in K and every one of them
+// streams the weights from HBM again: 1020 x 4096 x 14336 took 102 us instead of 91).
+struct PairWalk {
+  int u, kb0, kb1;
+  int step, end;
+  int pos, pos_end, nkb;
+  int row, mul, add;      // stream-K: unit row = pos / nkb is a row of weight tiles; this pair's tile in it is row * mul + add
+  __device__ __forceinline__ bool valid() const { return nkb > 0 ? pos < pos_end : u < end; }
+  __device__ __forceinline__ void seg() {
+    row = pos / nkb;
+    u = row * mul + add;
+    kb0 = pos - row * nkb;
+    kb1 = min(nkb, kb0 + (pos_end - pos));
+  }
+  __device__ __forceinline__ void next() {
+    if (nkb > 0) {
+      pos += kb1 - kb0;
+      if (pos < pos_end) seg();
+    } else {
+      u += step;
+    }
+  }
+};
+constexpr int SK_SLOT_FLOATS = 256 * BM_W;          // workspace slot of one CTA: a 128 x 256 fp32 accumulator
+
 template <int TN, int STAGES, bool DUAL, bool SPLITK = false>
 struct Gemm2Smem {
   static constexpr int A_BYTES = BM_W * BK * 2;            // this CTA's 128 weight rows: 16 KB
@@ -784,6 +819,24 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     unit_begin = tile_begin + (blockIdx.x >> 1);
     unit_step = gridDim.x >> 1;
   }
+  PairWalk walk0;
+  walk0.u = unit_begin; walk0.kb0 = kb0; walk0.kb1 = kb1;
+  walk0.step = unit_step; walk0.end = total_tiles;
+  walk0.pos = 0; walk0.pos_end = 0; walk0.nkb = 0;
+  walk0.row = 0; walk0.mul = 0; walk0.add = 0;
+  const int sk_pair = blockIdx.x >> 1;
+  const int sk_teams = int(gridDim.x >> 1) / num_m, sk_team = sk_pair / num_m;
+  const long long sk_total = (long long)num_n * num_kb;
+  if (!SPLITK && p.sk_on) {
+    walk0.nkb = num_kb;
+    walk0.mul = num_m;
+    walk0.add = sk_pair - sk_team * num_m;
+    if (sk_team < sk_teams) {                     // pairs beyond the last whole team have no work
+      walk0.pos = int(sk_total * sk_team / sk_teams);
+      walk0.pos_end = int(sk_total * (sk_team + 1) / sk_teams);
+    }
+    if (walk0.pos < walk0.pos_end) walk0.seg();
+  }
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -816,7 +869,8 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       uint32_t ag_ready = 0;
       int it = 0;
       bool dead = false;
-      for (int u = unit_begin; u < total_tiles && !dead; u += unit_step) {
+      for (PairWalk wk = walk0; wk.valid() && !dead; wk.next()) {
+        const int u = wk.u, kb0 = wk.kb0, kb1 = wk.kb1;
         const int m0 = (u % num_m) * TN + int(rank) * (TN / 2);          // this CTA's half of the token tile
         const int n0 = (u / num_m) * (2 * BM_W) + int(rank) * BM_W;      // this CTA's weight rows
         if (p.ag_world > 0) {
@@ -860,7 +914,8 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       constexpr uint32_t idesc = make_idesc_bf16(2 * BM_W, TN, 0, 0);
       int it = 0, ui = 0;
       bool dead = false;
-      for (int u = unit_begin; u < total_tiles && !dead; u += unit_step) {
+      for (PairWalk wk = walk0; wk.valid() && !dead; wk.next()) {
+        const int kb0 = wk.kb0, kb1 = wk.kb1;
         const int ab = NBUF == 1 ? 0 : (ui & 1);
         const uint32_t aph = NBUF == 1 ? (ui & 1) : ((ui >> 1) & 1);
         ++ui;
@@ -909,18 +964,85 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                         (p.residual == nullptr ||
                          ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
     int ui = 0;
-    for (int u = unit_begin; u < total_tiles; u += unit_step) {
+    for (PairWalk wk = walk0; wk.valid(); wk.next()) {
+      const int u = wk.u;
       const int m0 = (u % num_m) * TN;                                   // all TN tokens: the accumulator is 128 x TN
       const int n0 = (u / num_m) * (2 * BM_W) + int(rank) * BM_W;
       const int ab = NBUF == 1 ? 0 : (ui & 1);
       const uint32_t aph = NBUF == 1 ? (ui & 1) : ((ui >> 1) & 1);
       ++ui;
+      // Stream-K (plain GEMMs): a segment that does not cover the whole K range of its tile.  The pair that holds the
+      // head of the tile (kb0 == 0) owns it; every other segment parks its fp32 partial in this CTA's workspace slot
+      // and raises its flag.  A team works through its range front to back, so the partials of a tile's later K ranges
+      // (the first segments of the following teams) are written long before the owner reaches its last segment: the
+      // owner checks the flags and requests the first chunk of partials while its own MMAs are still running.
+      int sk_contrib = 0;
+      bool sk_part = false;
+      float pre[CH];
+      auto sk_slot = [&](int i) {
+        return p.sk_ws + (size_t)((sk_pair + i * num_m) * 2 + int(rank)) * SK_SLOT_FLOATS + et;
+      };
+      auto sk_prefetch = [&](int c) {
+        const float* src = sk_slot(1) + c * CH * BM_W;
+#pragma unroll
+        for (int j = 0; j < CH; ++j) pre[j] = __ldcg(src + j * BM_W);
+      };
+      if constexpr (!SPLITK && !DUAL) {
+        if (wk.nkb > 0 && !(wk.kb0 == 0 && wk.kb1 == wk.nkb)) {
+          sk_part = wk.kb0 > 0;
+          if (!sk_part) {
+            // owner: the same members of the following teams whose ranges start inside this row hold the rest of its K range
+            const long long row_end_pos = (long long)(wk.row + 1) * wk.nkb;
+            while (sk_team + 1 + sk_contrib < sk_teams &&
+                   sk_total * (sk_team + 1 + sk_contrib) / sk_teams < row_end_pos)
+              ++sk_contrib;
+            if (tid_e == 0) {
+              const uint64_t t0 = wait_ticks();
+              for (int i = 1; i <= sk_contrib; ++i) {
+                const uint32_t* f = p.sk_flags + (sk_pair + i * num_m) * 2 + int(rank);
+                uint32_t spin = 0, v = 0;
+                while (true) {
+                  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                  if (v != 0) break;
+                  if ((++spin & 31u) == 0 && (*abort_flag || wait_expired(t0, p.err))) {
+                    *abort_flag = 1;
+                    set_err(p.err, ERR_FLAG_TIMEOUT, 640);
+                    break;
+                  }
+                }
+              }
+            }
+            asm volatile("bar.sync 3, 256;" ::: "memory");
+            if (sk_contrib > 0) sk_prefetch(grp);
+          }
+        }
+      }
       mbar_wait(&tmem_full_bar[ab], aph, abort_flag, p.err, 630 + ab);
       tc_fence_after();
       const uint32_t lane_addr = tmem_base + ab * ACC_COLS + (uint32_t(q * 32) << 16);
       if constexpr (SPLITK) {
         // the partial stays in TMEM until every CTA of the cluster has finished its MMAs (see below)
         (void)lane_addr;
+        continue;
+      }
+      if (sk_part) {
+        float* dst = p.sk_ws + (size_t)(sk_pair * 2 + int(rank)) * SK_SLOT_FLOATS + et;
+#pragma unroll 1
+        for (int c = grp; c < NCH; c += 2) {
+          uint32_t r[CH];
+          tmem_ld_32x32(lane_addr + c * CH, r);
+          tmem_ld_wait();
+          if (c + 2 >= NCH) {
+            tc_fence_before();
+            mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty_bar[ab]), lead));
+          }
+#pragma unroll
+          for (int j = 0; j < CH; ++j) dst[(c * CH + j) * BM_W] = __uint_as_float(r[j]);
+        }
+        __threadfence();
+        asm volatile("bar.sync 3, 256;" ::: "memory");
+        if (tid_e == 0)
+          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.sk_flags + sk_pair * 2 + int(rank)), "r"(1u) : "memory");
         continue;
       }
       const int n = n0 + et;
@@ -936,6 +1058,16 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         if (c + 2 >= NCH) {
           tc_fence_before();
           mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty_bar[ab]), lead));   // hand the buffer back to the leader's MMA thread
+        }
+        if (sk_contrib > 0) {
+#pragma unroll
+          for (int j = 0; j < CH; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + pre[j]);
+          for (int i = 2; i <= sk_contrib; ++i) {
+            const float* src = sk_slot(i) + c * CH * BM_W;
+#pragma unroll
+            for (int j = 0; j < CH; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldcg(src + j * BM_W));
+          }
+          if (c + 2 < NCH) sk_prefetch(c + 2);       // in flight while this chunk is converted, staged and stored
         }
         epi_values<CH, DUAL>(r, r2, p.out_scale, bias_v, p.act);
         if (p.out_f32) {
@@ -972,6 +1104,13 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           }
           asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
         }
+      }
+      if (sk_contrib > 0) {
+        // every thread has read the partials: lower the flags for the next launch that uses this workspace
+        asm volatile("bar.sync 3, 256;" ::: "memory");
+        if (tid_e == 0)
+          for (int i = 1; i <= sk_contrib; ++i)
+            asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p.sk_flags + (sk_pair + i * num_m) * 2 + int(rank)), "r"(0u) : "memory");
       }
     }
     if (!SPLITK && p.rs_world > 0) {
@@ -1082,7 +1221,64 @@ struct GemmPlan {
   int tail_tiles, tail_splits;
   int pair;
   int tail_units;     // pair plans of a gated GEMM: 1-CTA tiles (128 tokens) that cover the tail's pair tiles
+  int sk;             // pair plans: stream-K schedule (one contiguous range of (tile, k-block) units per pair)
 };
+
+// ---- stream-K workspace: per device, a few lanes (one per stream that launches GEMMs), each with one fp32 slot and one
+// flag per CTA.  Allocated once, outside stream capture; a lane is bound to the first stream that asks for it.
+constexpr int SK_PAIRS_MAX = 80;
+constexpr int SK_LANES = 4;
+constexpr size_t SK_LANE_FLOATS = (size_t)SK_PAIRS_MAX * 2 * SK_SLOT_FLOATS;
+constexpr int SK_LANE_FLAGS = 256;
+struct SkDevice {
+  float* ws = nullptr;
+  uint32_t* flags = nullptr;
+  cudaStream_t owner[SK_LANES] = {};
+  int used = 0;
+  bool failed = false;
+};
+static SkDevice g_sk[UB_MAX_DEVICES];
+static std::mutex g_sk_mu;
+static thread_local bool tl_no_sk = false;     // plan_gemm: leave the stream-K schedule out (no workspace for this stream)
+
+static bool sk_workspace(cudaStream_t st, float** ws, uint32_t** flags) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= UB_MAX_DEVICES) return false;
+  std::lock_guard<std::mutex> lock(g_sk_mu);
+  SkDevice& d = g_sk[dev];
+  if (d.failed) return false;
+  if (d.ws == nullptr) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) {
+      (void)cudaGetLastError();
+      return false;                             // no allocation while a capture is open; the caller plans without it
+    }
+    float* w = nullptr;
+    uint32_t* f = nullptr;
+    if (cudaMalloc(&w, SK_LANES * SK_LANE_FLOATS * sizeof(float)) != cudaSuccess ||
+        cudaMalloc(&f, SK_LANES * SK_LANE_FLAGS * sizeof(uint32_t)) != cudaSuccess ||
+        cudaMemset(f, 0, SK_LANES * SK_LANE_FLAGS * sizeof(uint32_t)) != cudaSuccess) {
+      (void)cudaGetLastError();
+      if (w != nullptr) cudaFree(w);
+      d.failed = true;
+      return false;
+    }
+    d.ws = w;
+    d.flags = f;
+  }
+  int lane = -1;
+  for (int i = 0; i < d.used; ++i)
+    if (d.owner[i] == st) lane = i;
+  if (lane < 0) {
+    if (d.used >= SK_LANES) return false;
+    lane = d.used++;
+    d.owner[lane] = st;
+  }
+  *ws = d.ws + (size_t)lane * SK_LANE_FLOATS;
+  *flags = d.flags + lane * SK_LANE_FLAGS;
+  return true;
+}
 
 // How many thread-block clusters of `csize` CTAs (one CTA per SM, ~200 KB of shared memory each) the device can run at
 // the same time.  A cluster lives inside one GPC, so this is less than SMs / csize: split-K launches that ask for
@@ -1168,6 +1364,7 @@ static GemmPlan plan_gemm(const UbGemmArgs* a) {
   pl.tail_tiles = 0;
   pl.tail_splits = 1;
   pl.tail_units = 0;
+  pl.sk = 0;
   // Two-phase schedule: when the last round of a persistent launch would keep fewer than half of the SMs busy, those
   // tiles run as a second launch with K split over clusters, so the tail costs 1/splits of a tile time.
   if (splits == 1 && !grouped && a->tail_split != 1 && pl.tiles > sms && num_kb >= 16) {
@@ -1223,7 +1420,29 @@ static GemmPlan plan_gemm(const UbGemmArgs* a) {
     const int want_s = a->pair_splits > 0 ? a->pair_splits : s2;
     // short K in a single wave: the narrow 1-CTA tiles chosen above (more CTAs, shorter exposed epilogues) win
     const bool short_single = !dual && num_kb <= 32 && tiles2 <= pairs_now;
-    if (want == 2 || (a->tile_tokens <= 0 && !short_single && ((gains && enough && !(ragged && !dual)) || want_s > 1))) {
+    // Stream-K: teams of pairs take equal shares of the (weight row, k-block) units instead of whole tiles, so a thin
+    // last round or a round that leaves pairs idle costs nothing; the price is one fp32 partial per pair through L2.
+    // Plain GEMMs only (a gated pair tile fills TMEM with its two accumulators, so the partial's read-out would stall
+    // the MMAs; its thin last round goes to the two-phase schedule below), and only where it removes a round: parking
+    // and re-reading a partial costs every pair about as much as 20 k-blocks, so single-round launches with idle
+    // pairs gain nothing (1020 x 4096 x 14336: 90.8 -> 90.3 us, 640 x 4096 x 4096: 32.5 -> 33.1 us), while
+    // 1020 x 6144 x 4096 (96 tiles = 74 + 22) goes from 57.1 to 45.6 us.
+    static int env_sk = -1;
+    if (env_sk < 0) { const char* e = getenv("UB_GEMM_STREAMK"); env_sk = (e != nullptr && e[0] == '0') ? 0 : 1; }
+    bool sk_ok = false;
+    if (env_sk && !tl_no_sk && !dual && want_s <= 1 && a->tile_tokens <= 0 && a->tail_split != 1 && a->rs_world == 0 &&
+        pairs_now <= SK_PAIRS_MAX && pairs_now > 0) {
+      const int num_m2 = (a->M + tn2 - 1) / tn2, num_n2 = (a->N + 2 * BM_W - 1) / (2 * BM_W);
+      const int teams = pairs_now / num_m2;                  // a team = one pair per token tile, in lockstep over K
+      if (teams >= 2) {
+        const long long total = (long long)num_n2 * num_kb;
+        const int now_units = rounds2 * num_kb;
+        const int sk_units = (int)((total + teams - 1) / teams);
+        sk_ok = rounds2 >= 2 && sk_units >= 16 && (now_units - sk_units) * 4 >= now_units;
+      }
+    }
+    if (want == 2 || (a->tile_tokens <= 0 && !short_single &&
+                      ((gains && (enough || sk_ok) && !(ragged && !dual && !sk_ok)) || want_s > 1))) {
       pl.pair = 1;
       pl.tn = tn2;
       pl.tiles = tiles2;
@@ -1237,9 +1456,13 @@ static GemmPlan plan_gemm(const UbGemmArgs* a) {
       // 3 x 74 + 2; 186.9 -> 164.3 us).  Plain GEMMs gain nothing from it: the split launch's fixed cost (cold
       // start, reduction through distributed shared memory, exposed epilogue) is a full round of their shorter tiles
       // (1020 x 6144 x 4096: 54.3 -> 60.2 us).
+      if (sk_ok && pl.splits == 1 && want != 2) {
+        pl.sk = 1;
+        pl.ctas = 2 * pairs_now;
+      }
       static int env_tail = -1;
       if (env_tail < 0) { const char* e = getenv("UB_GEMM_PAIR_TAIL"); env_tail = (e != nullptr && e[0] == '0') ? 0 : 1; }
-      if (env_tail && pl.splits == 1 && a->tile_tokens <= 0 && a->tail_split != 1 && a->rs_world == 0 &&
+      if (!pl.sk && env_tail && pl.splits == 1 && a->tile_tokens <= 0 && a->tail_split != 1 && a->rs_world == 0 &&
           tiles2 > pairs_now && num_kb >= 32) {
         const int num_m2 = (a->M + tn2 - 1) / tn2;
         const int main_t = (((tiles2 / pairs_now) * pairs_now) / num_m2) * num_m2;
@@ -1411,8 +1634,20 @@ extern "C" int ub_gemm_tn(const UbGemmArgs* a, void* stream_v) {
   if (a->K % 8 != 0 || a->ldx % 8 != 0 || a->ldw % 8 != 0) return -2;  // TMA strides must be 16-byte multiples
   if ((reinterpret_cast<uintptr_t>(a->x) & 15) || (reinterpret_cast<uintptr_t>(a->w) & 15)) return -3;
   const bool dual = a->dual != 0;
-  const GemmPlan pl = plan_gemm(a);
+  GemmPlan pl = plan_gemm(a);
   GemmParams p;
+  p.sk_on = 0;
+  p.sk_ws = nullptr;
+  p.sk_flags = nullptr;
+  if (pl.sk) {
+    if (sk_workspace(stream, &p.sk_ws, &p.sk_flags)) {
+      p.sk_on = 1;
+    } else {
+      tl_no_sk = true;
+      pl = plan_gemm(a);
+      tl_no_sk = false;
+    }
+  }
   p.M = a->M; p.N = a->N; p.K = a->K;
   p.out = reinterpret_cast<__nv_bfloat16*>(a->out);
   p.ldo = a->ldo;
@@ -1512,6 +1747,20 @@ extern "C" int ub_gemm_tn(const UbGemmArgs* a, void* stream_v) {
   p.splits = pl.tail_splits;
   return dual ? dispatch_tn<true, true>(pl.tn, tw, tx, p, tail_pl, stream)
               : dispatch_tn<false, true>(pl.tn, tw, tx, p, tail_pl, stream);
+}
+
+// Lowers every stream-K flag of the current device (after a launch that gave up in a bounded wait and may have left
+// some raised).  Ordered on `stream`.
+extern "C" int ub_gemm_streamk_reset(void* stream_v) {
+  using namespace ub;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= UB_MAX_DEVICES) return 0;
+  std::lock_guard<std::mutex> lock(g_sk_mu);
+  if (g_sk[dev].flags == nullptr) return 0;
+  cudaError_t e = cudaMemsetAsync(g_sk[dev].flags, 0, SK_LANES * SK_LANE_FLAGS * sizeof(uint32_t),
+                                  reinterpret_cast<cudaStream_t>(stream_v));
+  return e == cudaSuccess ? 0 : -(int)e;
 }
 
 // Copies the timeline table of the last 1-CTA launches (UB_GEMM_DEBUG bit 4) to `out` ([512][12] uint64, nanoseconds).

@@ -71,6 +71,9 @@ typedef struct UbGemmArgs {
 int ub_gemm_tn(const UbGemmArgs* args, void* stream);
 /* Number of CTAs the launch for `args` will use; each CTA signals every peer once in F1 mode. */
 int ub_gemm_num_ctas(const UbGemmArgs* args);
+/* Lowers the flags of the GEMM's stream-K workspace on the current device; call after a launch reported a timed-out
+ * wait in the error word (a flag raised for a consumer that gave up would otherwise be taken for the next launch's). */
+int ub_gemm_streamk_reset(void* stream);
 
 /* ---------------- K5 : normalisation ---------------- */
 typedef struct UbNormArgs {

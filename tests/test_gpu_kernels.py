@@ -503,31 +503,81 @@ def test_gemm_2cta_splitk(M, N, K, tile, ps):
     assert torch.equal(cuda_ops.gemm_tn(x, w, bias=bias, residual=res, tile_tokens=tile, cta_pair=2, pair_splits=ps), out)
 
 
-@pytest.mark.parametrize("M,N,K,dual", [(1020, 6144, 4096, False), (1020, 6272, 2048, False), (1020, 4864, 2048, True),
-                                        (1000, 4992, 2048, True), (1020, 14336, 4096, True)])
-def test_gemm_pair_two_phase(M, N, K, dual):
-    """The planner's own choice for shapes whose CTA-pair tiles leave a thin last round.  Gated: full rounds on pairs, the
-    weight rows of the rest as 1-CTA tiles of 128 tokens with K split; plain: ragged rounds on pairs.  Ragged token and
-    feature edges; against fp32."""
+def _pair_schedule_case(M, N, K, dual, seed=61):
     from unillm_b200.ops import cuda_ops
 
-    sms = torch.cuda.get_device_properties(0).multi_processor_count
-    x = _rand(M, K, seed=61)
+    x = _rand(M, K, seed=seed)
     if dual:
-        w = _rand(2 * N, K, scale=1 / math.sqrt(K), seed=62)
-        if sms >= 132:
-            assert cuda_ops.gemm_num_ctas(M, N, K, True) > sms          # both launches counted
+        w = _rand(2 * N, K, scale=1 / math.sqrt(K), seed=seed + 1)
         out = cuda_ops.gemm_tn(x, w, dual_rows=N, act="silu")
         g, u = x.float() @ w[:N].float().t(), x.float() @ w[N:].float().t()
         _close(out, torch.nn.functional.silu(g) * u)
         assert torch.equal(cuda_ops.gemm_tn(x, w, dual_rows=N, act="silu"), out)
     else:
-        w = _rand(N, K, scale=1 / math.sqrt(K), seed=62)
-        bias, res = _rand(N, seed=63), _rand(M, N, seed=64)
+        w = _rand(N, K, scale=1 / math.sqrt(K), seed=seed + 1)
+        bias, res = _rand(N, seed=seed + 2), _rand(M, N, seed=seed + 3)
         out = cuda_ops.gemm_tn(x, w, bias=bias, residual=res)
         _close(out, x.float() @ w.float().t() + bias.float() + res.float())
         assert torch.equal(cuda_ops.gemm_tn(x, w, bias=bias, residual=res), out)
+        out32 = cuda_ops.gemm_tn(x, w, out_dtype=torch.float32)
+        _close(out32, x.float() @ w.float().t(), rtol=5e-3, atol=5e-3)
     cuda_ops.check_device_errors()
+
+
+@pytest.mark.parametrize("M,N,K,dual", [(1020, 6144, 4096, False), (1020, 6272, 2048, False), (1020, 4096, 14336, False),
+                                        (640, 4096, 4096, False), (1020, 4864, 2048, True), (1000, 4992, 2048, True),
+                                        (1020, 14336, 4096, True), (508, 14336, 4096, True)])
+def test_gemm_pair_stream_k(M, N, K, dual):
+    """The planner's own choice for shapes whose CTA-pair tiles do not fill whole rounds of the SM pairs.  Plain GEMMs that
+    lose a round that way (the first two shapes) run the stream-K schedule: teams of pairs take equal shares of the
+    (weight row, k-block) units and partial tiles are summed through the fp32 workspace; gated GEMMs run full rounds plus
+    1-CTA tiles with K split for the thin last round.  Ragged token and feature edges, bias / residual / activation
+    epilogues, bf16 and fp32 outputs, repeated launches (the flags are lowered by the owner); against fp32."""
+    _pair_schedule_case(M, N, K, dual)
+
+
+def test_gemm_pair_stream_k_back_to_back():
+    """Different stream-K shapes in one stream share the workspace lane: results must not depend on what ran before."""
+    from unillm_b200.ops import cuda_ops
+
+    shapes = [(1020, 6144, 4096), (640, 4096, 4096), (1020, 6272, 2048)]
+    xs = [_rand(M, K, seed=70 + i) for i, (M, N, K) in enumerate(shapes)]
+    ws = [_rand(N, K, scale=1 / math.sqrt(K), seed=80 + i) for i, (M, N, K) in enumerate(shapes)]
+    first = [cuda_ops.gemm_tn(x, w) for x, w in zip(xs, ws)]
+    for _ in range(3):
+        for i in (2, 0, 1, 1, 0, 2):
+            assert torch.equal(cuda_ops.gemm_tn(xs[i], ws[i]), first[i])
+    for (x, w, o) in zip(xs, ws, first):
+        _close(o, x.float() @ w.float().t())
+    cuda_ops.check_device_errors()
+
+
+def test_gemm_pair_two_phase_without_stream_k():
+    """With the stream-K schedule switched off (the variable is read once per process, hence the child process) the gated
+    GEMM falls back to full rounds on pairs plus 1-CTA tiles with K split for the thin last round."""
+    import os
+    import subprocess
+    import sys
+
+    code = (
+        "import math, torch\n"
+        "from unillm_b200.ops import cuda_ops\n"
+        "g = torch.Generator().manual_seed(5)\n"
+        "M, N, K = 1020, 4864, 2048\n"
+        "x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()\n"
+        "w = (torch.randn(2 * N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).cuda()\n"
+        "sms = torch.cuda.get_device_properties(0).multi_processor_count\n"
+        "assert sms < 132 or cuda_ops.gemm_num_ctas(M, N, K, True) > sms\n"
+        "out = cuda_ops.gemm_tn(x, w, dual_rows=N, act='silu').float()\n"
+        "ref = torch.nn.functional.silu(x.float() @ w[:N].float().t()) * (x.float() @ w[N:].float().t())\n"
+        "err = (out - ref).abs().max().item()\n"
+        "assert err < 0.05, err\n"
+        "cuda_ops.check_device_errors()\n"
+        "print('ok')\n")
+    env = dict(os.environ, UB_GEMM_STREAMK="0")
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300,
+                       cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr
 
 
 @pytest.mark.parametrize("D,Hq,Hkv,Sq,Sk,causal", [(128, 4, 2, 70, 70, True), (128, 4, 4, 33, 50, False), (64, 6, 2, 40, 40, False),

@@ -1216,6 +1216,7 @@ class GpuModelRunner:
         zeroes the arrival counters on every rank -- a collective call, every rank of the group has to make it."""
         torch.cuda.synchronize(self.device)
         K.err_word(self.device).zero_()
+        K.gemm_streamk_reset(self.device)
         for e in self.err_hosts:
             e.zero_()
         if self.tp.comm is not None:

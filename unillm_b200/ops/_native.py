@@ -192,6 +192,8 @@ def cuda_lib() -> C.CDLL:
                 getattr(lib, name).argtypes = [vp, vp]
         lib.ub_gemm_num_ctas.restype = i32
         lib.ub_gemm_num_ctas.argtypes = [vp]
+        lib.ub_gemm_streamk_reset.restype = i32
+        lib.ub_gemm_streamk_reset.argtypes = [vp]
         lib.ub_cuda_error_string.restype = C.c_char_p
         _cuda = lib
         return lib

@@ -43,9 +43,16 @@ def check_device_errors(device=None, reset: bool = True) -> None:
         if code != 0:
             if reset:
                 w.zero_()
+                gemm_streamk_reset(d)
             names = {1: "mbarrier wait timed out", 2: "flag wait timed out (peer or producer missing)",
                      3: "index out of range", 4: "bad argument"}
             raise RuntimeError(f"device error {code} ({names.get(code, '?')}), detail {detail} on {d}")
+
+
+def gemm_streamk_reset(device=None) -> None:
+    """Lowers the flags of the GEMM's stream-K workspace (after a step that reported a timed-out wait)."""
+    with torch.cuda.device(torch.device(device) if device is not None else torch.cuda.current_device()):
+        N_.cuda_lib().ub_gemm_streamk_reset(C.c_void_p(torch.cuda.current_stream().cuda_stream))
 
 
 def _p(t: Optional[torch.Tensor]) -> Optional[int]:
