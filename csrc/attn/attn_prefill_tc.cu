@@ -9,8 +9,13 @@
 //                      into shared memory in the 128-byte-swizzled K-major layout the MMA reads
 //   O_j = P V          tcgen05.mma with V as an MN-major operand straight from the page layout [key][d]
 //   acc = acc * alpha + O_j   in registers of the softmax threads (read back from TMEM)
-// K and V pages (16 keys x 128 d) are gathered through the block table by TMA boxes of {64 d, 16 keys}; Q comes
-// in through a 3-D tensor map (d, head, token) so that the packed-row order is produced by the copy itself.
+// K and V pages (16 keys x 128 d, 4 KB contiguous in the cache) are gathered through the block table with ONE TMA copy
+// per page: the caches are described as 4-D tensors (64 d, 8 keys, 2 halves of d, groups of 8 keys) whose box
+// {64, 8, 2, 2} lands in shared memory as [key group][d half][8 keys][128 B], i.e. as 128-byte-swizzled 8-row atoms with
+// the two d halves of a key group side by side (group stride 2048 B, half stride 1024 B in the MMA descriptors).  With
+// two copies per page (one per d half) the TMA unit was the limit: 32 copies per KV tile, tiles landing about 5 000
+// cycles after their request and the MMA thread waiting 750 - 1 200 cycles per tile for them.  Q comes in through a
+// 3-D tensor map (d, head, token) so that the packed-row order is produced by the copy itself.
 //
 // Handles head_dim 128, page size 16, causal (with offset, for chunked prefill and prefix-cache hits) or
 // bidirectional masks, optional log-sum-exp output for merging partial results.  Sliding windows, ALiBi and other
@@ -53,13 +58,26 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(m), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 
+// UB_ATTN_DEBUG=1: CTA (0, 0, 0) records SM-cycle stamps per KV tile (up to 16 tiles): [tile][0..4] softmax warp 2 (S ready,
+// S in registers, exponentials done, previous P V done, P published), [tile][5..9] MMA thread (K of the next tile landed,
+// its Q K^T issued, V of this tile landed, P half 0 seen, P half 1 seen); read with ub_attn_debug_timeline.
+__device__ unsigned long long g_attn_ts[16][10];
+
 struct Params {
+  int dbg;
   __nv_bfloat16* out;
   float* lse;
   const int* block_tables;
@@ -191,10 +209,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (ok && lane < PPT) {
-          const int row = (blk * p.Hkv + kh) * PAGE;
-          uint8_t* dst = dst_tile + lane * PAGE * 128;
-          tma_load_2d(dst, map, full, 0, row);
-          tma_load_2d(dst + HALF_BYTES, map, full, 64, row);
+          const int row = (blk * p.Hkv + kh) * PAGE;                 // first key row of the page: a multiple of 16
+          tma_load_4d(dst_tile + lane * (PAGE * HD * 2), map, full, 0, 0, 0, row >> 3);
         }
         return ok != 0;
       };
@@ -225,15 +241,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     if (lane == 0 && n_tiles > 0) {
       constexpr uint32_t idesc_qk = make_idesc_bf16(BM, BN, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc_bf16(BM, HD, 0, 1);   // B = V is MN-major ([key][d], d contiguous)
-      const uint32_t q_addr = smem_u32(smem + SMEM_Q), p_addr = smem_u32(smem + SMEM_P);
+      const uint32_t p_addr = smem_u32(smem + SMEM_P);
+      // descriptors are built once and advanced by constants: a dozen dependent scalar instructions per descriptor made
+      // this thread, not the tensor pipe, the limit (about 90 cycles per MMA issued against 64 to execute one)
+      const uint64_t q_desc = make_smem_desc_sw128(smem_u32(smem + SMEM_Q), 16, 1024);
+      const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(smem + SMEM_K), 16, 2048);
+      const uint64_t k_desc2 = make_smem_desc_sw128(smem_u32(smem + SMEM_P), 16, 2048);
+      const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(smem + SMEM_V), 1024, 2048);
       auto issue_qk = [&](int j) {
-        const uint32_t k_addr = smem_u32(k_stage(j % KST));
+        const int st = j % KST;
+        const uint64_t k_desc = st == 2 ? k_desc2 : smem_desc_advance(k_desc0, st * TILE_BYTES);
         const uint32_t d = tmem_s + (j & 1) * BN;
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
-          const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-          umma_bf16_ss(d, make_smem_desc_sw128(q_addr + off, 16, 1024), make_smem_desc_sw128(k_addr + off, 16, 1024),
-                       idesc_qk, k != 0);
+          const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;        // Q: [d half][128 rows][128 B]
+          const uint32_t koff = (k >> 2) * 1024 + (k & 3) * 32;             // K: [key group][d half][8 keys][128 B]
+          umma_bf16_ss(d, smem_desc_advance(q_desc, off), smem_desc_advance(k_desc, koff), idesc_qk, k != 0);
         }
       };
       bool ok = mbar_wait(q_full, 0, abort_flag, p.err, 520);
@@ -245,10 +268,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         umma_commit(&k_empty[0]);
       }
       for (int j = 0; j < n_tiles && ok; ++j) {
+        const bool stamp = p.dbg && j < 16 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
         if (j + 1 < n_tiles) {
           const int jn = j + 1, sn = jn & 1;
           const uint32_t phn = (jn >> 1) & 1;
           if (!mbar_wait(&k_full[jn % KST], (jn / KST) & 1, abort_flag, p.err, 522)) { ok = false; break; }
+          if (stamp) g_attn_ts[j][5] = clock64();
           // S buffer sn: its last readers were the softmax loads of tile j - 1 and, when P lives in TMEM, P V of
           // tile j - 1, which this thread issued before (the tensor pipe runs MMAs in issue order).
           if (!P_TMEM && !mbar_wait(&s_empty[sn], phn ^ 1, abort_flag, p.err, 523)) { ok = false; break; }
@@ -257,20 +282,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           umma_commit(&s_full[sn]);
           umma_commit(&k_empty[jn % KST]);
         }
+        if (stamp) g_attn_ts[j][6] = clock64();
         const int s = j & 1;
         if (!mbar_wait(&v_full[s], (j >> 1) & 1, abort_flag, p.err, 525)) { ok = false; break; }
-        const uint32_t v_addr = smem_u32(smem + SMEM_V + s * TILE_BYTES);
+        if (stamp) g_attn_ts[j][7] = clock64();
+        const uint64_t v_desc = smem_desc_advance(v_desc0, s * TILE_BYTES);
         // The two key halves of the tile are independent softmax streams with their own accumulators: P_h V_h is
         // issued as soon as half h has delivered its probabilities.
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           if (!mbar_wait(&p_full[h], j & 1, abort_flag, p.err, 524 + 10 * h)) { ok = false; break; }
+          if (stamp) g_attn_ts[j][8 + h] = clock64();
           tc_fence_after();
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const int kk = h * 4 + k;                                    // 16-key step inside the tile
-            // B = V, MN-major: 16 keys = two 8-key groups (1024 B apart); the two 64-wide d blocks are 16 KB apart
-            const uint64_t b_desc = make_smem_desc_sw128(v_addr + kk * 16 * 128, HALF_BYTES, 1024);
+            // B = V, MN-major: 16 keys = one page = two 8-key groups (2048 B apart); the two 64-wide d blocks of a
+            // group are 1024 B apart
+            const uint64_t b_desc = smem_desc_advance(v_desc, kk * (PAGE * HD * 2));
             const uint32_t accumulate = (j > 0 || k != 0) ? 1u : 0u;     // O stays in TMEM over all KV tiles
             if (P_TMEM) {
               // A = P in tensor memory: packed bf16 pairs over the first 32 columns of this half's S columns
@@ -317,6 +346,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     for (int j = 0; j < n_tiles; ++j) {
       const int b = j & 1;
       ok = ok && wait_all(&s_full[b], (j >> 1) & 1, 530);
+      const bool stamp = p.dbg && warp == 2 && lane == 0 && j < 16 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+      if (stamp) g_attn_ts[j][0] = clock64();
       tc_fence_after();
       const uint32_t s_addr = tmem_s + b * BN + half * 64 + lane_off;      // this half's 64 S columns
       const int key0 = (tile0 + j) * BN + half * 64;
@@ -326,6 +357,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       tmem_ld_32x32(s_addr, sv[0]);
       tmem_ld_32x32(s_addr + 32, sv[1]);
       tmem_ld_wait();
+      if (stamp) g_attn_ts[j][1] = clock64();
       if (!P_TMEM) {
         tc_fence_before();
         mbar_arrive(&s_empty[b]);
@@ -374,6 +406,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           packed[c * 16 + i] = pack_bf16x2(p0, p1);
         }
       }
+      if (stamp) g_attn_ts[j][2] = clock64() + (packed[0] & 0u);      // after the exponentials (data dependence keeps it there)
       if (P_TMEM) {
         // 64 keys = 32 packed columns, written over the head of this half's own S columns (already in registers)
         tmem_st_32x32(s_addr, packed);
@@ -402,10 +435,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           tmem_st_32x32(o_mine + c * 32, r);
         }
       }
+      if (stamp) g_attn_ts[j][3] = clock64();
       tmem_st_wait();
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(&p_full[half]);
+      if (stamp) g_attn_ts[j][4] = clock64();
     }
     // Merge of the two streams.  MMAs complete in issue order, so once this half's last P V has completed the other
     // half's barrier is at most one phase behind and its parity wait cannot alias.
@@ -546,7 +581,7 @@ static int encode(CUtensorMap* out, const void* base, int rank, const cuuint64_t
                   const cuuint32_t* box) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return -1;
-  cuuint32_t estr[3] = {1, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), dims, strides_bytes, box,
                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -587,16 +622,22 @@ extern "C" int ub_attn_prefill_tc(const UbAttnArgs* a, void* stream_v) {
     if (rc != 0) return rc;
   }
   {
-    // K / V caches viewed as rows of 128 d: row = (block * Hkv + kv head) * 16 + slot
-    cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)a->num_blocks * a->Hkv * PAGE};
-    cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
-    cuuint32_t box[2] = {64, PAGE};
-    int rc = encode(&tk, a->k_cache, 2, dims, strides, box);
+    // K / V caches: key row r = (block * Hkv + kv head) * 16 + slot is 256 B; viewed as (64 d, 8 keys, 2 d halves, r / 8)
+    // so that one box {64, 8, 2, 2} is a whole page, delivered as swizzled 8-key atoms with the d halves side by side
+    cuuint64_t dims[4] = {64, 8, 2, (cuuint64_t)a->num_blocks * a->Hkv * PAGE / 8};
+    cuuint64_t strides[3] = {(cuuint64_t)HD * 2, 128, (cuuint64_t)HD * 2 * 8};
+    cuuint32_t box[4] = {64, 8, 2, 2};
+    int rc = encode(&tk, a->k_cache, 4, dims, strides, box);
     if (rc != 0) return rc;
-    rc = encode(&tv, a->v_cache, 2, dims, strides, box);
+    rc = encode(&tv, a->v_cache, 4, dims, strides, box);
     if (rc != 0) return rc;
   }
   Params p;
+  {
+    static int dbg = -1;
+    if (dbg < 0) { const char* e = getenv("UB_ATTN_DEBUG"); dbg = e ? atoi(e) : 0; }
+    p.dbg = dbg;
+  }
   p.out = reinterpret_cast<__nv_bfloat16*>(a->out);
   p.lse = a->lse;
   p.block_tables = a->block_tables;
@@ -654,5 +695,11 @@ extern "C" int ub_attn_prefill_tc(const UbAttnArgs* a, void* stream_v) {
                a->Hq, p.out, (long long)a->o_stride, a->lse);
     e = cudaGetLastError();
   }
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+// Copies the per-tile stamps of the last launch made under UB_ATTN_DEBUG=1 to `out` ([16][10] uint64, SM cycles).
+extern "C" int ub_attn_debug_timeline(unsigned long long* out) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, ub::atc::g_attn_ts, sizeof(unsigned long long) * 16 * 10);
   return e == cudaSuccess ? 0 : -(int)e;
 }

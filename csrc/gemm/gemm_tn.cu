@@ -490,6 +490,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_bf16(BM_W, TN, 0, 0);
+      const uint64_t desc_base = make_smem_desc_sw128(smem_u32(smem), 16, 1024);     // stage 0, k-step 0 of the weight tile
       int it = 0, ui = 0;
       bool dead = false;
       for (int u = unit_begin; u < total_tiles && !dead; u += unit_step) {
@@ -506,18 +507,15 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
           if (!mbar_wait(&full_bar[s], ph, abort_flag, p.err, 200 + s)) { dead = true; break; }
           if (it == 0) ts_mark(p, 2);
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + s * S::STAGE_BYTES);
-          const uint32_t b_addr = a_addr + (DUAL ? 2 : 1) * S::A_BYTES;
+          const uint64_t adesc0 = smem_desc_advance(desc_base, uint32_t(s) * S::STAGE_BYTES);
+          const uint64_t bdesc0 = smem_desc_advance(adesc0, (DUAL ? 2 : 1) * S::A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t bdesc = make_smem_desc_sw128(b_addr + k * UMMA_K * 2, 16, 1024);
-            const uint64_t adesc = make_smem_desc_sw128(a_addr + k * UMMA_K * 2, 16, 1024);
+            const uint64_t bdesc = smem_desc_advance(bdesc0, k * UMMA_K * 2);
+            const uint64_t adesc = smem_desc_advance(adesc0, k * UMMA_K * 2);
             const uint32_t acc = (kb != kb0 || k != 0) ? 1u : 0u;
             umma_bf16_ss(d_tmem, adesc, bdesc, idesc, acc);
-            if (DUAL) {
-              const uint64_t a2desc = make_smem_desc_sw128(a_addr + S::A_BYTES + k * UMMA_K * 2, 16, 1024);
-              umma_bf16_ss(d_tmem + TN, a2desc, bdesc, idesc, acc);
-            }
+            if (DUAL) umma_bf16_ss(d_tmem + TN, smem_desc_advance(adesc, S::A_BYTES), bdesc, idesc, acc);
           }
           umma_commit(&empty_bar[s]);  // stage is free once these MMAs have read it
         }
@@ -912,6 +910,7 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     // ------------------------------ MMA issuer (leader CTA only) ------------------------------
     if (lane == 0 && leader) {
       constexpr uint32_t idesc = make_idesc_bf16(2 * BM_W, TN, 0, 0);
+      const uint64_t desc_base = make_smem_desc_sw128(smem_u32(smem), 16, 1024);     // stage 0, k-step 0 of the weight tile
       int it = 0, ui = 0;
       bool dead = false;
       for (PairWalk wk = walk0; wk.valid() && !dead; wk.next()) {
@@ -927,18 +926,15 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&full_bar[s], ph, abort_flag, p.err, 620 + s)) { dead = true; break; }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + s * S::STAGE_BYTES);
-          const uint32_t b_addr = a_addr + (DUAL ? 2 : 1) * S::A_BYTES;
+          const uint64_t adesc0 = smem_desc_advance(desc_base, uint32_t(s) * S::STAGE_BYTES);
+          const uint64_t bdesc0 = smem_desc_advance(adesc0, (DUAL ? 2 : 1) * S::A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t bdesc = make_smem_desc_sw128(b_addr + k * UMMA_K * 2, 16, 1024);
-            const uint64_t adesc = make_smem_desc_sw128(a_addr + k * UMMA_K * 2, 16, 1024);
+            const uint64_t bdesc = smem_desc_advance(bdesc0, k * UMMA_K * 2);
+            const uint64_t adesc = smem_desc_advance(adesc0, k * UMMA_K * 2);
             const uint32_t acc = (kb != kb0 || k != 0) ? 1u : 0u;
             umma_bf16_ss_cg2(d_tmem, adesc, bdesc, idesc, acc);
-            if (DUAL) {
-              const uint64_t a2desc = make_smem_desc_sw128(a_addr + S::A_BYTES + k * UMMA_K * 2, 16, 1024);
-              umma_bf16_ss_cg2(d_tmem + TN, a2desc, bdesc, idesc, acc);
-            }
+            if (DUAL) umma_bf16_ss_cg2(d_tmem + TN, smem_desc_advance(adesc, S::A_BYTES), bdesc, idesc, acc);
           }
           // the stage is free in BOTH CTAs once these MMAs have read it
           const uint32_t eb = smem_u32(&empty_bar[s]);

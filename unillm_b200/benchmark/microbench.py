@@ -242,6 +242,26 @@ def bench_attn(results, case="all"):
                  peaks=how)
         results.append(r)
         print(json.dumps(r))
+        if os.environ.get("UB_ATTN_DEBUG"):
+            # per-tile stamps of CTA (0, 0, 0) of the last launch, SM cycles relative to the first stamp
+            import ctypes as C
+
+            import numpy as np
+
+            from ..ops._native import cuda_lib
+
+            buf = np.zeros((16, 10), dtype=np.uint64)
+            rc = cuda_lib().ub_attn_debug_timeline(buf.ctypes.data_as(C.c_void_p))
+            if rc != 0 or not buf.any():
+                print(json.dumps(dict(kind="attn_prefill_timeline", error=f"nothing recorded (rc {rc})")))
+            else:
+                t = buf.astype(np.int64)[: min(16, (ctx + 127) // 128)]
+                t0 = t[t > 0].min()
+                names = ["S ready", "S in registers", "exponentials done", "previous PV done", "P published",
+                         "next K landed", "next QK issued", "V landed", "P half 0 seen", "P half 1 seen"]
+                tl = {n: [int(t[j, k] - t0) if t[j, k] > 0 else None for j in range(min(16, (ctx + 127) // 128))]
+                      for k, n in enumerate(names)}
+                print(json.dumps(dict(kind="attn_prefill_timeline", T=T, ctx=ctx, cycles=tl)))
 
 
 def bench_fused_emulated(results, world=8, batch=512, only=None):
