@@ -76,6 +76,32 @@ __device__ __forceinline__ float ex2_approx(float x) {
 // its Q K^T issued, V of this tile landed, P half 0 seen, P half 1 seen); read with ub_attn_debug_timeline.
 __device__ unsigned long long g_attn_ts[16][10];
 
+// Two fp32 values per instruction (fma.rn.f32x2 / add.f32x2) and a three-input maximum: the softmax of a KV tile is
+// bound by the instruction issue of its warps, and these cut a third of its arithmetic instructions.
+__device__ __forceinline__ uint64_t pack_f32x2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 struct Params {
   int dbg;
   __nv_bfloat16* out;
@@ -368,7 +394,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 #pragma unroll
         for (int c = 0; c < 2; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
+          for (int i = 0; i < 32; i += 2)
+            mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
       } else {
 #pragma unroll
         for (int c = 0; c < 2; ++c)
@@ -389,23 +416,28 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         // this half of the single P buffer in shared memory is free once P_h V_h of the previous tile has completed
         ok = ok && wait_all(&o_full[half], (j - 1) & 1, 531);
       }
-      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint64_t ps2[2] = {0ull, 0ull};                  // two chains of two packed row sums
+      const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), nm2 = pack_f32x2(-m_use, -m_use);
       uint32_t packed[32];
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float p0 = ex2_approx(fmaf(__uint_as_float(sv[c][2 * i]), p.scale_log2, -m_use));
-          float p1 = ex2_approx(fmaf(__uint_as_float(sv[c][2 * i + 1]), p.scale_log2, -m_use));
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[c][2 * i]), __uint_as_float(sv[c][2 * i + 1])), sc2, nm2), x0, x1);
+          float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
           if (!full) {
             const int k0 = key0 + c * 32 + 2 * i;
             if (!(k0 < limit && k0 >= kv_lo)) p0 = 0.f;
             if (!(k0 + 1 < limit && k0 + 1 >= kv_lo)) p1 = 0.f;
           }
-          ps4[i & 3] += p0 + p1;
+          ps2[i & 1] = add_f32x2(ps2[i & 1], pack_f32x2(p0, p1));
           packed[c * 16 + i] = pack_bf16x2(p0, p1);
         }
       }
+      float ps4[4];
+      unpack_f32x2(ps2[0], ps4[0], ps4[1]);
+      unpack_f32x2(ps2[1], ps4[2], ps4[3]);
       if (stamp) g_attn_ts[j][2] = clock64() + (packed[0] & 0u);      // after the exponentials (data dependence keeps it there)
       if (P_TMEM) {
         // 64 keys = 32 packed columns, written over the head of this half's own S columns (already in registers)
