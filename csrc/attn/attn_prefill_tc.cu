@@ -76,32 +76,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
 // its Q K^T issued, V of this tile landed, P half 0 seen, P half 1 seen); read with ub_attn_debug_timeline.
 __device__ unsigned long long g_attn_ts[16][10];
 
-// Two fp32 values per instruction (fma.rn.f32x2 / add.f32x2) and a three-input maximum: the softmax of a KV tile is
-// bound by the instruction issue of its warps, and these cut a third of its arithmetic instructions.
-__device__ __forceinline__ uint64_t pack_f32x2(float a, float b) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
-  return r;
-}
-__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& a, float& b) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
-}
-__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("add.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ float max3(float a, float b, float c) {
-  float d;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-  return d;
-}
-
 struct Params {
   int dbg;
   __nv_bfloat16* out;

@@ -122,6 +122,37 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 // compiler evaluate every branch (erf, tanh, exp ...) for every value, which dominated the epilogue.
 template <int N, bool DUAL, int ACT>
 __device__ __forceinline__ void epi_values_t(uint32_t (&r)[N], const uint32_t (&r2)[N], float scale, float bias_v) {
+  // The two hot forms run on packed fp32x2 instructions (the epilogue warps are bound by instruction issue):
+  // silu(gate) * up with sigmoid(v) = 0.5 * (1 + tanh(v / 2)), four instructions per value instead of seven, and the
+  // plain scale-and-bias as one multiply-add per two values.
+  if constexpr (DUAL && ACT == UB_ACT_SILU) {
+    const uint64_t s2 = pack_f32x2(scale, scale), h2 = pack_f32x2(0.5f, 0.5f);
+#pragma unroll
+    for (int j = 0; j < N; j += 2) {
+      const uint64_t g = mul_f32x2(pack_f32x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), s2);
+      const uint64_t u = mul_f32x2(pack_f32x2(__uint_as_float(r2[j]), __uint_as_float(r2[j + 1])), s2);
+      float a0, a1, t0, t1, o0, o1;
+      unpack_f32x2(mul_f32x2(g, h2), a0, a1);
+      asm("tanh.approx.f32 %0, %1;" : "=f"(t0) : "f"(a0));
+      asm("tanh.approx.f32 %0, %1;" : "=f"(t1) : "f"(a1));
+      const uint64_t sig = fma_f32x2(pack_f32x2(t0, t1), h2, h2);
+      unpack_f32x2(mul_f32x2(mul_f32x2(g, sig), u), o0, o1);
+      r[j] = __float_as_uint(o0);
+      r[j + 1] = __float_as_uint(o1);
+    }
+    return;
+  }
+  if constexpr (!DUAL && ACT == UB_ACT_NONE) {
+    const uint64_t s2 = pack_f32x2(scale, scale), b2 = pack_f32x2(bias_v, bias_v);
+#pragma unroll
+    for (int j = 0; j < N; j += 2) {
+      float o0, o1;
+      unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), s2, b2), o0, o1);
+      r[j] = __float_as_uint(o0);
+      r[j + 1] = __float_as_uint(o1);
+    }
+    return;
+  }
 #pragma unroll
   for (int j = 0; j < N; ++j) {
     float v = __uint_as_float(r[j]) * scale;
@@ -536,6 +567,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     const bool vec_ok = (p.N % 8 == 0) && (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
                         (p.residual == nullptr ||
                          ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
+    const bool raw_ok = vec_ok && p.residual == nullptr && p.rs_world == 0 && !p.out_f32;
     int ui = 0;
     for (int u = unit_begin; u < total_tiles; u += unit_step) {
       const TileCoord tc = tile_coord(p, u, num_m, TN);
@@ -605,6 +637,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             for (int idx = tid_g; idx < CH * 16; idx += 128) {
               const int tok = idx >> 4, c8 = idx & 15;
               const uint4 raw = *reinterpret_cast<const uint4*>(stb + tok * BM_W + c8 * 8);
+              if (raw_ok) {
+                // nothing to add and a local bf16 destination: the staged 16 bytes are the output bytes
+                const int m = m0 + c * CH + tok, nn = n0 + c8 * 8;
+                if (m < m_end && nn < p.N) *reinterpret_cast<uint4*>(p.out + (long long)m * p.ldo + nn) = raw;
+                continue;
+              }
               const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
               float v[8];
 #pragma unroll
@@ -959,6 +997,7 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     const bool vec_ok = (p.N % 8 == 0) && (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
                         (p.residual == nullptr ||
                          ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
+    const bool raw_ok = vec_ok && p.residual == nullptr && p.rs_world == 0 && !p.out_f32;
     int ui = 0;
     for (PairWalk wk = walk0; wk.valid(); wk.next()) {
       const int u = wk.u;
@@ -1092,6 +1131,12 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           for (int idx = tid_g; idx < CH * 16; idx += 128) {
             const int tok = idx >> 4, c8 = idx & 15;
             const uint4 raw = *reinterpret_cast<const uint4*>(stb + tok * BM_W + c8 * 8);
+            if (raw_ok) {
+              // nothing to add and a local bf16 destination: the staged 16 bytes are the output bytes
+              const int m = m0 + c * CH + tok, nn = n0 + c8 * 8;
+              if (m < p.M && nn < p.N) *reinterpret_cast<uint4*>(p.out + (long long)m * p.ldo + nn) = raw;
+              continue;
+            }
             const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
             float v[8];
 #pragma unroll
