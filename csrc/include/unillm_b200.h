@@ -71,6 +71,10 @@ typedef struct UbGemmArgs {
 int ub_gemm_tn(const UbGemmArgs* args, void* stream);
 /* Number of CTAs the launch for `args` will use; each CTA signals every peer once in F1 mode. */
 int ub_gemm_num_ctas(const UbGemmArgs* args);
+/* Shared-memory fill-rate probe (csrc/common/fill_probe.cu): one CTA per SM brings `steps` 16 KB tiles of the bf16 matrix
+ * buf[rows][K] into shared memory; mode 0 linear bulk copies, 1 tensor-map tiles of the row-major matrix, 2 tensor-map
+ * tiles stored contiguously.  cycles: int64 per SM.  Returns the number of CTAs, negative on error. */
+int ub_fill_probe(const void* buf, int rows, int K, int mode, int steps, int* err, long long* cycles, void* stream);
 /* Lowers the flags of the GEMM's stream-K workspace on the current device; call after a launch reported a timed-out
  * wait in the error word (a flag raised for a consumer that gave up would otherwise be taken for the next launch's). */
 int ub_gemm_streamk_reset(void* stream);

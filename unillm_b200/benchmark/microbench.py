@@ -264,6 +264,42 @@ def bench_attn(results, case="all"):
                 print(json.dumps(dict(kind="attn_prefill_timeline", T=T, ctx=ctx, cycles=tl)))
 
 
+def bench_fill(results):
+    """Rate at which an SM fills its shared memory from L2 with 16 KB operand tiles: linear bulk copies against the
+    tensor-map tile copies the GEMM producers issue (``csrc/common/fill_probe.cu``)."""
+    import ctypes as C
+
+    from ..ops._native import cuda_lib
+
+    lib = cuda_lib()
+    lib.ub_fill_probe.restype = C.c_int
+    lib.ub_fill_probe.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+    rows, K, steps = 6144, 4096, 512                           # 50 MB: stays in L2
+    buf = torch.ones(rows, K, device="cuda", dtype=torch.bfloat16)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    cyc = torch.zeros(sms, dtype=torch.int64, device="cuda")
+    err = cuda_ops.err_word("cuda")
+    names = ["linear bulk copy, 16 KB contiguous", "tensor-map tile {64, 128}, row pitch 8 KB", "tensor-map tile {64, 128}, tiles contiguous"]
+    for mode in range(3):
+        best = None
+        for _ in range(4):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            n = lib.ub_fill_probe(buf.data_ptr(), rows, K, mode, steps, err.data_ptr(), cyc.data_ptr(),
+                                  C.c_void_p(torch.cuda.current_stream().cuda_stream))
+            e1.record()
+            torch.cuda.synchronize()
+            if n <= 0:
+                raise RuntimeError(f"ub_fill_probe failed: {n}")
+            ms = e0.elapsed_time(e1)
+            best = ms if best is None else min(best, ms)
+        cuda_ops.check_device_errors()
+        r = dict(kind="smem_fill", mode=names[mode], ctas=n, tile_bytes=16384, tiles_per_cta=steps, us=best * 1e3,
+                 tb_per_s=n * steps * 16384 / best / 1e9, bytes_per_clk_per_sm=16384.0 * steps / float(cyc.float().mean()))
+        results.append(r)
+        print(json.dumps(r))
+
+
 def bench_fused_emulated(results, world=8, batch=512, only=None):
     """The fused tensor-parallel kernels of one layer at the serving step's per-rank shapes, with all ``world`` ranks
     emulated on ONE GPU: the peers' buffers are plain local tensors, the chain runs once for every rank (producers before
@@ -497,7 +533,7 @@ def bench_tp_layer(results, world=8, batch=512, variants=False):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", nargs="?", default="all", choices=["gemm", "attn", "norm", "tp", "quant", "fused", "all"])
+    ap.add_argument("what", nargs="?", default="all", choices=["gemm", "attn", "norm", "tp", "quant", "fused", "fill", "all"])
     ap.add_argument("--fused-case", default=None, help="fused only: run just this kernel a few times (for a profiler)")
     ap.add_argument("--world", type=int, default=8, help="tp only: tensor-parallel size whose per-rank shapes are timed")
     ap.add_argument("--batch", type=int, default=512, help="tp only: concurrent sequences of the serving step")
@@ -525,6 +561,8 @@ def main(argv=None):
         bench_quant(results)
     if a.what == "fused":
         bench_fused_emulated(results, a.world, a.batch, a.fused_case)
+    if a.what == "fill":
+        bench_fill(results)
     if a.json:
         os.makedirs(os.path.dirname(a.json) or ".", exist_ok=True)
         Path(a.json).write_text(json.dumps(results, indent=1))
