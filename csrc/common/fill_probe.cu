@@ -8,8 +8,9 @@
 // L2-resident buffer.  Every wait is bounded; a timed-out wait is reported in err[0].  Measured on B200 inside this
 // library: 31 - 34 B per clock and SM for all three modes, i.e. the address pattern and the kind of copy do not matter
 // at this depth; what does is the number of bytes in flight over the L2 round trip of about 3 000 cycles under load (a
-// stand-alone build of mode 0 with 32 KB copies, 192 KB in flight, reached 70 B per clock).  A GEMM stage ring of
-// 192 KB therefore cannot pull much more than it does (34.5 B per clock and SM on the plain projections).
+// stand-alone build of mode 0 with 32 KB copies, 192 KB in flight, reached 70 B per clock).  The plain GEMMs pull
+// 34.5 B per clock and SM whether they hold five or six stages, so they meet a chip-wide limit (about 9 TB/s for
+// their mix of L2 and HBM traffic) rather than this depth limit.
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
