@@ -242,8 +242,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       constexpr uint32_t idesc_qk = make_idesc_bf16(BM, BN, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc_bf16(BM, HD, 0, 1);   // B = V is MN-major ([key][d], d contiguous)
       const uint32_t p_addr = smem_u32(smem + SMEM_P);
-      // descriptors are built once and advanced by constants: a dozen dependent scalar instructions per descriptor made
-      // this thread, not the tensor pipe, the limit (about 90 cycles per MMA issued against 64 to execute one)
+      // descriptors are built once and advanced by constants (the issue of the eight Q K^T MMAs takes about 700 cycles
+      // either way: it proceeds at the pace of the tensor pipe)
       const uint64_t q_desc = make_smem_desc_sw128(smem_u32(smem + SMEM_Q), 16, 1024);
       const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(smem + SMEM_K), 16, 2048);
       const uint64_t k_desc2 = make_smem_desc_sw128(smem_u32(smem + SMEM_P), 16, 2048);

@@ -245,9 +245,9 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
 }
 
 // The descriptor of the same layout `bytes` further into shared memory (bytes % 16 == 0; the 14-bit address field must
-// not overflow, i.e. the operand stays inside the 256 KB window).  One add instead of rebuilding the descriptor: the
-// MMA-issuing thread runs a dependent scalar instruction chain per MMA, and at 64 tensor-pipe cycles per 128 x 128 x 16
-// MMA a dozen instructions per descriptor make the issue, not the pipe, the limit.
+// not overflow, i.e. the operand stays inside the 256 KB window).  One add instead of rebuilding the descriptor keeps
+// the scalar instruction chain of the MMA-issuing thread short (measured: no effect on the kernels' times, because the
+// issue of an MMA waits for the tensor pipe anyway; kept for the shorter code).
 __device__ __forceinline__ uint64_t smem_desc_advance(uint64_t desc, uint32_t bytes) { return desc + uint64_t(bytes >> 4); }
 
 // TMEM -> registers: 32 lanes x 32 consecutive 32-bit columns; thread i of the warp reads lane (base_lane + i).

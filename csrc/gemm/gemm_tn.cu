@@ -72,8 +72,8 @@ struct GemmParams {
   int grp_max_tiles;  // token-tile slots in the table
   int grp_w_rows;     // rows of w per expert; expert e's weights are rows [e*grp_w_rows, (e+1)*grp_w_rows)
   int tile_begin, tile_end;   // work units of this launch; tile_end == 0 means all
-  // Stream-K schedule of the CTA-pair kernel (sk_on != 0): the (tile, k-block) space is cut into one contiguous range
-  // per pair; partial tiles are summed through sk_ws (fp32, one slot per CTA) under the flags sk_flags (one per CTA).
+  // Stream-K schedule of the CTA-pair kernel (sk_on != 0, see PairWalk): teams of pairs take equal shares of the (weight
+  // row, k-block) space; partial tiles are summed through sk_ws (fp32, one slot per CTA) under sk_flags (one per CTA).
   int sk_on;
   float* sk_ws;
   uint32_t* sk_flags;
