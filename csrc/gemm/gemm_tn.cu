@@ -896,6 +896,9 @@ gemm_tn_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   cluster_sync_all();                              // barriers of both CTAs are initialised before anyone uses them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Programmatic dependent launch (see gemm_tn_kernel): TMEM and barriers are set up, nothing global has been touched.
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) ------------------------------
